@@ -1,0 +1,391 @@
+#!/usr/bin/env python
+"""Benchmark of the block-quantized decode GEMV path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--no-sweep]
+
+Headline workload (config.workload): the Q4_K 4096x4096 matvec (x fp32 [1,4096], y fp32 [1,4096]),
+the configuration the metric "Q4_K GEMV HBM GB/s" is quoted on.  One matrix is 9.4 MB and would sit in
+the 126 MB L2, so a STEP is one pass over ROT = 64 device copies of the matrix at distinct addresses
+(604 MB, > 4x L2): every launch streams its weights from HBM.  GB/s = ROT * 9 469 952 B / step time
+(algorithmic bytes: packed weights + x + y).
+
+  value     device-resident: one CUDA graph per step holding ROT x (quantise x -> int8, GEMV)
+  roofline  the GEMV kernel alone on pre-quantised activations, timed live with CUDA events on the
+            library's stream, against the measured HBM copy bandwidth in MEASURED_PEAKS.json
+  e2e       the same pass through the Backend interface with HOST buffers: per matrix, upload x from
+            pinned memory, execute a one-Linear plan, download y to pinned memory
+  sweep     (N=1) the other GEMV configurations: Q6_K 14336x4096 and ternary Q2_0 4096x14336 at
+            batch 1/4/8, Q4_K 14336x4096; each rotated over > 4x L2 of distinct copies
+  cpu_baseline  the CPU restatement of infr-cpu on the host cores, bounded sample (N=1, rank 0)
+
+--impl reference times the CPU restatement of infr-cpu (the reference is Rust; no Rust toolchain
+exists here, so its own binary cannot be built) on all host threads on the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+IN_F = OUT_F = 4096
+ROT = 64
+C1_BYTES = 4096 * 4096 // 256 * 144 + 4 * 4096 + 4 * 4096  # 9 469 952
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a timed region runs."""
+
+    BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)))
+                r = int(self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                for bit, name in self.BITS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nv:
+            self._stop.clear()
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        if self._thr:
+            self._stop.set()
+            self._thr.join()
+            self._thr = None
+
+    def summary(self):
+        med = int(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def _dist_setup(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist_
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if torch.cuda.is_available():
+            torch.cuda.set_device(local)
+            dist_.init_process_group("nccl", device_id=torch.device("cuda", local))
+        else:
+            dist_.init_process_group("gloo")
+        dist = dist_
+    return rank, world, local, dist
+
+
+def _barrier(dist):
+    if dist is not None:
+        dist.barrier()
+
+
+def _max_over_ranks(dist, v: float) -> float:
+    if dist is None:
+        return v
+    import torch
+
+    t = torch.tensor([v], dtype=torch.float64, device="cuda" if torch.cuda.is_available() else "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# ------------------------------------------------------------------------------------------------
+def _rotation(be, infr_b200, dtype, out_f, in_f, seed, min_bytes):
+    """Distinct device copies of one seeded weight; returns (buffers, host bytes)."""
+    from infr_b200 import synth
+
+    w = synth.weight(dtype, out_f, in_f, seed)
+    n = max(2, int(np.ceil(min_bytes / w.nbytes)))
+    first = be.from_numpy(w, infr_b200.USAGE_WEIGHTS)
+    bufs = [first]
+    for _ in range(n - 1):
+        b = be.alloc_uninit(w.nbytes, infr_b200.USAGE_WEIGHTS)
+        be.copy_buffer(first, b, w.nbytes)
+        bufs.append(b)
+    be.sync()
+    return bufs, w
+
+
+def _time_graph(be, graph, steps, warmup, dist=None):
+    for _ in range(warmup):
+        graph.launch()
+    be.sync()
+    _barrier(dist)
+    be.timer_start()
+    for _ in range(steps):
+        graph.launch()
+    ms = be.timer_stop()
+    return ms
+
+
+def _gemv_case(be, infr_b200, dtype, out_f, in_f, m, seed, steps, warmup, l2_bytes, hbm_peak):
+    """GB/s of quantise+GEMV and of the GEMV kernel alone for one configuration (rotated weights)."""
+    from infr_b200 import synth
+
+    bufs, w = _rotation(be, infr_b200, dtype, out_f, in_f, seed, 4 * l2_bytes + (64 << 20))
+    rot = len(bufs)
+    x = synth.normal(seed + 1, (m, in_f))
+    xb = be.from_numpy(x)
+    ys = [be.alloc(m * out_f * 4) for _ in range(rot)]
+    gran = 32 if dtype == infr_b200.Q2_0 else 256
+    qs, d = be.alloc(m * in_f), be.alloc(m * (in_f // gran) * 4)
+    s32, s16 = be.alloc(m * (in_f // 32) * 4), be.alloc(m * (in_f // 16) * 4)
+    be.gemv(dtype, bufs[0], xb, ys[0], m, in_f, out_f)  # warm the scratch before capture
+    be.quantize_q8(gran, xb, m, in_f, qs, d, s32, s16 if gran == 256 else None)
+    be.capture_begin()
+    for i in range(rot):
+        be.gemv(dtype, bufs[i], xb, ys[i], m, in_f, out_f)
+    g_full = be.capture_end()
+    be.capture_begin()
+    for i in range(rot):
+        be.gemv_q8(dtype, bufs[i], qs, d, s32, s16 if dtype == infr_b200.Q6K else None, ys[i], m, in_f, out_f)
+    g_kern = be.capture_end()
+    ms_full = _time_graph(be, g_full, steps, warmup)
+    ms_kern = _time_graph(be, g_kern, steps, warmup)
+    alg = w.nbytes + 4 * m * in_f + 4 * m * out_f
+    res = {
+        "workload": f"{synth.DTYPE_NAMES[dtype]} GEMV W {out_f}x{in_f} m={m}, {rot} distinct copies rotated",
+        "alg_bytes_per_launch": alg,
+        "gbs": alg * rot * steps / (ms_full * 1e-3) / 1e9,
+        "kernel_us": ms_kern * 1e3 / (steps * rot),
+        "kernel_gbs": alg * rot * steps / (ms_kern * 1e-3) / 1e9,
+    }
+    res["kernel_frac_of_measured_hbm"] = res["kernel_gbs"] / hbm_peak
+    for g in (g_full, g_kern):
+        g.close()
+    for b in bufs + ys + [xb, qs, d, s32, s16]:
+        b.close()
+    return res
+
+
+# ------------------------------------------------------------------------------------------------
+def run_b200(args):
+    import infr_b200
+    from infr_b200 import synth
+
+    rank, world, local, dist = _dist_setup(args.gpus)
+    hbm_peak, peak_src = _peaks()
+    be = infr_b200.CudaBackend(device=local)
+    caps = be.capabilities()
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    w = synth.weight(infr_b200.Q4K, OUT_F, IN_F, seed=0)
+    x = synth.normal(1, (1, IN_F))
+    first = be.from_numpy(w, infr_b200.USAGE_WEIGHTS)
+    ws = [first]
+    for _ in range(ROT - 1):
+        b = be.alloc_uninit(w.nbytes, infr_b200.USAGE_WEIGHTS)
+        be.copy_buffer(first, b, w.nbytes)
+        ws.append(b)
+    xb = be.from_numpy(x)
+    ys = [be.alloc(OUT_F * 4) for _ in range(ROT)]
+    qs, d, s32 = be.alloc(IN_F), be.alloc(IN_F // 256 * 4), be.alloc(IN_F // 32 * 4)
+    be.gemv(infr_b200.Q4K, ws[0], xb, ys[0], 1, IN_F, OUT_F)
+    be.quantize_q8(256, xb, 1, IN_F, qs, d, s32)
+    be.sync()
+
+    # ---- device-resident pass: one graph = ROT x (quantise + GEMV) ----
+    be.capture_begin()
+    for i in range(ROT):
+        be.gemv(infr_b200.Q4K, ws[i], xb, ys[i], 1, IN_F, OUT_F)
+    g_full = be.capture_end()
+    be.capture_begin()
+    for i in range(ROT):
+        be.gemv_q8(infr_b200.Q4K, ws[i], qs, d, s32, None, ys[i], 1, IN_F, OUT_F)
+    g_kern = be.capture_end()
+
+    sampler = ClockSampler(local)
+    l0 = be.launch_count()
+    with sampler:
+        ms = _time_graph(be, g_full, steps, warmup, dist)
+    launches = be.launch_count() - l0 - warmup * 2 * ROT
+    ms = _max_over_ranks(dist, ms)
+    with sampler:
+        ms_kern = _time_graph(be, g_kern, steps, warmup, dist)
+    ms_kern = _max_over_ranks(dist, ms_kern)
+
+    # ---- end to end through the Backend interface with host buffers ----
+    g = infr_b200.Graph()
+    xid = g.input(IN_F)
+    wid = g.weight(OUT_F * IN_F, infr_b200.Q4K)
+    did = g.output(OUT_F)
+    g.linear(xid, wid, did, 1, IN_F, OUT_F)
+    plan = be.compile(g)
+    hx = be.host_array((IN_F,), np.float32)
+    hy = be.host_array((ROT, OUT_F), np.float32)
+    hx[:] = x[0]
+    e2e_steps = max(3, min(steps, 50))
+
+    def e2e_pass():
+        for i in range(ROT):
+            be.upload_raw(xb, hx.ctypes.data, IN_F * 4)
+            be.execute(plan, {xid: xb, wid: ws[i], did: ys[i]})
+            be.download_raw(ys[i], hy[i].ctypes.data, OUT_F * 4)
+
+    for _ in range(3):
+        e2e_pass()
+    _barrier(dist)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_pass()
+    e2e_s = _max_over_ranks(dist, time.perf_counter() - t0)
+
+    total_bytes = C1_BYTES * ROT * world
+    value = total_bytes * steps / (ms * 1e-3) / 1e9
+    kern_gbs = C1_BYTES * ROT * steps / (ms_kern * 1e-3) / 1e9
+    out = {
+        "metric": "Q4_K GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 activations x 4-bit weights, int32 block accumulate, f32 out",
+        "data": "synthetic",
+        "config": {"workload": f"Q4_K GEMV W 4096x4096 (fp32 N(0,0.02) seed 0 -> Q4_K), x fp32 [1,4096] N(0,1); "
+                               f"step = one pass over {ROT} device copies at distinct addresses",
+                   "l2": f"inputs larger than L2: {ROT * w.nbytes / 1e6:.0f} MB of weights per step vs {caps.l2_bytes / 1e6:.0f} MB L2",
+                   "parallelism": f"{world} x independent row shards (no collective)" if world > 1 else "1 GPU",
+                   "fraction_of_8TBs": value / world / 8000.0},
+        "roofline": {"bound": "hbm", "achieved": kern_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": kern_gbs / hbm_peak,
+                     "traffic": None, "peak_source": f"{peak_src} HBM copy bandwidth",
+                     "kernel": "gemv_q4k_q8_kernel<1,false>", "kernel_us": ms_kern * 1e3 / (steps * ROT),
+                     "alg_bytes_per_launch": C1_BYTES},
+        "e2e": {"value": total_bytes * e2e_steps / e2e_s / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": ROT * IN_F * 4, "d2h_bytes_per_step": ROT * OUT_F * 4,
+                "ms_per_step": e2e_s * 1e3 / e2e_steps, "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": sampler.summary(),
+    }
+    # a parity spot check travels with the number (GPU vs GPU-free expectation is in tests/)
+    y0 = be.download(ys[0], np.float32)
+    out["config"]["y_checksum"] = float(np.abs(y0).sum())
+
+    if rank == 0 and world == 1 and not args.no_sweep:
+        sweep = []
+        sw_steps = max(20, min(steps, 100))
+        for dtype, o, i_, seed, ms_ in ((infr_b200.Q4K, 14336, 4096, 5, (1,)), (infr_b200.Q6K, 14336, 4096, 2, (1, 4, 8)),
+                                        (infr_b200.Q2_0, 4096, 14336, 3, (1, 4, 8))):
+            for m in ms_:
+                sweep.append(_gemv_case(be, infr_b200, dtype, o, i_, m, seed, sw_steps, 5, caps.l2_bytes, hbm_peak))
+        out["sweep"] = sweep
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        out["cpu_baseline"] = _cpu_baseline(w, x, budget_s=10.0)
+
+    be.close()
+    if rank == 0:
+        print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def _cpu_baseline(w, x, budget_s):
+    from oracle.cpu_oracle import Oracle, Q4K
+
+    orc = Oracle()
+    threads = os.cpu_count() or 1
+    orc.linear(Q4K, w, x, 1, IN_F, OUT_F, threads=threads)
+    t0 = time.perf_counter()
+    n = 0
+    while time.perf_counter() - t0 < budget_s and n < 2000:
+        orc.linear(Q4K, w, x, 1, IN_F, OUT_F, threads=threads)
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": C1_BYTES * n / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{n} Q4_K 4096x4096 matvecs (production int8 path of the C restatement of infr-cpu, "
+                      f"quantise + integer dots, OpenMP over rows), {dt:.1f} s; the matrix stays in the CPU caches"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from infr_b200 import synth
+    from oracle.cpu_oracle import Oracle, Q4K
+
+    orc = Oracle()
+    threads = os.cpu_count() or 1
+    steps, warmup = args.steps, args.warmup
+    # each step: a bounded sample of the pass — `per` matvecs over distinct copies of the matrix
+    per = 8
+    w = synth.weight(Q4K, OUT_F, IN_F, seed=0)
+    ws = [w.copy() for _ in range(per)]
+    x = synth.normal(1, (1, IN_F))
+    for _ in range(max(warmup, 1)):
+        for wi in ws:
+            orc.linear(Q4K, wi, x, 1, IN_F, OUT_F, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        for wi in ws:
+            orc.linear(Q4K, wi, x, 1, IN_F, OUT_F, threads=threads)
+    dt = time.perf_counter() - t0
+    value = C1_BYTES * per * steps / dt / 1e9
+    sample = (f"per step {per} of the {ROT} Q4_K 4096x4096 matvecs (distinct copies), production int8 path of the "
+              f"C restatement of infr-cpu on {threads} host threads; the Rust reference cannot be built (no Rust toolchain)")
+    out = {"impl": "reference", "metric": "Q4_K GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+           "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3 / steps, "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "int8 activations x 4-bit weights, int32 block accumulate, f32 out",
+           "data": "synthetic",
+           "config": {"workload": "Q4_K GEMV W 4096x4096, x fp32 [1,4096]; CPU arm, bounded sample per step"},
+           "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+           "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "gpu_launches": 0}
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,220 @@
+/*
+ * libinfr_cuda.so — C ABI of the sm_100a implementation of infr's block-quantized matmul path.
+ *
+ * This is the boundary a Rust `infr-cuda` crate binds with `extern "C"` to implement the reference's
+ * `trait Backend` (crates/infr-core/src/backend.rs:486-662) and its companion `Buffer` / `Plan`
+ * traits (:387-446).  Every entry point takes plain pointers and sizes; nothing here exposes C++,
+ * CUDA or torch types.  All functions return an int32 status (0 = ok, negative = error); the text of
+ * the last error of a context is fetched with infr_cuda_last_error().  Nothing in the library falls
+ * back to the CPU: without a usable CUDA device infr_cuda_create() fails.
+ *
+ * Threading: a context serialises its own calls with an internal mutex (the reference holds a
+ * backend as Arc<dyn Backend> and may call it from several threads, backend.rs:486).
+ */
+#ifndef INFR_CUDA_H
+#define INFR_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define INFR_API
+#else
+#define INFR_API __attribute__((visibility("default")))
+#endif
+
+/* ---- status codes (map onto infr_core::error::Error, crates/infr-core/src/error.rs:6-25) ---- */
+#define INFR_OK 0
+#define INFR_E_INVALID (-1)     /* Error::Backend: bad size / shape / null / unbound handle */
+#define INFR_E_UNSUPPORTED (-2) /* Error::Unsupported: op or dtype this backend does not run */
+#define INFR_E_OOM (-3)         /* Error::Backend: device allocation failed */
+#define INFR_E_CUDA (-4)        /* Error::Backend: a CUDA runtime call failed */
+#define INFR_E_NCCL (-5)
+#define INFR_E_TIMEOUT (-6)     /* a bounded device-side wait expired */
+
+/* ---- dtype codes: the declaration order of `enum DType`, crates/infr-core/src/tensor.rs:7-57 ---- */
+#define INFR_DT_F32 0
+#define INFR_DT_F16 1
+#define INFR_DT_I32 3
+#define INFR_DT_Q4K 12
+#define INFR_DT_Q6K 14
+#define INFR_DT_Q2_0 27
+
+/* ---- BufferUsage (crates/infr-core/src/backend.rs:359-380); advisory ---- */
+#define INFR_USAGE_WEIGHTS 0
+#define INFR_USAGE_ACTIVATIONS 1
+#define INFR_USAGE_KV 2
+#define INFR_USAGE_READBACK 3
+
+/* ---- TensorKind (crates/infr-core/src/graph.rs:111-122) ---- */
+#define INFR_TK_INPUT 0
+#define INFR_TK_WEIGHT 1
+#define INFR_TK_INTERNAL 2
+#define INFR_TK_OUTPUT 3
+
+/* ---- activation representation of a quantized Linear ---- */
+#define INFR_ACT_INT8 0 /* production infr-cpu arithmetic: Q8 activations, integer block dots */
+#define INFR_ACT_F32 1  /* `kernels.cpu.reference` arithmetic: dequantised weights, f32 dot */
+
+typedef struct infr_cuda_ctx infr_cuda_ctx;
+typedef struct infr_cuda_buf infr_cuda_buf;
+typedef struct infr_cuda_plan infr_cuda_plan;
+typedef struct infr_cuda_graph infr_cuda_graph;
+
+/* Options of infr_cuda_create.  `reference` mirrors CpuCfg::reference
+ * (crates/infr-core/src/config/mod.rs:425-438): when non-zero every quantized Linear / MoeFfn run by
+ * infr_cuda_execute uses INFR_ACT_F32 arithmetic. */
+typedef struct {
+    int32_t device;
+    int32_t reference;
+    int32_t reserved[6];
+} infr_cuda_opts;
+
+/* The subset of `struct Capabilities` (crates/infr-core/src/backend.rs:43-213) this backend sets;
+ * every field not listed is false / 0 / None on the Rust side. */
+typedef struct {
+    char name[32]; /* "cuda-sm100a" */
+    int32_t f16, i8, i8_dot, integrated, unified_memory, decode_replay, graph_input_inplace;
+    uint32_t max_shared_memory_bytes;
+    uint32_t sm_count;
+    uint64_t total_memory_bytes;
+    uint64_t l2_bytes;
+} infr_cuda_caps;
+
+/* ---- lifecycle: `Backend::name/capabilities`, backend.rs:487-488 ---- */
+INFR_API int32_t infr_cuda_create(const infr_cuda_opts *opts, infr_cuda_ctx **out);
+INFR_API void infr_cuda_destroy(infr_cuda_ctx *ctx);
+INFR_API int32_t infr_cuda_get_caps(infr_cuda_ctx *ctx, infr_cuda_caps *out);
+/* Copies the NUL-terminated message of the most recent failing call on `ctx` (NULL = the failing
+ * infr_cuda_create of this thread).  Returns the message length. */
+INFR_API int32_t infr_cuda_last_error(infr_cuda_ctx *ctx, char *dst, size_t cap);
+
+/* ---- memory: `Backend::alloc / alloc_uninit / upload / download / copy_buffer`, backend.rs:491-558;
+ *      `Buffer::len_bytes`, backend.rs:387-398.  alloc is zero-initialised (calloc semantics). ---- */
+INFR_API int32_t infr_cuda_alloc(infr_cuda_ctx *ctx, size_t bytes, int32_t usage, infr_cuda_buf **out);
+INFR_API int32_t infr_cuda_alloc_uninit(infr_cuda_ctx *ctx, size_t bytes, int32_t usage, infr_cuda_buf **out);
+INFR_API void infr_cuda_free(infr_cuda_ctx *ctx, infr_cuda_buf *buf);
+INFR_API size_t infr_cuda_buf_len(const infr_cuda_buf *buf);
+INFR_API uint64_t infr_cuda_buf_device_ptr(const infr_cuda_buf *buf);
+/* upload/download reject a transfer larger than the buffer (check_copy_bytes, backend.rs:23-30). */
+INFR_API int32_t infr_cuda_upload(infr_cuda_ctx *ctx, infr_cuda_buf *dst, const void *src, size_t bytes);
+INFR_API int32_t infr_cuda_upload_at(infr_cuda_ctx *ctx, infr_cuda_buf *dst, size_t dst_off, const void *src, size_t bytes);
+INFR_API int32_t infr_cuda_download(infr_cuda_ctx *ctx, const infr_cuda_buf *src, void *dst, size_t bytes);
+INFR_API int32_t infr_cuda_copy(infr_cuda_ctx *ctx, const infr_cuda_buf *src, infr_cuda_buf *dst, size_t bytes);
+/* Page-locked host memory for staging uploads/downloads (the reference's Vulkan backend stages
+ * through host-visible memory the same way; no counterpart on the CPU backend). */
+INFR_API int32_t infr_cuda_host_alloc(infr_cuda_ctx *ctx, size_t bytes, void **out);
+INFR_API void infr_cuda_host_free(infr_cuda_ctx *ctx, void *p);
+/* `Backend::sync`, backend.rs:596. */
+INFR_API int32_t infr_cuda_sync(infr_cuda_ctx *ctx);
+
+/* ---- graphs: `Backend::compile / execute`, backend.rs:561-562 ----
+ * infr_graph_desc is a flat POD mirror of `Graph` (crates/infr-core/src/graph.rs:1317-1460): an
+ * ordered op list over typed tensor handles; handle i is TensorId(i). */
+typedef struct {
+    uint32_t kind;  /* INFR_TK_* */
+    uint32_t dtype; /* INFR_DT_* */
+    uint64_t numel;
+} infr_tensor_decl;
+
+#define INFR_OP_LINEAR 1  /* Op::Linear, graph.rs:179-191 */
+#define INFR_OP_MOE_FFN 2 /* Op::MoeFfn, graph.rs:918-1011 */
+
+/* One op.  Field use per tag:
+ *  INFR_OP_LINEAR : t = {x, weight, dst}; u = {m, in_f, out_f, w_off}
+ *  INFR_OP_MOE_FFN: t = {x, router_x, router, gate_exps, up_exps, down_exps, dst};
+ *                   u = {ne, n_expert, n_used, n_ff_exp, norm_w, fused_gate_up, weight_before,
+ *                        act (0 = SiLU), gating (0 = Softmax)}; f = {scale}
+ *    Fields of Op::MoeFfn without a slot here (down_scale, swiglu_clamp, ep_band, exp_probs_b,
+ *    expert groups, expert_ids) must be None/0 on the Rust side; the binding returns
+ *    Error::Unsupported otherwise. */
+typedef struct {
+    uint32_t tag;
+    uint32_t t[8];
+    uint32_t u[12];
+    float f[4];
+} infr_op_desc;
+
+typedef struct {
+    const infr_tensor_decl *tensors;
+    uint32_t n_tensors;
+    const infr_op_desc *ops;
+    uint32_t n_ops;
+} infr_graph_desc;
+
+INFR_API int32_t infr_cuda_compile(infr_cuda_ctx *ctx, const infr_graph_desc *graph, infr_cuda_plan **out);
+INFR_API void infr_cuda_plan_free(infr_cuda_ctx *ctx, infr_cuda_plan *plan);
+/* bindings[i] is the buffer bound to TensorId(i), NULL = unbound (`Bindings`, backend.rs:457-483).
+ * Internal handles are backend scratch, zeroed before the walk (crates/infr-core/src/exec.rs:53-92).
+ * An unbound Input/Weight/Output handle used by an op is INFR_E_INVALID (the CPU reference panics
+ * there, crates/infr-cpu/src/lib.rs:754). */
+INFR_API int32_t infr_cuda_execute(infr_cuda_ctx *ctx, infr_cuda_plan *plan,
+                                   infr_cuda_buf *const *bindings, uint32_t n_bindings);
+
+/* ---- direct kernel entry points (what `execute` dispatches to; used by benches and tests) ----
+ * All pointers are infr_cuda_buf handles; byte offsets select a sub-range. */
+
+/* Activation quantiser.  gran = 256: `quantize_q8` (crates/infr-cpu/src/quant.rs:27-58): qs i8
+ * [rows,k], d f32 [rows,k/256], sums i32 [rows,k/32] (`bsums`), sums16 i32 [rows,k/16] (nullable).
+ * gran = 32: `quantize_q8_32` (quant.rs:97-117): d f32 [rows,k/32], sums i32 [rows,k/32]. */
+INFR_API int32_t infr_cuda_quantize_q8(infr_cuda_ctx *ctx, int32_t gran, const infr_cuda_buf *x,
+                                       uint32_t rows, uint32_t k, infr_cuda_buf *qs, infr_cuda_buf *d,
+                                       infr_cuda_buf *sums, infr_cuda_buf *sums16);
+/* The "Q8_1" view of the reference's GPU path (crates/infr-vulkan/shaders/quant_q8.comp:37-61):
+ * same int8 codes as gran = 32, dact = f16(d), sact = f16(d * float(sum of codes)). */
+INFR_API int32_t infr_cuda_quantize_q8_1(infr_cuda_ctx *ctx, const infr_cuda_buf *x, uint32_t rows,
+                                         uint32_t k, infr_cuda_buf *qs, infr_cuda_buf *dact,
+                                         infr_cuda_buf *sact);
+
+/* y[m,out_f] = x[m,in_f] * W^T for m <= 8 (decode).  W is raw GGUF blocks, row-major [rows,in_f];
+ * w_off is the ELEMENT offset of the first row used (Op::Linear::w_off).  act selects INFR_ACT_*.
+ * Replaces the m == 1 / small-m arms of crates/infr-cpu/src/lib.rs:1035-1167. */
+INFR_API int32_t infr_cuda_gemv(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off,
+                                const infr_cuda_buf *x, infr_cuda_buf *y, uint32_t m, uint32_t in_f,
+                                uint32_t out_f, int32_t act);
+/* infr_cuda_gemv(INFR_ACT_INT8) on activations that are ALREADY quantised by infr_cuda_quantize_q8
+ * (gran 256 for Q4_K / Q6_K — Q6_K also needs sums16 —, gran 32 for Q2_0): the CPU reference
+ * quantises an activation row once and reuses it for every weight row and every projection that
+ * reads it (crates/infr-cpu/src/lib.rs:1043-1062); this entry point is that reuse. */
+INFR_API int32_t infr_cuda_gemv_q8(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off,
+                                   const infr_cuda_buf *qs, const infr_cuda_buf *d, const infr_cuda_buf *sums,
+                                   const infr_cuda_buf *sums16, infr_cuda_buf *y, uint32_t m, uint32_t in_f,
+                                   uint32_t out_f);
+/* Same arithmetic as infr_cuda_gemv(INFR_ACT_INT8) for m = 1, but writes the per-block int32
+ * accumulators instead of y: Q4_K -> acc[out_f][in_f/256][2] = (sd, sm) of
+ * crates/infr-cpu/src/kernels.rs:161-181; Q6_K -> acc[out_f][in_f/256] = isum (:519-523);
+ * Q2_0 -> acc[out_f][in_f/32] = iprod (:5655-5663). */
+INFR_API int32_t infr_cuda_gemv_block_acc(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w,
+                                          uint64_t w_off, const infr_cuda_buf *x, infr_cuda_buf *acc,
+                                          uint32_t in_f, uint32_t out_f);
+
+/* Op::Linear of any m (crates/infr-cpu/src/lib.rs:985-1492): dispatches to the GEMV (m <= 8) or the
+ * MMQ GEMM.  act as above. */
+INFR_API int32_t infr_cuda_linear(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off,
+                                  const infr_cuda_buf *x, infr_cuda_buf *y, uint32_t m, uint32_t in_f,
+                                  uint32_t out_f, int32_t act);
+
+/* ---- stream capture and timing ----
+ * capture_begin .. capture_end records every kernel the calls in between enqueue into a CUDA graph
+ * that infr_cuda_graph_launch replays (decode replays a fixed kernel sequence every token).  Calls
+ * that allocate or synchronise are rejected while capturing. */
+INFR_API int32_t infr_cuda_capture_begin(infr_cuda_ctx *ctx);
+INFR_API int32_t infr_cuda_capture_end(infr_cuda_ctx *ctx, infr_cuda_graph **out);
+INFR_API int32_t infr_cuda_graph_launch(infr_cuda_ctx *ctx, infr_cuda_graph *graph);
+INFR_API void infr_cuda_graph_free(infr_cuda_ctx *ctx, infr_cuda_graph *graph);
+/* CUDA-event stopwatch on the context's stream: stop synchronises and returns milliseconds. */
+INFR_API int32_t infr_cuda_timer_start(infr_cuda_ctx *ctx);
+INFR_API int32_t infr_cuda_timer_stop(infr_cuda_ctx *ctx, float *ms);
+/* Overwrites a context-owned buffer larger than L2 (evicts cached weights between timed runs). */
+INFR_API int32_t infr_cuda_flush_l2(infr_cuda_ctx *ctx);
+/* Number of kernels this context has launched since creation (graph replays count their nodes). */
+INFR_API uint64_t infr_cuda_launch_count(infr_cuda_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INFR_CUDA_H */

@@ -1,0 +1,428 @@
+"""infr_b200 — sm_100a implementation of infr's GGUF block-quantized matmul path.
+
+The product is ``libinfr_cuda.so`` (hand-written CUDA kernels behind a C ABI, ``include/infr_cuda.h``).
+This package is the thin ctypes binding used by the tests and the benchmark; its class
+:class:`CudaBackend` mirrors the reference's ``trait Backend``
+(crates/infr-core/src/backend.rs:486-662): ``name / capabilities / alloc / upload / download /
+compile / execute / sync`` with the same argument meaning and error behaviour (errors raise
+:class:`BackendError`, the analogue of ``Err(Error::Backend(..))``; nothing falls back to the CPU).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import synth  # noqa: F401
+from .synth import F32, Q2_0, Q4K, Q6K
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libinfr_cuda.so")
+
+ACT_INT8, ACT_F32 = 0, 1
+TK_INPUT, TK_WEIGHT, TK_INTERNAL, TK_OUTPUT = 0, 1, 2, 3
+USAGE_WEIGHTS, USAGE_ACTIVATIONS, USAGE_KV, USAGE_READBACK = 0, 1, 2, 3
+OP_LINEAR, OP_MOE_FFN = 1, 2
+E_INVALID, E_UNSUPPORTED, E_OOM, E_CUDA, E_NCCL, E_TIMEOUT = -1, -2, -3, -4, -5, -6
+
+# Every symbol include/infr_cuda.h declares (checked by the CPU test-suite against the built library).
+EXPORTED_SYMBOLS = [
+    "infr_cuda_create", "infr_cuda_destroy", "infr_cuda_get_caps", "infr_cuda_last_error",
+    "infr_cuda_alloc", "infr_cuda_alloc_uninit", "infr_cuda_free", "infr_cuda_buf_len",
+    "infr_cuda_buf_device_ptr", "infr_cuda_upload", "infr_cuda_upload_at", "infr_cuda_download",
+    "infr_cuda_copy", "infr_cuda_host_alloc", "infr_cuda_host_free", "infr_cuda_sync", "infr_cuda_compile", "infr_cuda_plan_free", "infr_cuda_execute",
+    "infr_cuda_quantize_q8", "infr_cuda_quantize_q8_1", "infr_cuda_gemv", "infr_cuda_gemv_q8", "infr_cuda_gemv_block_acc",
+    "infr_cuda_linear", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
+    "infr_cuda_graph_free", "infr_cuda_timer_start", "infr_cuda_timer_stop", "infr_cuda_flush_l2",
+    "infr_cuda_launch_count",
+]
+
+
+class BackendError(RuntimeError):
+    """A failing C-ABI call: ``code`` is the INFR_E_* status, the text is infr_cuda_last_error()."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[{code}] {msg}")
+        self.code = code
+
+
+class _Opts(C.Structure):
+    _fields_ = [("device", C.c_int32), ("reference", C.c_int32), ("reserved", C.c_int32 * 6)]
+
+
+class _Caps(C.Structure):
+    _fields_ = [("name", C.c_char * 32), ("f16", C.c_int32), ("i8", C.c_int32), ("i8_dot", C.c_int32),
+                ("integrated", C.c_int32), ("unified_memory", C.c_int32), ("decode_replay", C.c_int32),
+                ("graph_input_inplace", C.c_int32), ("max_shared_memory_bytes", C.c_uint32),
+                ("sm_count", C.c_uint32), ("total_memory_bytes", C.c_uint64), ("l2_bytes", C.c_uint64)]
+
+
+class _TensorDecl(C.Structure):
+    _fields_ = [("kind", C.c_uint32), ("dtype", C.c_uint32), ("numel", C.c_uint64)]
+
+
+class _OpDesc(C.Structure):
+    _fields_ = [("tag", C.c_uint32), ("t", C.c_uint32 * 8), ("u", C.c_uint32 * 12), ("f", C.c_float * 4)]
+
+
+class _GraphDesc(C.Structure):
+    _fields_ = [("tensors", C.POINTER(_TensorDecl)), ("n_tensors", C.c_uint32),
+                ("ops", C.POINTER(_OpDesc)), ("n_ops", C.c_uint32)]
+
+
+_lib = None
+
+
+def load_library() -> C.CDLL:
+    """dlopen the in-tree library.  There is no fallback: a missing library is an error."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m infr_b200.build` (nvcc, sm_100a). "
+            "infr_b200 has no CPU or PyTorch fallback.")
+    L = C.CDLL(LIB_PATH)
+    vp, u32, u64, i32, sz = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32, C.c_size_t
+    sig = {
+        "infr_cuda_create": (i32, [C.POINTER(_Opts), C.POINTER(vp)]),
+        "infr_cuda_destroy": (None, [vp]),
+        "infr_cuda_get_caps": (i32, [vp, C.POINTER(_Caps)]),
+        "infr_cuda_last_error": (i32, [vp, C.c_char_p, sz]),
+        "infr_cuda_alloc": (i32, [vp, sz, i32, C.POINTER(vp)]),
+        "infr_cuda_alloc_uninit": (i32, [vp, sz, i32, C.POINTER(vp)]),
+        "infr_cuda_free": (None, [vp, vp]),
+        "infr_cuda_buf_len": (sz, [vp]),
+        "infr_cuda_buf_device_ptr": (u64, [vp]),
+        "infr_cuda_upload": (i32, [vp, vp, vp, sz]),
+        "infr_cuda_upload_at": (i32, [vp, vp, sz, vp, sz]),
+        "infr_cuda_download": (i32, [vp, vp, vp, sz]),
+        "infr_cuda_copy": (i32, [vp, vp, vp, sz]),
+        "infr_cuda_host_alloc": (i32, [vp, sz, C.POINTER(vp)]),
+        "infr_cuda_host_free": (None, [vp, vp]),
+        "infr_cuda_sync": (i32, [vp]),
+        "infr_cuda_compile": (i32, [vp, C.POINTER(_GraphDesc), C.POINTER(vp)]),
+        "infr_cuda_plan_free": (None, [vp, vp]),
+        "infr_cuda_execute": (i32, [vp, vp, C.POINTER(vp), u32]),
+        "infr_cuda_quantize_q8": (i32, [vp, i32, vp, u32, u32, vp, vp, vp, vp]),
+        "infr_cuda_quantize_q8_1": (i32, [vp, vp, u32, u32, vp, vp, vp]),
+        "infr_cuda_gemv": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
+        "infr_cuda_gemv_q8": (i32, [vp, i32, vp, u64, vp, vp, vp, vp, vp, u32, u32, u32]),
+        "infr_cuda_gemv_block_acc": (i32, [vp, i32, vp, u64, vp, vp, u32, u32]),
+        "infr_cuda_linear": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
+        "infr_cuda_capture_begin": (i32, [vp]),
+        "infr_cuda_capture_end": (i32, [vp, C.POINTER(vp)]),
+        "infr_cuda_graph_launch": (i32, [vp, vp]),
+        "infr_cuda_graph_free": (None, [vp, vp]),
+        "infr_cuda_timer_start": (i32, [vp]),
+        "infr_cuda_timer_stop": (i32, [vp, C.POINTER(C.c_float)]),
+        "infr_cuda_flush_l2": (i32, [vp]),
+        "infr_cuda_launch_count": (u64, [vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = L
+    return L
+
+
+@dataclass
+class Capabilities:
+    name: str
+    f16: bool
+    i8: bool
+    i8_dot: bool
+    integrated: bool
+    unified_memory: bool
+    decode_replay: bool
+    graph_input_inplace: bool
+    max_shared_memory_bytes: int
+    sm_count: int
+    total_memory_bytes: int
+    l2_bytes: int
+
+
+class Buffer:
+    """Device buffer handle (`trait Buffer`, backend.rs:387-416).  Freed on close() / GC."""
+
+    def __init__(self, be: "CudaBackend", handle: int, nbytes: int):
+        self._be, self.handle, self.nbytes = be, handle, nbytes
+
+    def len_bytes(self) -> int:
+        return self.nbytes
+
+    def device_ptr(self) -> int:
+        return int(self._be.L.infr_cuda_buf_device_ptr(self.handle))
+
+    def close(self):
+        if self.handle and self._be.ctx:
+            self._be.L.infr_cuda_free(self._be.ctx, self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Graph:
+    """Ordered op list over typed handles (crates/infr-core/src/graph.rs:1317-1460)."""
+
+    def __init__(self):
+        self.tensors: list[tuple[int, int, int]] = []
+        self.ops: list[_OpDesc] = []
+
+    def _decl(self, kind, dtype, numel) -> int:
+        self.tensors.append((kind, dtype, int(numel)))
+        return len(self.tensors) - 1
+
+    def input(self, numel, dtype=F32):
+        return self._decl(TK_INPUT, dtype, numel)
+
+    def weight(self, numel, dtype):
+        return self._decl(TK_WEIGHT, dtype, numel)
+
+    def internal(self, numel, dtype=F32):
+        return self._decl(TK_INTERNAL, dtype, numel)
+
+    def output(self, numel, dtype=F32):
+        return self._decl(TK_OUTPUT, dtype, numel)
+
+    def linear(self, x, weight, dst, m, in_f, out_f, w_off=0):
+        op = _OpDesc()
+        op.tag = OP_LINEAR
+        op.t[0], op.t[1], op.t[2] = x, weight, dst
+        op.u[0], op.u[1], op.u[2], op.u[3] = m, in_f, out_f, w_off
+        self.ops.append(op)
+
+    def moe_ffn(self, x, router_x, router, gate_exps, up_exps, down_exps, dst, *, ne, n_expert, n_used,
+                n_ff_exp, scale=1.0, norm_w=True, fused_gate_up=False, weight_before=False):
+        op = _OpDesc()
+        op.tag = OP_MOE_FFN
+        for i, t in enumerate((x, router_x, router, gate_exps, up_exps, down_exps, dst)):
+            op.t[i] = t
+        for i, v in enumerate((ne, n_expert, n_used, n_ff_exp, int(norm_w), int(fused_gate_up),
+                               int(weight_before), 0, 0)):
+            op.u[i] = v
+        op.f[0] = scale
+        self.ops.append(op)
+
+
+class Plan:
+    def __init__(self, be, handle):
+        self._be, self.handle = be, handle
+
+    def close(self):
+        if self.handle and self._be.ctx:
+            self._be.L.infr_cuda_plan_free(self._be.ctx, self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class CudaGraph:
+    def __init__(self, be, handle):
+        self._be, self.handle = be, handle
+
+    def launch(self):
+        self._be._check(self._be.L.infr_cuda_graph_launch(self._be.ctx, self.handle))
+
+    def close(self):
+        if self.handle and self._be.ctx:
+            self._be.L.infr_cuda_graph_free(self._be.ctx, self.handle)
+        self.handle = None
+
+
+class CudaBackend:
+    """`impl Backend for CudaBackend` over the C ABI."""
+
+    def __init__(self, device: int = 0, reference: bool = False):
+        self.L = load_library()
+        self.ctx = None
+        opts = _Opts(device=device, reference=int(reference))
+        ctx = C.c_void_p()
+        rc = self.L.infr_cuda_create(C.byref(opts), C.byref(ctx))
+        if rc != 0:
+            buf = C.create_string_buffer(512)
+            self.L.infr_cuda_last_error(None, buf, 512)
+            raise BackendError(rc, buf.value.decode())
+        self.ctx = ctx
+        self.device = device
+        self._pinned: list = []
+
+    # ---- plumbing ----
+    def _check(self, rc: int):
+        if rc != 0:
+            buf = C.create_string_buffer(1024)
+            self.L.infr_cuda_last_error(self.ctx, buf, 1024)
+            raise BackendError(rc, buf.value.decode())
+
+    def close(self):
+        if self.ctx:
+            for p in self._pinned:
+                self.L.infr_cuda_host_free(self.ctx, p)
+            self._pinned = []
+            self.L.infr_cuda_destroy(self.ctx)
+            self.ctx = None
+
+    def name(self) -> str:
+        return self.capabilities().name
+
+    def capabilities(self) -> Capabilities:
+        c = _Caps()
+        self._check(self.L.infr_cuda_get_caps(self.ctx, C.byref(c)))
+        return Capabilities(c.name.decode(), bool(c.f16), bool(c.i8), bool(c.i8_dot), bool(c.integrated),
+                            bool(c.unified_memory), bool(c.decode_replay), bool(c.graph_input_inplace),
+                            c.max_shared_memory_bytes, c.sm_count, c.total_memory_bytes, c.l2_bytes)
+
+    # ---- memory ----
+    def alloc(self, nbytes: int, usage: int = USAGE_ACTIVATIONS) -> Buffer:
+        h = C.c_void_p()
+        self._check(self.L.infr_cuda_alloc(self.ctx, nbytes, usage, C.byref(h)))
+        return Buffer(self, h, nbytes)
+
+    def alloc_uninit(self, nbytes: int, usage: int = USAGE_WEIGHTS) -> Buffer:
+        h = C.c_void_p()
+        self._check(self.L.infr_cuda_alloc_uninit(self.ctx, nbytes, usage, C.byref(h)))
+        return Buffer(self, h, nbytes)
+
+    def upload(self, dst: Buffer, src: np.ndarray, offset: int = 0):
+        src = np.ascontiguousarray(src)
+        if offset:
+            self._check(self.L.infr_cuda_upload_at(self.ctx, dst.handle, offset, src.ctypes.data, src.nbytes))
+        else:
+            self._check(self.L.infr_cuda_upload(self.ctx, dst.handle, src.ctypes.data, src.nbytes))
+
+    def download(self, src: Buffer, dtype, count: Optional[int] = None) -> np.ndarray:
+        dtype = np.dtype(dtype)
+        n = src.nbytes // dtype.itemsize if count is None else count
+        out = np.empty(n, dtype)
+        self._check(self.L.infr_cuda_download(self.ctx, src.handle, out.ctypes.data, out.nbytes))
+        return out
+
+    def download_into(self, src: Buffer, dst: np.ndarray):
+        self._check(self.L.infr_cuda_download(self.ctx, src.handle, dst.ctypes.data, dst.nbytes))
+
+    def copy_buffer(self, src: Buffer, dst: Buffer, nbytes: int):
+        self._check(self.L.infr_cuda_copy(self.ctx, src.handle, dst.handle, nbytes))
+
+    def from_numpy(self, a: np.ndarray, usage: int = USAGE_ACTIVATIONS) -> Buffer:
+        a = np.ascontiguousarray(a)
+        b = self.alloc_uninit(max(a.nbytes, 4), usage)
+        self.upload(b, a)
+        return b
+
+    def host_array(self, shape, dtype) -> np.ndarray:
+        """A numpy array over page-locked host memory (freed when the backend closes)."""
+        dtype = np.dtype(dtype)
+        n = int(np.prod(shape))
+        p = C.c_void_p()
+        self._check(self.L.infr_cuda_host_alloc(self.ctx, n * dtype.itemsize, C.byref(p)))
+        self._pinned.append(p)
+        buf = (C.c_uint8 * (n * dtype.itemsize)).from_address(p.value)
+        return np.frombuffer(buf, dtype=dtype, count=n).reshape(shape)
+
+    def upload_raw(self, dst: Buffer, host_ptr: int, nbytes: int):
+        self._check(self.L.infr_cuda_upload(self.ctx, dst.handle, host_ptr, nbytes))
+
+    def download_raw(self, src: Buffer, host_ptr: int, nbytes: int):
+        self._check(self.L.infr_cuda_download(self.ctx, src.handle, host_ptr, nbytes))
+
+    def sync(self):
+        self._check(self.L.infr_cuda_sync(self.ctx))
+
+    # ---- graphs ----
+    def compile(self, g: Graph) -> Plan:
+        tens = (_TensorDecl * max(len(g.tensors), 1))()
+        for i, (k, d, n) in enumerate(g.tensors):
+            tens[i] = _TensorDecl(k, d, n)
+        ops = (_OpDesc * max(len(g.ops), 1))(*g.ops)
+        desc = _GraphDesc(tens, len(g.tensors), ops, len(g.ops))
+        h = C.c_void_p()
+        self._check(self.L.infr_cuda_compile(self.ctx, C.byref(desc), C.byref(h)))
+        return Plan(self, h)
+
+    def execute(self, plan: Plan, bindings: dict[int, Buffer]):
+        n = (max(bindings) + 1) if bindings else 0
+        arr = (C.c_void_p * max(n, 1))()
+        for i, b in bindings.items():
+            arr[i] = b.handle
+        self._check(self.L.infr_cuda_execute(self.ctx, plan.handle, arr, n))
+
+    # ---- direct kernels ----
+    def quantize_q8(self, gran: int, x: Buffer, rows: int, k: int, qs: Buffer, d: Buffer, sums: Buffer,
+                    sums16: Optional[Buffer] = None):
+        self._check(self.L.infr_cuda_quantize_q8(self.ctx, gran, x.handle, rows, k, qs.handle, d.handle,
+                                                 sums.handle, sums16.handle if sums16 else None))
+
+    def quantize_q8_1(self, x: Buffer, rows: int, k: int, qs: Buffer, dact: Buffer, sact: Buffer):
+        self._check(self.L.infr_cuda_quantize_q8_1(self.ctx, x.handle, rows, k, qs.handle, dact.handle, sact.handle))
+
+    def gemv(self, dtype: int, w: Buffer, x: Buffer, y: Buffer, m: int, in_f: int, out_f: int,
+             act: int = ACT_INT8, w_off: int = 0):
+        self._check(self.L.infr_cuda_gemv(self.ctx, dtype, w.handle, w_off, x.handle, y.handle, m, in_f, out_f, act))
+
+    def gemv_q8(self, dtype: int, w: Buffer, qs: Buffer, d: Buffer, sums: Buffer, sums16: Optional[Buffer],
+                y: Buffer, m: int, in_f: int, out_f: int, w_off: int = 0):
+        self._check(self.L.infr_cuda_gemv_q8(self.ctx, dtype, w.handle, w_off, qs.handle, d.handle, sums.handle,
+                                             sums16.handle if sums16 else None, y.handle, m, in_f, out_f))
+
+    def linear(self, dtype: int, w: Buffer, x: Buffer, y: Buffer, m: int, in_f: int, out_f: int,
+               act: int = ACT_INT8, w_off: int = 0):
+        self._check(self.L.infr_cuda_linear(self.ctx, dtype, w.handle, w_off, x.handle, y.handle, m, in_f, out_f, act))
+
+    def gemv_block_acc(self, dtype: int, w: Buffer, x: Buffer, acc: Buffer, in_f: int, out_f: int, w_off: int = 0):
+        self._check(self.L.infr_cuda_gemv_block_acc(self.ctx, dtype, w.handle, w_off, x.handle, acc.handle, in_f, out_f))
+
+    # ---- capture / timing ----
+    def capture_begin(self):
+        self._check(self.L.infr_cuda_capture_begin(self.ctx))
+
+    def capture_end(self) -> CudaGraph:
+        h = C.c_void_p()
+        self._check(self.L.infr_cuda_capture_end(self.ctx, C.byref(h)))
+        return CudaGraph(self, h)
+
+    def timer_start(self):
+        self._check(self.L.infr_cuda_timer_start(self.ctx))
+
+    def timer_stop(self) -> float:
+        ms = C.c_float()
+        self._check(self.L.infr_cuda_timer_stop(self.ctx, C.byref(ms)))
+        return float(ms.value)
+
+    def flush_l2(self):
+        self._check(self.L.infr_cuda_flush_l2(self.ctx))
+
+    def launch_count(self) -> int:
+        return int(self.L.infr_cuda_launch_count(self.ctx))
+
+    # ---- convenience used by tests: host arrays in, host array out, through the graph seam ----
+    def run_linear(self, dtype: int, w_bytes: np.ndarray, x: np.ndarray, m: int, in_f: int, out_f: int,
+                   w_off: int = 0, total_rows: Optional[int] = None) -> np.ndarray:
+        """One-`Op::Linear` graph, the shape of infr_testkit::run_linear (testkit/src/lib.rs:314-337)."""
+        rows = total_rows if total_rows is not None else out_f
+        g = Graph()
+        xid = g.input(m * in_f)
+        wid = g.weight(rows * in_f, dtype)
+        dst = g.output(m * out_f)
+        g.linear(xid, wid, dst, m, in_f, out_f, w_off)
+        plan = self.compile(g)
+        xb = self.from_numpy(np.asarray(x, np.float32))
+        wb = self.from_numpy(np.asarray(w_bytes, np.uint8), USAGE_WEIGHTS)
+        ob = self.alloc(m * out_f * 4, USAGE_READBACK)
+        self.execute(plan, {xid: xb, wid: wb, dst: ob})
+        out = self.download(ob, np.float32).reshape(m, out_f)
+        for b in (xb, wb, ob):
+            b.close()
+        plan.close()
+        return out

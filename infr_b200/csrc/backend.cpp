@@ -1,0 +1,456 @@
+// CudaBackend: device memory, graph walking and op dispatch (host side).
+#include "backend.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+namespace infr {
+
+namespace {
+std::string fmt(const char *f, ...) __attribute__((format(printf, 1, 2)));
+std::string fmt(const char *f, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, f);
+    vsnprintf(buf, sizeof buf, f, ap);
+    va_end(ap);
+    return buf;
+}
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+}  // namespace
+
+Status CudaBackend::cuda_status(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return Status::Ok();
+    const int32_t code = e == cudaErrorMemoryAllocation ? INFR_E_OOM : INFR_E_CUDA;
+    return Status::Err(code, fmt("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e)));
+}
+
+Status CudaBackend::create(const infr_cuda_opts &opts, CudaBackend **out) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0)
+        return Status::Err(INFR_E_CUDA, fmt("no CUDA device: %s (this backend has no CPU fallback)",
+                                            e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e)));
+    if (opts.device < 0 || opts.device >= n)
+        return Status::Err(INFR_E_INVALID, fmt("device %d out of range (%d present)", opts.device, n));
+    auto *be = new CudaBackend();
+    be->device_ = opts.device;
+    be->reference_ = opts.reference != 0;
+    Status s;
+    if (!(s = be->cuda_status(cudaSetDevice(be->device_), "cudaSetDevice")).ok() ||
+        !(s = be->cuda_status(cudaGetDeviceProperties(&be->prop_, be->device_), "cudaGetDeviceProperties")).ok()) {
+        delete be;
+        return s;
+    }
+    if (be->prop_.major != 10) {
+        s = Status::Err(INFR_E_UNSUPPORTED, fmt("device %d is sm_%d%d; this library is built for sm_100a only",
+                                                be->device_, be->prop_.major, be->prop_.minor));
+        delete be;
+        return s;
+    }
+    be->dev_.sm_count = be->prop_.multiProcessorCount;
+    be->dev_.max_smem_optin = (int)be->prop_.sharedMemPerBlockOptin;
+    be->dev_.l2_bytes = (size_t)be->prop_.l2CacheSize;
+    if (!(s = be->cuda_status(cudaStreamCreateWithFlags(&be->stream_, cudaStreamNonBlocking), "cudaStreamCreate")).ok() ||
+        !(s = be->cuda_status(cudaEventCreate(&be->ev0_), "cudaEventCreate")).ok() ||
+        !(s = be->cuda_status(cudaEventCreate(&be->ev1_), "cudaEventCreate")).ok()) {
+        delete be;
+        return s;
+    }
+    *out = be;
+    return Status::Ok();
+}
+
+CudaBackend::~CudaBackend() {
+    cudaSetDevice(device_);
+    if (stream_) cudaStreamSynchronize(stream_);
+    if (scratch_) cudaFree(scratch_);
+    if (flush_) cudaFree(flush_);
+    if (ev0_) cudaEventDestroy(ev0_);
+    if (ev1_) cudaEventDestroy(ev1_);
+    if (stream_) cudaStreamDestroy(stream_);
+}
+
+infr_cuda_caps CudaBackend::capabilities() const {
+    infr_cuda_caps c;
+    memset(&c, 0, sizeof c);
+    snprintf(c.name, sizeof c.name, "%s", name());
+    c.f16 = 1;
+    c.i8 = 1;
+    c.i8_dot = 1;
+    c.integrated = 0;
+    c.unified_memory = 0;
+    c.decode_replay = 0;
+    c.graph_input_inplace = 1;
+    c.max_shared_memory_bytes = (uint32_t)dev_.max_smem_optin;
+    c.sm_count = (uint32_t)dev_.sm_count;
+    c.total_memory_bytes = (uint64_t)prop_.totalGlobalMem;
+    c.l2_bytes = (uint64_t)dev_.l2_bytes;
+    return c;
+}
+
+// ---------------------------------------------------------------------------------------- memory
+Status CudaBackend::alloc(size_t bytes, int usage, bool zero, infr_cuda_buf **out) {
+    if (capturing_) return Status::Err(INFR_E_INVALID, "alloc during stream capture");
+    cudaSetDevice(device_);
+    void *p = nullptr;
+    // Round up so 16-byte vector accesses on the tail of a row never leave the allocation.
+    const size_t padded = align_up(bytes ? bytes : 1, 256);
+    Status s = cuda_status(cudaMalloc(&p, padded), "cudaMalloc");
+    if (!s.ok()) return s;
+    if (zero) {
+        s = cuda_status(cudaMemsetAsync(p, 0, padded, stream_), "cudaMemsetAsync");
+    } else {
+        // only the padding must be defined
+        if (padded > bytes) s = cuda_status(cudaMemsetAsync((uint8_t *)p + bytes, 0, padded - bytes, stream_), "cudaMemsetAsync");
+    }
+    if (!s.ok()) {
+        cudaFree(p);
+        return s;
+    }
+    auto *b = new infr_cuda_buf();
+    b->ptr = p;
+    b->len = bytes;
+    b->usage = usage;
+    b->uid = next_uid_++;
+    *out = b;
+    return Status::Ok();
+}
+
+void CudaBackend::free_buffer(infr_cuda_buf *b) {
+    if (!b) return;
+    cudaSetDevice(device_);
+    cudaStreamSynchronize(stream_);
+    cudaFree(b->ptr);
+    delete b;
+}
+
+Status CudaBackend::upload(infr_cuda_buf *dst, size_t dst_off, const void *src, size_t bytes) {
+    if (!dst || (!src && bytes)) return Status::Err(INFR_E_INVALID, "upload: null argument");
+    if (dst_off > dst->len || bytes > dst->len - dst_off)
+        return Status::Err(INFR_E_INVALID, fmt("upload: %zu bytes at offset %zu into a %zu-byte buffer", bytes, dst_off, dst->len));
+    if (capturing_) return Status::Err(INFR_E_INVALID, "upload during stream capture");
+    cudaSetDevice(device_);
+    Status s = cuda_status(cudaMemcpyAsync((uint8_t *)dst->ptr + dst_off, src, bytes, cudaMemcpyHostToDevice, stream_), "upload");
+    if (!s.ok()) return s;
+    // The caller may reuse `src` as soon as this returns (the trait takes a borrowed slice).
+    return cuda_status(cudaStreamSynchronize(stream_), "upload sync");
+}
+
+Status CudaBackend::download(const infr_cuda_buf *src, void *dst, size_t bytes) {
+    if (!src || (!dst && bytes)) return Status::Err(INFR_E_INVALID, "download: null argument");
+    if (bytes > src->len)
+        return Status::Err(INFR_E_INVALID, fmt("download: %zu bytes from a %zu-byte buffer", bytes, src->len));
+    if (capturing_) return Status::Err(INFR_E_INVALID, "download during stream capture");
+    cudaSetDevice(device_);
+    Status s = cuda_status(cudaMemcpyAsync(dst, src->ptr, bytes, cudaMemcpyDeviceToHost, stream_), "download");
+    if (!s.ok()) return s;
+    return cuda_status(cudaStreamSynchronize(stream_), "download sync");
+}
+
+Status CudaBackend::copy_buffer(const infr_cuda_buf *src, infr_cuda_buf *dst, size_t bytes) {
+    if (!src || !dst) return Status::Err(INFR_E_INVALID, "copy: null buffer");
+    if (bytes > src->len || bytes > dst->len)
+        return Status::Err(INFR_E_INVALID, fmt("copy: %zu bytes between %zu- and %zu-byte buffers", bytes, src->len, dst->len));
+    cudaSetDevice(device_);
+    return cuda_status(cudaMemcpyAsync(dst->ptr, src->ptr, bytes, cudaMemcpyDeviceToDevice, stream_), "copy");
+}
+
+Status CudaBackend::sync() {
+    if (capturing_) return Status::Err(INFR_E_INVALID, "sync during stream capture");
+    cudaSetDevice(device_);
+    return cuda_status(cudaStreamSynchronize(stream_), "sync");
+}
+
+Status CudaBackend::ensure_scratch(size_t bytes) {
+    if (bytes <= scratch_bytes_) return Status::Ok();
+    if (capturing_)
+        return Status::Err(INFR_E_INVALID, "activation scratch would grow during stream capture; run the same calls once before capturing");
+    cudaSetDevice(device_);
+    Status s = cuda_status(cudaStreamSynchronize(stream_), "scratch sync");
+    if (!s.ok()) return s;
+    if (scratch_) cudaFree(scratch_);
+    scratch_ = nullptr;
+    scratch_bytes_ = 0;
+    const size_t want = align_up(bytes, 1 << 20);
+    s = cuda_status(cudaMalloc(&scratch_, want), "scratch cudaMalloc");
+    if (!s.ok()) return s;
+    scratch_bytes_ = want;
+    return Status::Ok();
+}
+
+// ------------------------------------------------------------------------------------------- ops
+Status CudaBackend::quantize_q8(int gran, const float *x, uint32_t rows, uint32_t k, int8_t *qs, float *d,
+                                int32_t *sums, int32_t *sums16, uint16_t *dact, uint16_t *sact) {
+    if (gran != 32 && gran != 256) return Status::Err(INFR_E_INVALID, fmt("quantize_q8: granularity %d (32 or 256)", gran));
+    if (k == 0 || k % (uint32_t)gran) return Status::Err(INFR_E_INVALID, fmt("quantize_q8: k=%u is not a multiple of %d", k, gran));
+    cudaSetDevice(device_);
+    Status s = cuda_status(launch_quantize_q8(x, (int)rows, (int)k, gran, qs, d, sums, sums16, dact, sact, stream_), "quantize_q8");
+    if (s.ok() && rows) launches_++;
+    return s;
+}
+
+// Lays the quantised rows out in the context scratch: qs | d | sums | sums16.
+Status CudaBackend::quantize_for(int dtype, const float *x, uint32_t rows, uint32_t k, Q8Dev *out) {
+    const int gran = act_gran(dtype);
+    const size_t qs_b = align_up((size_t)rows * k, 256);
+    const size_t d_b = align_up((size_t)rows * (k / gran) * 4, 256);
+    const size_t s_b = align_up((size_t)rows * (k / 32) * 4, 256);
+    const size_t s16_b = dtype == DT_Q6K ? align_up((size_t)rows * (k / 16) * 4, 256) : 0;
+    Status s = ensure_scratch(qs_b + d_b + s_b + s16_b);
+    if (!s.ok()) return s;
+    uint8_t *p = scratch();
+    int8_t *qs = reinterpret_cast<int8_t *>(p);
+    float *d = reinterpret_cast<float *>(p + qs_b);
+    int32_t *sums = reinterpret_cast<int32_t *>(p + qs_b + d_b);
+    int32_t *sums16 = s16_b ? reinterpret_cast<int32_t *>(p + qs_b + d_b + s_b) : nullptr;
+    s = quantize_q8(gran, x, rows, k, qs, d, sums, sums16, nullptr, nullptr);
+    if (!s.ok()) return s;
+    *out = Q8Dev{qs, d, sums, sums16, gran};
+    return Status::Ok();
+}
+
+Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y, uint32_t m, uint32_t in_f,
+                           uint32_t out_f, int act) {
+    if (dtype != DT_Q4K && dtype != DT_Q6K && dtype != DT_Q2_0)
+        return Status::Err(INFR_E_UNSUPPORTED, fmt("linear: weight dtype code %d is not supported (Q4_K, Q6_K, Q2_0)", dtype));
+    if (act != INFR_ACT_INT8 && act != INFR_ACT_F32) return Status::Err(INFR_E_INVALID, fmt("linear: activation mode %d", act));
+    const int be = block_elems(dtype);
+    if (in_f == 0 || in_f % (uint32_t)be) return Status::Err(INFR_E_INVALID, fmt("linear: in_f=%u is not a whole number of %d-element blocks", in_f, be));
+    if (in_f % 16) return Status::Err(INFR_E_INVALID, fmt("linear: in_f=%u must be a multiple of 16", in_f));
+    if (m == 0 || out_f == 0) return Status::Ok();
+    cudaSetDevice(device_);
+    // Decode shapes (m <= 8) run the streaming GEMV; wider batches are walked 8 rows at a time.
+    for (uint32_t r0 = 0; r0 < m; r0 += 8) {
+        const uint32_t mm = m - r0 < 8 ? m - r0 : 8;
+        const float *xr = x + (size_t)r0 * in_f;
+        float *yr = y + (size_t)r0 * out_f;
+        if (act == INFR_ACT_F32) {
+            Status s = cuda_status(launch_gemv_f32(dtype, w, xr, yr, (int)mm, (int)in_f, (int)out_f, dev_, stream_), "gemv_f32");
+            if (!s.ok()) return s;
+            launches_ += 1;
+        } else {
+            Q8Dev a;
+            Status s = quantize_for(dtype, xr, mm, in_f, &a);
+            if (!s.ok()) return s;
+            s = cuda_status(launch_gemv_q8(dtype, w, a, yr, (int)mm, (int)in_f, (int)out_f, nullptr, dev_, stream_), "gemv_q8");
+            if (!s.ok()) return s;
+            launches_ += 1;
+        }
+    }
+    return Status::Ok();
+}
+
+Status CudaBackend::gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f) {
+    if (dtype != DT_Q4K && dtype != DT_Q6K && dtype != DT_Q2_0)
+        return Status::Err(INFR_E_UNSUPPORTED, fmt("gemv_q8: weight dtype code %d", dtype));
+    if (m == 0 || m > 8) return Status::Err(INFR_E_INVALID, fmt("gemv_q8: m=%u (1..8)", m));
+    if (in_f == 0 || in_f % (uint32_t)block_elems(dtype) || in_f % 16) return Status::Err(INFR_E_INVALID, fmt("gemv_q8: in_f=%u", in_f));
+    if (a.gran != act_gran(dtype)) return Status::Err(INFR_E_INVALID, fmt("gemv_q8: activations have granularity %d, dtype needs %d", a.gran, act_gran(dtype)));
+    if (dtype == DT_Q6K && !a.sums16) return Status::Err(INFR_E_INVALID, "gemv_q8: Q6_K needs the per-16 sums");
+    cudaSetDevice(device_);
+    Status s = cuda_status(launch_gemv_q8(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, nullptr, dev_, stream_), "gemv_q8");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+Status CudaBackend::gemv_block_acc(int dtype, const uint8_t *w, const float *x, int32_t *acc, uint32_t in_f, uint32_t out_f) {
+    if (dtype != DT_Q4K && dtype != DT_Q6K && dtype != DT_Q2_0)
+        return Status::Err(INFR_E_UNSUPPORTED, fmt("gemv_block_acc: dtype code %d", dtype));
+    const int be = block_elems(dtype);
+    if (in_f == 0 || in_f % (uint32_t)be || in_f % 16) return Status::Err(INFR_E_INVALID, fmt("gemv_block_acc: in_f=%u", in_f));
+    cudaSetDevice(device_);
+    Q8Dev a;
+    Status s = quantize_for(dtype, x, 1, in_f, &a);
+    if (!s.ok()) return s;
+    s = cuda_status(launch_gemv_q8(dtype, w, a, nullptr, 1, (int)in_f, (int)out_f, acc, dev_, stream_), "gemv_block_acc");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+// ----------------------------------------------------------------------------------------- graphs
+static size_t dtype_bytes(uint32_t dt, uint64_t numel) {
+    const int be = block_elems((int)dt), bb = block_bytes((int)dt);
+    if (dt == DT_I32) return (size_t)numel * 4;
+    if (!bb) return 0;
+    return (size_t)(numel / (uint64_t)be) * (size_t)bb;
+}
+
+Status CudaBackend::compile(const infr_graph_desc &g, infr_cuda_plan **out) {
+    if ((g.n_tensors && !g.tensors) || (g.n_ops && !g.ops)) return Status::Err(INFR_E_INVALID, "compile: null graph arrays");
+    auto plan = new infr_cuda_plan();
+    plan->tensors.assign(g.tensors, g.tensors + g.n_tensors);
+    plan->ops.assign(g.ops, g.ops + g.n_ops);
+    plan->internal.assign(g.n_tensors, nullptr);
+    plan->internal_bytes.assign(g.n_tensors, 0);
+    auto fail = [&](Status s) {
+        free_plan(plan);
+        return s;
+    };
+    for (uint32_t i = 0; i < g.n_ops; i++) {
+        const infr_op_desc &op = g.ops[i];
+        const int nt = op.tag == INFR_OP_LINEAR ? 3 : (op.tag == INFR_OP_MOE_FFN ? 7 : -1);
+        if (nt < 0) return fail(Status::Err(INFR_E_UNSUPPORTED, fmt("compile: op %u has tag %u; this backend runs Linear and MoeFfn", i, op.tag)));
+        for (int k = 0; k < nt; k++)
+            if (op.t[k] >= g.n_tensors) return fail(Status::Err(INFR_E_INVALID, fmt("compile: op %u names tensor %u of %u", i, op.t[k], g.n_tensors)));
+        if (op.tag == INFR_OP_LINEAR) {
+            const uint32_t in_f = op.u[1], w_off = op.u[3];
+            const infr_tensor_decl &w = g.tensors[op.t[1]];
+            if (w.dtype != DT_Q4K && w.dtype != DT_Q6K && w.dtype != DT_Q2_0)
+                return fail(Status::Err(INFR_E_UNSUPPORTED, fmt("compile: Linear weight dtype code %u", w.dtype)));
+            if (in_f == 0 || w_off % in_f) return fail(Status::Err(INFR_E_INVALID, fmt("compile: Linear w_off=%u is not row-aligned (in_f=%u)", w_off, in_f)));
+            if ((uint64_t)w_off + (uint64_t)op.u[2] * in_f > w.numel)
+                return fail(Status::Err(INFR_E_INVALID, fmt("compile: Linear rows [%u,+%u) leave the %llu-element weight", w_off / in_f, op.u[2], (unsigned long long)w.numel)));
+        } else {
+            return fail(Status::Err(INFR_E_UNSUPPORTED, "compile: MoeFfn is not available in this build"));
+        }
+    }
+    cudaSetDevice(device_);
+    for (uint32_t i = 0; i < g.n_tensors; i++) {
+        if (g.tensors[i].kind != INFR_TK_INTERNAL) continue;
+        const size_t bytes = align_up(dtype_bytes(g.tensors[i].dtype, g.tensors[i].numel), 256);
+        if (!bytes) continue;
+        Status s = cuda_status(cudaMalloc(&plan->internal[i], bytes), "plan scratch cudaMalloc");
+        if (!s.ok()) return fail(s);
+        plan->internal_bytes[i] = bytes;
+    }
+    *out = plan;
+    return Status::Ok();
+}
+
+void CudaBackend::free_plan(infr_cuda_plan *p) {
+    if (!p) return;
+    cudaSetDevice(device_);
+    cudaStreamSynchronize(stream_);
+    for (void *q : p->internal)
+        if (q) cudaFree(q);
+    delete p;
+}
+
+Status CudaBackend::execute(infr_cuda_plan *plan, infr_cuda_buf *const *bindings, uint32_t n) {
+    if (!plan) return Status::Err(INFR_E_INVALID, "execute: null plan");
+    cudaSetDevice(device_);
+    const uint32_t nt = (uint32_t)plan->tensors.size();
+    // Provision: Internal handles are zeroed backend scratch (crates/infr-core/src/exec.rs:53-92).
+    for (uint32_t i = 0; i < nt; i++)
+        if (plan->internal[i]) {
+            Status s = cuda_status(cudaMemsetAsync(plan->internal[i], 0, plan->internal_bytes[i], stream_), "zero internal");
+            if (!s.ok()) return s;
+        }
+    auto resolve = [&](uint32_t id, size_t need, const char *role, DevSpan *out) -> Status {
+        const infr_tensor_decl &d = plan->tensors[id];
+        if (d.kind == INFR_TK_INTERNAL) {
+            *out = DevSpan{static_cast<uint8_t *>(plan->internal[id]), plan->internal_bytes[id]};
+        } else {
+            if (id >= n || !bindings || !bindings[id])
+                return Status::Err(INFR_E_INVALID, fmt("execute: %s handle %u is unbound", role, id));
+            *out = DevSpan{static_cast<uint8_t *>(bindings[id]->ptr), bindings[id]->len};
+        }
+        if (out->bytes < need)
+            return Status::Err(INFR_E_INVALID, fmt("execute: %s handle %u holds %zu bytes, op needs %zu", role, id, out->bytes, need));
+        return Status::Ok();
+    };
+    for (size_t i = 0; i < plan->ops.size(); i++) {
+        const infr_op_desc &op = plan->ops[i];
+        if (op.tag == INFR_OP_LINEAR) {
+            const uint32_t m = op.u[0], in_f = op.u[1], out_f = op.u[2], w_off = op.u[3];
+            const int dt = (int)plan->tensors[op.t[1]].dtype;
+            const size_t bpr = (size_t)(in_f / block_elems(dt)) * block_bytes(dt);
+            const size_t row0 = w_off / in_f;
+            DevSpan x, w, y;
+            Status s;
+            if (!(s = resolve(op.t[0], (size_t)m * in_f * 4, "Linear x", &x)).ok()) return s;
+            if (!(s = resolve(op.t[1], (row0 + out_f) * bpr, "Linear weight", &w)).ok()) return s;
+            if (!(s = resolve(op.t[2], (size_t)m * out_f * 4, "Linear dst", &y)).ok()) return s;
+            s = linear(dt, w.ptr + row0 * bpr, reinterpret_cast<const float *>(x.ptr), reinterpret_cast<float *>(y.ptr), m, in_f,
+                       out_f, reference_ ? INFR_ACT_F32 : INFR_ACT_INT8);
+            if (!s.ok()) return s;
+        } else {
+            return Status::Err(INFR_E_UNSUPPORTED, fmt("execute: op %zu tag %u", i, op.tag));
+        }
+    }
+    // Outputs live in their bound device buffers already; the caller's download (or sync) orders
+    // after this stream's work, as Backend::execute + Backend::download do on the other backends.
+    return Status::Ok();
+}
+
+// ------------------------------------------------------------------------------ capture and timing
+Status CudaBackend::capture_begin() {
+    if (capturing_) return Status::Err(INFR_E_INVALID, "capture_begin: already capturing");
+    cudaSetDevice(device_);
+    Status s = cuda_status(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    if (s.ok()) capturing_ = true;
+    return s;
+}
+
+Status CudaBackend::capture_end(infr_cuda_graph **out) {
+    if (!capturing_) return Status::Err(INFR_E_INVALID, "capture_end: not capturing");
+    capturing_ = false;
+    cudaSetDevice(device_);
+    auto *g = new infr_cuda_graph();
+    Status s = cuda_status(cudaStreamEndCapture(stream_, &g->graph), "cudaStreamEndCapture");
+    if (s.ok()) s = cuda_status(cudaGraphInstantiate(&g->exec, g->graph, 0), "cudaGraphInstantiate");
+    if (s.ok()) {
+        size_t nn = 0;
+        cudaGraphGetNodes(g->graph, nullptr, &nn);
+        std::vector<cudaGraphNode_t> nodes(nn);
+        if (nn) cudaGraphGetNodes(g->graph, nodes.data(), &nn);
+        for (auto nd : nodes) {
+            cudaGraphNodeType ty;
+            if (cudaGraphNodeGetType(nd, &ty) == cudaSuccess && ty == cudaGraphNodeTypeKernel) g->kernel_nodes++;
+        }
+    }
+    if (!s.ok()) {
+        graph_free(g);
+        return s;
+    }
+    *out = g;
+    return Status::Ok();
+}
+
+Status CudaBackend::graph_launch(infr_cuda_graph *g) {
+    if (!g || !g->exec) return Status::Err(INFR_E_INVALID, "graph_launch: null graph");
+    cudaSetDevice(device_);
+    Status s = cuda_status(cudaGraphLaunch(g->exec, stream_), "cudaGraphLaunch");
+    if (s.ok()) launches_ += g->kernel_nodes;
+    return s;
+}
+
+void CudaBackend::graph_free(infr_cuda_graph *g) {
+    if (!g) return;
+    cudaSetDevice(device_);
+    cudaStreamSynchronize(stream_);
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+}
+
+Status CudaBackend::timer_start() {
+    cudaSetDevice(device_);
+    return cuda_status(cudaEventRecord(ev0_, stream_), "cudaEventRecord");
+}
+
+Status CudaBackend::timer_stop(float *ms) {
+    if (!ms) return Status::Err(INFR_E_INVALID, "timer_stop: null output");
+    cudaSetDevice(device_);
+    Status s = cuda_status(cudaEventRecord(ev1_, stream_), "cudaEventRecord");
+    if (s.ok()) s = cuda_status(cudaEventSynchronize(ev1_), "cudaEventSynchronize");
+    if (s.ok()) s = cuda_status(cudaEventElapsedTime(ms, ev0_, ev1_), "cudaEventElapsedTime");
+    return s;
+}
+
+Status CudaBackend::flush_l2() {
+    cudaSetDevice(device_);
+    if (!flush_) {
+        if (capturing_) return Status::Err(INFR_E_INVALID, "flush_l2: first use during stream capture");
+        flush_bytes_ = align_up(dev_.l2_bytes * 2 + (64u << 20), 1 << 20);
+        Status s = cuda_status(cudaMalloc(&flush_, flush_bytes_), "flush cudaMalloc");
+        if (!s.ok()) return s;
+    }
+    Status s = cuda_status(launch_fill_u32(static_cast<uint32_t *>(flush_), flush_bytes_ / 4, (uint32_t)launches_, stream_), "flush_l2");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+}  // namespace infr

@@ -1,0 +1,130 @@
+// Host side of the CUDA backend: a C++ mirror of the reference's `trait Backend`
+// (crates/infr-core/src/backend.rs:486-662) with the same method names, argument meaning and error
+// behaviour (errors are returned, never thrown across the C ABI; bad sizes are errors, not panics —
+// `check_copy_bytes`, backend.rs:23-30).  The C ABI in c_api.cpp is a thin shell over this class.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/infr_cuda.h"
+#include "kernels.h"
+
+// Opaque handles of the C ABI.
+struct infr_cuda_buf {
+    void *ptr = nullptr;
+    size_t len = 0;  // logical size in bytes (Buffer::len_bytes, backend.rs:387-398)
+    int usage = 0;
+    uint64_t uid = 0;  // never reused: derived-data caches key on this, not on the address
+};
+
+struct infr_cuda_plan {
+    std::vector<infr_tensor_decl> tensors;
+    std::vector<infr_op_desc> ops;
+    std::vector<void *> internal;  // device scratch of every Internal handle (null for the others)
+    std::vector<size_t> internal_bytes;
+};
+
+struct infr_cuda_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernel_nodes = 0;
+};
+
+namespace infr {
+
+struct Status {
+    int32_t code = INFR_OK;
+    std::string msg;
+    bool ok() const { return code == INFR_OK; }
+    static Status Ok() { return {}; }
+    static Status Err(int32_t c, std::string m) { return {c, std::move(m)}; }
+};
+
+// Raw device view of an activation / weight operand (a buffer handle plus a byte offset).
+struct DevSpan {
+    uint8_t *ptr;
+    size_t bytes;
+};
+
+class CudaBackend {
+public:
+    static Status create(const infr_cuda_opts &opts, CudaBackend **out);
+    ~CudaBackend();
+
+    const char *name() const { return "cuda-sm100a"; }
+    infr_cuda_caps capabilities() const;
+
+    // ---- memory ----
+    Status alloc(size_t bytes, int usage, bool zero, infr_cuda_buf **out);
+    void free_buffer(infr_cuda_buf *b);
+    Status upload(infr_cuda_buf *dst, size_t dst_off, const void *src, size_t bytes);
+    Status download(const infr_cuda_buf *src, void *dst, size_t bytes);
+    Status copy_buffer(const infr_cuda_buf *src, infr_cuda_buf *dst, size_t bytes);
+    Status sync();
+
+    // ---- graphs ----
+    Status compile(const infr_graph_desc &g, infr_cuda_plan **out);
+    void free_plan(infr_cuda_plan *p);
+    Status execute(infr_cuda_plan *plan, infr_cuda_buf *const *bindings, uint32_t n);
+
+    // ---- ops (device pointers already validated by the callers above / the C ABI) ----
+    Status quantize_q8(int gran, const float *x, uint32_t rows, uint32_t k, int8_t *qs, float *d,
+                       int32_t *sums, int32_t *sums16, uint16_t *dact, uint16_t *sact);
+    Status linear(int dtype, const uint8_t *w, const float *x, float *y, uint32_t m, uint32_t in_f,
+                  uint32_t out_f, int act);
+    Status gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f);
+    Status gemv_block_acc(int dtype, const uint8_t *w, const float *x, int32_t *acc, uint32_t in_f,
+                          uint32_t out_f);
+
+    // ---- capture / timing ----
+    Status capture_begin();
+    Status capture_end(infr_cuda_graph **out);
+    Status graph_launch(infr_cuda_graph *g);
+    void graph_free(infr_cuda_graph *g);
+    Status timer_start();
+    Status timer_stop(float *ms);
+    Status flush_l2();
+    uint64_t launch_count() const { return launches_; }
+
+    std::mutex &mutex() { return mu_; }
+    void set_error(const Status &s) { last_error_ = s.msg; }
+    const std::string &last_error() const { return last_error_; }
+    bool reference() const { return reference_; }
+    cudaStream_t stream() const { return stream_; }
+    const DeviceInfo &device_info() const { return dev_; }
+    Status cuda_status(cudaError_t e, const char *what);
+    // Grows the context's activation scratch; refused while capturing.
+    Status ensure_scratch(size_t bytes);
+    uint8_t *scratch() const { return static_cast<uint8_t *>(scratch_); }
+    void count_launches(uint64_t n) { launches_ += n; }
+
+private:
+    CudaBackend() = default;
+    Status quantize_for(int dtype, const float *x, uint32_t rows, uint32_t k, Q8Dev *out);
+
+    int device_ = 0;
+    bool reference_ = false;
+    cudaStream_t stream_ = nullptr;
+    cudaDeviceProp prop_{};
+    DeviceInfo dev_{};
+    std::mutex mu_;
+    std::string last_error_;
+    void *scratch_ = nullptr;
+    size_t scratch_bytes_ = 0;
+    void *flush_ = nullptr;
+    size_t flush_bytes_ = 0;
+    cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+    bool capturing_ = false;
+    uint64_t launches_ = 0;
+    uint64_t next_uid_ = 1;
+};
+
+}  // namespace infr
+
+struct infr_cuda_ctx {
+    infr::CudaBackend *be;
+};

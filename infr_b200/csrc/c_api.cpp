@@ -1,0 +1,287 @@
+// extern "C" shell of libinfr_cuda.so: argument checks, locking, error text; no arithmetic here.
+#include <cstring>
+#include <string>
+
+#include "backend.h"
+
+using infr::CudaBackend;
+using infr::Status;
+
+namespace {
+thread_local std::string g_create_error;
+
+int32_t finish(infr_cuda_ctx *ctx, const Status &s) {
+    if (!s.ok() && ctx && ctx->be) ctx->be->set_error(s);
+    return s.code;
+}
+
+#define INFR_CTX_OR_RETURN(ctx)                  \
+    if (!(ctx) || !(ctx)->be) return INFR_E_INVALID; \
+    std::lock_guard<std::mutex> lock_((ctx)->be->mutex())
+
+// Checks that [off, off+need) lies inside the buffer and returns the device address.
+Status span(const infr_cuda_buf *b, size_t need, const char *what, uint8_t **out) {
+    if (!b) return Status::Err(INFR_E_INVALID, std::string(what) + ": null buffer");
+    if (b->len < need)
+        return Status::Err(INFR_E_INVALID, std::string(what) + ": buffer holds " + std::to_string(b->len) +
+                                               " bytes, call needs " + std::to_string(need));
+    *out = static_cast<uint8_t *>(b->ptr);
+    return Status::Ok();
+}
+}  // namespace
+
+extern "C" {
+
+int32_t infr_cuda_create(const infr_cuda_opts *opts, infr_cuda_ctx **out) {
+    if (!out) return INFR_E_INVALID;
+    infr_cuda_opts o;
+    memset(&o, 0, sizeof o);
+    if (opts) o = *opts;
+    CudaBackend *be = nullptr;
+    Status s = CudaBackend::create(o, &be);
+    if (!s.ok()) {
+        g_create_error = s.msg;
+        return s.code;
+    }
+    *out = new infr_cuda_ctx{be};
+    return INFR_OK;
+}
+
+void infr_cuda_destroy(infr_cuda_ctx *ctx) {
+    if (!ctx) return;
+    delete ctx->be;
+    delete ctx;
+}
+
+int32_t infr_cuda_get_caps(infr_cuda_ctx *ctx, infr_cuda_caps *out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (!out) return finish(ctx, Status::Err(INFR_E_INVALID, "get_caps: null output"));
+    *out = ctx->be->capabilities();
+    return INFR_OK;
+}
+
+int32_t infr_cuda_last_error(infr_cuda_ctx *ctx, char *dst, size_t cap) {
+    const std::string &m = (ctx && ctx->be) ? ctx->be->last_error() : g_create_error;
+    if (dst && cap) {
+        const size_t n = m.size() < cap - 1 ? m.size() : cap - 1;
+        memcpy(dst, m.data(), n);
+        dst[n] = 0;
+    }
+    return (int32_t)m.size();
+}
+
+int32_t infr_cuda_alloc(infr_cuda_ctx *ctx, size_t bytes, int32_t usage, infr_cuda_buf **out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (!out) return finish(ctx, Status::Err(INFR_E_INVALID, "alloc: null output"));
+    return finish(ctx, ctx->be->alloc(bytes, usage, true, out));
+}
+
+int32_t infr_cuda_alloc_uninit(infr_cuda_ctx *ctx, size_t bytes, int32_t usage, infr_cuda_buf **out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (!out) return finish(ctx, Status::Err(INFR_E_INVALID, "alloc_uninit: null output"));
+    return finish(ctx, ctx->be->alloc(bytes, usage, false, out));
+}
+
+void infr_cuda_free(infr_cuda_ctx *ctx, infr_cuda_buf *buf) {
+    if (!ctx || !ctx->be) return;
+    std::lock_guard<std::mutex> lock_(ctx->be->mutex());
+    ctx->be->free_buffer(buf);
+}
+
+size_t infr_cuda_buf_len(const infr_cuda_buf *buf) { return buf ? buf->len : 0; }
+uint64_t infr_cuda_buf_device_ptr(const infr_cuda_buf *buf) { return buf ? (uint64_t)(uintptr_t)buf->ptr : 0; }
+
+int32_t infr_cuda_upload(infr_cuda_ctx *ctx, infr_cuda_buf *dst, const void *src, size_t bytes) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->upload(dst, 0, src, bytes));
+}
+
+int32_t infr_cuda_upload_at(infr_cuda_ctx *ctx, infr_cuda_buf *dst, size_t dst_off, const void *src, size_t bytes) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->upload(dst, dst_off, src, bytes));
+}
+
+int32_t infr_cuda_download(infr_cuda_ctx *ctx, const infr_cuda_buf *src, void *dst, size_t bytes) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->download(src, dst, bytes));
+}
+
+int32_t infr_cuda_copy(infr_cuda_ctx *ctx, const infr_cuda_buf *src, infr_cuda_buf *dst, size_t bytes) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->copy_buffer(src, dst, bytes));
+}
+
+int32_t infr_cuda_host_alloc(infr_cuda_ctx *ctx, size_t bytes, void **out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (!out) return finish(ctx, Status::Err(INFR_E_INVALID, "host_alloc: null output"));
+    return finish(ctx, ctx->be->cuda_status(cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault), "cudaHostAlloc"));
+}
+
+void infr_cuda_host_free(infr_cuda_ctx *ctx, void *p) {
+    if (!ctx || !ctx->be || !p) return;
+    std::lock_guard<std::mutex> lock_(ctx->be->mutex());
+    cudaFreeHost(p);
+}
+
+int32_t infr_cuda_sync(infr_cuda_ctx *ctx) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->sync());
+}
+
+int32_t infr_cuda_compile(infr_cuda_ctx *ctx, const infr_graph_desc *graph, infr_cuda_plan **out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (!graph || !out) return finish(ctx, Status::Err(INFR_E_INVALID, "compile: null argument"));
+    return finish(ctx, ctx->be->compile(*graph, out));
+}
+
+void infr_cuda_plan_free(infr_cuda_ctx *ctx, infr_cuda_plan *plan) {
+    if (!ctx || !ctx->be) return;
+    std::lock_guard<std::mutex> lock_(ctx->be->mutex());
+    ctx->be->free_plan(plan);
+}
+
+int32_t infr_cuda_execute(infr_cuda_ctx *ctx, infr_cuda_plan *plan, infr_cuda_buf *const *bindings, uint32_t n) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->execute(plan, bindings, n));
+}
+
+int32_t infr_cuda_quantize_q8(infr_cuda_ctx *ctx, int32_t gran, const infr_cuda_buf *x, uint32_t rows, uint32_t k,
+                              infr_cuda_buf *qs, infr_cuda_buf *d, infr_cuda_buf *sums, infr_cuda_buf *sums16) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (gran != 32 && gran != 256) return finish(ctx, Status::Err(INFR_E_INVALID, "quantize_q8: granularity must be 32 or 256"));
+    uint8_t *px, *pq, *pd, *ps, *p16 = nullptr;
+    Status s;
+    const size_t n = (size_t)rows * k;
+    if (!(s = span(x, n * 4, "quantize_q8 x", &px)).ok() || !(s = span(qs, n, "quantize_q8 qs", &pq)).ok() ||
+        !(s = span(d, n / (size_t)gran * 4, "quantize_q8 d", &pd)).ok() ||
+        !(s = span(sums, n / 32 * 4, "quantize_q8 sums", &ps)).ok())
+        return finish(ctx, s);
+    if (sums16 && !(s = span(sums16, n / 16 * 4, "quantize_q8 sums16", &p16)).ok()) return finish(ctx, s);
+    return finish(ctx, ctx->be->quantize_q8(gran, (const float *)px, rows, k, (int8_t *)pq, (float *)pd, (int32_t *)ps,
+                                            (int32_t *)p16, nullptr, nullptr));
+}
+
+int32_t infr_cuda_quantize_q8_1(infr_cuda_ctx *ctx, const infr_cuda_buf *x, uint32_t rows, uint32_t k, infr_cuda_buf *qs,
+                                infr_cuda_buf *dact, infr_cuda_buf *sact) {
+    INFR_CTX_OR_RETURN(ctx);
+    uint8_t *px, *pq, *pd, *ps;
+    Status s;
+    const size_t n = (size_t)rows * k;
+    if (!(s = span(x, n * 4, "quantize_q8_1 x", &px)).ok() || !(s = span(qs, n, "quantize_q8_1 qs", &pq)).ok() ||
+        !(s = span(dact, n / 32 * 2, "quantize_q8_1 dact", &pd)).ok() ||
+        !(s = span(sact, n / 32 * 2, "quantize_q8_1 sact", &ps)).ok())
+        return finish(ctx, s);
+    // The f32 scales and i32 sums the kernel also produces go to the context scratch.
+    const size_t nb = n / 32;
+    if (!(s = ctx->be->ensure_scratch(nb * 8 + 512)).ok()) return finish(ctx, s);
+    float *d32 = reinterpret_cast<float *>(ctx->be->scratch());
+    int32_t *s32 = reinterpret_cast<int32_t *>(ctx->be->scratch() + (nb * 4 + 255) / 256 * 256);
+    return finish(ctx, ctx->be->quantize_q8(32, (const float *)px, rows, k, (int8_t *)pq, d32, s32, nullptr, (uint16_t *)pd,
+                                            (uint16_t *)ps));
+}
+
+static Status linear_args(const infr_cuda_buf *w, uint64_t w_off, const infr_cuda_buf *x, const infr_cuda_buf *y, int32_t dtype,
+                          uint32_t m, uint32_t in_f, uint32_t out_f, uint8_t **pw, uint8_t **px, uint8_t **py) {
+    const int be = infr::block_elems(dtype), bb = infr::block_bytes(dtype);
+    if (!bb || (dtype != INFR_DT_Q4K && dtype != INFR_DT_Q6K && dtype != INFR_DT_Q2_0))
+        return Status::Err(INFR_E_UNSUPPORTED, "weight dtype code " + std::to_string(dtype) + " is not supported (Q4_K, Q6_K, Q2_0)");
+    if (in_f == 0 || in_f % (uint32_t)be) return Status::Err(INFR_E_INVALID, "in_f is not a whole number of weight blocks");
+    if (w_off % in_f) return Status::Err(INFR_E_INVALID, "w_off is not row-aligned");
+    const size_t bpr = (size_t)(in_f / (uint32_t)be) * (size_t)bb;
+    const size_t row0 = (size_t)(w_off / in_f);
+    Status s;
+    if (!(s = span(w, (row0 + out_f) * bpr, "weight", pw)).ok()) return s;
+    *pw += row0 * bpr;
+    if (!(s = span(x, (size_t)m * in_f * 4, "x", px)).ok()) return s;
+    if (py && !(s = span(y, (size_t)m * out_f * 4, "y", py)).ok()) return s;
+    return Status::Ok();
+}
+
+int32_t infr_cuda_gemv(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off, const infr_cuda_buf *x,
+                       infr_cuda_buf *y, uint32_t m, uint32_t in_f, uint32_t out_f, int32_t act) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (m > 8) return finish(ctx, Status::Err(INFR_E_INVALID, "gemv: m must be <= 8 (use infr_cuda_linear)"));
+    uint8_t *pw, *px, *py;
+    Status s = linear_args(w, w_off, x, y, dtype, m, in_f, out_f, &pw, &px, &py);
+    if (!s.ok()) return finish(ctx, s);
+    return finish(ctx, ctx->be->linear(dtype, pw, (const float *)px, (float *)py, m, in_f, out_f, act));
+}
+
+int32_t infr_cuda_linear(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off, const infr_cuda_buf *x,
+                         infr_cuda_buf *y, uint32_t m, uint32_t in_f, uint32_t out_f, int32_t act) {
+    INFR_CTX_OR_RETURN(ctx);
+    uint8_t *pw, *px, *py;
+    Status s = linear_args(w, w_off, x, y, dtype, m, in_f, out_f, &pw, &px, &py);
+    if (!s.ok()) return finish(ctx, s);
+    return finish(ctx, ctx->be->linear(dtype, pw, (const float *)px, (float *)py, m, in_f, out_f, act));
+}
+
+int32_t infr_cuda_gemv_q8(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off, const infr_cuda_buf *qs,
+                          const infr_cuda_buf *d, const infr_cuda_buf *sums, const infr_cuda_buf *sums16, infr_cuda_buf *y,
+                          uint32_t m, uint32_t in_f, uint32_t out_f) {
+    INFR_CTX_OR_RETURN(ctx);
+    uint8_t *pw, *pq, *pd, *ps, *p16 = nullptr, *py;
+    const int be = infr::block_elems(dtype), bb = infr::block_bytes(dtype);
+    if (dtype != INFR_DT_Q4K && dtype != INFR_DT_Q6K && dtype != INFR_DT_Q2_0)
+        return finish(ctx, Status::Err(INFR_E_UNSUPPORTED, "gemv_q8: weight dtype is not supported"));
+    if (in_f == 0 || in_f % (uint32_t)be || w_off % in_f) return finish(ctx, Status::Err(INFR_E_INVALID, "gemv_q8: in_f / w_off"));
+    const int gran = infr::act_gran(dtype);
+    const size_t bpr = (size_t)(in_f / (uint32_t)be) * (size_t)bb, row0 = (size_t)(w_off / in_f), n = (size_t)m * in_f;
+    Status s;
+    if (!(s = span(w, (row0 + out_f) * bpr, "gemv_q8 weight", &pw)).ok() || !(s = span(qs, n, "gemv_q8 qs", &pq)).ok() ||
+        !(s = span(d, n / (size_t)gran * 4, "gemv_q8 d", &pd)).ok() || !(s = span(sums, n / 32 * 4, "gemv_q8 sums", &ps)).ok() ||
+        !(s = span(y, (size_t)m * out_f * 4, "gemv_q8 y", &py)).ok())
+        return finish(ctx, s);
+    if (sums16 && !(s = span(sums16, n / 16 * 4, "gemv_q8 sums16", &p16)).ok()) return finish(ctx, s);
+    infr::Q8Dev a{(const int8_t *)pq, (const float *)pd, (const int32_t *)ps, (const int32_t *)p16, gran};
+    return finish(ctx, ctx->be->gemv_q8(dtype, pw + row0 * bpr, a, (float *)py, m, in_f, out_f));
+}
+
+int32_t infr_cuda_gemv_block_acc(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off,
+                                 const infr_cuda_buf *x, infr_cuda_buf *acc, uint32_t in_f, uint32_t out_f) {
+    INFR_CTX_OR_RETURN(ctx);
+    uint8_t *pw, *px, *pa;
+    Status s = linear_args(w, w_off, x, nullptr, dtype, 1, in_f, out_f, &pw, &px, nullptr);
+    if (!s.ok()) return finish(ctx, s);
+    const size_t per_row = dtype == INFR_DT_Q4K ? (size_t)in_f / 256 * 2 : (dtype == INFR_DT_Q6K ? (size_t)in_f / 256 : (size_t)in_f / 32);
+    if (!(s = span(acc, (size_t)out_f * per_row * 4, "acc", &pa)).ok()) return finish(ctx, s);
+    return finish(ctx, ctx->be->gemv_block_acc(dtype, pw, (const float *)px, (int32_t *)pa, in_f, out_f));
+}
+
+int32_t infr_cuda_capture_begin(infr_cuda_ctx *ctx) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->capture_begin());
+}
+int32_t infr_cuda_capture_end(infr_cuda_ctx *ctx, infr_cuda_graph **out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (!out) return finish(ctx, Status::Err(INFR_E_INVALID, "capture_end: null output"));
+    return finish(ctx, ctx->be->capture_end(out));
+}
+int32_t infr_cuda_graph_launch(infr_cuda_ctx *ctx, infr_cuda_graph *graph) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->graph_launch(graph));
+}
+void infr_cuda_graph_free(infr_cuda_ctx *ctx, infr_cuda_graph *graph) {
+    if (!ctx || !ctx->be) return;
+    std::lock_guard<std::mutex> lock_(ctx->be->mutex());
+    ctx->be->graph_free(graph);
+}
+int32_t infr_cuda_timer_start(infr_cuda_ctx *ctx) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->timer_start());
+}
+int32_t infr_cuda_timer_stop(infr_cuda_ctx *ctx, float *ms) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->timer_stop(ms));
+}
+int32_t infr_cuda_flush_l2(infr_cuda_ctx *ctx) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->flush_l2());
+}
+uint64_t infr_cuda_launch_count(infr_cuda_ctx *ctx) {
+    if (!ctx || !ctx->be) return 0;
+    std::lock_guard<std::mutex> lock_(ctx->be->mutex());
+    return ctx->be->launch_count();
+}
+
+}  // extern "C"

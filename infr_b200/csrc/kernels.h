@@ -1,0 +1,53 @@
+// Internal launch interface between the host backend and the sm_100a kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace infr {
+
+enum : int { DT_F32 = 0, DT_F16 = 1, DT_I32 = 3, DT_Q4K = 12, DT_Q6K = 14, DT_Q2_0 = 27 };
+
+inline int block_elems(int dt) { return dt == DT_Q2_0 ? 64 : (dt == DT_Q4K || dt == DT_Q6K ? 256 : 1); }
+inline int block_bytes(int dt) {
+    switch (dt) {
+    case DT_Q4K: return 144;
+    case DT_Q6K: return 210;
+    case DT_Q2_0: return 18;
+    case DT_F32: return 4;
+    case DT_F16: return 2;
+    default: return 0;
+    }
+}
+// Activation granularity of the production int8 path: 256 for the K-quants, 32 for Q2_0
+// (crates/infr-cpu/src/lib.rs:1043-1076).
+inline int act_gran(int dt) { return dt == DT_Q2_0 ? 32 : 256; }
+
+// Quantised activation rows in device memory (struct Q8 / Q8x32, crates/infr-cpu/src/quant.rs:8-25, :90-95).
+struct Q8Dev {
+    const int8_t *qs;      // [rows, k]
+    const float *d;        // [rows, k/gran]
+    const int32_t *sums;   // [rows, k/32]
+    const int32_t *sums16; // [rows, k/16] or null
+    int gran;
+};
+
+struct DeviceInfo {
+    int sm_count;
+    int max_smem_optin;
+    size_t l2_bytes;
+};
+
+cudaError_t launch_quantize_q8(const float *x, int rows, int k, int gran, int8_t *qs, float *d,
+                               int32_t *sums, int32_t *sums16, uint16_t *dact, uint16_t *sact,
+                               cudaStream_t st);
+
+// y[m,out_f] (m <= 8) from int8 activations; acc_out != null switches to the accumulator dump (m = 1).
+cudaError_t launch_gemv_q8(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
+                           int32_t *acc_out, const DeviceInfo &dev, cudaStream_t st);
+// y[m,out_f] (m <= 8) from f32 activations and dequantised weights.
+cudaError_t launch_gemv_f32(int dt, const uint8_t *w, const float *x, float *y, int m, int in_f, int out_f,
+                            const DeviceInfo &dev, cudaStream_t st);
+
+cudaError_t launch_fill_u32(uint32_t *p, size_t n, uint32_t v, cudaStream_t st);
+
+}  // namespace infr

@@ -207,7 +207,7 @@ def run_b200(args):
 
     rank, world, local, dist = _dist_setup(args.gpus)
     hbm_peak, peak_src = _peaks()
-    be = infr_b200.CudaBackend(device=local)
+    be = infr_b200.CudaBackend(device=local, _dev_opts=[int(os.environ.get('INFR_DEV_GEMV_IMPL', '0'))])
     caps = be.capabilities()
     steps, warmup = args.steps, max(args.warmup, 3)
 

@@ -245,10 +245,12 @@ class CudaGraph:
 class CudaBackend:
     """`impl Backend for CudaBackend` over the C ABI."""
 
-    def __init__(self, device: int = 0, reference: bool = False):
+    def __init__(self, device: int = 0, reference: bool = False, _dev_opts: Sequence[int] = ()):
         self.L = load_library()
         self.ctx = None
         opts = _Opts(device=device, reference=int(reference))
+        for i, v in enumerate(_dev_opts):
+            opts.reserved[i] = int(v)
         ctx = C.c_void_p()
         rc = self.L.infr_cuda_create(C.byref(opts), C.byref(ctx))
         if rc != 0:

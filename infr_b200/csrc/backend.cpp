@@ -58,7 +58,24 @@ Status CudaBackend::create(const infr_cuda_opts &opts, CudaBackend **out) {
         delete be;
         return s;
     }
+    be->gemv_impl_ = opts.reserved[0];
+    if (!(s = be->cuda_status(cudaHostAlloc((void **)&be->status_host_, 64, cudaHostAllocMapped), "cudaHostAlloc")).ok() ||
+        !(s = be->cuda_status(cudaHostGetDevicePointer((void **)&be->status_dev_, be->status_host_, 0), "cudaHostGetDevicePointer")).ok()) {
+        delete be;
+        return s;
+    }
+    *be->status_host_ = 0;
     *out = be;
+    return Status::Ok();
+}
+
+// A kernel whose bounded wait expired leaves a non-zero word in mapped host memory.
+Status CudaBackend::check_device_status() {
+    if (status_host_ && *(volatile uint32_t *)status_host_) {
+        const uint32_t v = *(volatile uint32_t *)status_host_;
+        *(volatile uint32_t *)status_host_ = 0;
+        return Status::Err(INFR_E_TIMEOUT, fmt("a device-side wait expired (kernel status %u); results of this stream are invalid", v));
+    }
     return Status::Ok();
 }
 
@@ -67,6 +84,7 @@ CudaBackend::~CudaBackend() {
     if (stream_) cudaStreamSynchronize(stream_);
     if (scratch_) cudaFree(scratch_);
     if (flush_) cudaFree(flush_);
+    if (status_host_) cudaFreeHost(status_host_);
     if (ev0_) cudaEventDestroy(ev0_);
     if (ev1_) cudaEventDestroy(ev1_);
     if (stream_) cudaStreamDestroy(stream_);
@@ -146,7 +164,8 @@ Status CudaBackend::download(const infr_cuda_buf *src, void *dst, size_t bytes) 
     cudaSetDevice(device_);
     Status s = cuda_status(cudaMemcpyAsync(dst, src->ptr, bytes, cudaMemcpyDeviceToHost, stream_), "download");
     if (!s.ok()) return s;
-    return cuda_status(cudaStreamSynchronize(stream_), "download sync");
+    s = cuda_status(cudaStreamSynchronize(stream_), "download sync");
+    return s.ok() ? check_device_status() : s;
 }
 
 Status CudaBackend::copy_buffer(const infr_cuda_buf *src, infr_cuda_buf *dst, size_t bytes) {
@@ -160,7 +179,8 @@ Status CudaBackend::copy_buffer(const infr_cuda_buf *src, infr_cuda_buf *dst, si
 Status CudaBackend::sync() {
     if (capturing_) return Status::Err(INFR_E_INVALID, "sync during stream capture");
     cudaSetDevice(device_);
-    return cuda_status(cudaStreamSynchronize(stream_), "sync");
+    Status s = cuda_status(cudaStreamSynchronize(stream_), "sync");
+    return s.ok() ? check_device_status() : s;
 }
 
 Status CudaBackend::ensure_scratch(size_t bytes) {
@@ -234,7 +254,9 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
             Q8Dev a;
             Status s = quantize_for(dtype, xr, mm, in_f, &a);
             if (!s.ok()) return s;
-            s = cuda_status(launch_gemv_q8(dtype, w, a, yr, (int)mm, (int)in_f, (int)out_f, nullptr, dev_, stream_), "gemv_q8");
+            s = cuda_status(gemv_impl_ == 1 ? launch_gemv_q8(dtype, w, a, yr, (int)mm, (int)in_f, (int)out_f, nullptr, dev_, stream_)
+                                            : launch_gemv_stream(dtype, w, a, yr, (int)mm, (int)in_f, (int)out_f, dev_, status_dev_, stream_),
+                            "gemv_q8");
             if (!s.ok()) return s;
             launches_ += 1;
         }
@@ -250,7 +272,9 @@ Status CudaBackend::gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *
     if (a.gran != act_gran(dtype)) return Status::Err(INFR_E_INVALID, fmt("gemv_q8: activations have granularity %d, dtype needs %d", a.gran, act_gran(dtype)));
     if (dtype == DT_Q6K && !a.sums16) return Status::Err(INFR_E_INVALID, "gemv_q8: Q6_K needs the per-16 sums");
     cudaSetDevice(device_);
-    Status s = cuda_status(launch_gemv_q8(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, nullptr, dev_, stream_), "gemv_q8");
+    Status s = cuda_status(gemv_impl_ == 1 ? launch_gemv_q8(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, nullptr, dev_, stream_)
+                                           : launch_gemv_stream(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_),
+                           "gemv_q8");
     if (s.ok()) launches_++;
     return s;
 }
@@ -437,7 +461,7 @@ Status CudaBackend::timer_stop(float *ms) {
     Status s = cuda_status(cudaEventRecord(ev1_, stream_), "cudaEventRecord");
     if (s.ok()) s = cuda_status(cudaEventSynchronize(ev1_), "cudaEventSynchronize");
     if (s.ok()) s = cuda_status(cudaEventElapsedTime(ms, ev0_, ev1_), "cudaEventElapsedTime");
-    return s;
+    return s.ok() ? check_device_status() : s;
 }
 
 Status CudaBackend::flush_l2() {

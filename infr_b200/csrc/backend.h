@@ -121,6 +121,10 @@ private:
     bool capturing_ = false;
     uint64_t launches_ = 0;
     uint64_t next_uid_ = 1;
+    uint32_t *status_host_ = nullptr;  // pinned + mapped: kernels report expired waits here
+    uint32_t *status_dev_ = nullptr;
+    int gemv_impl_ = 0;                // 0 = bulk-copy ring kernel, 1 = direct-load kernel
+    Status check_device_status();
 };
 
 }  // namespace infr

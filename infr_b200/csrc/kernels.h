@@ -44,6 +44,10 @@ cudaError_t launch_quantize_q8(const float *x, int rows, int k, int gran, int8_t
 // y[m,out_f] (m <= 8) from int8 activations; acc_out != null switches to the accumulator dump (m = 1).
 cudaError_t launch_gemv_q8(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
                            int32_t *acc_out, const DeviceInfo &dev, cudaStream_t st);
+// Same contract as launch_gemv_q8 without the accumulator dump: the bulk-copy ring kernel.  `status`
+// is a device-visible word the kernel sets non-zero if a bounded wait expires.
+cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
+                               const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
 // y[m,out_f] (m <= 8) from f32 activations and dequantised weights.
 cudaError_t launch_gemv_f32(int dt, const uint8_t *w, const float *x, float *y, int m, int in_f, int out_f,
                             const DeviceInfo &dev, cudaStream_t st);

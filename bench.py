@@ -318,6 +318,33 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_profile_case(args):
+    """A few plain launches of one GEMV configuration (for an ncu capture on a small case):
+    --profile-case DTYPE:OUT_F:IN_F:M, e.g. q4_k:14336:4096:1; weights rotate over > L2 of copies."""
+    import infr_b200
+    from infr_b200 import synth
+
+    name, out_f, in_f, m = args.profile_case.split(":")
+    dtype = {v: k for k, v in synth.DTYPE_NAMES.items()}[name]
+    out_f, in_f, m = int(out_f), int(in_f), int(m)
+    be = infr_b200.CudaBackend(device=0, _dev_opts=[int(os.environ.get('INFR_DEV_GEMV_IMPL', '0'))])
+    caps = be.capabilities()
+    bufs, w = _rotation(be, infr_b200, dtype, out_f, in_f, 5, caps.l2_bytes + (32 << 20))
+    x = synth.normal(6, (m, in_f))
+    xb = be.from_numpy(x)
+    yb = be.alloc(m * out_f * 4)
+    gran = 32 if dtype == infr_b200.Q2_0 else 256
+    qs, d = be.alloc(m * in_f), be.alloc(m * (in_f // gran) * 4)
+    s32, s16 = be.alloc(m * (in_f // 32) * 4), be.alloc(m * (in_f // 16) * 4)
+    be.quantize_q8(gran, xb, m, in_f, qs, d, s32, s16 if gran == 256 else None)
+    for i in range(args.steps):
+        be.gemv_q8(dtype, bufs[i % len(bufs)], qs, d, s32, s16 if dtype == infr_b200.Q6K else None, yb, m, in_f, out_f)
+    be.sync()
+    print(json.dumps({"profile_case": args.profile_case, "launches": args.steps, "copies": len(bufs),
+                      "alg_bytes_per_launch": w.nbytes + 4 * m * (in_f + out_f)}))
+    be.close()
+
+
 def _cpu_baseline(w, x, budget_s):
     from oracle.cpu_oracle import Oracle, Q4K
 
@@ -380,8 +407,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--profile-case", default=None, help="DTYPE:OUT_F:IN_F:M — plain launches of one GEMV case")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

@@ -1,32 +1,35 @@
 // Streaming decode GEMV (int8 activations) for sm_100a: weights travel HBM -> shared memory through
-// the bulk-copy engine (cp.async.bulk, 1-D TMA) into a multi-stage ring guarded by mbarriers, so the
-// bytes in flight per SM are set by the ring size, not by how many registers the math warps can hold.
+// the bulk-copy engine (cp.async.bulk, 1-D TMA) and are consumed from there, so the bytes in flight per
+// SM are set by the shared-memory rings, not by how many registers the math warps can hold.
 //
-// Work split.  The grid is one persistent CTA per SM; CTA i owns a contiguous, balanced range of
-// output rows.  Rows are taken kRows at a time (one per consumer warp) and every row is cut into
-// K-slices of kSliceBytes; a ring stage holds one K-slice of kRows rows and is filled by kRows bulk
-// copies issued in parallel by the lanes of the producer warp.  Consumer warp w accumulates row w
-// across its K-slices in registers, reduces with one shuffle tree and writes y.  The arithmetic is
-// the production infr-cpu arithmetic (crates/infr-cpu/src/kernels.rs:151-184, :487-526, :5641-5668):
+// Work split.  The grid is up to two persistent CTAs per SM; CTA i owns a contiguous, balanced range
+// of output rows and its warps claim rows from a CTA-local counter.  Every warp runs its OWN pipeline:
+// lane 0 issues the bulk copy of the next K-slice of the warp's current row into one of the warp's
+// private ring slots (completion on a per-slot mbarrier), the whole warp then reduces a landed slice
+// against the staged activations and immediately refills the slot it has just drained.  Warps never
+// wait on each other after the one barrier that publishes the staged activations.  A row's partial sum
+// stays in registers across its slices, meets in one shuffle tree and is written once.  The arithmetic
+// is the production infr-cpu arithmetic (crates/infr-cpu/src/kernels.rs:151-184, :487-526, :5641-5668):
 // exact int32 block sums, f32 only for the per-block scale products.
 //
 // Q6_K / Q2_0 blocks are 210 / 18 bytes, so a slice of a row may start on any even address: the copy
 // fetches the 16-byte-aligned superset and the consumer indexes from the remainder.
 //
 // Programmatic dependent launch: the weights do not depend on the previous kernel in the stream, so
-// the producer starts streaming them immediately and only the activation staging waits on
+// every warp puts its first slices in flight at once and only the activation staging waits on
 // `griddepcontrol.wait`; `griddepcontrol.launch_dependents` lets the next kernel's CTAs begin their
 // own weight stream while this one drains.
 //
-// Every mbarrier wait is bounded: when the limit is hit the kernel records a status word for the
-// host, stops issuing work, drains the copies it has in flight (bounded again) and returns.
+// Every mbarrier wait is bounded: when the limit is hit the warp records a status word for the host,
+// stops claiming work, waits (bounded again) for the copies it still has in flight and returns.
 #include "gemv_common.cuh"
 
 namespace infr {
 namespace {
 
-constexpr int kRows = 16;                 // consumer warps == rows per ring stage
-constexpr int kStreamThreads = (kRows + 1) * 32;
+constexpr int kStreamWarps = 16;
+constexpr int kStreamThreads = kStreamWarps * 32;
+constexpr int kMaxSlots = 4;              // ring slots per warp
 constexpr uint32_t kSpinLimit = 1u << 22; // polls of mbarrier.try_wait before giving up
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -71,53 +74,67 @@ template <int DT>
 struct Fmt;
 template <>
 struct Fmt<DT_Q4K> {
-    static constexpr int kBlockBytes = 144, kBlockElems = 256, kSliceBlocks = 8;
+    static constexpr int kBlockBytes = 144, kBlockElems = 256, kSliceBlocks = 16, kStepBlocks = 8;
 };
 template <>
 struct Fmt<DT_Q6K> {
-    static constexpr int kBlockBytes = 210, kBlockElems = 256, kSliceBlocks = 8;
+    static constexpr int kBlockBytes = 210, kBlockElems = 256, kSliceBlocks = 16, kStepBlocks = 2;
 };
 template <>
 struct Fmt<DT_Q2_0> {
-    static constexpr int kBlockBytes = 18, kBlockElems = 64, kSliceBlocks = 64;
+    static constexpr int kBlockBytes = 18, kBlockElems = 64, kSliceBlocks = 128, kStepBlocks = 8;
 };
 
 // ---- per-format slice processors: `sl` points at the first block of this row's slice in shared
 // memory, `nblk` blocks long, whose first block is block `gb0` of the row. --------------------------
+// Q4_K: 4 lanes per super-block, lane j owns the 32 nibble bytes of sub-block pair (2j, 2j+1): the low
+// nibbles are the 32 elements of sub-block 2j, the high nibbles those of 2j+1.  High nibbles are fed to
+// the byte dot product unshifted (values 16x) and the sum is shifted back once, exactly.  A slice of 8
+// blocks is one warp step.  Staged activations are laid out [block pair][k][block&1][j] in 16-byte
+// units (k = 0,1: elements 0-15 / 16-31 of sub-block 2j; k = 2,3: of 2j+1) so that every 128-bit
+// shared-memory read of a quarter-warp covers 128 contiguous bytes.
 template <int M>
 __device__ __forceinline__ void slice_q4k(const uint8_t *sl, int nblk, int gb0, int nb, int in_f, const int8_t *s_qa,
                                           const float *s_d, const int32_t *s_bs, int lane, float (&acc)[M]) {
-    const int g = lane >> 3, c = lane & 7, j = c >> 1;
-#pragma unroll 2
-    for (int b0 = 0; b0 < nblk; b0 += 4) {
-        const int bl = b0 + g;
-        if (bl < nblk) {
-            const int b = gb0 + bl;
-            const uint8_t *blk = sl + bl * 144;
-            const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
-            const uint4 qv = *reinterpret_cast<const uint4 *>(blk + 16 + c * 16);
-            int sc0, m0, sc1, m1;
-            k4_pair(hdr.y, hdr.z, hdr.w, j, sc0, m0, sc1, m1);
-            const float d = h2f(hdr.x), dmin = h2f(hdr.x >> 16);
-            const int mc = (c & 1) ? m1 : m0;
-            const uint32_t q[4] = {qv.x, qv.y, qv.z, qv.w};
+    const int j = lane & 3;
+    const int tok_stride = (nb + 1) / 2 * 512;
+    for (int bl = lane >> 2; bl < nblk; bl += 8) {
+    const int b = gb0 + bl;
+    const uint8_t *blk = sl + bl * 144;
+    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+    const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16 + j * 32);
+    const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32 + j * 32);
+    // get_scale_min_k4 for the pair (2j, 2j+1), on packed bytes
+    uint32_t scw, mw;
+    if (j < 2) {
+        scw = hdr.y & 0x3F3F3F3Fu;
+        mw = hdr.z & 0x3F3F3F3Fu;
+    } else {
+        scw = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+        mw = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+    }
+    const uint32_t sel = (j & 1) ? 0x4442u : 0x4440u;  // byte 2 or byte 0, zero-extended
+    const int sc0 = (int)__byte_perm(scw, 0, sel), sc1 = (int)__byte_perm(scw, 0, sel + 1);
+    const int m0 = (int)__byte_perm(mw, 0, sel), m1 = (int)__byte_perm(mw, 0, sel + 1);
+    const float d = h2f(hdr.x), dmin = h2f(hdr.x >> 16);
+    const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
-            for (int t = 0; t < M; t++) {
-                const uint4 alo = reinterpret_cast<const uint4 *>(s_qa + (size_t)t * in_f)[b * 16 + c];
-                const uint4 ahi = reinterpret_cast<const uint4 *>(s_qa + (size_t)t * in_f)[b * 16 + 8 + c];
-                const int al[4] = {(int)alo.x, (int)alo.y, (int)alo.z, (int)alo.w};
-                const int ah[4] = {(int)ahi.x, (int)ahi.y, (int)ahi.z, (int)ahi.w};
-                int ilo = 0, ihi = 0;
+    for (int t = 0; t < M; t++) {
+        const uint4 *au = reinterpret_cast<const uint4 *>(s_qa + (size_t)t * tok_stride) + (b >> 1) * 32 + (b & 1) * 4 + j;
+        const uint4 a0 = au[0], a1 = au[8], a2 = au[16], a3 = au[24];
+        const int al[8] = {(int)a0.x, (int)a0.y, (int)a0.z, (int)a0.w, (int)a1.x, (int)a1.y, (int)a1.z, (int)a1.w};
+        const int ah[8] = {(int)a2.x, (int)a2.y, (int)a2.z, (int)a2.w, (int)a3.x, (int)a3.y, (int)a3.z, (int)a3.w};
+        int ilo = 0, ihi = 0;
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    ilo = dp4a_us(q[i] & 0x0F0F0F0Fu, al[i], ilo);
-                    ihi = dp4a_us((q[i] >> 4) & 0x0F0F0F0Fu, ah[i], ihi);
-                }
-                const int sd = sc0 * ilo + sc1 * ihi;
-                const int sm = mc * s_bs[(t * nb + b) * 8 + c];
-                acc[t] += s_d[t * nb + b] * (d * (float)sd - dmin * (float)sm);
-            }
+        for (int i = 0; i < 8; i++) {
+            ilo = dp4a_us(q[i] & 0x0F0F0F0Fu, al[i], ilo);
+            ihi = dp4a_us(q[i] & 0xF0F0F0F0u, ah[i], ihi);
         }
+        const int2 bs = *reinterpret_cast<const int2 *>(s_bs + (t * nb + b) * 8 + 2 * j);
+        const int sd = sc0 * ilo + sc1 * (ihi >> 4);
+        const int sm = m0 * bs.x + m1 * bs.y;
+        acc[t] += s_d[t * nb + b] * (d * (float)sd - dmin * (float)sm);
+    }
     }
 }
 
@@ -192,8 +209,8 @@ __device__ __forceinline__ void slice_q2_0(const uint8_t *sl, int nblk, int gb0,
 struct StreamGeom {
     int nb;          // weight blocks per row
     int n_slices;    // K-slices per row
-    int slot_bytes;  // shared-memory bytes reserved per (stage, row)
-    int stages;
+    int slot_bytes;  // shared-memory bytes per ring slot
+    int slots;       // ring slots per warp
     uint32_t act_bytes;  // staged activations (codes + scales + sums), 16-byte aligned
 };
 
@@ -203,83 +220,68 @@ __global__ void __launch_bounds__(kStreamThreads, (M <= 2 ? 2 : 1))
                        StreamGeom geo, uint32_t *__restrict__ status) {
     using F = Fmt<DT>;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int nb = geo.nb, S = geo.stages;
-    uint8_t *ring = smem;
-    uint8_t *act = smem + (size_t)S * kRows * geo.slot_bytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(act + geo.act_bytes);  // full[S], empty[S]
-    __shared__ int s_abort;
+    const int nb = geo.nb, S = geo.slots;
+    uint8_t *act = smem + (size_t)kStreamWarps * S * geo.slot_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(act + geo.act_bytes);  // [warp][slot]
+    int2 *meta = reinterpret_cast<int2 *>(bars + kStreamWarps * kMaxSlots); // [warp][slot] = (row, slice)
+    __shared__ int s_next;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        s_abort = 0;
-        for (int s = 0; s < S; s++) {
-            mbar_init(smem_u32(bars + s), 1);
-            mbar_init(smem_u32(bars + S + s), kRows);
-        }
+        s_next = 0;
+        for (int i = 0; i < kStreamWarps * kMaxSlots; i++) mbar_init(smem_u32(bars + i), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    pdl_launch_dependents();
 
     // balanced contiguous row range of this CTA
     const int G = gridDim.x, base = out_f / G, rem = out_f % G;
     const int r_begin = blockIdx.x * base + (blockIdx.x < rem ? blockIdx.x : rem);
     const int r_count = base + (blockIdx.x < rem ? 1 : 0);
-    const int n_groups = (r_count + kRows - 1) / kRows;
-    const int n_tiles = n_groups * geo.n_slices;
     const size_t row_bytes = (size_t)nb * F::kBlockBytes;
+    uint8_t *ring = smem + (size_t)warp * S * geo.slot_bytes;
+    uint64_t *wbar = bars + warp * kMaxSlots;
+    int2 *wmeta = meta + warp * kMaxSlots;
 
-    if (warp == kRows) {
-        // ------------------------------------------------------------------ producer warp
-        pdl_launch_dependents();
-        bool ok = true;
-        int issued = 0;
-        for (int t = 0; t < n_tiles && ok; t++) {
-            const int s = t % S, use = t / S;
-            if (use > 0) ok = mbar_wait(smem_u32(bars + S + s), (uint32_t)((use - 1) & 1));
-            if (*(volatile int *)&s_abort) ok = false;
-            if (!ok) break;
-            const int grp = t / geo.n_slices, ks = t - grp * geo.n_slices;
-            const int row = r_begin + grp * kRows + lane;
-            const int blk0 = ks * F::kSliceBlocks;
-            const int nblk = min(F::kSliceBlocks, nb - blk0);
-            uint32_t bytes = 0;
-            const uint8_t *src = nullptr;
-            if (lane < kRows && row < r_begin + r_count) {
-                const size_t start = (size_t)W + (size_t)row * row_bytes + (size_t)blk0 * F::kBlockBytes;
-                const size_t end = start + (size_t)nblk * F::kBlockBytes;
-                const size_t a0 = start & ~(size_t)15, a1 = (end + 15) & ~(size_t)15;
-                src = reinterpret_cast<const uint8_t *>(a0);
-                bytes = (uint32_t)(a1 - a0);
-            }
-            uint32_t total = bytes;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-            if (lane == 0) mbar_expect_tx(smem_u32(bars + s), total);
-            __syncwarp();
-            if (bytes) bulk_g2s(smem_u32(ring + ((size_t)s * kRows + lane) * geo.slot_bytes), src, bytes, smem_u32(bars + s));
-            issued = t + 1;
+    // ---- issue side (warp-uniform state; lane 0 talks to the copy engine) ----
+    int i_row = -1, i_ks = 0;
+    auto issue = [&](int slot) {
+        if (i_ks == 0) {
+            int idx = 0;
+            if (lane == 0) idx = atomicAdd(&s_next, 1);
+            idx = __shfl_sync(0xffffffffu, idx, 0);
+            i_row = idx < r_count ? r_begin + idx : -1;
         }
-        if (!ok) {
-            if (lane == 0) {
-                atomicExch(status, 1u);
-                *(volatile int *)&s_abort = 1;
+        if (lane == 0) {
+            wmeta[slot] = make_int2(i_row, i_ks);
+            if (i_row >= 0) {
+                const int blk0 = i_ks * F::kSliceBlocks;
+                const int nblk = min(F::kSliceBlocks, nb - blk0);
+                const size_t start = (size_t)W + (size_t)i_row * row_bytes + (size_t)blk0 * F::kBlockBytes;
+                const size_t a0 = start & ~(size_t)15;
+                const uint32_t bytes = (uint32_t)(((start + (size_t)nblk * F::kBlockBytes + 15) & ~(size_t)15) - a0);
+                const uint32_t bar = smem_u32(wbar + slot);
+                // order this warp's earlier reads of the slot before the engine overwrites it
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_expect_tx(bar, bytes);
+                bulk_g2s(smem_u32(ring + (size_t)slot * geo.slot_bytes), reinterpret_cast<const void *>(a0), bytes, bar);
             }
-            // drain: every stage filled but possibly not yet landed
-            for (int t = max(0, issued - S); t < issued; t++) mbar_wait(smem_u32(bars + (t % S)), (uint32_t)((t / S) & 1));
         }
-        return;
-    }
+        __syncwarp();
+        if (i_row >= 0) i_ks = (i_ks + 1 == geo.n_slices) ? 0 : i_ks + 1;
+    };
+    for (int s = 0; s < S; s++) issue(s);
 
-    // ---------------------------------------------------------------------- consumer warps
-    pdl_wait();  // activations come from the previous kernel in the stream
+    // ---- activations: produced by the previous kernel in the stream ----
+    pdl_wait();
+    int8_t *s_qa = reinterpret_cast<int8_t *>(act);
+    const int code_bytes = DT != DT_Q2_0 ? M * ((nb + 1) / 2 * 512) : M * in_f;
+    float *s_d = reinterpret_cast<float *>(act + code_bytes);
+    const int nd = in_f / a.gran;
+    int32_t *s_bs = reinterpret_cast<int32_t *>(act + code_bytes + ((M * nd * 4 + 15) & ~15));
     {
-        int8_t *s_qa = reinterpret_cast<int8_t *>(act);
-        const int code_bytes = DT == DT_Q6K ? M * ((nb + 1) / 2 * 512) : M * in_f;
-        float *s_d = reinterpret_cast<float *>(act + code_bytes);
-        const int nd = in_f / a.gran;
-        int32_t *s_bs = reinterpret_cast<int32_t *>(s_d + M * nd);
-        // stage_q8 strides by blockDim.x; only the consumer threads take part here
-        const int tid = threadIdx.x, nthr = kRows * 32;
+        const int tid = threadIdx.x, nthr = kStreamThreads;
         const int units = in_f / 16;
         for (int idx = tid; idx < M * units; idx += nthr) {
             const int t = idx / units, u = idx - t * units;
@@ -287,7 +289,8 @@ __global__ void __launch_bounds__(kStreamThreads, (M <= 2 ? 2 : 1))
             if (t < m) v = *reinterpret_cast<const uint4 *>(a.qs + (size_t)t * in_f + (size_t)u * 16);
             if (DT == DT_Q4K) {
                 const int b = u >> 4, uu = u & 15, s = uu >> 1, h = uu & 1;
-                reinterpret_cast<uint4 *>(s_qa + (size_t)t * in_f)[b * 16 + (s & 1) * 8 + (s >> 1) * 2 + h] = v;
+                const int k = (s & 1) * 2 + h, j = s >> 1;
+                reinterpret_cast<uint4 *>(s_qa + (size_t)t * ((nb + 1) / 2 * 512))[(b >> 1) * 32 + k * 8 + (b & 1) * 4 + j] = v;
             } else if (DT == DT_Q6K) {
                 const int b = u >> 4, uu = u & 15;
                 uint32_t *dstw = reinterpret_cast<uint32_t *>(s_qa + (size_t)t * ((nb + 1) / 2 * 512));
@@ -318,47 +321,51 @@ __global__ void __launch_bounds__(kStreamThreads, (M <= 2 ? 2 : 1))
             const int t = idx / ns, i = idx - t * ns;
             s_bs[idx] = t < m ? src[(size_t)t * ns + i] : 0;
         }
-        // consumer-only barrier (named barrier 1, kRows warps)
-        asm volatile("bar.sync 1, %0;" ::"r"(kRows * 32) : "memory");
+    }
+    __syncthreads();
 
-        float acc[M];
-        for (int t = 0; t < n_tiles; t++) {
-            const int s = t % S, use = t / S;
-            const int grp = t / geo.n_slices, ks = t - grp * geo.n_slices;
-            if (ks == 0) {
+    // ---- consume side ----
+    float acc[M];
 #pragma unroll
-                for (int i = 0; i < M; i++) acc[i] = 0.f;
+    for (int i = 0; i < M; i++) acc[i] = 0.f;
+    int slot = 0;
+    uint32_t phase = 0;
+    for (;;) {
+        const int2 job = wmeta[slot];  // written by this warp's lane 0 before a __syncwarp
+        const int row = job.x, ks = job.y;
+        if (row < 0) break;
+        if (!mbar_wait(smem_u32(wbar + slot), phase)) {
+            if (lane == 0) atomicExch(status, 2u);
+            // stop claiming work; give the copies still in flight a bounded chance to land
+            for (int k = 1; k < S; k++) {
+                const int s2 = (slot + k) % S;
+                if (wmeta[s2].x >= 0) mbar_wait(smem_u32(wbar + s2), s2 > slot ? phase : phase ^ 1u);
             }
-            if (!mbar_wait(smem_u32(bars + s), (uint32_t)(use & 1)) || *(volatile int *)&s_abort) {
-                if (lane == 0) {
-                    atomicExch(status, 2u);
-                    *(volatile int *)&s_abort = 1;
-                }
-                return;
-            }
-            const int row = r_begin + grp * kRows + warp;
-            const bool live = row < r_begin + r_count;
-            const int blk0 = ks * F::kSliceBlocks;
-            const int nblk = min(F::kSliceBlocks, nb - blk0);
-            if (live) {
-                const size_t start = (size_t)W + (size_t)row * row_bytes + (size_t)blk0 * F::kBlockBytes;
-                const uint8_t *sl = ring + ((size_t)s * kRows + warp) * geo.slot_bytes + (start & 15);
-                if (DT == DT_Q4K)
-                    slice_q4k<M>(sl, nblk, blk0, nb, in_f, s_qa, s_d, s_bs, lane, acc);
-                else if (DT == DT_Q6K)
-                    slice_q6k<M>(sl, nblk, blk0, nb, in_f, s_qa, s_d, s_bs, lane, acc);
-                else
-                    slice_q2_0<M>(sl, nblk, blk0, nb, in_f, s_qa, s_d, s_bs, lane, acc);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(bars + S + s));
-            if (live && ks == geo.n_slices - 1) {
+            return;
+        }
+        const int blk0 = ks * F::kSliceBlocks;
+        const int nblk = min(F::kSliceBlocks, nb - blk0);
+        const size_t start = (size_t)W + (size_t)row * row_bytes + (size_t)blk0 * F::kBlockBytes;
+        const uint8_t *sl = ring + (size_t)slot * geo.slot_bytes + (DT == DT_Q4K ? 0 : (int)(start & 15));
+        if (DT == DT_Q4K)
+            slice_q4k<M>(sl, nblk, blk0, nb, in_f, s_qa, s_d, s_bs, lane, acc);
+        else if (DT == DT_Q6K)
+            slice_q6k<M>(sl, nblk, blk0, nb, in_f, s_qa, s_d, s_bs, lane, acc);
+        else
+            slice_q2_0<M>(sl, nblk, blk0, nb, in_f, s_qa, s_d, s_bs, lane, acc);
+        __syncwarp();
+        issue(slot);
+        if (ks == geo.n_slices - 1) {
 #pragma unroll
-                for (int i = 0; i < M; i++) {
-                    const float v = warp_sum(acc[i]);
-                    if (lane == 0 && i < m) y[(size_t)i * out_f + row] = v;
-                }
+            for (int i = 0; i < M; i++) {
+                const float v = warp_sum(acc[i]);
+                if (lane == 0 && i < m) y[(size_t)i * out_f + row] = v;
+                acc[i] = 0.f;
             }
+        }
+        if (++slot == S) {
+            slot = 0;
+            phase ^= 1u;
         }
     }
 }
@@ -372,20 +379,23 @@ cudaError_t launch_stream_dt(const uint8_t *w, const Q8Dev &a, float *y, int m, 
     geo.n_slices = (geo.nb + F::kSliceBlocks - 1) / F::kSliceBlocks;
     const int slice_bytes = (geo.nb < F::kSliceBlocks ? geo.nb : F::kSliceBlocks) * F::kBlockBytes;
     geo.slot_bytes = ((slice_bytes + 15) / 16 * 16) + 32;
-    const size_t codes = DT == DT_Q6K ? (size_t)M * ((geo.nb + 1) / 2 * 512) : (size_t)M * in_f;
-    const size_t acts = codes + (size_t)M * (in_f / a.gran) * 4 + (size_t)M * (DT == DT_Q6K ? in_f / 16 : in_f / 32) * 4;
+    const size_t codes = DT != DT_Q2_0 ? (size_t)M * ((geo.nb + 1) / 2 * 512) : (size_t)M * in_f;
+    const size_t acts = codes + (((size_t)M * (in_f / a.gran) * 4 + 15) & ~(size_t)15) +
+                        (size_t)M * (DT == DT_Q6K ? in_f / 16 : in_f / 32) * 4;
     geo.act_bytes = (uint32_t)((acts + 15) / 16 * 16);
-    // ring budget: leave room for a second CTA (the next kernel, launched early) on the same SM
-    const size_t budget = (size_t)dev.max_smem_optin / 2 - 2048;
-    if (geo.act_bytes + 64 + 2 * (size_t)kRows * geo.slot_bytes > (size_t)dev.max_smem_optin - 1024) return cudaErrorInvalidValue;
-    size_t ring_budget = budget > geo.act_bytes ? budget - geo.act_bytes : 0;
-    int stages = (int)(ring_budget / ((size_t)kRows * geo.slot_bytes));
-    if (stages < 2) stages = 2;
-    if (stages > 8) stages = 8;
-    geo.stages = stages;
-    const size_t smem = (size_t)stages * kRows * geo.slot_bytes + geo.act_bytes + 2 * stages * 8 + 16;
-    int grid = (out_f + kRows - 1) / kRows;
-    if (grid > dev.sm_count) grid = dev.sm_count;
+    const size_t fixed = geo.act_bytes + (size_t)kStreamWarps * kMaxSlots * 16 + 64;
+    const size_t per_slot = (size_t)kStreamWarps * geo.slot_bytes;
+    if (fixed + 2 * per_slot > (size_t)dev.max_smem_optin) return cudaErrorInvalidValue;
+    // Two resident CTAs per SM when they fit with at least 2 ring slots per warp.
+    const size_t half = (size_t)dev.max_smem_optin / 2 - 2048;
+    int per_sm = (M <= 2 && fixed + 2 * per_slot <= half) ? 2 : 1;
+    const size_t budget = per_sm == 2 ? half : (size_t)dev.max_smem_optin - 1024;
+    int slots = (int)((budget - fixed) / per_slot);
+    if (slots > kMaxSlots) slots = kMaxSlots;
+    geo.slots = slots;
+    const size_t smem = (size_t)slots * per_slot + fixed;
+    int grid = (out_f + kStreamWarps - 1) / kStreamWarps;
+    if (grid > dev.sm_count * per_sm) grid = dev.sm_count * per_sm;
     auto kernel = gemv_stream_kernel<DT, M>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

@@ -330,6 +330,8 @@ def run_profile_case(args):
     be = infr_b200.CudaBackend(device=0, _dev_opts=[int(os.environ.get('INFR_DEV_GEMV_IMPL', '0'))])
     caps = be.capabilities()
     bufs, w = _rotation(be, infr_b200, dtype, out_f, in_f, 5, caps.l2_bytes + (32 << 20))
+    if args.copies:
+        bufs = bufs[:args.copies]
     x = synth.normal(6, (m, in_f))
     xb = be.from_numpy(x)
     yb = be.alloc(m * out_f * 4)
@@ -337,11 +339,12 @@ def run_profile_case(args):
     qs, d = be.alloc(m * in_f), be.alloc(m * (in_f // gran) * 4)
     s32, s16 = be.alloc(m * (in_f // 32) * 4), be.alloc(m * (in_f // 16) * 4)
     be.quantize_q8(gran, xb, m, in_f, qs, d, s32, s16 if gran == 256 else None)
+    be.timer_start()
     for i in range(args.steps):
         be.gemv_q8(dtype, bufs[i % len(bufs)], qs, d, s32, s16 if dtype == infr_b200.Q6K else None, yb, m, in_f, out_f)
-    be.sync()
+    ms = be.timer_stop()
     print(json.dumps({"profile_case": args.profile_case, "launches": args.steps, "copies": len(bufs),
-                      "alg_bytes_per_launch": w.nbytes + 4 * m * (in_f + out_f)}))
+                      "alg_bytes_per_launch": w.nbytes + 4 * m * (in_f + out_f), "us_per_launch_incl_host": ms * 1e3 / args.steps}))
     be.close()
 
 
@@ -407,6 +410,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--copies", type=int, default=0, help="with --profile-case: use only this many weight copies")
     ap.add_argument("--profile-case", default=None, help="DTYPE:OUT_F:IN_F:M — plain launches of one GEMV case")
     args = ap.parse_args()
     if args.profile_case:

@@ -250,6 +250,11 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
             Status s = cuda_status(launch_gemv_f32(dtype, w, xr, yr, (int)mm, (int)in_f, (int)out_f, dev_, stream_), "gemv_f32");
             if (!s.ok()) return s;
             launches_ += 1;
+        } else if (dtype == DT_Q4K && gemv_impl_ == 0) {
+            // one kernel: activation rows are quantised inside the GEMV while the first weights stream in
+            Status s = cuda_status(launch_gemv_q4k_mma(w, nullptr, xr, yr, (int)mm, (int)in_f, (int)out_f, dev_, status_dev_, stream_), "gemv_q4k");
+            if (!s.ok()) return s;
+            launches_ += 1;
         } else {
             Q8Dev a;
             Status s = quantize_for(dtype, xr, mm, in_f, &a);
@@ -272,8 +277,10 @@ Status CudaBackend::gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *
     if (a.gran != act_gran(dtype)) return Status::Err(INFR_E_INVALID, fmt("gemv_q8: activations have granularity %d, dtype needs %d", a.gran, act_gran(dtype)));
     if (dtype == DT_Q6K && !a.sums16) return Status::Err(INFR_E_INVALID, "gemv_q8: Q6_K needs the per-16 sums");
     cudaSetDevice(device_);
-    Status s = cuda_status(gemv_impl_ == 1 ? launch_gemv_q8(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, nullptr, dev_, stream_)
-                                           : launch_gemv_stream(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_),
+    Status s = cuda_status(gemv_impl_ == 1   ? launch_gemv_q8(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, nullptr, dev_, stream_)
+                           : (dtype == DT_Q4K && gemv_impl_ == 0)
+                               ? launch_gemv_q4k_mma(w, &a, nullptr, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_)
+                               : launch_gemv_stream(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_),
                            "gemv_q8");
     if (s.ok()) launches_++;
     return s;

@@ -1,0 +1,431 @@
+// Q4_K decode GEMV / small-batch GEMM (m <= 8) on the warp-level int8 matrix unit.
+//
+// y[m,out_f] = x[m,in_f] * W^T with the production infr-cpu arithmetic
+// (crates/infr-cpu/src/kernels.rs:151-184): per 256-element super-block
+//     sd = sum_s sc_s * (sum_i q4_si * q8_si)      sm = sum_s m_s * bsum_s        (exact int32)
+//     y += d8 * (d * float(sd) - dmin * float(sm))
+//
+// Why a matrix instruction for a matvec: the kernel is HBM-bound only if the SM can unpack 23 bytes
+// of 4-bit weights per clock, and with scalar byte dot products the instruction stream (mask, dot,
+// scale, reduce) needs more issue slots than an SM has.  `mma.sync.m16n8k32.u8.s8` takes 16 weight
+// rows x 32 K per instruction and the 8 columns hold up to 8 activation rows, so the per-byte
+// instruction count roughly halves and batch 1..8 all cost the same.  The K index of the instruction
+// is only a summation index, so each lane feeds it the 8 nibble bytes it can fetch with one 64-bit
+// shared-memory read; the activations are staged in shared memory in the matching order.  High
+// nibbles are multiplied unshifted (x16) and the int32 result is shifted back, exactly.  The min term
+// sm is one more instruction per half: A = the 8 min bytes, B = bsum split as 64*h + l (both int8).
+//
+// Data movement: weights go HBM -> shared memory by tiled TMA (cp.async.bulk.tensor.2d over a tensor
+// map of the weight matrix viewed as [rows][row_bytes/4] 32-bit words; one instruction fetches the
+// 16-row x K-step box of a ring slot, rows past the end of the matrix are zero-filled) into
+// warp-private rings; a CTA owns a contiguous balanced row range, walks it 16 rows at a time and
+// its 8 warps split K.  Partial sums meet in shared memory once per 16 rows in a fixed order (the
+// result does not depend on timing).  Programmatic dependent launch: weights are prefetched before
+// `griddepcontrol.wait`; only the activation staging waits for the previous kernel.
+//
+// When `x` is given instead of pre-quantised activations the CTA quantises the rows itself while the
+// first weights are in flight (same arithmetic as quantize.cu, so the same bits), which makes a
+// quantized Linear a single kernel.
+//
+// All mbarrier waits are bounded; an expired wait records a status word for the host and the warp
+// stops consuming (the block still reaches its barriers, results of the launch are invalid).
+#include <cuda.h>
+
+#include "gemv_common.cuh"
+
+namespace infr {
+namespace {
+
+constexpr int kW = 4;               // warps per CTA (K split)
+constexpr int kThreadsMma = kW * 32;
+constexpr int kTileRows = 16;
+constexpr int kStepBlocks = 2;      // super-blocks per ring slot per row
+constexpr int kSlotBytes = kTileRows * kStepBlocks * 144;
+constexpr int kMaxSlotsMma = 4;
+constexpr uint32_t kSpin = 1u << 22;
+
+__device__ __forceinline__ uint32_t s_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpin; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// Tiled TMA load of one box: x = word offset inside the row (a multiple of 4 -> 16-byte aligned), y = row.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+// D = A(16x32, u8) * B(32x8, s8), int32, zero accumulator input.
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// All eight (scale, min) pairs of a Q4_K header as bytes (get_scale_min_k4,
+// crates/infr-gguf/src/dequant.rs:73-83): sc[0] = scales 0..3, sc[1] = 4..7, likewise mn.
+__device__ __forceinline__ void k4_all(uint32_t y, uint32_t z, uint32_t w, uint32_t (&sc)[2], uint32_t (&mn)[2]) {
+    sc[0] = y & 0x3F3F3F3Fu;
+    mn[0] = z & 0x3F3F3F3Fu;
+    sc[1] = (w & 0x0F0F0F0Fu) | ((y >> 2) & 0x30303030u);
+    mn[1] = ((w >> 4) & 0x0F0F0F0Fu) | ((z >> 2) & 0x30303030u);
+}
+
+struct MmaGeom {
+    int nb;         // super-blocks per row
+    int bpw;        // super-blocks per warp (K split)
+    int slots;      // ring slots per warp
+    int act_bytes;  // staged activation bytes
+};
+
+// Shared-memory layout of the staged activations, per token n (0..7) and super-block b:
+//   codes  : 256 B at (n*nb + b)*256, element (sub-block s, l = 8t+i) at t*64 + s*8 + i
+//   bsplit : 16 B at (n*nb + b)*16: bytes 0..7 = low 6 bits of bsum_s, bytes 8..15 = bsum_s >> 6
+//   d8     : float [n*nb + b]
+template <int M, bool FUSED>
+__global__ void __launch_bounds__(kThreadsMma, 4)
+    gemv_q4k_mma_kernel(const __grid_constant__ CUtensorMap tmap, Q8Dev a, const float *__restrict__ x, float *__restrict__ y, int m,
+                        int in_f, int out_f, MmaGeom geo, uint32_t *__restrict__ status) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int nb = geo.nb, S = geo.slots;
+    uint8_t *rings = smem;                                         // [kW][S][kSlotBytes]
+    uint8_t *s_codes = smem + (size_t)kW * S * kSlotBytes;         // [M][nb][256]
+    uint8_t *s_bsplit = s_codes + (size_t)M * nb * 256;            // [M][nb][16]
+    float *s_d8 = reinterpret_cast<float *>(s_bsplit + (size_t)M * nb * 16);  // [M][nb], padded to 16 B
+    float *s_part = s_d8 + ((M * nb + 3) & ~3);                    // [2][kW][16][8]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_part + 2 * kW * 128);  // [kW][kMaxSlotsMma]
+    __shared__ int s_bad;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    if (threadIdx.x == 0) {
+        s_bad = 0;
+        for (int i = 0; i < kW * kMaxSlotsMma; i++) bar_init(s_u32(bars + i), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // balanced contiguous range of 16-row tiles of this CTA (only the matrix's last tile can be partial)
+    const int total_tiles = (out_f + kTileRows - 1) / kTileRows;
+    const int G = gridDim.x, base = total_tiles / G, rem = total_tiles % G;
+    const int t_begin = blockIdx.x * base + (blockIdx.x < rem ? blockIdx.x : rem);
+    const int n_tiles = base + (blockIdx.x < rem ? 1 : 0);
+    const int r_begin = t_begin * kTileRows;
+    const int r_count = min(out_f - r_begin, n_tiles * kTileRows);
+    // this warp's K range
+    const int kb0 = warp * geo.bpw;
+    const int kb1 = min(nb, kb0 + geo.bpw);
+    const int my_blocks = max(0, kb1 - kb0);
+    const int steps_per_tile = (my_blocks + kStepBlocks - 1) / kStepBlocks;
+    const int n_jobs = n_tiles * steps_per_tile;
+    uint8_t *ring = rings + (size_t)warp * S * kSlotBytes;
+    uint64_t *wbar = bars + warp * kMaxSlotsMma;
+
+    // ---- issue side: one elected lane fetches the 16-row x K-step box of the slot ----
+    int j_issue = 0, i_tile = 0, i_step = 0;
+    auto issue = [&](int slot) {
+        if (j_issue >= n_jobs) return;
+        if (lane == 0) {
+            const int blk0 = kb0 + i_step * kStepBlocks;
+            const uint32_t bar = s_u32(wbar + slot);
+            // order this warp's earlier reads of the slot before the engine overwrites it
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            bar_expect_tx(bar, (uint32_t)kSlotBytes);
+            tma_load_2d(s_u32(ring + (size_t)slot * kSlotBytes), &tmap, blk0 * 36, r_begin + i_tile * kTileRows, bar);
+        }
+        __syncwarp();
+        j_issue++;
+        if (++i_step == steps_per_tile) {
+            i_step = 0;
+            i_tile++;
+        }
+    };
+    for (int s = 0; s < S; s++) issue(s);
+
+    // ---- activations (from the previous kernel in the stream) ----
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (FUSED) {
+        // quantize_q8 (crates/infr-cpu/src/quant.rs:27-58) per 256-block, one warp per block
+        for (int n = 0; n < M; n++)
+        for (int b = warp; b < nb; b += kW) {
+            float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+            if (n < m) {
+                const float *xp = x + (size_t)n * in_f + (size_t)b * 256;
+                v0 = *reinterpret_cast<const float4 *>(xp + lane * 8);
+                v1 = *reinterpret_cast<const float4 *>(xp + lane * 8 + 4);
+            }
+            float am = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                             fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            const float dd = am / 127.0f;
+            const float id = dd > 0.0f ? 1.0f / dd : 0.0f;
+            const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            int q[8], sum = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float r = roundf(vv[i] * id);
+                r = fminf(fmaxf(r, -127.0f), 127.0f);
+                q[i] = (int)r;
+                sum += q[i];
+            }
+            // lane holds elements 8*lane..8*lane+7 = sub-block s = lane/4, l = 8*(lane&3)+i
+            const int s = lane >> 2, tt = lane & 3;
+            uint2 pk;
+            pk.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+            pk.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+            *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * 256 + tt * 64 + s * 8) = pk;
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if (tt == 0) {
+                s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum & 63);
+                s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
+            }
+            if (lane == 0) s_d8[n * nb + b] = dd;
+        }
+    } else {
+        const int units = in_f / 8;  // 8-byte units
+        for (int n = 0; n < M; n++) {
+            const bool on = n < m;
+            for (int u = threadIdx.x; u < units; u += kThreadsMma) {
+                uint2 v = make_uint2(0, 0);
+                if (on) v = *reinterpret_cast<const uint2 *>(a.qs + (size_t)n * in_f + (size_t)u * 8);
+                const int b = u >> 5, uu = u & 31, s = uu >> 2, tt = uu & 3;
+                *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * 256 + tt * 64 + s * 8) = v;
+            }
+            for (int r = threadIdx.x; r < nb * 8; r += kThreadsMma) {
+                const int b = r >> 3, s = r & 7;
+                const int sum = on ? a.sums[(size_t)n * nb * 8 + r] : 0;
+                s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum & 63);
+                s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
+            }
+            for (int b = threadIdx.x; b < nb; b += kThreadsMma) s_d8[n * nb + b] = on ? a.d[(size_t)n * nb + b] : 0.f;
+        }
+    }
+    __syncthreads();
+
+    // ---- consume ----
+    const bool btok = g < M;  // this lane's B column carries a real token
+    int slot = 0, jc = 0;
+    uint32_t phase = 0;
+    bool dead = false;
+    for (int tile = 0; tile < n_tiles; tile++) {
+        float accf[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int step = 0; step < steps_per_tile; step++, jc++) {
+            if (!dead && !bar_wait(s_u32(wbar + slot), phase)) {
+                dead = true;
+                if (lane == 0) {
+                    atomicExch(status, 3u);
+                    s_bad = 1;
+                }
+            }
+            const int blk0 = kb0 + step * kStepBlocks;
+            const int nblk = min(kStepBlocks, kb1 - blk0);
+            const uint8_t *sl = ring + (size_t)slot * kSlotBytes;
+            if (!dead) {
+                for (int bl = 0; bl < nblk; bl++) {
+                    const int b = blk0 + bl;
+                    const uint8_t *r0 = sl + (size_t)g * (kStepBlocks * 144) + bl * 144;
+                    const uint8_t *r1 = r0 + 8 * (kStepBlocks * 144);
+                    const uint4 h0 = *reinterpret_cast<const uint4 *>(r0);
+                    const uint4 h1 = *reinterpret_cast<const uint4 *>(r1);
+                    uint32_t sc0[2], mn0[2], sc1[2], mn1[2];
+                    k4_all(h0.y, h0.z, h0.w, sc0, mn0);
+                    k4_all(h1.y, h1.z, h1.w, sc1, mn1);
+                    // B operands of this block for token g
+                    uint32_t bq[16];
+                    uint32_t bl_ = 0, bh_ = 0;
+                    if (btok) {
+                        const uint4 *cp = reinterpret_cast<const uint4 *>(s_codes + (size_t)(g * nb + b) * 256 + t * 64);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint4 v = cp[i];
+                            bq[4 * i] = v.x;
+                            bq[4 * i + 1] = v.y;
+                            bq[4 * i + 2] = v.z;
+                            bq[4 * i + 3] = v.w;
+                        }
+                        if (t < 2) {
+                            bl_ = *reinterpret_cast<const uint32_t *>(s_bsplit + (size_t)(g * nb + b) * 16 + t * 4);
+                            bh_ = *reinterpret_cast<const uint32_t *>(s_bsplit + (size_t)(g * nb + b) * 16 + 8 + t * 4);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) bq[i] = 0;
+                    }
+                    int sdl[4] = {0, 0, 0, 0}, sdh[4] = {0, 0, 0, 0};  // low / high (x16) nibble sums, scaled
+#pragma unroll
+                    for (int p = 0; p < 4; p++) {
+                        const uint2 w0 = *reinterpret_cast<const uint2 *>(r0 + 16 + p * 32 + t * 8);
+                        const uint2 w1 = *reinterpret_cast<const uint2 *>(r1 + 16 + p * 32 + t * 8);
+                        int dlo[4], dhi[4];
+                        mma_u8s8(dlo, w0.x & 0x0F0F0F0Fu, w1.x & 0x0F0F0F0Fu, w0.y & 0x0F0F0F0Fu, w1.y & 0x0F0F0F0Fu,
+                                 bq[4 * p], bq[4 * p + 1]);
+                        mma_u8s8(dhi, w0.x & 0xF0F0F0F0u, w1.x & 0xF0F0F0F0u, w0.y & 0xF0F0F0F0u, w1.y & 0xF0F0F0F0u,
+                                 bq[4 * p + 2], bq[4 * p + 3]);
+                        // scales of sub-block 2p (low nibbles) and 2p+1 (high nibbles) for rows g and g+8
+                        const uint32_t sel = (p & 1) ? 0x4442u : 0x4440u;
+                        const int sa_lo = (int)__byte_perm(sc0[p >> 1], 0, sel), sa_hi = (int)__byte_perm(sc0[p >> 1], 0, sel + 1);
+                        const int sb_lo = (int)__byte_perm(sc1[p >> 1], 0, sel), sb_hi = (int)__byte_perm(sc1[p >> 1], 0, sel + 1);
+                        sdl[0] += sa_lo * dlo[0];
+                        sdh[0] += sa_hi * dhi[0];
+                        sdl[2] += sb_lo * dlo[2];
+                        sdh[2] += sb_hi * dhi[2];
+                        if (M > 1) {
+                            sdl[1] += sa_lo * dlo[1];
+                            sdh[1] += sa_hi * dhi[1];
+                            sdl[3] += sb_lo * dlo[3];
+                            sdh[3] += sb_hi * dhi[3];
+                        }
+                    }
+                    int sd[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) sd[i] = sdl[i] + (sdh[i] >> 4);  // exact: sdh is a multiple of 16
+                    // min term: K slots 0..7 carry the eight m_s (lanes t = 0, 1), the rest are zero
+                    int sml[4], smh[4];
+                    const uint32_t am0 = t < 2 ? mn0[t] : 0u, am1 = t < 2 ? mn1[t] : 0u;
+                    mma_u8s8(sml, am0, am1, 0u, 0u, bl_, 0u);
+                    mma_u8s8(smh, am0, am1, 0u, 0u, bh_, 0u);
+                    const float d0 = h2f(h0.x), dm0 = h2f(h0.x >> 16), d1 = h2f(h1.x), dm1 = h2f(h1.x >> 16);
+                    const float e0 = 2 * t < M ? s_d8[(2 * t) * nb + b] : 0.f;
+                    accf[0] += e0 * (d0 * (float)sd[0] - dm0 * (float)(sml[0] + 64 * smh[0]));
+                    accf[2] += e0 * (d1 * (float)sd[2] - dm1 * (float)(sml[2] + 64 * smh[2]));
+                    if (M > 1) {
+                        const float e1 = 2 * t + 1 < M ? s_d8[(2 * t + 1) * nb + b] : 0.f;
+                        accf[1] += e1 * (d0 * (float)sd[1] - dm0 * (float)(sml[1] + 64 * smh[1]));
+                        accf[3] += e1 * (d1 * (float)sd[3] - dm1 * (float)(sml[3] + 64 * smh[3]));
+                    }
+                }
+            }
+            __syncwarp();
+            issue(slot);
+            if (++slot == S) {
+                slot = 0;
+                phase ^= 1u;
+            }
+        }
+        // partial sums of this warp's K range: [row 0..15][token 0..7]
+        float *part = s_part + ((size_t)(tile & 1) * kW + warp) * 128;
+        part[g * 8 + 2 * t] = accf[0];
+        part[g * 8 + 2 * t + 1] = accf[1];
+        part[(g + 8) * 8 + 2 * t] = accf[2];
+        part[(g + 8) * 8 + 2 * t + 1] = accf[3];
+        __syncthreads();
+        {
+            const int r = threadIdx.x >> 3, n = threadIdx.x & 7;
+            const int row = r_begin + tile * kTileRows + r;
+            if (n < m && row < r_begin + r_count) {
+                const float *pp = s_part + (size_t)(tile & 1) * kW * 128 + r * 8 + n;
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < kW; w++) v += pp[w * 128];
+                y[(size_t)n * out_f + row] = v;
+            }
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+template <int M, bool FUSED>
+cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
+                         const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+    MmaGeom geo;
+    geo.nb = in_f / 256;
+    geo.bpw = (geo.nb + kW - 1) / kW;
+    const size_t acts = (size_t)M * geo.nb * (256 + 16) + (size_t)((M * geo.nb + 3) & ~3) * 4;
+    geo.act_bytes = (int)acts;
+    const size_t fixed = acts + (size_t)2 * kW * 128 * 4 + (size_t)kW * kMaxSlotsMma * 8 + 64;
+    const size_t per_slot = (size_t)kW * kSlotBytes;
+    if (fixed + 2 * per_slot > (size_t)dev.max_smem_optin - 1024) return cudaErrorInvalidValue;
+    const size_t half = (size_t)dev.max_smem_optin / 2 - 2048;
+    // up to four resident CTAs (16 math warps) per SM, each with at least two ring slots per warp
+    const size_t quarter = (size_t)dev.max_smem_optin / 4 - 2048;
+    const int per_sm = fixed + 2 * per_slot <= quarter ? 4 : (fixed + 2 * per_slot <= half ? 2 : 1);
+    const size_t budget = per_sm == 4 ? quarter : (per_sm == 2 ? half : (size_t)dev.max_smem_optin - 1024);
+    int slots = (int)((budget - fixed) / per_slot);
+    if (slots > kMaxSlotsMma) slots = kMaxSlotsMma;
+    geo.slots = slots;
+    const size_t smem = fixed + (size_t)slots * per_slot;
+    int grid = (out_f + kTileRows - 1) / kTileRows;
+    if (grid > dev.sm_count * per_sm) grid = dev.sm_count * per_sm;
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap tmap;
+    {
+        const cuuint64_t gdim[2] = {(cuuint64_t)geo.nb * 36, (cuuint64_t)out_f};
+        const cuuint64_t gstride[1] = {(cuuint64_t)geo.nb * 144};
+        const cuuint32_t box[2] = {(cuuint32_t)kStepBlocks * 36, (cuuint32_t)kTileRows};
+        const cuuint32_t estr[2] = {1, 1};
+        if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    auto kernel = gemv_q4k_mma_kernel<M, FUSED>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreadsMma);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, tmap, a, x, y, m, in_f, out_f, geo, status);
+}
+
+template <bool FUSED>
+cudaError_t launch_mma(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
+                       const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+    if (m == 1) return launch_mma_m<1, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st);
+    if (m == 2) return launch_mma_m<2, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st);
+    if (m <= 4) return launch_mma_m<4, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st);
+    return launch_mma_m<8, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st);
+}
+
+}  // namespace
+
+cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,
+                                const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+    if (m < 1 || m > 8 || in_f % 256) return cudaErrorInvalidValue;
+    if (a) return launch_mma<false>(w, *a, nullptr, y, m, in_f, out_f, dev, status, st);
+    Q8Dev none{nullptr, nullptr, nullptr, nullptr, 256};
+    return launch_mma<true>(w, none, x, y, m, in_f, out_f, dev, status, st);
+}
+
+}  // namespace infr

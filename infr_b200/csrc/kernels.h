@@ -48,6 +48,10 @@ cudaError_t launch_gemv_q8(int dt, const uint8_t *w, const Q8Dev &a, float *y, i
 // is a device-visible word the kernel sets non-zero if a bounded wait expires.
 cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
                                const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
+// Q4_K, m <= 8, on the warp-level int8 matrix unit.  Exactly one of `a` (pre-quantised rows) and `x`
+// (f32 rows, quantised inside the kernel) is non-null.
+cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,
+                                const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
 // y[m,out_f] (m <= 8) from f32 activations and dequantised weights.
 cudaError_t launch_gemv_f32(int dt, const uint8_t *w, const float *x, float *y, int m, int in_f, int out_f,
                             const DeviceInfo &dev, cudaStream_t st);

@@ -302,7 +302,7 @@ def run_b200(args):
     if rank == 0 and world == 1 and not args.no_sweep:
         sweep = []
         sw_steps = max(20, min(steps, 100))
-        for dtype, o, i_, seed, ms_ in ((infr_b200.Q4K, 14336, 4096, 5, (1,)), (infr_b200.Q6K, 14336, 4096, 2, (1, 4, 8)),
+        for dtype, o, i_, seed, ms_ in ((infr_b200.Q4K, 14336, 4096, 5, (1, 4, 8)), (infr_b200.Q6K, 14336, 4096, 2, (1, 4, 8)),
                                         (infr_b200.Q2_0, 4096, 14336, 3, (1, 4, 8))):
             for m in ms_:
                 sweep.append(_gemv_case(be, infr_b200, dtype, o, i_, m, seed, sw_steps, 5, caps.l2_bytes, hbm_peak))

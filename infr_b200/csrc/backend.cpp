@@ -251,10 +251,23 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
             if (!s.ok()) return s;
             launches_ += 1;
         } else if (dtype == DT_Q4K && gemv_impl_ == 0) {
-            // one kernel: activation rows are quantised inside the GEMV while the first weights stream in
-            Status s = cuda_status(launch_gemv_q4k_mma(w, nullptr, xr, yr, (int)mm, (int)in_f, (int)out_f, dev_, status_dev_, stream_), "gemv_q4k");
-            if (!s.ok()) return s;
-            launches_ += 1;
+            // one kernel: activation rows are quantised inside the GEMV while the first weights stream in.
+            // Rows so long that `mm` staged activation rows exceed shared memory are run in narrower batches.
+            uint32_t step = mm;
+            for (uint32_t t0 = 0; t0 < mm;) {
+                const uint32_t n = mm - t0 < step ? mm - t0 : step;
+                cudaError_t e = launch_gemv_q4k_mma(w, nullptr, xr + (size_t)t0 * in_f, yr + (size_t)t0 * out_f, (int)n, (int)in_f,
+                                                    (int)out_f, dev_, status_dev_, stream_);
+                if (e == cudaErrorInvalidValue && step > 1) {
+                    cudaGetLastError();
+                    step /= 2;
+                    continue;
+                }
+                Status s = cuda_status(e, "gemv_q4k");
+                if (!s.ok()) return s;
+                launches_ += 1;
+                t0 += n;
+            }
         } else {
             Q8Dev a;
             Status s = quantize_for(dtype, xr, mm, in_f, &a);

@@ -36,11 +36,7 @@
 namespace infr {
 namespace {
 
-constexpr int kW = 4;               // warps per CTA (K split)
-constexpr int kThreadsMma = kW * 32;
 constexpr int kTileRows = 16;
-constexpr int kStepBlocks = 2;      // super-blocks per ring slot per row
-constexpr int kSlotBytes = kTileRows * kStepBlocks * 144;
 constexpr int kMaxSlotsMma = 4;
 constexpr uint32_t kSpin = 1u << 22;
 
@@ -99,10 +95,12 @@ struct MmaGeom {
 //   codes  : 256 B at (n*nb + b)*256, element (sub-block s, l = 8t+i) at t*64 + s*8 + i
 //   bsplit : 16 B at (n*nb + b)*16: bytes 0..7 = low 6 bits of bsum_s, bytes 8..15 = bsum_s >> 6
 //   d8     : float [n*nb + b]
-template <int M, bool FUSED>
-__global__ void __launch_bounds__(kThreadsMma, 4)
+// KW = warps per CTA (they split K), SB = super-blocks per ring slot per row.
+template <int M, bool FUSED, int KW, int SB>
+__global__ void __launch_bounds__(KW * 32, 16 / KW)
     gemv_q4k_mma_kernel(const __grid_constant__ CUtensorMap tmap, Q8Dev a, const float *__restrict__ x, float *__restrict__ y, int m,
                         int in_f, int out_f, MmaGeom geo, uint32_t *__restrict__ status) {
+    constexpr int kW = KW, kThreadsMma = KW * 32, kStepBlocks = SB, kSlotBytes = kTileRows * SB * 144;
     extern __shared__ __align__(128) uint8_t smem[];
     const int nb = geo.nb, S = geo.slots;
     uint8_t *rings = smem;                                         // [kW][S][kSlotBytes]
@@ -223,7 +221,7 @@ __global__ void __launch_bounds__(kThreadsMma, 4)
     __syncthreads();
 
     // ---- consume ----
-    const bool btok = g < M;  // this lane's B column carries a real token
+    const int gt = g < M ? g : 0;  // token whose codes this lane feeds as its B column
     int slot = 0, jc = 0;
     uint32_t phase = 0;
     bool dead = false;
@@ -241,7 +239,9 @@ __global__ void __launch_bounds__(kThreadsMma, 4)
             const int nblk = min(kStepBlocks, kb1 - blk0);
             const uint8_t *sl = ring + (size_t)slot * kSlotBytes;
             if (!dead) {
-                for (int bl = 0; bl < nblk; bl++) {
+#pragma unroll
+                for (int bl = 0; bl < kStepBlocks; bl++) {
+                    if (bl >= nblk) break;
                     const int b = blk0 + bl;
                     const uint8_t *r0 = sl + (size_t)g * (kStepBlocks * 144) + bl * 144;
                     const uint8_t *r1 = r0 + 8 * (kStepBlocks * 144);
@@ -251,26 +251,21 @@ __global__ void __launch_bounds__(kThreadsMma, 4)
                     k4_all(h0.y, h0.z, h0.w, sc0, mn0);
                     k4_all(h1.y, h1.z, h1.w, sc1, mn1);
                     // B operands of this block for token g
+                    // Output column n depends on B column n only, and columns >= M are never stored, so
+                    // lanes of those columns simply re-read token gt; likewise the bsum words of lanes
+                    // t >= 2 meet zero A operands.
                     uint32_t bq[16];
-                    uint32_t bl_ = 0, bh_ = 0;
-                    if (btok) {
-                        const uint4 *cp = reinterpret_cast<const uint4 *>(s_codes + (size_t)(g * nb + b) * 256 + t * 64);
+                    const uint4 *cp = reinterpret_cast<const uint4 *>(s_codes + (size_t)(gt * nb + b) * 256 + t * 64);
 #pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const uint4 v = cp[i];
-                            bq[4 * i] = v.x;
-                            bq[4 * i + 1] = v.y;
-                            bq[4 * i + 2] = v.z;
-                            bq[4 * i + 3] = v.w;
-                        }
-                        if (t < 2) {
-                            bl_ = *reinterpret_cast<const uint32_t *>(s_bsplit + (size_t)(g * nb + b) * 16 + t * 4);
-                            bh_ = *reinterpret_cast<const uint32_t *>(s_bsplit + (size_t)(g * nb + b) * 16 + 8 + t * 4);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; i++) bq[i] = 0;
+                    for (int i = 0; i < 4; i++) {
+                        const uint4 v = cp[i];
+                        bq[4 * i] = v.x;
+                        bq[4 * i + 1] = v.y;
+                        bq[4 * i + 2] = v.z;
+                        bq[4 * i + 3] = v.w;
                     }
+                    const uint32_t bl_ = *reinterpret_cast<const uint32_t *>(s_bsplit + (size_t)(gt * nb + b) * 16 + (t & 1) * 4);
+                    const uint32_t bh_ = *reinterpret_cast<const uint32_t *>(s_bsplit + (size_t)(gt * nb + b) * 16 + 8 + (t & 1) * 4);
                     int sdl[4] = {0, 0, 0, 0}, sdh[4] = {0, 0, 0, 0};  // low / high (x16) nibble sums, scaled
 #pragma unroll
                     for (int p = 0; p < 4; p++) {
@@ -301,7 +296,7 @@ __global__ void __launch_bounds__(kThreadsMma, 4)
                     for (int i = 0; i < 4; i++) sd[i] = sdl[i] + (sdh[i] >> 4);  // exact: sdh is a multiple of 16
                     // min term: K slots 0..7 carry the eight m_s (lanes t = 0, 1), the rest are zero
                     int sml[4], smh[4];
-                    const uint32_t am0 = t < 2 ? mn0[t] : 0u, am1 = t < 2 ? mn1[t] : 0u;
+                    const uint32_t am0 = t == 0 ? mn0[0] : (t == 1 ? mn0[1] : 0u), am1 = t == 0 ? mn1[0] : (t == 1 ? mn1[1] : 0u);
                     mma_u8s8(sml, am0, am1, 0u, 0u, bl_, 0u);
                     mma_u8s8(smh, am0, am1, 0u, 0u, bh_, 0u);
                     const float d0 = h2f(h0.x), dm0 = h2f(h0.x >> 16), d1 = h2f(h1.x), dm1 = h2f(h1.x >> 16);
@@ -329,7 +324,7 @@ __global__ void __launch_bounds__(kThreadsMma, 4)
         part[(g + 8) * 8 + 2 * t] = accf[2];
         part[(g + 8) * 8 + 2 * t + 1] = accf[3];
         __syncthreads();
-        {
+        if (threadIdx.x < kTileRows * 8) {  // 16 rows x 8 token columns; CTAs have at least 128 threads
             const int r = threadIdx.x >> 3, n = threadIdx.x & 7;
             const int row = r_begin + tile * kTileRows + r;
             if (n < m && row < r_begin + r_count) {
@@ -358,22 +353,22 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-template <int M, bool FUSED>
-cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
-                         const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+template <int M, bool FUSED, int KW, int SB>
+cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
+                           const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+    constexpr int kSlotBytes = kTileRows * SB * 144;
     MmaGeom geo;
     geo.nb = in_f / 256;
-    geo.bpw = (geo.nb + kW - 1) / kW;
+    geo.bpw = (geo.nb + KW - 1) / KW;
     const size_t acts = (size_t)M * geo.nb * (256 + 16) + (size_t)((M * geo.nb + 3) & ~3) * 4;
     geo.act_bytes = (int)acts;
-    const size_t fixed = acts + (size_t)2 * kW * 128 * 4 + (size_t)kW * kMaxSlotsMma * 8 + 64;
-    const size_t per_slot = (size_t)kW * kSlotBytes;
+    const size_t fixed = acts + (size_t)2 * KW * 128 * 4 + (size_t)KW * kMaxSlotsMma * 8 + 64;
+    const size_t per_slot = (size_t)KW * kSlotBytes;
     if (fixed + 2 * per_slot > (size_t)dev.max_smem_optin - 1024) return cudaErrorInvalidValue;
-    const size_t half = (size_t)dev.max_smem_optin / 2 - 2048;
-    // up to four resident CTAs (16 math warps) per SM, each with at least two ring slots per warp
-    const size_t quarter = (size_t)dev.max_smem_optin / 4 - 2048;
-    const int per_sm = fixed + 2 * per_slot <= quarter ? 4 : (fixed + 2 * per_slot <= half ? 2 : 1);
-    const size_t budget = per_sm == 4 ? quarter : (per_sm == 2 ? half : (size_t)dev.max_smem_optin - 1024);
+    // resident CTAs per SM: 16 math warps in total, each warp with at least two ring slots
+    int per_sm = 16 / KW;
+    while (per_sm > 1 && fixed + 2 * per_slot > (size_t)dev.max_smem_optin / per_sm - 2048) per_sm /= 2;
+    const size_t budget = (size_t)dev.max_smem_optin / per_sm - (per_sm > 1 ? 2048 : 1024);
     int slots = (int)((budget - fixed) / per_slot);
     if (slots > kMaxSlotsMma) slots = kMaxSlotsMma;
     geo.slots = slots;
@@ -386,19 +381,19 @@ cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float
     {
         const cuuint64_t gdim[2] = {(cuuint64_t)geo.nb * 36, (cuuint64_t)out_f};
         const cuuint64_t gstride[1] = {(cuuint64_t)geo.nb * 144};
-        const cuuint32_t box[2] = {(cuuint32_t)kStepBlocks * 36, (cuuint32_t)kTileRows};
+        const cuuint32_t box[2] = {(cuuint32_t)SB * 36, (cuuint32_t)kTileRows};
         const cuuint32_t estr[2] = {1, 1};
         if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    auto kernel = gemv_q4k_mma_kernel<M, FUSED>;
+    auto kernel = gemv_q4k_mma_kernel<M, FUSED, KW, SB>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreadsMma);
+    cfg.blockDim = dim3(KW * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -407,6 +402,40 @@ cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, tmap, a, x, y, m, in_f, out_f, geo, status);
+}
+
+// Few 16-row tiles (small matrices) -> more warps share a tile's K range so that a tile's latency is short;
+// many tiles -> four warps per tile and the SM overlaps independent tiles instead.
+template <int M, bool FUSED>
+cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
+                         const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+    const int nb = in_f / 256, tiles = (out_f + kTileRows - 1) / kTileRows;
+    // shared memory a configuration needs with two ring slots per warp
+    auto need = [&](int kw) {
+        const int sb = (nb + kw - 1) / kw == 1 ? 1 : 2;
+        return (size_t)M * nb * 272 + (size_t)((M * nb + 3) & ~3) * 4 + (size_t)2 * kw * 512 + (size_t)kw * kMaxSlotsMma * 8 + 64 +
+               (size_t)2 * kw * kTileRows * sb * 144;
+    };
+    int kw = tiles >= 4 * dev.sm_count ? 4 : (tiles >= 2 * dev.sm_count ? 8 : 16);
+    // wide batches stage more activation bytes per CTA: let more warps share one staging copy so that
+    // 16 math warps stay resident per SM
+    while (kw < 16 && need(kw) > (size_t)dev.max_smem_optin / (16 / kw) - 2048) kw *= 2;
+    while (kw > 4 && kw > nb) kw /= 2;
+    // long rows with a wide batch may not fit at all with many warps: fall back to fewer
+    while (kw > 4 && need(kw) > (size_t)dev.max_smem_optin - 1024) kw /= 2;
+    const int bpw = (nb + kw - 1) / kw;
+#define INFR_MMA(KW_, SB_) return launch_mma_cfg<M, FUSED, KW_, SB_>(w, a, x, y, m, in_f, out_f, dev, status, st)
+    if (kw == 16) {
+        if (bpw == 1) INFR_MMA(16, 1);
+        INFR_MMA(16, 2);
+    }
+    if (kw == 8) {
+        if (bpw == 1) INFR_MMA(8, 1);
+        INFR_MMA(8, 2);
+    }
+    if (bpw == 1) INFR_MMA(4, 1);
+    INFR_MMA(4, 2);
+#undef INFR_MMA
 }
 
 template <bool FUSED>

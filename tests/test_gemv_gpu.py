@@ -54,6 +54,8 @@ SHAPES = [
     (Q4K, 768, 40),      # 3 super-blocks: a partial 4-block warp step
     (Q4K, 2048, 768),    # MoE expert gate/up
     (Q4K, 4096, 4096),   # the Q4_K 4096x4096 matvec configuration
+    (Q4K, 1024, 6408),   # 401 row tiles (the last one partial): the 8-warps-per-tile configuration
+    (Q4K, 14336, 1000),  # long rows: 56 super-blocks split over the warps of a tile
     (Q6K, 768, 24),
     (Q6K, 4096, 14336),  # decode sweep: W 14336 x 4096 in Q6_K
     (Q2_0, 704, 16),     # 11 blocks: not a multiple of 8 blocks nor of 256 elements

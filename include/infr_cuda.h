@@ -184,6 +184,20 @@ INFR_API int32_t infr_cuda_gemv_q8(infr_cuda_ctx *ctx, int32_t dtype, const infr
                                    const infr_cuda_buf *qs, const infr_cuda_buf *d, const infr_cuda_buf *sums,
                                    const infr_cuda_buf *sums16, infr_cuda_buf *y, uint32_t m, uint32_t in_f,
                                    uint32_t out_f);
+/* No counterpart in the reference: a decode GEMV (INFR_ACT_INT8 arithmetic, same results as
+ * infr_cuda_gemv) for callers that cannot allocate device memory when they need it — plugins living
+ * inside another engine's memory pool, loops that must stay clear of the driver's allocator after
+ * start-up.  It takes RAW device pointers (w: GGUF blocks of the first row used, x: f32 [m,in_f],
+ * y: f32 [m,out_f]) and a cudaStream_t passed as void* (NULL = the default stream), needs no context,
+ * and keeps its quantised activations in a 192 KiB array built into the library (held by every GPU
+ * that loads it) instead of allocating: the call runs no cudaMalloc / cudaFree / allocating routine.
+ * Limits: m <= 8, in_f <= 16384; larger sizes are rejected with INFR_E_INVALID.  The first call on a
+ * device looks up the array's device address (cudaGetSymbolAddress) — make that call before any
+ * stream capture.  All calls share the one array: calls that overlap on the GPU (different streams,
+ * or threads) race on it; calls on one stream are ordered and need no clearing in between.  Work is
+ * enqueued on `stream`; the caller synchronises.  On failure a message is copied into err. */
+INFR_API int32_t infr_cuda_gemv_noalloc(int32_t dtype, const void *w, const float *x, float *y, uint32_t m,
+                                        uint32_t in_f, uint32_t out_f, void *stream, char *err, size_t err_cap);
 /* Same arithmetic as infr_cuda_gemv(INFR_ACT_INT8) for m = 1, but writes the per-block int32
  * accumulators instead of y: Q4_K -> acc[out_f][in_f/256][2] = (sd, sm) of
  * crates/infr-cpu/src/kernels.rs:161-181; Q6_K -> acc[out_f][in_f/256] = isum (:519-523);

@@ -34,7 +34,7 @@ EXPORTED_SYMBOLS = [
     "infr_cuda_alloc", "infr_cuda_alloc_uninit", "infr_cuda_free", "infr_cuda_buf_len",
     "infr_cuda_buf_device_ptr", "infr_cuda_upload", "infr_cuda_upload_at", "infr_cuda_download",
     "infr_cuda_copy", "infr_cuda_host_alloc", "infr_cuda_host_free", "infr_cuda_sync", "infr_cuda_compile", "infr_cuda_plan_free", "infr_cuda_execute",
-    "infr_cuda_quantize_q8", "infr_cuda_quantize_q8_1", "infr_cuda_gemv", "infr_cuda_gemv_q8", "infr_cuda_gemv_block_acc",
+    "infr_cuda_quantize_q8", "infr_cuda_quantize_q8_1", "infr_cuda_gemv", "infr_cuda_gemv_q8", "infr_cuda_gemv_noalloc", "infr_cuda_gemv_block_acc",
     "infr_cuda_linear", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
     "infr_cuda_graph_free", "infr_cuda_timer_start", "infr_cuda_timer_stop", "infr_cuda_flush_l2",
     "infr_cuda_launch_count",
@@ -111,6 +111,7 @@ def load_library() -> C.CDLL:
         "infr_cuda_quantize_q8_1": (i32, [vp, vp, u32, u32, vp, vp, vp]),
         "infr_cuda_gemv": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
         "infr_cuda_gemv_q8": (i32, [vp, i32, vp, u64, vp, vp, vp, vp, vp, u32, u32, u32]),
+        "infr_cuda_gemv_noalloc": (i32, [i32, vp, vp, vp, u32, u32, u32, vp, C.c_char_p, sz]),
         "infr_cuda_gemv_block_acc": (i32, [vp, i32, vp, u64, vp, vp, u32, u32]),
         "infr_cuda_linear": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
         "infr_cuda_capture_begin": (i32, [vp]),

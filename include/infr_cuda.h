@@ -212,6 +212,24 @@ INFR_API int32_t infr_cuda_linear(infr_cuda_ctx *ctx, int32_t dtype, const infr_
                                   const infr_cuda_buf *x, infr_cuda_buf *y, uint32_t m, uint32_t in_f,
                                   uint32_t out_f, int32_t act);
 
+/* Op::MoeFfn as a direct call (crates/infr-core/src/graph.rs:918-1011; CPU semantics
+ * crates/infr-cpu/src/lib.rs:2264-2984): F32 router [n_expert, ne], expert banks gate/up
+ * [n_expert][n_ff_exp, ne] and down [n_expert][ne, n_ff_exp] as raw GGUF blocks, softmax gating,
+ * top-n_used with ties to the lower expert id, SiLU gate, output-side weighting.  dst is f32 [rows, ne].
+ * Optional outputs for parity checks (NULL = not wanted): sel_ids i32 [rows, n_used] in rank order,
+ * sel_w f32 [rows, n_used], logits f32 [rows, n_expert]. */
+typedef struct {
+    uint32_t rows, ne, n_expert, n_used, n_ff_exp;
+    float scale;
+    int32_t norm_w;
+    int32_t router_dtype, gate_dtype, up_dtype, down_dtype; /* INFR_DT_* */
+} infr_moe_desc;
+INFR_API int32_t infr_cuda_moe_ffn(infr_cuda_ctx *ctx, const infr_moe_desc *desc, const infr_cuda_buf *x,
+                                   const infr_cuda_buf *router_x, const infr_cuda_buf *router,
+                                   const infr_cuda_buf *gate_exps, const infr_cuda_buf *up_exps,
+                                   const infr_cuda_buf *down_exps, infr_cuda_buf *dst, infr_cuda_buf *sel_ids,
+                                   infr_cuda_buf *sel_w, infr_cuda_buf *logits);
+
 /* ---- stream capture and timing ----
  * capture_begin .. capture_end records every kernel the calls in between enqueue into a CUDA graph
  * that infr_cuda_graph_launch replays (decode replays a fixed kernel sequence every token).  Calls

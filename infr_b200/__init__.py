@@ -35,7 +35,7 @@ EXPORTED_SYMBOLS = [
     "infr_cuda_buf_device_ptr", "infr_cuda_upload", "infr_cuda_upload_at", "infr_cuda_download",
     "infr_cuda_copy", "infr_cuda_host_alloc", "infr_cuda_host_free", "infr_cuda_sync", "infr_cuda_compile", "infr_cuda_plan_free", "infr_cuda_execute",
     "infr_cuda_quantize_q8", "infr_cuda_quantize_q8_1", "infr_cuda_gemv", "infr_cuda_gemv_q8", "infr_cuda_gemv_noalloc", "infr_cuda_gemv_block_acc",
-    "infr_cuda_linear", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
+    "infr_cuda_linear", "infr_cuda_moe_ffn", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
     "infr_cuda_graph_free", "infr_cuda_timer_start", "infr_cuda_timer_stop", "infr_cuda_flush_l2",
     "infr_cuda_launch_count",
 ]
@@ -66,6 +66,12 @@ class _TensorDecl(C.Structure):
 
 class _OpDesc(C.Structure):
     _fields_ = [("tag", C.c_uint32), ("t", C.c_uint32 * 8), ("u", C.c_uint32 * 12), ("f", C.c_float * 4)]
+
+
+class _MoeDesc(C.Structure):
+    _fields_ = [("rows", C.c_uint32), ("ne", C.c_uint32), ("n_expert", C.c_uint32), ("n_used", C.c_uint32),
+                ("n_ff_exp", C.c_uint32), ("scale", C.c_float), ("norm_w", C.c_int32), ("router_dtype", C.c_int32),
+                ("gate_dtype", C.c_int32), ("up_dtype", C.c_int32), ("down_dtype", C.c_int32)]
 
 
 class _GraphDesc(C.Structure):
@@ -114,6 +120,7 @@ def load_library() -> C.CDLL:
         "infr_cuda_gemv_noalloc": (i32, [i32, vp, vp, vp, u32, u32, u32, vp, C.c_char_p, sz]),
         "infr_cuda_gemv_block_acc": (i32, [vp, i32, vp, u64, vp, vp, u32, u32]),
         "infr_cuda_linear": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
+        "infr_cuda_moe_ffn": (i32, [vp, C.POINTER(_MoeDesc), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
         "infr_cuda_capture_begin": (i32, [vp]),
         "infr_cuda_capture_end": (i32, [vp, C.POINTER(vp)]),
         "infr_cuda_graph_launch": (i32, [vp, vp]),
@@ -382,6 +389,15 @@ class CudaBackend:
     def linear(self, dtype: int, w: Buffer, x: Buffer, y: Buffer, m: int, in_f: int, out_f: int,
                act: int = ACT_INT8, w_off: int = 0):
         self._check(self.L.infr_cuda_linear(self.ctx, dtype, w.handle, w_off, x.handle, y.handle, m, in_f, out_f, act))
+
+    def moe_ffn(self, x: Buffer, router_x: Buffer, router: Buffer, gate: Buffer, up: Buffer, down: Buffer, dst: Buffer, *,
+                rows: int, ne: int, n_expert: int, n_used: int, n_ff_exp: int, scale: float = 1.0, norm_w: bool = True,
+                wdt: int = Q4K, sel_ids: Optional[Buffer] = None, sel_w: Optional[Buffer] = None,
+                logits: Optional[Buffer] = None):
+        d = _MoeDesc(rows, ne, n_expert, n_used, n_ff_exp, scale, int(norm_w), F32, wdt, wdt, wdt)
+        h = lambda b: b.handle if b is not None else None
+        self._check(self.L.infr_cuda_moe_ffn(self.ctx, C.byref(d), x.handle, router_x.handle, router.handle, gate.handle,
+                                             up.handle, down.handle, dst.handle, h(sel_ids), h(sel_w), h(logits)))
 
     def gemv_block_acc(self, dtype: int, w: Buffer, x: Buffer, acc: Buffer, in_f: int, out_f: int, w_off: int = 0):
         self._check(self.L.infr_cuda_gemv_block_acc(self.ctx, dtype, w.handle, w_off, x.handle, acc.handle, in_f, out_f))

@@ -299,6 +299,76 @@ Status CudaBackend::gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *
     return s;
 }
 
+Status CudaBackend::moe_ffn(const MoeArgs &a) {
+    if (a.gate_dt != DT_Q4K || a.up_dt != DT_Q4K || a.down_dt != DT_Q4K)
+        return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: expert banks must be Q4_K");
+    if (a.ne == 0 || a.ne % 256 || a.n_ff == 0 || a.n_ff % 256)
+        return Status::Err(INFR_E_UNSUPPORTED, fmt("moe_ffn: ne=%u and n_ff_exp=%u must be multiples of 256", a.ne, a.n_ff));
+    if (a.n_expert == 0 || a.n_expert > 1024 || a.n_used == 0 || a.n_used > 32 || a.n_used > a.n_expert)
+        return Status::Err(INFR_E_INVALID, fmt("moe_ffn: n_expert=%u (<=1024), n_used=%u (<=32)", a.n_expert, a.n_used));
+    if (a.rows < 2 || reference_)
+        return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: the single-row / reference (f32 activation) expert path is not built yet");
+    if (a.rows == 0) return Status::Ok();
+    cudaSetDevice(device_);
+    const size_t rows = a.rows, ne = a.ne, nff = a.n_ff, nu = a.n_used, nx = a.n_expert;
+    const size_t n_pairs = rows * nu;
+    const size_t max_items = n_pairs / 8 + nx + 1;
+    // scratch carve-up (all 256-byte aligned)
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += align_up(bytes, 256);
+        return o;
+    };
+    const size_t o_logits = take(rows * nx * 4), o_ids = take(n_pairs * 4), o_w = take(n_pairs * 4);
+    const size_t o_prow = take(n_pairs * 4), o_pslot = take(n_pairs * 4);
+    const size_t o_ie = take(max_items * 4), o_ip = take(max_items * 4), o_ic = take(max_items * 4), o_ni = take(4);
+    const size_t o_xq = take(rows * ne), o_xd = take(rows * (ne / 256) * 4), o_xs = take(rows * (ne / 32) * 4);
+    const size_t o_g = take(n_pairs * nff * 4), o_u = take(n_pairs * nff * 4);
+    const size_t o_aq = take(n_pairs * nff), o_ad = take(n_pairs * (nff / 256) * 4), o_as = take(n_pairs * (nff / 32) * 4);
+    const size_t o_y = take(n_pairs * ne * 4);
+    Status s = ensure_scratch(off);
+    if (!s.ok()) return s;
+    uint8_t *b = scratch();
+    float *logits = a.logits ? a.logits : reinterpret_cast<float *>(b + o_logits);
+    int32_t *ids = a.sel_ids ? a.sel_ids : reinterpret_cast<int32_t *>(b + o_ids);
+    float *w = a.sel_w ? a.sel_w : reinterpret_cast<float *>(b + o_w);
+    int32_t *prow = reinterpret_cast<int32_t *>(b + o_prow), *pslot = reinterpret_cast<int32_t *>(b + o_pslot);
+    int32_t *ie = reinterpret_cast<int32_t *>(b + o_ie), *ip = reinterpret_cast<int32_t *>(b + o_ip);
+    int32_t *ic = reinterpret_cast<int32_t *>(b + o_ic), *ni = reinterpret_cast<int32_t *>(b + o_ni);
+    int8_t *xq = reinterpret_cast<int8_t *>(b + o_xq);
+    float *xd = reinterpret_cast<float *>(b + o_xd);
+    int32_t *xs = reinterpret_cast<int32_t *>(b + o_xs);
+    float *g = reinterpret_cast<float *>(b + o_g), *u = reinterpret_cast<float *>(b + o_u);
+    int8_t *aq = reinterpret_cast<int8_t *>(b + o_aq);
+    float *ad = reinterpret_cast<float *>(b + o_ad);
+    int32_t *as = reinterpret_cast<int32_t *>(b + o_as);
+    float *y = reinterpret_cast<float *>(b + o_y);
+#define INFR_STEP(call, what)                       \
+    do {                                            \
+        s = cuda_status((call), what);              \
+        if (!s.ok()) return s;                      \
+        launches_++;                                \
+    } while (0)
+    INFR_STEP(launch_moe_router(a.router, a.router_x, logits, (int)rows, (int)ne, (int)nx, stream_), "moe router");
+    INFR_STEP(launch_moe_route(logits, (int)rows, (int)nx, (int)nu, a.scale, a.norm_w, ids, w, stream_), "moe route");
+    INFR_STEP(launch_moe_bucket(ids, (int)rows, (int)nu, (int)nx, prow, pslot, ie, ip, ic, ni, nullptr, stream_), "moe bucket");
+    // stage A: every distinct row quantised once (lib.rs:2688-2718)
+    INFR_STEP(launch_quantize_q8(a.x, (int)rows, (int)ne, 256, xq, xd, xs, nullptr, nullptr, nullptr, stream_), "moe quantize x");
+    Q8Dev xa{xq, xd, xs, nullptr, 256};
+    // stage B: gate and up expert GEMMs, rows gathered per pair
+    INFR_STEP(launch_grouped_q4k_mma(a.gate, (int)nx, xa, g, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_items, dev_, status_dev_, stream_), "moe gate");
+    INFR_STEP(launch_grouped_q4k_mma(a.up, (int)nx, xa, u, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_items, dev_, status_dev_, stream_), "moe up");
+    // stage C: SwiGLU and re-quantisation per pair
+    INFR_STEP(launch_moe_swiglu_quant(g, u, (int)n_pairs, (int)nff, aq, ad, as, nullptr, stream_), "moe swiglu");
+    Q8Dev aa{aq, ad, as, nullptr, 256};
+    // stage D: down GEMMs; stage E: rank-order combine
+    INFR_STEP(launch_grouped_q4k_mma(a.down, (int)nx, aa, y, (int)nff, (int)ne, ie, ip, ic, ni, nullptr, (int)max_items, dev_, status_dev_, stream_), "moe down");
+    INFR_STEP(launch_moe_combine(y, pslot, w, (int)rows, (int)nu, (int)ne, a.dst, stream_), "moe combine");
+#undef INFR_STEP
+    return Status::Ok();
+}
+
 Status CudaBackend::gemv_block_acc(int dtype, const uint8_t *w, const float *x, int32_t *acc, uint32_t in_f, uint32_t out_f) {
     if (dtype != DT_Q4K && dtype != DT_Q6K && dtype != DT_Q2_0)
         return Status::Err(INFR_E_UNSUPPORTED, fmt("gemv_block_acc: dtype code %d", dtype));
@@ -347,7 +417,14 @@ Status CudaBackend::compile(const infr_graph_desc &g, infr_cuda_plan **out) {
             if ((uint64_t)w_off + (uint64_t)op.u[2] * in_f > w.numel)
                 return fail(Status::Err(INFR_E_INVALID, fmt("compile: Linear rows [%u,+%u) leave the %llu-element weight", w_off / in_f, op.u[2], (unsigned long long)w.numel)));
         } else {
-            return fail(Status::Err(INFR_E_UNSUPPORTED, "compile: MoeFfn is not available in this build"));
+            // u = {ne, n_expert, n_used, n_ff_exp, norm_w, fused_gate_up, weight_before, act, gating}
+            if (op.u[5] || op.u[6] || op.u[7] || op.u[8])
+                return fail(Status::Err(INFR_E_UNSUPPORTED, "compile: MoeFfn with fused gate/up, weight_before, a non-SiLU activation or non-softmax gating"));
+            if (g.tensors[op.t[2]].dtype != DT_F32)
+                return fail(Status::Err(INFR_E_UNSUPPORTED, "compile: MoeFfn router weights must be F32"));
+            for (int k = 3; k <= 5; k++)
+                if (g.tensors[op.t[k]].dtype != DT_Q4K)
+                    return fail(Status::Err(INFR_E_UNSUPPORTED, "compile: MoeFfn expert banks must be Q4_K"));
         }
     }
     cudaSetDevice(device_);
@@ -409,6 +486,25 @@ Status CudaBackend::execute(infr_cuda_plan *plan, infr_cuda_buf *const *bindings
             if (!(s = resolve(op.t[2], (size_t)m * out_f * 4, "Linear dst", &y)).ok()) return s;
             s = linear(dt, w.ptr + row0 * bpr, reinterpret_cast<const float *>(x.ptr), reinterpret_cast<float *>(y.ptr), m, in_f,
                        out_f, reference_ ? INFR_ACT_F32 : INFR_ACT_INT8);
+            if (!s.ok()) return s;
+        } else if (op.tag == INFR_OP_MOE_FFN) {
+            const uint32_t ne = op.u[0], nx = op.u[1], nu = op.u[2], nff = op.u[3];
+            const infr_tensor_decl &xd = plan->tensors[op.t[0]];
+            const uint32_t rows = ne ? (uint32_t)(xd.numel / ne) : 0;
+            const size_t bank_gu = (size_t)nx * nff * (ne / 256) * 144, bank_d = (size_t)nx * ne * (nff / 256) * 144;
+            DevSpan x, rx, r, gt, up, dn, dst;
+            Status s;
+            if (!(s = resolve(op.t[0], (size_t)rows * ne * 4, "MoeFfn x", &x)).ok()) return s;
+            if (!(s = resolve(op.t[1], (size_t)rows * ne * 4, "MoeFfn router_x", &rx)).ok()) return s;
+            if (!(s = resolve(op.t[2], (size_t)nx * ne * 4, "MoeFfn router", &r)).ok()) return s;
+            if (!(s = resolve(op.t[3], bank_gu, "MoeFfn gate_exps", &gt)).ok()) return s;
+            if (!(s = resolve(op.t[4], bank_gu, "MoeFfn up_exps", &up)).ok()) return s;
+            if (!(s = resolve(op.t[5], bank_d, "MoeFfn down_exps", &dn)).ok()) return s;
+            if (!(s = resolve(op.t[6], (size_t)rows * ne * 4, "MoeFfn dst", &dst)).ok()) return s;
+            MoeArgs a{reinterpret_cast<const float *>(x.ptr), reinterpret_cast<const float *>(rx.ptr), reinterpret_cast<const float *>(r.ptr),
+                      gt.ptr, up.ptr, dn.ptr, DT_Q4K, DT_Q4K, DT_Q4K, reinterpret_cast<float *>(dst.ptr), rows, ne, nx, nu, nff, op.f[0],
+                      (int)op.u[4], nullptr, nullptr, nullptr};
+            s = moe_ffn(a);
             if (!s.ok()) return s;
         } else {
             return Status::Err(INFR_E_UNSUPPORTED, fmt("execute: op %zu tag %u", i, op.tag));

@@ -76,6 +76,20 @@ public:
                        int32_t *sums, int32_t *sums16, uint16_t *dact, uint16_t *sact);
     Status linear(int dtype, const uint8_t *w, const float *x, float *y, uint32_t m, uint32_t in_f,
                   uint32_t out_f, int act);
+    // Op::MoeFfn (crates/infr-cpu/src/lib.rs:2264-2984), qwen3moe configuration.  Optional debug outputs:
+    // sel_ids [rows,n_used] i32, sel_w [rows,n_used] f32, logits [rows,n_expert] f32 (null = not wanted).
+    struct MoeArgs {
+        const float *x, *router_x, *router;
+        const uint8_t *gate, *up, *down;
+        int gate_dt, up_dt, down_dt;
+        float *dst;
+        uint32_t rows, ne, n_expert, n_used, n_ff;
+        float scale;
+        int norm_w;
+        int32_t *sel_ids;
+        float *sel_w, *logits;
+    };
+    Status moe_ffn(const MoeArgs &a);
     Status gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f);
     Status gemv_block_acc(int dtype, const uint8_t *w, const float *x, int32_t *acc, uint32_t in_f,
                           uint32_t out_f);

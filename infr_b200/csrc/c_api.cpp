@@ -248,6 +248,36 @@ int32_t infr_cuda_gemv_block_acc(infr_cuda_ctx *ctx, int32_t dtype, const infr_c
     return finish(ctx, ctx->be->gemv_block_acc(dtype, pw, (const float *)px, (int32_t *)pa, in_f, out_f));
 }
 
+int32_t infr_cuda_moe_ffn(infr_cuda_ctx *ctx, const infr_moe_desc *d, const infr_cuda_buf *x, const infr_cuda_buf *router_x,
+                          const infr_cuda_buf *router, const infr_cuda_buf *gate, const infr_cuda_buf *up, const infr_cuda_buf *down,
+                          infr_cuda_buf *dst, infr_cuda_buf *sel_ids, infr_cuda_buf *sel_w, infr_cuda_buf *logits) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (!d) return finish(ctx, Status::Err(INFR_E_INVALID, "moe_ffn: null descriptor"));
+    if (d->router_dtype != INFR_DT_F32) return finish(ctx, Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: router weights must be F32"));
+    auto bank_bytes = [&](int dt, size_t out_f, size_t in_f) -> size_t {
+        const int be = infr::block_elems(dt), bb = infr::block_bytes(dt);
+        if (!bb || in_f % (size_t)be) return (size_t)-1;
+        return (size_t)d->n_expert * out_f * (in_f / (size_t)be) * (size_t)bb;
+    };
+    const size_t rows = d->rows, ne = d->ne, nff = d->n_ff_exp;
+    uint8_t *px, *prx, *pr, *pg, *pu, *pd, *pdst, *pids = nullptr, *pw = nullptr, *plog = nullptr;
+    Status s;
+    if (!(s = span(x, rows * ne * 4, "moe_ffn x", &px)).ok() || !(s = span(router_x, rows * ne * 4, "moe_ffn router_x", &prx)).ok() ||
+        !(s = span(router, (size_t)d->n_expert * ne * 4, "moe_ffn router", &pr)).ok() ||
+        !(s = span(gate, bank_bytes(d->gate_dtype, nff, ne), "moe_ffn gate_exps", &pg)).ok() ||
+        !(s = span(up, bank_bytes(d->up_dtype, nff, ne), "moe_ffn up_exps", &pu)).ok() ||
+        !(s = span(down, bank_bytes(d->down_dtype, ne, nff), "moe_ffn down_exps", &pd)).ok() ||
+        !(s = span(dst, rows * ne * 4, "moe_ffn dst", &pdst)).ok())
+        return finish(ctx, s);
+    if (sel_ids && !(s = span(sel_ids, rows * d->n_used * 4, "moe_ffn sel_ids", &pids)).ok()) return finish(ctx, s);
+    if (sel_w && !(s = span(sel_w, rows * d->n_used * 4, "moe_ffn sel_w", &pw)).ok()) return finish(ctx, s);
+    if (logits && !(s = span(logits, rows * d->n_expert * 4, "moe_ffn logits", &plog)).ok()) return finish(ctx, s);
+    CudaBackend::MoeArgs a{(const float *)px, (const float *)prx, (const float *)pr, pg, pu, pd, d->gate_dtype, d->up_dtype, d->down_dtype,
+                           (float *)pdst, d->rows, d->ne, d->n_expert, d->n_used, d->n_ff_exp, d->scale, d->norm_w,
+                           (int32_t *)pids, (float *)pw, (float *)plog};
+    return finish(ctx, ctx->be->moe_ffn(a));
+}
+
 int32_t infr_cuda_capture_begin(infr_cuda_ctx *ctx) {
     INFR_CTX_OR_RETURN(ctx);
     return finish(ctx, ctx->be->capture_begin());

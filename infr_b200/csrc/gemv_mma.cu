@@ -91,6 +91,17 @@ struct MmaGeom {
     int act_bytes;  // staged activation bytes
 };
 
+// Grouped (mixture-of-experts) mode: blockIdx.y walks a device-built list of work items, each up to 8
+// activation rows routed to one expert.  The weight bank holds the experts' matrices back to back, so
+// expert e's rows start at e * out_f of the tensor map.  item_* == nullptr means an ordinary GEMV.
+struct MmaGroup {
+    const int *item_expert;  // [n_items] expert of the item
+    const int *item_p0;      // [n_items] first routed pair of the item
+    const int *item_cnt;     // [n_items] pairs in the item (1..8)
+    const int *n_items;      // device scalar
+    const int *pair_row;     // [n_pairs] activation row of each pair, or nullptr: pair p reads row p
+};
+
 // Shared-memory layout of the staged activations, per token n (0..7) and super-block b:
 //   codes  : 256 B at (n*nb + b)*256, element (sub-block s, l = 8t+i) at t*64 + s*8 + i
 //   bsplit : 16 B at (n*nb + b)*16: bytes 0..7 = low 6 bits of bsum_s, bytes 8..15 = bsum_s >> 6
@@ -99,7 +110,7 @@ struct MmaGeom {
 template <int M, bool FUSED, int KW, int SB>
 __global__ void __launch_bounds__(KW * 32, 16 / KW)
     gemv_q4k_mma_kernel(const __grid_constant__ CUtensorMap tmap, Q8Dev a, const float *__restrict__ x, float *__restrict__ y, int m,
-                        int in_f, int out_f, MmaGeom geo, uint32_t *__restrict__ status) {
+                        int in_f, int out_f, MmaGeom geo, MmaGroup grp, uint32_t *__restrict__ status) {
     constexpr int kW = KW, kThreadsMma = KW * 32, kStepBlocks = SB, kSlotBytes = kTileRows * SB * 144;
     extern __shared__ __align__(128) uint8_t smem[];
     const int nb = geo.nb, S = geo.slots;
@@ -120,6 +131,15 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
     }
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    int row_base = 0, p0 = 0;  // grouped mode: first row of the expert in the bank, first pair of the item
+    if (grp.item_expert) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // the work list comes from the previous kernels
+        const int item = blockIdx.y;
+        if (item >= *grp.n_items) return;
+        row_base = grp.item_expert[item] * out_f;
+        p0 = grp.item_p0[item];
+        m = grp.item_cnt[item];
+    }
 
     // balanced contiguous range of 16-row tiles of this CTA (only the matrix's last tile can be partial)
     const int total_tiles = (out_f + kTileRows - 1) / kTileRows;
@@ -147,7 +167,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
             // order this warp's earlier reads of the slot before the engine overwrites it
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             bar_expect_tx(bar, (uint32_t)kSlotBytes);
-            tma_load_2d(s_u32(ring + (size_t)slot * kSlotBytes), &tmap, blk0 * 36, r_begin + i_tile * kTileRows, bar);
+            tma_load_2d(s_u32(ring + (size_t)slot * kSlotBytes), &tmap, blk0 * 36, row_base + r_begin + i_tile * kTileRows, bar);
         }
         __syncwarp();
         j_issue++;
@@ -203,19 +223,21 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
         const int units = in_f / 8;  // 8-byte units
         for (int n = 0; n < M; n++) {
             const bool on = n < m;
+            // activation row of column n: the item's n-th pair (gathered through pair_row when given)
+            const size_t ar = !on ? 0 : (size_t)(grp.pair_row ? grp.pair_row[p0 + n] : p0 + n);
             for (int u = threadIdx.x; u < units; u += kThreadsMma) {
                 uint2 v = make_uint2(0, 0);
-                if (on) v = *reinterpret_cast<const uint2 *>(a.qs + (size_t)n * in_f + (size_t)u * 8);
+                if (on) v = *reinterpret_cast<const uint2 *>(a.qs + ar * in_f + (size_t)u * 8);
                 const int b = u >> 5, uu = u & 31, s = uu >> 2, tt = uu & 3;
                 *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * 256 + tt * 64 + s * 8) = v;
             }
             for (int r = threadIdx.x; r < nb * 8; r += kThreadsMma) {
                 const int b = r >> 3, s = r & 7;
-                const int sum = on ? a.sums[(size_t)n * nb * 8 + r] : 0;
+                const int sum = on ? a.sums[ar * nb * 8 + r] : 0;
                 s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum & 63);
                 s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
             }
-            for (int b = threadIdx.x; b < nb; b += kThreadsMma) s_d8[n * nb + b] = on ? a.d[(size_t)n * nb + b] : 0.f;
+            for (int b = threadIdx.x; b < nb; b += kThreadsMma) s_d8[n * nb + b] = on ? a.d[ar * nb + b] : 0.f;
         }
     }
     __syncthreads();
@@ -332,7 +354,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < kW; w++) v += pp[w * 128];
-                y[(size_t)n * out_f + row] = v;
+                y[(size_t)(p0 + n) * out_f + row] = v;
             }
         }
     }
@@ -355,7 +377,8 @@ EncodeTiledFn encode_tiled() {
 
 template <int M, bool FUSED, int KW, int SB>
 cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
-                           const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+                           const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const MmaGroup &grp = MmaGroup{},
+                           int n_experts = 1, int max_items = 1) {
     constexpr int kSlotBytes = kTileRows * SB * 144;
     MmaGeom geo;
     geo.nb = in_f / 256;
@@ -379,7 +402,7 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
     if (!enc) return cudaErrorNotSupported;
     CUtensorMap tmap;
     {
-        const cuuint64_t gdim[2] = {(cuuint64_t)geo.nb * 36, (cuuint64_t)out_f};
+        const cuuint64_t gdim[2] = {(cuuint64_t)geo.nb * 36, (cuuint64_t)out_f * (cuuint64_t)n_experts};
         const cuuint64_t gstride[1] = {(cuuint64_t)geo.nb * 144};
         const cuuint32_t box[2] = {(cuuint32_t)SB * 36, (cuuint32_t)kTileRows};
         const cuuint32_t estr[2] = {1, 1};
@@ -392,7 +415,12 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
+    if (grp.item_expert) {
+        // many small (expert, 8-row) items: a few CTAs per item, the SMs fill up across items
+        const int tiles = (out_f + kTileRows - 1) / kTileRows;
+        grid = tiles < 4 ? tiles : 4;
+    }
+    cfg.gridDim = dim3((unsigned)grid, (unsigned)max_items);
     cfg.blockDim = dim3(KW * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -401,7 +429,7 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, tmap, a, x, y, m, in_f, out_f, geo, status);
+    return cudaLaunchKernelEx(&cfg, kernel, tmap, a, x, y, m, in_f, out_f, geo, grp, status);
 }
 
 // Few 16-row tiles (small matrices) -> more warps share a tile's K range so that a tile's latency is short;
@@ -448,6 +476,21 @@ cudaError_t launch_mma(const uint8_t *w, const Q8Dev &a, const float *x, float *
 }
 
 }  // namespace
+
+cudaError_t launch_grouped_q4k_mma(const uint8_t *bank, int n_experts, const Q8Dev &a, float *y, int in_f, int out_f,
+                                   const int *item_expert, const int *item_p0, const int *item_cnt, const int *n_items,
+                                   const int *pair_row, int max_items, const DeviceInfo &dev, uint32_t *status,
+                                   cudaStream_t st) {
+    if (in_f % 256 || max_items < 1) return cudaErrorInvalidValue;
+    MmaGroup grp{item_expert, item_p0, item_cnt, n_items, pair_row};
+    const int nb = in_f / 256;
+    if (nb >= 8) {
+        if ((nb + 7) / 8 == 1) return launch_mma_cfg<8, false, 8, 1>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
+        return launch_mma_cfg<8, false, 8, 2>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
+    }
+    if ((nb + 3) / 4 == 1) return launch_mma_cfg<8, false, 4, 1>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
+    return launch_mma_cfg<8, false, 4, 2>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
+}
 
 cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,
                                 const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {

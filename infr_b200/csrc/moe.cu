@@ -1,0 +1,251 @@
+// Mixture-of-experts routing and glue kernels around the grouped expert GEMMs.
+//
+// Follows the staged Op::MoeFfn of crates/infr-cpu/src/lib.rs:2264-2984 for the qwen3moe family
+// (split gate/up banks, softmax gating, top-k by stable descending sort, optional renormalisation,
+// SiLU gate, output-side weighting):
+//   router logits  : F32 router rows against the raw f32 activations with the reference's `dot`
+//                    (8 FMA lanes, lanes summed in order, kernels.rs:6557-6573) -> same bits as the CPU
+//   route          : softmax over all experts with max shift, sequential sums (lib.rs:2427-2436),
+//                    top-k = repeated arg-max with the lower expert id winning ties (:2527-2529),
+//                    w = p / max(sum p_sel, 1e-20) * scale (:2536-2538)
+//   bucket         : pairs (row, rank) grouped by expert, in (row, rank) order inside an expert
+//                    (:2554-2587), plus the 8-row work items of the grouped GEMM
+//   swiglu_quant   : act = silu(g) * u per pair (kernels.rs:6578-6597), re-quantised per 256
+//                    (lib.rs:2862-2873) with the arithmetic of quantize.cu
+//   combine        : out[r] += w * y in rank order, multiply and add rounded separately (:2970-2982)
+#include "kernels.h"
+
+namespace infr {
+
+// logits[r, e] = dot(router[e, :], x[r, :]).  Eight lanes per dot product replay the eight
+// accumulators of the CPU `dot`; four dot products per warp.
+__global__ void __launch_bounds__(256) moe_router_kernel(const float *__restrict__ router, const float *__restrict__ x,
+                                                         float *__restrict__ logits, int rows, int ne, int n_expert) {
+    const int lane = threadIdx.x & 31, sub = lane >> 3, j = lane & 7;
+    const long long dot_id = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 4 + sub;
+    const bool live = dot_id < (long long)rows * n_expert;
+    const int r = live ? (int)(dot_id / n_expert) : 0, e = live ? (int)(dot_id % n_expert) : 0;
+    const float *w = router + (size_t)e * ne, *xr = x + (size_t)r * ne;
+    const int chunks = ne / 8;
+    float acc = 0.f;
+    for (int c = 0; c < chunks; c++) acc = fmaf(w[c * 8 + j], xr[c * 8 + j], acc);
+    // s = ((((acc0 + acc1) + acc2) + ...) + acc7), then the FMA tail
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) s = __fadd_rn(s, __shfl_sync(0xffffffffu, acc, sub * 8 + k));
+    for (int i = chunks * 8; i < ne; i++) s = fmaf(w[i], xr[i], s);
+    if (live && j == 0) logits[(size_t)r * n_expert + e] = s;
+}
+
+// One warp per row.  n_expert <= 1024.
+__global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict__ logits, int rows, int n_expert, int n_used,
+                                                        float scale, int norm_w, int32_t *__restrict__ sel_ids,
+                                                        float *__restrict__ sel_w) {
+    extern __shared__ float s_p[];  // [warps][n_expert]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (r >= rows) return;
+    float *p = s_p + (size_t)warp * n_expert;
+    const float *lg = logits + (size_t)r * n_expert;
+    float mx = -INFINITY;
+    for (int e = lane; e < n_expert; e += 32) mx = fmaxf(mx, lg[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    for (int e = lane; e < n_expert; e += 32) p[e] = expf(lg[e] - mx);
+    __syncwarp();
+    float psum = 0.f;
+    if (lane == 0)
+        for (int e = 0; e < n_expert; e++) psum = __fadd_rn(psum, p[e]);  // the CPU sums in index order
+    psum = __shfl_sync(0xffffffffu, psum, 0);
+    for (int e = lane; e < n_expert; e += 32) p[e] = __fdiv_rn(p[e], psum);
+    __syncwarp();
+    // top-k: k rounds of arg-max; ties go to the lower expert id (what a stable descending sort does)
+    float wsum = 0.f;
+    float myw = 0.f;  // lane k keeps the k-th selected probability (n_used <= 32)
+    int myid = 0;
+    for (int k = 0; k < n_used; k++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < n_expert; e += 32) {
+            const float v = p[e];
+            if (v > best) {
+                best = v;
+                bi = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        wsum = __fadd_rn(wsum, best);
+        if (lane == k) {
+            myw = best;
+            myid = bi;
+        }
+        if (lane == 0) p[bi] = -1.0f;  // probabilities are >= 0: never selected again
+        __syncwarp();
+    }
+    wsum = fmaxf(wsum, 1e-20f);
+    if (lane < n_used) {
+        sel_ids[(size_t)r * n_used + lane] = myid;
+        sel_w[(size_t)r * n_used + lane] = norm_w ? __fmul_rn(__fdiv_rn(myw, wsum), scale) : __fmul_rn(myw, scale);
+    }
+}
+
+// One CTA.  Thread e owns expert e: counts its pairs, the block scans the counts, then the thread
+// lists its pairs in (row, rank) order and cuts them into work items of up to 8 rows.
+//   pair_row[p], pair_of_slot[r * n_used + rank] = p, item_{expert,p0,cnt}[], n_items
+__global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restrict__ sel_ids, int rows, int n_used, int n_expert,
+                                                          int32_t *__restrict__ pair_row, int32_t *__restrict__ pair_of_slot,
+                                                          int32_t *__restrict__ item_expert, int32_t *__restrict__ item_p0,
+                                                          int32_t *__restrict__ item_cnt, int32_t *__restrict__ n_items,
+                                                          int32_t *__restrict__ counts_out) {
+    __shared__ int s_cnt[1024], s_off[1024], s_ioff[1024];
+    const int e = threadIdx.x;
+    const int n_pairs = rows * n_used;
+    int cnt = 0;
+    if (e < n_expert)
+        for (int i = 0; i < n_pairs; i++) cnt += sel_ids[i] == e;
+    s_cnt[e] = e < n_expert ? cnt : 0;
+    __syncthreads();
+    if (e == 0) {
+        int off = 0, ioff = 0;
+        for (int k = 0; k < n_expert; k++) {
+            s_off[k] = off;
+            s_ioff[k] = ioff;
+            off += s_cnt[k];
+            ioff += (s_cnt[k] + 7) / 8;
+        }
+        *n_items = ioff;
+    }
+    __syncthreads();
+    if (e >= n_expert) return;
+    if (counts_out) counts_out[e] = cnt;
+    int p = s_off[e];
+    for (int i = 0; i < n_pairs; i++)
+        if (sel_ids[i] == e) {
+            pair_row[p] = i / n_used;
+            pair_of_slot[i] = p;
+            p++;
+        }
+    int it = s_ioff[e];
+    for (int c = 0; c < cnt; c += 8, it++) {
+        item_expert[it] = e;
+        item_p0[it] = s_off[e] + c;
+        item_cnt[it] = cnt - c < 8 ? cnt - c : 8;
+    }
+}
+
+// One warp per (pair, 256-block): act = silu(gate) * up, then quantize_q8 of that block.
+__global__ void __launch_bounds__(256) moe_swiglu_quant_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                                                               int n_pairs, int nff, int8_t *__restrict__ qs, float *__restrict__ d,
+                                                               int32_t *__restrict__ sums, float *__restrict__ act_out) {
+    const int lane = threadIdx.x & 31;
+    const int nbk = nff / 256;
+    const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wg >= (long long)n_pairs * nbk) return;
+    const int p = (int)(wg / nbk), b = (int)(wg % nbk);
+    const size_t base = (size_t)p * nff + (size_t)b * 256 + lane * 8;
+    float v[8];
+    float am = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const float4 g4 = *reinterpret_cast<const float4 *>(gate + base + h * 4);
+        const float4 u4 = *reinterpret_cast<const float4 *>(up + base + h * 4);
+        const float gg[4] = {g4.x, g4.y, g4.z, g4.w}, uu[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float sg = __fdiv_rn(gg[i], __fadd_rn(1.0f, expf(-gg[i])));
+            v[h * 4 + i] = __fmul_rn(sg, uu[i]);
+            am = fmaxf(am, fabsf(v[h * 4 + i]));
+        }
+    }
+    if (act_out) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) act_out[base + i] = v[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    const float dd = am / 127.0f;
+    const float id = dd > 0.0f ? 1.0f / dd : 0.0f;
+    int q[8], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float r = roundf(v[i] * id);
+        r = fminf(fmaxf(r, -127.0f), 127.0f);
+        q[i] = (int)r;
+        sum += q[i];
+    }
+    uint2 pk;
+    pk.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+    pk.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+    *reinterpret_cast<uint2 *>(qs + base) = pk;
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if ((lane & 3) == 0) sums[((size_t)p * nbk + b) * 8 + (lane >> 2)] = sum;
+    if (lane == 0) d[(size_t)p * nbk + b] = dd;
+}
+
+// out[r, i] = sum over ranks (in rank order) of w[r, rank] * y[pair_of_slot[r, rank], i].
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restrict__ y_pairs, const int32_t *__restrict__ pair_of_slot,
+                                                          const float *__restrict__ sel_w, int rows, int n_used, int ne,
+                                                          float *__restrict__ out) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)rows * ne) return;
+    const int r = (int)(idx / ne), i = (int)(idx % ne);
+    float o = 0.f;
+    for (int k = 0; k < n_used; k++) {
+        const int p = pair_of_slot[(size_t)r * n_used + k];
+        o = __fadd_rn(o, __fmul_rn(sel_w[(size_t)r * n_used + k], y_pairs[(size_t)p * ne + i]));
+    }
+    out[idx] = o;
+}
+
+cudaError_t launch_moe_router(const float *router, const float *x, float *logits, int rows, int ne, int n_expert,
+                              cudaStream_t st) {
+    const long long dots = (long long)rows * n_expert;
+    const long long warps = (dots + 3) / 4;
+    const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+    moe_router_kernel<<<blocks, 256, 0, st>>>(router, x, logits, rows, ne, n_expert);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_route(const float *logits, int rows, int n_expert, int n_used, float scale, int norm_w,
+                             int32_t *sel_ids, float *sel_w, cudaStream_t st) {
+    if (n_expert > 1024 || n_used > 32 || n_used > n_expert) return cudaErrorInvalidValue;
+    const int warps = 4;
+    moe_route_kernel<<<(rows + warps - 1) / warps, warps * 32, (size_t)warps * n_expert * 4, st>>>(logits, rows, n_expert, n_used,
+                                                                                              scale, norm_w, sel_ids, sel_w);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int n_expert, int32_t *pair_row,
+                              int32_t *pair_of_slot, int32_t *item_expert, int32_t *item_p0, int32_t *item_cnt,
+                              int32_t *n_items, int32_t *counts_out, cudaStream_t st) {
+    if (n_expert > 1024) return cudaErrorInvalidValue;
+    moe_bucket_kernel<<<1, 1024, 0, st>>>(sel_ids, rows, n_used, n_expert, pair_row, pair_of_slot, item_expert, item_p0, item_cnt,
+                                          n_items, counts_out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_swiglu_quant(const float *gate, const float *up, int n_pairs, int nff, int8_t *qs, float *d,
+                                    int32_t *sums, float *act_out, cudaStream_t st) {
+    if (nff % 256) return cudaErrorInvalidValue;
+    const long long warps = (long long)n_pairs * (nff / 256);
+    moe_swiglu_quant_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(gate, up, n_pairs, nff, qs, d, sums, act_out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_combine(const float *y_pairs, const int32_t *pair_of_slot, const float *sel_w, int rows, int n_used,
+                               int ne, float *out, cudaStream_t st) {
+    const long long n = (long long)rows * ne;
+    moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(y_pairs, pair_of_slot, sel_w, rows, n_used, ne, out);
+    return cudaGetLastError();
+}
+
+}  // namespace infr

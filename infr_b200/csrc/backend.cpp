@@ -241,6 +241,15 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
     if (in_f % 16) return Status::Err(INFR_E_INVALID, fmt("linear: in_f=%u must be a multiple of 16", in_f));
     if (m == 0 || out_f == 0) return Status::Ok();
     cudaSetDevice(device_);
+    // Prefill shapes: Q4_K with int8 activations goes to the tcgen05 MMQ GEMM (all rows quantised once).
+    if (m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0) {
+        Q8Dev a;
+        Status s = quantize_for(dtype, x, m, in_f, &a);
+        if (!s.ok()) return s;
+        s = cuda_status(launch_mmq_q4k(w, a, y, (int)m, (int)in_f, (int)out_f, status_dev_, stream_), "mmq_q4k");
+        if (s.ok()) launches_++;
+        return s;
+    }
     // Decode shapes (m <= 8) run the streaming GEMV; wider batches are walked 8 rows at a time.
     for (uint32_t r0 = 0; r0 < m; r0 += 8) {
         const uint32_t mm = m - r0 < 8 ? m - r0 : 8;

@@ -200,6 +200,30 @@ def _gemv_case(be, infr_b200, dtype, out_f, in_f, m, seed, steps, warmup, l2_byt
     return res
 
 
+def _mmq_case(be, infr_b200, m, in_f, out_f, seed, steps, warmup):
+    """Prefill MMQ (Linear with m > 8): int8 TOPS = 2*m*in_f*out_f / time; the activation quantiser is inside."""
+    from infr_b200 import synth
+
+    w = synth.weight(infr_b200.Q4K, out_f, in_f, seed)
+    wb = be.from_numpy(w, infr_b200.USAGE_WEIGHTS)
+    xb = be.from_numpy(synth.normal(seed + 1, (m, in_f)))
+    yb = be.alloc(m * out_f * 4)
+    for _ in range(warmup):
+        be.linear(infr_b200.Q4K, wb, xb, yb, m, in_f, out_f)
+    be.sync()
+    be.timer_start()
+    for _ in range(steps):
+        be.linear(infr_b200.Q4K, wb, xb, yb, m, in_f, out_f)
+    ms = be.timer_stop()
+    ops = 2.0 * m * in_f * out_f
+    res = {"workload": f"prefill MMQ q4_k M={m} K={in_f} N={out_f} (quantise + tcgen05 kind::i8 GEMM)",
+           "int8_ops": ops, "us": ms * 1e3 / steps, "tops": ops * steps / (ms * 1e-3) / 1e12,
+           "frac_of_4500_tops_spec": ops * steps / (ms * 1e-3) / 1e12 / 4500.0}
+    for b in (wb, xb, yb):
+        b.close()
+    return res
+
+
 # ------------------------------------------------------------------------------------------------
 def run_b200(args):
     import infr_b200
@@ -307,6 +331,7 @@ def run_b200(args):
             for m in ms_:
                 sweep.append(_gemv_case(be, infr_b200, dtype, o, i_, m, seed, sw_steps, 5, caps.l2_bytes, hbm_peak))
         out["sweep"] = sweep
+        out["mmq"] = _mmq_case(be, infr_b200, 512, 4096, 14336, 5, 20, 3)
 
     if rank == 0 and world == 1 and not args.no_cpu:
         out["cpu_baseline"] = _cpu_baseline(w, x, budget_s=10.0)

@@ -212,15 +212,16 @@ Status CudaBackend::quantize_q8(int gran, const float *x, uint32_t rows, uint32_
 }
 
 // Lays the quantised rows out in the context scratch: qs | d | sums | sums16.
-Status CudaBackend::quantize_for(int dtype, const float *x, uint32_t rows, uint32_t k, Q8Dev *out) {
+Status CudaBackend::quantize_for(int dtype, const float *x, uint32_t rows, uint32_t k, Q8Dev *out, size_t extra, uint8_t **extra_ptr) {
     const int gran = act_gran(dtype);
     const size_t qs_b = align_up((size_t)rows * k, 256);
     const size_t d_b = align_up((size_t)rows * (k / gran) * 4, 256);
     const size_t s_b = align_up((size_t)rows * (k / 32) * 4, 256);
     const size_t s16_b = dtype == DT_Q6K ? align_up((size_t)rows * (k / 16) * 4, 256) : 0;
-    Status s = ensure_scratch(qs_b + d_b + s_b + s16_b);
+    Status s = ensure_scratch(qs_b + d_b + s_b + s16_b + align_up(extra, 256));
     if (!s.ok()) return s;
     uint8_t *p = scratch();
+    if (extra_ptr) *extra_ptr = p + qs_b + d_b + s_b + s16_b;
     int8_t *qs = reinterpret_cast<int8_t *>(p);
     float *d = reinterpret_cast<float *>(p + qs_b);
     int32_t *sums = reinterpret_cast<int32_t *>(p + qs_b + d_b);
@@ -244,10 +245,11 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
     // Prefill shapes: Q4_K with int8 activations goes to the tcgen05 MMQ GEMM (all rows quantised once).
     if (m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0) {
         Q8Dev a;
-        Status s = quantize_for(dtype, x, m, in_f, &a);
+        uint8_t *rec = nullptr;
+        Status s = quantize_for(dtype, x, m, in_f, &a, mmq_q4k_record_bytes((int)m, (int)in_f), &rec);
         if (!s.ok()) return s;
-        s = cuda_status(launch_mmq_q4k(w, a, y, (int)m, (int)in_f, (int)out_f, status_dev_, stream_), "mmq_q4k");
-        if (s.ok()) launches_++;
+        s = cuda_status(launch_mmq_q4k(w, a, rec, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_), "mmq_q4k");
+        if (s.ok()) launches_ += 2;
         return s;
     }
     // Decode shapes (m <= 8) run the streaming GEMV; wider batches are walked 8 rows at a time.

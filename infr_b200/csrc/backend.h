@@ -118,7 +118,9 @@ public:
 
 private:
     CudaBackend() = default;
-    Status quantize_for(int dtype, const float *x, uint32_t rows, uint32_t k, Q8Dev *out);
+    // Quantises `rows` activation rows into the context scratch; `extra` more bytes are reserved behind them.
+    Status quantize_for(int dtype, const float *x, uint32_t rows, uint32_t k, Q8Dev *out, size_t extra = 0,
+                        uint8_t **extra_ptr = nullptr);
 
     int device_ = 0;
     bool reference_ = false;

@@ -58,8 +58,11 @@ cudaError_t launch_gemv_f32(int dt, const uint8_t *w, const float *x, float *y, 
 
 // Prefill GEMM C[m,out_f] = Q8(256) activations x Q4_K weights on tcgen05 (kind::i8, TMEM accumulators);
 // bit-identical to the CPU production path.
-cudaError_t launch_mmq_q4k(const uint8_t *w, const Q8Dev &a, float *c, int m, int in_f, int out_f, uint32_t *status,
-                           cudaStream_t st);
+// `records` is scratch of mmq_q4k_record_bytes(m, in_f) bytes (per-token block sums and scales in the layout
+// the kernel's TMA loads expect).
+size_t mmq_q4k_record_bytes(int m, int in_f);
+cudaError_t launch_mmq_q4k(const uint8_t *w, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
+                           const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
 // Grouped Q4_K GEMM over a bank of n_experts matrices [out_f, in_f] stored back to back: work item i
 // multiplies up to 8 quantised activation rows (pairs item_p0[i]..+item_cnt[i], gathered through
 // pair_row when non-null) with expert item_expert[i]; y is [n_pairs, out_f].

@@ -19,6 +19,8 @@
 //
 // Every mbarrier wait is bounded; on expiry the CTA records a status word and leaves (after freeing
 // its tensor memory).
+#include <cuda.h>
+
 #include "gemv_common.cuh"
 
 namespace infr {
@@ -47,195 +49,317 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
         : "r"(taddr));
 }
 
-__global__ void __launch_bounds__(kTM) mmq_q4k_kernel(const uint8_t *__restrict__ W, Q8Dev a, float *__restrict__ C, int m, int in_f,
-                                                      int out_f, uint32_t *__restrict__ status) {
+// Per (token, super-block) record the kernel fetches by TMA next to the int8 codes: 32 bytes =
+// [l_0..l_7][h_0..h_7] (bsum_s = 64 * h_s + l_s) then the f32 scale d8 and 12 bytes of padding.
+__global__ void mmq_prep_kernel(const int32_t *__restrict__ sums, const float *__restrict__ d, int n_rec,
+                                uint32_t *__restrict__ rec) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rec) return;
+    uint32_t l[2] = {0, 0}, h[2] = {0, 0};
+#pragma unroll
+    for (int s = 0; s < 8; s++) {
+        const int bs = sums[(size_t)i * 8 + s];
+        l[s >> 2] |= (uint32_t)(bs & 63) << (8 * (s & 3));
+        h[s >> 2] |= (uint32_t)((bs >> 6) & 0xFF) << (8 * (s & 3));
+    }
+    uint4 *o = reinterpret_cast<uint4 *>(rec + (size_t)i * 8);
+    o[0] = make_uint4(l[0], l[1], h[0], h[1]);
+    o[1] = make_uint4(__float_as_uint(d[i]), 0, 0, 0);
+}
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    uint32_t ok = 0;
+    for (uint32_t i = 0; i < kMmqSpin && !ok; i++)
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_3d(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+                 : "memory");
+}
+
+// Shared-memory plan (bytes): two load stages {raw weights 128 x 144, code planes [16][64][16], record
+// planes [2][64][16]}, two operand buffers {A_lo [16][128][16], A_hi [16][128][16], A_ml [128][16],
+// A_mh [128][16]}, one zero plane [128][16], three d8 rows [64] f32.
+constexpr int kRawBytes = kTM * 144, kCodeBytes = 16 * kTN * 16, kRecBytes = 2 * kTN * 16;
+constexpr int kStageBytes = kRawBytes + kCodeBytes + kRecBytes;
+constexpr int kABufBytes = 2 * 16 * kTM * 16 + 2 * kTM * 16;
+constexpr int kSmemMmq = 2 * kStageBytes + 2 * kABufBytes + kTM * 16 + 3 * kTN * 4 + 256;
+
+// Warps 0..3 (thread r = weight row r = tensor-memory lane r) unpack, issue the MMAs and run the
+// epilogue; warp 4 is the TMA producer.  Persistent CTA: it walks tiles blockIdx.x, +gridDim.x, ...
+__global__ void __launch_bounds__(kTM + 32, 1)
+    mmq_q4k_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q,
+                   const __grid_constant__ CUtensorMap map_r, float *__restrict__ C, int m, int in_f, int out_f,
+                   uint32_t *__restrict__ status) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t *sA_lo = smem;                        // [16][128][16]
-    uint8_t *sA_hi = sA_lo + 16 * kTM * 16;       // [16][128][16]
-    uint8_t *sA_m = sA_hi + 16 * kTM * 16;        // [2][128][16]
-    uint8_t *sB = sA_m + 2 * kTM * 16;            // [16][64][16]
-    uint8_t *sB_ml = sB + 16 * kTN * 16;          // [2][64][16]
-    uint8_t *sB_mh = sB_ml + 2 * kTN * 16;        // [2][64][16]
-    float *s_d8 = reinterpret_cast<float *>(sB_mh + 2 * kTN * 16);  // [64]
-    __shared__ uint64_t bar;
+    uint8_t *stage0 = smem;
+    uint8_t *abuf0 = smem + 2 * kStageBytes;
+    uint8_t *zero_plane = abuf0 + 2 * kABufBytes;
+    float *d8buf = reinterpret_cast<float *>(zero_plane + kTM * 16);  // [3][64]
+    __shared__ uint64_t bars[4];  // full[2], mma_done[2]
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_dead;
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int nb = in_f >> 8;
-    const size_t row_bytes = (size_t)nb * 144;
-    const int row0 = blockIdx.x * kTM, tok0 = blockIdx.y * kTN;
-    const int row = row0 + tid;
-    const bool row_ok = row < out_f;
+    const int row_tiles = (out_f + kTM - 1) / kTM, tok_tiles = (m + kTN - 1) / kTN;
+    const int n_tiles = row_tiles * tok_tiles;
+    int my_tiles = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) my_tiles++;
+    (void)my_tiles;
+
     if (tid == 0) {
         s_dead = 0;
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sm_u32(&bar)));
+        for (int i = 0; i < 4; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sm_u32(&bars[i])));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_u32(&tmem_base_s)), "r"(256));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_u32(&tmem_base_s)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
-    // planes that never change: second half of the min-term operands is zero
-    for (int i = tid; i < kTM; i += kTM) *reinterpret_cast<uint4 *>(sA_m + (size_t)(kTM + i) * 16) = make_uint4(0, 0, 0, 0);
-    for (int i = tid; i < kTN; i += kTM) {
-        *reinterpret_cast<uint4 *>(sB_ml + (size_t)(kTN + i) * 16) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4 *>(sB_mh + (size_t)(kTN + i) * 16) = make_uint4(0, 0, 0, 0);
-    }
+    if (tid < kTM) *reinterpret_cast<uint4 *>(zero_plane + (size_t)tid * 16) = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base_s;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer
+        if ((tid & 31) == 0) {
+            int j = 0;
+            for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+                const int rt = t % row_tiles, tt = t / row_tiles;  // consecutive CTAs share a token tile
+                for (int b = 0; b < nb; b++, j++) {
+                    const int s = j & 1;
+                    if (j >= 2 && !mbar_wait_bounded(sm_u32(&bars[2 + s]), (uint32_t)(((j >> 1) - 1) & 1))) {
+                        atomicExch(status, 5u);
+                        *(volatile int *)&s_dead = 1;
+                        return;
+                    }
+                    if (*(volatile int *)&s_dead) return;
+                    uint8_t *st = stage0 + (size_t)s * kStageBytes;
+                    const uint32_t bar = sm_u32(&bars[s]);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kStageBytes) : "memory");
+                    tma_2d(sm_u32(st), &map_w, b * 36, rt * kTM, bar);
+                    tma_3d(sm_u32(st + kRawBytes), &map_q, 0, tt * kTN, b * 16, bar);
+                    tma_3d(sm_u32(st + kRawBytes + kCodeBytes), &map_r, 0, tt * kTN, b * 2, bar);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- math warps
     const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(kTN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
-
+    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
     float acc[kTN];
-#pragma unroll
-    for (int j = 0; j < kTN; j++) acc[j] = 0.f;
-    uint32_t phase = 0;
+    float dw_prev = 0.f, dmin_prev = 0.f;
+    bool dead = false;
 
-    for (int b = 0; b < nb; b++) {
-        // ---- unpack this thread's weight row: A_lo = q * (sc & 7), A_hi = q * (sc >> 3), A_m = m ----
-        float dw = 0.f, dminw = 0.f;
-        {
-            uint4 hdr = make_uint4(0, 0, 0, 0);
-            const uint8_t *blk = W + (size_t)(row_ok ? row : 0) * row_bytes + (size_t)b * 144;
-            if (row_ok) hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
-            dw = h2f(hdr.x);
-            dminw = h2f(hdr.x >> 16);
-            uint32_t sc[2], mn[2];
-            sc[0] = hdr.y & 0x3F3F3F3Fu;
-            mn[0] = hdr.z & 0x3F3F3F3Fu;
-            sc[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
-            mn[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-            *reinterpret_cast<uint4 *>(sA_m + (size_t)tid * 16) = make_uint4(mn[0], mn[1], 0, 0);
-#pragma unroll
-            for (int p = 0; p < 4; p++) {
-                uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0;
-                if (row_ok) {
-                    q0 = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + p * 32));
-                    q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32 + p * 32));
-                }
-                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-                for (int hl = 0; hl < 2; hl++) {  // hl = 0: low nibbles = sub-block 2p; 1: high nibbles = 2p+1
-                    const int s = 2 * p + hl;
-                    const uint32_t scs = (sc[s >> 2] >> (8 * (s & 3))) & 0xFFu;
-                    const uint32_t f_lo = scs & 7u, f_hi = scs >> 3;
-                    uint32_t lo[8], hi[8];
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const uint32_t nib = (hl ? (w[i] >> 4) : w[i]) & 0x0F0F0F0Fu;
-                        lo[i] = nib * f_lo;  // bytes <= 15 * 7: no carry between bytes
-                        hi[i] = nib * f_hi;
-                    }
-                    // elements 0..15 of sub-block s -> plane 2s, 16..31 -> plane 2s + 1
-                    *reinterpret_cast<uint4 *>(sA_lo + ((size_t)(2 * s) * kTM + tid) * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                    *reinterpret_cast<uint4 *>(sA_lo + ((size_t)(2 * s + 1) * kTM + tid) * 16) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-                    *reinterpret_cast<uint4 *>(sA_hi + ((size_t)(2 * s) * kTM + tid) * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *reinterpret_cast<uint4 *>(sA_hi + ((size_t)(2 * s + 1) * kTM + tid) * 16) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-                }
-            }
+    // epilogue of job j: fold the block's tensor-memory sums into the running f32 sums
+    auto epilogue = [&](int j, float dw, float dminw) {
+        const int s = j & 1;
+        if (!mbar_wait_bounded(sm_u32(&bars[2 + s]), (uint32_t)((j >> 1) & 1))) {
+            *(volatile int *)&s_dead = 1;
+            return;
         }
-        // ---- activations of this block: codes as planes, bsum split, d8 ----
-        {
-            const int tk = tid & (kTN - 1), half = tid >> 6;  // 2 threads per token, 8 planes each
-            const int tok = tok0 + tk;
-            const bool tok_ok = tok < m;
-#pragma unroll
-            for (int k = 0; k < 8; k++) {
-                const int k16 = half * 8 + k;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (tok_ok) v = *reinterpret_cast<const uint4 *>(a.qs + (size_t)tok * in_f + (size_t)b * 256 + k16 * 16);
-                *reinterpret_cast<uint4 *>(sB + ((size_t)k16 * kTN + tk) * 16) = v;
-            }
-            if (half == 0) {
-                uint32_t l[2] = {0, 0}, h[2] = {0, 0};
-                if (tok_ok) {
-#pragma unroll
-                    for (int s = 0; s < 8; s++) {
-                        const int bs = a.sums[((size_t)tok * nb + b) * 8 + s];
-                        l[s >> 2] |= (uint32_t)(bs & 63) << (8 * (s & 3));
-                        h[s >> 2] |= (uint32_t)((bs >> 6) & 0xFF) << (8 * (s & 3));
-                    }
-                }
-                *reinterpret_cast<uint4 *>(sB_ml + (size_t)tk * 16) = make_uint4(l[0], l[1], 0, 0);
-                *reinterpret_cast<uint4 *>(sB_mh + (size_t)tk * 16) = make_uint4(h[0], h[1], 0, 0);
-                s_d8[tk] = tok_ok ? a.d[(size_t)tok * nb + b] : 0.f;
-            }
-        }
-        // generic-proxy writes -> visible to the tensor core (async proxy); also orders the previous
-        // block's tensor-memory reads before this block's MMAs overwrite the accumulators
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (tid == 0) {
-#pragma unroll
-            for (int s = 0; s < 8; s++) {
-                const uint64_t db = umma_desc(sm_u32(sB + (size_t)(2 * s) * kTN * 16), kTN * 16, 128);
-                umma_i8(tmem + 0, umma_desc(sm_u32(sA_lo + (size_t)(2 * s) * kTM * 16), kTM * 16, 128), db, idesc, s > 0);
-                umma_i8(tmem + kTN, umma_desc(sm_u32(sA_hi + (size_t)(2 * s) * kTM * 16), kTM * 16, 128), db, idesc, s > 0);
-            }
-            const uint64_t dam = umma_desc(sm_u32(sA_m), kTM * 16, 128);
-            umma_i8(tmem + 2 * kTN, dam, umma_desc(sm_u32(sB_ml), kTN * 16, 128), idesc, 0);
-            umma_i8(tmem + 3 * kTN, dam, umma_desc(sm_u32(sB_mh), kTN * 16, 128), idesc, 0);
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sm_u32(&bar)) : "memory");
-        }
-        // ---- wait for the MMAs, then fold the block into the running sums ----
-        {
-            uint32_t ok = 0;
-            for (uint32_t i = 0; i < kMmqSpin && !ok; i++)
-                asm volatile(
-                    "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                    : "=r"(ok)
-                    : "r"(sm_u32(&bar)), "r"(phase)
-                    : "memory");
-            if (!ok) s_dead = 1;
-        }
-        phase ^= 1u;
-        __syncthreads();
-        if (s_dead) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+        const float *d8 = d8buf + (j % 3) * kTN;
+        const uint32_t tb = lane_addr + (uint32_t)s * 256;
 #pragma unroll
         for (int c0 = 0; c0 < kTN; c0 += 16) {
             int vlo[16], vhi[16], vml[16], vmh[16];
-            tmem_ld16(lane_addr + c0, vlo);
-            tmem_ld16(lane_addr + kTN + c0, vhi);
-            tmem_ld16(lane_addr + 2 * kTN + c0, vml);
-            tmem_ld16(lane_addr + 3 * kTN + c0, vmh);
+            tmem_ld16(tb + c0, vlo);
+            tmem_ld16(tb + kTN + c0, vhi);
+            tmem_ld16(tb + 2 * kTN + c0, vml);
+            tmem_ld16(tb + 3 * kTN + c0, vmh);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const int sd = vlo[j] + 8 * vhi[j];
-                const int sm = vml[j] + 64 * vmh[j];
+            for (int i = 0; i < 16; i++) {
+                const int sd = vlo[i] + 8 * vhi[i];
+                const int sm = vml[i] + 64 * vmh[i];
                 const float t = __fsub_rn(__fmul_rn(dw, (float)sd), __fmul_rn(dminw, (float)sm));
-                acc[c0 + j] = __fadd_rn(acc[c0 + j], __fmul_rn(s_d8[c0 + j], t));
+                acc[c0 + i] = __fadd_rn(acc[c0 + i], __fmul_rn(d8[c0 + i], t));
             }
         }
-    }
-    if (s_dead) {
-        if (tid == 0) atomicExch(status, 4u);
-    } else if (row_ok) {
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    };
+    auto store_tile = [&](int t) {
+        const int rt = t % row_tiles, tt = t / row_tiles;
+        const int row = rt * kTM + tid;
+        if (row < out_f) {
 #pragma unroll
-        for (int j = 0; j < kTN; j++)
-            if (tok0 + j < m) C[(size_t)(tok0 + j) * out_f + row] = acc[j];
+            for (int i = 0; i < kTN; i++)
+                if (tt * kTN + i < m) C[(size_t)(tt * kTN + i) * out_f + row] = acc[i];
+        }
+    };
+
+    int j = 0, prev_tile = -1;
+    for (int t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x) {
+        for (int b = 0; b < nb && !dead; b++, j++) {
+            const int s = j & 1;
+            uint8_t *st = stage0 + (size_t)s * kStageBytes;
+            uint8_t *ab = abuf0 + (size_t)s * kABufBytes;
+            uint8_t *sA_lo = ab, *sA_hi = ab + 16 * kTM * 16, *sA_ml = ab + 2 * 16 * kTM * 16, *sA_mh = sA_ml + kTM * 16;
+            // A thread whose bounded wait expires raises the CTA-wide flag but still walks to the next
+            // barrier, where every thread sees the flag and leaves together.
+            if (!mbar_wait_bounded(sm_u32(&bars[s]), (uint32_t)((j >> 1) & 1))) *(volatile int *)&s_dead = 1;
+            // ---- unpack weight row `tid` of this block from the raw tile ----
+            const uint8_t *blk = st + (size_t)tid * 144;
+            const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+            const float dw = h2f(hdr.x), dminw = h2f(hdr.x >> 16);
+            {
+                uint32_t sc[2], mn[2];
+                sc[0] = hdr.y & 0x3F3F3F3Fu;
+                mn[0] = hdr.z & 0x3F3F3F3Fu;
+                sc[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+                mn[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+                *reinterpret_cast<uint4 *>(sA_ml + (size_t)tid * 16) = make_uint4(mn[0], mn[1], 0, 0);
+                *reinterpret_cast<uint4 *>(sA_mh + (size_t)tid * 16) = make_uint4(0, 0, mn[0], mn[1]);
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 16 + p * 32);
+                    const uint4 q1 = *reinterpret_cast<const uint4 *>(blk + 32 + p * 32);
+                    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+                    for (int hl = 0; hl < 2; hl++) {
+                        const int sb = 2 * p + hl;
+                        const uint32_t scs = (sc[sb >> 2] >> (8 * (sb & 3))) & 0xFFu;
+                        const uint32_t f_lo = scs & 7u, f_hi = scs >> 3;
+                        uint32_t lo[8], hi[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const uint32_t nib = (hl ? (w[i] >> 4) : w[i]) & 0x0F0F0F0Fu;
+                            lo[i] = nib * f_lo;
+                            hi[i] = nib * f_hi;
+                        }
+                        *reinterpret_cast<uint4 *>(sA_lo + ((size_t)(2 * sb) * kTM + tid) * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        *reinterpret_cast<uint4 *>(sA_lo + ((size_t)(2 * sb + 1) * kTM + tid) * 16) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                        *reinterpret_cast<uint4 *>(sA_hi + ((size_t)(2 * sb) * kTM + tid) * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                        *reinterpret_cast<uint4 *>(sA_hi + ((size_t)(2 * sb + 1) * kTM + tid) * 16) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                    }
+                }
+            }
+            // d8 of this block's tokens: first word of record plane 1
+            if (tid < kTN) d8buf[(j % 3) * kTN + tid] = *reinterpret_cast<const float *>(st + kRawBytes + kCodeBytes + kTN * 16 + (size_t)tid * 16);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"r"(kTM) : "memory");
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (*(volatile int *)&s_dead) {
+                dead = true;
+                break;
+            }
+            if (tid == 0) {
+                const uint32_t td = tmem + (uint32_t)s * 256;
+                const uint8_t *sB = st + kRawBytes, *sR = sB + kCodeBytes;
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const uint64_t db = umma_desc(sm_u32(sB + (size_t)(2 * k) * kTN * 16), kTN * 16, 128);
+                    umma_i8(td, umma_desc(sm_u32(sA_lo + (size_t)(2 * k) * kTM * 16), kTM * 16, 128), db, idesc, k > 0);
+                    umma_i8(td + kTN, umma_desc(sm_u32(sA_hi + (size_t)(2 * k) * kTM * 16), kTM * 16, 128), db, idesc, k > 0);
+                }
+                // min term: the A operand's second K half is the zero plane, so record plane 1 (d8) is inert
+                const uint64_t dbr = umma_desc(sm_u32(sR), kTN * 16, 128);
+                umma_i8(td + 2 * kTN, umma_desc(sm_u32(sA_ml), (uint32_t)(zero_plane - sA_ml), 128), dbr, idesc, 0);
+                umma_i8(td + 3 * kTN, umma_desc(sm_u32(sA_mh), (uint32_t)(zero_plane - sA_mh), 128), dbr, idesc, 0);
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sm_u32(&bars[2 + s])) : "memory");
+            }
+            // ---- epilogue of the previous block overlaps this block's MMAs ----
+            if (j > 0) {
+                epilogue(j - 1, dw_prev, dmin_prev);
+                // a finished tile is stored only if nothing expired (the flag is re-checked CTA-wide at the
+                // next barrier; a partial store of a failed launch is harmless, the launch reports an error)
+                if (b == 0 && !*(volatile int *)&s_dead) store_tile(prev_tile);
+            }
+            if (b == 0) {
+#pragma unroll
+                for (int i = 0; i < kTN; i++) acc[i] = 0.f;
+            }
+            dw_prev = dw;
+            dmin_prev = dminw;
+        }
+        prev_tile = t;
     }
+    if (!dead && j > 0) epilogue(j - 1, dw_prev, dmin_prev);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256));
+    asm volatile("bar.sync 1, %0;" ::"r"(kTM) : "memory");
+    if (*(volatile int *)&s_dead) {
+        if (tid == 0) atomicExch(status, 4u);
+    } else if (j > 0) {
+        store_tile(prev_tile);
+    }
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+}
+
+typedef CUresult (*EncodeTiledFn2)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn2 encode_tiled2() {
+    static EncodeTiledFn2 fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiledFn2>(p);
+    }();
+    return fn;
 }
 
 }  // namespace
 
-cudaError_t launch_mmq_q4k(const uint8_t *w, const Q8Dev &a, float *c, int m, int in_f, int out_f, uint32_t *status,
-                           cudaStream_t st) {
+size_t mmq_q4k_record_bytes(int m, int in_f) { return (size_t)m * (in_f / 256) * 32; }
+
+cudaError_t launch_mmq_q4k(const uint8_t *w, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
+                           const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
     if (m < 1 || in_f % 256 || out_f < 1) return cudaErrorInvalidValue;
-    const size_t smem = (size_t)16 * kTM * 16 * 2 + 2 * kTM * 16 + 16 * kTN * 16 + 2 * 2 * kTN * 16 + kTN * 4 + 1024;
-    cudaError_t e = cudaFuncSetAttribute(mmq_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    EncodeTiledFn2 enc = encode_tiled2();
+    if (!enc) return cudaErrorNotSupported;
+    const int nb = in_f / 256;
+    const int n_rec = m * nb;
+    mmq_prep_kernel<<<(n_rec + 255) / 256, 256, 0, st>>>(a.sums, a.d, n_rec, static_cast<uint32_t *>(records));
+    CUtensorMap map_w, map_q, map_r;
+    const cuuint32_t one3[3] = {1, 1, 1};
+    {
+        const cuuint64_t gdim[2] = {(cuuint64_t)nb * 36, (cuuint64_t)out_f};
+        const cuuint64_t gstr[1] = {(cuuint64_t)nb * 144};
+        const cuuint32_t box[2] = {36, (cuuint32_t)kTM};
+        if (enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(w), gdim, gstr, box, one3, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    {
+        // codes [m][in_f] viewed as (16 bytes, token, 16-byte column): the box lands as planes [k/16][token][16]
+        const cuuint64_t gdim[3] = {16, (cuuint64_t)m, (cuuint64_t)in_f / 16};
+        const cuuint64_t gstr[2] = {(cuuint64_t)in_f, 16};
+        const cuuint32_t box[3] = {16, (cuuint32_t)kTN, 16};
+        if (enc(&map_q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t *>(a.qs), gdim, gstr, box, one3, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    {
+        const cuuint64_t gdim[3] = {16, (cuuint64_t)m, (cuuint64_t)nb * 2};
+        const cuuint64_t gstr[2] = {(cuuint64_t)nb * 32, 16};
+        const cuuint32_t box[3] = {16, (cuuint32_t)kTN, 2};
+        if (enc(&map_r, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, records, gdim, gstr, box, one3, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    cudaError_t e = cudaFuncSetAttribute(mmq_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMmq);
     if (e != cudaSuccess) return e;
-    dim3 grid((unsigned)((out_f + kTM - 1) / kTM), (unsigned)((m + kTN - 1) / kTN));
-    mmq_q4k_kernel<<<grid, kTM, smem, st>>>(w, a, c, m, in_f, out_f, status);
+    const int n_tiles = ((out_f + kTM - 1) / kTM) * ((m + kTN - 1) / kTN);
+    const int grid = n_tiles < dev.sm_count ? n_tiles : dev.sm_count;
+    mmq_q4k_kernel<<<grid, kTM + 32, kSmemMmq, st>>>(map_w, map_q, map_r, c, m, in_f, out_f, status);
     return cudaGetLastError();
 }
 

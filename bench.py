@@ -350,6 +350,11 @@ def run_profile_case(args):
     from infr_b200 import synth
 
     name, out_f, in_f, m = args.profile_case.split(":")
+    if name == "mmq":  # mmq:OUT_F:IN_F:M — the prefill GEMM (Linear with m > 8)
+        be = infr_b200.CudaBackend(device=0)
+        print(json.dumps(_mmq_case(be, infr_b200, int(m), int(in_f), int(out_f), 5, args.steps, 2)))
+        be.close()
+        return
     dtype = {v: k for k, v in synth.DTYPE_NAMES.items()}[name]
     out_f, in_f, m = int(out_f), int(in_f), int(m)
     be = infr_b200.CudaBackend(device=0, _dev_opts=[int(os.environ.get('INFR_DEV_GEMV_IMPL', '0'))])

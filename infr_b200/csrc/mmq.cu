@@ -28,6 +28,9 @@ namespace {
 
 constexpr int kTM = 128;  // weight rows per tile (MMA M)
 constexpr int kTN = 64;   // tokens per tile (MMA N)
+constexpr int kMathWarps = 16;                 // 4 per tensor-memory lane quarter
+constexpr int kMathThreads = kMathWarps * 32;  // thread = (weight row, 16-column group)
+constexpr int kCG = kTN / 4;                   // columns per thread in the epilogue
 constexpr uint32_t kMmqSpin = 1u << 22;
 
 __device__ __forceinline__ uint32_t sm_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -87,26 +90,28 @@ __device__ __forceinline__ void tma_3d(uint32_t dst, const CUtensorMap *map, int
                  : "memory");
 }
 
-// Shared-memory plan (bytes): two load stages {raw weights 128 x 144, code planes [16][64][16], record
-// planes [2][64][16]}, two operand buffers {A_lo [16][128][16], A_hi [16][128][16], A_ml [128][16],
-// A_mh [128][16]}, one zero plane [128][16], three d8 rows [64] f32.
+// Shared-memory plan (bytes): four load stages {raw weights 128 x 144, code planes [16][64][16], record
+// planes [2][64][16]}, one operand buffer {A_lo [16][128][16], A_hi [16][128][16], A_ml [128][16],
+// A_mh [128][16]}, one zero plane [128][16], three d8 rows [64] f32.  Tensor memory is double-buffered.
 constexpr int kRawBytes = kTM * 144, kCodeBytes = 16 * kTN * 16, kRecBytes = 2 * kTN * 16;
 constexpr int kStageBytes = kRawBytes + kCodeBytes + kRecBytes;
 constexpr int kABufBytes = 2 * 16 * kTM * 16 + 2 * kTM * 16;
-constexpr int kSmemMmq = 2 * kStageBytes + 2 * kABufBytes + kTM * 16 + 3 * kTN * 4 + 256;
+constexpr int kStages = 4;  // TMA latency is several block-times: keep four blocks in flight
+constexpr int kSmemMmq = kStages * kStageBytes + kABufBytes + kTM * 16 + 3 * kTN * 4 + 256;
 
-// Warps 0..3 (thread r = weight row r = tensor-memory lane r) unpack, issue the MMAs and run the
-// epilogue; warp 4 is the TMA producer.  Persistent CTA: it walks tiles blockIdx.x, +gridDim.x, ...
-__global__ void __launch_bounds__(kTM + 32, 1)
+// Warps 0..15 are math warps: warp w works on tensor-memory lanes / weight rows 32*(w&3) .. +31 and on
+// sub-block pair / column group (w>>2): it unpacks that pair of its rows, and in the epilogue folds 16
+// token columns.  Warp 16 is the TMA producer.  Persistent CTA: it walks tiles blockIdx.x, +gridDim.x, ...
+__global__ void __launch_bounds__(kMathThreads + 32, 1)
     mmq_q4k_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q,
                    const __grid_constant__ CUtensorMap map_r, float *__restrict__ C, int m, int in_f, int out_f,
                    uint32_t *__restrict__ status) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *stage0 = smem;
-    uint8_t *abuf0 = smem + 2 * kStageBytes;
-    uint8_t *zero_plane = abuf0 + 2 * kABufBytes;
+    uint8_t *abuf0 = smem + kStages * kStageBytes;
+    uint8_t *zero_plane = abuf0 + kABufBytes;
     float *d8buf = reinterpret_cast<float *>(zero_plane + kTM * 16);  // [3][64]
-    __shared__ uint64_t bars[4];  // full[2], mma_done[2]
+    __shared__ uint64_t bars[2 * kStages + 2];  // full[kStages], mma_done[2], empty[kStages]
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_dead;
 
@@ -120,7 +125,7 @@ __global__ void __launch_bounds__(kTM + 32, 1)
 
     if (tid == 0) {
         s_dead = 0;
-        for (int i = 0; i < 4; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sm_u32(&bars[i])));
+        for (int i = 0; i < 2 * kStages + 2; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sm_u32(&bars[i])));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -128,21 +133,25 @@ __global__ void __launch_bounds__(kTM + 32, 1)
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     if (tid < kTM) *reinterpret_cast<uint4 *>(zero_plane + (size_t)tid * 16) = make_uint4(0, 0, 0, 0);
+    const int row_in_tile = (warp & 3) * 32 + (tid & 31), cg = warp >> 2;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base_s;
 
-    if (warp == 4) {
+    if (warp == kMathWarps) {
         // ------------------------------------------------------------------ TMA producer
         if ((tid & 31) == 0) {
             int j = 0;
             for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
                 const int rt = t % row_tiles, tt = t / row_tiles;  // consecutive CTAs share a token tile
                 for (int b = 0; b < nb; b++, j++) {
-                    const int s = j & 1;
-                    if (j >= 2 && !mbar_wait_bounded(sm_u32(&bars[2 + s]), (uint32_t)(((j >> 1) - 1) & 1))) {
+                    // stage j % kStages was last used by job j - kStages; its codes are free once that job's MMAs are done
+                    // (a second commit of that job arrives on empty[stage]; a barrier per stage is never more than
+                    // one phase ahead of this wait)
+                    const int s = j % kStages;
+                    if (j >= kStages && !mbar_wait_bounded(sm_u32(&bars[kStages + 2 + s]), (uint32_t)((j / kStages - 1) & 1))) {
                         atomicExch(status, 5u);
                         *(volatile int *)&s_dead = 1;
                         return;
@@ -162,61 +171,67 @@ __global__ void __launch_bounds__(kTM + 32, 1)
 
     // ---------------------------------------------------------------------- math warps
     const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(kTN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-    float acc[kTN];
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(cg * kCG);
+    float acc[kCG];
     float dw_prev = 0.f, dmin_prev = 0.f;
     bool dead = false;
 
     // epilogue of job j: fold the block's tensor-memory sums into the running f32 sums
     auto epilogue = [&](int j, float dw, float dminw) {
         const int s = j & 1;
-        if (!mbar_wait_bounded(sm_u32(&bars[2 + s]), (uint32_t)((j >> 1) & 1))) {
+        if (!mbar_wait_bounded(sm_u32(&bars[kStages + s]), (uint32_t)((j >> 1) & 1))) {
             *(volatile int *)&s_dead = 1;
             return;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const float *d8 = d8buf + (j % 3) * kTN;
+        const float *d8 = d8buf + (j % 3) * kTN + cg * kCG;
         const uint32_t tb = lane_addr + (uint32_t)s * 256;
+        int vlo[16], vhi[16], vml[16], vmh[16];
+        tmem_ld16(tb, vlo);
+        tmem_ld16(tb + kTN, vhi);
+        tmem_ld16(tb + 2 * kTN, vml);
+        tmem_ld16(tb + 3 * kTN, vmh);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int c0 = 0; c0 < kTN; c0 += 16) {
-            int vlo[16], vhi[16], vml[16], vmh[16];
-            tmem_ld16(tb + c0, vlo);
-            tmem_ld16(tb + kTN + c0, vhi);
-            tmem_ld16(tb + 2 * kTN + c0, vml);
-            tmem_ld16(tb + 3 * kTN + c0, vmh);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const int sd = vlo[i] + 8 * vhi[i];
-                const int sm = vml[i] + 64 * vmh[i];
-                const float t = __fsub_rn(__fmul_rn(dw, (float)sd), __fmul_rn(dminw, (float)sm));
-                acc[c0 + i] = __fadd_rn(acc[c0 + i], __fmul_rn(d8[c0 + i], t));
-            }
+        for (int i = 0; i < kCG; i++) {
+            const int sd = vlo[i] + 8 * vhi[i];
+            const int sm = vml[i] + 64 * vmh[i];
+            const float t = __fsub_rn(__fmul_rn(dw, (float)sd), __fmul_rn(dminw, (float)sm));
+            acc[i] = __fadd_rn(acc[i], __fmul_rn(d8[i], t));
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     };
     auto store_tile = [&](int t) {
         const int rt = t % row_tiles, tt = t / row_tiles;
-        const int row = rt * kTM + tid;
+        const int row = rt * kTM + row_in_tile;
         if (row < out_f) {
 #pragma unroll
-            for (int i = 0; i < kTN; i++)
-                if (tt * kTN + i < m) C[(size_t)(tt * kTN + i) * out_f + row] = acc[i];
+            for (int i = 0; i < kCG; i++)
+                if (tt * kTN + cg * kCG + i < m) C[(size_t)(tt * kTN + cg * kCG + i) * out_f + row] = acc[i];
         }
     };
 
     int j = 0, prev_tile = -1;
     for (int t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x) {
         for (int b = 0; b < nb && !dead; b++, j++) {
-            const int s = j & 1;
-            uint8_t *st = stage0 + (size_t)s * kStageBytes;
-            uint8_t *ab = abuf0 + (size_t)s * kABufBytes;
+            const int s = j & 1, ls = j % kStages;
+            uint8_t *st = stage0 + (size_t)ls * kStageBytes;
+            uint8_t *ab = abuf0;
+            // ---- the previous block: its MMAs must be done before the operand buffer is rewritten ----
+            if (j > 0) {
+                epilogue(j - 1, dw_prev, dmin_prev);
+                if (b == 0 && !*(volatile int *)&s_dead) store_tile(prev_tile);
+            }
+            if (b == 0) {
+#pragma unroll
+                for (int i = 0; i < kCG; i++) acc[i] = 0.f;
+            }
             uint8_t *sA_lo = ab, *sA_hi = ab + 16 * kTM * 16, *sA_ml = ab + 2 * 16 * kTM * 16, *sA_mh = sA_ml + kTM * 16;
             // A thread whose bounded wait expires raises the CTA-wide flag but still walks to the next
             // barrier, where every thread sees the flag and leaves together.
-            if (!mbar_wait_bounded(sm_u32(&bars[s]), (uint32_t)((j >> 1) & 1))) *(volatile int *)&s_dead = 1;
+            if (!mbar_wait_bounded(sm_u32(&bars[ls]), (uint32_t)((j / kStages) & 1))) *(volatile int *)&s_dead = 1;
             // ---- unpack weight row `tid` of this block from the raw tile ----
-            const uint8_t *blk = st + (size_t)tid * 144;
+            const uint8_t *blk = st + (size_t)row_in_tile * 144;
             const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
             const float dw = h2f(hdr.x), dminw = h2f(hdr.x >> 16);
             {
@@ -225,37 +240,39 @@ __global__ void __launch_bounds__(kTM + 32, 1)
                 mn[0] = hdr.z & 0x3F3F3F3Fu;
                 sc[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
                 mn[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-                *reinterpret_cast<uint4 *>(sA_ml + (size_t)tid * 16) = make_uint4(mn[0], mn[1], 0, 0);
-                *reinterpret_cast<uint4 *>(sA_mh + (size_t)tid * 16) = make_uint4(0, 0, mn[0], mn[1]);
+                if (cg == 0) {
+                    *reinterpret_cast<uint4 *>(sA_ml + (size_t)row_in_tile * 16) = make_uint4(mn[0], mn[1], 0, 0);
+                    *reinterpret_cast<uint4 *>(sA_mh + (size_t)row_in_tile * 16) = make_uint4(0, 0, mn[0], mn[1]);
+                }
+                const int p = cg;  // this thread's sub-block pair (2p, 2p+1)
+                const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 16 + p * 32);
+                const uint4 q1 = *reinterpret_cast<const uint4 *>(blk + 32 + p * 32);
+                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                const uint32_t scp = sc[p >> 1] >> (16 * (p & 1));
 #pragma unroll
-                for (int p = 0; p < 4; p++) {
-                    const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 16 + p * 32);
-                    const uint4 q1 = *reinterpret_cast<const uint4 *>(blk + 32 + p * 32);
-                    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                for (int hl = 0; hl < 2; hl++) {
+                    const int sb = 2 * p + hl;
+                    const uint32_t scs = (scp >> (8 * hl)) & 0xFFu;
+                    const uint32_t f_lo = scs & 7u, f_hi = scs >> 3;
+                    uint32_t lo[8], hi[8];
 #pragma unroll
-                    for (int hl = 0; hl < 2; hl++) {
-                        const int sb = 2 * p + hl;
-                        const uint32_t scs = (sc[sb >> 2] >> (8 * (sb & 3))) & 0xFFu;
-                        const uint32_t f_lo = scs & 7u, f_hi = scs >> 3;
-                        uint32_t lo[8], hi[8];
-#pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            const uint32_t nib = (hl ? (w[i] >> 4) : w[i]) & 0x0F0F0F0Fu;
-                            lo[i] = nib * f_lo;
-                            hi[i] = nib * f_hi;
-                        }
-                        *reinterpret_cast<uint4 *>(sA_lo + ((size_t)(2 * sb) * kTM + tid) * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                        *reinterpret_cast<uint4 *>(sA_lo + ((size_t)(2 * sb + 1) * kTM + tid) * 16) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-                        *reinterpret_cast<uint4 *>(sA_hi + ((size_t)(2 * sb) * kTM + tid) * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                        *reinterpret_cast<uint4 *>(sA_hi + ((size_t)(2 * sb + 1) * kTM + tid) * 16) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                    for (int i = 0; i < 8; i++) {
+                        const uint32_t nib = (hl ? (w[i] >> 4) : w[i]) & 0x0F0F0F0Fu;
+                        lo[i] = nib * f_lo;  // bytes <= 15 * 7: no carry between bytes
+                        hi[i] = nib * f_hi;
                     }
+                    // elements 0..15 of sub-block sb -> plane 2*sb, 16..31 -> plane 2*sb + 1
+                    *reinterpret_cast<uint4 *>(sA_lo + ((size_t)(2 * sb) * kTM + row_in_tile) * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4 *>(sA_lo + ((size_t)(2 * sb + 1) * kTM + row_in_tile) * 16) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                    *reinterpret_cast<uint4 *>(sA_hi + ((size_t)(2 * sb) * kTM + row_in_tile) * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4 *>(sA_hi + ((size_t)(2 * sb + 1) * kTM + row_in_tile) * 16) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
                 }
             }
             // d8 of this block's tokens: first word of record plane 1
             if (tid < kTN) d8buf[(j % 3) * kTN + tid] = *reinterpret_cast<const float *>(st + kRawBytes + kCodeBytes + kTN * 16 + (size_t)tid * 16);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            asm volatile("bar.sync 1, %0;" ::"r"(kTM) : "memory");
+            asm volatile("bar.sync 1, %0;" ::"r"(kMathThreads) : "memory");
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (*(volatile int *)&s_dead) {
                 dead = true;
@@ -274,18 +291,8 @@ __global__ void __launch_bounds__(kTM + 32, 1)
                 const uint64_t dbr = umma_desc(sm_u32(sR), kTN * 16, 128);
                 umma_i8(td + 2 * kTN, umma_desc(sm_u32(sA_ml), (uint32_t)(zero_plane - sA_ml), 128), dbr, idesc, 0);
                 umma_i8(td + 3 * kTN, umma_desc(sm_u32(sA_mh), (uint32_t)(zero_plane - sA_mh), 128), dbr, idesc, 0);
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sm_u32(&bars[2 + s])) : "memory");
-            }
-            // ---- epilogue of the previous block overlaps this block's MMAs ----
-            if (j > 0) {
-                epilogue(j - 1, dw_prev, dmin_prev);
-                // a finished tile is stored only if nothing expired (the flag is re-checked CTA-wide at the
-                // next barrier; a partial store of a failed launch is harmless, the launch reports an error)
-                if (b == 0 && !*(volatile int *)&s_dead) store_tile(prev_tile);
-            }
-            if (b == 0) {
-#pragma unroll
-                for (int i = 0; i < kTN; i++) acc[i] = 0.f;
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sm_u32(&bars[kStages + s])) : "memory");
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sm_u32(&bars[kStages + 2 + ls])) : "memory");
             }
             dw_prev = dw;
             dmin_prev = dminw;
@@ -294,7 +301,7 @@ __global__ void __launch_bounds__(kTM + 32, 1)
     }
     if (!dead && j > 0) epilogue(j - 1, dw_prev, dmin_prev);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    asm volatile("bar.sync 1, %0;" ::"r"(kTM) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"r"(kMathThreads) : "memory");
     if (*(volatile int *)&s_dead) {
         if (tid == 0) atomicExch(status, 4u);
     } else if (j > 0) {
@@ -359,7 +366,7 @@ cudaError_t launch_mmq_q4k(const uint8_t *w, const Q8Dev &a, void *records, floa
     if (e != cudaSuccess) return e;
     const int n_tiles = ((out_f + kTM - 1) / kTM) * ((m + kTN - 1) / kTN);
     const int grid = n_tiles < dev.sm_count ? n_tiles : dev.sm_count;
-    mmq_q4k_kernel<<<grid, kTM + 32, kSmemMmq, st>>>(map_w, map_q, map_r, c, m, in_f, out_f, status);
+    mmq_q4k_kernel<<<grid, kMathThreads + 32, kSmemMmq, st>>>(map_w, map_q, map_r, c, m, in_f, out_f, status);
     return cudaGetLastError();
 }
 

@@ -1,0 +1,48 @@
+"""Row (column-parallel) sharding of a block-quantized weight across ranks.
+
+The quantized matmul shards by OUTPUT rows with no exchange inside the op: rank r owns rows
+[r*out_f/W, (r+1)*out_f/W) of the row-major [out_f, in_f] weight, whole GGUF blocks stay whole because a
+row is a whole number of blocks, activations are replicated, and every rank produces its own slice of y.
+This is the column-parallel half of the reference's tensor-parallel lowering
+(crates/infr-llama/src/seam/mod.rs:2711-2798, `tp_slice_column`).  A collective is needed only where
+the next consumer wants the full vector: `gather_rows` is that all-gather.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from .synth import row_bytes
+
+
+def row_range(out_f: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous balanced row range of `rank` (the first out_f % world ranks get one extra row)."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    base, rem = divmod(out_f, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def row_shard(dtype: int, w_bytes: np.ndarray, out_f: int, in_f: int, rank: int, world: int) -> tuple[np.ndarray, int, int]:
+    """(bytes of this rank's rows, first row, row count)."""
+    bpr = row_bytes(dtype, in_f)
+    w = np.ascontiguousarray(w_bytes, dtype=np.uint8).reshape(-1)
+    if w.size != out_f * bpr:
+        raise ValueError(f"weight holds {w.size} bytes, expected {out_f} rows x {bpr}")
+    lo, hi = row_range(out_f, rank, world)
+    return w[lo * bpr:hi * bpr], lo, hi - lo
+
+
+def gather_rows(dist, y_local: np.ndarray, out_f: int, rank: int, world: int) -> np.ndarray:
+    """All-gather of the ranks' y slices [m, rows_r] into the full [m, out_f] (torch.distributed)."""
+    import torch
+
+    m = y_local.shape[0]
+    counts = [row_range(out_f, r, world)[1] - row_range(out_f, r, world)[0] for r in range(world)]
+    width = max(counts)
+    pad = np.zeros((m, width), np.float32)
+    pad[:, :y_local.shape[1]] = y_local
+    mine = torch.from_numpy(pad)
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)
+    return np.concatenate([parts[r].numpy()[:, :counts[r]] for r in range(world)], axis=1)

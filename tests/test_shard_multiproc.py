@@ -1,0 +1,68 @@
+"""Row sharding across ranks, exercised with two gloo ranks on CPU.
+
+Each rank takes its row slice of a Q4_K / Q6_K weight, multiplies with the CPU restatement (the GPU is
+not needed to check the partition and the gather) and the gathered result must equal the unsharded one
+bit for bit — the op has no cross-rank arithmetic.
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, dt, out_f, in_f, m, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+
+    from infr_b200 import shard, synth
+    from oracle.cpu_oracle import Oracle
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        orc = Oracle()
+        w = synth.weight(dt, out_f, in_f, seed=3)
+        x = synth.normal(4, (m, in_f))
+        mine, lo, n = shard.row_shard(dt, w, out_f, in_f, rank, world)
+        y_local = orc.linear(dt, mine, x, m, in_f, n, threads=2)
+        full = shard.gather_rows(dist, y_local, out_f, rank, world)
+        want = orc.linear(dt, w, x, m, in_f, out_f, threads=2)
+        q.put((rank, bool((full.view(np.uint32) == want.view(np.uint32)).all()), lo, n))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dt,out_f,in_f,m", [(12, 37, 512, 2), (14, 64, 256, 1)])
+def test_row_shards_gather_to_the_unsharded_result(dt, out_f, in_f, m):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + dt) % 2000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, dt, out_f, in_f, m, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok, _, _ in res)
+    assert res[0][2] == 0 and res[0][2] + res[0][3] == res[1][2] and res[1][2] + res[1][3] == out_f
+
+
+def test_row_range_is_a_balanced_partition():
+    sys.path.insert(0, ROOT)
+    from infr_b200 import shard
+
+    for out_f in (1, 7, 4096, 14336, 128256):
+        for world in (1, 2, 3, 8):
+            spans = [shard.row_range(out_f, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == out_f
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        shard.row_range(10, 2, 2)

@@ -444,7 +444,9 @@ cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float
         return (size_t)M * nb * 272 + (size_t)((M * nb + 3) & ~3) * 4 + (size_t)2 * kw * 512 + (size_t)kw * kMaxSlotsMma * 8 + 64 +
                (size_t)2 * kw * kTileRows * sb * 144;
     };
-    int kw = tiles >= 4 * dev.sm_count ? 4 : (tiles >= 2 * dev.sm_count ? 8 : 16);
+    // 16 math warps per SM: with kw warps per tile an SM holds 16/kw tiles at once.  Prefer the widest
+    // split that still lets every tile be resident in the first wave.
+    int kw = tiles > 2 * dev.sm_count ? 4 : (tiles > dev.sm_count ? 8 : 16);
     // wide batches stage more activation bytes per CTA: let more warps share one staging copy so that
     // 16 math warps stay resident per SM
     while (kw < 16 && need(kw) > (size_t)dev.max_smem_optin / (16 / kw) - 2048) kw *= 2;

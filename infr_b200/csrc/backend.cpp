@@ -310,6 +310,50 @@ Status CudaBackend::gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *
     return s;
 }
 
+// rows == 1 or `reference`: every expert bank works on raw f32 activations (int8_ok false,
+// crates/infr-cpu/src/lib.rs:2359): dequantised weight rows, f32 dot, pairs kept in (row, rank) order.
+Status CudaBackend::moe_ffn_f32(const MoeArgs &a) {
+    cudaSetDevice(device_);
+    const size_t rows = a.rows, ne = a.ne, nff = a.n_ff, nu = a.n_used, nx = a.n_expert;
+    const size_t n_pairs = rows * nu;
+    if (n_pairs > 65535) return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn (f32 path): more than 65535 routed pairs");
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += align_up(bytes, 256);
+        return o;
+    };
+    const size_t o_logits = take(rows * nx * 4), o_ids = take(n_pairs * 4), o_w = take(n_pairs * 4);
+    const size_t o_g = take(n_pairs * nff * 4), o_u = take(n_pairs * nff * 4), o_act = take(n_pairs * nff * 4);
+    const size_t o_q = take(n_pairs * nff), o_d = take(n_pairs * (nff / 256) * 4), o_s = take(n_pairs * (nff / 32) * 4);
+    const size_t o_y = take(n_pairs * ne * 4);
+    Status s = ensure_scratch(off);
+    if (!s.ok()) return s;
+    uint8_t *b = scratch();
+    float *logits = a.logits ? a.logits : reinterpret_cast<float *>(b + o_logits);
+    int32_t *ids = a.sel_ids ? a.sel_ids : reinterpret_cast<int32_t *>(b + o_ids);
+    float *w = a.sel_w ? a.sel_w : reinterpret_cast<float *>(b + o_w);
+    float *g = reinterpret_cast<float *>(b + o_g), *u = reinterpret_cast<float *>(b + o_u), *act = reinterpret_cast<float *>(b + o_act);
+    float *y = reinterpret_cast<float *>(b + o_y);
+    const size_t gu_stride = nff * (ne / 256) * 144, d_stride = ne * (nff / 256) * 144;
+#define INFR_STEP(call, what)          \
+    do {                               \
+        s = cuda_status((call), what); \
+        if (!s.ok()) return s;         \
+        launches_++;                   \
+    } while (0)
+    INFR_STEP(launch_moe_router(a.router, a.router_x, logits, (int)rows, (int)ne, (int)nx, stream_), "moe router");
+    INFR_STEP(launch_moe_route(logits, (int)rows, (int)nx, (int)nu, a.scale, a.norm_w, ids, w, stream_), "moe route");
+    INFR_STEP(launch_gemv_q4k_f32_sel(a.gate, ids, gu_stride, a.x, (int)nu, g, (int)n_pairs, (int)ne, (int)nff, dev_, stream_), "moe gate f32");
+    INFR_STEP(launch_gemv_q4k_f32_sel(a.up, ids, gu_stride, a.x, (int)nu, u, (int)n_pairs, (int)ne, (int)nff, dev_, stream_), "moe up f32");
+    INFR_STEP(launch_moe_swiglu_quant(g, u, (int)n_pairs, (int)nff, reinterpret_cast<int8_t *>(b + o_q), reinterpret_cast<float *>(b + o_d),
+                                      reinterpret_cast<int32_t *>(b + o_s), act, stream_), "moe swiglu");
+    INFR_STEP(launch_gemv_q4k_f32_sel(a.down, ids, d_stride, act, 0, y, (int)n_pairs, (int)nff, (int)ne, dev_, stream_), "moe down f32");
+    INFR_STEP(launch_moe_combine(y, nullptr, w, (int)rows, (int)nu, (int)ne, a.dst, stream_), "moe combine");
+#undef INFR_STEP
+    return Status::Ok();
+}
+
 Status CudaBackend::moe_ffn(const MoeArgs &a) {
     if (a.gate_dt != DT_Q4K || a.up_dt != DT_Q4K || a.down_dt != DT_Q4K)
         return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: expert banks must be Q4_K");
@@ -317,9 +361,8 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
         return Status::Err(INFR_E_UNSUPPORTED, fmt("moe_ffn: ne=%u and n_ff_exp=%u must be multiples of 256", a.ne, a.n_ff));
     if (a.n_expert == 0 || a.n_expert > 1024 || a.n_used == 0 || a.n_used > 32 || a.n_used > a.n_expert)
         return Status::Err(INFR_E_INVALID, fmt("moe_ffn: n_expert=%u (<=1024), n_used=%u (<=32)", a.n_expert, a.n_used));
-    if (a.rows < 2 || reference_)
-        return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: the single-row / reference (f32 activation) expert path is not built yet");
     if (a.rows == 0) return Status::Ok();
+    if (a.rows < 2 || reference_) return moe_ffn_f32(a);
     cudaSetDevice(device_);
     const size_t rows = a.rows, ne = a.ne, nff = a.n_ff, nu = a.n_used, nx = a.n_expert;
     const size_t n_pairs = rows * nu;

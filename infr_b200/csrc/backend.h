@@ -90,6 +90,7 @@ public:
         float *sel_w, *logits;
     };
     Status moe_ffn(const MoeArgs &a);
+    Status moe_ffn_f32(const MoeArgs &a);
     Status gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f);
     Status gemv_block_acc(int dtype, const uint8_t *w, const float *x, int32_t *acc, uint32_t in_f,
                           uint32_t out_f);

@@ -279,11 +279,26 @@ __device__ __forceinline__ void stage_f32(const float *x, int m, int in_f, float
     }
 }
 
+// Expert selection for the f32 (single-row / reference) MoE path: blockIdx.y = routed pair p, whose
+// weights are expert sel[p] of a bank, whose activation row is p / x_div (x_div = 0: row p) and whose
+// output row is p.  sel == nullptr: an ordinary GEMV.
+struct SelArgs {
+    const int32_t *sel;
+    size_t w_stride;
+    int x_div;
+};
+
 template <int M>
 __global__ void __launch_bounds__(kThreads) gemv_q4k_f32_kernel(const uint8_t *__restrict__ W,
                                                                 const float *__restrict__ x,
                                                                 float *__restrict__ y, int m, int in_f,
-                                                                int out_f) {
+                                                                int out_f, SelArgs sa) {
+    if (sa.sel) {
+        const int p = blockIdx.y;
+        W += (size_t)sa.sel[p] * sa.w_stride;
+        x += (size_t)(sa.x_div ? p / sa.x_div : p) * in_f;
+        y += (size_t)p * out_f;
+    }
     extern __shared__ __align__(16) uint8_t smem[];
     float *s_x = reinterpret_cast<float *>(smem);
     stage_f32<M>(x, m, in_f, s_x);
@@ -496,9 +511,10 @@ cudaError_t launch_f32_m(int dt, const uint8_t *w, const float *x, float *y, int
         if ((e = set_smem(KERNEL, smem)) != cudaSuccess) return e;   \
         KERNEL<<<grid, kThreads, smem, st>>>(w, x, y, m, in_f, out_f); \
     } while (0)
-    if (dt == DT_Q4K)
-        INFR_LAUNCH(gemv_q4k_f32_kernel<M>);
-    else if (dt == DT_Q6K)
+    if (dt == DT_Q4K) {
+        if ((e = set_smem(gemv_q4k_f32_kernel<M>, smem)) != cudaSuccess) return e;
+        gemv_q4k_f32_kernel<M><<<grid, kThreads, smem, st>>>(w, x, y, m, in_f, out_f, SelArgs{nullptr, 0, 0});
+    } else if (dt == DT_Q6K)
         INFR_LAUNCH(gemv_q6k_f32_kernel<M>);
     else
         INFR_LAUNCH(gemv_q2_0_f32_kernel<M>);
@@ -507,6 +523,19 @@ cudaError_t launch_f32_m(int dt, const uint8_t *w, const float *x, float *y, int
 }
 
 }  // namespace
+
+cudaError_t launch_gemv_q4k_f32_sel(const uint8_t *bank, const int32_t *sel, size_t w_stride, const float *x, int x_div,
+                                    float *y, int n_pairs, int in_f, int out_f, const DeviceInfo &dev, cudaStream_t st) {
+    const size_t smem = (size_t)in_f * 4;
+    if (smem > (size_t)dev.max_smem_optin || n_pairs < 1 || n_pairs > 65535) return cudaErrorInvalidValue;
+    cudaError_t e = set_smem(gemv_q4k_f32_kernel<1>, smem);
+    if (e != cudaSuccess) return e;
+    int gx = (out_f + kWarps - 1) / kWarps;
+    const int cap = (dev.sm_count * 4 + n_pairs - 1) / n_pairs;
+    if (gx > cap) gx = cap < 1 ? 1 : cap;
+    gemv_q4k_f32_kernel<1><<<dim3((unsigned)gx, (unsigned)n_pairs), kThreads, smem, st>>>(bank, x, y, 1, in_f, out_f, SelArgs{sel, w_stride, x_div});
+    return cudaGetLastError();
+}
 
 cudaError_t launch_gemv_q8(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
                            int32_t *acc_out, const DeviceInfo &dev, cudaStream_t st) {

@@ -82,6 +82,11 @@ cudaError_t launch_moe_swiglu_quant(const float *gate, const float *up, int n_pa
 cudaError_t launch_moe_combine(const float *y_pairs, const int32_t *pair_of_slot, const float *sel_w, int rows, int n_used,
                                int ne, float *out, cudaStream_t st);
 
+// f32-activation GEMV of routed pair p against expert sel[p] of a Q4_K bank (stride w_stride bytes):
+// y[p, :] = dequant(bank[sel[p]]) * x[x_div ? p / x_div : p, :].
+cudaError_t launch_gemv_q4k_f32_sel(const uint8_t *bank, const int32_t *sel, size_t w_stride, const float *x, int x_div,
+                                    float *y, int n_pairs, int in_f, int out_f, const DeviceInfo &dev, cudaStream_t st);
+
 cudaError_t launch_fill_u32(uint32_t *p, size_t n, uint32_t v, cudaStream_t st);
 
 }  // namespace infr

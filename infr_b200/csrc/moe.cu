@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restric
     const int r = (int)(idx / ne), i = (int)(idx % ne);
     float o = 0.f;
     for (int k = 0; k < n_used; k++) {
-        const int p = pair_of_slot[(size_t)r * n_used + k];
+        const int p = pair_of_slot ? pair_of_slot[(size_t)r * n_used + k] : r * n_used + k;
         o = __fadd_rn(o, __fmul_rn(sel_w[(size_t)r * n_used + k], y_pairs[(size_t)p * ne + i]));
     }
     out[idx] = o;

@@ -96,7 +96,43 @@ def test_moe_through_the_graph_seam_and_skewed_routing(backend, oracle):
     want, ids, _, _ = oracle.moe_ffn(x, router, gate, up, down, rows=rows, ne=ne, n_expert=n_expert, n_used=n_used, n_ff_exp=nff)
     assert (ids[:, 0] == 5).all() and (ids[:, 1] == 2).all()
     assert fx.rel_l2(got, want) < 1e-3
-    with pytest.raises(infr_b200.BackendError) as ei:   # a single row takes the f32 expert path, not built yet
-        backend.moe_ffn(bufs[xid], bufs[xid], bufs[rid], bufs[gid], bufs[uid], bufs[did], bufs[oid], rows=1, ne=ne,
-                        n_expert=n_expert, n_used=n_used, n_ff_exp=nff)
-    assert ei.value.code == infr_b200.E_UNSUPPORTED
+
+
+def test_moe_single_row_takes_the_f32_activation_path(backend, oracle):
+    # rows == 1 (decode): int8_ok is false (crates/infr-cpu/src/lib.rs:2359) -> raw f32 activations,
+    # dequantised weight rows and `dot`; compared like reference mode, 1e-5 of the output's magnitude
+    ne, n_expert, n_used, nff = 512, 16, 4, 768
+    gate, up, down = _banks(n_expert, nff, ne, seed=200)
+    router = synth.normal(17, (n_expert, ne), 1.0 / np.sqrt(ne))
+    for seed in (1, 2):
+        x = synth.normal(seed, (1, ne))
+        got, ids, w, lg = _run(backend, x, router, gate, up, down, 1, ne, n_expert, n_used, nff)
+        want, o_ids, o_w, o_lg = oracle.moe_ffn(x, router, gate, up, down, rows=1, ne=ne, n_expert=n_expert, n_used=n_used,
+                                                n_ff_exp=nff)
+        np.testing.assert_array_equal(lg.view(np.uint32), o_lg.view(np.uint32))
+        np.testing.assert_array_equal(ids, o_ids)
+        assert np.abs(got - want).max() / np.abs(want).max() < 1e-5
+        # and it is NOT the int8 path: the production batch path on the same row differs by ~1e-3
+        x2 = np.concatenate([x, x])
+        prod, _, _, _ = oracle.moe_ffn(x2, router, gate, up, down, rows=2, ne=ne, n_expert=n_expert, n_used=n_used, n_ff_exp=nff)
+        assert fx.rel_l2(prod[0], want[0]) > 1e-5
+
+
+def test_moe_reference_mode_backend(oracle):
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    be = infr_b200.CudaBackend(device=0, reference=True)
+    try:
+        rows, ne, n_expert, n_used, nff = 5, 256, 8, 2, 256
+        gate, up, down = _banks(n_expert, nff, ne, seed=300)
+        router = synth.normal(27, (n_expert, ne), 1.0 / np.sqrt(ne))
+        x = synth.normal(28, (rows, ne))
+        got, ids, _, _ = _run(be, x, router, gate, up, down, rows, ne, n_expert, n_used, nff)
+        want, o_ids, _, _ = oracle.moe_ffn(x, router, gate, up, down, rows=rows, ne=ne, n_expert=n_expert, n_used=n_used,
+                                           n_ff_exp=nff, reference=True)
+        np.testing.assert_array_equal(ids, o_ids)
+        assert np.abs(got - want).max() / np.abs(want).max() < 1e-5
+    finally:
+        be.close()

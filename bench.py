@@ -224,6 +224,36 @@ def _mmq_case(be, infr_b200, m, in_f, out_f, seed, steps, warmup):
     return res
 
 
+def _moe_case(be, infr_b200, steps, warmup):
+    """Qwen3-30B-A3B-shaped MoE layer: 256 tokens, hidden 2048, 128 experts (gate/up 2048->768, down 768->2048,
+    Q4_K), softmax top-8.  Bank bytes are random valid Q4_K blocks (timing does not depend on the values)."""
+    from infr_b200 import synth
+
+    rows, ne, nx, nu, nff = 256, 2048, 128, 8, 768
+    gate = be.from_numpy(synth.random_blocks(infr_b200.Q4K, nx * nff * ne, 100), infr_b200.USAGE_WEIGHTS)
+    up = be.from_numpy(synth.random_blocks(infr_b200.Q4K, nx * nff * ne, 101), infr_b200.USAGE_WEIGHTS)
+    down = be.from_numpy(synth.random_blocks(infr_b200.Q4K, nx * ne * nff, 102), infr_b200.USAGE_WEIGHTS)
+    router = be.from_numpy(synth.normal(7, (nx, ne), 1.0 / np.sqrt(ne)))
+    x = be.from_numpy(synth.normal(8, (rows, ne)))
+    dst = be.alloc(rows * ne * 4)
+    kw = dict(rows=rows, ne=ne, n_expert=nx, n_used=nu, n_ff_exp=nff)
+    for _ in range(warmup):
+        be.moe_ffn(x, x, router, gate, up, down, dst, **kw)
+    be.sync()
+    be.timer_start()
+    for _ in range(steps):
+        be.moe_ffn(x, x, router, gate, up, down, dst, **kw)
+    ms = be.timer_stop()
+    w_bytes = 3 * nx * nff * ne // 256 * 144
+    ops = rows * nu * 3 * 2.0 * ne * nff
+    res = {"workload": "MoE layer 256 tok x hidden 2048, 128 experts x (2048->768->2048) Q4_K, softmax top-8 (9 kernels)",
+           "us": ms * 1e3 / steps, "weight_bytes": w_bytes, "weights_gbs": w_bytes * steps / (ms * 1e-3) / 1e9,
+           "int8_tops": ops * steps / (ms * 1e-3) / 1e12, "l2": "weights 340 MB > L2"}
+    for b in (gate, up, down, router, x, dst):
+        b.close()
+    return res
+
+
 # ------------------------------------------------------------------------------------------------
 def run_b200(args):
     import infr_b200
@@ -337,6 +367,7 @@ def run_b200(args):
                 sweep.append(_gemv_case(be, infr_b200, dtype, o, i_, m, seed, sw_steps, 5, caps.l2_bytes, hbm_peak))
         out["sweep"] = sweep
         out["mmq"] = _mmq_case(be, infr_b200, 512, 4096, 14336, 5, 20, 3)
+        out["moe"] = _moe_case(be, infr_b200, 20, 3)
 
     if rank == 0 and world == 1 and not args.no_cpu:
         out["cpu_baseline"] = _cpu_baseline(w, x, budget_s=10.0)
@@ -355,6 +386,11 @@ def run_profile_case(args):
     from infr_b200 import synth
 
     name, out_f, in_f, m = args.profile_case.split(":")
+    if name == "moe":
+        be = infr_b200.CudaBackend(device=0)
+        print(json.dumps(_moe_case(be, infr_b200, args.steps, 2)))
+        be.close()
+        return
     if name == "mmq":  # mmq:OUT_F:IN_F:M — the prefill GEMM (Linear with m > 8)
         be = infr_b200.CudaBackend(device=0)
         print(json.dumps(_mmq_case(be, infr_b200, int(m), int(in_f), int(out_f), 5, args.steps, 2)))

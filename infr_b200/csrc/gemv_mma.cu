@@ -486,10 +486,8 @@ cudaError_t launch_grouped_q4k_mma(const uint8_t *bank, int n_experts, const Q8D
     if (in_f % 256 || max_items < 1) return cudaErrorInvalidValue;
     MmaGroup grp{item_expert, item_p0, item_cnt, n_items, pair_row};
     const int nb = in_f / 256;
-    if (nb >= 8) {
-        if ((nb + 7) / 8 == 1) return launch_mma_cfg<8, false, 8, 1>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
-        return launch_mma_cfg<8, false, 8, 2>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
-    }
+    // four warps per 16-row tile: an item has few tiles and few K blocks, so the per-tile barrier and
+    // reduction are shared by two blocks per warp where the rows are long enough
     if ((nb + 3) / 4 == 1) return launch_mma_cfg<8, false, 4, 1>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
     return launch_mma_cfg<8, false, 4, 2>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
 }

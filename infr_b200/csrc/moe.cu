@@ -97,8 +97,9 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
     }
 }
 
-// One CTA.  Thread e owns expert e: counts its pairs, the block scans the counts, then the thread
-// lists its pairs in (row, rank) order and cuts them into work items of up to 8 rows.
+// One CTA of 32 warps.  Warp w owns experts w, w+32, ...: it counts an expert's pairs with ballots over
+// 32 pairs at a time, the block scans the counts, then the warp lists the pairs in (row, rank) order
+// (ballot + prefix popcount keeps the order) and cuts them into work items of up to 8 rows.
 //   pair_row[p], pair_of_slot[r * n_used + rank] = p, item_{expert,p0,cnt}[], n_items
 __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restrict__ sel_ids, int rows, int n_used, int n_expert,
                                                           int32_t *__restrict__ pair_row, int32_t *__restrict__ pair_of_slot,
@@ -106,14 +107,18 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
                                                           int32_t *__restrict__ item_cnt, int32_t *__restrict__ n_items,
                                                           int32_t *__restrict__ counts_out) {
     __shared__ int s_cnt[1024], s_off[1024], s_ioff[1024];
-    const int e = threadIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_pairs = rows * n_used;
-    int cnt = 0;
-    if (e < n_expert)
-        for (int i = 0; i < n_pairs; i++) cnt += sel_ids[i] == e;
-    s_cnt[e] = e < n_expert ? cnt : 0;
+    for (int e = warp; e < n_expert; e += 32) {
+        int cnt = 0;
+        for (int i0 = 0; i0 < n_pairs; i0 += 32) {
+            const int i = i0 + lane;
+            cnt += __popc(__ballot_sync(0xffffffffu, i < n_pairs && sel_ids[i] == e));
+        }
+        if (lane == 0) s_cnt[e] = cnt;
+    }
     __syncthreads();
-    if (e == 0) {
+    if (threadIdx.x == 0) {
         int off = 0, ioff = 0;
         for (int k = 0; k < n_expert; k++) {
             s_off[k] = off;
@@ -124,20 +129,27 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
         *n_items = ioff;
     }
     __syncthreads();
-    if (e >= n_expert) return;
-    if (counts_out) counts_out[e] = cnt;
-    int p = s_off[e];
-    for (int i = 0; i < n_pairs; i++)
-        if (sel_ids[i] == e) {
-            pair_row[p] = i / n_used;
-            pair_of_slot[i] = p;
-            p++;
+    for (int e = warp; e < n_expert; e += 32) {
+        const int cnt = s_cnt[e];
+        if (counts_out && lane == 0) counts_out[e] = cnt;
+        int p = s_off[e];
+        for (int i0 = 0; i0 < n_pairs; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < n_pairs && sel_ids[i] == e;
+            const uint32_t mask = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int q = p + __popc(mask & ((1u << lane) - 1u));
+                pair_row[q] = i / n_used;
+                pair_of_slot[i] = q;
+            }
+            p += __popc(mask);
         }
-    int it = s_ioff[e];
-    for (int c = 0; c < cnt; c += 8, it++) {
-        item_expert[it] = e;
-        item_p0[it] = s_off[e] + c;
-        item_cnt[it] = cnt - c < 8 ? cnt - c : 8;
+        for (int c = lane * 8; c < cnt; c += 256) {
+            const int it = s_ioff[e] + c / 8;
+            item_expert[it] = e;
+            item_p0[it] = s_off[e] + c;
+            item_cnt[it] = cnt - c < 8 ? cnt - c : 8;
+        }
     }
 }
 

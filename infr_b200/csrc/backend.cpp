@@ -59,6 +59,7 @@ Status CudaBackend::create(const infr_cuda_opts &opts, CudaBackend **out) {
         return s;
     }
     be->gemv_impl_ = opts.reserved[0];
+    be->mmq_impl_ = opts.reserved[1];
     if (!(s = be->cuda_status(cudaHostAlloc((void **)&be->status_host_, 64, cudaHostAllocMapped), "cudaHostAlloc")).ok() ||
         !(s = be->cuda_status(cudaHostGetDevicePointer((void **)&be->status_dev_, be->status_host_, 0), "cudaHostGetDevicePointer")).ok()) {
         delete be;
@@ -246,9 +247,12 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
     if (m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0) {
         Q8Dev a;
         uint8_t *rec = nullptr;
-        Status s = quantize_for(dtype, x, m, in_f, &a, mmq_q4k_record_bytes((int)m, (int)in_f), &rec);
+        const size_t rec_bytes = mmq_impl_ == 1 ? mmq_q4k_record_bytes((int)m, (int)in_f) : mmq_ws_record_bytes((int)m, (int)in_f);
+        Status s = quantize_for(dtype, x, m, in_f, &a, rec_bytes, &rec);
         if (!s.ok()) return s;
-        s = cuda_status(launch_mmq_q4k(w, a, rec, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_), "mmq_q4k");
+        s = cuda_status(mmq_impl_ == 1 ? launch_mmq_q4k(w, a, rec, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_)
+                                       : launch_mmq_ws_q4k(w, a, rec, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_),
+                        "mmq_q4k");
         if (s.ok()) launches_ += 2;
         return s;
     }

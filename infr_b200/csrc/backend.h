@@ -141,6 +141,7 @@ private:
     uint32_t *status_host_ = nullptr;  // pinned + mapped: kernels report expired waits here
     uint32_t *status_dev_ = nullptr;
     int gemv_impl_ = 0;                // 0 = bulk-copy ring kernel, 1 = direct-load kernel
+    int mmq_impl_ = 0;                 // 0 = warp-specialised MMQ (f32 within rounding of the CPU), 1 = bit-identical MMQ
     Status check_device_status();
 };
 

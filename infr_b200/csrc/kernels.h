@@ -63,6 +63,11 @@ cudaError_t launch_gemv_f32(int dt, const uint8_t *w, const float *x, float *y, 
 size_t mmq_q4k_record_bytes(int m, int in_f);
 cudaError_t launch_mmq_q4k(const uint8_t *w, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
                            const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
+// The same GEMM with specialised warps (unpack / MMA issue / epilogue overlap) and the min term summed in
+// tensor memory by kind::tf32 MMAs: int32 block sums identical, f32 result within rounding of the CPU's.
+size_t mmq_ws_record_bytes(int m, int in_f);
+cudaError_t launch_mmq_ws_q4k(const uint8_t *w, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
+                              const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
 // Grouped Q4_K GEMM over a bank of n_experts matrices [out_f, in_f] stored back to back: work item i
 // multiplies up to 8 quantised activation rows (pairs item_p0[i]..+item_cnt[i], gathered through
 // pair_row when non-null) with expert item_expert[i]; y is [n_pairs, out_f].

@@ -15,6 +15,9 @@ NVCC_FLAGS = [
 ]
 
 
+NVCC_FLAGS += os.environ.get("INFR_NVCC_EXTRA", "").split()
+
+
 def nvcc() -> str:
     cand = os.environ.get("NVCC") or "/usr/local/cuda/bin/nvcc"
     return cand if os.path.exists(cand) else "nvcc"

@@ -13,20 +13,21 @@
 // sd = D_lo + 8 * D_hi.
 //
 // Roles in a CTA (one 128-row x 64-token tile at a time, persistent over tiles; job = one super-block of a tile):
-//   warps 0-7    unpack: thread = (weight row, half of the block); reads its 80 bytes of the Q4_K block straight
-//                from global memory one job ahead and writes the int8 operand planes of the whole block into one
-//                of two 64 KB buffers (the first four warps also the tf32 min planes and the row scale d)
+//   warps 0-7    unpack: thread = (weight row, K half of the block); turns its 4 sub-blocks into int8 operand words
+//                and stores them into TENSOR MEMORY (tcgen05.st), a ring of three half-block slots; the A operand
+//                of the MMAs is read from there, so shared memory carries only the token side
+//                (warps 0-3 also write the tf32 min planes and the row scale d)
 //   warps 8-15   epilogue: warp = (tensor-memory lane quarter, 32-column half); folds each job's int32 sums
 //                into 32 running f32 sums per thread
-//   warp 16      TMA producer of the activation planes (codes and tf32 block-sum pieces), three stages
-//   warps 17, 18 MMA issuers: issuer i runs the jobs j = i (mod 2) on operand buffer i and accumulator i,
-//                16 kind::i8 + 3 kind::tf32 instructions per job and ONE commit
-// A job's completion barrier (that one commit) releases its operand buffer, its activation stage and its
-// accumulator to the epilogue at once; a single issuer thread doing one barrier operation per quarter block
-// left the tensor pipe idle three quarters of the time.
+//   warp 16      TMA producer: raw Q4_K rows + activation planes (codes, tf32 block-sum pieces), five stages
+//   warp 17      MMA issuer: per job 16 kind::i8 + 3 kind::tf32 instructions, interleaved over three
+//                accumulator chains (an MMA that accumulates into the tile of the previous one waits ~95 cycles)
+// Tensor memory (512 columns): accumulators {D_lo, D_hi} x 2 jobs = 256, min sums 64, operand ring 3 x 64.
 // Every wait is bounded: on expiry the role raises a CTA flag and a status word, every role leaves its
 // loop, in-flight copies are drained and the tensor memory is freed.
 #include <cuda.h>
+#include <cstdio>
+#include <cstdlib>
 
 #include "gemv_common.cuh"
 
@@ -34,32 +35,40 @@ namespace infr {
 namespace {
 
 constexpr int kTM = 128, kTN = 64;
-constexpr int kStages = 3;                    // activation stages
+constexpr int kStages = 5;
 constexpr int kPlanes = 20;                   // activation planes per super-block: 16 code planes + B1[2] + B2[2]
-constexpr int kStageBytes = kPlanes * kTN * 16;
-constexpr int kABuf = 2 * 16 * kTM * 16;      // {lo, hi} x 16 planes x 128 rows x 16 B: one whole super-block
+constexpr int kRawBytes = kTM * 144, kActBytes = kPlanes * kTN * 16;
+constexpr int kStageBytes = kRawBytes + kActBytes;
 constexpr int kMinBytes = 4 * kTM * 16;       // A1 planes [2], A2 planes [2]
 constexpr int kRing = 4;                      // depth of the row-scale ring read by the epilogue
-constexpr int kSmem = kStages * kStageBytes + 2 * (kABuf + kMinBytes) + kRing * kTM * 4;
-constexpr int kThreadsWs = 19 * 32;
+constexpr int kSmem = kStages * kStageBytes + 2 * kMinBytes + kRing * kTM * 4;
+constexpr int kThreadsWs = 18 * 32;
 constexpr uint32_t kSpin = 1u << 22;
+// tensor-memory columns
+constexpr uint32_t kColMin = 256, kColA = 320, kSlotCols = 64, kSlots = 3;
 
-// barrier indices: FULL[stage] (TMA bytes), AREADY[buffer] (8 unpack warps), DONE[j % 4] (the job's commit),
-// ACCFREE[accumulator] (8 epilogue warps), DRAIN[issuer]
-constexpr int B_FULL = 0, B_AREADY = B_FULL + kStages, B_DONE = B_AREADY + 2, B_ACCFREE = B_DONE + 4, B_DRAIN = B_ACCFREE + 2,
-              B_COUNT = B_DRAIN + 2;
+// barrier indices: FULL[stage] (TMA bytes), DONE[stage] (the job's last commit), AREADY/AFREE[operand slot],
+// ACCFREE[accumulator] (8 epilogue warps), MINFREE (8 epilogue warps), DRAIN
+constexpr int B_FULL = 0, B_DONE = B_FULL + kStages, B_AREADY = B_DONE + kStages, B_AFREE = B_AREADY + kSlots,
+              B_ACCFREE = B_AFREE + kSlots, B_MINFREE = B_ACCFREE + 2, B_DRAIN = B_MINFREE + 1, B_COUNT = B_DRAIN + 1;
 
 __device__ __forceinline__ uint32_t su32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint64_t mk_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
     return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46);
 }
-__device__ __forceinline__ void mma_i8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+__device__ __forceinline__ void mma_i8_ta(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d),
-        "l"(a), "l"(b), "r"(idesc), "r"(acc), "r"(0)
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d),
+        "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc), "r"(0)
         : "memory");
 }
+__device__ __forceinline__ void tst8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tst_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void mma_tf32(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -146,6 +155,13 @@ __global__ void mmq_ws_prep_kernel(const int8_t *__restrict__ qs, const int32_t 
     d8t[(size_t)b * m_pad + tok] = d8;
 }
 
+
+#ifdef MMQ_TRACE
+__device__ long long g_trace[8][64][4];
+#define TR(role, j, k) do { if (blockIdx.x == 0 && (j) >= 32 && (j) < 96 && (threadIdx.x & 31) == 0) g_trace[role][(j) - 32][k] = clock64(); } while (0)
+#else
+#define TR(role, j, k)
+#endif
 namespace {
 
 __device__ __forceinline__ bool wait_plain(uint32_t bar, uint32_t parity, uint32_t limit) {
@@ -159,19 +175,14 @@ __device__ __forceinline__ bool wait_plain(uint32_t bar, uint32_t parity, uint32
     }
     return false;
 }
-__device__ __forceinline__ uint4 ldg_stream(const uint8_t *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
 
 __global__ void __launch_bounds__(kThreadsWs, 1)
-    mmq_ws_kernel(const __grid_constant__ CUtensorMap map_q, const uint8_t *__restrict__ W, const float *__restrict__ d8t,
-                  float *__restrict__ C, int m, int m_pad, int in_f, int out_f, uint32_t *__restrict__ status) {
+    mmq_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q,
+                  const float *__restrict__ d8t, float *__restrict__ C, int m, int m_pad, int in_f, int out_f,
+                  uint32_t *__restrict__ status) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t *stage0 = smem;                              // [kStages][kStageBytes]
-    uint8_t *abuf0 = smem + kStages * kStageBytes;       // [2][kABuf]
-    uint8_t *minbuf0 = abuf0 + 2 * kABuf;                // [2][kMinBytes]
+    uint8_t *stage0 = smem;                                              // [kStages]{raw rows, activation planes}
+    uint8_t *minbuf0 = smem + kStages * kStageBytes;                     // [2][kMinBytes]
     float *dwring = reinterpret_cast<float *>(minbuf0 + 2 * kMinBytes);  // [kRing][kTM]
     __shared__ uint64_t bars[B_COUNT];
     __shared__ uint32_t tmem_base_s;
@@ -186,7 +197,7 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
     if (tid == 0) {
         s_dead = 0;
         for (int i = 0; i < B_COUNT; i++) {
-            const int cnt = (i >= B_AREADY && i < B_AREADY + 2) ? 8 : (i >= B_ACCFREE && i < B_ACCFREE + 2) ? 8 : 1;
+            const int cnt = (i >= B_AREADY && i < B_AREADY + kSlots) ? 4 : (i >= B_ACCFREE && i <= B_MINFREE) ? 8 : 1;
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(su32(&bars[i])), "r"(cnt));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -200,25 +211,27 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
     auto bar = [&](int i) { return su32(&bars[i]); };
-    // "job j is complete" = its issuer's commit has arrived
-    auto wait_done = [&](int j) { return wait_bar(bar(B_DONE + (j & 3)), (uint32_t)((j >> 2) & 1), dead); };
 
     if (warp == 16) {
-        // ------------------------------------------------------------------ TMA producer (activation planes)
+        // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int j = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                const int tt = t / row_tiles;  // consecutive CTAs share a token tile
+                const int rt = t % row_tiles, tt = t / row_tiles;  // consecutive CTAs share a token tile
                 for (int b = 0; b < nb; b++, j++) {
                     const int s = j % kStages;
-                    if (j >= kStages && !wait_done(j - kStages)) {
+                    // the stage's previous job is complete (its operands were read by the MMAs, its rows unpacked)
+                    if (j >= kStages && !wait_bar(bar(B_DONE + s), (uint32_t)((j / kStages - 1) & 1), dead)) {
                         ok = false;
                         break;
                     }
+                    TR(0, j, 0);
+                    uint8_t *st = stage0 + (size_t)s * kStageBytes;
                     const uint32_t fb = bar(B_FULL + s);
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb), "r"(kStageBytes) : "memory");
-                    tma2(su32(stage0 + (size_t)s * kStageBytes), &map_q, tt * kTN * 4, b * kPlanes, fb);
+                    tma2(su32(st), &map_w, b * 36, rt * kTM, fb);
+                    tma2(su32(st + kRawBytes), &map_q, tt * kTN * 4, b * kPlanes, fb);
                 }
             }
             if (!ok) {
@@ -231,97 +244,104 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                     wait_plain(bar(B_FULL + k % kStages), (uint32_t)((k / kStages) & 1), 1u << 16);
             }
         }
-    } else if (warp >= 17) {
-        // ------------------------------------------------------------------ MMA issuers
-        const int me = warp - 17;
-        if (lane == 0) {
-            const uint32_t idesc_i8 = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(kTN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
-            const uint32_t idesc_tf = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
-            const uint8_t *ab = abuf0 + (size_t)me * kABuf, *mb = minbuf0 + (size_t)me * kMinBytes;
-            const uint64_t a1 = mk_desc(su32(mb), kTM * 16, 128), a2 = mk_desc(su32(mb + 2 * kTM * 16), kTM * 16, 128);
-            const uint64_t alo = mk_desc(su32(ab), kTM * 16, 128), ahi = mk_desc(su32(ab + kABuf / 2), kTM * 16, 128);
-            const uint32_t td = tmem + (uint32_t)me * 2 * kTN;
-            int j = 0, tile_i = 0;
-            bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, tile_i++) {
-                const uint32_t tmin = tmem + 256 + (uint32_t)(tile_i & 1) * 2 * kTN + (uint32_t)me * kTN;
-                bool first = true;  // this issuer's first job of the tile starts its min accumulator
-                for (int b = 0; b < nb; b++, j++) {
-                    if ((j & 1) != me) continue;
-                    const int ls = j % kStages;
-                    if (!wait_bar(bar(B_FULL + ls), (uint32_t)((j / kStages) & 1), dead) ||
-                        !wait_bar(bar(B_AREADY + me), (uint32_t)((j >> 1) & 1), dead) ||
-                        (j >= 2 && !wait_bar(bar(B_ACCFREE + me), (uint32_t)(((j >> 1) - 1) & 1), dead))) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t sB = su32(stage0 + (size_t)ls * kStageBytes);
-                    const uint64_t db0 = mk_desc(sB, kTN * 16, 128);
-#pragma unroll
-                    for (int sb = 0; sb < 8; sb++) {
-                        // sub-block sb = planes 2sb, 2sb+1: the descriptor start address field counts 16-byte units
-                        const uint64_t db = db0 + (uint64_t)(sb * 2 * kTN);
-                        mma_i8(td, alo + (uint64_t)(sb * 2 * kTM), db, idesc_i8, sb > 0 ? 1u : 0u);
-                        mma_i8(td + kTN, ahi + (uint64_t)(sb * 2 * kTM), db, idesc_i8, sb > 0 ? 1u : 0u);
-                    }
-                    const uint64_t b1 = db0 + (uint64_t)(16 * kTN), b2 = db0 + (uint64_t)(18 * kTN);
-                    mma_tf32(tmin, a1, b1, idesc_tf, first ? 0u : 1u);
-                    mma_tf32(tmin, a2, b1, idesc_tf, 1u);
-                    mma_tf32(tmin, a1, b2, idesc_tf, 1u);
-                    first = false;
-                    mma_commit(bar(B_DONE + (j & 3)));
-                }
-            }
-            if (!ok) {
-                if (!*dead) atomicExch(status, 6u);
-                *dead = 1;
-            }
-            // every issued MMA has completed before the tensor memory is freed
-            mma_commit(bar(B_DRAIN + me));
-            wait_plain(bar(B_DRAIN + me), 0u, 1u << 20);
-        }
-    } else if (warp < 8) {
-        // ------------------------------------------------------------------ unpack warps
-        const int row = tid & 127, h = tid >> 7;
-        // the thread's 80 bytes of a job's Q4_K block: header + the 64 nibble bytes of sub-blocks 4h..4h+3
-        uint4 nh = make_uint4(0, 0, 0, 0), nq[4] = {nh, nh, nh, nh};
-        auto fetch = [&](int t, int b) {
-            const int grow = (t % row_tiles) * kTM + row;
-            if (grow < out_f) {
-                const uint8_t *p = W + ((size_t)grow * nb + b) * 144;
-                nh = ldg_stream(p);
-#pragma unroll
-                for (int k = 0; k < 4; k++) nq[k] = ldg_stream(p + 16 + 64 * h + 16 * k);
-            } else {
-                nh = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                for (int k = 0; k < 4; k++) nq[k] = nh;
-            }
-        };
-        int j = 0;
+    } else if (warp == 17) {
+        // ------------------------------------------------------------------ MMA issuer
+        // One barrier operation costs its thread ~100 cycles, so the job's four waits are spread over four
+        // lanes and complete together; lane 0 then issues the job's MMAs and its three commits.
+        const uint32_t idesc_i8 = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(kTN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
+        const uint32_t idesc_tf = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
+        const uint32_t tmin = tmem + kColMin;
+        int j = 0, tile_i = 0;
         bool ok = true;
-        if ((int)blockIdx.x < n_tiles) fetch(blockIdx.x, 0);
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-            for (int b = 0; b < nb; b++, j++) {
-                const uint4 hdr = nh;
-                const uint32_t w[16] = {nq[0].x, nq[0].y, nq[0].z, nq[0].w, nq[1].x, nq[1].y, nq[1].z, nq[1].w,
-                                        nq[2].x, nq[2].y, nq[2].z, nq[2].w, nq[3].x, nq[3].y, nq[3].z, nq[3].w};
-                // next job's bytes are in flight while this one is unpacked
-                if (b + 1 < nb) fetch(t, b + 1);
-                else if (t + (int)gridDim.x < n_tiles) fetch(t + gridDim.x, 0);
-                const int bi = j & 1;
-                if (j >= 2 && !wait_bar_warp(bar(B_DONE + ((j - 2) & 3)), (uint32_t)(((j - 2) >> 2) & 1), dead)) {
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, tile_i++) {
+            for (int b = 0; b < nb && ok; b++, j++) {
+                const int s = j & 1, ls = j % kStages;
+                const int slot0 = (2 * j) % (int)kSlots, n0 = (2 * j) / (int)kSlots;
+                const int slot1 = (2 * j + 1) % (int)kSlots, n1 = (2 * j + 1) / (int)kSlots;
+                TR(1, j, 0);
+                bool mine = true;
+                if (lane == 0) mine = wait_bar(bar(B_FULL + ls), (uint32_t)((j / kStages) & 1), dead);
+                if (lane == 1 && j >= 2) mine = wait_bar(bar(B_ACCFREE + s), (uint32_t)(((j >> 1) - 1) & 1), dead);
+                if (lane == 2) mine = wait_bar(bar(B_AREADY + slot0), (uint32_t)(n0 & 1), dead);
+                if (lane == 3) mine = wait_bar(bar(B_AREADY + slot1), (uint32_t)(n1 & 1), dead);
+                // the tile's first min MMA overwrites the sums of the previous tile: the epilogue has read them
+                if (lane == 4 && b == 0 && tile_i >= 1) mine = wait_bar(bar(B_MINFREE), (uint32_t)((tile_i - 1) & 1), dead);
+                if (!__all_sync(0xffffffffu, mine)) {
                     ok = false;
                     break;
                 }
-                uint8_t *ab = abuf0 + (size_t)bi * kABuf;
+                TR(1, j, 1);
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint64_t db0 = mk_desc(su32(stage0 + (size_t)ls * kStageBytes + kRawBytes), kTN * 16, 128);
+                    const uint8_t *mb = minbuf0 + (size_t)s * kMinBytes;
+                    const uint64_t am[3] = {mk_desc(su32(mb), kTM * 16, 128), mk_desc(su32(mb + 2 * kTM * 16), kTM * 16, 128),
+                                            mk_desc(su32(mb), kTM * 16, 128)};
+                    const uint64_t bm[3] = {db0 + (uint64_t)(16 * kTN), db0 + (uint64_t)(16 * kTN), db0 + (uint64_t)(18 * kTN)};
+                    const uint32_t td = tmem + (uint32_t)s * 2 * kTN;
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const uint32_t ta = tmem + kColA + (uint32_t)(h ? slot1 : slot0) * kSlotCols;
+#pragma unroll
+                        for (int sbl = 0; sbl < 4; sbl++) {
+                            const int sb = 4 * h + sbl;
+                            // sub-block sb = activation planes 2sb, 2sb+1: the descriptor start address counts 16-byte units
+                            const uint64_t db = db0 + (uint64_t)(sb * 2 * kTN);
+                            mma_i8_ta(td, ta + (uint32_t)(sbl * 8), db, idesc_i8, sb > 0 ? 1u : 0u);
+                            mma_i8_ta(td + kTN, ta + 32 + (uint32_t)(sbl * 8), db, idesc_i8, sb > 0 ? 1u : 0u);
+                            // the three min MMAs ride between the pairs as a third accumulator chain
+                            if (h == 0 && sbl < 3) mma_tf32(tmin, am[sbl], bm[sbl], idesc_tf, (b > 0 || sbl > 0) ? 1u : 0u);
+                        }
+                        mma_commit(bar(B_AFREE + (h ? slot1 : slot0)));
+                    }
+                    mma_commit(bar(B_DONE + ls));
+                }
+                __syncwarp();
+                TR(1, j, 2);
+            }
+        }
+        if (!ok && lane == 0) {
+            if (!*dead) atomicExch(status, 6u);
+            *dead = 1;
+        }
+        if (lane == 0) {
+            // every issued MMA has completed before the tensor memory is freed
+            mma_commit(bar(B_DRAIN));
+            wait_plain(bar(B_DRAIN), 0u, 1u << 20);
+        }
+    } else if (warp < 8) {
+        // ------------------------------------------------------------------ unpack warps
+        const int quarter = warp & 3, h = warp >> 2, row = quarter * 32 + lane;
+        const uint32_t tl = tmem + ((uint32_t)(quarter * 32) << 16) + kColA;
+        int j = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            for (int b = 0; b < nb; b++, j++) {
+                const int ls = j % kStages;
+                const int r = 2 * j + h, slot = r % (int)kSlots, n = r / (int)kSlots;
+                if (quarter == 0) TR(2 + h, j, 0);
+                // two waits on two lanes: the rows have landed, the operand slot's previous MMAs are complete
+                bool mine = true;
+                if (lane == 0) mine = wait_bar(bar(B_FULL + ls), (uint32_t)((j / kStages) & 1), dead);
+                if (lane == 1 && n >= 1) mine = wait_bar(bar(B_AFREE + slot), (uint32_t)((n - 1) & 1), dead);
+                if (!__all_sync(0xffffffffu, mine)) {
+                    ok = false;
+                    break;
+                }
+                if (quarter == 0) TR(2 + h, j, 1);
+                const uint8_t *blk = stage0 + (size_t)ls * kStageBytes + (size_t)row * 144;
+                const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+                const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 64 * h), q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 64 * h);
+                const uint4 q2 = *reinterpret_cast<const uint4 *>(blk + 48 + 64 * h), q3 = *reinterpret_cast<const uint4 *>(blk + 64 + 64 * h);
+                const uint32_t w[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w, q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
                 uint32_t sc[2], mn[2];
                 sc[0] = hdr.y & 0x3F3F3F3Fu;
                 mn[0] = hdr.z & 0x3F3F3F3Fu;
                 sc[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
                 mn[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
                 const uint32_t sc4 = sc[h];  // scales of sub-blocks 4h..4h+3
+                tc_fence_after();
+                const uint32_t ts = tl + (uint32_t)slot * kSlotCols;
 #pragma unroll
                 for (int pp = 0; pp < 2; pp++) {
 #pragma unroll
@@ -336,11 +356,9 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                             lo[i] = nib * f_lo;  // bytes <= 15 * 7: no carry between bytes
                             hi[i] = nib * f_hi;
                         }
-                        uint8_t *pl = ab + ((size_t)(2 * (4 * h + sbl)) * kTM + row) * 16;
-                        *reinterpret_cast<uint4 *>(pl) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                        *reinterpret_cast<uint4 *>(pl + kTM * 16) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-                        *reinterpret_cast<uint4 *>(pl + kABuf / 2) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                        *reinterpret_cast<uint4 *>(pl + kABuf / 2 + kTM * 16) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                        // column c of a lane = K elements 4c..4c+3 of the row: 8 columns per sub-block
+                        tst8(ts + (uint32_t)(sbl * 8), lo);
+                        tst8(ts + 32 + (uint32_t)(sbl * 8), hi);
                     }
                 }
                 if (h == 0) {
@@ -353,16 +371,20 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                         p1[s8] = __float_as_uint(v) & 0xFFFFE000u;
                         p2[s8] = __float_as_uint(v - __uint_as_float(p1[s8]));
                     }
-                    uint8_t *mp = minbuf0 + (size_t)bi * kMinBytes + (size_t)row * 16;
+                    uint8_t *mp = minbuf0 + (size_t)(j & 1) * kMinBytes + (size_t)row * 16;
                     *reinterpret_cast<uint4 *>(mp) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
                     *reinterpret_cast<uint4 *>(mp + kTM * 16) = make_uint4(p1[4], p1[5], p1[6], p1[7]);
                     *reinterpret_cast<uint4 *>(mp + 2 * kTM * 16) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
                     *reinterpret_cast<uint4 *>(mp + 3 * kTM * 16) = make_uint4(p2[4], p2[5], p2[6], p2[7]);
                     dwring[(j % kRing) * kTM + row] = dw;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (quarter == 0) TR(2 + h, j, 2);
+                tst_wait();
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) bar_arrive(bar(B_AREADY + bi));
+                if (lane == 0) bar_arrive(bar(B_AREADY + slot));
+                if (quarter == 0) TR(2 + h, j, 3);
             }
         }
         if (!ok) {
@@ -380,7 +402,6 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, tile_i++) {
             const int rt = t % row_tiles, tt = t / row_tiles;
             const float4 *d8p = reinterpret_cast<const float4 *>(d8t + (size_t)tt * kTN + half * 32);
-            const int j_tile = j;
 #pragma unroll
             for (int i = 0; i < 32; i++) acc[i] = 0.f;
             for (int b = 0; b < nb; b++, j++) {
@@ -388,10 +409,12 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 float4 dd[4];
 #pragma unroll
                 for (int i4 = 0; i4 < 4; i4++) dd[i4] = __ldg(d8p + (size_t)b * (m_pad / 4) + i4);
-                if (!wait_bar_warp(bar(B_DONE + (j & 3)), (uint32_t)((j >> 2) & 1), dead)) {
+                if (warp == 8) TR(4, j, 0);
+                if (!wait_bar_warp(bar(B_DONE + j % kStages), (uint32_t)((j / kStages) & 1), dead)) {
                     ok = false;
                     break;
                 }
+                if (warp == 8) TR(4, j, 1);
                 tc_fence_after();
                 const float dw = dwring[(j % kRing) * kTM + row];
 #pragma unroll
@@ -404,11 +427,11 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                         for (int i4 = 0; i4 < 4; i4++) dd[i4] = __ldg(d8p + (size_t)b * (m_pad / 4) + 4 + i4);
                     }
                     tld_wait();
-                    // the last job of a tile keeps its accumulator until the tile's min sums are read
-                    if (c == 1 && b + 1 < nb) {
+                    if (c == 1) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) bar_arrive(bar(B_ACCFREE + s));
+                        if (warp == 8) TR(4, j, 2);
                     }
 #pragma unroll
                     for (int i4 = 0; i4 < 4; i4++) {
@@ -422,29 +445,26 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                     }
                 }
             }
+            if (warp == 8) TR(4, j - 1, 3);
             if (!ok) break;
-            // tile end: subtract the min sums of the issuers that ran jobs of this tile, then store
+            // tile end: subtract the min sums and store
             const int grow = rt * kTM + row;
-            const bool use0 = nb >= 2 || (j_tile & 1) == 0, use1 = nb >= 2 || (j_tile & 1) == 1;
 #pragma unroll
             for (int c = 0; c < 2; c++) {
-                uint32_t m0[16], m1[16];
-                const uint32_t tm = tlane + (uint32_t)(256 + (tile_i & 1) * 2 * kTN + c * 16);
-                tld16(tm, m0);
-                tld16(tm + kTN, m1);
+                uint32_t mv[16];
+                tld16(tlane + kColMin + (uint32_t)(c * 16), mv);
                 tld_wait();
+                if (c == 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) bar_arrive(bar(B_MINFREE));
+                }
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
                     const int tok = tt * kTN + half * 32 + c * 16 + i;
-                    float v = acc[c * 16 + i];
-                    if (use0) v -= __uint_as_float(m0[i]);
-                    if (use1) v -= __uint_as_float(m1[i]);
-                    if (grow < out_f && tok < m) C[(size_t)tok * out_f + grow] = v;
+                    if (grow < out_f && tok < m) C[(size_t)tok * out_f + grow] = acc[c * 16 + i] - __uint_as_float(mv[i]);
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) bar_arrive(bar(B_ACCFREE + ((j - 1) & 1)));
         }
         if (!ok) {
             if (!*dead) atomicExch(status, 4u);
@@ -484,8 +504,16 @@ cudaError_t launch_mmq_ws_q4k(const uint8_t *w, const Q8Dev &a, void *records, f
     const int nb = in_f / 256, m_pad = (m + kTN - 1) / kTN * kTN;
     const int n_rec = m * nb;
     mmq_ws_prep_kernel<<<(n_rec + 255) / 256, 256, 0, st>>>(a.qs, a.sums, a.d, m, m_pad, nb, static_cast<uint4 *>(records));
-    CUtensorMap map_q;
+    CUtensorMap map_w, map_q;
     const cuuint32_t one2[2] = {1, 1};
+    {
+        const cuuint64_t gdim[2] = {(cuuint64_t)nb * 36, (cuuint64_t)out_f};
+        const cuuint64_t gstr[1] = {(cuuint64_t)nb * 144};
+        const cuuint32_t box[2] = {36, (cuuint32_t)kTM};
+        if (enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(w), gdim, gstr, box, one2, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
     {
         // activation planes [nb * 20][m][16 B] as rows of m * 4 words: a tile is 20 rows of 256 words
         const cuuint64_t gdim[2] = {(cuuint64_t)m * 4, (cuuint64_t)nb * kPlanes};
@@ -500,7 +528,16 @@ cudaError_t launch_mmq_ws_q4k(const uint8_t *w, const Q8Dev &a, void *records, f
     if (e != cudaSuccess) return e;
     const int n_tiles = ((out_f + kTM - 1) / kTM) * ((m + kTN - 1) / kTN);
     const int grid = n_tiles < dev.sm_count ? n_tiles : dev.sm_count;
-    mmq_ws_kernel<<<grid, kThreadsWs, kSmem, st>>>(map_q, w, d8t, c, m, m_pad, in_f, out_f, status);
+    mmq_ws_kernel<<<grid, kThreadsWs, kSmem, st>>>(map_w, map_q, d8t, c, m, m_pad, in_f, out_f, status);
+#ifdef MMQ_TRACE
+    if (getenv("INFR_MMQ_TRACE")) {
+        cudaDeviceSynchronize();
+        static long long h[8][64][4];
+        cudaMemcpyFromSymbol(h, g_trace, sizeof(h));
+        for (int r = 0; r < 5; r++)
+            for (int j = 0; j < 64; j++) fprintf(stderr, "TR %d %d %lld %lld %lld %lld\n", r, j + 32, h[r][j][0], h[r][j][1], h[r][j][2], h[r][j][3]);
+    }
+#endif
     return cudaGetLastError();
 }
 

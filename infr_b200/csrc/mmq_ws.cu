@@ -107,6 +107,25 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
     return false;
 }
 
+// Warp-collective wait on up to 32 barriers at once: every lane names its own barrier (or need = false) and
+// all lanes poll in the same instruction, so k waits cost the latency of one.
+__device__ __forceinline__ bool wait_multi(uint32_t bar, uint32_t parity, bool need, volatile int *dead) {
+    bool pending = need;
+    for (uint32_t i = 0; i < kSpin; i++) {
+        if (pending) {
+            uint32_t ok;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok)
+                         : "r"(bar), "r"(parity)
+                         : "memory");
+            pending = !ok;
+        }
+        if (!__any_sync(0xffffffffu, pending)) return true;
+        if ((i & 1023u) == 1023u && *dead) return false;
+    }
+    return false;
+}
+
 // Warp-collective form: lane 0 polls, the result is broadcast (the shuffle also orders memory in the warp).
 __device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, volatile int *dead) {
     int ok = 0;
@@ -259,14 +278,15 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 const int slot0 = (2 * j) % (int)kSlots, n0 = (2 * j) / (int)kSlots;
                 const int slot1 = (2 * j + 1) % (int)kSlots, n1 = (2 * j + 1) / (int)kSlots;
                 TR(1, j, 0);
-                bool mine = true;
-                if (lane == 0) mine = wait_bar(bar(B_FULL + ls), (uint32_t)((j / kStages) & 1), dead);
-                if (lane == 1 && j >= 2) mine = wait_bar(bar(B_ACCFREE + s), (uint32_t)(((j >> 1) - 1) & 1), dead);
-                if (lane == 2) mine = wait_bar(bar(B_AREADY + slot0), (uint32_t)(n0 & 1), dead);
-                if (lane == 3) mine = wait_bar(bar(B_AREADY + slot1), (uint32_t)(n1 & 1), dead);
+                uint32_t wb = 0, wp = 0;
+                bool need = false;
+                if (lane == 0) wb = bar(B_FULL + ls), wp = (uint32_t)((j / kStages) & 1), need = true;
+                if (lane == 1) wb = bar(B_ACCFREE + s), wp = (uint32_t)(((j >> 1) - 1) & 1), need = j >= 2;
+                if (lane == 2) wb = bar(B_AREADY + slot0), wp = (uint32_t)(n0 & 1), need = true;
+                if (lane == 3) wb = bar(B_AREADY + slot1), wp = (uint32_t)(n1 & 1), need = true;
                 // the tile's first min MMA overwrites the sums of the previous tile: the epilogue has read them
-                if (lane == 4 && b == 0 && tile_i >= 1) mine = wait_bar(bar(B_MINFREE), (uint32_t)((tile_i - 1) & 1), dead);
-                if (!__all_sync(0xffffffffu, mine)) {
+                if (lane == 4) wb = bar(B_MINFREE), wp = (uint32_t)((tile_i - 1) & 1), need = b == 0 && tile_i >= 1;
+                if (!wait_multi(wb, wp, need, dead)) {
                     ok = false;
                     break;
                 }
@@ -321,10 +341,11 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 const int r = 2 * j + h, slot = r % (int)kSlots, n = r / (int)kSlots;
                 if (quarter == 0) TR(2 + h, j, 0);
                 // two waits on two lanes: the rows have landed, the operand slot's previous MMAs are complete
-                bool mine = true;
-                if (lane == 0) mine = wait_bar(bar(B_FULL + ls), (uint32_t)((j / kStages) & 1), dead);
-                if (lane == 1 && n >= 1) mine = wait_bar(bar(B_AFREE + slot), (uint32_t)((n - 1) & 1), dead);
-                if (!__all_sync(0xffffffffu, mine)) {
+                uint32_t wb = 0, wp = 0;
+                bool need = false;
+                if (lane == 0) wb = bar(B_FULL + ls), wp = (uint32_t)((j / kStages) & 1), need = true;
+                if (lane == 1) wb = bar(B_AFREE + slot), wp = (uint32_t)((n - 1) & 1), need = n >= 1;
+                if (!wait_multi(wb, wp, need, dead)) {
                     ok = false;
                     break;
                 }

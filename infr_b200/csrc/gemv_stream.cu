@@ -22,6 +22,8 @@
 //
 // Every mbarrier wait is bounded: when the limit is hit the warp records a status word for the host,
 // stops claiming work, waits (bounded again) for the copies it still has in flight and returns.
+#include <cstdlib>
+
 #include "gemv_common.cuh"
 
 namespace infr {
@@ -420,11 +422,23 @@ cudaError_t launch_stream_m(int dt, const uint8_t *w, const Q8Dev &a, float *y, 
     return launch_stream_dt<DT_Q2_0, M>(w, a, y, m, in_f, out_f, dev, status, st);
 }
 
+bool getenv_flag(const char *name) {
+    const char *v = getenv(name);
+    return v && v[0] && v[0] != '0';
+}
+
 }  // namespace
 
 cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
                                const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
     if (m < 1 || m > 8 || (dt != DT_Q4K && dt != DT_Q6K && dt != DT_Q2_0)) return cudaErrorInvalidValue;
+    if (dt == DT_Q2_0 && in_f % 512 == 0 && a.gran == 32 && !getenv_flag("INFR_DEV_Q2_STREAM")) {
+        // rows of whole 512-element chunks take the matrix-unit kernel; it declines shapes whose staged
+        // activations do not fit, and those fall through to the byte-dot kernel below
+        const cudaError_t e = launch_gemv_q2_mma(w, a, y, m, in_f, out_f, dev, status, st);
+        if (e != cudaErrorInvalidValue) return e;
+        cudaGetLastError();
+    }
     if (m == 1) return launch_stream_m<1>(dt, w, a, y, m, in_f, out_f, dev, status, st);
     if (m == 2) return launch_stream_m<2>(dt, w, a, y, m, in_f, out_f, dev, status, st);
     if (m <= 4) return launch_stream_m<4>(dt, w, a, y, m, in_f, out_f, dev, status, st);

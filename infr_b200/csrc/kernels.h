@@ -48,6 +48,10 @@ cudaError_t launch_gemv_q8(int dt, const uint8_t *w, const Q8Dev &a, float *y, i
 // is a device-visible word the kernel sets non-zero if a bounded wait expires.
 cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
                                const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
+// Q2_0, m <= 8, rows of whole 512-element chunks, on the warp-level int8 matrix unit (activations quantised
+// per 32).  cudaErrorInvalidValue = shape not taken (the caller uses the byte-dot kernel).
+cudaError_t launch_gemv_q2_mma(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f, const DeviceInfo &dev,
+                               uint32_t *status, cudaStream_t st);
 // Q4_K, m <= 8, on the warp-level int8 matrix unit.  Exactly one of `a` (pre-quantised rows) and `x`
 // (f32 rows, quantised inside the kernel) is non-null.
 cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,

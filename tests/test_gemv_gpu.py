@@ -59,7 +59,10 @@ SHAPES = [
     (Q6K, 768, 24),
     (Q6K, 4096, 14336),  # decode sweep: W 14336 x 4096 in Q6_K
     (Q2_0, 704, 16),     # 11 blocks: not a multiple of 8 blocks nor of 256 elements
-    (Q2_0, 14336, 4096), # decode sweep: ternary W 4096 x 14336
+    (Q2_0, 14336, 4096), # decode sweep: ternary W 4096 x 14336 (matrix-unit kernel, 28 chunks over 4 warps)
+    (Q2_0, 512, 40),     # one 512-element chunk, partial last 16-row tile (16 warps, most of them idle)
+    (Q2_0, 2048, 6408),  # many tiles: four warps per tile, one chunk each
+    (Q2_0, 4096, 2500),  # eight warps per tile, partial last tile
 ]
 
 

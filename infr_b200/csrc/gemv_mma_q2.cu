@@ -23,6 +23,8 @@ constexpr int kRows = 16;
 constexpr int kMaxSlots = 4;
 constexpr int kChunkBytes = 144, kChunkElems = 512, kChunkGroups = 16;
 constexpr int kSlotBytes = kRows * kChunkBytes;
+constexpr int kLaneStride = 136;               // staged bytes of one K lane of a chunk (128 + 8: the four lanes hit distinct banks)
+constexpr int kStagedChunk = 4 * kLaneStride;  // staged bytes of one chunk of one token
 constexpr uint32_t kSpinQ2 = 1u << 22;
 
 __device__ __forceinline__ uint32_t sm32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -56,8 +58,9 @@ struct Q2Geom {
     int slots;  // ring slots per warp
 };
 
-// Shared memory: rings [KW][slots][16 x 144 B]; staged activations per token n and chunk c: codes 512 B
-// at (n*nch + c)*512, the 8 bytes of group s that lane t feeds at t*128 + s*8; d8 and bsum [n][nch*16].
+// Shared memory: rings [KW][slots][16 x 144 B]; staged activations per token n and chunk c: codes 544 B
+// at (n*nch + c)*544, the 8 bytes of group s that lane t feeds at t*136 + s*8; d8 and bsum [group][8 tokens]
+// (a lane's two result columns are neighbours).
 template <int M, int KW>
 __global__ void __launch_bounds__(KW * 32, 16 / KW)
     gemv_q2_mma_kernel(const __grid_constant__ CUtensorMap tmap, Q8Dev a, float *__restrict__ y, int m, int in_f, int out_f,
@@ -66,9 +69,9 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
     const int nch = geo.nch, S = geo.slots, ng = nch * kChunkGroups;
     uint8_t *rings = smem;
     uint8_t *s_codes = smem + (size_t)KW * S * kSlotBytes;
-    float *s_d8 = reinterpret_cast<float *>(s_codes + (size_t)M * nch * kChunkElems);
-    int32_t *s_bs = reinterpret_cast<int32_t *>(s_d8 + (size_t)M * ng);
-    float *s_part = reinterpret_cast<float *>(s_bs + (size_t)M * ng);       // [2][KW][16][8]
+    float *s_d8 = reinterpret_cast<float *>(s_codes + (size_t)M * nch * kStagedChunk);  // [ng][8]
+    int32_t *s_bs = reinterpret_cast<int32_t *>(s_d8 + (size_t)8 * ng);               // [ng][8]
+    float *s_part = reinterpret_cast<float *>(s_bs + (size_t)8 * ng);                  // [2][KW][16][8]
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_part + 2 * KW * 128);  // [KW][kMaxSlots]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -124,12 +127,14 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                 const int c = u >> 6, uu = u & 63, s = uu >> 2, tt = uu & 3;
                 // bytes e0..e7 -> [e0 e4 e1 e5], [e2 e6 e3 e7]: the order spread8 gives the codes
                 const uint2 pv = make_uint2(__byte_perm(v.x, v.y, 0x5140), __byte_perm(v.x, v.y, 0x7362));
-                *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nch + c) * kChunkElems + tt * 128 + s * 8) = pv;
+                *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nch + c) * kStagedChunk + tt * kLaneStride + s * 8) = pv;
             }
-            for (int i = threadIdx.x; i < ng; i += KW * 32) {
-                s_d8[n * ng + i] = on ? a.d[(size_t)n * ng + i] : 0.f;
-                s_bs[n * ng + i] = on ? a.sums[(size_t)n * ng + i] : 0;
-            }
+        }
+        for (int i = threadIdx.x; i < ng * 8; i += KW * 32) {
+            const int gi = i >> 3, n = i & 7;
+            const bool on = n < m;
+            s_d8[i] = on ? a.d[(size_t)n * ng + gi] : 0.f;
+            s_bs[i] = on ? a.sums[(size_t)n * ng + gi] : 0;
         }
     }
     __syncthreads();
@@ -150,7 +155,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
             if (!dead) {
                 const int c = c0 + ci;
                 const uint8_t *r0 = ring + (size_t)slot * kSlotBytes + (size_t)g * kChunkBytes, *r1 = r0 + 8 * kChunkBytes;
-                const uint8_t *bp = s_codes + (size_t)(gt * nch + c) * kChunkElems + t * 128;
+                const uint8_t *bp = s_codes + (size_t)(gt * nch + c) * kStagedChunk + t * kLaneStride;
 #pragma unroll
                 for (int bq = 0; bq < 8; bq++) {
                     const float d0 = h2f(*reinterpret_cast<const unsigned short *>(r0 + bq * 18));
@@ -166,18 +171,15 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                         spread8(x1, a1, a3);
                         int pr[4];
                         mma_q2(pr, a0, a1, a2, a3, bv.x, bv.y);
+                        // scales and sums of the lane's two result columns (zero for absent tokens: no branch)
                         const int gi = c * kChunkGroups + s;
-                        if (n0 < M) {
-                            const float e = s_d8[n0 * ng + gi];
-                            const int bs = s_bs[n0 * ng + gi];
-                            accf[0] = fmaf(d0 * e, (float)(pr[0] - bs), accf[0]);
-                            accf[2] = fmaf(d1 * e, (float)(pr[2] - bs), accf[2]);
-                        }
-                        if (n1 < M) {
-                            const float e = s_d8[n1 * ng + gi];
-                            const int bs = s_bs[n1 * ng + gi];
-                            accf[1] = fmaf(d0 * e, (float)(pr[1] - bs), accf[1]);
-                            accf[3] = fmaf(d1 * e, (float)(pr[3] - bs), accf[3]);
+                        const float2 e = *reinterpret_cast<const float2 *>(s_d8 + gi * 8 + n0);
+                        const int2 bs = *reinterpret_cast<const int2 *>(s_bs + gi * 8 + n0);
+                        accf[0] = fmaf(d0 * e.x, (float)(pr[0] - bs.x), accf[0]);
+                        accf[2] = fmaf(d1 * e.x, (float)(pr[2] - bs.x), accf[2]);
+                        if (M > 1) {
+                            accf[1] = fmaf(d0 * e.y, (float)(pr[1] - bs.y), accf[1]);
+                            accf[3] = fmaf(d1 * e.y, (float)(pr[3] - bs.y), accf[3]);
                         }
                     }
                 }
@@ -230,7 +232,7 @@ cudaError_t launch_cfg(const uint8_t *w, const Q8Dev &a, float *y, int m, int in
     geo.nch = in_f / kChunkElems;
     geo.cpw = (geo.nch + KW - 1) / KW;
     const size_t ng = (size_t)geo.nch * kChunkGroups;
-    const size_t fixed = (size_t)M * in_f + (size_t)M * ng * 8 + (size_t)2 * KW * 128 * 4 + (size_t)KW * kMaxSlots * 8 + 64;
+    const size_t fixed = (size_t)M * geo.nch * kStagedChunk + ng * 64 + (size_t)2 * KW * 128 * 4 + (size_t)KW * kMaxSlots * 8 + 64;
     const size_t per_slot = (size_t)KW * kSlotBytes;
     if (fixed + 2 * per_slot > (size_t)dev.max_smem_optin - 1024) return cudaErrorInvalidValue;
     int per_sm = 16 / KW;
@@ -272,14 +274,12 @@ template <int M>
 cudaError_t launch_m(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f, const DeviceInfo &dev,
                      uint32_t *status, cudaStream_t st) {
     const int nch = in_f / kChunkElems, tiles = (out_f + kRows - 1) / kRows;
-    auto need = [&](int kw) { return (size_t)M * in_f * 5 / 4 + (size_t)2 * kw * 512 + (size_t)kw * kMaxSlots * 8 + 64 + (size_t)2 * kw * kSlotBytes; };
+    auto need = [&](int kw) { return (size_t)M * nch * kStagedChunk + (size_t)nch * kChunkGroups * 64 + (size_t)2 * kw * 512 + (size_t)kw * kMaxSlots * 8 + 64 + (size_t)2 * kw * kSlotBytes; };
     // as for Q4_K: few tiles -> more warps split a tile's K; many tiles -> four warps per tile
     int kw = tiles > 2 * dev.sm_count ? 4 : (tiles > dev.sm_count ? 8 : 16);
     while (kw < 16 && need(kw) > (size_t)dev.max_smem_optin / (16 / kw) - 2048) kw *= 2;
     while (kw > 4 && kw > nch) kw /= 2;
     while (kw > 4 && need(kw) > (size_t)dev.max_smem_optin - 1024) kw /= 2;
-    // an uneven K split leaves warps idle: prefer a split that divides the chunk count
-    if (kw == 8 && nch % 8 != 0 && nch % 4 == 0 && need(4) <= (size_t)dev.max_smem_optin / 4 - 2048) kw = 4;
     if (kw == 16) return launch_cfg<M, 16>(w, a, y, m, in_f, out_f, dev, status, st);
     if (kw == 8) return launch_cfg<M, 8>(w, a, y, m, in_f, out_f, dev, status, st);
     return launch_cfg<M, 4>(w, a, y, m, in_f, out_f, dev, status, st);

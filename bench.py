@@ -254,6 +254,66 @@ def _moe_case(be, infr_b200, steps, warmup):
     return res
 
 
+def _decode_linears_case(be, infr_b200, batch, steps, warmup):
+    """The Linear ops of one Llama-3-8B-shaped decode step in the Q4_K_M mix (32 layers: q, k, o, gate, up in Q4_K,
+    v and down in Q6_K; output head in Q6_K), every layer on its own device copy of the weights (4.9 GB, far
+    beyond L2), captured in one CUDA graph.  Attention, norms and RoPE are not part of this path yet, so the
+    figure is the matmul share of a decode step.  Weight bytes are random valid blocks."""
+    from infr_b200 import synth
+
+    Q4K, Q6K = infr_b200.Q4K, infr_b200.Q6K
+    n_layer, h, kv, ff, vocab = 32, 4096, 1024, 14336, 128256
+    shapes = [("wq", Q4K, h, h), ("wk", Q4K, kv, h), ("wv", Q6K, kv, h), ("wo", Q4K, h, h),
+              ("gate", Q4K, ff, h), ("up", Q4K, ff, h), ("down", Q6K, h, ff)]
+    masters = {name: be.from_numpy(synth.random_blocks(dt, o * i, 200 + k), infr_b200.USAGE_WEIGHTS)
+               for k, (name, dt, o, i) in enumerate(shapes)}
+    layers, total_bytes = [], 0
+    for _ in range(n_layer):
+        bufs = {}
+        for name, dt, o, i in shapes:
+            nbytes = o * i // synth.BLOCK_ELEMS[dt] * synth.BLOCK_BYTES[dt]
+            b = be.alloc_uninit(nbytes, infr_b200.USAGE_WEIGHTS)
+            be.copy_buffer(masters[name], b, nbytes)
+            bufs[name] = b
+            total_bytes += nbytes
+        layers.append(bufs)
+    head_bytes = vocab * h // 256 * 210
+    head = be.from_numpy(synth.random_blocks(Q6K, vocab * h, 299), infr_b200.USAGE_WEIGHTS)
+    total_bytes += head_bytes
+    xh = be.from_numpy(synth.normal(31, (batch, h)))
+    xf = be.from_numpy(synth.normal(32, (batch, ff)))
+    yh, ykv, yff, ylog = be.alloc(batch * h * 4), be.alloc(batch * kv * 4), be.alloc(batch * ff * 4), be.alloc(batch * vocab * 4)
+
+    def step():
+        n = 0
+        for L in layers:
+            for name, dt, o, i in shapes:
+                src = xf if i == ff else xh
+                dst = yff if o == ff else (ykv if o == kv else yh)
+                be.linear(dt, L[name], src, dst, batch, i, o)
+                n += 1
+        be.linear(Q6K, head, xh, ylog, batch, h, vocab)
+        return n + 1
+
+    step()  # sizes the context scratch before capture
+    be.sync()
+    l0 = be.launch_count()
+    be.capture_begin()
+    n_linear = step()
+    graph = be.capture_end()
+    kernels = be.launch_count() - l0
+    ms = _time_graph(be, graph, steps, warmup)
+    us = ms * 1e3 / steps
+    res = {"workload": f"Linear ops of an 8B-shape decode step, batch {batch}: {n_linear} Linears, Q4_K_M mix "
+                       f"(v/down/head Q6_K), {total_bytes / 1e9:.2f} GB of weights, one CUDA graph",
+           "us_per_step": us, "tok_per_s_matmul_only": batch / (us * 1e-6), "weights_gbs": total_bytes / (us * 1e-6) / 1e9,
+           "kernels_per_step": kernels, "not_included": "attention, norms, RoPE, sampling (not built)"}
+    graph.close()
+    for b in [head, xh, xf, yh, ykv, yff, ylog] + list(masters.values()) + [b for L in layers for b in L.values()]:
+        b.close()
+    return res
+
+
 # ------------------------------------------------------------------------------------------------
 def run_b200(args):
     import infr_b200
@@ -368,6 +428,7 @@ def run_b200(args):
         out["sweep"] = sweep
         out["mmq"] = _mmq_case(be, infr_b200, 512, 4096, 14336, 5, 20, 3)
         out["moe"] = _moe_case(be, infr_b200, 20, 3)
+        out["decode_linears"] = [_decode_linears_case(be, infr_b200, b, 10, 3) for b in (1, 32)]
 
     if rank == 0 and world == 1 and not args.no_cpu:
         out["cpu_baseline"] = _cpu_baseline(w, x, budget_s=10.0)
@@ -389,6 +450,11 @@ def run_profile_case(args):
     if name == "moe":
         be = infr_b200.CudaBackend(device=0)
         print(json.dumps(_moe_case(be, infr_b200, args.steps, 2)))
+        be.close()
+        return
+    if name == "decode":  # decode:0:0:BATCH — the Linear ops of an 8B-shape decode step
+        be = infr_b200.CudaBackend(device=0)
+        print(json.dumps(_decode_linears_case(be, infr_b200, int(m), args.steps, 2)))
         be.close()
         return
     if name == "mmq":  # mmq:OUT_F:IN_F:M — the prefill GEMM (Linear with m > 8)

@@ -287,11 +287,29 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
             Q8Dev a;
             Status s = quantize_for(dtype, xr, mm, in_f, &a);
             if (!s.ok()) return s;
-            s = cuda_status(gemv_impl_ == 1 ? launch_gemv_q8(dtype, w, a, yr, (int)mm, (int)in_f, (int)out_f, nullptr, dev_, stream_)
-                                            : launch_gemv_stream(dtype, w, a, yr, (int)mm, (int)in_f, (int)out_f, dev_, status_dev_, stream_),
-                            "gemv_q8");
-            if (!s.ok()) return s;
-            launches_ += 1;
+            // rows so long that `mm` staged activation rows exceed shared memory are run in narrower batches
+            const int gran = a.gran, ngr = (int)in_f / gran;
+            uint32_t step = mm;
+            for (uint32_t t0 = 0; t0 < mm;) {
+                const uint32_t n = mm - t0 < step ? mm - t0 : step;
+                Q8Dev sub = a;
+                sub.qs = a.qs + (size_t)t0 * in_f;
+                sub.d = a.d + (size_t)t0 * ngr;
+                sub.sums = a.sums + (size_t)t0 * (in_f / 32);
+                if (a.sums16) sub.sums16 = a.sums16 + (size_t)t0 * (in_f / 16);
+                float *yt = yr + (size_t)t0 * out_f;
+                cudaError_t e = gemv_impl_ == 1 ? launch_gemv_q8(dtype, w, sub, yt, (int)n, (int)in_f, (int)out_f, nullptr, dev_, stream_)
+                                                : launch_gemv_stream(dtype, w, sub, yt, (int)n, (int)in_f, (int)out_f, dev_, status_dev_, stream_);
+                if (e == cudaErrorInvalidValue && step > 1) {
+                    cudaGetLastError();
+                    step /= 2;
+                    continue;
+                }
+                s = cuda_status(e, "gemv_q8");
+                if (!s.ok()) return s;
+                launches_ += 1;
+                t0 += n;
+            }
         }
     }
     return Status::Ok();

@@ -440,6 +440,12 @@ cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *
         if (e != cudaErrorInvalidValue) return e;
         cudaGetLastError();
     }
+    if (dt == DT_Q6K && in_f % 2048 == 0 && a.gran == 256 && a.sums16 && !getenv_flag("INFR_DEV_Q6_STREAM")) {
+        // rows whose byte length is a multiple of 16 take the matrix-unit kernel (same fall-through rule)
+        const cudaError_t e = launch_gemv_q6_mma(w, a, y, m, in_f, out_f, dev, status, st);
+        if (e != cudaErrorInvalidValue) return e;
+        cudaGetLastError();
+    }
     if (m == 1) return launch_stream_m<1>(dt, w, a, y, m, in_f, out_f, dev, status, st);
     if (m == 2) return launch_stream_m<2>(dt, w, a, y, m, in_f, out_f, dev, status, st);
     if (m <= 4) return launch_stream_m<4>(dt, w, a, y, m, in_f, out_f, dev, status, st);

@@ -52,6 +52,10 @@ cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *
 // per 32).  cudaErrorInvalidValue = shape not taken (the caller uses the byte-dot kernel).
 cudaError_t launch_gemv_q2_mma(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f, const DeviceInfo &dev,
                                uint32_t *status, cudaStream_t st);
+// Q6_K, m <= 8, rows of 8k blocks (row bytes a multiple of 16), on the warp-level int8 matrix unit; needs the
+// 16-element activation sums.  cudaErrorInvalidValue = shape not taken.
+cudaError_t launch_gemv_q6_mma(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f, const DeviceInfo &dev,
+                               uint32_t *status, cudaStream_t st);
 // Q4_K, m <= 8, on the warp-level int8 matrix unit.  Exactly one of `a` (pre-quantised rows) and `x`
 // (f32 rows, quantised inside the kernel) is non-null.
 cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,

@@ -57,7 +57,10 @@ SHAPES = [
     (Q4K, 1024, 6408),   # 401 row tiles (the last one partial): the 8-warps-per-tile configuration
     (Q4K, 14336, 1000),  # long rows: 56 super-blocks split over the warps of a tile
     (Q6K, 768, 24),
-    (Q6K, 4096, 14336),  # decode sweep: W 14336 x 4096 in Q6_K
+    (Q6K, 4096, 14336),  # decode sweep: W 14336 x 4096 in Q6_K (matrix-unit kernel: 16 blocks, odd ones off a word boundary)
+    (Q6K, 2048, 100),    # 8 blocks over 16 warps (half of them idle), partial last 16-row tile
+    (Q6K, 14336, 520),   # 56 blocks per row
+    (Q6K, 4096, 4000),   # eight warps per tile
     (Q2_0, 704, 16),     # 11 blocks: not a multiple of 8 blocks nor of 256 elements
     (Q2_0, 14336, 4096), # decode sweep: ternary W 4096 x 14336 (matrix-unit kernel, 28 chunks over 4 warps)
     (Q2_0, 512, 40),     # one 512-element chunk, partial last 16-row tile (16 warps, most of them idle)

@@ -38,6 +38,8 @@ namespace {
 
 constexpr int kTileRows = 16;
 constexpr int kMaxSlotsMma = 4;
+constexpr int kLaneBytes = 80;               // staged codes of one K lane of a super-block (64 + 16: distinct banks for 128-bit reads)
+constexpr int kStagedBytes = 4 * kLaneBytes;  // staged codes of one super-block of one token
 constexpr uint32_t kSpin = 1u << 22;
 
 __device__ __forceinline__ uint32_t s_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -103,9 +105,9 @@ struct MmaGroup {
 };
 
 // Shared-memory layout of the staged activations, per token n (0..7) and super-block b:
-//   codes  : 256 B at (n*nb + b)*256, element (sub-block s, l = 8t+i) at t*64 + s*8 + i
+//   codes  : 320 B at (n*nb + b)*320, element (sub-block s, l = 8t+i) at t*80 + s*8 + i
 //   bsplit : 16 B at (n*nb + b)*16: bytes 0..7 = low 6 bits of bsum_s, bytes 8..15 = bsum_s >> 6
-//   d8     : float [n*nb + b]
+//   d8     : float [b][8 tokens], zero for absent tokens (a lane's two result columns are neighbours)
 // KW = warps per CTA (they split K), SB = super-blocks per ring slot per row.
 template <int M, bool FUSED, int KW, int SB>
 __global__ void __launch_bounds__(KW * 32, 16 / KW)
@@ -116,9 +118,9 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
     const int nb = geo.nb, S = geo.slots;
     uint8_t *rings = smem;                                         // [kW][S][kSlotBytes]
     uint8_t *s_codes = smem + (size_t)kW * S * kSlotBytes;         // [M][nb][256]
-    uint8_t *s_bsplit = s_codes + (size_t)M * nb * 256;            // [M][nb][16]
-    float *s_d8 = reinterpret_cast<float *>(s_bsplit + (size_t)M * nb * 16);  // [M][nb], padded to 16 B
-    float *s_part = s_d8 + ((M * nb + 3) & ~3);                    // [2][kW][16][8]
+    uint8_t *s_bsplit = s_codes + (size_t)M * nb * kStagedBytes;   // [M][nb][16]
+    float *s_d8 = reinterpret_cast<float *>(s_bsplit + (size_t)M * nb * 16);  // [nb][8]
+    float *s_part = s_d8 + (size_t)nb * 8;                         // [2][kW][16][8]
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_part + 2 * kW * 128);  // [kW][kMaxSlotsMma]
     __shared__ int s_bad;
 
@@ -180,6 +182,9 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
 
     // ---- activations (from the previous kernel in the stream) ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (M < 8)  // scale columns of tokens the template does not stage
+        for (int i = threadIdx.x; i < nb * 8; i += kThreadsMma)
+            if ((i & 7) >= M) s_d8[i] = 0.f;
     if (FUSED) {
         // quantize_q8 (crates/infr-cpu/src/quant.rs:27-58) per 256-block, one warp per block
         for (int n = 0; n < M; n++)
@@ -210,14 +215,14 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
             uint2 pk;
             pk.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
             pk.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
-            *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * 256 + tt * 64 + s * 8) = pk;
+            *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * kStagedBytes + tt * kLaneBytes + s * 8) = pk;
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             if (tt == 0) {
                 s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum & 63);
                 s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
             }
-            if (lane == 0) s_d8[n * nb + b] = dd;
+            if (lane == 0) s_d8[b * 8 + n] = dd;
         }
     } else {
         const int units = in_f / 8;  // 8-byte units
@@ -229,7 +234,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                 uint2 v = make_uint2(0, 0);
                 if (on) v = *reinterpret_cast<const uint2 *>(a.qs + ar * in_f + (size_t)u * 8);
                 const int b = u >> 5, uu = u & 31, s = uu >> 2, tt = uu & 3;
-                *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * 256 + tt * 64 + s * 8) = v;
+                *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * kStagedBytes + tt * kLaneBytes + s * 8) = v;
             }
             for (int r = threadIdx.x; r < nb * 8; r += kThreadsMma) {
                 const int b = r >> 3, s = r & 7;
@@ -237,7 +242,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                 s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum & 63);
                 s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
             }
-            for (int b = threadIdx.x; b < nb; b += kThreadsMma) s_d8[n * nb + b] = on ? a.d[ar * nb + b] : 0.f;
+            for (int b = threadIdx.x; b < nb; b += kThreadsMma) s_d8[b * 8 + n] = on ? a.d[ar * nb + b] : 0.f;
         }
     }
     __syncthreads();
@@ -277,7 +282,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                     // lanes of those columns simply re-read token gt; likewise the bsum words of lanes
                     // t >= 2 meet zero A operands.
                     uint32_t bq[16];
-                    const uint4 *cp = reinterpret_cast<const uint4 *>(s_codes + (size_t)(gt * nb + b) * 256 + t * 64);
+                    const uint4 *cp = reinterpret_cast<const uint4 *>(s_codes + (size_t)(gt * nb + b) * kStagedBytes + t * kLaneBytes);
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         const uint4 v = cp[i];
@@ -322,11 +327,12 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                     mma_u8s8(sml, am0, am1, 0u, 0u, bl_, 0u);
                     mma_u8s8(smh, am0, am1, 0u, 0u, bh_, 0u);
                     const float d0 = h2f(h0.x), dm0 = h2f(h0.x >> 16), d1 = h2f(h1.x), dm1 = h2f(h1.x >> 16);
-                    const float e0 = 2 * t < M ? s_d8[(2 * t) * nb + b] : 0.f;
+                    const float2 e01 = *reinterpret_cast<const float2 *>(s_d8 + b * 8 + 2 * t);
+                    const float e0 = e01.x;
                     accf[0] += e0 * (d0 * (float)sd[0] - dm0 * (float)(sml[0] + 64 * smh[0]));
                     accf[2] += e0 * (d1 * (float)sd[2] - dm1 * (float)(sml[2] + 64 * smh[2]));
                     if (M > 1) {
-                        const float e1 = 2 * t + 1 < M ? s_d8[(2 * t + 1) * nb + b] : 0.f;
+                        const float e1 = e01.y;
                         accf[1] += e1 * (d0 * (float)sd[1] - dm0 * (float)(sml[1] + 64 * smh[1]));
                         accf[3] += e1 * (d1 * (float)sd[3] - dm1 * (float)(sml[3] + 64 * smh[3]));
                     }
@@ -383,7 +389,7 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
     MmaGeom geo;
     geo.nb = in_f / 256;
     geo.bpw = (geo.nb + KW - 1) / KW;
-    const size_t acts = (size_t)M * geo.nb * (256 + 16) + (size_t)((M * geo.nb + 3) & ~3) * 4;
+    const size_t acts = (size_t)M * geo.nb * (kStagedBytes + 16) + (size_t)geo.nb * 32;
     geo.act_bytes = (int)acts;
     const size_t fixed = acts + (size_t)2 * KW * 128 * 4 + (size_t)KW * kMaxSlotsMma * 8 + 64;
     const size_t per_slot = (size_t)KW * kSlotBytes;
@@ -438,22 +444,29 @@ template <int M, bool FUSED>
 cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
                          const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
     const int nb = in_f / 256, tiles = (out_f + kTileRows - 1) / kTileRows;
-    // shared memory a configuration needs with two ring slots per warp
-    auto need = [&](int kw) {
-        const int sb = (nb + kw - 1) / kw == 1 ? 1 : 2;
-        return (size_t)M * nb * 272 + (size_t)((M * nb + 3) & ~3) * 4 + (size_t)2 * kw * 512 + (size_t)kw * kMaxSlotsMma * 8 + 64 +
+    // shared memory a configuration needs with two ring slots per warp of `sb` super-blocks each
+    auto need_sb = [&](int kw, int sb) {
+        return (size_t)M * nb * (kStagedBytes + 16) + (size_t)nb * 32 + (size_t)2 * kw * 512 + (size_t)kw * kMaxSlotsMma * 8 + 64 +
                (size_t)2 * kw * kTileRows * sb * 144;
     };
+    auto need = [&](int kw) { return need_sb(kw, (nb + kw - 1) / kw == 1 ? 1 : 2); };
     // 16 math warps per SM: with kw warps per tile an SM holds 16/kw tiles at once.  Prefer the widest
     // split that still lets every tile be resident in the first wave.
-    int kw = tiles > 2 * dev.sm_count ? 4 : (tiles > dev.sm_count ? 8 : 16);
+    const int kw0 = tiles > 2 * dev.sm_count ? 4 : (tiles > dev.sm_count ? 8 : 16);
+    int kw = kw0;
     // wide batches stage more activation bytes per CTA: let more warps share one staging copy so that
     // 16 math warps stay resident per SM
     while (kw < 16 && need(kw) > (size_t)dev.max_smem_optin / (16 / kw) - 2048) kw *= 2;
     while (kw > 4 && kw > nb) kw /= 2;
     // long rows with a wide batch may not fit at all with many warps: fall back to fewer
     while (kw > 4 && need(kw) > (size_t)dev.max_smem_optin - 1024) kw /= 2;
-    const int bpw = (nb + kw - 1) / kw;
+    int bpw = (nb + kw - 1) / kw;
+    // one CTA of 16 warps per SM pays a 16-warp barrier and reduction per tile for one block of work per warp:
+    // with many tiles, two CTAs of 8 warps and one-block ring slots are better when they fit
+    if (kw == 16 && kw0 < 16 && nb >= 8 && need_sb(8, 1) <= (size_t)dev.max_smem_optin / 2 - 2048) {
+        kw = 8;
+        bpw = 1;  // selects SB = 1 below; the kernel walks a warp's blocks one slot at a time
+    }
 #define INFR_MMA(KW_, SB_) return launch_mma_cfg<M, FUSED, KW_, SB_>(w, a, x, y, m, in_f, out_f, dev, status, st)
     if (kw == 16) {
         if (bpw == 1) INFR_MMA(16, 1);

@@ -314,6 +314,94 @@ def _decode_linears_case(be, infr_b200, batch, steps, warmup):
     return res
 
 
+def _tp_decode(be, infr_b200, dist, rank, world, local, steps, warmup):
+    """Tensor-parallel form of the decode step's Linear ops (batch 1): q/k/v/gate/up and the output head are
+    split by output rows, o and down by input columns with an NCCL all-reduce of the 4096-float result after each
+    (2 per layer), the head's logits are all-gathered.  Activations live in torch tensors that the backend wraps
+    in place (infr_cuda_wrap) and torch runs on the backend's stream (infr_cuda_stream), so the Linears and the
+    collectives are ordered on one stream and the whole step is one CUDA graph when capture succeeds.
+    Strong scaling: the same model on N GPUs."""
+    import torch
+    from infr_b200 import synth
+
+    Q4K, Q6K = infr_b200.Q4K, infr_b200.Q6K
+    dev = torch.device("cuda", local)
+    N = world
+    n_layer, h, kvd, ff, vocab = 32, 4096, 1024, 14336, 128256
+    shapes = [("wq", Q4K, h // N, h), ("wk", Q4K, kvd // N, h), ("wv", Q6K, kvd // N, h), ("wo", Q4K, h, h // N),
+              ("gate", Q4K, ff // N, h), ("up", Q4K, ff // N, h), ("down", Q6K, h, ff // N)]
+    nbytes = lambda dt, o, i: o * i // synth.BLOCK_ELEMS[dt] * synth.BLOCK_BYTES[dt]
+    masters = {name: be.from_numpy(synth.random_blocks(dt, o * i, 300 + k), infr_b200.USAGE_WEIGHTS)
+               for k, (name, dt, o, i) in enumerate(shapes)}
+    layers = []
+    for _ in range(n_layer):
+        L = {}
+        for name, dt, o, i in shapes:
+            L[name] = be.alloc_uninit(nbytes(dt, o, i), infr_b200.USAGE_WEIGHTS)
+            be.copy_buffer(masters[name], L[name], nbytes(dt, o, i))
+        layers.append(L)
+    head = be.from_numpy(synth.random_blocks(Q6K, (vocab // N) * h, 399), infr_b200.USAGE_WEIGHTS)
+    total_bytes = n_layer * sum(nbytes(dt, o, i) for _, dt, o, i in shapes) + nbytes(Q6K, vocab // N, h)
+    f32 = dict(dtype=torch.float32, device=dev)
+    t = {"x_h": torch.randn(h, **f32), "x_hs": torch.randn(h // N, **f32), "x_ffs": torch.randn(ff // N, **f32),
+         "y_q": torch.empty(h // N, **f32), "y_kv": torch.empty(kvd // N, **f32), "y_o": torch.empty(h, **f32),
+         "y_ff": torch.empty(ff // N, **f32), "y_d": torch.empty(h, **f32), "logits": torch.empty(vocab // N, **f32)}
+    gathered = torch.empty(vocab // N * N, **f32)
+    torch.cuda.synchronize(dev)
+    b = {k: be.wrap(v.data_ptr(), v.numel() * 4, infr_b200.USAGE_ACTIVATIONS) for k, v in t.items()}
+
+    def step():
+        for L in layers:
+            be.linear(Q4K, L["wq"], b["x_h"], b["y_q"], 1, h, h // N)
+            be.linear(Q4K, L["wk"], b["x_h"], b["y_kv"], 1, h, kvd // N)
+            be.linear(Q6K, L["wv"], b["x_h"], b["y_kv"], 1, h, kvd // N)
+            be.linear(Q4K, L["wo"], b["x_hs"], b["y_o"], 1, h // N, h)      # row-parallel: partial sums of the full vector
+            if N > 1:
+                dist.all_reduce(t["y_o"])
+            be.linear(Q4K, L["gate"], b["y_o"], b["y_ff"], 1, h, ff // N)
+            be.linear(Q4K, L["up"], b["y_o"], b["y_ff"], 1, h, ff // N)
+            be.linear(Q6K, L["down"], b["x_ffs"], b["y_d"], 1, ff // N, h)  # row-parallel
+            if N > 1:
+                dist.all_reduce(t["y_d"])
+        be.linear(Q6K, head, b["y_d"], b["logits"], 1, h, vocab // N)
+        if N > 1:
+            dist.all_gather_into_tensor(gathered, t["logits"])
+
+    ext = torch.cuda.ExternalStream(be.stream(), device=dev)
+    mode = "cuda graph"
+    with torch.cuda.stream(ext):
+        for _ in range(3):
+            step()  # sizes the context's scratch before capture
+        ext.synchronize()
+        graph = None
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=ext):
+                step()
+        except Exception as e:  # capture refused (collectives or stream rules): time the eager step
+            graph, mode = None, f"eager ({type(e).__name__}: {str(e)[:80]})"
+        run = graph.replay if graph is not None else step
+        for _ in range(warmup):
+            run()
+        ext.synchronize()
+        _barrier(dist)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ext)
+        for _ in range(steps):
+            run()
+        e1.record(ext)
+        e1.synchronize()
+        ms = e0.elapsed_time(e1)
+    ms = _max_over_ranks(dist, ms)
+    us = ms * 1e3 / steps
+    for v in list(b.values()) + list(masters.values()) + [head] + [x for L in layers for x in L.values()]:
+        v.close()
+    return {"workload": f"tensor-parallel Linear ops of an 8B-shape decode step, batch 1, {N} GPU(s): 225 Linears per rank "
+                        f"({total_bytes / 1e9:.2f} GB of weights per rank), {2 * n_layer if N > 1 else 0} NCCL all-reduces of 16 KB + 1 all-gather",
+            "us_per_step": us, "tok_per_s_matmul_only": 1e6 / us, "mode": mode, "scaling": "strong",
+            "not_included": "attention, norms, RoPE, sampling (not built)"}
+
+
 # ------------------------------------------------------------------------------------------------
 def run_b200(args):
     import infr_b200
@@ -429,6 +517,11 @@ def run_b200(args):
         out["mmq"] = _mmq_case(be, infr_b200, 512, 4096, 14336, 5, 20, 3)
         out["moe"] = _moe_case(be, infr_b200, 20, 3)
         out["decode_linears"] = [_decode_linears_case(be, infr_b200, b, 10, 3) for b in (1, 32)]
+
+    if not args.no_sweep:
+        tp = _tp_decode(be, infr_b200, dist, rank, world, local, 10, 3)
+        if rank == 0:
+            out["tp_decode"] = tp
 
     if rank == 0 and world == 1 and not args.no_cpu:
         out["cpu_baseline"] = _cpu_baseline(w, x, budget_s=10.0)

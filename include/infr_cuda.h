@@ -97,6 +97,16 @@ INFR_API int32_t infr_cuda_last_error(infr_cuda_ctx *ctx, char *dst, size_t cap)
  *      `Buffer::len_bytes`, backend.rs:387-398.  alloc is zero-initialised (calloc semantics). ---- */
 INFR_API int32_t infr_cuda_alloc(infr_cuda_ctx *ctx, size_t bytes, int32_t usage, infr_cuda_buf **out);
 INFR_API int32_t infr_cuda_alloc_uninit(infr_cuda_ctx *ctx, size_t bytes, int32_t usage, infr_cuda_buf **out);
+/* No counterpart in the trait (its buffers are always the backend's own): a handle over device memory the
+ * caller owns — a tensor of the host framework, a slice of another engine's pool — so that ops can read and
+ * write it in place.  Nothing is allocated or copied; infr_cuda_free on such a handle drops the handle only.
+ * The pointer must be 16-byte aligned and the range must stay valid while the handle is in use; ranges handed
+ * to ops as weights must be readable 256 bytes past `bytes` rounded down to 16 (vector loads on a row's tail
+ * never leave the backend's own padded allocations, and must not leave the caller's either). */
+INFR_API int32_t infr_cuda_wrap(infr_cuda_ctx *ctx, void *device_ptr, size_t bytes, int32_t usage, infr_cuda_buf **out);
+/* The CUDA stream (cudaStream_t as void*) the context enqueues all its work on, so that a caller can order
+ * its own kernels and collectives with the context's without a device-wide synchronise. */
+INFR_API void *infr_cuda_stream(infr_cuda_ctx *ctx);
 INFR_API void infr_cuda_free(infr_cuda_ctx *ctx, infr_cuda_buf *buf);
 INFR_API size_t infr_cuda_buf_len(const infr_cuda_buf *buf);
 INFR_API uint64_t infr_cuda_buf_device_ptr(const infr_cuda_buf *buf);

@@ -32,7 +32,7 @@ E_INVALID, E_UNSUPPORTED, E_OOM, E_CUDA, E_NCCL, E_TIMEOUT = -1, -2, -3, -4, -5,
 EXPORTED_SYMBOLS = [
     "infr_cuda_create", "infr_cuda_destroy", "infr_cuda_get_caps", "infr_cuda_last_error",
     "infr_cuda_alloc", "infr_cuda_alloc_uninit", "infr_cuda_free", "infr_cuda_buf_len",
-    "infr_cuda_buf_device_ptr", "infr_cuda_upload", "infr_cuda_upload_at", "infr_cuda_download",
+    "infr_cuda_buf_device_ptr", "infr_cuda_wrap", "infr_cuda_stream", "infr_cuda_upload", "infr_cuda_upload_at", "infr_cuda_download",
     "infr_cuda_copy", "infr_cuda_host_alloc", "infr_cuda_host_free", "infr_cuda_sync", "infr_cuda_compile", "infr_cuda_plan_free", "infr_cuda_execute",
     "infr_cuda_quantize_q8", "infr_cuda_quantize_q8_1", "infr_cuda_gemv", "infr_cuda_gemv_q8", "infr_cuda_gemv_noalloc", "infr_cuda_gemv_block_acc",
     "infr_cuda_linear", "infr_cuda_moe_ffn", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
@@ -115,6 +115,8 @@ def load_library() -> C.CDLL:
         "infr_cuda_execute": (i32, [vp, vp, C.POINTER(vp), u32]),
         "infr_cuda_quantize_q8": (i32, [vp, i32, vp, u32, u32, vp, vp, vp, vp]),
         "infr_cuda_quantize_q8_1": (i32, [vp, vp, u32, u32, vp, vp, vp]),
+        "infr_cuda_wrap": (i32, [vp, vp, sz, i32, C.POINTER(vp)]),
+        "infr_cuda_stream": (vp, [vp]),
         "infr_cuda_gemv": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
         "infr_cuda_gemv_q8": (i32, [vp, i32, vp, u64, vp, vp, vp, vp, vp, u32, u32, u32]),
         "infr_cuda_gemv_noalloc": (i32, [i32, vp, vp, vp, u32, u32, u32, vp, C.c_char_p, sz]),
@@ -304,6 +306,17 @@ class CudaBackend:
         h = C.c_void_p()
         self._check(self.L.infr_cuda_alloc_uninit(self.ctx, nbytes, usage, C.byref(h)))
         return Buffer(self, h, nbytes)
+
+    def wrap(self, device_ptr: int, nbytes: int, usage: int = USAGE_WEIGHTS) -> Buffer:
+        """A handle over device memory the caller owns (e.g. ``tensor.data_ptr()``): nothing is allocated or
+        copied and closing the handle leaves the memory alone.  The caller keeps the memory alive."""
+        h = C.c_void_p()
+        self._check(self.L.infr_cuda_wrap(self.ctx, C.c_void_p(device_ptr), nbytes, usage, C.byref(h)))
+        return Buffer(self, h, nbytes)
+
+    def stream(self) -> int:
+        """The context's cudaStream_t as an integer (0 = the default stream)."""
+        return int(self.L.infr_cuda_stream(self.ctx) or 0)
 
     def upload(self, dst: Buffer, src: np.ndarray, offset: int = 0):
         src = np.ascontiguousarray(src)

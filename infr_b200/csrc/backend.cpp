@@ -137,11 +137,24 @@ Status CudaBackend::alloc(size_t bytes, int usage, bool zero, infr_cuda_buf **ou
     return Status::Ok();
 }
 
+Status CudaBackend::wrap(void *device_ptr, size_t bytes, int usage, infr_cuda_buf **out) {
+    if (!device_ptr || !bytes) return Status::Err(INFR_E_INVALID, "wrap: null pointer or empty range");
+    if ((uintptr_t)device_ptr % 16) return Status::Err(INFR_E_INVALID, "wrap: the device pointer must be 16-byte aligned");
+    auto *b = new infr_cuda_buf();
+    b->ptr = device_ptr;
+    b->len = bytes;
+    b->usage = usage;
+    b->uid = next_uid_++;
+    b->owned = false;
+    *out = b;
+    return Status::Ok();
+}
+
 void CudaBackend::free_buffer(infr_cuda_buf *b) {
     if (!b) return;
     cudaSetDevice(device_);
-    cudaStreamSynchronize(stream_);
-    cudaFree(b->ptr);
+    if (!capturing_) cudaStreamSynchronize(stream_);
+    if (b->owned) cudaFree(b->ptr);
     delete b;
 }
 

@@ -19,6 +19,7 @@ struct infr_cuda_buf {
     size_t len = 0;  // logical size in bytes (Buffer::len_bytes, backend.rs:387-398)
     int usage = 0;
     uint64_t uid = 0;  // never reused: derived-data caches key on this, not on the address
+    bool owned = true;  // false: the memory belongs to the caller (infr_cuda_wrap), free drops only the handle
 };
 
 struct infr_cuda_plan {
@@ -61,6 +62,9 @@ public:
     // ---- memory ----
     Status alloc(size_t bytes, int usage, bool zero, infr_cuda_buf **out);
     void free_buffer(infr_cuda_buf *b);
+    // A handle over device memory the caller owns (another engine's pool, a framework tensor): nothing is
+    // allocated or copied, free_buffer drops the handle only.
+    Status wrap(void *device_ptr, size_t bytes, int usage, infr_cuda_buf **out);
     Status upload(infr_cuda_buf *dst, size_t dst_off, const void *src, size_t bytes);
     Status download(const infr_cuda_buf *src, void *dst, size_t bytes);
     Status copy_buffer(const infr_cuda_buf *src, infr_cuda_buf *dst, size_t bytes);

@@ -82,6 +82,17 @@ int32_t infr_cuda_alloc_uninit(infr_cuda_ctx *ctx, size_t bytes, int32_t usage, 
     return finish(ctx, ctx->be->alloc(bytes, usage, false, out));
 }
 
+int32_t infr_cuda_wrap(infr_cuda_ctx *ctx, void *device_ptr, size_t bytes, int32_t usage, infr_cuda_buf **out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (!out) return finish(ctx, Status::Err(INFR_E_INVALID, "wrap: null output"));
+    return finish(ctx, ctx->be->wrap(device_ptr, bytes, usage, out));
+}
+
+void *infr_cuda_stream(infr_cuda_ctx *ctx) {
+    if (!ctx || !ctx->be) return nullptr;
+    return (void *)ctx->be->stream();
+}
+
 void infr_cuda_free(infr_cuda_ctx *ctx, infr_cuda_buf *buf) {
     if (!ctx || !ctx->be) return;
     std::lock_guard<std::mutex> lock_(ctx->be->mutex());

@@ -2,7 +2,7 @@
 // w = d * sc_s * (q - 32)) decode GEMV / small-batch GEMM (m <= 8) on the warp-level int8 matrix unit, for
 // rows whose byte length is a multiple of 16 (8 | blocks per row), the stride rule of a TMA tensor map.
 //
-// Arithmetic of vec_dot_q6k (crates/infr-cpu/src/kernels.rs, restated in oracle/infr_cpu_oracle.c): per block
+// Arithmetic of vec_dot_q6k (vec_dot_q6k_scalar, crates/infr-cpu/src/kernels.rs:487-526): per block
 //     isum = sum_s sc_s * (sum_{l in s} q_l a_l - 32 * bsum16_s)      exact int32, 16 sub-blocks of 16
 //     y   += d * d8 * float(isum)
 //

@@ -350,55 +350,103 @@ def _tp_decode(be, infr_b200, dist, rank, world, local, steps, warmup):
     torch.cuda.synchronize(dev)
     b = {k: be.wrap(v.data_ptr(), v.numel() * 4, infr_b200.USAGE_ACTIVATIONS) for k, v in t.items()}
 
-    def step():
+    # the library's own small-message all-reduce over NVLink peer memory (one kernel on the context's stream)
+    comm, ar_us = None, None
+    if N > 1:
+        comm = be.comm_create(rank, N, h)
+        handles = [None] * N
+        dist.all_gather_object(handles, comm.export())
+        comm.connect(handles)
+        # same sums as NCCL on random data before it is trusted with the timing
+        probe = torch.randn(h, **f32)
+        ref = probe.clone()
+        torch.cuda.synchronize(dev)
+        pw = be.wrap(probe.data_ptr(), h * 4, infr_b200.USAGE_ACTIVATIONS)
+        be.all_reduce(comm, pw, h)
+        be.sync()
+        dist.all_reduce(ref)
+        torch.cuda.synchronize(dev)
+        err = float((probe - ref).abs().max() / ref.abs().max())
+        assert err < 1e-6, f"peer-memory all-reduce differs from NCCL: {err}"
+        # latency of one exchange, back to back on the stream
+        ar_us = {}
+        with torch.cuda.stream(torch.cuda.ExternalStream(be.stream(), device=dev)) as _:
+            for name, fn in (("own", lambda: be.all_reduce(comm, pw, h)), ("nccl", lambda: dist.all_reduce(probe))):
+                for _ in range(20):
+                    fn()
+                be.sync()
+                _barrier(dist)
+                be.timer_start()
+                for _ in range(200):
+                    fn()
+                ar_us[name] = _max_over_ranks(dist, be.timer_stop()) * 1e3 / 200
+        pw.close()
+
+    def step(own):
+        def reduce_(name):
+            if N == 1 or own is None:
+                return
+            if own:
+                be.all_reduce(comm, b[name], h)
+            else:
+                dist.all_reduce(t[name])
         for L in layers:
             be.linear(Q4K, L["wq"], b["x_h"], b["y_q"], 1, h, h // N)
             be.linear(Q4K, L["wk"], b["x_h"], b["y_kv"], 1, h, kvd // N)
             be.linear(Q6K, L["wv"], b["x_h"], b["y_kv"], 1, h, kvd // N)
             be.linear(Q4K, L["wo"], b["x_hs"], b["y_o"], 1, h // N, h)      # row-parallel: partial sums of the full vector
-            if N > 1:
-                dist.all_reduce(t["y_o"])
+            reduce_("y_o")
             be.linear(Q4K, L["gate"], b["y_o"], b["y_ff"], 1, h, ff // N)
             be.linear(Q4K, L["up"], b["y_o"], b["y_ff"], 1, h, ff // N)
             be.linear(Q6K, L["down"], b["x_ffs"], b["y_d"], 1, ff // N, h)  # row-parallel
-            if N > 1:
-                dist.all_reduce(t["y_d"])
+            reduce_("y_d")
         be.linear(Q6K, head, b["y_d"], b["logits"], 1, h, vocab // N)
         if N > 1:
             dist.all_gather_into_tensor(gathered, t["logits"])
 
     ext = torch.cuda.ExternalStream(be.stream(), device=dev)
-    mode = "cuda graph"
-    with torch.cuda.stream(ext):
-        for _ in range(3):
-            step()  # sizes the context's scratch before capture
-        ext.synchronize()
-        graph = None
-        try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=ext):
-                step()
-        except Exception as e:  # capture refused (collectives or stream rules): time the eager step
-            graph, mode = None, f"eager ({type(e).__name__}: {str(e)[:80]})"
-        run = graph.replay if graph is not None else step
-        for _ in range(warmup):
-            run()
-        ext.synchronize()
-        _barrier(dist)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(ext)
-        for _ in range(steps):
-            run()
-        e1.record(ext)
-        e1.synchronize()
-        ms = e0.elapsed_time(e1)
-    ms = _max_over_ranks(dist, ms)
-    us = ms * 1e3 / steps
+
+    def timed(own):
+        mode = "cuda graph"
+        with torch.cuda.stream(ext):
+            for _ in range(3):
+                step(own)  # sizes the context's scratch before capture
+            ext.synchronize()
+            graph = None
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=ext):
+                    step(own)
+            except Exception as e:  # capture refused (collectives or stream rules): time the eager step
+                graph, mode = None, f"eager ({type(e).__name__}: {str(e)[:80]})"
+            run = graph.replay if graph is not None else (lambda: step(own))
+            for _ in range(warmup):
+                run()
+            ext.synchronize()
+            _barrier(dist)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(ext)
+            for _ in range(steps):
+                run()
+            e1.record(ext)
+            e1.synchronize()
+            ms = e0.elapsed_time(e1)
+            del graph
+        return _max_over_ranks(dist, ms) * 1e3 / steps, mode
+
+    us, mode = timed(True)
+    us_nccl = timed(False)[0] if N > 1 else None
+    us_none = timed(None)[0] if N > 1 else None  # the ranks' Linears alone (no exchange: not a valid step, a floor)
+    be.sync()  # a bounded wait that expired in the exchange surfaces here
+    if comm is not None:
+        comm.close()
     for v in list(b.values()) + list(masters.values()) + [head] + [x for L in layers for x in L.values()]:
         v.close()
     return {"workload": f"tensor-parallel Linear ops of an 8B-shape decode step, batch 1, {N} GPU(s): 225 Linears per rank "
-                        f"({total_bytes / 1e9:.2f} GB of weights per rank), {2 * n_layer if N > 1 else 0} NCCL all-reduces of 16 KB + 1 all-gather",
+                        f"({total_bytes / 1e9:.2f} GB of weights per rank), {2 * n_layer if N > 1 else 0} all-reduces of 16 KB "
+                        f"(peer-memory kernel of this library) + 1 NCCL all-gather",
             "us_per_step": us, "tok_per_s_matmul_only": 1e6 / us, "mode": mode, "scaling": "strong",
+            "us_per_step_with_nccl_all_reduce": us_nccl, "us_per_step_without_all_reduce": us_none, "all_reduce_16KB_us": ar_us if N > 1 else None,
             "not_included": "attention, norms, RoPE, sampling (not built)"}
 
 

@@ -63,6 +63,7 @@ extern "C" {
 typedef struct infr_cuda_ctx infr_cuda_ctx;
 typedef struct infr_cuda_buf infr_cuda_buf;
 typedef struct infr_cuda_plan infr_cuda_plan;
+typedef struct infr_cuda_comm infr_cuda_comm;
 typedef struct infr_cuda_graph infr_cuda_graph;
 
 /* Options of infr_cuda_create.  `reference` mirrors CpuCfg::reference
@@ -108,6 +109,20 @@ INFR_API int32_t infr_cuda_wrap(infr_cuda_ctx *ctx, void *device_ptr, size_t byt
  * its own kernels and collectives with the context's without a device-wide synchronise. */
 INFR_API void *infr_cuda_stream(infr_cuda_ctx *ctx);
 INFR_API void infr_cuda_free(infr_cuda_ctx *ctx, infr_cuda_buf *buf);
+
+/* No counterpart in the reference (it has no multi-GPU path): the exchange a row-parallel Linear needs when a
+ * model is split over the GPUs of one box, one process per GPU.  In-place sum of n f32 (a multiple of 4, at
+ * most max_floats <= 65536) over `world` <= 8 ranks, as one kernel over NVLink peer memory on the context's
+ * stream (capturable in a CUDA graph); every rank gets the same bits (slots are summed in rank order).
+ * Set-up: every rank creates a comm, exports its 64-byte handle (a CUDA IPC memory handle), the host program
+ * gathers the handles of all ranks in rank order by whatever channel it has, and every rank connects.
+ * All ranks must issue the same sequence of all-reduces.  A peer that never arrives makes the bounded wait
+ * expire: the data is left unsummed and the next infr_cuda_sync returns INFR_E_TIMEOUT. */
+INFR_API int32_t infr_cuda_comm_create(infr_cuda_ctx *ctx, int32_t rank, int32_t world, uint32_t max_floats, infr_cuda_comm **out);
+INFR_API int32_t infr_cuda_comm_export(infr_cuda_ctx *ctx, infr_cuda_comm *comm, uint8_t *handle64);
+INFR_API int32_t infr_cuda_comm_connect(infr_cuda_ctx *ctx, infr_cuda_comm *comm, const uint8_t *handles /* [world][64] */);
+INFR_API int32_t infr_cuda_all_reduce_f32(infr_cuda_ctx *ctx, infr_cuda_comm *comm, infr_cuda_buf *data, uint32_t n);
+INFR_API void infr_cuda_comm_destroy(infr_cuda_ctx *ctx, infr_cuda_comm *comm);
 INFR_API size_t infr_cuda_buf_len(const infr_cuda_buf *buf);
 INFR_API uint64_t infr_cuda_buf_device_ptr(const infr_cuda_buf *buf);
 /* upload/download reject a transfer larger than the buffer (check_copy_bytes, backend.rs:23-30). */

@@ -32,7 +32,8 @@ E_INVALID, E_UNSUPPORTED, E_OOM, E_CUDA, E_NCCL, E_TIMEOUT = -1, -2, -3, -4, -5,
 EXPORTED_SYMBOLS = [
     "infr_cuda_create", "infr_cuda_destroy", "infr_cuda_get_caps", "infr_cuda_last_error",
     "infr_cuda_alloc", "infr_cuda_alloc_uninit", "infr_cuda_free", "infr_cuda_buf_len",
-    "infr_cuda_buf_device_ptr", "infr_cuda_wrap", "infr_cuda_stream", "infr_cuda_upload", "infr_cuda_upload_at", "infr_cuda_download",
+    "infr_cuda_buf_device_ptr", "infr_cuda_wrap", "infr_cuda_stream", "infr_cuda_comm_create", "infr_cuda_comm_export", "infr_cuda_comm_connect",
+    "infr_cuda_all_reduce_f32", "infr_cuda_comm_destroy", "infr_cuda_upload", "infr_cuda_upload_at", "infr_cuda_download",
     "infr_cuda_copy", "infr_cuda_host_alloc", "infr_cuda_host_free", "infr_cuda_sync", "infr_cuda_compile", "infr_cuda_plan_free", "infr_cuda_execute",
     "infr_cuda_quantize_q8", "infr_cuda_quantize_q8_1", "infr_cuda_gemv", "infr_cuda_gemv_q8", "infr_cuda_gemv_noalloc", "infr_cuda_gemv_block_acc",
     "infr_cuda_linear", "infr_cuda_moe_ffn", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
@@ -117,6 +118,11 @@ def load_library() -> C.CDLL:
         "infr_cuda_quantize_q8_1": (i32, [vp, vp, u32, u32, vp, vp, vp]),
         "infr_cuda_wrap": (i32, [vp, vp, sz, i32, C.POINTER(vp)]),
         "infr_cuda_stream": (vp, [vp]),
+        "infr_cuda_comm_create": (i32, [vp, i32, i32, u32, C.POINTER(vp)]),
+        "infr_cuda_comm_export": (i32, [vp, vp, vp]),
+        "infr_cuda_comm_connect": (i32, [vp, vp, vp]),
+        "infr_cuda_all_reduce_f32": (i32, [vp, vp, vp, u32]),
+        "infr_cuda_comm_destroy": (None, [vp, vp]),
         "infr_cuda_gemv": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
         "infr_cuda_gemv_q8": (i32, [vp, i32, vp, u64, vp, vp, vp, vp, vp, u32, u32, u32]),
         "infr_cuda_gemv_noalloc": (i32, [i32, vp, vp, vp, u32, u32, u32, vp, C.c_char_p, sz]),
@@ -178,6 +184,29 @@ class Buffer:
             self.close()
         except Exception:
             pass
+
+
+class Comm:
+    """Peer-memory exchange group of one box (infr_cuda_comm_*): export() -> gather the handles of all ranks in rank
+    order -> connect(handles) -> CudaBackend.all_reduce."""
+
+    def __init__(self, be: "CudaBackend", handle, world: int):
+        self._be, self.handle, self.world = be, handle, world
+
+    def export(self) -> bytes:
+        buf = (C.c_uint8 * 64)()
+        self._be._check(self._be.L.infr_cuda_comm_export(self._be.ctx, self.handle, buf))
+        return bytes(buf)
+
+    def connect(self, handles: Sequence[bytes]):
+        assert len(handles) == self.world and all(len(h) == 64 for h in handles)
+        blob = (C.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(handles))
+        self._be._check(self._be.L.infr_cuda_comm_connect(self._be.ctx, self.handle, blob))
+
+    def close(self):
+        if self.handle and self._be.ctx:
+            self._be.L.infr_cuda_comm_destroy(self._be.ctx, self.handle)
+        self.handle = None
 
 
 class Graph:
@@ -313,6 +342,15 @@ class CudaBackend:
         h = C.c_void_p()
         self._check(self.L.infr_cuda_wrap(self.ctx, C.c_void_p(device_ptr), nbytes, usage, C.byref(h)))
         return Buffer(self, h, nbytes)
+
+    def comm_create(self, rank: int, world: int, max_floats: int) -> "Comm":
+        h = C.c_void_p()
+        self._check(self.L.infr_cuda_comm_create(self.ctx, rank, world, max_floats, C.byref(h)))
+        return Comm(self, h, world)
+
+    def all_reduce(self, comm: "Comm", data: Buffer, n: int):
+        """In-place sum of n f32 over the comm's ranks, enqueued on the context's stream."""
+        self._check(self.L.infr_cuda_all_reduce_f32(self.ctx, comm.handle, data.handle, n))
 
     def stream(self) -> int:
         """The context's cudaStream_t as an integer (0 = the default stream)."""

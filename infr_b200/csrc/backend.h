@@ -22,6 +22,8 @@ struct infr_cuda_buf {
     bool owned = true;  // false: the memory belongs to the caller (infr_cuda_wrap), free drops only the handle
 };
 
+struct infr_cuda_comm;  // comm.cu
+
 struct infr_cuda_plan {
     std::vector<infr_tensor_decl> tensors;
     std::vector<infr_op_desc> ops;
@@ -65,6 +67,12 @@ public:
     // A handle over device memory the caller owns (another engine's pool, a framework tensor): nothing is
     // allocated or copied, free_buffer drops the handle only.
     Status wrap(void *device_ptr, size_t bytes, int usage, infr_cuda_buf **out);
+    // Small-message all-reduce over peer memory of the GPUs of one box (comm.cu).
+    Status comm_create(int rank, int world, uint32_t max_floats, infr_cuda_comm **out);
+    Status comm_export(infr_cuda_comm *c, uint8_t *handle64);
+    Status comm_connect(infr_cuda_comm *c, const uint8_t *handles);
+    Status all_reduce_f32(infr_cuda_comm *c, float *data, uint32_t n);
+    void comm_destroy(infr_cuda_comm *c);
     Status upload(infr_cuda_buf *dst, size_t dst_off, const void *src, size_t bytes);
     Status download(const infr_cuda_buf *src, void *dst, size_t bytes);
     Status copy_buffer(const infr_cuda_buf *src, infr_cuda_buf *dst, size_t bytes);

@@ -88,6 +88,34 @@ int32_t infr_cuda_wrap(infr_cuda_ctx *ctx, void *device_ptr, size_t bytes, int32
     return finish(ctx, ctx->be->wrap(device_ptr, bytes, usage, out));
 }
 
+int32_t infr_cuda_comm_create(infr_cuda_ctx *ctx, int32_t rank, int32_t world, uint32_t max_floats, infr_cuda_comm **out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (!out) return finish(ctx, Status::Err(INFR_E_INVALID, "comm_create: null output"));
+    return finish(ctx, ctx->be->comm_create(rank, world, max_floats, out));
+}
+
+int32_t infr_cuda_comm_export(infr_cuda_ctx *ctx, infr_cuda_comm *comm, uint8_t *handle64) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->comm_export(comm, handle64));
+}
+
+int32_t infr_cuda_comm_connect(infr_cuda_ctx *ctx, infr_cuda_comm *comm, const uint8_t *handles) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->comm_connect(comm, handles));
+}
+
+int32_t infr_cuda_all_reduce_f32(infr_cuda_ctx *ctx, infr_cuda_comm *comm, infr_cuda_buf *data, uint32_t n) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (!data || (size_t)n * 4 > data->len) return finish(ctx, Status::Err(INFR_E_INVALID, "all_reduce: buffer smaller than n floats"));
+    return finish(ctx, ctx->be->all_reduce_f32(comm, static_cast<float *>(data->ptr), n));
+}
+
+void infr_cuda_comm_destroy(infr_cuda_ctx *ctx, infr_cuda_comm *comm) {
+    if (!ctx || !ctx->be) return;
+    std::lock_guard<std::mutex> lock_(ctx->be->mutex());
+    ctx->be->comm_destroy(comm);
+}
+
 void *infr_cuda_stream(infr_cuda_ctx *ctx) {
     if (!ctx || !ctx->be) return nullptr;
     return (void *)ctx->be->stream();

@@ -1,4 +1,4 @@
-"""Row (column-parallel) sharding of a block-quantized weight across ranks.
+"""Row (column-parallel) and column (row-parallel) sharding of a block-quantized weight across ranks.
 
 The quantized matmul shards by OUTPUT rows with no exchange inside the op: rank r owns rows
 [r*out_f/W, (r+1)*out_f/W) of the row-major [out_f, in_f] weight, whole GGUF blocks stay whole because a
@@ -31,6 +31,35 @@ def row_shard(dtype: int, w_bytes: np.ndarray, out_f: int, in_f: int, rank: int,
         raise ValueError(f"weight holds {w.size} bytes, expected {out_f} rows x {bpr}")
     lo, hi = row_range(out_f, rank, world)
     return w[lo * bpr:hi * bpr], lo, hi - lo
+
+
+def col_range(dtype: int, in_f: int, rank: int, world: int, unit: int = 0) -> tuple[int, int]:
+    """Contiguous balanced range of INPUT columns of `rank`, in whole weight blocks (or multiples of `unit`
+    elements when given: the activation quantiser's granule, 256 for Q4_K / Q6_K, must stay whole too so that a
+    rank's int8 codes and scales are the unsharded ones).  This is the row-parallel half of the reference's
+    tensor-parallel lowering (`tp_slice_row`, crates/infr-llama/src/seam/mod.rs:2711-2798): every rank multiplies
+    its column slice with its slice of the activations and the partial results are summed (all-reduce)."""
+    from .synth import BLOCK_ELEMS
+
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    g = max(BLOCK_ELEMS[dtype], unit)
+    if in_f % g:
+        raise ValueError(f"in_f={in_f} is not a whole number of {g}-element granules")
+    base, rem = divmod(in_f // g, world)
+    lo = rank * base + min(rank, rem)
+    return lo * g, (lo + base + (1 if rank < rem else 0)) * g
+
+
+def col_shard(dtype: int, w_bytes: np.ndarray, out_f: int, in_f: int, rank: int, world: int, unit: int = 0) -> tuple[np.ndarray, int, int]:
+    """(bytes of this rank's column slice as a dense [out_f, cols] weight, first column, column count)."""
+    from .synth import BLOCK_BYTES, BLOCK_ELEMS
+
+    bpr = row_bytes(dtype, in_f)
+    w = np.ascontiguousarray(w_bytes, dtype=np.uint8).reshape(out_f, bpr)
+    lo, hi = col_range(dtype, in_f, rank, world, unit)
+    be, bb = BLOCK_ELEMS[dtype], BLOCK_BYTES[dtype]
+    return np.ascontiguousarray(w[:, lo // be * bb:hi // be * bb]).reshape(-1), lo, hi - lo
 
 
 def gather_rows(dist, y_local: np.ndarray, out_f: int, rank: int, world: int) -> np.ndarray:

@@ -53,6 +53,62 @@ def test_row_shards_gather_to_the_unsharded_result(dt, out_f, in_f, m):
     assert res[0][2] == 0 and res[0][2] + res[0][3] == res[1][2] and res[1][2] + res[1][3] == out_f
 
 
+def _col_worker(rank, world, port, dt, out_f, in_f, m, q):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+
+    from infr_b200 import shard, synth
+    from oracle.cpu_oracle import Oracle
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        orc = Oracle()
+        w = synth.weight(dt, out_f, in_f, seed=5)
+        x = synth.normal(6, (m, in_f))
+        mine, lo, n = shard.col_shard(dt, w, out_f, in_f, rank, world, unit=256)
+        part = torch.from_numpy(orc.linear(dt, mine, np.ascontiguousarray(x[:, lo:lo + n]), m, n, out_f, threads=2))
+        dist.all_reduce(part)  # the exchange of a row-parallel Linear
+        want = orc.linear(dt, w, x, m, in_f, out_f, threads=2)
+        rel = float(np.linalg.norm(part.numpy() - want) / np.linalg.norm(want))
+        q.put((rank, rel, lo, n))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dt,out_f,in_f,m", [(12, 24, 1024, 2), (14, 16, 768, 1)])
+def test_column_shards_sum_to_the_unsharded_result(dt, out_f, in_f, m):
+    # whole 256-element granules per rank: every block term is the unsharded one, only the f32 sum order differs
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() + dt) % 2000
+    procs = [ctx.Process(target=_col_worker, args=(r, 2, port, dt, out_f, in_f, m, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(rel < 1e-6 for _, rel, _, _ in res), res
+    assert res[0][2] == 0 and res[0][2] + res[0][3] == res[1][2] and res[1][2] + res[1][3] == in_f
+
+
+def test_col_range_keeps_blocks_and_granules_whole():
+    sys.path.insert(0, ROOT)
+    from infr_b200 import shard
+
+    for dt, in_f, unit in ((12, 4096, 256), (14, 14336, 256), (27, 14336, 64), (27, 14336, 512)):
+        for world in (1, 2, 4, 8):
+            spans = [shard.col_range(dt, in_f, r, world, unit) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == in_f
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert all(a % unit == 0 and b % unit == 0 for a, b in spans)
+    with pytest.raises(ValueError):
+        shard.col_range(12, 4096 + 128, 0, 2)
+
+
 def test_row_range_is_a_balanced_partition():
     sys.path.insert(0, ROOT)
     from infr_b200 import shard

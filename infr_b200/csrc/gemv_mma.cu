@@ -225,24 +225,53 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
             if (lane == 0) s_d8[b * 8 + n] = dd;
         }
     } else {
-        const int units = in_f / 8;  // 8-byte units
-        for (int n = 0; n < M; n++) {
-            const bool on = n < m;
-            // activation row of column n: the item's n-th pair (gathered through pair_row when given)
-            const size_t ar = !on ? 0 : (size_t)(grp.pair_row ? grp.pair_row[p0 + n] : p0 + n);
-            for (int u = threadIdx.x; u < units; u += kThreadsMma) {
-                uint2 v = make_uint2(0, 0);
-                if (on) v = *reinterpret_cast<const uint2 *>(a.qs + ar * in_f + (size_t)u * 8);
+        if (M == 1) {
+            // one row: a plain strided copy (the batched form below costs a barrier more than it saves here)
+            const size_t ar = (size_t)(grp.pair_row ? grp.pair_row[p0] : p0);
+            for (int u = threadIdx.x; u < in_f / 8; u += kThreadsMma) {
+                const uint2 v = *reinterpret_cast<const uint2 *>(a.qs + ar * in_f + (size_t)u * 8);
                 const int b = u >> 5, uu = u & 31, s = uu >> 2, tt = uu & 3;
-                *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * kStagedBytes + tt * kLaneBytes + s * 8) = v;
+                *reinterpret_cast<uint2 *>(s_codes + (size_t)b * kStagedBytes + tt * kLaneBytes + s * 8) = v;
             }
             for (int r = threadIdx.x; r < nb * 8; r += kThreadsMma) {
-                const int b = r >> 3, s = r & 7;
-                const int sum = on ? a.sums[ar * nb * 8 + r] : 0;
-                s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum & 63);
-                s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
+                const int b = r >> 3, s = r & 7, sum = a.sums[ar * nb * 8 + r];
+                s_bsplit[(size_t)b * 16 + s] = (uint8_t)(sum & 63);
+                s_bsplit[(size_t)b * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
             }
-            for (int b = threadIdx.x; b < nb; b += kThreadsMma) s_d8[b * 8 + n] = on ? a.d[ar * nb + b] : 0.f;
+            for (int b = threadIdx.x; b < nb; b += kThreadsMma) s_d8[b * 8] = a.d[ar * nb + b];
+        } else {
+        // activation row of column n: the item's n-th pair (gathered through pair_row when given)
+        __shared__ uint32_t s_row[8];
+        if (threadIdx.x < 8) s_row[threadIdx.x] = threadIdx.x < m ? (uint32_t)(grp.pair_row ? grp.pair_row[p0 + threadIdx.x] : p0 + threadIdx.x) : 0u;
+        __syncthreads();
+        // eight independent 8-byte loads in flight per thread: the copy is latency-bound, not bandwidth-bound
+        // (flattened over tokens and units: with one token's few hundred units per pass most of the loads would be masked)
+        const int units = in_f / 8, total = M * units;
+        for (int i0 = threadIdx.x; i0 < total; i0 += 8 * kThreadsMma) {
+            uint2 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int i = i0 + k * kThreadsMma, n = i / units, u = i - n * units;
+                v[k] = make_uint2(0, 0);
+                if (i < total && n < m) v[k] = *reinterpret_cast<const uint2 *>(a.qs + (size_t)s_row[n] * in_f + (size_t)u * 8);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int i = i0 + k * kThreadsMma, n = i / units, u = i - n * units;
+                const int b = u >> 5, uu = u & 31, s = uu >> 2, tt = uu & 3;
+                if (i < total) *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * kStagedBytes + tt * kLaneBytes + s * 8) = v[k];
+            }
+        }
+        for (int i = threadIdx.x; i < M * nb * 8; i += kThreadsMma) {
+            const int n = i / (nb * 8), r = i - n * nb * 8, b = r >> 3, s = r & 7;
+            const int sum = n < m ? a.sums[(size_t)s_row[n] * nb * 8 + r] : 0;
+            s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum & 63);
+            s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
+        }
+        for (int i = threadIdx.x; i < M * nb; i += kThreadsMma) {
+            const int n = i / nb, b = i - n * nb;
+            s_d8[b * 8 + n] = n < m ? a.d[(size_t)s_row[n] * nb + b] : 0.f;
+        }
         }
     }
     __syncthreads();

@@ -118,16 +118,26 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
     // ---- activations (from the previous kernel in the stream) ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
     {
+        // eight independent 8-byte loads in flight per thread (the copy is latency-bound)
         const int units = in_f / 8;
         for (int n = 0; n < M; n++) {
             const bool on = n < m;
-            for (int u = threadIdx.x; u < units; u += KW * 32) {
-                uint2 v = make_uint2(0, 0);
-                if (on) v = *reinterpret_cast<const uint2 *>(a.qs + (size_t)n * in_f + (size_t)u * 8);
-                const int c = u >> 6, uu = u & 63, s = uu >> 2, tt = uu & 3;
-                // bytes e0..e7 -> [e0 e4 e1 e5], [e2 e6 e3 e7]: the order spread8 gives the codes
-                const uint2 pv = make_uint2(__byte_perm(v.x, v.y, 0x5140), __byte_perm(v.x, v.y, 0x7362));
-                *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nch + c) * kStagedChunk + tt * kLaneStride + s * 8) = pv;
+            for (int u0 = threadIdx.x; u0 < units; u0 += 8 * KW * 32) {
+                uint2 v[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const int u = u0 + k * KW * 32;
+                    v[k] = make_uint2(0, 0);
+                    if (on && u < units) v[k] = *reinterpret_cast<const uint2 *>(a.qs + (size_t)n * in_f + (size_t)u * 8);
+                }
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const int u = u0 + k * KW * 32;
+                    const int c = u >> 6, uu = u & 63, s = uu >> 2, tt = uu & 3;
+                    // bytes e0..e7 -> [e0 e4 e1 e5], [e2 e6 e3 e7]: the order spread8 gives the codes
+                    const uint2 pv = make_uint2(__byte_perm(v[k].x, v[k].y, 0x5140), __byte_perm(v[k].x, v[k].y, 0x7362));
+                    if (u < units) *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nch + c) * kStagedChunk + tt * kLaneStride + s * 8) = pv;
+                }
             }
         }
         for (int i = threadIdx.x; i < ng * 8; i += KW * 32) {

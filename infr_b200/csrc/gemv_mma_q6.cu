@@ -200,21 +200,36 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
     // ---- activations (from the previous kernel in the stream) ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
     {
-        const int words = in_f / 4;
-        for (int n = 0; n < M; n++) {
-            const bool on = n < m;
-            for (int u = threadIdx.x; u < words; u += KW * 32) {
-                const uint32_t v = on ? *reinterpret_cast<const uint32_t *>(a.qs + (size_t)n * in_f + (size_t)u * 4) : 0u;
-                const int b = u >> 6, uu = u & 63, s = uu >> 2, tt = uu & 3;
-                *reinterpret_cast<uint32_t *>(s_act + (size_t)(n * nb + b) * kStagedBlock + tt * kLane6 + s * 4) = v;
+        // 16 bytes = the 16 codes of one sub-block = one word for each of the four K lanes; four loads in flight per
+        // thread (the copy is latency-bound)
+        // (flattened over tokens and units: with one token's few hundred units per pass most of the loads would be masked)
+        const int units = in_f / 16, total = M * units;
+        for (int i0 = threadIdx.x; i0 < total; i0 += 4 * KW * 32) {
+            uint4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int i = i0 + k * KW * 32, n = M == 1 ? 0 : i / units, u = i - n * units;
+                v[k] = make_uint4(0, 0, 0, 0);
+                if (i < total && n < m) v[k] = *reinterpret_cast<const uint4 *>(a.qs + (size_t)n * in_f + (size_t)u * 16);
             }
-            for (int i = threadIdx.x; i < nb * 16; i += KW * 32) {
-                const int b = i >> 4, s = i & 15;
-                const int bs = on ? a.sums16[(size_t)n * nb * 16 + i] : 0;
-                uint8_t *sp = s_act + (size_t)(n * nb + b) * kStagedBlock + 4 * kLane6;
-                sp[s] = (uint8_t)(bs & 63);
-                sp[16 + s] = (uint8_t)(int8_t)(bs >> 6);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int i = i0 + k * KW * 32, n = M == 1 ? 0 : i / units, u = i - n * units;
+                if (i < total) {
+                    uint8_t *dst = s_act + (size_t)(n * nb + (u >> 4)) * kStagedBlock + (u & 15) * 4;
+                    *reinterpret_cast<uint32_t *>(dst) = v[k].x;
+                    *reinterpret_cast<uint32_t *>(dst + kLane6) = v[k].y;
+                    *reinterpret_cast<uint32_t *>(dst + 2 * kLane6) = v[k].z;
+                    *reinterpret_cast<uint32_t *>(dst + 3 * kLane6) = v[k].w;
+                }
             }
+        }
+        for (int i = threadIdx.x; i < M * nb * 16; i += KW * 32) {
+            const int n = i / (nb * 16), r = i - n * nb * 16, b = r >> 4, s = r & 15;
+            const int bs = n < m ? a.sums16[(size_t)n * nb * 16 + r] : 0;
+            uint8_t *sp = s_act + (size_t)(n * nb + b) * kStagedBlock + 4 * kLane6;
+            sp[s] = (uint8_t)(bs & 63);
+            sp[16 + s] = (uint8_t)(int8_t)(bs >> 6);
         }
         for (int i = threadIdx.x; i < nb * 8; i += KW * 32) {
             const int b = i >> 3, n = i & 7;

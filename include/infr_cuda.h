@@ -248,6 +248,11 @@ typedef struct {
     float scale;
     int32_t norm_w;
     int32_t router_dtype, gate_dtype, up_dtype, down_dtype; /* INFR_DT_* */
+    /* Expert parallelism (no counterpart in the reference): n_local != 0 says the banks hold only experts
+     * [expert_lo, expert_lo + n_local) — bank index = expert - expert_lo — and dst receives only their
+     * contribution; the router stays whole and every rank routes every row, so the ranks' dst add up to the
+     * unsharded result (the caller all-reduces them).  n_local == 0: all experts are here.  Needs rows >= 2. */
+    uint32_t expert_lo, n_local;
 } infr_moe_desc;
 INFR_API int32_t infr_cuda_moe_ffn(infr_cuda_ctx *ctx, const infr_moe_desc *desc, const infr_cuda_buf *x,
                                    const infr_cuda_buf *router_x, const infr_cuda_buf *router,

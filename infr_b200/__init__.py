@@ -72,7 +72,8 @@ class _OpDesc(C.Structure):
 class _MoeDesc(C.Structure):
     _fields_ = [("rows", C.c_uint32), ("ne", C.c_uint32), ("n_expert", C.c_uint32), ("n_used", C.c_uint32),
                 ("n_ff_exp", C.c_uint32), ("scale", C.c_float), ("norm_w", C.c_int32), ("router_dtype", C.c_int32),
-                ("gate_dtype", C.c_int32), ("up_dtype", C.c_int32), ("down_dtype", C.c_int32)]
+                ("gate_dtype", C.c_int32), ("up_dtype", C.c_int32), ("down_dtype", C.c_int32),
+                ("expert_lo", C.c_uint32), ("n_local", C.c_uint32)]
 
 
 class _GraphDesc(C.Structure):
@@ -444,8 +445,10 @@ class CudaBackend:
     def moe_ffn(self, x: Buffer, router_x: Buffer, router: Buffer, gate: Buffer, up: Buffer, down: Buffer, dst: Buffer, *,
                 rows: int, ne: int, n_expert: int, n_used: int, n_ff_exp: int, scale: float = 1.0, norm_w: bool = True,
                 wdt: int = Q4K, sel_ids: Optional[Buffer] = None, sel_w: Optional[Buffer] = None,
-                logits: Optional[Buffer] = None):
-        d = _MoeDesc(rows, ne, n_expert, n_used, n_ff_exp, scale, int(norm_w), F32, wdt, wdt, wdt)
+                logits: Optional[Buffer] = None, expert_lo: int = 0, n_local: int = 0):
+        """Op::MoeFfn as a direct call.  n_local != 0: expert-parallel slice — the banks hold experts
+        [expert_lo, expert_lo + n_local) and dst gets their contribution only (the ranks' dst add up)."""
+        d = _MoeDesc(rows, ne, n_expert, n_used, n_ff_exp, scale, int(norm_w), F32, wdt, wdt, wdt, expert_lo, n_local)
         h = lambda b: b.handle if b is not None else None
         self._check(self.L.infr_cuda_moe_ffn(self.ctx, C.byref(d), x.handle, router_x.handle, router.handle, gate.handle,
                                              up.handle, down.handle, dst.handle, h(sel_ids), h(sel_w), h(logits)))

@@ -397,7 +397,10 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
     if (a.n_expert == 0 || a.n_expert > 1024 || a.n_used == 0 || a.n_used > 32 || a.n_used > a.n_expert)
         return Status::Err(INFR_E_INVALID, fmt("moe_ffn: n_expert=%u (<=1024), n_used=%u (<=32)", a.n_expert, a.n_used));
     if (a.rows == 0) return Status::Ok();
-    if (a.rows < 2 || reference_) return moe_ffn_f32(a);
+    if (a.rows < 2 || reference_) {
+        if (a.n_local != a.n_expert) return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: a local expert range needs the int8 path (rows >= 2, no reference mode)");
+        return moe_ffn_f32(a);
+    }
     cudaSetDevice(device_);
     const size_t rows = a.rows, ne = a.ne, nff = a.n_ff, nu = a.n_used, nx = a.n_expert;
     const size_t n_pairs = rows * nu;
@@ -441,18 +444,18 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
     } while (0)
     INFR_STEP(launch_moe_router(a.router, a.router_x, logits, (int)rows, (int)ne, (int)nx, stream_), "moe router");
     INFR_STEP(launch_moe_route(logits, (int)rows, (int)nx, (int)nu, a.scale, a.norm_w, ids, w, stream_), "moe route");
-    INFR_STEP(launch_moe_bucket(ids, (int)rows, (int)nu, (int)nx, prow, pslot, ie, ip, ic, ni, nullptr, stream_), "moe bucket");
+    INFR_STEP(launch_moe_bucket(ids, (int)rows, (int)nu, (int)nx, (int)a.expert_lo, (int)a.n_local, prow, pslot, ie, ip, ic, ni, nullptr, stream_), "moe bucket");
     // stage A: every distinct row quantised once (lib.rs:2688-2718)
     INFR_STEP(launch_quantize_q8(a.x, (int)rows, (int)ne, 256, xq, xd, xs, nullptr, nullptr, nullptr, stream_), "moe quantize x");
     Q8Dev xa{xq, xd, xs, nullptr, 256};
     // stage B: gate and up expert GEMMs, rows gathered per pair
-    INFR_STEP(launch_grouped_q4k_mma(a.gate, (int)nx, xa, g, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_items, dev_, status_dev_, stream_), "moe gate");
-    INFR_STEP(launch_grouped_q4k_mma(a.up, (int)nx, xa, u, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_items, dev_, status_dev_, stream_), "moe up");
+    INFR_STEP(launch_grouped_q4k_mma(a.gate, (int)a.n_local, xa, g, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_items, dev_, status_dev_, stream_), "moe gate");
+    INFR_STEP(launch_grouped_q4k_mma(a.up, (int)a.n_local, xa, u, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_items, dev_, status_dev_, stream_), "moe up");
     // stage C: SwiGLU and re-quantisation per pair
     INFR_STEP(launch_moe_swiglu_quant(g, u, (int)n_pairs, (int)nff, aq, ad, as, nullptr, stream_), "moe swiglu");
     Q8Dev aa{aq, ad, as, nullptr, 256};
     // stage D: down GEMMs; stage E: rank-order combine
-    INFR_STEP(launch_grouped_q4k_mma(a.down, (int)nx, aa, y, (int)nff, (int)ne, ie, ip, ic, ni, nullptr, (int)max_items, dev_, status_dev_, stream_), "moe down");
+    INFR_STEP(launch_grouped_q4k_mma(a.down, (int)a.n_local, aa, y, (int)nff, (int)ne, ie, ip, ic, ni, nullptr, (int)max_items, dev_, status_dev_, stream_), "moe down");
     INFR_STEP(launch_moe_combine(y, pslot, w, (int)rows, (int)nu, (int)ne, a.dst, stream_), "moe combine");
 #undef INFR_STEP
     return Status::Ok();
@@ -592,7 +595,7 @@ Status CudaBackend::execute(infr_cuda_plan *plan, infr_cuda_buf *const *bindings
             if (!(s = resolve(op.t[6], (size_t)rows * ne * 4, "MoeFfn dst", &dst)).ok()) return s;
             MoeArgs a{reinterpret_cast<const float *>(x.ptr), reinterpret_cast<const float *>(rx.ptr), reinterpret_cast<const float *>(r.ptr),
                       gt.ptr, up.ptr, dn.ptr, DT_Q4K, DT_Q4K, DT_Q4K, reinterpret_cast<float *>(dst.ptr), rows, ne, nx, nu, nff, op.f[0],
-                      (int)op.u[4], nullptr, nullptr, nullptr};
+                      (int)op.u[4], nullptr, nullptr, nullptr, 0u, nx};
             s = moe_ffn(a);
             if (!s.ok()) return s;
         } else {

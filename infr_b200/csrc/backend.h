@@ -100,6 +100,7 @@ public:
         int norm_w;
         int32_t *sel_ids;
         float *sel_w, *logits;
+        uint32_t expert_lo, n_local;  // the banks hold experts [expert_lo, expert_lo + n_local)
     };
     Status moe_ffn(const MoeArgs &a);
     Status moe_ffn_f32(const MoeArgs &a);

@@ -296,8 +296,10 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx *ctx, const infr_moe_desc *d, const infr
     auto bank_bytes = [&](int dt, size_t out_f, size_t in_f) -> size_t {
         const int be = infr::block_elems(dt), bb = infr::block_bytes(dt);
         if (!bb || in_f % (size_t)be) return (size_t)-1;
-        return (size_t)d->n_expert * out_f * (in_f / (size_t)be) * (size_t)bb;
+        return (size_t)(d->n_local ? d->n_local : d->n_expert) * out_f * (in_f / (size_t)be) * (size_t)bb;
     };
+    if (d->n_local && ((uint64_t)d->expert_lo + d->n_local > d->n_expert))
+        return finish(ctx, Status::Err(INFR_E_INVALID, "moe_ffn: the local expert range leaves [0, n_expert)"));
     const size_t rows = d->rows, ne = d->ne, nff = d->n_ff_exp;
     uint8_t *px, *prx, *pr, *pg, *pu, *pd, *pdst, *pids = nullptr, *pw = nullptr, *plog = nullptr;
     Status s;
@@ -313,7 +315,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx *ctx, const infr_moe_desc *d, const infr
     if (logits && !(s = span(logits, rows * d->n_expert * 4, "moe_ffn logits", &plog)).ok()) return finish(ctx, s);
     CudaBackend::MoeArgs a{(const float *)px, (const float *)prx, (const float *)pr, pg, pu, pd, d->gate_dtype, d->up_dtype, d->down_dtype,
                            (float *)pdst, d->rows, d->ne, d->n_expert, d->n_used, d->n_ff_exp, d->scale, d->norm_w,
-                           (int32_t *)pids, (float *)pw, (float *)plog};
+                           (int32_t *)pids, (float *)pw, (float *)plog, d->n_local ? d->expert_lo : 0u, d->n_local ? d->n_local : d->n_expert};
     return finish(ctx, ctx->be->moe_ffn(a));
 }
 

@@ -87,7 +87,7 @@ cudaError_t launch_moe_router(const float *router, const float *x, float *logits
                               cudaStream_t st);
 cudaError_t launch_moe_route(const float *logits, int rows, int n_expert, int n_used, float scale, int norm_w,
                              int32_t *sel_ids, float *sel_w, cudaStream_t st);
-cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int n_expert, int32_t *pair_row,
+cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int n_expert, int e_lo, int n_local, int32_t *pair_row,
                               int32_t *pair_of_slot, int32_t *item_expert, int32_t *item_p0, int32_t *item_cnt,
                               int32_t *n_items, int32_t *counts_out, cudaStream_t st);
 cudaError_t launch_moe_swiglu_quant(const float *gate, const float *up, int n_pairs, int nff, int8_t *qs, float *d,

@@ -101,7 +101,10 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
 // 32 pairs at a time, the block scans the counts, then the warp lists the pairs in (row, rank) order
 // (ballot + prefix popcount keeps the order) and cuts them into work items of up to 8 rows.
 //   pair_row[p], pair_of_slot[r * n_used + rank] = p, item_{expert,p0,cnt}[], n_items
+// Expert parallelism: only experts [e_lo, e_lo + n_local) are listed (item_expert is the index inside this
+// rank's banks); pairs routed elsewhere get pair_of_slot = -1 and contribute nothing to this rank's output.
 __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restrict__ sel_ids, int rows, int n_used, int n_expert,
+                                                          int e_lo, int n_local,
                                                           int32_t *__restrict__ pair_row, int32_t *__restrict__ pair_of_slot,
                                                           int32_t *__restrict__ item_expert, int32_t *__restrict__ item_p0,
                                                           int32_t *__restrict__ item_cnt, int32_t *__restrict__ n_items,
@@ -109,8 +112,17 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
     __shared__ int s_cnt[1024], s_off[1024], s_ioff[1024];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_pairs = rows * n_used;
+    if (n_local < n_expert)
+        for (int i = threadIdx.x; i < n_pairs; i += 1024) {
+            const int e = sel_ids[i];
+            if (e < e_lo || e >= e_lo + n_local) pair_of_slot[i] = -1;
+        }
     for (int e = warp; e < n_expert; e += 32) {
         int cnt = 0;
+        if (e < e_lo || e >= e_lo + n_local) {  // not this rank's expert: no pairs, no items
+            if (lane == 0) s_cnt[e] = 0;
+            continue;
+        }
         for (int i0 = 0; i0 < n_pairs; i0 += 32) {
             const int i = i0 + lane;
             cnt += __popc(__ballot_sync(0xffffffffu, i < n_pairs && sel_ids[i] == e));
@@ -132,6 +144,7 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
     for (int e = warp; e < n_expert; e += 32) {
         const int cnt = s_cnt[e];
         if (counts_out && lane == 0) counts_out[e] = cnt;
+        if (e < e_lo || e >= e_lo + n_local) continue;
         int p = s_off[e];
         for (int i0 = 0; i0 < n_pairs; i0 += 32) {
             const int i = i0 + lane;
@@ -146,7 +159,7 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
         }
         for (int c = lane * 8; c < cnt; c += 256) {
             const int it = s_ioff[e] + c / 8;
-            item_expert[it] = e;
+            item_expert[it] = e - e_lo;
             item_p0[it] = s_off[e] + c;
             item_cnt[it] = cnt - c < 8 ? cnt - c : 8;
         }
@@ -213,6 +226,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restric
     float o = 0.f;
     for (int k = 0; k < n_used; k++) {
         const int p = pair_of_slot ? pair_of_slot[(size_t)r * n_used + k] : r * n_used + k;
+        if (p < 0) continue;  // routed to an expert of another rank
         o = __fadd_rn(o, __fmul_rn(sel_w[(size_t)r * n_used + k], y_pairs[(size_t)p * ne + i]));
     }
     out[idx] = o;
@@ -236,11 +250,11 @@ cudaError_t launch_moe_route(const float *logits, int rows, int n_expert, int n_
     return cudaGetLastError();
 }
 
-cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int n_expert, int32_t *pair_row,
+cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int n_expert, int e_lo, int n_local, int32_t *pair_row,
                               int32_t *pair_of_slot, int32_t *item_expert, int32_t *item_p0, int32_t *item_cnt,
                               int32_t *n_items, int32_t *counts_out, cudaStream_t st) {
     if (n_expert > 1024) return cudaErrorInvalidValue;
-    moe_bucket_kernel<<<1, 1024, 0, st>>>(sel_ids, rows, n_used, n_expert, pair_row, pair_of_slot, item_expert, item_p0, item_cnt,
+    moe_bucket_kernel<<<1, 1024, 0, st>>>(sel_ids, rows, n_used, n_expert, e_lo, n_local, pair_row, pair_of_slot, item_expert, item_p0, item_cnt,
                                           n_items, counts_out);
     return cudaGetLastError();
 }

@@ -136,3 +136,39 @@ def test_moe_reference_mode_backend(oracle):
         assert np.abs(got - want).max() / np.abs(want).max() < 1e-5
     finally:
         be.close()
+
+
+def test_expert_parallel_slices_add_up_to_the_whole_layer(backend):
+    """Two 'ranks' run one after the other on the same GPU, each with its half of the expert banks; their outputs
+    add up to the unsharded layer's (the per-pair values are the same bits, only the order of the final adds
+    differs), and a slice whose experts nobody picked contributes exactly zero."""
+    rows, ne, nx, nu, nff = 24, 512, 8, 2, 256
+    blk = lambda o, i, seed: synth.weight(Q4K, o, i, seed)
+    gate = np.concatenate([blk(nff, ne, 50 + e) for e in range(nx)])
+    up = np.concatenate([blk(nff, ne, 70 + e) for e in range(nx)])
+    down = np.concatenate([blk(ne, nff, 90 + e) for e in range(nx)])
+    router = synth.normal(3, (nx, ne), 1.0 / np.sqrt(ne))
+    x = synth.normal(4, (rows, ne))
+    per_g, per_d = gate.nbytes // nx, down.nbytes // nx
+    xb, rb = backend.from_numpy(x), backend.from_numpy(router)
+    kw = dict(rows=rows, ne=ne, n_expert=nx, n_used=nu, n_ff_exp=nff)
+
+    def run(lo, n):
+        g = backend.from_numpy(gate[lo * per_g:(lo + n) * per_g], infr_b200.USAGE_WEIGHTS)
+        u = backend.from_numpy(up[lo * per_g:(lo + n) * per_g], infr_b200.USAGE_WEIGHTS)
+        d = backend.from_numpy(down[lo * per_d:(lo + n) * per_d], infr_b200.USAGE_WEIGHTS)
+        dst = backend.alloc(rows * ne * 4)
+        backend.moe_ffn(xb, xb, rb, g, u, d, dst, expert_lo=lo, n_local=n, **kw)
+        out = backend.download(dst, np.float32).reshape(rows, ne)
+        for b in (g, u, d, dst):
+            b.close()
+        return out
+
+    whole = run(0, nx)
+    halves = run(0, nx // 2) + run(nx // 2, nx // 2)
+    assert np.abs(whole).max() > 1e-3
+    assert fx.rel_l2(halves, whole) < 1e-6
+    thirds = run(0, 3) + run(3, 3) + run(6, 2)
+    assert fx.rel_l2(thirds, whole) < 1e-6
+    with pytest.raises(infr_b200.BackendError):
+        run(6, 3)  # leaves [0, n_expert)

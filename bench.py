@@ -450,6 +450,69 @@ def _tp_decode(be, infr_b200, dist, rank, world, local, steps, warmup):
             "not_included": "attention, norms, RoPE, sampling (not built)"}
 
 
+def _ep_moe(be, infr_b200, dist, rank, world, local, steps, warmup):
+    """Expert-parallel form of the C4 MoE layer: every rank holds 128 / N experts and all 256 tokens, routes all
+    tokens (the router is replicated), runs its experts' grouped GEMMs and adds its share of the output; the
+    shares are summed by one NCCL all-reduce of the [256, 2048] f32 result (2 MB) on the backend's stream, the
+    layer and the exchange in one CUDA graph.  With all tokens resident everywhere no token dispatch is needed;
+    an all-to-all dispatch (tokens sharded) is not built.  Strong scaling: one layer on N GPUs."""
+    import torch
+    from infr_b200 import synth
+
+    dev = torch.device("cuda", local)
+    rows, ne, nx, nu, nff = 256, 2048, 128, 8, 768
+    n_local = nx // world
+    lo = rank * n_local
+    gate = be.from_numpy(synth.random_blocks(infr_b200.Q4K, n_local * nff * ne, 100 + rank), infr_b200.USAGE_WEIGHTS)
+    up = be.from_numpy(synth.random_blocks(infr_b200.Q4K, n_local * nff * ne, 200 + rank), infr_b200.USAGE_WEIGHTS)
+    down = be.from_numpy(synth.random_blocks(infr_b200.Q4K, n_local * ne * nff, 300 + rank), infr_b200.USAGE_WEIGHTS)
+    router = be.from_numpy(synth.normal(7, (nx, ne), 1.0 / np.sqrt(ne)))
+    x = be.from_numpy(synth.normal(8, (rows, ne)))
+    out_t = torch.zeros(rows * ne, dtype=torch.float32, device=dev)
+    torch.cuda.synchronize(dev)
+    dst = be.wrap(out_t.data_ptr(), rows * ne * 4, infr_b200.USAGE_ACTIVATIONS)
+    kw = dict(rows=rows, ne=ne, n_expert=nx, n_used=nu, n_ff_exp=nff, expert_lo=lo, n_local=n_local)
+
+    def step():
+        be.moe_ffn(x, x, router, gate, up, down, dst, **kw)
+        if world > 1:
+            dist.all_reduce(out_t)
+
+    ext = torch.cuda.ExternalStream(be.stream(), device=dev)
+    mode = "cuda graph"
+    with torch.cuda.stream(ext):
+        for _ in range(3):
+            step()
+        ext.synchronize()
+        graph = None
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=ext):
+                step()
+        except Exception as e:
+            graph, mode = None, f"eager ({type(e).__name__}: {str(e)[:80]})"
+        run = graph.replay if graph is not None else step
+        for _ in range(warmup):
+            run()
+        ext.synchronize()
+        _barrier(dist)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ext)
+        for _ in range(steps):
+            run()
+        e1.record(ext)
+        e1.synchronize()
+        ms = e0.elapsed_time(e1)
+        del graph
+    us = _max_over_ranks(dist, ms) * 1e3 / steps
+    be.sync()
+    for b in (dst, gate, up, down, router, x):
+        b.close()
+    return {"workload": f"expert-parallel MoE layer, {world} GPU(s): 256 tok x hidden 2048, {n_local} of 128 experts per rank "
+                        f"(2048->768->2048, Q4_K), softmax top-8, tokens replicated, 1 NCCL all-reduce of 2 MB",
+            "us_per_layer": us, "mode": mode, "scaling": "strong"}
+
+
 # ------------------------------------------------------------------------------------------------
 def run_b200(args):
     import infr_b200
@@ -568,8 +631,10 @@ def run_b200(args):
 
     if not args.no_sweep:
         tp = _tp_decode(be, infr_b200, dist, rank, world, local, 10, 3)
+        ep = _ep_moe(be, infr_b200, dist, rank, world, local, 20, 3)
         if rank == 0:
             out["tp_decode"] = tp
+            out["ep_moe"] = ep
 
     if rank == 0 and world == 1 and not args.no_cpu:
         out["cpu_baseline"] = _cpu_baseline(w, x, budget_s=10.0)

@@ -16,18 +16,18 @@
 //   warps 0-7    unpack: thread = (weight row, K half of the block); turns its 4 sub-blocks into int8 operand words
 //                and stores them into TENSOR MEMORY (tcgen05.st), a ring of three half-block slots; the A operand
 //                of the MMAs is read from there, so shared memory carries only the token side
-//                (warps 0-3 also write the tf32 min planes and the row scale d)
+//                (each half also writes its K plane of the tf32 min operands; warps 0-3 the row scale d)
 //   warps 8-15   epilogue: warp = (tensor-memory lane quarter, 32-column half); folds each job's int32 sums
 //                into 32 running f32 sums per thread
 //   warp 16      TMA producer: raw Q4_K rows + activation planes (codes, tf32 block-sum pieces), five stages
-//   warp 17      MMA issuer: per job 16 kind::i8 + 3 kind::tf32 instructions; its barrier waits are spread
-//                over lanes so that they complete together
+//   warps 17-19  MMA issuers, one per accumulator chain (D_lo: 8 kind::i8 per job, D_hi: 8, min sums: 3
+//                kind::tf32): a tcgen05.mma holds its issuing thread ~90 cycles but threads issue concurrently
 // Tensor memory (512 columns): accumulators {D_lo, D_hi} x 2 jobs = 256, min sums 64, operand ring 3 x 64.
 //
 // Measured on B200 and limiting this kernel: a tcgen05.mma with 32 bytes of K (kind::i8 K = 32, kind::tf32
 // K = 8) occupies the issuing thread and the tensor pipe ~95 cycles for every N <= 128 (N = 256: 138), from
-// shared-memory or tensor-memory operands alike, so the 19 instructions of a 64-token job cost ~1700 cycles
-// where their arithmetic needs 600; accumulators leave tensor memory at ~128 B/clk per SM; one mbarrier
+// shared-memory or tensor-memory operands alike — per issuing THREAD: two threads issue at twice the rate, which
+// is why the job's 19 instructions are split over three issuer warps; accumulators leave tensor memory at ~128 B/clk per SM; one mbarrier
 // operation costs its thread ~100 cycles.
 // Every wait is bounded: on expiry the role raises a CTA flag and a status word, every role leaves its
 // loop, in-flight copies are drained and the tensor memory is freed.
@@ -48,7 +48,7 @@ constexpr int kStageBytes = kRawBytes + kActBytes;
 constexpr int kMinBytes = 4 * kTM * 16;       // A1 planes [2], A2 planes [2]
 constexpr int kRing = 4;                      // depth of the row-scale ring read by the epilogue
 constexpr int kSmem = kStages * kStageBytes + 2 * kMinBytes + kRing * kTM * 4;
-constexpr int kThreadsWs = 18 * 32;
+constexpr int kThreadsWs = 20 * 32;
 constexpr uint32_t kSpin = 1u << 22;
 // tensor-memory columns
 constexpr uint32_t kColMin = 256, kColA = 320, kSlotCols = 64, kSlots = 3;
@@ -56,7 +56,7 @@ constexpr uint32_t kColMin = 256, kColA = 320, kSlotCols = 64, kSlots = 3;
 // barrier indices: FULL[stage] (TMA bytes), DONE[stage] (the job's last commit), AREADY/AFREE[operand slot],
 // ACCFREE[accumulator] (8 epilogue warps), MINFREE (8 epilogue warps), DRAIN
 constexpr int B_FULL = 0, B_DONE = B_FULL + kStages, B_AREADY = B_DONE + kStages, B_AFREE = B_AREADY + kSlots,
-              B_ACCFREE = B_AFREE + kSlots, B_MINFREE = B_ACCFREE + 2, B_DRAIN = B_MINFREE + 1, B_COUNT = B_DRAIN + 1;
+              B_ACCFREE = B_AFREE + kSlots, B_MINFREE = B_ACCFREE + 2, B_DRAIN = B_MINFREE + 1, B_COUNT = B_DRAIN + 3;
 
 __device__ __forceinline__ uint32_t su32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint64_t mk_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
@@ -222,7 +222,11 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
     if (tid == 0) {
         s_dead = 0;
         for (int i = 0; i < B_COUNT; i++) {
-            const int cnt = (i >= B_AREADY && i < B_AREADY + kSlots) ? 4 : (i >= B_ACCFREE && i <= B_MINFREE) ? 8 : 1;
+            const int cnt = (i >= B_AREADY && i < B_AREADY + kSlots)  ? 4    // the four unpack warps of a K half
+                            : (i >= B_ACCFREE && i <= B_MINFREE)      ? 8    // the epilogue warps
+                            : (i >= B_AFREE && i < B_AFREE + kSlots)  ? 2    // the D_lo and D_hi issuers
+                            : (i >= B_DONE && i < B_DONE + kStages)   ? 3    // all three issuers
+                                                                      : 1;
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(su32(&bars[i])), "r"(cnt));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -269,10 +273,13 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                     wait_plain(bar(B_FULL + k % kStages), (uint32_t)((k / kStages) & 1), 1u << 16);
             }
         }
-    } else if (warp == 17) {
-        // ------------------------------------------------------------------ MMA issuer
-        // One barrier operation costs its thread ~100 cycles, so the job's four waits are spread over four
-        // lanes and complete together; lane 0 then issues the job's MMAs and its three commits.
+    } else if (warp >= 17) {
+        // ------------------------------------------------------------------ MMA issuers
+        // A tcgen05.mma keeps its issuing thread ~90 cycles whatever its size, but threads issue concurrently
+        // (two threads: twice the rate), so the job's instructions are split over three warps by accumulator
+        // chain: D_lo, D_hi, and the tf32 min sums.  Each issuer commits for itself; the barriers the chains
+        // share count one arrival per issuer.  A role's waits are spread over lanes and complete together.
+        const int role = warp - 17;  // 0: D_lo, 1: D_hi, 2: min sums
         const uint32_t idesc_i8 = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(kTN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
         const uint32_t idesc_tf = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
         const uint32_t tmin = tmem + kColMin;
@@ -287,11 +294,11 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 uint32_t wb = 0, wp = 0;
                 bool need = false;
                 if (lane == 0) wb = bar(B_FULL + ls), wp = (uint32_t)((j / kStages) & 1), need = true;
-                if (lane == 1) wb = bar(B_ACCFREE + s), wp = (uint32_t)(((j >> 1) - 1) & 1), need = j >= 2;
-                if (lane == 2) wb = bar(B_AREADY + slot0), wp = (uint32_t)(n0 & 1), need = true;
+                if (lane == 1) wb = bar(B_ACCFREE + s), wp = (uint32_t)(((j >> 1) - 1) & 1), need = role < 2 && j >= 2;
+                if (lane == 2) wb = bar(B_AREADY + slot0), wp = (uint32_t)(n0 & 1), need = true;  // operands and min planes
                 if (lane == 3) wb = bar(B_AREADY + slot1), wp = (uint32_t)(n1 & 1), need = true;
                 // the tile's first min MMA overwrites the sums of the previous tile: the epilogue has read them
-                if (lane == 4) wb = bar(B_MINFREE), wp = (uint32_t)((tile_i - 1) & 1), need = b == 0 && tile_i >= 1;
+                if (lane == 4) wb = bar(B_MINFREE), wp = (uint32_t)((tile_i - 1) & 1), need = role == 2 && b == 0 && tile_i >= 1;
                 if (!wait_multi(wb, wp, need, dead)) {
                     ok = false;
                     break;
@@ -300,25 +307,26 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 tc_fence_after();
                 if (lane == 0) {
                     const uint64_t db0 = mk_desc(su32(stage0 + (size_t)ls * kStageBytes + kRawBytes), kTN * 16, 128);
-                    const uint8_t *mb = minbuf0 + (size_t)s * kMinBytes;
-                    const uint64_t am[3] = {mk_desc(su32(mb), kTM * 16, 128), mk_desc(su32(mb + 2 * kTM * 16), kTM * 16, 128),
-                                            mk_desc(su32(mb), kTM * 16, 128)};
-                    const uint64_t bm[3] = {db0 + (uint64_t)(16 * kTN), db0 + (uint64_t)(16 * kTN), db0 + (uint64_t)(18 * kTN)};
-                    const uint32_t td = tmem + (uint32_t)s * 2 * kTN;
+                    if (role == 2) {
+                        const uint8_t *mb = minbuf0 + (size_t)s * kMinBytes;
+                        const uint64_t a1 = mk_desc(su32(mb), kTM * 16, 128), a2 = mk_desc(su32(mb + 2 * kTM * 16), kTM * 16, 128);
+                        const uint64_t b1 = db0 + (uint64_t)(16 * kTN), b2 = db0 + (uint64_t)(18 * kTN);
+                        mma_tf32(tmin, a1, b1, idesc_tf, b > 0 ? 1u : 0u);
+                        mma_tf32(tmin, a2, b1, idesc_tf, 1u);
+                        mma_tf32(tmin, a1, b2, idesc_tf, 1u);
+                    } else {
+                        const uint32_t td = tmem + (uint32_t)s * 2 * kTN + (uint32_t)role * kTN;
 #pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const uint32_t ta = tmem + kColA + (uint32_t)(h ? slot1 : slot0) * kSlotCols;
+                        for (int h = 0; h < 2; h++) {
+                            const uint32_t ta = tmem + kColA + (uint32_t)(h ? slot1 : slot0) * kSlotCols + (uint32_t)role * 32;
 #pragma unroll
-                        for (int sbl = 0; sbl < 4; sbl++) {
-                            const int sb = 4 * h + sbl;
-                            // sub-block sb = activation planes 2sb, 2sb+1: the descriptor start address counts 16-byte units
-                            const uint64_t db = db0 + (uint64_t)(sb * 2 * kTN);
-                            mma_i8_ta(td, ta + (uint32_t)(sbl * 8), db, idesc_i8, sb > 0 ? 1u : 0u);
-                            mma_i8_ta(td + kTN, ta + 32 + (uint32_t)(sbl * 8), db, idesc_i8, sb > 0 ? 1u : 0u);
-                            // the three min MMAs ride between the pairs as a third accumulator chain
-                            if (h == 0 && sbl < 3) mma_tf32(tmin, am[sbl], bm[sbl], idesc_tf, (b > 0 || sbl > 0) ? 1u : 0u);
+                            for (int sbl = 0; sbl < 4; sbl++) {
+                                const int sb = 4 * h + sbl;
+                                // sub-block sb = activation planes 2sb, 2sb+1: the descriptor start address counts 16-byte units
+                                mma_i8_ta(td, ta + (uint32_t)(sbl * 8), db0 + (uint64_t)(sb * 2 * kTN), idesc_i8, sb > 0 ? 1u : 0u);
+                            }
+                            mma_commit(bar(B_AFREE + (h ? slot1 : slot0)));
                         }
-                        mma_commit(bar(B_AFREE + (h ? slot1 : slot0)));
                     }
                     mma_commit(bar(B_DONE + ls));
                 }
@@ -332,8 +340,8 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
         }
         if (lane == 0) {
             // every issued MMA has completed before the tensor memory is freed
-            mma_commit(bar(B_DRAIN));
-            wait_plain(bar(B_DRAIN), 0u, 1u << 20);
+            mma_commit(bar(B_DRAIN + role));
+            wait_plain(bar(B_DRAIN + role), 0u, 1u << 20);
         }
     } else if (warp < 8) {
         // ------------------------------------------------------------------ unpack warps
@@ -351,6 +359,8 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 bool need = false;
                 if (lane == 0) wb = bar(B_FULL + ls), wp = (uint32_t)((j / kStages) & 1), need = true;
                 if (lane == 1) wb = bar(B_AFREE + slot), wp = (uint32_t)((n - 1) & 1), need = n >= 1;
+                // the min planes of job j - 2 (same buffer) have been read by the min issuer's MMAs
+                if (lane == 2) wb = bar(B_DONE + (j - 2 + kStages) % kStages), wp = (uint32_t)((((j - 2) / kStages)) & 1), need = j >= 2;
                 if (!wait_multi(wb, wp, need, dead)) {
                     ok = false;
                     break;
@@ -388,22 +398,21 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                         tst8(ts + 32 + (uint32_t)(sbl * 8), hi);
                     }
                 }
-                if (h == 0) {
-                    // min planes: dmin * m_s = A1 + A2 exactly, both representable in tf32
-                    const float dw = h2f(hdr.x), dminw = h2f(hdr.x >> 16);
-                    uint32_t p1[8], p2[8];
+                {
+                    // min planes of this half's four sub-blocks (K plane h of A1 and of A2): dmin * m_s = A1 + A2
+                    // exactly, both representable in tf32
+                    const float dminw = h2f(hdr.x >> 16);
+                    uint32_t p1[4], p2[4];
 #pragma unroll
-                    for (int s8 = 0; s8 < 8; s8++) {
-                        const float v = dminw * (float)((mn[s8 >> 2] >> (8 * (s8 & 3))) & 0xFFu);
-                        p1[s8] = __float_as_uint(v) & 0xFFFFE000u;
-                        p2[s8] = __float_as_uint(v - __uint_as_float(p1[s8]));
+                    for (int s4 = 0; s4 < 4; s4++) {
+                        const float v = dminw * (float)((mn[h] >> (8 * s4)) & 0xFFu);
+                        p1[s4] = __float_as_uint(v) & 0xFFFFE000u;
+                        p2[s4] = __float_as_uint(v - __uint_as_float(p1[s4]));
                     }
-                    uint8_t *mp = minbuf0 + (size_t)(j & 1) * kMinBytes + (size_t)row * 16;
+                    uint8_t *mp = minbuf0 + (size_t)(j & 1) * kMinBytes + (size_t)(h * kTM + row) * 16;
                     *reinterpret_cast<uint4 *>(mp) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
-                    *reinterpret_cast<uint4 *>(mp + kTM * 16) = make_uint4(p1[4], p1[5], p1[6], p1[7]);
                     *reinterpret_cast<uint4 *>(mp + 2 * kTM * 16) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
-                    *reinterpret_cast<uint4 *>(mp + 3 * kTM * 16) = make_uint4(p2[4], p2[5], p2[6], p2[7]);
-                    dwring[(j % kRing) * kTM + row] = dw;
+                    if (h == 0) dwring[(j % kRing) * kTM + row] = h2f(hdr.x);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
                 if (quarter == 0) TR(2 + h, j, 2);

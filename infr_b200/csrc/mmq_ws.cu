@@ -16,7 +16,7 @@
 //   warps 0-7    unpack: thread = (weight row, K half of the block); turns its 4 sub-blocks into int8 operand words
 //                and stores them into TENSOR MEMORY (tcgen05.st), a ring of three half-block slots; the A operand
 //                of the MMAs is read from there, so shared memory carries only the token side
-//                (each half also writes its K plane of the tf32 min operands; warps 0-3 the row scale d)
+//                (warps 0-3 also write the tf32 min planes and the row scale d)
 //   warps 8-15   epilogue: warp = (tensor-memory lane quarter, 32-column half); folds each job's int32 sums
 //                into 32 running f32 sums per thread
 //   warp 16      TMA producer: raw Q4_K rows + activation planes (codes, tf32 block-sum pieces), five stages
@@ -54,9 +54,9 @@ constexpr uint32_t kSpin = 1u << 22;
 constexpr uint32_t kColMin = 256, kColA = 320, kSlotCols = 64, kSlots = 3;
 
 // barrier indices: FULL[stage] (TMA bytes), DONE[stage] (the job's last commit), AREADY/AFREE[operand slot],
-// ACCFREE[accumulator] (8 epilogue warps), MINFREE (8 epilogue warps), DRAIN
+// ACCFREE[accumulator] (8 epilogue warps), MINFREE (8 epilogue warps), MINREADY[min-plane buffer] (4 unpack warps), DRAIN
 constexpr int B_FULL = 0, B_DONE = B_FULL + kStages, B_AREADY = B_DONE + kStages, B_AFREE = B_AREADY + kSlots,
-              B_ACCFREE = B_AFREE + kSlots, B_MINFREE = B_ACCFREE + 2, B_DRAIN = B_MINFREE + 1, B_COUNT = B_DRAIN + 3;
+              B_ACCFREE = B_AFREE + kSlots, B_MINFREE = B_ACCFREE + 2, B_MINREADY = B_MINFREE + 1, B_DRAIN = B_MINREADY + 2, B_COUNT = B_DRAIN + 3;
 
 __device__ __forceinline__ uint32_t su32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint64_t mk_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
@@ -223,6 +223,7 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
         s_dead = 0;
         for (int i = 0; i < B_COUNT; i++) {
             const int cnt = (i >= B_AREADY && i < B_AREADY + kSlots)  ? 4    // the four unpack warps of a K half
+                            : (i >= B_MINREADY && i < B_MINREADY + 2) ? 4    // the four unpack warps that write the min planes
                             : (i >= B_ACCFREE && i <= B_MINFREE)      ? 8    // the epilogue warps
                             : (i >= B_AFREE && i < B_AFREE + kSlots)  ? 2    // the D_lo and D_hi issuers
                             : (i >= B_DONE && i < B_DONE + kStages)   ? 3    // all three issuers
@@ -295,8 +296,13 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 bool need = false;
                 if (lane == 0) wb = bar(B_FULL + ls), wp = (uint32_t)((j / kStages) & 1), need = true;
                 if (lane == 1) wb = bar(B_ACCFREE + s), wp = (uint32_t)(((j >> 1) - 1) & 1), need = role < 2 && j >= 2;
-                if (lane == 2) wb = bar(B_AREADY + slot0), wp = (uint32_t)(n0 & 1), need = true;  // operands and min planes
-                if (lane == 3) wb = bar(B_AREADY + slot1), wp = (uint32_t)(n1 & 1), need = true;
+                if (lane == 2) wb = bar(B_AREADY + slot0), wp = (uint32_t)(n0 & 1), need = role < 2;
+                if (lane == 3) wb = bar(B_AREADY + slot1), wp = (uint32_t)(n1 & 1), need = role < 2;
+                // The min issuer has a barrier of its own for its operands.  It must not wait on AREADY: that barrier
+                // advances with the D_lo / D_hi issuers alone, and an issuer held up at a tile boundary would find it two
+                // phases ahead, which a parity wait cannot tell from "not yet".  MINREADY[s] can only be one phase
+                // ahead: its next arrival needs the commit of this job.
+                if (lane == 5) wb = bar(B_MINREADY + s), wp = (uint32_t)((j >> 1) & 1), need = role == 2;
                 // the tile's first min MMA overwrites the sums of the previous tile: the epilogue has read them
                 if (lane == 4) wb = bar(B_MINFREE), wp = (uint32_t)((tile_i - 1) & 1), need = role == 2 && b == 0 && tile_i >= 1;
                 if (!wait_multi(wb, wp, need, dead)) {
@@ -360,7 +366,7 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 if (lane == 0) wb = bar(B_FULL + ls), wp = (uint32_t)((j / kStages) & 1), need = true;
                 if (lane == 1) wb = bar(B_AFREE + slot), wp = (uint32_t)((n - 1) & 1), need = n >= 1;
                 // the min planes of job j - 2 (same buffer) have been read by the min issuer's MMAs
-                if (lane == 2) wb = bar(B_DONE + (j - 2 + kStages) % kStages), wp = (uint32_t)((((j - 2) / kStages)) & 1), need = j >= 2;
+                if (lane == 2) wb = bar(B_DONE + (j - 2 + kStages) % kStages), wp = (uint32_t)((((j - 2) / kStages)) & 1), need = h == 0 && j >= 2;
                 if (!wait_multi(wb, wp, need, dead)) {
                     ok = false;
                     break;
@@ -398,22 +404,25 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                         tst8(ts + 32 + (uint32_t)(sbl * 8), hi);
                     }
                 }
-                {
-                    // min planes of this half's four sub-blocks (K plane h of A1 and of A2): dmin * m_s = A1 + A2
-                    // exactly, both representable in tf32
-                    const float dminw = h2f(hdr.x >> 16);
-                    uint32_t p1[4], p2[4];
+                if (h == 0) {
+                    // min planes: dmin * m_s = A1 + A2 exactly, both representable in tf32
+                    const float dw = h2f(hdr.x), dminw = h2f(hdr.x >> 16);
+                    uint32_t p1[8], p2[8];
 #pragma unroll
-                    for (int s4 = 0; s4 < 4; s4++) {
-                        const float v = dminw * (float)((mn[h] >> (8 * s4)) & 0xFFu);
-                        p1[s4] = __float_as_uint(v) & 0xFFFFE000u;
-                        p2[s4] = __float_as_uint(v - __uint_as_float(p1[s4]));
+                    for (int s8 = 0; s8 < 8; s8++) {
+                        const float v = dminw * (float)((mn[s8 >> 2] >> (8 * (s8 & 3))) & 0xFFu);
+                        p1[s8] = __float_as_uint(v) & 0xFFFFE000u;
+                        p2[s8] = __float_as_uint(v - __uint_as_float(p1[s8]));
                     }
-                    uint8_t *mp = minbuf0 + (size_t)(j & 1) * kMinBytes + (size_t)(h * kTM + row) * 16;
+                    uint8_t *mp = minbuf0 + (size_t)(j & 1) * kMinBytes + (size_t)row * 16;
                     *reinterpret_cast<uint4 *>(mp) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
+                    *reinterpret_cast<uint4 *>(mp + kTM * 16) = make_uint4(p1[4], p1[5], p1[6], p1[7]);
                     *reinterpret_cast<uint4 *>(mp + 2 * kTM * 16) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
-                    if (h == 0) dwring[(j % kRing) * kTM + row] = h2f(hdr.x);
+                    *reinterpret_cast<uint4 *>(mp + 3 * kTM * 16) = make_uint4(p2[4], p2[5], p2[6], p2[7]);
+                    dwring[(j % kRing) * kTM + row] = dw;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) bar_arrive(bar(B_MINREADY + (j & 1)));
                 }
                 if (quarter == 0) TR(2 + h, j, 2);
                 tst_wait();

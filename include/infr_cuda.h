@@ -125,7 +125,10 @@ INFR_API int32_t infr_cuda_all_reduce_f32(infr_cuda_ctx *ctx, infr_cuda_comm *co
 INFR_API void infr_cuda_comm_destroy(infr_cuda_ctx *ctx, infr_cuda_comm *comm);
 INFR_API size_t infr_cuda_buf_len(const infr_cuda_buf *buf);
 INFR_API uint64_t infr_cuda_buf_device_ptr(const infr_cuda_buf *buf);
-/* upload/download reject a transfer larger than the buffer (check_copy_bytes, backend.rs:23-30). */
+/* upload/download reject a transfer larger than the buffer (check_copy_bytes, backend.rs:23-30).  `src` may be
+ * reused as soon as upload returns: transfers of at most 64 KB are staged through pinned memory of the context and
+ * return without waiting for the stream, larger ones wait for their copy; either way the data is in place for every
+ * op enqueued afterwards.  download returns when `dst` holds the data. */
 INFR_API int32_t infr_cuda_upload(infr_cuda_ctx *ctx, infr_cuda_buf *dst, const void *src, size_t bytes);
 INFR_API int32_t infr_cuda_upload_at(infr_cuda_ctx *ctx, infr_cuda_buf *dst, size_t dst_off, const void *src, size_t bytes);
 INFR_API int32_t infr_cuda_download(infr_cuda_ctx *ctx, const infr_cuda_buf *src, void *dst, size_t bytes);

@@ -66,6 +66,15 @@ Status CudaBackend::create(const infr_cuda_opts &opts, CudaBackend **out) {
         return s;
     }
     *be->status_host_ = 0;
+    if (!(s = be->cuda_status(cudaHostAlloc((void **)&be->up_ring_, kUpSlots * kUpSlotBytes, cudaHostAllocDefault), "cudaHostAlloc(upload ring)")).ok()) {
+        delete be;
+        return s;
+    }
+    for (int i = 0; i < kUpSlots; i++)
+        if (!(s = be->cuda_status(cudaEventCreateWithFlags(&be->up_ev_[i], cudaEventDisableTiming), "cudaEventCreate")).ok()) {
+            delete be;
+            return s;
+        }
     *out = be;
     return Status::Ok();
 }
@@ -86,6 +95,9 @@ CudaBackend::~CudaBackend() {
     if (scratch_) cudaFree(scratch_);
     if (flush_) cudaFree(flush_);
     if (status_host_) cudaFreeHost(status_host_);
+    if (up_ring_) cudaFreeHost(up_ring_);
+    for (cudaEvent_t e : up_ev_)
+        if (e) cudaEventDestroy(e);
     if (ev0_) cudaEventDestroy(ev0_);
     if (ev1_) cudaEventDestroy(ev1_);
     if (stream_) cudaStreamDestroy(stream_);
@@ -164,9 +176,22 @@ Status CudaBackend::upload(infr_cuda_buf *dst, size_t dst_off, const void *src, 
         return Status::Err(INFR_E_INVALID, fmt("upload: %zu bytes at offset %zu into a %zu-byte buffer", bytes, dst_off, dst->len));
     if (capturing_) return Status::Err(INFR_E_INVALID, "upload during stream capture");
     cudaSetDevice(device_);
+    // The caller may reuse `src` as soon as this returns (the trait takes a borrowed slice).  A small upload (a
+    // decode step's activations) is copied into a pinned slot of the context's ring and sent from there, so that
+    // the call returns without waiting for the stream; a slot is reused only after its copy has completed.
+    if (bytes <= kUpSlotBytes) {
+        const int slot = up_next_;
+        up_next_ = (up_next_ + 1) % kUpSlots;
+        Status s = cuda_status(cudaEventSynchronize(up_ev_[slot]), "upload slot");
+        if (!s.ok()) return s;
+        uint8_t *stage = up_ring_ + (size_t)slot * kUpSlotBytes;
+        memcpy(stage, src, bytes);
+        s = cuda_status(cudaMemcpyAsync((uint8_t *)dst->ptr + dst_off, stage, bytes, cudaMemcpyHostToDevice, stream_), "upload");
+        if (!s.ok()) return s;
+        return cuda_status(cudaEventRecord(up_ev_[slot], stream_), "upload event");
+    }
     Status s = cuda_status(cudaMemcpyAsync((uint8_t *)dst->ptr + dst_off, src, bytes, cudaMemcpyHostToDevice, stream_), "upload");
     if (!s.ok()) return s;
-    // The caller may reuse `src` as soon as this returns (the trait takes a borrowed slice).
     return cuda_status(cudaStreamSynchronize(stream_), "upload sync");
 }
 

@@ -153,6 +153,12 @@ private:
     uint64_t next_uid_ = 1;
     uint32_t *status_host_ = nullptr;  // pinned + mapped: kernels report expired waits here
     uint32_t *status_dev_ = nullptr;
+    // small uploads go through a ring of pinned slots, so that upload() can return without a stream sync
+    static constexpr int kUpSlots = 8;
+    static constexpr size_t kUpSlotBytes = 64 << 10;
+    uint8_t *up_ring_ = nullptr;
+    cudaEvent_t up_ev_[kUpSlots] = {};
+    int up_next_ = 0;
     int gemv_impl_ = 0;                // 0 = bulk-copy ring kernel, 1 = direct-load kernel
     int mmq_impl_ = 0;                 // 0 = warp-specialised MMQ (f32 within rounding of the CPU), 1 = bit-identical MMQ
     Status check_device_status();

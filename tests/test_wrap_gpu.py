@@ -60,3 +60,25 @@ def test_stream_is_usable_from_torch(backend):
         ext.synchronize()
     want = backend.run_linear(Q4K, w, np.ones((1, in_f), np.float32), m, in_f, out_f)
     np.testing.assert_allclose(y2.cpu().numpy(), 2.0 * want[0], rtol=0, atol=0)
+
+
+def test_small_uploads_do_not_alias_when_the_source_is_reused(backend):
+    """upload() of a small buffer returns before the copy has run (it goes through a ring of pinned slots); the
+    caller's source may be overwritten at once, as the trait's borrowed slice allows, and more uploads than the
+    ring has slots must still land with their own bytes."""
+    n_buf, n = 40, 4096
+    host = backend.host_array((n,), np.float32)
+    bufs = [backend.alloc(n * 4) for _ in range(n_buf)]
+    for i, b in enumerate(bufs):
+        host[:] = np.float32(i) + np.arange(n, dtype=np.float32) / n
+        backend.upload_raw(b, host.ctypes.data, n * 4)
+        host[:] = -1.0  # reuse of the source right after the call
+    for i, b in enumerate(bufs):
+        want = np.float32(i) + np.arange(n, dtype=np.float32) / n
+        np.testing.assert_array_equal(backend.download(b, np.float32), want)
+    # a size that spans the small / large boundary on both sides
+    for nbytes in (64 << 10, (64 << 10) + 256):
+        src = np.arange(nbytes, dtype=np.uint8)
+        big = backend.alloc(nbytes)
+        backend.upload(big, src)
+        np.testing.assert_array_equal(backend.download(big, np.uint8), src)

@@ -314,6 +314,81 @@ def _decode_linears_case(be, infr_b200, batch, steps, warmup):
     return res
 
 
+def _decode_step_case(be, infr_b200, batch, steps, warmup, hbm_peak, pos=4096):
+    """A whole Llama-3-8B-shape decode step: 32 layers of RmsNorm, q/k/v Linears, RoPE + f16 KV write, causal
+    attention over a KV cache pre-filled to `pos` positions, o Linear, residual add + RmsNorm, gate/up Linears, SiLU
+    gate, down Linear, residual add; then the output norm, the 128256-row head and argmax.  Q4_K_M mix (attn_v and
+    ffn_down Q6_K, the rest Q4_K), every layer on its own device copy of the weights, `batch` independent sequences
+    with their own caches, the step captured in one CUDA graph.  The input rows stand for the host-embedded token
+    rows (the graph restores them at the start of every replay).  Weight bytes are random valid blocks; cache
+    values are N(0,1) halves."""
+    import numpy as np
+    from infr_b200 import synth
+    from infr_b200.decode import DecodeStep, LlamaShape
+
+    Q4K = infr_b200.Q4K
+    s = LlamaShape()
+    max_ctx = pos + 8
+    masters = {name: be.from_numpy(synth.random_blocks(dt, o * i, 200 + k), infr_b200.USAGE_WEIGHTS)
+               for k, (name, dt, o, i) in enumerate(s.linears())}
+    norm = be.from_numpy((1.0 + 0.02 * synth.normal(40, (s.hidden,))).astype(np.float32))
+    layers, w_bytes, owned = [], 0, []
+    for _ in range(s.n_layer):
+        L = {"attn_norm": norm, "ffn_norm": norm}
+        for name, dt, o, i in s.linears():
+            nbytes = o * i // synth.BLOCK_ELEMS[dt] * synth.BLOCK_BYTES[dt]
+            b = be.alloc_uninit(nbytes, infr_b200.USAGE_WEIGHTS)
+            be.copy_buffer(masters[name], b, nbytes)
+            L[name] = b
+            owned.append(b)
+            w_bytes += nbytes
+        layers.append(L)
+    head = be.from_numpy(synth.random_blocks(Q4K, s.vocab * s.hidden, 299), infr_b200.USAGE_WEIGHTS)
+    w_bytes += s.vocab * s.hidden // 256 * 144
+    seq_bytes = max_ctx * s.kv_dim * 2
+    kv_master = be.from_numpy(synth.normal(9, (max_ctx, s.kv_dim)).astype(np.float16).view(np.uint16))
+    kc, vc = [], []
+    for _ in range(s.n_layer):
+        for lst in (kc, vc):
+            c = be.alloc_uninit(batch * seq_bytes, infr_b200.USAGE_ACTIVATIONS)
+            for q in range(batch):
+                view = be.wrap(c.device_ptr() + q * seq_bytes, seq_bytes, infr_b200.USAGE_ACTIVATIONS)
+                be.copy_buffer(kv_master, view, seq_bytes)
+                view.close()
+            lst.append(c)
+    step = DecodeStep(be, s, batch, max_ctx, layers, norm, head, Q4K, kc, vc)
+    hidden0 = be.from_numpy(synth.normal(31, (batch, s.hidden)))
+    step.set_inputs(synth.normal(31, (batch, s.hidden)), pos)
+
+    def one():
+        be.copy_buffer(hidden0, step.hidden, batch * s.hidden * 4)
+        return step.run(pos, fused=True)
+
+    one()  # sizes the context scratch before capture
+    be.sync()
+    tok_eager = be.download(step.tok, np.uint32)
+    l0 = be.launch_count()
+    be.capture_begin()
+    n_ops = one()
+    graph = be.capture_end()
+    kernels = be.launch_count() - l0
+    ms = _time_graph(be, graph, steps, warmup)
+    us = ms * 1e3 / steps
+    tok = be.download(step.tok, np.uint32)
+    kv_bytes = s.n_layer * 2 * (pos + 1) * s.kv_dim * 2 * batch
+    alg = w_bytes + kv_bytes
+    res = {"workload": f"8B-shape decode step, batch {batch} (independent sequences), KV context {pos} (kv_len {pos + 1}), Q4_K_M mix, "
+                       f"{n_ops} ops in one CUDA graph",
+           "us_per_step": us, "tok_per_s": batch / (us * 1e-6), "weight_bytes": w_bytes, "kv_bytes_read": kv_bytes,
+           "hbm_gbs": alg / (us * 1e-6) / 1e9, "frac_of_measured_hbm": alg / (us * 1e-6) / 1e9 / hbm_peak,
+           "kernels_per_step": kernels, "tokens_same_eager_and_graph": bool((tok == tok_eager).all()),
+           "first_token_ids": [int(t) for t in tok[:4]]}
+    graph.close()
+    for b in owned + kc + vc + [head, kv_master, hidden0, norm] + list(masters.values()):
+        b.close()
+    return res
+
+
 def _tp_decode(be, infr_b200, dist, rank, world, local, steps, warmup):
     """Tensor-parallel form of the decode step's Linear ops (batch 1): q/k/v/gate/up and the output head are
     split by output rows, o and down by input columns with an NCCL all-reduce of the 4096-float result after each
@@ -628,6 +703,7 @@ def run_b200(args):
         out["mmq"] = _mmq_case(be, infr_b200, 512, 4096, 14336, 5, 20, 3)
         out["moe"] = _moe_case(be, infr_b200, 20, 3)
         out["decode_linears"] = [_decode_linears_case(be, infr_b200, b, 10, 3) for b in (1, 32)]
+        out["decode_step"] = [_decode_step_case(be, infr_b200, b, 10, 3, hbm_peak) for b in (1, 32)]
 
     if not args.no_sweep:
         tp = _tp_decode(be, infr_b200, dist, rank, world, local, 10, 3)
@@ -661,6 +737,11 @@ def run_profile_case(args):
     if name == "decode":  # decode:0:0:BATCH — the Linear ops of an 8B-shape decode step
         be = infr_b200.CudaBackend(device=0)
         print(json.dumps(_decode_linears_case(be, infr_b200, int(m), args.steps, 2)))
+        be.close()
+        return
+    if name == "step":  # step:0:CONTEXT:BATCH — the whole 8B-shape decode step
+        be = infr_b200.CudaBackend(device=0)
+        print(json.dumps(_decode_step_case(be, infr_b200, int(m), args.steps, 2, 6542.7, pos=int(in_f) or 4096)))
         be.close()
         return
     if name == "mmq":  # mmq:OUT_F:IN_F:M — the prefill GEMM (Linear with m > 8)

@@ -263,6 +263,47 @@ INFR_API int32_t infr_cuda_moe_ffn(infr_cuda_ctx *ctx, const infr_moe_desc *desc
                                    const infr_cuda_buf *down_exps, infr_cuda_buf *dst, infr_cuda_buf *sel_ids,
                                    infr_cuda_buf *sel_w, infr_cuda_buf *logits);
 
+/* ---- the other ops of a dense decode step (the reference's op sequence per layer:
+ * crates/infr-llama/src/seam/runner.rs:2641-4286; semantics: the CPU backend's arms in
+ * crates/infr-cpu/src/lib.rs).  All buffers hold f32 unless said otherwise. ---- */
+/* Op::RmsNorm (graph.rs; cpu lib.rs:801-825): dst[r,i] = x[r,i] / sqrt(mean(x[r]^2) + eps) * weight[i]. */
+INFR_API int32_t infr_cuda_rms_norm(infr_cuda_ctx *ctx, const infr_cuda_buf *x, const infr_cuda_buf *weight, infr_cuda_buf *dst,
+                                    uint32_t rows, uint32_t dim, float eps);
+/* Op::Add followed by Op::RmsNorm in one launch (runner.rs:3824-3838): sum_dst = a + b (sum_dst may be a),
+ * norm_dst = rms_norm(sum_dst). */
+INFR_API int32_t infr_cuda_add_rms_norm(infr_cuda_ctx *ctx, const infr_cuda_buf *a, const infr_cuda_buf *b, infr_cuda_buf *sum_dst,
+                                        const infr_cuda_buf *weight, infr_cuda_buf *norm_dst, uint32_t rows, uint32_t dim, float eps);
+/* Op::Rope without freq_factors (cpu lib.rs:1493-1553).  positions: int32 [rows].  neox = 0: pairs (2p, 2p+1). */
+INFR_API int32_t infr_cuda_rope(infr_cuda_ctx *ctx, const infr_cuda_buf *x, const infr_cuda_buf *positions, infr_cuda_buf *dst,
+                                uint32_t rows, uint32_t n_head, uint32_t head_dim, uint32_t rope_dim, float theta, int32_t neox);
+/* Op::WriteKv into an f16 cache [max_ctx, row_stride] (cpu lib.rs:1635-1673): f32 -> f16, round to nearest even. */
+INFR_API int32_t infr_cuda_write_kv(infr_cuda_ctx *ctx, const infr_cuda_buf *src, infr_cuda_buf *cache, uint32_t rows,
+                                    uint32_t row_stride, uint32_t pos);
+typedef struct infr_attn_desc {
+    uint32_t rows;      /* query rows per sequence: consecutive positions pos .. pos+rows-1 (causal) */
+    uint32_t pos;       /* position of the first query row; it attends keys [0, pos] */
+    uint32_t n_head, n_kv, head_dim; /* head_dim 64 or 128; n_head / n_kv in {1, 2, 4, 8} */
+    float scale;
+    uint32_t n_seq;     /* 0 or 1: the reference's op.  > 1: independent sequences, q holds n_seq * rows rows */
+    uint32_t reserved;
+    uint64_t seq_stride; /* elements between the caches of consecutive sequences */
+} infr_attn_desc;
+/* Op::Attention with AttnMask::Causal over f16 K / V caches [max_ctx, n_kv * head_dim] (cpu lib.rs:1744-1888). */
+INFR_API int32_t infr_cuda_attention(infr_cuda_ctx *ctx, const infr_attn_desc *desc, const infr_cuda_buf *q,
+                                     const infr_cuda_buf *k_cache, const infr_cuda_buf *v_cache, infr_cuda_buf *dst);
+/* Rope(q) in place, Rope(k) and v straight into the f16 caches: the four ops of runner.rs:3611-3656 in one launch.
+ * rope_dim == head_dim.  Row r belongs to sequence r / desc->rows and is written at cache row positions[r]. */
+INFR_API int32_t infr_cuda_rope_write_kv(infr_cuda_ctx *ctx, const infr_attn_desc *desc, float theta, int32_t neox, infr_cuda_buf *q,
+                                         const infr_cuda_buf *k, const infr_cuda_buf *v, const infr_cuda_buf *positions,
+                                         infr_cuda_buf *k_cache, infr_cuda_buf *v_cache);
+/* Op::GatedAct with Activation::Silu on dense [rows, nff] gate and up (cpu lib.rs:1890-1944). */
+INFR_API int32_t infr_cuda_gated_act(infr_cuda_ctx *ctx, const infr_cuda_buf *gate, const infr_cuda_buf *up, infr_cuda_buf *dst,
+                                     uint32_t rows, uint32_t nff);
+/* Op::Add (cpu lib.rs:1972-1987). */
+INFR_API int32_t infr_cuda_add(infr_cuda_ctx *ctx, const infr_cuda_buf *a, const infr_cuda_buf *b, infr_cuda_buf *dst, uint64_t n);
+/* Op::Argmax (cpu lib.rs:2167-2187): dst uint32 [rows], lowest index on ties. */
+INFR_API int32_t infr_cuda_argmax(infr_cuda_ctx *ctx, const infr_cuda_buf *x, infr_cuda_buf *dst, uint32_t n, uint32_t rows);
+
 /* ---- stream capture and timing ----
  * capture_begin .. capture_end records every kernel the calls in between enqueue into a CUDA graph
  * that infr_cuda_graph_launch replays (decode replays a fixed kernel sequence every token).  Calls

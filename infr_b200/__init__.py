@@ -39,6 +39,8 @@ EXPORTED_SYMBOLS = [
     "infr_cuda_linear", "infr_cuda_moe_ffn", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
     "infr_cuda_graph_free", "infr_cuda_timer_start", "infr_cuda_timer_stop", "infr_cuda_flush_l2",
     "infr_cuda_launch_count",
+    "infr_cuda_rms_norm", "infr_cuda_add_rms_norm", "infr_cuda_rope", "infr_cuda_write_kv", "infr_cuda_attention", "infr_cuda_rope_write_kv",
+    "infr_cuda_gated_act", "infr_cuda_add", "infr_cuda_argmax",
 ]
 
 
@@ -74,6 +76,11 @@ class _MoeDesc(C.Structure):
                 ("n_ff_exp", C.c_uint32), ("scale", C.c_float), ("norm_w", C.c_int32), ("router_dtype", C.c_int32),
                 ("gate_dtype", C.c_int32), ("up_dtype", C.c_int32), ("down_dtype", C.c_int32),
                 ("expert_lo", C.c_uint32), ("n_local", C.c_uint32)]
+
+
+class _AttnDesc(C.Structure):
+    _fields_ = [("rows", C.c_uint32), ("pos", C.c_uint32), ("n_head", C.c_uint32), ("n_kv", C.c_uint32), ("head_dim", C.c_uint32),
+                ("scale", C.c_float), ("n_seq", C.c_uint32), ("reserved", C.c_uint32), ("seq_stride", C.c_uint64)]
 
 
 class _GraphDesc(C.Structure):
@@ -138,6 +145,15 @@ def load_library() -> C.CDLL:
         "infr_cuda_timer_stop": (i32, [vp, C.POINTER(C.c_float)]),
         "infr_cuda_flush_l2": (i32, [vp]),
         "infr_cuda_launch_count": (u64, [vp]),
+        "infr_cuda_rms_norm": (i32, [vp, vp, vp, vp, u32, u32, C.c_float]),
+        "infr_cuda_add_rms_norm": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, C.c_float]),
+        "infr_cuda_rope": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, C.c_float, i32]),
+        "infr_cuda_write_kv": (i32, [vp, vp, vp, u32, u32, u32]),
+        "infr_cuda_attention": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, vp]),
+        "infr_cuda_rope_write_kv": (i32, [vp, C.POINTER(_AttnDesc), C.c_float, i32, vp, vp, vp, vp, vp, vp]),
+        "infr_cuda_gated_act": (i32, [vp, vp, vp, vp, u32, u32]),
+        "infr_cuda_add": (i32, [vp, vp, vp, vp, u64]),
+        "infr_cuda_argmax": (i32, [vp, vp, vp, u32, u32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -452,6 +468,44 @@ class CudaBackend:
         h = lambda b: b.handle if b is not None else None
         self._check(self.L.infr_cuda_moe_ffn(self.ctx, C.byref(d), x.handle, router_x.handle, router.handle, gate.handle,
                                              up.handle, down.handle, dst.handle, h(sel_ids), h(sel_w), h(logits)))
+
+    # ---- the other ops of a dense decode step (names and arguments follow the reference's Op variants) ----
+    def rms_norm(self, x: Buffer, weight: Buffer, dst: Buffer, rows: int, dim: int, eps: float):
+        self._check(self.L.infr_cuda_rms_norm(self.ctx, x.handle, weight.handle, dst.handle, rows, dim, eps))
+
+    def add_rms_norm(self, a: Buffer, b: Buffer, sum_dst: Buffer, weight: Buffer, norm_dst: Buffer, rows: int, dim: int, eps: float):
+        self._check(self.L.infr_cuda_add_rms_norm(self.ctx, a.handle, b.handle, sum_dst.handle, weight.handle, norm_dst.handle, rows, dim, eps))
+
+    def rope(self, x: Buffer, positions: Buffer, dst: Buffer, rows: int, n_head: int, head_dim: int, rope_dim: int, theta: float,
+             neox: bool = False):
+        self._check(self.L.infr_cuda_rope(self.ctx, x.handle, positions.handle, dst.handle, rows, n_head, head_dim, rope_dim, theta, int(neox)))
+
+    def write_kv(self, src: Buffer, cache: Buffer, rows: int, row_stride: int, pos: int):
+        self._check(self.L.infr_cuda_write_kv(self.ctx, src.handle, cache.handle, rows, row_stride, pos))
+
+    @staticmethod
+    def _attn_desc(rows, pos, n_head, n_kv, head_dim, scale, n_seq, seq_stride):
+        return _AttnDesc(rows, pos, n_head, n_kv, head_dim, scale, n_seq, 0, seq_stride)
+
+    def attention(self, q: Buffer, k_cache: Buffer, v_cache: Buffer, dst: Buffer, *, rows: int, pos: int, n_head: int, n_kv: int,
+                  head_dim: int, scale: float, n_seq: int = 1, seq_stride: int = 0):
+        d = self._attn_desc(rows, pos, n_head, n_kv, head_dim, scale, n_seq, seq_stride)
+        self._check(self.L.infr_cuda_attention(self.ctx, C.byref(d), q.handle, k_cache.handle, v_cache.handle, dst.handle))
+
+    def rope_write_kv(self, q: Buffer, k: Buffer, v: Buffer, positions: Buffer, k_cache: Buffer, v_cache: Buffer, *, rows: int, pos: int,
+                      n_head: int, n_kv: int, head_dim: int, theta: float, neox: bool = False, n_seq: int = 1, seq_stride: int = 0):
+        d = self._attn_desc(rows, pos, n_head, n_kv, head_dim, 0.0, n_seq, seq_stride)
+        self._check(self.L.infr_cuda_rope_write_kv(self.ctx, C.byref(d), theta, int(neox), q.handle, k.handle, v.handle, positions.handle,
+                                                   k_cache.handle, v_cache.handle))
+
+    def gated_act(self, gate: Buffer, up: Buffer, dst: Buffer, rows: int, nff: int):
+        self._check(self.L.infr_cuda_gated_act(self.ctx, gate.handle, up.handle, dst.handle, rows, nff))
+
+    def add(self, a: Buffer, b: Buffer, dst: Buffer, n: int):
+        self._check(self.L.infr_cuda_add(self.ctx, a.handle, b.handle, dst.handle, n))
+
+    def argmax(self, x: Buffer, dst: Buffer, n: int, rows: int):
+        self._check(self.L.infr_cuda_argmax(self.ctx, x.handle, dst.handle, n, rows))
 
     def gemv_block_acc(self, dtype: int, w: Buffer, x: Buffer, acc: Buffer, in_f: int, out_f: int, w_off: int = 0):
         self._check(self.L.infr_cuda_gemv_block_acc(self.ctx, dtype, w.handle, w_off, x.handle, acc.handle, in_f, out_f))

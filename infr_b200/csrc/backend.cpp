@@ -165,7 +165,7 @@ Status CudaBackend::wrap(void *device_ptr, size_t bytes, int usage, infr_cuda_bu
 void CudaBackend::free_buffer(infr_cuda_buf *b) {
     if (!b) return;
     cudaSetDevice(device_);
-    if (!capturing_) cudaStreamSynchronize(stream_);
+    if (!capturing_ && b->owned) cudaStreamSynchronize(stream_);  // a non-owning handle frees nothing
     if (b->owned) cudaFree(b->ptr);
     delete b;
 }
@@ -367,6 +367,76 @@ Status CudaBackend::gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *
                                : launch_gemv_stream(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_),
                            "gemv_q8");
     if (s.ok()) launches_++;
+    return s;
+}
+
+// ---- the other ops of a dense decode step ----
+Status CudaBackend::rms_norm(const float *a, const float *b, float *sum_dst, const float *w, float *dst, uint32_t rows, uint32_t dim, float eps) {
+    cudaSetDevice(device_);
+    Status s = cuda_status(launch_rms_norm(a, b, sum_dst, w, dst, (int)rows, (int)dim, eps, stream_), "rms_norm");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+Status CudaBackend::rope(const float *x, const int32_t *positions, float *dst, uint32_t rows, uint32_t n_head, uint32_t head_dim,
+                         uint32_t rope_dim, float theta, int neox) {
+    cudaSetDevice(device_);
+    Status s = cuda_status(launch_rope(x, positions, dst, (int)rows, (int)n_head, (int)head_dim, (int)rope_dim, theta, neox, dev_, stream_), "rope");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+Status CudaBackend::write_kv(const float *src, void *cache_at_pos, size_t n) {
+    cudaSetDevice(device_);
+    Status s = cuda_status(launch_write_kv_f16(src, cache_at_pos, n, dev_, stream_), "write_kv");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+Status CudaBackend::rope_write_kv(const infr_attn_desc &d, float theta, int neox, float *q, const float *k, const float *v,
+                                  const int32_t *positions, void *k_cache, void *v_cache) {
+    cudaSetDevice(device_);
+    const uint32_t n_seq = d.n_seq ? d.n_seq : 1;
+    Status s = cuda_status(launch_rope_write_kv(q, k, v, positions, k_cache, v_cache, (int)(n_seq * d.rows), (int)d.n_head, (int)d.n_kv,
+                                                (int)d.head_dim, theta, neox, (int)d.rows, (size_t)d.seq_stride, dev_, stream_),
+                           "rope_write_kv");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+Status CudaBackend::attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst) {
+    cudaSetDevice(device_);
+    const uint32_t n_seq = d.n_seq ? d.n_seq : 1;
+    const size_t ws = attention_workspace_bytes((int)(n_seq * d.rows), (int)d.n_head, (int)d.head_dim, (int)(d.pos + d.rows));
+    Status s = ensure_scratch(ws);
+    if (!s.ok()) return s;
+    s = cuda_status(launch_attention(q, k_cache, v_cache, dst, scratch_, (int)n_seq, (int)d.rows, (int)d.n_head, (int)d.n_kv, (int)d.head_dim,
+                                     d.scale, (int)d.pos, (size_t)d.seq_stride, stream_),
+                    "attention");
+    if (s.ok()) launches_ += 2;
+    return s;
+}
+
+Status CudaBackend::gated_act(const float *gate, const float *up, float *dst, size_t n) {
+    cudaSetDevice(device_);
+    Status s = cuda_status(launch_gated_silu(gate, up, dst, n, dev_, stream_), "gated_act");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+Status CudaBackend::add(const float *a, const float *b, float *dst, size_t n) {
+    cudaSetDevice(device_);
+    Status s = cuda_status(launch_add(a, b, dst, n, dev_, stream_), "add");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+Status CudaBackend::argmax(const float *x, uint32_t *dst, uint32_t n, uint32_t rows) {
+    cudaSetDevice(device_);
+    Status s = ensure_scratch(argmax_workspace_bytes(n, rows));
+    if (!s.ok()) return s;
+    s = cuda_status(launch_argmax(x, dst, scratch_, n, rows, stream_), "argmax");
+    if (s.ok()) launches_ += 2;
     return s;
 }
 

@@ -105,6 +105,17 @@ public:
     Status moe_ffn(const MoeArgs &a);
     Status moe_ffn_f32(const MoeArgs &a);
     Status gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f);
+    // ---- the other ops of a dense decode step (decode_ops.cu); arguments checked by the C ABI ----
+    Status rms_norm(const float *a, const float *b, float *sum_dst, const float *w, float *dst, uint32_t rows, uint32_t dim, float eps);
+    Status rope(const float *x, const int32_t *positions, float *dst, uint32_t rows, uint32_t n_head, uint32_t head_dim, uint32_t rope_dim,
+                float theta, int neox);
+    Status write_kv(const float *src, void *cache_at_pos, size_t n);
+    Status rope_write_kv(const infr_attn_desc &d, float theta, int neox, float *q, const float *k, const float *v, const int32_t *positions,
+                         void *k_cache, void *v_cache);
+    Status attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst);
+    Status gated_act(const float *gate, const float *up, float *dst, size_t n);
+    Status add(const float *a, const float *b, float *dst, size_t n);
+    Status argmax(const float *x, uint32_t *dst, uint32_t n, uint32_t rows);
     Status gemv_block_acc(int dtype, const uint8_t *w, const float *x, int32_t *acc, uint32_t in_f,
                           uint32_t out_f);
 

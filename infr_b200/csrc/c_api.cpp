@@ -287,6 +287,140 @@ int32_t infr_cuda_gemv_block_acc(infr_cuda_ctx *ctx, int32_t dtype, const infr_c
     return finish(ctx, ctx->be->gemv_block_acc(dtype, pw, (const float *)px, (int32_t *)pa, in_f, out_f));
 }
 
+// ---- the other ops of a dense decode step ----
+int32_t infr_cuda_rms_norm(infr_cuda_ctx *ctx, const infr_cuda_buf *x, const infr_cuda_buf *weight, infr_cuda_buf *dst, uint32_t rows,
+                           uint32_t dim, float eps) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (rows == 0 || dim == 0) return finish(ctx, Status::Err(INFR_E_INVALID, "rms_norm: rows and dim must be positive"));
+    uint8_t *px, *pw, *pd;
+    const size_t n = (size_t)rows * dim * 4;
+    Status s;
+    if (!(s = span(x, n, "rms_norm x", &px)).ok() || !(s = span(weight, (size_t)dim * 4, "rms_norm weight", &pw)).ok() ||
+        !(s = span(dst, n, "rms_norm dst", &pd)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->rms_norm((const float *)px, nullptr, nullptr, (const float *)pw, (float *)pd, rows, dim, eps));
+}
+
+int32_t infr_cuda_add_rms_norm(infr_cuda_ctx *ctx, const infr_cuda_buf *a, const infr_cuda_buf *b, infr_cuda_buf *sum_dst,
+                               const infr_cuda_buf *weight, infr_cuda_buf *norm_dst, uint32_t rows, uint32_t dim, float eps) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (rows == 0 || dim == 0) return finish(ctx, Status::Err(INFR_E_INVALID, "add_rms_norm: rows and dim must be positive"));
+    uint8_t *pa, *pb, *ps, *pw, *pd;
+    const size_t n = (size_t)rows * dim * 4;
+    Status s;
+    if (!(s = span(a, n, "add_rms_norm a", &pa)).ok() || !(s = span(b, n, "add_rms_norm b", &pb)).ok() ||
+        !(s = span(sum_dst, n, "add_rms_norm sum_dst", &ps)).ok() || !(s = span(weight, (size_t)dim * 4, "add_rms_norm weight", &pw)).ok() ||
+        !(s = span(norm_dst, n, "add_rms_norm norm_dst", &pd)).ok())
+        return finish(ctx, s);
+    if (pd == ps || pd == pa || pd == pb) return finish(ctx, Status::Err(INFR_E_INVALID, "add_rms_norm: norm_dst must not alias the sum or its inputs"));
+    return finish(ctx, ctx->be->rms_norm((const float *)pa, (const float *)pb, (float *)ps, (const float *)pw, (float *)pd, rows, dim, eps));
+}
+
+int32_t infr_cuda_rope(infr_cuda_ctx *ctx, const infr_cuda_buf *x, const infr_cuda_buf *positions, infr_cuda_buf *dst, uint32_t rows,
+                       uint32_t n_head, uint32_t head_dim, uint32_t rope_dim, float theta, int32_t neox) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (rows == 0 || n_head == 0 || head_dim == 0 || rope_dim == 0 || rope_dim > head_dim || (rope_dim & 1))
+        return finish(ctx, Status::Err(INFR_E_INVALID, "rope: rows, n_head, head_dim positive; rope_dim even and <= head_dim"));
+    uint8_t *px, *pp, *pd;
+    const size_t n = (size_t)rows * n_head * head_dim * 4;
+    Status s;
+    if (!(s = span(x, n, "rope x", &px)).ok() || !(s = span(positions, (size_t)rows * 4, "rope positions", &pp)).ok() ||
+        !(s = span(dst, n, "rope dst", &pd)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->rope((const float *)px, (const int32_t *)pp, (float *)pd, rows, n_head, head_dim, rope_dim, theta, neox != 0));
+}
+
+int32_t infr_cuda_write_kv(infr_cuda_ctx *ctx, const infr_cuda_buf *src, infr_cuda_buf *cache, uint32_t rows, uint32_t row_stride,
+                           uint32_t pos) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (rows == 0 || row_stride == 0) return finish(ctx, Status::Err(INFR_E_INVALID, "write_kv: rows and row_stride must be positive"));
+    uint8_t *ps, *pc;
+    const size_t n = (size_t)rows * row_stride;
+    Status s;
+    // the cache holds the whole context: a write past its end is an error, not a ring wrap
+    if (!(s = span(src, n * 4, "write_kv src", &ps)).ok() || !(s = span(cache, ((size_t)pos * row_stride + n) * 2, "write_kv cache", &pc)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->write_kv((const float *)ps, pc + (size_t)pos * row_stride * 2, n));
+}
+
+namespace {
+Status check_attn(const infr_attn_desc *d, const char *what) {
+    if (!d) return Status::Err(INFR_E_INVALID, std::string(what) + ": null descriptor");
+    if (d->rows == 0 || d->n_head == 0 || d->n_kv == 0 || d->n_head % d->n_kv)
+        return Status::Err(INFR_E_INVALID, std::string(what) + ": rows, n_head, n_kv positive and n_head a multiple of n_kv");
+    const uint32_t g = d->n_head / d->n_kv;
+    if ((d->head_dim != 64 && d->head_dim != 128) || (g != 1 && g != 2 && g != 4 && g != 8))
+        return Status::Err(INFR_E_UNSUPPORTED, std::string(what) + ": head_dim 64 or 128 and n_head / n_kv in {1, 2, 4, 8}");
+    if (d->n_seq > 1 && d->seq_stride < (uint64_t)(d->pos + d->rows) * d->n_kv * d->head_dim)
+        return Status::Err(INFR_E_INVALID, std::string(what) + ": seq_stride is smaller than one sequence's rows");
+    return Status::Ok();
+}
+}  // namespace
+
+int32_t infr_cuda_attention(infr_cuda_ctx *ctx, const infr_attn_desc *d, const infr_cuda_buf *q, const infr_cuda_buf *k_cache,
+                            const infr_cuda_buf *v_cache, infr_cuda_buf *dst) {
+    INFR_CTX_OR_RETURN(ctx);
+    Status s = check_attn(d, "attention");
+    if (!s.ok()) return finish(ctx, s);
+    const size_t n_seq = d->n_seq ? d->n_seq : 1;
+    const size_t qn = n_seq * d->rows * d->n_head * d->head_dim * 4;
+    const size_t cn = ((n_seq - 1) * (size_t)d->seq_stride + (size_t)(d->pos + d->rows) * d->n_kv * d->head_dim) * 2;
+    uint8_t *pq, *pk, *pv, *pd;
+    if (!(s = span(q, qn, "attention q", &pq)).ok() || !(s = span(k_cache, cn, "attention k_cache", &pk)).ok() ||
+        !(s = span(v_cache, cn, "attention v_cache", &pv)).ok() || !(s = span(dst, qn, "attention dst", &pd)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->attention(*d, (const float *)pq, pk, pv, (float *)pd));
+}
+
+int32_t infr_cuda_rope_write_kv(infr_cuda_ctx *ctx, const infr_attn_desc *d, float theta, int32_t neox, infr_cuda_buf *q, const infr_cuda_buf *k,
+                                const infr_cuda_buf *v, const infr_cuda_buf *positions, infr_cuda_buf *k_cache, infr_cuda_buf *v_cache) {
+    INFR_CTX_OR_RETURN(ctx);
+    Status s = check_attn(d, "rope_write_kv");
+    if (!s.ok()) return finish(ctx, s);
+    const size_t n_seq = d->n_seq ? d->n_seq : 1, rows = n_seq * d->rows;
+    const size_t cn = ((n_seq - 1) * (size_t)d->seq_stride + (size_t)(d->pos + d->rows) * d->n_kv * d->head_dim) * 2;
+    uint8_t *pq, *pk, *pv, *pp, *pkc, *pvc;
+    if (!(s = span(q, rows * d->n_head * d->head_dim * 4, "rope_write_kv q", &pq)).ok() ||
+        !(s = span(k, rows * d->n_kv * d->head_dim * 4, "rope_write_kv k", &pk)).ok() ||
+        !(s = span(v, rows * d->n_kv * d->head_dim * 4, "rope_write_kv v", &pv)).ok() ||
+        !(s = span(positions, rows * 4, "rope_write_kv positions", &pp)).ok() || !(s = span(k_cache, cn, "rope_write_kv k_cache", &pkc)).ok() ||
+        !(s = span(v_cache, cn, "rope_write_kv v_cache", &pvc)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->rope_write_kv(*d, theta, neox != 0, (float *)pq, (const float *)pk, (const float *)pv, (const int32_t *)pp, pkc, pvc));
+}
+
+int32_t infr_cuda_gated_act(infr_cuda_ctx *ctx, const infr_cuda_buf *gate, const infr_cuda_buf *up, infr_cuda_buf *dst, uint32_t rows,
+                            uint32_t nff) {
+    INFR_CTX_OR_RETURN(ctx);
+    uint8_t *pg, *pu, *pd;
+    const size_t n = (size_t)rows * nff;
+    Status s;
+    if (!(s = span(gate, n * 4, "gated_act gate", &pg)).ok() || !(s = span(up, n * 4, "gated_act up", &pu)).ok() ||
+        !(s = span(dst, n * 4, "gated_act dst", &pd)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->gated_act((const float *)pg, (const float *)pu, (float *)pd, n));
+}
+
+int32_t infr_cuda_add(infr_cuda_ctx *ctx, const infr_cuda_buf *a, const infr_cuda_buf *b, infr_cuda_buf *dst, uint64_t n) {
+    INFR_CTX_OR_RETURN(ctx);
+    uint8_t *pa, *pb, *pd;
+    Status s;
+    if (!(s = span(a, (size_t)n * 4, "add a", &pa)).ok() || !(s = span(b, (size_t)n * 4, "add b", &pb)).ok() ||
+        !(s = span(dst, (size_t)n * 4, "add dst", &pd)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->add((const float *)pa, (const float *)pb, (float *)pd, (size_t)n));
+}
+
+int32_t infr_cuda_argmax(infr_cuda_ctx *ctx, const infr_cuda_buf *x, infr_cuda_buf *dst, uint32_t n, uint32_t rows) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (n == 0 || rows == 0 || rows > 65535) return finish(ctx, Status::Err(INFR_E_INVALID, "argmax: n positive, rows in 1..65535"));
+    uint8_t *px, *pd;
+    Status s;
+    if (!(s = span(x, (size_t)rows * n * 4, "argmax x", &px)).ok() || !(s = span(dst, (size_t)rows * 4, "argmax dst", &pd)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->argmax((const float *)px, (uint32_t *)pd, n, rows));
+}
+
 int32_t infr_cuda_moe_ffn(infr_cuda_ctx *ctx, const infr_moe_desc *d, const infr_cuda_buf *x, const infr_cuda_buf *router_x,
                           const infr_cuda_buf *router, const infr_cuda_buf *gate, const infr_cuda_buf *up, const infr_cuda_buf *down,
                           infr_cuda_buf *dst, infr_cuda_buf *sel_ids, infr_cuda_buf *sel_w, infr_cuda_buf *logits) {

@@ -1,0 +1,526 @@
+// The ops of a dense decode step that sit between the quantized Linears: RMSNorm (optionally fused with the
+// residual add in front of it), RoPE, the f16 KV-cache write (optionally fused with RoPE of q and k), causal
+// attention over an f16 KV cache with the keys split over CTAs, the SiLU gate, the residual add and argmax.
+// Semantics follow the reference's CPU backend op by op (crates/infr-cpu/src/lib.rs: RmsNorm 801-825, Rope
+// 1493-1553, WriteKv 1635-1673, Attention 1744-1888, GatedAct 1890-1944, Add 1972-1987, Argmax 2167-2187).
+// All of them are HBM- or latency-bound elementwise / reduction kernels; every kernel waits for its producer
+// with `griddepcontrol.wait` before its first read, so a chain of them can overlap launch with the tail of
+// the previous kernel.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "kernels.h"
+
+namespace infr {
+namespace {
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_go() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+// ---------------------------------------------------------------------------------------------- RMSNorm
+// One CTA per row.  With ADD the row is a + b, which is also written to sum_dst (the residual stream).
+template <bool ADD>
+__global__ void __launch_bounds__(1024) rms_norm_kernel(const float *a, const float *b, float *sum_dst,  // sum_dst may alias a
+                                                        const float *__restrict__ w, float *__restrict__ dst, int dim, float eps) {
+    __shared__ float s_part[32];
+    __shared__ float s_scale;
+    pdl_go();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * dim;
+    const int n4 = dim >> 2;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+        float4 v = reinterpret_cast<const float4 *>(a + base)[i];
+        if (ADD) {
+            const float4 u = reinterpret_cast<const float4 *>(b + base)[i];
+            v.x += u.x, v.y += u.y, v.z += u.z, v.w += u.w;
+            reinterpret_cast<float4 *>(sum_dst + base)[i] = v;
+        }
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    for (int i = (n4 << 2) + threadIdx.x; i < dim; i += blockDim.x) {
+        float v = a[base + i];
+        if (ADD) {
+            v += b[base + i];
+            sum_dst[base + i] = v;
+        }
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x + 31) / 32 ? s_part[threadIdx.x] : 0.f;
+        t = warp_sum(t);
+        if (threadIdx.x == 0) s_scale = 1.0f / sqrtf(t / (float)dim + eps);
+    }
+    __syncthreads();
+    const float s = s_scale;
+    const float *src = ADD ? sum_dst : a;  // a thread re-reads only what it wrote itself
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+        const float4 v = reinterpret_cast<const float4 *>(src + base)[i];
+        const float4 g = reinterpret_cast<const float4 *>(w)[i];
+        reinterpret_cast<float4 *>(dst + base)[i] = make_float4(v.x * s * g.x, v.y * s * g.y, v.z * s * g.z, v.w * s * g.w);
+    }
+    for (int i = (n4 << 2) + threadIdx.x; i < dim; i += blockDim.x) dst[base + i] = src[base + i] * s * w[i];
+}
+
+// ---------------------------------------------------------------------------------------------- RoPE
+// theta^(-2p/rope_dim): the exponent is formed in f32 like the reference's, the power in f64 and rounded once,
+// which is what a correctly rounded f32 powf returns.
+__device__ __forceinline__ float rope_freq(float theta, int p, int rope_dim) {
+    const float e = -2.0f * (float)p / (float)rope_dim;
+    return (float)pow((double)theta, (double)e);
+}
+
+__device__ __forceinline__ void rope_pair(float a, float b, float ang, float *oa, float *ob) {
+    const float sn = sinf(ang), c = cosf(ang);
+    *oa = a * c - b * sn;
+    *ob = a * sn + b * c;
+}
+
+// thread = (row, head, pair or pass-through element)
+__global__ void __launch_bounds__(256) rope_kernel(const float *__restrict__ x, const int32_t *__restrict__ positions,
+                                                   float *__restrict__ dst, int rows, int n_head, int head_dim, int rope_dim,
+                                                   float theta, int neox) {
+    pdl_go();
+    pdl_wait();
+    const int hf = rope_dim / 2, per_head = hf + (head_dim - rope_dim);
+    const size_t total = (size_t)rows * n_head * per_head;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int e = (int)(i % per_head);
+        const size_t rh = i / per_head;
+        const int r = (int)(rh / n_head);
+        const size_t b = rh * head_dim;
+        if (e < hf) {
+            const int i0 = neox ? e : 2 * e, i1 = neox ? e + hf : 2 * e + 1;
+            const float ang = (float)positions[r] * rope_freq(theta, e, rope_dim);
+            float oa, ob;
+            rope_pair(x[b + i0], x[b + i1], ang, &oa, &ob);
+            dst[b + i0] = oa;
+            dst[b + i1] = ob;
+        } else {
+            const int j = rope_dim + (e - hf);
+            dst[b + j] = x[b + j];
+        }
+    }
+}
+
+// RoPE of q in place, RoPE of k straight into the f16 K cache, v into the f16 V cache: one launch instead of
+// Rope, Rope, WriteKv, WriteKv (crates/infr-llama/src/seam/runner.rs:3611-3656).  Row r belongs to sequence
+// r / rows_per_seq, whose caches start seq_stride elements after the previous sequence's, and lands at cache
+// row positions[r].  Full-head rotation only (rope_dim == head_dim).
+__global__ void __launch_bounds__(256) rope_write_kv_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                                            const int32_t *__restrict__ positions, __half *__restrict__ k_cache,
+                                                            __half *__restrict__ v_cache, int rows, int n_head, int n_kv, int head_dim,
+                                                            float theta, int neox, int rows_per_seq, size_t seq_stride) {
+    pdl_go();
+    pdl_wait();
+    const int hf = head_dim / 2;
+    const size_t nq = (size_t)rows * n_head * hf, nk = (size_t)rows * n_kv * hf, total = nq + 2 * nk;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        if (i < nq) {
+            const int p = (int)(i % hf);
+            const size_t rh = i / hf;
+            const int r = (int)(rh / n_head);
+            const size_t b = rh * head_dim;
+            const int i0 = neox ? p : 2 * p, i1 = neox ? p + hf : 2 * p + 1;
+            float oa, ob;
+            rope_pair(q[b + i0], q[b + i1], (float)positions[r] * rope_freq(theta, p, head_dim), &oa, &ob);
+            q[b + i0] = oa;
+            q[b + i1] = ob;
+        } else {
+            const bool is_v = i >= nq + nk;
+            const size_t t = i - nq - (is_v ? nk : 0);
+            const int p = (int)(t % hf);
+            const size_t rh = t / hf;  // row * n_kv + head
+            const int r = (int)(rh / n_kv), h = (int)(rh % n_kv);
+            const size_t b = rh * head_dim;
+            const size_t cb = (size_t)(r / rows_per_seq) * seq_stride + ((size_t)positions[r] * n_kv + h) * head_dim;
+            if (is_v) {
+                v_cache[cb + 2 * p] = __float2half_rn(v[b + 2 * p]);
+                v_cache[cb + 2 * p + 1] = __float2half_rn(v[b + 2 * p + 1]);
+            } else {
+                const int i0 = neox ? p : 2 * p, i1 = neox ? p + hf : 2 * p + 1;
+                float oa, ob;
+                rope_pair(k[b + i0], k[b + i1], (float)positions[r] * rope_freq(theta, p, head_dim), &oa, &ob);
+                k_cache[cb + i0] = __float2half_rn(oa);
+                k_cache[cb + i1] = __float2half_rn(ob);
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) write_kv_kernel(const float *__restrict__ src, __half *__restrict__ cache, size_t n) {
+    pdl_go();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        cache[i] = __float2half_rn(src[i]);
+}
+
+// ---------------------------------------------------------------------------------------------- attention
+constexpr int kAttnTile = 128;  // keys per CTA = threads per CTA
+
+// CTA = (key tile, KV head, query row).  Phase 1: thread t scores key t of the tile against the G query heads
+// that share the KV head (q in shared memory, the key row streamed as 16-byte loads).  Phase 2: one warp per
+// head turns the tile's scores into exp(s - m) and their sum.  Phase 3: warp w multiplies keys 32w..32w+31 of
+// the tile into the head_dim outputs (lane = HD/32 dims), the four warps' partial sums are added through
+// shared memory, and the tile's (m, l, o) goes to the workspace for attn_combine_kernel.
+template <int HD, int G>
+__global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__restrict__ q, const __half *__restrict__ k_cache,
+                                                               const __half *__restrict__ v_cache, float *__restrict__ part_o,
+                                                               float *__restrict__ part_ml, int rows, int n_head, int n_kv, int pos,
+                                                               float scale, int n_splits, size_t seq_stride) {
+    constexpr int DPL = HD / 32;  // dims per lane in phase 3
+    __shared__ __align__(16) float s_q[G * HD];
+    __shared__ float s_p[G][kAttnTile];
+    __shared__ float s_ml[G][2];
+    __shared__ __align__(16) float s_o[4][G][HD];
+    const int split = blockIdx.x, kvh = blockIdx.y, qr = blockIdx.z;
+    const int seq = qr / rows, ti = qr % rows;
+    const int n_keys = pos + ti + 1;
+    const int key0 = split * kAttnTile;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_go();
+    pdl_wait();
+    const size_t out_idx = ((size_t)qr * n_head + (size_t)kvh * G) * n_splits + split;  // + g * n_splits
+    if (key0 >= n_keys) {  // a tile beyond this row's causal end contributes nothing
+        if (tid < G) {
+            part_ml[(out_idx + (size_t)tid * n_splits) * 2] = -INFINITY;
+            part_ml[(out_idx + (size_t)tid * n_splits) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    const float *qrow = q + ((size_t)qr * n_head + (size_t)kvh * G) * HD;
+    for (int i = tid; i < G * HD; i += kAttnTile) s_q[i] = qrow[i];
+    __syncthreads();
+    const size_t kv_row = (size_t)n_kv * HD;
+    const __half *kbase = k_cache + (size_t)seq * seq_stride + (size_t)kvh * HD;
+    const __half *vbase = v_cache + (size_t)seq * seq_stride + (size_t)kvh * HD;
+    // ---- phase 1
+    {
+        const int j = key0 + tid;
+        float acc[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) acc[g] = 0.f;
+        if (j < n_keys) {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)j * kv_row);
+#pragma unroll 4
+            for (int c = 0; c < HD / 8; c++) {
+                const uint4 raw = __ldg(kr + c);
+                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+                float kf[8];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __half22float2(h2[e]);
+                    kf[2 * e] = f.x, kf[2 * e + 1] = f.y;
+                }
+#pragma unroll
+                for (int g = 0; g < G; g++) {
+                    const float4 q0 = *reinterpret_cast<const float4 *>(s_q + g * HD + c * 8);
+                    const float4 q1 = *reinterpret_cast<const float4 *>(s_q + g * HD + c * 8 + 4);
+                    acc[g] = fmaf(q0.x, kf[0], acc[g]);
+                    acc[g] = fmaf(q0.y, kf[1], acc[g]);
+                    acc[g] = fmaf(q0.z, kf[2], acc[g]);
+                    acc[g] = fmaf(q0.w, kf[3], acc[g]);
+                    acc[g] = fmaf(q1.x, kf[4], acc[g]);
+                    acc[g] = fmaf(q1.y, kf[5], acc[g]);
+                    acc[g] = fmaf(q1.z, kf[6], acc[g]);
+                    acc[g] = fmaf(q1.w, kf[7], acc[g]);
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++) s_p[g][tid] = j < n_keys ? acc[g] * scale : -INFINITY;
+    }
+    __syncthreads();
+    // ---- phase 2
+    for (int g = warp; g < G; g += 4) {
+        float v[4], m = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 4; e++) v[e] = s_p[g][lane + 32 * e], m = fmaxf(m, v[e]);
+        m = warp_max(m);  // finite: the tile holds at least one valid key
+        float l = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float p = expf(v[e] - m);
+            s_p[g][lane + 32 * e] = p;
+            l += p;
+        }
+        l = warp_sum(l);
+        if (lane == 0) s_ml[g][0] = m, s_ml[g][1] = l;
+    }
+    __syncthreads();
+    // ---- phase 3
+    {
+        float o[G][DPL];
+#pragma unroll
+        for (int g = 0; g < G; g++)
+#pragma unroll
+            for (int e = 0; e < DPL; e++) o[g][e] = 0.f;
+        const int jw = key0 + warp * 32;
+        const int cnt = min(32, n_keys - jw);  // may be <= 0
+        const __half *vr = vbase + (size_t)jw * kv_row + lane * DPL;
+#pragma unroll 4
+        for (int jj = 0; jj < cnt; jj++) {
+            float vf[DPL];
+            if (DPL == 4) {
+                const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(vr + (size_t)jj * kv_row));
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+                vf[0] = f0.x, vf[1] = f0.y, vf[2] = f1.x, vf[3] = f1.y;
+            } else {
+                const uint32_t raw = __ldg(reinterpret_cast<const uint32_t *>(vr + (size_t)jj * kv_row));
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw));
+                vf[0] = f0.x, vf[1] = f0.y;
+            }
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const float p = s_p[g][warp * 32 + jj];
+#pragma unroll
+                for (int e = 0; e < DPL; e++) o[g][e] = fmaf(vf[e], p, o[g][e]);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++)
+#pragma unroll
+            for (int e = 0; e < DPL; e++) s_o[warp][g][lane * DPL + e] = o[g][e];
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += kAttnTile) {
+        const int g = i / HD, d = i % HD;
+        part_o[(out_idx + (size_t)g * n_splits) * HD + d] = s_o[0][g][d] + s_o[1][g][d] + s_o[2][g][d] + s_o[3][g][d];
+    }
+    if (tid < G) {
+        part_ml[(out_idx + (size_t)tid * n_splits) * 2] = s_ml[tid][0];
+        part_ml[(out_idx + (size_t)tid * n_splits) * 2 + 1] = s_ml[tid][1];
+    }
+}
+
+// CTA = (query row, head), thread = output dim: merges the tiles' (m, l, o).
+__global__ void attn_combine_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, float *__restrict__ dst,
+                                    int head_dim, int n_splits) {
+    pdl_go();
+    pdl_wait();
+    const size_t rh = blockIdx.x;
+    const float *ml = part_ml + rh * n_splits * 2;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
+    float l = 0.f, o = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+        const float ls = ml[2 * s + 1];
+        if (ls == 0.f) continue;
+        const float wgt = expf(ml[2 * s] - m);
+        l += wgt * ls;
+        o = fmaf(wgt, part_o[(rh * n_splits + s) * head_dim + threadIdx.x], o);
+    }
+    dst[rh * head_dim + threadIdx.x] = o / l;
+}
+
+// ---------------------------------------------------------------------------------------------- elementwise
+__global__ void __launch_bounds__(256) gated_silu_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                                                         float *__restrict__ dst, size_t n) {
+    pdl_go();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float g = gate[i];
+        dst[i] = g / (1.0f + expf(-g)) * up[i];
+    }
+}
+
+__global__ void __launch_bounds__(256) add_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ dst, size_t n) {
+    pdl_go();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = a[i] + b[i];
+}
+
+// Strict `>` with the lowest index on ties, per row.  Stage 1: CTA (chunk, row) -> best of its chunk;
+// stage 2: one CTA per row over the chunk winners.
+__device__ __forceinline__ void argmax_merge(float &bv, uint32_t &bi, float v, uint32_t i) {
+    if (v > bv || (v == bv && i < bi)) bv = v, bi = i;
+}
+__device__ __forceinline__ void argmax_block(float bv, uint32_t bi, float *s_v, uint32_t *s_i, float *ov, uint32_t *oi) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        const float v = __shfl_xor_sync(0xffffffffu, bv, o);
+        const uint32_t i = __shfl_xor_sync(0xffffffffu, bi, o);
+        argmax_merge(bv, bi, v, i);
+    }
+    if ((threadIdx.x & 31) == 0) s_v[threadIdx.x >> 5] = bv, s_i[threadIdx.x >> 5] = bi;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int nw = (blockDim.x + 31) / 32;
+        bv = threadIdx.x < nw ? s_v[threadIdx.x] : -INFINITY;
+        bi = threadIdx.x < nw ? s_i[threadIdx.x] : 0xffffffffu;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float v = __shfl_xor_sync(0xffffffffu, bv, o);
+            const uint32_t i = __shfl_xor_sync(0xffffffffu, bi, o);
+            argmax_merge(bv, bi, v, i);
+        }
+        if (threadIdx.x == 0) *ov = bv, *oi = bi;
+    }
+}
+
+__global__ void __launch_bounds__(256) argmax_stage1_kernel(const float *__restrict__ x, float *__restrict__ cand_v,
+                                                            uint32_t *__restrict__ cand_i, uint32_t n, uint32_t chunk) {
+    __shared__ float s_v[32];
+    __shared__ uint32_t s_i[32];
+    pdl_go();
+    pdl_wait();
+    const uint32_t lo = blockIdx.x * chunk, hi = min(n, lo + chunk);
+    const float *row = x + (size_t)blockIdx.y * n;
+    float bv = -INFINITY;
+    uint32_t bi = 0xffffffffu;
+    for (uint32_t i = lo + threadIdx.x; i < hi; i += blockDim.x) argmax_merge(bv, bi, row[i], i);
+    argmax_block(bv, bi, s_v, s_i, cand_v + (size_t)blockIdx.y * gridDim.x + blockIdx.x, cand_i + (size_t)blockIdx.y * gridDim.x + blockIdx.x);
+}
+
+__global__ void __launch_bounds__(256) argmax_stage2_kernel(const float *__restrict__ cand_v, const uint32_t *__restrict__ cand_i,
+                                                            uint32_t *__restrict__ dst, uint32_t n_chunks) {
+    __shared__ float s_v[32];
+    __shared__ uint32_t s_i[32];
+    __shared__ float s_bv;
+    __shared__ uint32_t s_bi;
+    pdl_go();
+    pdl_wait();
+    float bv = -INFINITY;
+    uint32_t bi = 0xffffffffu;
+    for (uint32_t c = threadIdx.x; c < n_chunks; c += blockDim.x)
+        argmax_merge(bv, bi, cand_v[(size_t)blockIdx.x * n_chunks + c], cand_i[(size_t)blockIdx.x * n_chunks + c]);
+    argmax_block(bv, bi, s_v, s_i, &s_bv, &s_bi);
+    __syncthreads();
+    // a row with no value above -inf (all -inf or NaN) answers index 0, like the reference's scan
+    if (threadIdx.x == 0) dst[blockIdx.x] = s_bi == 0xffffffffu ? 0u : s_bi;
+}
+
+inline unsigned grid_for(size_t n, int block, const DeviceInfo &dev) {
+    const size_t want = (n + (size_t)block - 1) / (size_t)block;
+    const size_t cap = (size_t)dev.sm_count * 8;
+    return (unsigned)(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+}  // namespace
+
+cudaError_t launch_rms_norm(const float *a, const float *b, float *sum_dst, const float *w, float *dst, int rows, int dim, float eps,
+                            cudaStream_t st) {
+    if (rows <= 0 || dim <= 0) return cudaErrorInvalidValue;
+    int threads = ((dim / 4 + 31) / 32) * 32;
+    threads = threads < 32 ? 32 : (threads > 1024 ? 1024 : threads);
+    if (b) return launch_pdl(rms_norm_kernel<true>, dim3(rows), dim3(threads), 0, st, a, b, sum_dst, w, dst, dim, eps);
+    return launch_pdl(rms_norm_kernel<false>, dim3(rows), dim3(threads), 0, st, a, (const float *)nullptr, (float *)nullptr, w, dst, dim, eps);
+}
+
+cudaError_t launch_rope(const float *x, const int32_t *positions, float *dst, int rows, int n_head, int head_dim, int rope_dim, float theta,
+                        int neox, const DeviceInfo &dev, cudaStream_t st) {
+    if (rows <= 0 || n_head <= 0 || head_dim <= 0 || rope_dim <= 0 || rope_dim > head_dim || (rope_dim & 1)) return cudaErrorInvalidValue;
+    const size_t total = (size_t)rows * n_head * (rope_dim / 2 + head_dim - rope_dim);
+    return launch_pdl(rope_kernel, dim3(grid_for(total, 256, dev)), dim3(256), 0, st, x, positions, dst, rows, n_head, head_dim, rope_dim, theta,
+                      neox);
+}
+
+cudaError_t launch_rope_write_kv(float *q, const float *k, const float *v, const int32_t *positions, void *k_cache, void *v_cache, int rows,
+                                 int n_head, int n_kv, int head_dim, float theta, int neox, int rows_per_seq, size_t seq_stride,
+                                 const DeviceInfo &dev, cudaStream_t st) {
+    if (rows <= 0 || n_head <= 0 || n_kv <= 0 || head_dim <= 0 || (head_dim & 1) || rows_per_seq <= 0) return cudaErrorInvalidValue;
+    const size_t total = (size_t)rows * (n_head + 2 * n_kv) * (head_dim / 2);
+    return launch_pdl(rope_write_kv_kernel, dim3(grid_for(total, 256, dev)), dim3(256), 0, st, q, k, v, positions, (__half *)k_cache,
+                      (__half *)v_cache, rows, n_head, n_kv, head_dim, theta, neox, rows_per_seq, seq_stride);
+}
+
+cudaError_t launch_write_kv_f16(const float *src, void *cache_at_pos, size_t n, const DeviceInfo &dev, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    return launch_pdl(write_kv_kernel, dim3(grid_for(n, 256, dev)), dim3(256), 0, st, src, (__half *)cache_at_pos, n);
+}
+
+size_t attention_workspace_bytes(int q_rows, int n_head, int head_dim, int max_keys) {
+    const size_t n_splits = ((size_t)max_keys + kAttnTile - 1) / kAttnTile;
+    return (size_t)q_rows * n_head * n_splits * ((size_t)head_dim + 2) * sizeof(float);
+}
+
+template <int HD>
+static cudaError_t launch_attn_hd(int group, dim3 grid, cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *po, float *pml,
+                                  int rows, int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride) {
+    switch (group) {
+        case 1: return launch_pdl(attn_split_kernel<HD, 1>, grid, dim3(kAttnTile), 0, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        case 2: return launch_pdl(attn_split_kernel<HD, 2>, grid, dim3(kAttnTile), 0, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        case 4: return launch_pdl(attn_split_kernel<HD, 4>, grid, dim3(kAttnTile), 0, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        case 8: return launch_pdl(attn_split_kernel<HD, 8>, grid, dim3(kAttnTile), 0, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_cache, float *dst, void *workspace, int n_seq, int rows, int n_head,
+                             int n_kv, int head_dim, float scale, int pos, size_t seq_stride, cudaStream_t st) {
+    if (n_seq <= 0 || rows <= 0 || n_head <= 0 || n_kv <= 0 || n_head % n_kv || pos < 0) return cudaErrorInvalidValue;
+    const int max_keys = pos + rows, n_splits = (max_keys + kAttnTile - 1) / kAttnTile, q_rows = n_seq * rows;
+    if (n_kv > 65535 || q_rows > 65535) return cudaErrorInvalidValue;
+    float *po = static_cast<float *>(workspace);
+    float *pml = po + (size_t)q_rows * n_head * n_splits * head_dim;
+    const dim3 grid(n_splits, n_kv, q_rows);
+    const __half *kc = static_cast<const __half *>(k_cache), *vc = static_cast<const __half *>(v_cache);
+    cudaError_t e;
+    if (head_dim == 128)
+        e = launch_attn_hd<128>(n_head / n_kv, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+    else if (head_dim == 64)
+        e = launch_attn_hd<64>(n_head / n_kv, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+    else
+        return cudaErrorInvalidValue;
+    if (e != cudaSuccess) return e;
+    return launch_pdl(attn_combine_kernel, dim3(q_rows * n_head), dim3(head_dim), 0, st, (const float *)po, (const float *)pml, dst, head_dim, n_splits);
+}
+
+cudaError_t launch_gated_silu(const float *gate, const float *up, float *dst, size_t n, const DeviceInfo &dev, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    return launch_pdl(gated_silu_kernel, dim3(grid_for(n, 256, dev)), dim3(256), 0, st, gate, up, dst, n);
+}
+
+cudaError_t launch_add(const float *a, const float *b, float *dst, size_t n, const DeviceInfo &dev, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    return launch_pdl(add_kernel, dim3(grid_for(n, 256, dev)), dim3(256), 0, st, a, b, dst, n);
+}
+
+size_t argmax_workspace_bytes(uint32_t n, uint32_t rows) {
+    const uint32_t chunk = 4096, n_chunks = (n + chunk - 1) / chunk;
+    return (size_t)rows * n_chunks * 8;
+}
+
+cudaError_t launch_argmax(const float *x, uint32_t *dst, void *workspace, uint32_t n, uint32_t rows, cudaStream_t st) {
+    if (n == 0 || rows == 0 || rows > 65535) return cudaErrorInvalidValue;
+    const uint32_t chunk = 4096, n_chunks = (n + chunk - 1) / chunk;
+    float *cv = static_cast<float *>(workspace);
+    uint32_t *ci = reinterpret_cast<uint32_t *>(cv + (size_t)rows * n_chunks);
+    cudaError_t e = launch_pdl(argmax_stage1_kernel, dim3(n_chunks, rows), dim3(256), 0, st, x, cv, ci, n, chunk);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(argmax_stage2_kernel, dim3(rows), dim3(256), 0, st, (const float *)cv, (const uint32_t *)ci, dst, n_chunks);
+}
+
+}  // namespace infr

@@ -102,4 +102,22 @@ cudaError_t launch_gemv_q4k_f32_sel(const uint8_t *bank, const int32_t *sel, siz
 
 cudaError_t launch_fill_u32(uint32_t *p, size_t n, uint32_t v, cudaStream_t st);
 
+// ---- dense decode-step ops (decode_ops.cu) ----
+// RMSNorm of `rows` rows; with b != nullptr the row is a + b, also written to sum_dst (may alias a).
+cudaError_t launch_rms_norm(const float *a, const float *b, float *sum_dst, const float *w, float *dst, int rows, int dim, float eps,
+                            cudaStream_t st);
+cudaError_t launch_rope(const float *x, const int32_t *positions, float *dst, int rows, int n_head, int head_dim, int rope_dim, float theta,
+                        int neox, const DeviceInfo &dev, cudaStream_t st);
+cudaError_t launch_rope_write_kv(float *q, const float *k, const float *v, const int32_t *positions, void *k_cache, void *v_cache, int rows,
+                                 int n_head, int n_kv, int head_dim, float theta, int neox, int rows_per_seq, size_t seq_stride,
+                                 const DeviceInfo &dev, cudaStream_t st);
+cudaError_t launch_write_kv_f16(const float *src, void *cache_at_pos, size_t n, const DeviceInfo &dev, cudaStream_t st);
+size_t attention_workspace_bytes(int q_rows, int n_head, int head_dim, int max_keys);
+cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_cache, float *dst, void *workspace, int n_seq, int rows, int n_head,
+                             int n_kv, int head_dim, float scale, int pos, size_t seq_stride, cudaStream_t st);
+cudaError_t launch_gated_silu(const float *gate, const float *up, float *dst, size_t n, const DeviceInfo &dev, cudaStream_t st);
+cudaError_t launch_add(const float *a, const float *b, float *dst, size_t n, const DeviceInfo &dev, cudaStream_t st);
+size_t argmax_workspace_bytes(uint32_t n, uint32_t rows);
+cudaError_t launch_argmax(const float *x, uint32_t *dst, void *workspace, uint32_t n, uint32_t rows, cudaStream_t st);
+
 }  // namespace infr

@@ -1,0 +1,125 @@
+"""One decode step of a Llama-family model as the sequence of backend ops the reference emits for it
+(crates/infr-llama/src/seam/runner.rs:2641-4493: RmsNorm, Linear q/k/v, Rope, WriteKv, Attention, Linear o, Add,
+RmsNorm, Linear gate/up, GatedAct, Linear down, Add, ..., RmsNorm, Linear lm_head, Argmax), issued through the
+C ABI.  `fused=True` uses the fused launches (Add+RmsNorm, Rope+Rope+WriteKv+WriteKv); `fused=False` issues the
+reference's ops one by one.  The batch is `n_seq` independent sequences, one new token each, all at position `pos`,
+every sequence with its own f16 KV cache."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import ACT_INT8, Q4K, Q6K, USAGE_ACTIVATIONS, USAGE_WEIGHTS
+
+
+@dataclass
+class LlamaShape:
+    n_layer: int = 32
+    hidden: int = 4096
+    n_head: int = 32
+    n_kv: int = 8
+    head_dim: int = 128
+    ffn: int = 14336
+    vocab: int = 128256
+    theta: float = 500000.0
+    eps: float = 1e-5
+
+    @property
+    def q_dim(self) -> int:
+        return self.n_head * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.n_kv * self.head_dim
+
+    def linears(self):
+        """(name, dtype, out_f, in_f) of one layer in the Q4_K_M mix: attn_v and ffn_down in Q6_K, the rest Q4_K."""
+        h, q, kv, ff = self.hidden, self.q_dim, self.kv_dim, self.ffn
+        return [("wq", Q4K, q, h), ("wk", Q4K, kv, h), ("wv", Q6K, kv, h), ("wo", Q4K, h, q),
+                ("gate", Q4K, ff, h), ("up", Q4K, ff, h), ("down", Q6K, h, ff)]
+
+
+class DecodeStep:
+    """Holds the device buffers of one model replica and issues one decode step.
+
+    `layers` is a list of dicts name -> weight Buffer (the names of LlamaShape.linears plus "attn_norm" and
+    "ffn_norm", f32), `head` the lm_head weight (`head_dtype`), `out_norm` the output norm.  `k_cache` / `v_cache`
+    are per-layer Buffers holding `n_seq` caches of `max_ctx` rows each."""
+
+    def __init__(self, be, shape: LlamaShape, n_seq: int, max_ctx: int, layers, out_norm, head, head_dtype, k_cache, v_cache):
+        self.be, self.s, self.n_seq, self.max_ctx = be, shape, n_seq, max_ctx
+        self.layers, self.out_norm, self.head, self.head_dtype = layers, out_norm, head, head_dtype
+        self.k_cache, self.v_cache = k_cache, v_cache
+        s, b = shape, n_seq
+        f32 = lambda n: be.alloc(b * n * 4, USAGE_ACTIVATIONS)
+        self.hidden, self.hn, self.sub = f32(s.hidden), f32(s.hidden), f32(s.hidden)
+        self.q, self.k, self.v, self.k_rot, self.attn = f32(s.q_dim), f32(s.kv_dim), f32(s.kv_dim), f32(s.kv_dim), f32(s.q_dim)
+        self.g, self.u, self.act = f32(s.ffn), f32(s.ffn), f32(s.ffn)
+        self.logits = f32(s.vocab)
+        self.tok = be.alloc(b * 4, USAGE_ACTIVATIONS)
+        self.positions = be.alloc(b * 4, USAGE_ACTIVATIONS)
+        self.seq_stride = max_ctx * s.kv_dim
+
+    def set_inputs(self, hidden: np.ndarray, pos: int):
+        self.be.upload(self.hidden, np.ascontiguousarray(hidden, np.float32))
+        self.be.upload(self.positions, np.full(self.n_seq, pos, np.int32))
+
+    def run(self, pos: int, fused: bool = True) -> int:
+        """Enqueues one step (reads self.hidden / self.positions, leaves logits and token ids on the device).
+        Returns the number of ops issued."""
+        be, s, b = self.be, self.s, self.n_seq
+        h, ff = s.hidden, s.ffn
+        scale = 1.0 / float(np.sqrt(s.head_dim))
+        n = 0
+        lin = lambda dt, w, x, y, i, o: be.linear(dt, w, x, y, b, i, o, ACT_INT8)
+        be.rms_norm(self.hidden, self.layers[0]["attn_norm"], self.hn, b, h, s.eps)
+        n += 1
+        for li, L in enumerate(self.layers):
+            lin(Q4K, L["wq"], self.hn, self.q, h, s.q_dim)
+            lin(Q4K, L["wk"], self.hn, self.k, h, s.kv_dim)
+            lin(Q6K, L["wv"], self.hn, self.v, h, s.kv_dim)
+            n += 3
+            if fused:
+                be.rope_write_kv(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], rows=1, pos=pos,
+                                 n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
+                n += 1
+            else:
+                be.rope(self.k, self.positions, self.k_rot, b, s.n_kv, s.head_dim, s.head_dim, s.theta)
+                be.rope(self.q, self.positions, self.q, b, s.n_head, s.head_dim, s.head_dim, s.theta)
+                n += 2
+                for sq in range(b):  # Op::WriteKv addresses one cache: one call per sequence
+                    for src, cache in ((self.k_rot, self.k_cache[li]), (self.v, self.v_cache[li])):
+                        row = be.wrap(src.device_ptr() + sq * s.kv_dim * 4, s.kv_dim * 4, USAGE_ACTIVATIONS)
+                        one = be.wrap(cache.device_ptr() + sq * self.seq_stride * 2, self.seq_stride * 2, USAGE_ACTIVATIONS)
+                        be.write_kv(row, one, 1, s.kv_dim, pos)
+                        row.close()
+                        one.close()
+                        n += 1
+            be.attention(self.q, self.k_cache[li], self.v_cache[li], self.attn, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
+                         head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride)
+            lin(Q4K, L["wo"], self.attn, self.sub, s.q_dim, h)
+            n += 2
+            if fused:
+                be.add_rms_norm(self.hidden, self.sub, self.hidden, L["ffn_norm"], self.hn, b, h, s.eps)
+                n += 1
+            else:
+                be.add(self.hidden, self.sub, self.hidden, b * h)
+                be.rms_norm(self.hidden, L["ffn_norm"], self.hn, b, h, s.eps)
+                n += 2
+            lin(Q4K, L["gate"], self.hn, self.g, h, ff)
+            lin(Q4K, L["up"], self.hn, self.u, h, ff)
+            be.gated_act(self.g, self.u, self.act, b, ff)
+            lin(Q6K, L["down"], self.act, self.sub, ff, h)
+            n += 4
+            nxt = self.layers[li + 1]["attn_norm"] if li + 1 < len(self.layers) else self.out_norm
+            if fused:
+                be.add_rms_norm(self.hidden, self.sub, self.hidden, nxt, self.hn, b, h, s.eps)
+                n += 1
+            else:
+                be.add(self.hidden, self.sub, self.hidden, b * h)
+                be.rms_norm(self.hidden, nxt, self.hn, b, h, s.eps)
+                n += 2
+        lin(self.head_dtype, self.head, self.hn, self.logits, h, s.vocab)
+        be.argmax(self.logits, self.tok, s.vocab, b)
+        return n + 2

@@ -70,6 +70,14 @@ class Oracle:
                                   _u8p, C.c_float, C.c_int, C.c_int, _f32p, _i32p, _f32p, _f32p,
                                   C.c_int]
         L.orc_num_threads.restype = C.c_int
+        L.orc_rms_norm.argtypes = [_f32p, _f32p, _f32p, C.c_size_t, C.c_size_t, C.c_float]
+        L.orc_rope.argtypes = [_f32p, _f32p, _f32p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_float, C.c_int]
+        L.orc_write_kv_f16.argtypes = [_f32p, _u16p, C.c_size_t, C.c_size_t, C.c_size_t]
+        L.orc_attention.argtypes = [_f32p, _u16p, _u16p, _f32p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t,
+                                    C.c_float, C.c_size_t]
+        L.orc_gated_act.argtypes = [_f32p, _f32p, _f32p, C.c_size_t]
+        L.orc_add.argtypes = [_f32p, _f32p, _f32p, C.c_size_t]
+        L.orc_argmax.argtypes = [_f32p, C.POINTER(C.c_uint32), C.c_size_t, C.c_size_t]
 
     # ---- scalars ---------------------------------------------------------------------------
     def f16_to_f32(self, h: int) -> float:
@@ -204,3 +212,55 @@ class Oracle:
                                 _p(ids, _i32p), _p(wts, _f32p), _p(logits, _f32p), threads)
         assert rc == 0
         return dst, ids, wts, logits
+
+    # ---- dense decode-step ops -------------------------------------------------------------
+    def rms_norm(self, x, w, eps) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        w = np.ascontiguousarray(w, np.float32)
+        rows, dim = x.reshape(-1, w.size).shape
+        out = np.empty_like(x)
+        self.L.orc_rms_norm(_p(x, _f32p), _p(w, _f32p), _p(out, _f32p), rows, dim, eps)
+        return out
+
+    def rope(self, x, pos, n_head, head_dim, rope_dim, theta, neox=False) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        pos = np.ascontiguousarray(pos, np.float32)
+        out = np.empty_like(x)
+        self.L.orc_rope(_p(x, _f32p), _p(pos, _f32p), _p(out, _f32p), pos.size, n_head, head_dim, rope_dim, theta,
+                        int(neox))
+        return out
+
+    def write_kv_f16(self, src, cache, rows, row_stride, pos):
+        """Writes into `cache` (uint16 array, modified in place)."""
+        src = np.ascontiguousarray(src, np.float32)
+        assert cache.dtype == np.uint16 and cache.flags.c_contiguous
+        self.L.orc_write_kv_f16(_p(src, _f32p), _p(cache, _u16p), rows, row_stride, pos)
+
+    def attention(self, q, k_cache, v_cache, rows, n_head, n_kv, head_dim, scale, pos) -> np.ndarray:
+        q = np.ascontiguousarray(q, np.float32)
+        assert k_cache.dtype == np.uint16 and v_cache.dtype == np.uint16
+        out = np.empty((rows, n_head * head_dim), np.float32)
+        self.L.orc_attention(_p(q, _f32p), _p(k_cache, _u16p), _p(v_cache, _u16p), _p(out, _f32p), rows, n_head, n_kv,
+                             head_dim, scale, pos)
+        return out
+
+    def gated_act(self, gate, up) -> np.ndarray:
+        gate = np.ascontiguousarray(gate, np.float32)
+        up = np.ascontiguousarray(up, np.float32)
+        out = np.empty_like(gate)
+        self.L.orc_gated_act(_p(gate, _f32p), _p(up, _f32p), _p(out, _f32p), gate.size)
+        return out
+
+    def add(self, a, b) -> np.ndarray:
+        a = np.ascontiguousarray(a, np.float32)
+        b = np.ascontiguousarray(b, np.float32)
+        out = np.empty_like(a)
+        self.L.orc_add(_p(a, _f32p), _p(b, _f32p), _p(out, _f32p), a.size)
+        return out
+
+    def argmax(self, x, n) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        rows = x.size // n
+        out = np.empty(rows, np.uint32)
+        self.L.orc_argmax(_p(x, _f32p), out.ctypes.data_as(C.POINTER(C.c_uint32)), n, rows)
+        return out

@@ -1,0 +1,93 @@
+"""A whole decode step (small Llama-shaped model, two sequences) through the C ABI against the same op sequence
+evaluated with the CPU restatement: same argmax, logits within the stated 1e-3 relative L2, KV rows written."""
+import numpy as np
+import pytest
+
+import fixtures as fx
+import infr_b200
+from infr_b200 import Q4K, Q6K, synth
+from infr_b200.decode import DecodeStep, LlamaShape
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = LlamaShape(n_layer=2, hidden=512, n_head=4, n_kv=2, head_dim=128, ffn=1024, vocab=1000)
+N_SEQ, MAX_CTX, POS = 2, 48, 37
+
+
+def _model(seed0=1000):
+    s = SHAPE
+    layers = []
+    for li in range(s.n_layer):
+        L = {}
+        for t, (name, dt, o, i) in enumerate(s.linears()):
+            L[name] = (dt, synth.weight(dt, o, i, seed=seed0 + li * 16 + t), o, i)
+        L["attn_norm"] = (1.0 + 0.02 * synth.normal(seed0 + li * 16 + 8, (s.hidden,))).astype(np.float32)
+        L["ffn_norm"] = (1.0 + 0.02 * synth.normal(seed0 + li * 16 + 9, (s.hidden,))).astype(np.float32)
+        layers.append(L)
+    out_norm = (1.0 + 0.02 * synth.normal(seed0 + 900, (s.hidden,))).astype(np.float32)
+    head = synth.weight(Q4K, s.vocab, s.hidden, seed=seed0 + 901)
+    kc = [synth.normal(9 + 2 * li, (N_SEQ * MAX_CTX, s.kv_dim)).astype(np.float16).view(np.uint16) for li in range(s.n_layer)]
+    vc = [synth.normal(10 + 2 * li, (N_SEQ * MAX_CTX, s.kv_dim)).astype(np.float16).view(np.uint16) for li in range(s.n_layer)]
+    return layers, out_norm, head, kc, vc
+
+
+def _oracle_step(o, layers, out_norm, head, kc, vc, hidden):
+    """The reference's op order on the CPU restatement; kc / vc are modified in place."""
+    s, b = SHAPE, N_SEQ
+    scale = 1.0 / np.sqrt(s.head_dim)
+    pos = np.full(b, POS, np.float32)
+    lin = lambda w, x: o.linear(w[0], w[1], x, b, w[3], w[2])
+    hidden = hidden.copy()
+    for li, L in enumerate(layers):
+        hn = o.rms_norm(hidden, L["attn_norm"], s.eps)
+        q, k, v = lin(L["wq"], hn), lin(L["wk"], hn), lin(L["wv"], hn)
+        k16 = o.rope(k, pos, s.n_kv, s.head_dim, s.head_dim, s.theta)
+        q = o.rope(q, pos, s.n_head, s.head_dim, s.head_dim, s.theta)
+        attn = np.empty((b, s.q_dim), np.float32)
+        for sq in range(b):
+            ks, vs = kc[li][sq * MAX_CTX:(sq + 1) * MAX_CTX], vc[li][sq * MAX_CTX:(sq + 1) * MAX_CTX]
+            o.write_kv_f16(k16[sq], ks, 1, s.kv_dim, POS)
+            o.write_kv_f16(v[sq], vs, 1, s.kv_dim, POS)
+            attn[sq] = o.attention(q[sq], ks, vs, 1, s.n_head, s.n_kv, s.head_dim, scale, POS)
+        hidden = o.add(hidden, lin(L["wo"], attn))
+        hn = o.rms_norm(hidden, L["ffn_norm"], s.eps)
+        act = o.gated_act(lin(L["gate"], hn), lin(L["up"], hn))
+        hidden = o.add(hidden, lin(L["down"], act))
+    hn = o.rms_norm(hidden, out_norm, s.eps)
+    logits = o.linear(Q4K, head, hn, b, s.hidden, s.vocab)
+    return logits, o.argmax(logits, s.vocab)
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_decode_step_matches_the_cpu_op_sequence(backend, oracle, fused):
+    s = SHAPE
+    layers, out_norm, head, kc, vc = _model()
+    hidden = synth.normal(77, (N_SEQ, s.hidden))
+    dev_layers = []
+    for L in layers:
+        d = {name: backend.from_numpy(L[name][1], infr_b200.USAGE_WEIGHTS) for name, *_ in s.linears()}
+        d["attn_norm"], d["ffn_norm"] = backend.from_numpy(L["attn_norm"]), backend.from_numpy(L["ffn_norm"])
+        dev_layers.append(d)
+    kcb, vcb = [backend.from_numpy(c) for c in kc], [backend.from_numpy(c) for c in vc]
+    step = DecodeStep(backend, s, N_SEQ, MAX_CTX, dev_layers, backend.from_numpy(out_norm), backend.from_numpy(head, infr_b200.USAGE_WEIGHTS),
+                      Q4K, kcb, vcb)
+    step.set_inputs(hidden, POS)
+    n_ops = step.run(POS, fused=fused)
+    assert n_ops > 0
+    got_logits = backend.download(step.logits, np.float32).reshape(N_SEQ, s.vocab)
+    got_tok = backend.download(step.tok, np.uint32)
+
+    want_kc, want_vc = [c.copy() for c in kc], [c.copy() for c in vc]
+    want_logits, want_tok = _oracle_step(oracle, layers, out_norm, head, want_kc, want_vc, hidden)
+    err = fx.rel_l2(got_logits, want_logits)
+    assert err < 1e-3, err
+    np.testing.assert_array_equal(got_tok, want_tok)
+    print(f"decode step fused={fused}: logits rel-L2 {err:.2e}, max-abs-diff {np.abs(got_logits - want_logits).max():.3e}")
+    # the new V rows are plain casts of a Linear output: compare as values (the Linear differs in f32 rounding)
+    for li in range(s.n_layer):
+        g = backend.download(vcb[li], np.uint16).reshape(vc[li].shape)
+        rows = [POS, MAX_CTX + POS]
+        assert fx.rel_l2(g[rows].view(np.float16).astype(np.float32), want_vc[li][rows].view(np.float16).astype(np.float32)) < 2e-3
+        keep = np.ones(g.shape[0], bool)
+        keep[rows] = False
+        np.testing.assert_array_equal(g[keep], vc[li][keep])

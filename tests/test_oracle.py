@@ -319,3 +319,82 @@ def test_moe_top_k_ties_keep_the_lower_expert_id(oracle):
                                     n_used=n_used, n_ff_exp=nff)
     np.testing.assert_array_equal(ids, np.array([[0, 1, 2], [0, 1, 2]], np.int32))
     np.testing.assert_allclose(wts, 1 / 3, rtol=1e-6)
+
+
+# ---- the dense decode-step ops: the reference holds no literal vectors for them, so the restatement is pinned by
+# ---- properties and by independent numpy / float64 evaluations of the same formulas
+def test_rms_norm_properties(oracle):
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((3, 512)).astype(np.float32) * 5
+    w = (1 + 0.1 * rng.standard_normal(512)).astype(np.float32)
+    y = oracle.rms_norm(x, w, 1e-5)
+    want = x.astype(np.float64) / np.sqrt((x.astype(np.float64) ** 2).mean(1, keepdims=True) + 1e-5) * w
+    assert fx.rel_l2(y, want) < 1e-6
+    y1 = oracle.rms_norm(x, np.ones(512, np.float32), 0.0)
+    np.testing.assert_allclose((y1.astype(np.float64) ** 2).mean(1), 1.0, rtol=1e-5)
+
+
+@pytest.mark.parametrize("neox", [False, True])
+def test_rope_is_a_rotation_by_relative_position(oracle, neox):
+    rng = np.random.default_rng(2)
+    nh, hd = 3, 64
+    q = rng.standard_normal((1, nh * hd)).astype(np.float32)
+    k = rng.standard_normal((1, nh * hd)).astype(np.float32)
+    np.testing.assert_array_equal(oracle.rope(q, [0.0], nh, hd, hd, 10000.0, neox), q)  # position 0: identity
+    # <rope(q, a), rope(k, b)> depends on a - b only, per head
+    def dots(a, b):
+        qa = oracle.rope(q, [a], nh, hd, hd, 10000.0, neox).reshape(nh, hd).astype(np.float64)
+        kb = oracle.rope(k, [b], nh, hd, hd, 10000.0, neox).reshape(nh, hd).astype(np.float64)
+        return (qa * kb).sum(1)
+    np.testing.assert_allclose(dots(17.0, 5.0), dots(112.0, 100.0), atol=2e-4)
+    # the first pair turns by exactly `pos` radians; a partial rope_dim leaves the tail alone
+    r = oracle.rope(q, [2.0], nh, hd, 32, 10000.0, neox).reshape(nh, hd)
+    i0, i1 = (0, 16) if neox else (0, 1)
+    q3 = q.reshape(nh, hd)
+    np.testing.assert_allclose(r[:, i0], q3[:, i0] * np.cos(2.0) - q3[:, i1] * np.sin(2.0), rtol=1e-5, atol=1e-6)
+    np.testing.assert_array_equal(r[:, 32:], q3[:, 32:])
+
+
+def test_write_kv_is_numpy_float16_rounding(oracle):
+    rng = np.random.default_rng(3)
+    src = (rng.standard_normal((2, 256)) * 10).astype(np.float32)
+    src[0, :3] = [65504.0, 65520.0, 5.96e-8]
+    cache = np.zeros((8, 256), np.uint16)
+    oracle.write_kv_f16(src, cache, 2, 256, 3)
+    with np.errstate(over="ignore"):
+        np.testing.assert_array_equal(cache[3:5], src.astype(np.float16).view(np.uint16))
+    assert not cache[:3].any() and not cache[5:].any()
+
+
+def test_attention_against_float64_softmax(oracle):
+    rng = np.random.default_rng(4)
+    nh, nkv, hd, pos, rows = 4, 2, 64, 20, 2
+    kc = rng.standard_normal((pos + rows, nkv * hd)).astype(np.float16)
+    vc = rng.standard_normal((pos + rows, nkv * hd)).astype(np.float16)
+    q = rng.standard_normal((rows, nh * hd)).astype(np.float32)
+    got = oracle.attention(q, kc.view(np.uint16), vc.view(np.uint16), rows, nh, nkv, hd, 0.125, pos)
+    want = np.empty_like(got, dtype=np.float64)
+    for ti in range(rows):
+        for h in range(nh):
+            kv = h // (nh // nkv)
+            K = kc[:pos + ti + 1, kv * hd:(kv + 1) * hd].astype(np.float64)
+            V = vc[:pos + ti + 1, kv * hd:(kv + 1) * hd].astype(np.float64)
+            sc = K @ q[ti, h * hd:(h + 1) * hd].astype(np.float64) * 0.125
+            p = np.exp(sc - sc.max())
+            want[ti, h * hd:(h + 1) * hd] = (p / p.sum()) @ V
+    assert fx.rel_l2(got, want) < 1e-6
+    # a single key: the output is that key's value row
+    one = oracle.attention(q[:1], kc.view(np.uint16), vc.view(np.uint16), 1, nh, nkv, hd, 0.125, 0)
+    np.testing.assert_array_equal(one.reshape(nh, hd)[0], vc[0, :hd].astype(np.float32))
+
+
+def test_gated_act_add_argmax(oracle):
+    rng = np.random.default_rng(5)
+    g, u = rng.standard_normal(1000).astype(np.float32) * 3, rng.standard_normal(1000).astype(np.float32)
+    want = g.astype(np.float64) / (1 + np.exp(-g.astype(np.float64))) * u
+    assert fx.rel_l2(oracle.gated_act(g, u), want) < 1e-6
+    np.testing.assert_array_equal(oracle.add(g, u), g + u)
+    x = rng.standard_normal((3, 500)).astype(np.float32)
+    x[1, 7] = x[1, 300] = 9.0
+    x[2, :] = -np.inf
+    np.testing.assert_array_equal(oracle.argmax(x, 500), [int(np.argmax(x[0])), 7, 0])

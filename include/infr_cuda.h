@@ -301,6 +301,19 @@ INFR_API int32_t infr_cuda_gated_act(infr_cuda_ctx *ctx, const infr_cuda_buf *ga
                                      uint32_t rows, uint32_t nff);
 /* Op::Add (cpu lib.rs:1972-1987). */
 INFR_API int32_t infr_cuda_add(infr_cuda_ctx *ctx, const infr_cuda_buf *a, const infr_cuda_buf *b, infr_cuda_buf *dst, uint64_t n);
+/* Producers fused with the activation quantiser: the result is written as the int8 codes, per-256 scales and code
+ * sums that infr_cuda_quantize_q8 (granularity 256) would produce from the f32 result, bit for bit, ready for
+ * infr_cuda_gemv_q8.  The row width (dim, nff, n_head * head_dim) must be a multiple of 256; sums16 may be NULL. */
+typedef struct infr_q8_out {
+    infr_cuda_buf *qs, *d, *sums, *sums16;
+} infr_q8_out;
+/* b == NULL: plain RmsNorm of a; else sum_dst = a + b (may be a) and the norm of the sum. */
+INFR_API int32_t infr_cuda_add_rms_norm_q8(infr_cuda_ctx *ctx, const infr_cuda_buf *a, const infr_cuda_buf *b, infr_cuda_buf *sum_dst,
+                                           const infr_cuda_buf *weight, uint32_t rows, uint32_t dim, float eps, const infr_q8_out *out);
+INFR_API int32_t infr_cuda_gated_act_q8(infr_cuda_ctx *ctx, const infr_cuda_buf *gate, const infr_cuda_buf *up, uint32_t rows, uint32_t nff,
+                                        const infr_q8_out *out);
+INFR_API int32_t infr_cuda_attention_q8(infr_cuda_ctx *ctx, const infr_attn_desc *desc, const infr_cuda_buf *q, const infr_cuda_buf *k_cache,
+                                        const infr_cuda_buf *v_cache, const infr_q8_out *out);
 /* Op::Argmax (cpu lib.rs:2167-2187): dst uint32 [rows], lowest index on ties. */
 INFR_API int32_t infr_cuda_argmax(infr_cuda_ctx *ctx, const infr_cuda_buf *x, infr_cuda_buf *dst, uint32_t n, uint32_t rows);
 

@@ -40,7 +40,7 @@ EXPORTED_SYMBOLS = [
     "infr_cuda_graph_free", "infr_cuda_timer_start", "infr_cuda_timer_stop", "infr_cuda_flush_l2",
     "infr_cuda_launch_count",
     "infr_cuda_rms_norm", "infr_cuda_add_rms_norm", "infr_cuda_rope", "infr_cuda_write_kv", "infr_cuda_attention", "infr_cuda_rope_write_kv",
-    "infr_cuda_gated_act", "infr_cuda_add", "infr_cuda_argmax",
+    "infr_cuda_gated_act", "infr_cuda_add", "infr_cuda_argmax", "infr_cuda_add_rms_norm_q8", "infr_cuda_gated_act_q8", "infr_cuda_attention_q8",
 ]
 
 
@@ -81,6 +81,10 @@ class _MoeDesc(C.Structure):
 class _AttnDesc(C.Structure):
     _fields_ = [("rows", C.c_uint32), ("pos", C.c_uint32), ("n_head", C.c_uint32), ("n_kv", C.c_uint32), ("head_dim", C.c_uint32),
                 ("scale", C.c_float), ("n_seq", C.c_uint32), ("reserved", C.c_uint32), ("seq_stride", C.c_uint64)]
+
+
+class _Q8Out(C.Structure):
+    _fields_ = [("qs", C.c_void_p), ("d", C.c_void_p), ("sums", C.c_void_p), ("sums16", C.c_void_p)]
 
 
 class _GraphDesc(C.Structure):
@@ -154,6 +158,9 @@ def load_library() -> C.CDLL:
         "infr_cuda_gated_act": (i32, [vp, vp, vp, vp, u32, u32]),
         "infr_cuda_add": (i32, [vp, vp, vp, vp, u64]),
         "infr_cuda_argmax": (i32, [vp, vp, vp, u32, u32]),
+        "infr_cuda_add_rms_norm_q8": (i32, [vp, vp, vp, vp, vp, u32, u32, C.c_float, C.POINTER(_Q8Out)]),
+        "infr_cuda_gated_act_q8": (i32, [vp, vp, vp, u32, u32, C.POINTER(_Q8Out)]),
+        "infr_cuda_attention_q8": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, C.POINTER(_Q8Out)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -503,6 +510,28 @@ class CudaBackend:
 
     def add(self, a: Buffer, b: Buffer, dst: Buffer, n: int):
         self._check(self.L.infr_cuda_add(self.ctx, a.handle, b.handle, dst.handle, n))
+
+    @staticmethod
+    def _q8_out(qs: Buffer, d: Buffer, sums: Buffer, sums16: Optional[Buffer]):
+        return _Q8Out(qs.handle, d.handle, sums.handle, sums16.handle if sums16 else None)
+
+    def add_rms_norm_q8(self, a: Buffer, b: Optional[Buffer], sum_dst: Optional[Buffer], weight: Buffer, rows: int, dim: int, eps: float,
+                        qs: Buffer, d: Buffer, sums: Buffer, sums16: Optional[Buffer] = None):
+        """RmsNorm (of a + b when b is given, the sum also written to sum_dst) ending in the activation quantiser."""
+        o = self._q8_out(qs, d, sums, sums16)
+        self._check(self.L.infr_cuda_add_rms_norm_q8(self.ctx, a.handle, b.handle if b else None, sum_dst.handle if sum_dst else None,
+                                                     weight.handle, rows, dim, eps, C.byref(o)))
+
+    def gated_act_q8(self, gate: Buffer, up: Buffer, rows: int, nff: int, qs: Buffer, d: Buffer, sums: Buffer,
+                     sums16: Optional[Buffer] = None):
+        o = self._q8_out(qs, d, sums, sums16)
+        self._check(self.L.infr_cuda_gated_act_q8(self.ctx, gate.handle, up.handle, rows, nff, C.byref(o)))
+
+    def attention_q8(self, q: Buffer, k_cache: Buffer, v_cache: Buffer, qs: Buffer, d: Buffer, sums: Buffer, sums16: Optional[Buffer] = None, *,
+                     rows: int, pos: int, n_head: int, n_kv: int, head_dim: int, scale: float, n_seq: int = 1, seq_stride: int = 0):
+        dsc = self._attn_desc(rows, pos, n_head, n_kv, head_dim, scale, n_seq, seq_stride)
+        o = self._q8_out(qs, d, sums, sums16)
+        self._check(self.L.infr_cuda_attention_q8(self.ctx, C.byref(dsc), q.handle, k_cache.handle, v_cache.handle, C.byref(o)))
 
     def argmax(self, x: Buffer, dst: Buffer, n: int, rows: int):
         self._check(self.L.infr_cuda_argmax(self.ctx, x.handle, dst.handle, n, rows))

@@ -404,14 +404,34 @@ Status CudaBackend::rope_write_kv(const infr_attn_desc &d, float theta, int neox
     return s;
 }
 
-Status CudaBackend::attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst) {
+Status CudaBackend::rms_norm_q8(const float *a, const float *b, float *sum_dst, const float *w, uint32_t rows, uint32_t dim, float eps, const Q8Dev &q8) {
+    cudaSetDevice(device_);
+    Status s = cuda_status(launch_rms_norm_q8(a, b, sum_dst, w, (int)rows, (int)dim, eps, const_cast<int8_t *>(q8.qs), const_cast<float *>(q8.d),
+                                              const_cast<int32_t *>(q8.sums), const_cast<int32_t *>(q8.sums16), stream_),
+                           "rms_norm_q8");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+Status CudaBackend::gated_act_q8(const float *gate, const float *up, uint32_t rows, uint32_t nff, const Q8Dev &q8) {
+    cudaSetDevice(device_);
+    Status s = cuda_status(launch_gated_silu_q8(gate, up, (int)rows, (int)nff, const_cast<int8_t *>(q8.qs), const_cast<float *>(q8.d),
+                                                const_cast<int32_t *>(q8.sums), const_cast<int32_t *>(q8.sums16), stream_),
+                           "gated_act_q8");
+    if (s.ok()) launches_++;
+    return s;
+}
+
+Status CudaBackend::attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst, const Q8Dev *q8) {
     cudaSetDevice(device_);
     const uint32_t n_seq = d.n_seq ? d.n_seq : 1;
     const size_t ws = attention_workspace_bytes((int)(n_seq * d.rows), (int)d.n_head, (int)d.head_dim, (int)(d.pos + d.rows));
     Status s = ensure_scratch(ws);
     if (!s.ok()) return s;
     s = cuda_status(launch_attention(q, k_cache, v_cache, dst, scratch_, (int)n_seq, (int)d.rows, (int)d.n_head, (int)d.n_kv, (int)d.head_dim,
-                                     d.scale, (int)d.pos, (size_t)d.seq_stride, stream_),
+                                     d.scale, (int)d.pos, (size_t)d.seq_stride, stream_, q8 ? const_cast<int8_t *>(q8->qs) : nullptr,
+                                     q8 ? const_cast<float *>(q8->d) : nullptr, q8 ? const_cast<int32_t *>(q8->sums) : nullptr,
+                                     q8 ? const_cast<int32_t *>(q8->sums16) : nullptr),
                     "attention");
     if (s.ok()) launches_ += 2;
     return s;

@@ -112,7 +112,9 @@ public:
     Status write_kv(const float *src, void *cache_at_pos, size_t n);
     Status rope_write_kv(const infr_attn_desc &d, float theta, int neox, float *q, const float *k, const float *v, const int32_t *positions,
                          void *k_cache, void *v_cache);
-    Status attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst);
+    Status attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst, const Q8Dev *q8 = nullptr);
+    Status rms_norm_q8(const float *a, const float *b, float *sum_dst, const float *w, uint32_t rows, uint32_t dim, float eps, const Q8Dev &q8);
+    Status gated_act_q8(const float *gate, const float *up, uint32_t rows, uint32_t nff, const Q8Dev &q8);
     Status gated_act(const float *gate, const float *up, float *dst, size_t n);
     Status add(const float *a, const float *b, float *dst, size_t n);
     Status argmax(const float *x, uint32_t *dst, uint32_t n, uint32_t rows);

@@ -351,8 +351,8 @@ Status check_attn(const infr_attn_desc *d, const char *what) {
     const uint32_t g = d->n_head / d->n_kv;
     if ((d->head_dim != 64 && d->head_dim != 128) || (g != 1 && g != 2 && g != 4 && g != 8))
         return Status::Err(INFR_E_UNSUPPORTED, std::string(what) + ": head_dim 64 or 128 and n_head / n_kv in {1, 2, 4, 8}");
-    if (d->n_seq > 1 && d->seq_stride < (uint64_t)(d->pos + d->rows) * d->n_kv * d->head_dim)
-        return Status::Err(INFR_E_INVALID, std::string(what) + ": seq_stride is smaller than one sequence's rows");
+    if (d->n_seq > 1 && (d->seq_stride < (uint64_t)(d->pos + d->rows) * d->n_kv * d->head_dim || d->seq_stride % 8))
+        return Status::Err(INFR_E_INVALID, std::string(what) + ": seq_stride must cover one sequence's rows and be a multiple of 8 elements");
     return Status::Ok();
 }
 }  // namespace
@@ -387,6 +387,68 @@ int32_t infr_cuda_rope_write_kv(infr_cuda_ctx *ctx, const infr_attn_desc *d, flo
         !(s = span(v_cache, cn, "rope_write_kv v_cache", &pvc)).ok())
         return finish(ctx, s);
     return finish(ctx, ctx->be->rope_write_kv(*d, theta, neox != 0, (float *)pq, (const float *)pk, (const float *)pv, (const int32_t *)pp, pkc, pvc));
+}
+
+namespace {
+// Checks the four outputs of a fused quantiser for `rows` rows of `k` elements.
+Status q8_out_args(const infr_q8_out *o, size_t rows, size_t k, const char *what, infr::Q8Dev *out) {
+    if (!o) return Status::Err(INFR_E_INVALID, std::string(what) + ": null int8 output descriptor");
+    if (k == 0 || k % 256) return Status::Err(INFR_E_INVALID, std::string(what) + ": the row width must be a multiple of 256");
+    uint8_t *pq, *pd, *ps, *p16 = nullptr;
+    Status s;
+    const size_t n = rows * k;
+    if (!(s = span(o->qs, n, what, &pq)).ok() || !(s = span(o->d, n / 256 * 4, what, &pd)).ok() || !(s = span(o->sums, n / 32 * 4, what, &ps)).ok())
+        return s;
+    if (o->sums16 && !(s = span(o->sums16, n / 16 * 4, what, &p16)).ok()) return s;
+    *out = infr::Q8Dev{(const int8_t *)pq, (const float *)pd, (const int32_t *)ps, (const int32_t *)p16, 256};
+    return Status::Ok();
+}
+}  // namespace
+
+int32_t infr_cuda_add_rms_norm_q8(infr_cuda_ctx *ctx, const infr_cuda_buf *a, const infr_cuda_buf *b, infr_cuda_buf *sum_dst,
+                                  const infr_cuda_buf *weight, uint32_t rows, uint32_t dim, float eps, const infr_q8_out *out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (rows == 0) return finish(ctx, Status::Err(INFR_E_INVALID, "add_rms_norm_q8: rows must be positive"));
+    infr::Q8Dev q8;
+    Status s = q8_out_args(out, rows, dim, "add_rms_norm_q8 output", &q8);
+    if (!s.ok()) return finish(ctx, s);
+    uint8_t *pa, *pb = nullptr, *ps = nullptr, *pw;
+    const size_t n = (size_t)rows * dim * 4;
+    if (!(s = span(a, n, "add_rms_norm_q8 a", &pa)).ok() || !(s = span(weight, (size_t)dim * 4, "add_rms_norm_q8 weight", &pw)).ok())
+        return finish(ctx, s);
+    if (b && (!(s = span(b, n, "add_rms_norm_q8 b", &pb)).ok() || !(s = span(sum_dst, n, "add_rms_norm_q8 sum_dst", &ps)).ok()))
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->rms_norm_q8((const float *)pa, (const float *)pb, (float *)ps, (const float *)pw, rows, dim, eps, q8));
+}
+
+int32_t infr_cuda_gated_act_q8(infr_cuda_ctx *ctx, const infr_cuda_buf *gate, const infr_cuda_buf *up, uint32_t rows, uint32_t nff,
+                               const infr_q8_out *out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (rows == 0) return finish(ctx, Status::Err(INFR_E_INVALID, "gated_act_q8: rows must be positive"));
+    infr::Q8Dev q8;
+    Status s = q8_out_args(out, rows, nff, "gated_act_q8 output", &q8);
+    if (!s.ok()) return finish(ctx, s);
+    uint8_t *pg, *pu;
+    const size_t n = (size_t)rows * nff * 4;
+    if (!(s = span(gate, n, "gated_act_q8 gate", &pg)).ok() || !(s = span(up, n, "gated_act_q8 up", &pu)).ok()) return finish(ctx, s);
+    return finish(ctx, ctx->be->gated_act_q8((const float *)pg, (const float *)pu, rows, nff, q8));
+}
+
+int32_t infr_cuda_attention_q8(infr_cuda_ctx *ctx, const infr_attn_desc *d, const infr_cuda_buf *q, const infr_cuda_buf *k_cache,
+                               const infr_cuda_buf *v_cache, const infr_q8_out *out) {
+    INFR_CTX_OR_RETURN(ctx);
+    Status s = check_attn(d, "attention_q8");
+    if (!s.ok()) return finish(ctx, s);
+    const size_t n_seq = d->n_seq ? d->n_seq : 1;
+    infr::Q8Dev q8;
+    if (!(s = q8_out_args(out, n_seq * d->rows, (size_t)d->n_head * d->head_dim, "attention_q8 output", &q8)).ok()) return finish(ctx, s);
+    const size_t qn = n_seq * d->rows * d->n_head * d->head_dim * 4;
+    const size_t cn = ((n_seq - 1) * (size_t)d->seq_stride + (size_t)(d->pos + d->rows) * d->n_kv * d->head_dim) * 2;
+    uint8_t *pq, *pk, *pv;
+    if (!(s = span(q, qn, "attention_q8 q", &pq)).ok() || !(s = span(k_cache, cn, "attention_q8 k_cache", &pk)).ok() ||
+        !(s = span(v_cache, cn, "attention_q8 v_cache", &pv)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->attention(*d, (const float *)pq, pk, pv, nullptr, &q8));
 }
 
 int32_t infr_cuda_gated_act(infr_cuda_ctx *ctx, const infr_cuda_buf *gate, const infr_cuda_buf *up, infr_cuda_buf *dst, uint32_t rows,

@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(const float *a, const fl
     pdl_go();
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * dim;
-    const int n4 = dim >> 2;
+    const int n4 = (dim & 3) ? 0 : dim >> 2;  // 16-byte accesses only when every row starts on a 16-byte boundary
     float ss = 0.f;
     for (int i = threadIdx.x; i < n4; i += blockDim.x) {
         float4 v = reinterpret_cast<const float4 *>(a + base)[i];
@@ -219,12 +219,32 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
         }
         return;
     }
-    const float *qrow = q + ((size_t)qr * n_head + (size_t)kvh * G) * HD;
-    for (int i = tid; i < G * HD; i += kAttnTile) s_q[i] = qrow[i];
-    __syncthreads();
     const size_t kv_row = (size_t)n_kv * HD;
     const __half *kbase = k_cache + (size_t)seq * seq_stride + (size_t)kvh * HD;
     const __half *vbase = v_cache + (size_t)seq * seq_stride + (size_t)kvh * HD;
+    // the value rows of this warp's 32 keys are requested first and used last (phase 3), the key row of this
+    // thread's key next: every global load of the CTA is in flight before the first multiply
+    const int jw = key0 + warp * 32;
+    const int cnt = min(32, n_keys - jw);  // may be <= 0
+    const __half *vr = vbase + (size_t)jw * kv_row + lane * DPL;
+    uint32_t raw[32][DPL / 2];
+#pragma unroll
+    for (int jj = 0; jj < 32; jj++) {
+        if (jj < cnt) {
+            if (DPL == 4) {
+                const uint2 t = __ldg(reinterpret_cast<const uint2 *>(vr + (size_t)jj * kv_row));
+                raw[jj][0] = t.x, raw[jj][DPL / 2 - 1] = t.y;
+            } else {
+                raw[jj][0] = __ldg(reinterpret_cast<const uint32_t *>(vr + (size_t)jj * kv_row));
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < DPL / 2; e++) raw[jj][e] = 0u;
+        }
+    }
+    const float *qrow = q + ((size_t)qr * n_head + (size_t)kvh * G) * HD;
+    for (int i = tid; i < G * HD; i += kAttnTile) s_q[i] = qrow[i];
+    __syncthreads();
     // ---- phase 1
     {
         const int j = key0 + tid;
@@ -233,10 +253,12 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
         for (int g = 0; g < G; g++) acc[g] = 0.f;
         if (j < n_keys) {
             const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)j * kv_row);
-#pragma unroll 4
+            uint4 kraw[HD / 8];
+#pragma unroll
+            for (int c = 0; c < HD / 8; c++) kraw[c] = __ldg(kr + c);
+#pragma unroll
             for (int c = 0; c < HD / 8; c++) {
-                const uint4 raw = __ldg(kr + c);
-                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+                const __half2 *h2 = reinterpret_cast<const __half2 *>(&kraw[c]);
                 float kf[8];
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
@@ -286,25 +308,17 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
         for (int g = 0; g < G; g++)
 #pragma unroll
             for (int e = 0; e < DPL; e++) o[g][e] = 0.f;
-        const int jw = key0 + warp * 32;
-        const int cnt = min(32, n_keys - jw);  // may be <= 0
-        const __half *vr = vbase + (size_t)jw * kv_row + lane * DPL;
-#pragma unroll 4
-        for (int jj = 0; jj < cnt; jj++) {
+#pragma unroll
+        for (int jj = 0; jj < 32; jj++) {
             float vf[DPL];
-            if (DPL == 4) {
-                const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(vr + (size_t)jj * kv_row));
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-                const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-                vf[0] = f0.x, vf[1] = f0.y, vf[2] = f1.x, vf[3] = f1.y;
-            } else {
-                const uint32_t raw = __ldg(reinterpret_cast<const uint32_t *>(vr + (size_t)jj * kv_row));
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw));
-                vf[0] = f0.x, vf[1] = f0.y;
+#pragma unroll
+            for (int e = 0; e < DPL / 2; e++) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&raw[jj][e]));
+                vf[2 * e] = f.x, vf[2 * e + 1] = f.y;
             }
 #pragma unroll
             for (int g = 0; g < G; g++) {
-                const float p = s_p[g][warp * 32 + jj];
+                const float p = jj < cnt ? s_p[g][warp * 32 + jj] : 0.f;
 #pragma unroll
                 for (int e = 0; e < DPL; e++) o[g][e] = fmaf(vf[e], p, o[g][e]);
             }
@@ -422,6 +436,141 @@ __global__ void __launch_bounds__(256) argmax_stage2_kernel(const float *__restr
     if (threadIdx.x == 0) dst[blockIdx.x] = s_bi == 0xffffffffu ? 0u : s_bi;
 }
 
+// ---------------------------------------------------------------------------------------------- producers that emit int8
+// The activation quantiser's arithmetic for one 256-element block held by one warp (lane l owns elements 4l..4l+3
+// and 128+4l..128+4l+3): d = amax / 127, id = d > 0 ? 1/d : 0, q = clamp(roundf(x * id), -127, 127), plus the
+// per-32 and per-16 code sums (crates/infr-cpu/src/quant.rs:27-58).  Same operations in the same order as
+// quantize_q8_kernel<256>, so a producer that ends with this emits the bits the separate quantiser would.
+__device__ __forceinline__ float q8_amax4(float4 v) { return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))); }
+__device__ __forceinline__ int q8_code(float v, float id) {
+    float r = roundf(v * id);
+    r = fminf(fmaxf(r, -127.0f), 127.0f);
+    return (int)r;
+}
+__device__ __forceinline__ void quantize_block256(const float4 v[2], int lane, size_t row, int k, int chunk, int8_t *__restrict__ qs,
+                                                  float *__restrict__ d, int32_t *__restrict__ sums, int32_t *__restrict__ sums16) {
+    float m = fmaxf(q8_amax4(v[0]), q8_amax4(v[1]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float dd = m / 127.0f;
+    const float id = dd > 0.0f ? 1.0f / dd : 0.0f;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int e = chunk * 256 + h * 128 + lane * 4;
+        const int q0 = q8_code(v[h].x, id), q1 = q8_code(v[h].y, id), q2 = q8_code(v[h].z, id), q3 = q8_code(v[h].w, id);
+        int sm = q0 + q1 + q2 + q3;
+        sm += __shfl_xor_sync(0xffffffffu, sm, 1);
+        sm += __shfl_xor_sync(0xffffffffu, sm, 2);
+        const int s16 = sm;
+        sm += __shfl_xor_sync(0xffffffffu, sm, 4);
+        const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+        *reinterpret_cast<uint32_t *>(qs + row * k + e) = packed;
+        if (sums16 && (lane & 3) == 0) sums16[row * (k / 16) + e / 16] = s16;
+        if ((lane & 7) == 0) sums[row * (k / 32) + e / 32] = sm;
+    }
+    if (lane == 0) d[row * (k / 256) + chunk] = dd;
+}
+
+// RMSNorm (optionally of a + b, written to sum_dst) whose output goes straight to int8; dim % 256 == 0.
+template <bool ADD>
+__global__ void __launch_bounds__(1024) rms_norm_q8_kernel(const float *a, const float *b, float *sum_dst, const float *__restrict__ w, int dim,
+                                                           float eps, int8_t *__restrict__ qs, float *__restrict__ d, int32_t *__restrict__ sums,
+                                                           int32_t *__restrict__ sums16) {
+    __shared__ float s_part[32];
+    __shared__ float s_scale;
+    pdl_go();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * dim;
+    const int n4 = dim >> 2;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+        float4 v = reinterpret_cast<const float4 *>(a + base)[i];
+        if (ADD) {
+            const float4 u = reinterpret_cast<const float4 *>(b + base)[i];
+            v.x += u.x, v.y += u.y, v.z += u.z, v.w += u.w;
+            reinterpret_cast<float4 *>(sum_dst + base)[i] = v;
+        }
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();  // also orders the CTA's sum_dst stores before the loads below
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x + 31) / 32 ? s_part[threadIdx.x] : 0.f;
+        t = warp_sum(t);
+        if (threadIdx.x == 0) s_scale = 1.0f / sqrtf(t / (float)dim + eps);
+    }
+    __syncthreads();
+    const float s = s_scale;
+    const float *src = (ADD ? sum_dst : a) + base;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int chunk = warp; chunk < dim / 256; chunk += nw) {
+        float4 v[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int e = chunk * 256 + h * 128 + lane * 4;
+            const float4 x = *reinterpret_cast<const float4 *>(src + e);
+            const float4 g = *reinterpret_cast<const float4 *>(w + e);
+            v[h] = make_float4(x.x * s * g.x, x.y * s * g.y, x.z * s * g.z, x.w * s * g.w);
+        }
+        quantize_block256(v, lane, blockIdx.x, dim, chunk, qs, d, sums, sums16);
+    }
+}
+
+// silu(gate) * up straight to int8: warp = (row, 256-element block); nff % 256 == 0.
+__global__ void __launch_bounds__(256) gated_silu_q8_kernel(const float *__restrict__ gate, const float *__restrict__ up, int rows, int nff,
+                                                            int8_t *__restrict__ qs, float *__restrict__ d, int32_t *__restrict__ sums,
+                                                            int32_t *__restrict__ sums16) {
+    pdl_go();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, cpr = nff / 256;
+    const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wg >= (long long)rows * cpr) return;
+    const int row = (int)(wg / cpr), chunk = (int)(wg % cpr);
+    float4 v[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const size_t e = (size_t)row * nff + chunk * 256 + h * 128 + lane * 4;
+        const float4 g = *reinterpret_cast<const float4 *>(gate + e), u = *reinterpret_cast<const float4 *>(up + e);
+        v[h] = make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y, g.z / (1.0f + expf(-g.z)) * u.z,
+                           g.w / (1.0f + expf(-g.w)) * u.w);
+    }
+    quantize_block256(v, lane, (size_t)row, nff, chunk, qs, d, sums, sums16);
+}
+
+// The merge of the key tiles with the result quantised in place of an f32 store: warp = (query row, 256 outputs).
+__global__ void __launch_bounds__(256) attn_combine_q8_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int q_rows,
+                                                              int n_head, int head_dim, int n_splits, int8_t *__restrict__ qs,
+                                                              float *__restrict__ d, int32_t *__restrict__ sums, int32_t *__restrict__ sums16) {
+    pdl_go();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, k = n_head * head_dim, cpr = k / 256;
+    const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wg >= (long long)q_rows * cpr) return;
+    const int row = (int)(wg / cpr), chunk = (int)(wg % cpr);
+    float4 v[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int e = chunk * 256 + h * 128 + lane * 4, head = e / head_dim, dim0 = e % head_dim;
+        const size_t rh = (size_t)row * n_head + head;
+        const float *ml = part_ml + rh * n_splits * 2;
+        float m = -INFINITY;
+        for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
+        float l = 0.f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < n_splits; s++) {
+            const float ls = ml[2 * s + 1];
+            if (ls == 0.f) continue;
+            const float wgt = expf(ml[2 * s] - m);
+            l += wgt * ls;
+            const float4 p = *reinterpret_cast<const float4 *>(part_o + (rh * n_splits + s) * head_dim + dim0);
+            o.x = fmaf(wgt, p.x, o.x), o.y = fmaf(wgt, p.y, o.y), o.z = fmaf(wgt, p.z, o.z), o.w = fmaf(wgt, p.w, o.w);
+        }
+        v[h] = make_float4(o.x / l, o.y / l, o.z / l, o.w / l);
+    }
+    quantize_block256(v, lane, (size_t)row, k, chunk, qs, d, sums, sums16);
+}
+
 inline unsigned grid_for(size_t n, int block, const DeviceInfo &dev) {
     const size_t want = (n + (size_t)block - 1) / (size_t)block;
     const size_t cap = (size_t)dev.sm_count * 8;
@@ -479,7 +628,8 @@ static cudaError_t launch_attn_hd(int group, dim3 grid, cudaStream_t st, const f
 }
 
 cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_cache, float *dst, void *workspace, int n_seq, int rows, int n_head,
-                             int n_kv, int head_dim, float scale, int pos, size_t seq_stride, cudaStream_t st) {
+                             int n_kv, int head_dim, float scale, int pos, size_t seq_stride, cudaStream_t st, int8_t *qs, float *d, int32_t *sums,
+                             int32_t *sums16) {
     if (n_seq <= 0 || rows <= 0 || n_head <= 0 || n_kv <= 0 || n_head % n_kv || pos < 0) return cudaErrorInvalidValue;
     const int max_keys = pos + rows, n_splits = (max_keys + kAttnTile - 1) / kAttnTile, q_rows = n_seq * rows;
     if (n_kv > 65535 || q_rows > 65535) return cudaErrorInvalidValue;
@@ -495,7 +645,30 @@ cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_
     else
         return cudaErrorInvalidValue;
     if (e != cudaSuccess) return e;
+    if (qs) {  // the merged rows go straight to int8 (n_head * head_dim must be whole 256-element blocks)
+        if ((n_head * head_dim) % 256) return cudaErrorInvalidValue;
+        const long long warps = (long long)q_rows * (n_head * head_dim / 256);
+        return launch_pdl(attn_combine_q8_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, st, (const float *)po, (const float *)pml,
+                          q_rows, n_head, head_dim, n_splits, qs, d, sums, sums16);
+    }
     return launch_pdl(attn_combine_kernel, dim3(q_rows * n_head), dim3(head_dim), 0, st, (const float *)po, (const float *)pml, dst, head_dim, n_splits);
+}
+
+cudaError_t launch_rms_norm_q8(const float *a, const float *b, float *sum_dst, const float *w, int rows, int dim, float eps, int8_t *qs, float *d,
+                               int32_t *sums, int32_t *sums16, cudaStream_t st) {
+    if (rows <= 0 || dim <= 0 || dim % 256) return cudaErrorInvalidValue;
+    int threads = dim / 256 * 32;
+    threads = threads > 1024 ? 1024 : threads;
+    if (b) return launch_pdl(rms_norm_q8_kernel<true>, dim3(rows), dim3(threads), 0, st, a, b, sum_dst, w, dim, eps, qs, d, sums, sums16);
+    return launch_pdl(rms_norm_q8_kernel<false>, dim3(rows), dim3(threads), 0, st, a, (const float *)nullptr, (float *)nullptr, w, dim, eps, qs, d, sums,
+                      sums16);
+}
+
+cudaError_t launch_gated_silu_q8(const float *gate, const float *up, int rows, int nff, int8_t *qs, float *d, int32_t *sums, int32_t *sums16,
+                                 cudaStream_t st) {
+    if (rows <= 0 || nff <= 0 || nff % 256) return cudaErrorInvalidValue;
+    const long long warps = (long long)rows * (nff / 256);
+    return launch_pdl(gated_silu_q8_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, st, gate, up, rows, nff, qs, d, sums, sums16);
 }
 
 cudaError_t launch_gated_silu(const float *gate, const float *up, float *dst, size_t n, const DeviceInfo &dev, cudaStream_t st) {

@@ -1,8 +1,9 @@
 """One decode step of a Llama-family model as the sequence of backend ops the reference emits for it
 (crates/infr-llama/src/seam/runner.rs:2641-4493: RmsNorm, Linear q/k/v, Rope, WriteKv, Attention, Linear o, Add,
 RmsNorm, Linear gate/up, GatedAct, Linear down, Add, ..., RmsNorm, Linear lm_head, Argmax), issued through the
-C ABI.  `fused=True` uses the fused launches (Add+RmsNorm, Rope+Rope+WriteKv+WriteKv); `fused=False` issues the
-reference's ops one by one.  The batch is `n_seq` independent sequences, one new token each, all at position `pos`,
+C ABI.  `fused=True` uses the fused launches (Add+RmsNorm, Rope+Rope+WriteKv+WriteKv) and, for at most 8 rows, the
+producers that end in the activation quantiser, so that every Linear is one GEMV launch on int8 codes shared by all
+Linears that read the same input; `fused=False` issues the reference's ops one by one.  The batch is `n_seq` independent sequences, one new token each, all at position `pos`,
 every sequence with its own f16 KV cache."""
 from __future__ import annotations
 
@@ -60,26 +61,80 @@ class DecodeStep:
         self.tok = be.alloc(b * 4, USAGE_ACTIVATIONS)
         self.positions = be.alloc(b * 4, USAGE_ACTIVATIONS)
         self.seq_stride = max_ctx * s.kv_dim
+        # int8 activations shared by the Linears that read the same input (q/k/v; gate/up): codes, per-256 scales,
+        # per-32 and per-16 code sums, sized for the widest input
+        kmax = max(s.hidden, s.ffn, s.q_dim)
+        self.a_qs = be.alloc(b * kmax, USAGE_ACTIVATIONS)
+        self.a_d = be.alloc(b * (kmax // 256) * 4, USAGE_ACTIVATIONS)
+        self.a_sums = be.alloc(b * (kmax // 32) * 4, USAGE_ACTIVATIONS)
+        self.a_sums16 = be.alloc(b * (kmax // 16) * 4, USAGE_ACTIVATIONS)
 
     def set_inputs(self, hidden: np.ndarray, pos: int):
         self.be.upload(self.hidden, np.ascontiguousarray(hidden, np.float32))
         self.be.upload(self.positions, np.full(self.n_seq, pos, np.int32))
 
-    def run(self, pos: int, fused: bool = True) -> int:
+    def run(self, pos: int, fused: bool = True, q8_fused=None) -> int:
         """Enqueues one step (reads self.hidden / self.positions, leaves logits and token ids on the device).
         Returns the number of ops issued."""
+        s, b = self.s, self.n_seq
+        if q8_fused is None:
+            q8_fused = fused and b <= 8 and s.hidden % 256 == 0 and s.ffn % 256 == 0 and s.q_dim % 256 == 0
+        return self._run_q8(pos) if q8_fused else self._run_f32(pos, fused)
+
+    def _run_q8(self, pos: int) -> int:
+        """At most 8 rows: activations travel between ops as int8 codes wherever the consumer is a Linear."""
+        be, s, b = self.be, self.s, self.n_seq
+        h, ff = s.hidden, s.ffn
+        scale = 1.0 / float(np.sqrt(s.head_dim))
+        a8 = (self.a_qs, self.a_d, self.a_sums, self.a_sums16)
+        gemv = lambda dt, w, y, k, o: be.gemv_q8(dt, w, self.a_qs, self.a_d, self.a_sums, self.a_sums16, y, b, k, o)
+        be.add_rms_norm_q8(self.hidden, None, None, self.layers[0]["attn_norm"], b, h, s.eps, *a8)
+        n = 1
+        for li, L in enumerate(self.layers):
+            gemv(Q4K, L["wq"], self.q, h, s.q_dim)
+            gemv(Q4K, L["wk"], self.k, h, s.kv_dim)
+            gemv(Q6K, L["wv"], self.v, h, s.kv_dim)
+            be.rope_write_kv(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], rows=1, pos=pos,
+                             n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
+            be.attention_q8(self.q, self.k_cache[li], self.v_cache[li], *a8, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
+                            head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride)
+            gemv(Q4K, L["wo"], self.sub, s.q_dim, h)
+            be.add_rms_norm_q8(self.hidden, self.sub, self.hidden, L["ffn_norm"], b, h, s.eps, *a8)
+            gemv(Q4K, L["gate"], self.g, h, ff)
+            gemv(Q4K, L["up"], self.u, h, ff)
+            be.gated_act_q8(self.g, self.u, b, ff, *a8)
+            gemv(Q6K, L["down"], self.sub, ff, h)
+            nxt = self.layers[li + 1]["attn_norm"] if li + 1 < len(self.layers) else self.out_norm
+            be.add_rms_norm_q8(self.hidden, self.sub, self.hidden, nxt, b, h, s.eps, *a8)
+            n += 13
+        gemv(self.head_dtype, self.head, self.logits, h, s.vocab)
+        be.argmax(self.logits, self.tok, s.vocab, b)
+        return n + 2
+
+    def _run_f32(self, pos: int, fused: bool) -> int:
         be, s, b = self.be, self.s, self.n_seq
         h, ff = s.hidden, s.ffn
         scale = 1.0 / float(np.sqrt(s.head_dim))
         n = 0
         lin = lambda dt, w, x, y, i, o: be.linear(dt, w, x, y, b, i, o, ACT_INT8)
+        # fused and at most 8 rows: quantise an input once and run every Linear that reads it on the shared codes
+        # (the same quantiser and GEMV kernels that Linear uses: bit-identical results)
+        share = fused and b <= 8 and h % 256 == 0 and ff % 256 == 0
+
+        def lin_many(x, k, outs):
+            nonlocal n
+            if share:
+                be.quantize_q8(256, x, b, k, self.a_qs, self.a_d, self.a_sums, self.a_sums16)
+                for dt, w, y, o in outs:
+                    be.gemv_q8(dt, w, self.a_qs, self.a_d, self.a_sums, self.a_sums16, y, b, k, o)
+            else:
+                for dt, w, y, o in outs:
+                    lin(dt, w, x, y, k, o)
+            n += len(outs)
         be.rms_norm(self.hidden, self.layers[0]["attn_norm"], self.hn, b, h, s.eps)
         n += 1
         for li, L in enumerate(self.layers):
-            lin(Q4K, L["wq"], self.hn, self.q, h, s.q_dim)
-            lin(Q4K, L["wk"], self.hn, self.k, h, s.kv_dim)
-            lin(Q6K, L["wv"], self.hn, self.v, h, s.kv_dim)
-            n += 3
+            lin_many(self.hn, h, [(Q4K, L["wq"], self.q, s.q_dim), (Q4K, L["wk"], self.k, s.kv_dim), (Q6K, L["wv"], self.v, s.kv_dim)])
             if fused:
                 be.rope_write_kv(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], rows=1, pos=pos,
                                  n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
@@ -107,11 +162,10 @@ class DecodeStep:
                 be.add(self.hidden, self.sub, self.hidden, b * h)
                 be.rms_norm(self.hidden, L["ffn_norm"], self.hn, b, h, s.eps)
                 n += 2
-            lin(Q4K, L["gate"], self.hn, self.g, h, ff)
-            lin(Q4K, L["up"], self.hn, self.u, h, ff)
+            lin_many(self.hn, h, [(Q4K, L["gate"], self.g, ff), (Q4K, L["up"], self.u, ff)])
             be.gated_act(self.g, self.u, self.act, b, ff)
             lin(Q6K, L["down"], self.act, self.sub, ff, h)
-            n += 4
+            n += 2
             nxt = self.layers[li + 1]["attn_norm"] if li + 1 < len(self.layers) else self.out_norm
             if fused:
                 be.add_rms_norm(self.hidden, self.sub, self.hidden, nxt, self.hn, b, h, s.eps)

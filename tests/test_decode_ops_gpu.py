@@ -159,3 +159,57 @@ def test_argmax_lowest_index_on_ties(backend, oracle):
     got = backend.download(db, np.uint32)
     np.testing.assert_array_equal(got, oracle.argmax(x, n))
     assert got[1] == 777 and got[2] == 0 and got[3] == n - 1
+
+
+def _q8_bufs(backend, rows, k):
+    return backend.alloc(rows * k), backend.alloc(rows * k // 256 * 4), backend.alloc(rows * k // 32 * 4), backend.alloc(rows * k // 16 * 4)
+
+
+def _q8_equal(backend, got, want):
+    for g, w, dt in zip(got, want, (np.int8, np.uint32, np.int32, np.int32)):  # scales compared as bit patterns
+        np.testing.assert_array_equal(backend.download(g, dt), backend.download(w, dt))
+
+
+def test_producers_ending_in_the_quantiser_emit_the_quantisers_bits(backend, oracle):
+    """add_rms_norm_q8 / gated_act_q8 / attention_q8 == the f32 op followed by quantize_q8, bit for bit; and the
+    codes agree with the CPU quantiser applied to the CPU op's output wherever the f32 values agree."""
+    rows, dim, nff = 3, 4096, 14336
+    a, b = synth.normal(30, (rows, dim)), synth.normal(31, (rows, dim))
+    w = (1.0 + 0.02 * synth.normal(32, (dim,))).astype(np.float32)
+    ab, bb, wb = backend.from_numpy(a), backend.from_numpy(b), backend.from_numpy(w)
+    sum1, sum2, nrm = backend.alloc(a.nbytes), backend.alloc(a.nbytes), backend.alloc(a.nbytes)
+    want, got = _q8_bufs(backend, rows, dim), _q8_bufs(backend, rows, dim)
+    backend.add_rms_norm(ab, bb, sum1, wb, nrm, rows, dim, 1e-5)
+    backend.quantize_q8(256, nrm, rows, dim, *want)
+    backend.add_rms_norm_q8(ab, bb, sum2, wb, rows, dim, 1e-5, *got)
+    _q8_equal(backend, got, want)
+    np.testing.assert_array_equal(backend.download(sum1, np.float32), backend.download(sum2, np.float32))
+    qs_cpu, d_cpu, _, _ = oracle.quantize_q8(oracle.rms_norm(oracle.add(a, b), w, 1e-5))[:4]
+    assert (backend.download(got[0], np.int8) != np.asarray(qs_cpu).ravel()).mean() < 1e-3  # f32 ulps can flip a rounding
+    # without the residual
+    backend.rms_norm(ab, wb, nrm, rows, dim, 1e-5)
+    backend.quantize_q8(256, nrm, rows, dim, *want)
+    backend.add_rms_norm_q8(ab, None, None, wb, rows, dim, 1e-5, *got)
+    _q8_equal(backend, got, want)
+
+    g, u = synth.normal(33, (rows, nff)) * 3.0, synth.normal(34, (rows, nff))
+    gb, ub, act = backend.from_numpy(g), backend.from_numpy(u), backend.alloc(g.nbytes)
+    want, got = _q8_bufs(backend, rows, nff), _q8_bufs(backend, rows, nff)
+    backend.gated_act(gb, ub, act, rows, nff)
+    backend.quantize_q8(256, act, rows, nff, *want)
+    backend.gated_act_q8(gb, ub, rows, nff, *got)
+    _q8_equal(backend, got, want)
+
+    n_seq, n_head, n_kv, hd, pos = 2, 8, 2, 128, 333
+    ctx = pos + 4
+    kc, vc = _f16_cache(35, n_seq * ctx, n_kv * hd), _f16_cache(36, n_seq * ctx, n_kv * hd)
+    q = synth.normal(37, (n_seq, n_head * hd))
+    qb, kb, vb, ob = backend.from_numpy(q), backend.from_numpy(kc), backend.from_numpy(vc), backend.alloc(q.nbytes)
+    kw = dict(rows=1, pos=pos, n_head=n_head, n_kv=n_kv, head_dim=hd, scale=0.088, n_seq=n_seq, seq_stride=ctx * n_kv * hd)
+    want, got = _q8_bufs(backend, n_seq, n_head * hd), _q8_bufs(backend, n_seq, n_head * hd)
+    backend.attention(qb, kb, vb, ob, **kw)
+    backend.quantize_q8(256, ob, n_seq, n_head * hd, *want)
+    backend.attention_q8(qb, kb, vb, *got, **kw)
+    _q8_equal(backend, got, want)
+    with pytest.raises(infr_b200.BackendError):
+        backend.gated_act_q8(gb, ub, rows, 1000, *got)  # not whole 256-element blocks

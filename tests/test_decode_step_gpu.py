@@ -58,8 +58,8 @@ def _oracle_step(o, layers, out_norm, head, kc, vc, hidden):
     return logits, o.argmax(logits, s.vocab)
 
 
-@pytest.mark.parametrize("fused", [False, True])
-def test_decode_step_matches_the_cpu_op_sequence(backend, oracle, fused):
+@pytest.mark.parametrize("fused,q8_fused", [(False, False), (True, False), (True, True)], ids=["op-by-op", "fused", "fused-int8"])
+def test_decode_step_matches_the_cpu_op_sequence(backend, oracle, fused, q8_fused):
     s = SHAPE
     layers, out_norm, head, kc, vc = _model()
     hidden = synth.normal(77, (N_SEQ, s.hidden))
@@ -72,7 +72,7 @@ def test_decode_step_matches_the_cpu_op_sequence(backend, oracle, fused):
     step = DecodeStep(backend, s, N_SEQ, MAX_CTX, dev_layers, backend.from_numpy(out_norm), backend.from_numpy(head, infr_b200.USAGE_WEIGHTS),
                       Q4K, kcb, vcb)
     step.set_inputs(hidden, POS)
-    n_ops = step.run(POS, fused=fused)
+    n_ops = step.run(POS, fused=fused, q8_fused=q8_fused)
     assert n_ops > 0
     got_logits = backend.download(step.logits, np.float32).reshape(N_SEQ, s.vocab)
     got_tok = backend.download(step.tok, np.uint32)
@@ -82,7 +82,7 @@ def test_decode_step_matches_the_cpu_op_sequence(backend, oracle, fused):
     err = fx.rel_l2(got_logits, want_logits)
     assert err < 1e-3, err
     np.testing.assert_array_equal(got_tok, want_tok)
-    print(f"decode step fused={fused}: logits rel-L2 {err:.2e}, max-abs-diff {np.abs(got_logits - want_logits).max():.3e}")
+    print(f"decode step fused={fused} int8-producers={q8_fused}: logits rel-L2 {err:.2e}, max-abs-diff {np.abs(got_logits - want_logits).max():.3e}")
     # the new V rows are plain casts of a Linear output: compare as values (the Linear differs in f32 rounding)
     for li in range(s.n_layer):
         g = backend.download(vcb[li], np.uint16).reshape(vc[li].shape)

@@ -472,48 +472,70 @@ __device__ __forceinline__ void quantize_block256(const float4 v[2], int lane, s
 }
 
 // RMSNorm (optionally of a + b, written to sum_dst) whose output goes straight to int8; dim % 256 == 0.
-template <bool ADD>
+// Warp c owns the 256-element blocks c, c + warps, ...; with one block per warp (dim <= 256 * warps, the launcher's
+// choice up to dim 8192) the row stays in registers between the sum of squares and the scaling.
+// With Q8 false the scaled row is stored as f32 to dst instead: the same arithmetic, so both forms agree bit for bit.
+template <bool ADD, bool Q8>
 __global__ void __launch_bounds__(1024) rms_norm_q8_kernel(const float *a, const float *b, float *sum_dst, const float *__restrict__ w, int dim,
-                                                           float eps, int8_t *__restrict__ qs, float *__restrict__ d, int32_t *__restrict__ sums,
-                                                           int32_t *__restrict__ sums16) {
+                                                           float eps, float *__restrict__ dst, int8_t *__restrict__ qs, float *__restrict__ d,
+                                                           int32_t *__restrict__ sums, int32_t *__restrict__ sums16) {
     __shared__ float s_part[32];
     __shared__ float s_scale;
     pdl_go();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, chunks = dim / 256;
+    const bool in_regs = chunks <= nw;
+    // the norm weights do not depend on the previous kernel: fetch them before waiting for it
+    float4 g[2];
+    if (in_regs && warp < chunks) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) g[h] = *reinterpret_cast<const float4 *>(w + warp * 256 + h * 128 + lane * 4);
+    }
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * dim;
-    const int n4 = dim >> 2;
+    float4 x[2];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-        float4 v = reinterpret_cast<const float4 *>(a + base)[i];
-        if (ADD) {
-            const float4 u = reinterpret_cast<const float4 *>(b + base)[i];
-            v.x += u.x, v.y += u.y, v.z += u.z, v.w += u.w;
-            reinterpret_cast<float4 *>(sum_dst + base)[i] = v;
+    for (int chunk = warp; chunk < chunks; chunk += nw) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int e = chunk * 256 + h * 128 + lane * 4;
+            float4 v = *reinterpret_cast<const float4 *>(a + base + e);
+            if (ADD) {
+                const float4 u = *reinterpret_cast<const float4 *>(b + base + e);
+                v.x += u.x, v.y += u.y, v.z += u.z, v.w += u.w;
+                *reinterpret_cast<float4 *>(sum_dst + base + e) = v;
+            }
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            x[h] = v;
         }
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
-    __syncthreads();  // also orders the CTA's sum_dst stores before the loads below
-    if (threadIdx.x < 32) {
-        float t = threadIdx.x < (blockDim.x + 31) / 32 ? s_part[threadIdx.x] : 0.f;
+    if (lane == 0) s_part[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? s_part[lane] : 0.f;
         t = warp_sum(t);
-        if (threadIdx.x == 0) s_scale = 1.0f / sqrtf(t / (float)dim + eps);
+        if (lane == 0) s_scale = 1.0f / sqrtf(t / (float)dim + eps);
     }
     __syncthreads();
     const float s = s_scale;
-    const float *src = (ADD ? sum_dst : a) + base;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int chunk = warp; chunk < dim / 256; chunk += nw) {
+    const float *src = (ADD ? sum_dst : a) + base;  // re-read by the warp that wrote it
+    for (int chunk = warp; chunk < chunks; chunk += nw) {
         float4 v[2];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int e = chunk * 256 + h * 128 + lane * 4;
-            const float4 x = *reinterpret_cast<const float4 *>(src + e);
-            const float4 g = *reinterpret_cast<const float4 *>(w + e);
-            v[h] = make_float4(x.x * s * g.x, x.y * s * g.y, x.z * s * g.z, x.w * s * g.w);
+            if (!in_regs) {
+                x[h] = *reinterpret_cast<const float4 *>(src + e);
+                g[h] = *reinterpret_cast<const float4 *>(w + e);
+            }
+            v[h] = make_float4(x[h].x * s * g[h].x, x[h].y * s * g[h].y, x[h].z * s * g[h].z, x[h].w * s * g[h].w);
         }
-        quantize_block256(v, lane, blockIdx.x, dim, chunk, qs, d, sums, sums16);
+        if (Q8) {
+            quantize_block256(v, lane, blockIdx.x, dim, chunk, qs, d, sums, sums16);
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; h++) *reinterpret_cast<float4 *>(dst + base + chunk * 256 + h * 128 + lane * 4) = v[h];
+        }
     }
 }
 
@@ -538,37 +560,75 @@ __global__ void __launch_bounds__(256) gated_silu_q8_kernel(const float *__restr
     quantize_block256(v, lane, (size_t)row, nff, chunk, qs, d, sums, sums16);
 }
 
-// The merge of the key tiles with the result quantised in place of an f32 store: warp = (query row, 256 outputs).
-__global__ void __launch_bounds__(256) attn_combine_q8_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int q_rows,
-                                                              int n_head, int head_dim, int n_splits, int8_t *__restrict__ qs,
-                                                              float *__restrict__ d, int32_t *__restrict__ sums, int32_t *__restrict__ sums16) {
+// The merge of the key tiles with the result quantised in place of an f32 store.  CTA = (query row, 256 outputs),
+// 8 warps: warp h < heads-per-block first turns head h's tile maxima into weights exp(m_s - M) in shared memory,
+// then warp w accumulates tiles w, w + 8, ... for the block's 256 outputs (lane = 2 x 4 dims), the eight partial
+// sums meet in shared memory and warp 0 normalises and quantises.
+// With Q8 false the same sums are stored as f32 instead, so the two forms agree bit for bit.
+constexpr int kCombineMaxSplits = 512;
+template <bool Q8>
+__global__ void __launch_bounds__(256) attn_combine_wide_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int n_head,
+                                                                int head_dim, int n_splits, float *__restrict__ dst, int8_t *__restrict__ qs,
+                                                                float *__restrict__ d, int32_t *__restrict__ sums, int32_t *__restrict__ sums16) {
+    __shared__ float s_w[4][kCombineMaxSplits];
+    __shared__ float s_l[4];
+    __shared__ __align__(16) float s_acc[8][256];
     pdl_go();
     pdl_wait();
-    const int lane = threadIdx.x & 31, k = n_head * head_dim, cpr = k / 256;
-    const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    if (wg >= (long long)q_rows * cpr) return;
-    const int row = (int)(wg / cpr), chunk = (int)(wg % cpr);
-    float4 v[2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, k = n_head * head_dim, cpr = k / 256;
+    const int row = blockIdx.x / cpr, chunk = blockIdx.x % cpr;
+    const int heads = 256 / head_dim, head0 = chunk * heads;
+    if (warp < heads) {
+        const float *ml = part_ml + ((size_t)row * n_head + head0 + warp) * n_splits * 2;
+        float m = -INFINITY;
+        for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, ml[2 * s]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int s = lane; s < n_splits; s += 32) {
+            const float ls = ml[2 * s + 1];
+            const float wgt = ls == 0.f ? 0.f : expf(ml[2 * s] - m);
+            s_w[warp][s] = wgt;
+            l += wgt * ls;
+        }
+        l = warp_sum(l);
+        if (lane == 0) s_l[warp] = l;
+    }
+    __syncthreads();
 #pragma unroll
     for (int h = 0; h < 2; h++) {
-        const int e = chunk * 256 + h * 128 + lane * 4, head = e / head_dim, dim0 = e % head_dim;
-        const size_t rh = (size_t)row * n_head + head;
-        const float *ml = part_ml + rh * n_splits * 2;
-        float m = -INFINITY;
-        for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
-        float l = 0.f;
-        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s = 0; s < n_splits; s++) {
-            const float ls = ml[2 * s + 1];
-            if (ls == 0.f) continue;
-            const float wgt = expf(ml[2 * s] - m);
-            l += wgt * ls;
-            const float4 p = *reinterpret_cast<const float4 *>(part_o + (rh * n_splits + s) * head_dim + dim0);
-            o.x = fmaf(wgt, p.x, o.x), o.y = fmaf(wgt, p.y, o.y), o.z = fmaf(wgt, p.z, o.z), o.w = fmaf(wgt, p.w, o.w);
+        const int e = h * 128 + lane * 4, hh = e / head_dim, dim0 = e % head_dim;
+        const float *po = part_o + ((size_t)row * n_head + head0 + hh) * n_splits * head_dim + dim0;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int s = warp; s < n_splits; s += 8) {
+            const float wgt = s_w[hh][s];
+            const float4 p = *reinterpret_cast<const float4 *>(po + (size_t)s * head_dim);
+            acc.x = fmaf(wgt, p.x, acc.x), acc.y = fmaf(wgt, p.y, acc.y), acc.z = fmaf(wgt, p.z, acc.z), acc.w = fmaf(wgt, p.w, acc.w);
         }
-        v[h] = make_float4(o.x / l, o.y / l, o.z / l, o.w / l);
+        *reinterpret_cast<float4 *>(&s_acc[warp][e]) = acc;
     }
-    quantize_block256(v, lane, (size_t)row, k, chunk, qs, d, sums, sums16);
+    __syncthreads();
+    if (warp == 0) {
+        float4 v[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int e = h * 128 + lane * 4;
+            float4 t = *reinterpret_cast<const float4 *>(&s_acc[0][e]);
+#pragma unroll
+            for (int w = 1; w < 8; w++) {
+                const float4 u = *reinterpret_cast<const float4 *>(&s_acc[w][e]);
+                t.x += u.x, t.y += u.y, t.z += u.z, t.w += u.w;
+            }
+            const float l = s_l[e / head_dim];
+            v[h] = make_float4(t.x / l, t.y / l, t.z / l, t.w / l);
+        }
+        if (Q8) {
+            quantize_block256(v, lane, (size_t)row, k, chunk, qs, d, sums, sums16);
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; h++) *reinterpret_cast<float4 *>(dst + (size_t)row * k + chunk * 256 + h * 128 + lane * 4) = v[h];
+        }
+    }
 }
 
 inline unsigned grid_for(size_t n, int block, const DeviceInfo &dev) {
@@ -582,6 +642,15 @@ inline unsigned grid_for(size_t n, int block, const DeviceInfo &dev) {
 cudaError_t launch_rms_norm(const float *a, const float *b, float *sum_dst, const float *w, float *dst, int rows, int dim, float eps,
                             cudaStream_t st) {
     if (rows <= 0 || dim <= 0) return cudaErrorInvalidValue;
+    if (dim % 256 == 0) {  // the block-per-warp kernel, storing f32
+        int t = dim / 256 * 32;
+        t = t > 1024 ? 1024 : t;
+        int8_t *nq = nullptr;
+        float *nd = nullptr;
+        int32_t *ns = nullptr;
+        if (b) return launch_pdl(rms_norm_q8_kernel<true, false>, dim3(rows), dim3(t), 0, st, a, b, sum_dst, w, dim, eps, dst, nq, nd, ns, ns);
+        return launch_pdl(rms_norm_q8_kernel<false, false>, dim3(rows), dim3(t), 0, st, a, (const float *)nullptr, nd, w, dim, eps, dst, nq, nd, ns, ns);
+    }
     int threads = ((dim / 4 + 31) / 32) * 32;
     threads = threads < 32 ? 32 : (threads > 1024 ? 1024 : threads);
     if (b) return launch_pdl(rms_norm_kernel<true>, dim3(rows), dim3(threads), 0, st, a, b, sum_dst, w, dst, dim, eps);
@@ -646,11 +715,14 @@ cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_
         return cudaErrorInvalidValue;
     if (e != cudaSuccess) return e;
     if (qs) {  // the merged rows go straight to int8 (n_head * head_dim must be whole 256-element blocks)
-        if ((n_head * head_dim) % 256) return cudaErrorInvalidValue;
-        const long long warps = (long long)q_rows * (n_head * head_dim / 256);
-        return launch_pdl(attn_combine_q8_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, st, (const float *)po, (const float *)pml,
-                          q_rows, n_head, head_dim, n_splits, qs, d, sums, sums16);
+        if ((n_head * head_dim) % 256 || n_splits > kCombineMaxSplits) return cudaErrorInvalidValue;
+        return launch_pdl(attn_combine_wide_kernel<true>, dim3((unsigned)(q_rows * (n_head * head_dim / 256))), dim3(256), 0, st, (const float *)po,
+                          (const float *)pml, n_head, head_dim, n_splits, (float *)nullptr, qs, d, sums, sums16);
     }
+    if ((n_head * head_dim) % 256 == 0 && n_splits <= kCombineMaxSplits)
+        return launch_pdl(attn_combine_wide_kernel<false>, dim3((unsigned)(q_rows * (n_head * head_dim / 256))), dim3(256), 0, st, (const float *)po,
+                          (const float *)pml, n_head, head_dim, n_splits, dst, (int8_t *)nullptr, (float *)nullptr, (int32_t *)nullptr,
+                          (int32_t *)nullptr);
     return launch_pdl(attn_combine_kernel, dim3(q_rows * n_head), dim3(head_dim), 0, st, (const float *)po, (const float *)pml, dst, head_dim, n_splits);
 }
 
@@ -659,8 +731,9 @@ cudaError_t launch_rms_norm_q8(const float *a, const float *b, float *sum_dst, c
     if (rows <= 0 || dim <= 0 || dim % 256) return cudaErrorInvalidValue;
     int threads = dim / 256 * 32;
     threads = threads > 1024 ? 1024 : threads;
-    if (b) return launch_pdl(rms_norm_q8_kernel<true>, dim3(rows), dim3(threads), 0, st, a, b, sum_dst, w, dim, eps, qs, d, sums, sums16);
-    return launch_pdl(rms_norm_q8_kernel<false>, dim3(rows), dim3(threads), 0, st, a, (const float *)nullptr, (float *)nullptr, w, dim, eps, qs, d, sums,
+    float *none = nullptr;
+    if (b) return launch_pdl(rms_norm_q8_kernel<true, true>, dim3(rows), dim3(threads), 0, st, a, b, sum_dst, w, dim, eps, none, qs, d, sums, sums16);
+    return launch_pdl(rms_norm_q8_kernel<false, true>, dim3(rows), dim3(threads), 0, st, a, (const float *)nullptr, none, w, dim, eps, none, qs, d, sums,
                       sums16);
 }
 

@@ -189,21 +189,43 @@ __global__ void __launch_bounds__(256) write_kv_kernel(const float *__restrict__
 // ---------------------------------------------------------------------------------------------- attention
 constexpr int kAttnTile = 128;  // keys per CTA = threads per CTA
 
-// CTA = (key tile, KV head, query row).  Phase 1: thread t scores key t of the tile against the G query heads
-// that share the KV head (q in shared memory, the key row streamed as 16-byte loads).  Phase 2: one warp per
-// head turns the tile's scores into exp(s - m) and their sum.  Phase 3: warp w multiplies keys 32w..32w+31 of
-// the tile into the head_dim outputs (lane = HD/32 dims), the four warps' partial sums are added through
-// shared memory, and the tile's (m, l, o) goes to the workspace for attn_combine_kernel.
+// CTA = (key tile, KV head, query row).  The tile's 128 key rows and 128 value rows (head_dim halves each) are
+// copied into shared memory with 16-byte cp.async, consecutive threads taking consecutive 16-byte pieces of a row, so
+// every global request is a whole 128-byte line; all copies of the CTA are in flight together and none occupies a
+// register.  Phase 1: thread t scores key t against the G query heads that share the KV head (q in shared memory; the
+// key rows sit 16 bytes apart from a multiple of 128, which spreads the threads' 16-byte reads over all banks).
+// Phase 2: one warp per head turns the tile's scores into exp(s - m) and their sum.  Phase 3: warp w multiplies keys
+// 32w..32w+31 into the outputs (lane = HD/32 dims), the four warps' partial sums are added through shared memory
+// (over the key tile, which is dead by then), and the tile's (m, l, o) goes to the workspace for the merge kernel.
+template <int HD>
+struct AttnSmem {
+    static constexpr int kKeyStride = HD * 2 + 16;  // bytes
+    static constexpr int kValStride = HD * 2;
+    static constexpr int kBytes = kAttnTile * (kKeyStride + kValStride);
+};
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int HD, int G>
 __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__restrict__ q, const __half *__restrict__ k_cache,
                                                                const __half *__restrict__ v_cache, float *__restrict__ part_o,
                                                                float *__restrict__ part_ml, int rows, int n_head, int n_kv, int pos,
                                                                float scale, int n_splits, size_t seq_stride) {
-    constexpr int DPL = HD / 32;  // dims per lane in phase 3
+    constexpr int DPL = HD / 32;       // dims per lane in phase 3
+    constexpr int CPR = HD * 2 / 16;   // 16-byte pieces per row
+    using L = AttnSmem<HD>;
+    extern __shared__ __align__(16) uint8_t dyn_smem[];
+    uint8_t *s_k = dyn_smem, *s_v = dyn_smem + kAttnTile * L::kKeyStride;
+    float(*s_o)[G][HD] = reinterpret_cast<float(*)[G][HD]>(dyn_smem);  // 4 x G x HD floats <= the key tile (G <= 8)
     __shared__ __align__(16) float s_q[G * HD];
     __shared__ float s_p[G][kAttnTile];
     __shared__ float s_ml[G][2];
-    __shared__ __align__(16) float s_o[4][G][HD];
+    static_assert(4 * G * HD * 4 <= kAttnTile * L::kKeyStride, "the partial outputs reuse the key tile");
     const int split = blockIdx.x, kvh = blockIdx.y, qr = blockIdx.z;
     const int seq = qr / rows, ti = qr % rows;
     const int n_keys = pos + ti + 1;
@@ -220,45 +242,34 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
         return;
     }
     const size_t kv_row = (size_t)n_kv * HD;
-    const __half *kbase = k_cache + (size_t)seq * seq_stride + (size_t)kvh * HD;
-    const __half *vbase = v_cache + (size_t)seq * seq_stride + (size_t)kvh * HD;
-    // the value rows of this warp's 32 keys are requested first and used last (phase 3), the key row of this
-    // thread's key next: every global load of the CTA is in flight before the first multiply
-    const int jw = key0 + warp * 32;
-    const int cnt = min(32, n_keys - jw);  // may be <= 0
-    const __half *vr = vbase + (size_t)jw * kv_row + lane * DPL;
-    uint32_t raw[32][DPL / 2];
-#pragma unroll
-    for (int jj = 0; jj < 32; jj++) {
-        if (jj < cnt) {
-            if (DPL == 4) {
-                const uint2 t = __ldg(reinterpret_cast<const uint2 *>(vr + (size_t)jj * kv_row));
-                raw[jj][0] = t.x, raw[jj][DPL / 2 - 1] = t.y;
-            } else {
-                raw[jj][0] = __ldg(reinterpret_cast<const uint32_t *>(vr + (size_t)jj * kv_row));
-            }
-        } else {
-#pragma unroll
-            for (int e = 0; e < DPL / 2; e++) raw[jj][e] = 0u;
-        }
+    const __half *kbase = k_cache + (size_t)seq * seq_stride + (size_t)kvh * HD + (size_t)key0 * kv_row;
+    const __half *vbase = v_cache + (size_t)seq * seq_stride + (size_t)kvh * HD + (size_t)key0 * kv_row;
+    const int tile_keys = min(kAttnTile, n_keys - key0);
+    for (int i = tid; i < tile_keys * CPR; i += kAttnTile) {
+        const int key = i / CPR, c = i % CPR;
+        cp_async16(s_k + key * L::kKeyStride + c * 16, kbase + (size_t)key * kv_row + c * 8);
     }
+    cp_async_commit();
+    for (int i = tid; i < tile_keys * CPR; i += kAttnTile) {
+        const int key = i / CPR, c = i % CPR;
+        cp_async16(s_v + key * L::kValStride + c * 16, vbase + (size_t)key * kv_row + c * 8);
+    }
+    cp_async_commit();
     const float *qrow = q + ((size_t)qr * n_head + (size_t)kvh * G) * HD;
     for (int i = tid; i < G * HD; i += kAttnTile) s_q[i] = qrow[i];
-    __syncthreads();
+    cp_async_wait<1>();  // this thread's key pieces have landed
+    __syncthreads();     // everybody's have, and q is staged
     // ---- phase 1
     {
-        const int j = key0 + tid;
         float acc[G];
 #pragma unroll
         for (int g = 0; g < G; g++) acc[g] = 0.f;
-        if (j < n_keys) {
-            const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)j * kv_row);
-            uint4 kraw[HD / 8];
-#pragma unroll
-            for (int c = 0; c < HD / 8; c++) kraw[c] = __ldg(kr + c);
-#pragma unroll
-            for (int c = 0; c < HD / 8; c++) {
-                const __half2 *h2 = reinterpret_cast<const __half2 *>(&kraw[c]);
+        if (tid < tile_keys) {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(s_k + tid * L::kKeyStride);
+#pragma unroll 4
+            for (int c = 0; c < CPR; c++) {
+                const uint4 raw = kr[c];
+                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
                 float kf[8];
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
@@ -281,9 +292,10 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
             }
         }
 #pragma unroll
-        for (int g = 0; g < G; g++) s_p[g][tid] = j < n_keys ? acc[g] * scale : -INFINITY;
+        for (int g = 0; g < G; g++) s_p[g][tid] = tid < tile_keys ? acc[g] * scale : -INFINITY;
     }
-    __syncthreads();
+    cp_async_wait<0>();  // this thread's value pieces
+    __syncthreads();     // scores complete, value tile complete, key tile no longer read
     // ---- phase 2
     for (int g = warp; g < G; g += 4) {
         float v[4], m = -INFINITY;
@@ -308,17 +320,24 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
         for (int g = 0; g < G; g++)
 #pragma unroll
             for (int e = 0; e < DPL; e++) o[g][e] = 0.f;
-#pragma unroll
-        for (int jj = 0; jj < 32; jj++) {
+        const int cnt = min(32, tile_keys - warp * 32);  // may be <= 0
+        const uint8_t *vr = s_v + (size_t)(warp * 32) * L::kValStride + lane * DPL * 2;
+#pragma unroll 4
+        for (int jj = 0; jj < cnt; jj++) {
             float vf[DPL];
-#pragma unroll
-            for (int e = 0; e < DPL / 2; e++) {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&raw[jj][e]));
-                vf[2 * e] = f.x, vf[2 * e + 1] = f.y;
+            if (DPL == 4) {
+                const uint2 raw = *reinterpret_cast<const uint2 *>(vr + jj * L::kValStride);
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+                vf[0] = f0.x, vf[1] = f0.y, vf[DPL - 2] = f1.x, vf[DPL - 1] = f1.y;
+            } else {
+                const uint32_t raw = *reinterpret_cast<const uint32_t *>(vr + jj * L::kValStride);
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw));
+                vf[0] = f0.x, vf[1] = f0.y;
             }
 #pragma unroll
             for (int g = 0; g < G; g++) {
-                const float p = jj < cnt ? s_p[g][warp * 32 + jj] : 0.f;
+                const float p = s_p[g][warp * 32 + jj];
 #pragma unroll
                 for (int e = 0; e < DPL; e++) o[g][e] = fmaf(vf[e], p, o[g][e]);
             }
@@ -684,21 +703,34 @@ size_t attention_workspace_bytes(int q_rows, int n_head, int head_dim, int max_k
     return (size_t)q_rows * n_head * n_splits * ((size_t)head_dim + 2) * sizeof(float);
 }
 
+template <int HD, int G>
+static cudaError_t launch_attn_one(dim3 grid, cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *po, float *pml, int rows,
+                                   int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride) {
+    static bool configured = false;  // per instantiation: the tile needs more than the default 48 KB of dynamic shared memory
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<HD>::kBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    return launch_pdl(attn_split_kernel<HD, G>, grid, dim3(kAttnTile), (size_t)AttnSmem<HD>::kBytes, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos,
+                      scale, n_splits, seq_stride);
+}
+
 template <int HD>
 static cudaError_t launch_attn_hd(int group, dim3 grid, cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *po, float *pml,
                                   int rows, int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride) {
     switch (group) {
-        case 1: return launch_pdl(attn_split_kernel<HD, 1>, grid, dim3(kAttnTile), 0, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
-        case 2: return launch_pdl(attn_split_kernel<HD, 2>, grid, dim3(kAttnTile), 0, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
-        case 4: return launch_pdl(attn_split_kernel<HD, 4>, grid, dim3(kAttnTile), 0, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
-        case 8: return launch_pdl(attn_split_kernel<HD, 8>, grid, dim3(kAttnTile), 0, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        case 1: return launch_attn_one<HD, 1>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        case 2: return launch_attn_one<HD, 2>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        case 4: return launch_attn_one<HD, 4>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        case 8: return launch_attn_one<HD, 8>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
         default: return cudaErrorInvalidValue;
     }
 }
 
 cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_cache, float *dst, void *workspace, int n_seq, int rows, int n_head,
-                             int n_kv, int head_dim, float scale, int pos, size_t seq_stride, cudaStream_t st, int8_t *qs, float *d, int32_t *sums,
-                             int32_t *sums16) {
+                             int n_kv, int head_dim, float scale, int pos, size_t seq_stride, int sm_count, cudaStream_t st, int8_t *qs, float *d,
+                             int32_t *sums, int32_t *sums16) {
     if (n_seq <= 0 || rows <= 0 || n_head <= 0 || n_kv <= 0 || n_head % n_kv || pos < 0) return cudaErrorInvalidValue;
     const int max_keys = pos + rows, n_splits = (max_keys + kAttnTile - 1) / kAttnTile, q_rows = n_seq * rows;
     if (n_kv > 65535 || q_rows > 65535) return cudaErrorInvalidValue;
@@ -707,10 +739,12 @@ cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_
     const dim3 grid(n_splits, n_kv, q_rows);
     const __half *kc = static_cast<const __half *>(k_cache), *vc = static_cast<const __half *>(v_cache);
     cudaError_t e;
+    (void)sm_count;
+    const int g = n_head / n_kv;
     if (head_dim == 128)
-        e = launch_attn_hd<128>(n_head / n_kv, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        e = launch_attn_hd<128>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
     else if (head_dim == 64)
-        e = launch_attn_hd<64>(n_head / n_kv, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        e = launch_attn_hd<64>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
     else
         return cudaErrorInvalidValue;
     if (e != cudaSuccess) return e;

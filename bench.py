@@ -16,6 +16,9 @@ the 126 MB L2, so a STEP is one pass over ROT = 64 device copies of the matrix a
             pinned memory, execute a one-Linear plan, download y to pinned memory
   sweep     (N=1) the other GEMV configurations: Q6_K 14336x4096 and ternary Q2_0 4096x14336 at
             batch 1/4/8, Q4_K 14336x4096; each rotated over > 4x L2 of distinct copies
+  decode_step   (N=1) a whole 8B-shape decode step (32 layers: norms, Linears, RoPE + KV write, causal
+            attention over a 4096-token f16 KV cache, SiLU gate, residual adds; head; argmax) at batch 1 and 32,
+            one CUDA graph, tok/s = batch / step time
   cpu_baseline  the CPU restatement of infr-cpu on the host cores, bounded sample (N=1, rank 0)
 
 --impl reference times the CPU restatement of infr-cpu (the reference is Rust; no Rust toolchain

@@ -187,15 +187,17 @@ __global__ void __launch_bounds__(256) write_kv_kernel(const float *__restrict__
 }
 
 // ---------------------------------------------------------------------------------------------- attention
-constexpr int kAttnTile = 128;  // keys per CTA = threads per CTA
+constexpr int kAttnTile = 128;     // keys per CTA
+constexpr int kAttnThreads = 256;  // two threads per key in the score phase, eight warps over the values
 
 // CTA = (key tile, KV head, query row).  The tile's 128 key rows and 128 value rows (head_dim halves each) are
 // copied into shared memory with 16-byte cp.async, consecutive threads taking consecutive 16-byte pieces of a row, so
 // every global request is a whole 128-byte line; all copies of the CTA are in flight together and none occupies a
-// register.  Phase 1: thread t scores key t against the G query heads that share the KV head (q in shared memory; the
-// key rows sit 16 bytes apart from a multiple of 128, which spreads the threads' 16-byte reads over all banks).
+// register.  Phase 1: two threads per key, each over half of the dims, score the key against the G query heads that
+// share the KV head (q in shared memory; the key rows sit 16 bytes apart from a multiple of 128, which spreads the
+// threads' 16-byte reads over all banks).
 // Phase 2: one warp per head turns the tile's scores into exp(s - m) and their sum.  Phase 3: warp w multiplies keys
-// 32w..32w+31 into the outputs (lane = HD/32 dims), the four warps' partial sums are added through shared memory
+// 16w..16w+15 into the outputs (lane = HD/32 dims), the eight warps' partial sums are added through shared memory
 // (over the key tile, which is dead by then), and the tile's (m, l, o) goes to the workspace for the merge kernel.
 template <int HD>
 struct AttnSmem {
@@ -212,7 +214,7 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <int HD, int G>
-__global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__restrict__ q, const __half *__restrict__ k_cache,
+__global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *__restrict__ q, const __half *__restrict__ k_cache,
                                                                const __half *__restrict__ v_cache, float *__restrict__ part_o,
                                                                float *__restrict__ part_ml, int rows, int n_head, int n_kv, int pos,
                                                                float scale, int n_splits, size_t seq_stride) {
@@ -221,11 +223,12 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
     using L = AttnSmem<HD>;
     extern __shared__ __align__(16) uint8_t dyn_smem[];
     uint8_t *s_k = dyn_smem, *s_v = dyn_smem + kAttnTile * L::kKeyStride;
-    float(*s_o)[G][HD] = reinterpret_cast<float(*)[G][HD]>(dyn_smem);  // 4 x G x HD floats <= the key tile (G <= 8)
+    float(*s_o)[G][HD] = reinterpret_cast<float(*)[G][HD]>(dyn_smem);  // 8 x G x HD floats <= the key tile (G <= 8)
     __shared__ __align__(16) float s_q[G * HD];
     __shared__ float s_p[G][kAttnTile];
+    __shared__ float s_p2[G][kAttnTile];  // the second half of the dims of each dot product
     __shared__ float s_ml[G][2];
-    static_assert(4 * G * HD * 4 <= kAttnTile * L::kKeyStride, "the partial outputs reuse the key tile");
+    static_assert(8 * G * HD * 4 <= kAttnTile * L::kKeyStride, "the partial outputs reuse the key tile");
     const int split = blockIdx.x, kvh = blockIdx.y, qr = blockIdx.z;
     const int seq = qr / rows, ti = qr % rows;
     const int n_keys = pos + ti + 1;
@@ -245,29 +248,31 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
     const __half *kbase = k_cache + (size_t)seq * seq_stride + (size_t)kvh * HD + (size_t)key0 * kv_row;
     const __half *vbase = v_cache + (size_t)seq * seq_stride + (size_t)kvh * HD + (size_t)key0 * kv_row;
     const int tile_keys = min(kAttnTile, n_keys - key0);
-    for (int i = tid; i < tile_keys * CPR; i += kAttnTile) {
+    for (int i = tid; i < tile_keys * CPR; i += kAttnThreads) {
         const int key = i / CPR, c = i % CPR;
         cp_async16(s_k + key * L::kKeyStride + c * 16, kbase + (size_t)key * kv_row + c * 8);
     }
     cp_async_commit();
-    for (int i = tid; i < tile_keys * CPR; i += kAttnTile) {
+    for (int i = tid; i < tile_keys * CPR; i += kAttnThreads) {
         const int key = i / CPR, c = i % CPR;
         cp_async16(s_v + key * L::kValStride + c * 16, vbase + (size_t)key * kv_row + c * 8);
     }
     cp_async_commit();
     const float *qrow = q + ((size_t)qr * n_head + (size_t)kvh * G) * HD;
-    for (int i = tid; i < G * HD; i += kAttnTile) s_q[i] = qrow[i];
+    for (int i = tid; i < G * HD; i += kAttnThreads) s_q[i] = qrow[i];
     cp_async_wait<1>();  // this thread's key pieces have landed
     __syncthreads();     // everybody's have, and q is staged
-    // ---- phase 1
+    // ---- phase 1: two threads per key, each over half of the dims, two accumulators per head
     {
-        float acc[G];
+        const int key = tid & (kAttnTile - 1), half = tid >> 7;
+        float acc[G][2];
 #pragma unroll
-        for (int g = 0; g < G; g++) acc[g] = 0.f;
-        if (tid < tile_keys) {
-            const uint4 *kr = reinterpret_cast<const uint4 *>(s_k + tid * L::kKeyStride);
+        for (int g = 0; g < G; g++) acc[g][0] = acc[g][1] = 0.f;
+        if (key < tile_keys) {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(s_k + key * L::kKeyStride) + half * (CPR / 2);
+            const float *qh = s_q + half * (HD / 2);
 #pragma unroll 4
-            for (int c = 0; c < CPR; c++) {
+            for (int c = 0; c < CPR / 2; c++) {
                 const uint4 raw = kr[c];
                 const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
                 float kf[8];
@@ -278,29 +283,33 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
                 }
 #pragma unroll
                 for (int g = 0; g < G; g++) {
-                    const float4 q0 = *reinterpret_cast<const float4 *>(s_q + g * HD + c * 8);
-                    const float4 q1 = *reinterpret_cast<const float4 *>(s_q + g * HD + c * 8 + 4);
-                    acc[g] = fmaf(q0.x, kf[0], acc[g]);
-                    acc[g] = fmaf(q0.y, kf[1], acc[g]);
-                    acc[g] = fmaf(q0.z, kf[2], acc[g]);
-                    acc[g] = fmaf(q0.w, kf[3], acc[g]);
-                    acc[g] = fmaf(q1.x, kf[4], acc[g]);
-                    acc[g] = fmaf(q1.y, kf[5], acc[g]);
-                    acc[g] = fmaf(q1.z, kf[6], acc[g]);
-                    acc[g] = fmaf(q1.w, kf[7], acc[g]);
+                    const float4 q0 = *reinterpret_cast<const float4 *>(qh + g * HD + c * 8);
+                    const float4 q1 = *reinterpret_cast<const float4 *>(qh + g * HD + c * 8 + 4);
+                    acc[g][0] = fmaf(q0.x, kf[0], acc[g][0]);
+                    acc[g][0] = fmaf(q0.y, kf[1], acc[g][0]);
+                    acc[g][0] = fmaf(q0.z, kf[2], acc[g][0]);
+                    acc[g][0] = fmaf(q0.w, kf[3], acc[g][0]);
+                    acc[g][1] = fmaf(q1.x, kf[4], acc[g][1]);
+                    acc[g][1] = fmaf(q1.y, kf[5], acc[g][1]);
+                    acc[g][1] = fmaf(q1.z, kf[6], acc[g][1]);
+                    acc[g][1] = fmaf(q1.w, kf[7], acc[g][1]);
                 }
             }
         }
 #pragma unroll
-        for (int g = 0; g < G; g++) s_p[g][tid] = tid < tile_keys ? acc[g] * scale : -INFINITY;
+        for (int g = 0; g < G; g++) (half ? s_p2 : s_p)[g][key] = acc[g][0] + acc[g][1];
     }
     cp_async_wait<0>();  // this thread's value pieces
     __syncthreads();     // scores complete, value tile complete, key tile no longer read
     // ---- phase 2
-    for (int g = warp; g < G; g += 4) {
+    for (int g = warp; g < G; g += kAttnThreads / 32) {
         float v[4], m = -INFINITY;
 #pragma unroll
-        for (int e = 0; e < 4; e++) v[e] = s_p[g][lane + 32 * e], m = fmaxf(m, v[e]);
+        for (int e = 0; e < 4; e++) {
+            const int key = lane + 32 * e;
+            v[e] = key < tile_keys ? (s_p[g][key] + s_p2[g][key]) * scale : -INFINITY;
+            m = fmaxf(m, v[e]);
+        }
         m = warp_max(m);  // finite: the tile holds at least one valid key
         float l = 0.f;
 #pragma unroll
@@ -320,8 +329,9 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
         for (int g = 0; g < G; g++)
 #pragma unroll
             for (int e = 0; e < DPL; e++) o[g][e] = 0.f;
-        const int cnt = min(32, tile_keys - warp * 32);  // may be <= 0
-        const uint8_t *vr = s_v + (size_t)(warp * 32) * L::kValStride + lane * DPL * 2;
+        constexpr int KPW = kAttnTile / (kAttnThreads / 32);  // keys per warp
+        const int cnt = min(KPW, tile_keys - warp * KPW);  // may be <= 0
+        const uint8_t *vr = s_v + (size_t)(warp * KPW) * L::kValStride + lane * DPL * 2;
 #pragma unroll 4
         for (int jj = 0; jj < cnt; jj++) {
             float vf[DPL];
@@ -337,7 +347,7 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
             }
 #pragma unroll
             for (int g = 0; g < G; g++) {
-                const float p = s_p[g][warp * 32 + jj];
+                const float p = s_p[g][warp * KPW + jj];
 #pragma unroll
                 for (int e = 0; e < DPL; e++) o[g][e] = fmaf(vf[e], p, o[g][e]);
             }
@@ -348,9 +358,12 @@ __global__ void __launch_bounds__(kAttnTile) attn_split_kernel(const float *__re
             for (int e = 0; e < DPL; e++) s_o[warp][g][lane * DPL + e] = o[g][e];
     }
     __syncthreads();
-    for (int i = tid; i < G * HD; i += kAttnTile) {
+    for (int i = tid; i < G * HD; i += kAttnThreads) {
         const int g = i / HD, d = i % HD;
-        part_o[(out_idx + (size_t)g * n_splits) * HD + d] = s_o[0][g][d] + s_o[1][g][d] + s_o[2][g][d] + s_o[3][g][d];
+        float t = s_o[0][g][d];
+#pragma unroll
+        for (int w = 1; w < kAttnThreads / 32; w++) t += s_o[w][g][d];
+        part_o[(out_idx + (size_t)g * n_splits) * HD + d] = t;
     }
     if (tid < G) {
         part_ml[(out_idx + (size_t)tid * n_splits) * 2] = s_ml[tid][0];
@@ -712,7 +725,7 @@ static cudaError_t launch_attn_one(dim3 grid, cudaStream_t st, const float *q, c
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    return launch_pdl(attn_split_kernel<HD, G>, grid, dim3(kAttnTile), (size_t)AttnSmem<HD>::kBytes, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos,
+    return launch_pdl(attn_split_kernel<HD, G>, grid, dim3(kAttnThreads), (size_t)AttnSmem<HD>::kBytes, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos,
                       scale, n_splits, seq_stride);
 }
 

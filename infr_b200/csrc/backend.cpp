@@ -282,7 +282,16 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
     if (m == 0 || out_f == 0) return Status::Ok();
     cudaSetDevice(device_);
     // Prefill shapes: Q4_K with int8 activations goes to the tcgen05 MMQ GEMM (all rows quantised once).
-    if (m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0) {
+    bool use_mmq = m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0;
+    if (use_mmq && mmq_impl_ == 0 && m <= 32) {
+        // A batch of a few dozen rows is still bandwidth work, and the GEMM's serial walk over K (about 1 us per
+        // 256-column block and tile, whatever the number of rows) plus its activation re-layout cost ~31 us on
+        // 4096 columns: below that, 8 rows at a time through the GEMV (measured ~2.5 us + 0.34 us per MB of weights
+        // per launch) is faster.  The large matrices of a decode step (gate / up) stay on the GEMM.
+        const double mb = (double)out_f * in_f * 0.5625e-6, gemm_us = 7.0 + 1.5 * (in_f / 256);
+        if (((m + 7) / 8) * (2.5 + 0.34 * mb) < gemm_us) use_mmq = false;
+    }
+    if (use_mmq) {
         Q8Dev a;
         uint8_t *rec = nullptr;
         const size_t rec_bytes = mmq_impl_ == 1 ? mmq_q4k_record_bytes((int)m, (int)in_f) : mmq_ws_record_bytes((int)m, (int)in_f);
@@ -294,7 +303,13 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
         if (s.ok()) launches_ += 2;
         return s;
     }
-    // Decode shapes (m <= 8) run the streaming GEMV; wider batches are walked 8 rows at a time.
+    // Decode shapes (m <= 8) run the streaming GEMV; wider batches are walked 8 rows at a time, all rows quantised once.
+    Q8Dev a_all{};
+    const bool pre_quantised = act == INFR_ACT_INT8 && !(dtype == DT_Q4K && gemv_impl_ == 0);
+    if (pre_quantised) {
+        Status s = quantize_for(dtype, x, m, in_f, &a_all);
+        if (!s.ok()) return s;
+    }
     for (uint32_t r0 = 0; r0 < m; r0 += 8) {
         const uint32_t mm = m - r0 < 8 ? m - r0 : 8;
         const float *xr = x + (size_t)r0 * in_f;
@@ -322,11 +337,15 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
                 t0 += n;
             }
         } else {
-            Q8Dev a;
-            Status s = quantize_for(dtype, xr, mm, in_f, &a);
-            if (!s.ok()) return s;
-            // rows so long that `mm` staged activation rows exceed shared memory are run in narrower batches
+            // this chunk's rows of the quantised batch
+            Q8Dev a = a_all;
+            Status s;
             const int gran = a.gran, ngr = (int)in_f / gran;
+            a.qs = a_all.qs + (size_t)r0 * in_f;
+            a.d = a_all.d + (size_t)r0 * ngr;
+            a.sums = a_all.sums + (size_t)r0 * (in_f / 32);
+            if (a_all.sums16) a.sums16 = a_all.sums16 + (size_t)r0 * (in_f / 16);
+            // rows so long that `mm` staged activation rows exceed shared memory are run in narrower batches
             uint32_t step = mm;
             for (uint32_t t0 = 0; t0 < mm;) {
                 const uint32_t n = mm - t0 < step ? mm - t0 : step;

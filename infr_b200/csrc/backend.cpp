@@ -305,7 +305,8 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
     }
     // Decode shapes (m <= 8) run the streaming GEMV; wider batches are walked 8 rows at a time, all rows quantised once.
     Q8Dev a_all{};
-    const bool pre_quantised = act == INFR_ACT_INT8 && !(dtype == DT_Q4K && gemv_impl_ == 0);
+    // (a single Q4_K chunk quantises its rows inside the GEMV; with several chunks that would repeat the work in every CTA)
+    const bool pre_quantised = act == INFR_ACT_INT8 && (!(dtype == DT_Q4K && gemv_impl_ == 0) || m > 8);
     if (pre_quantised) {
         Status s = quantize_for(dtype, x, m, in_f, &a_all);
         if (!s.ok()) return s;
@@ -318,8 +319,8 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
             Status s = cuda_status(launch_gemv_f32(dtype, w, xr, yr, (int)mm, (int)in_f, (int)out_f, dev_, stream_), "gemv_f32");
             if (!s.ok()) return s;
             launches_ += 1;
-        } else if (dtype == DT_Q4K && gemv_impl_ == 0) {
-            // one kernel: activation rows are quantised inside the GEMV while the first weights stream in.
+        } else if (!pre_quantised) {
+            // Q4_K, one kernel: activation rows are quantised inside the GEMV while the first weights stream in.
             // Rows so long that `mm` staged activation rows exceed shared memory are run in narrower batches.
             uint32_t step = mm;
             for (uint32_t t0 = 0; t0 < mm;) {
@@ -355,8 +356,9 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
                 sub.sums = a.sums + (size_t)t0 * (in_f / 32);
                 if (a.sums16) sub.sums16 = a.sums16 + (size_t)t0 * (in_f / 16);
                 float *yt = yr + (size_t)t0 * out_f;
-                cudaError_t e = gemv_impl_ == 1 ? launch_gemv_q8(dtype, w, sub, yt, (int)n, (int)in_f, (int)out_f, nullptr, dev_, stream_)
-                                                : launch_gemv_stream(dtype, w, sub, yt, (int)n, (int)in_f, (int)out_f, dev_, status_dev_, stream_);
+                cudaError_t e = gemv_impl_ == 1   ? launch_gemv_q8(dtype, w, sub, yt, (int)n, (int)in_f, (int)out_f, nullptr, dev_, stream_)
+                                : dtype == DT_Q4K ? launch_gemv_q4k_mma(w, &sub, nullptr, yt, (int)n, (int)in_f, (int)out_f, dev_, status_dev_, stream_)
+                                                  : launch_gemv_stream(dtype, w, sub, yt, (int)n, (int)in_f, (int)out_f, dev_, status_dev_, stream_);
                 if (e == cudaErrorInvalidValue && step > 1) {
                     cudaGetLastError();
                     step /= 2;

@@ -310,7 +310,7 @@ def _decode_linears_case(be, infr_b200, batch, steps, warmup):
     res = {"workload": f"Linear ops of an 8B-shape decode step, batch {batch}: {n_linear} Linears, Q4_K_M mix "
                        f"(v/down/head Q6_K), {total_bytes / 1e9:.2f} GB of weights, one CUDA graph",
            "us_per_step": us, "tok_per_s_matmul_only": batch / (us * 1e-6), "weights_gbs": total_bytes / (us * 1e-6) / 1e9,
-           "kernels_per_step": kernels, "not_included": "attention, norms, RoPE, sampling (not built)"}
+           "kernels_per_step": kernels, "not_included": "attention, norms, RoPE, sampling: see decode_step"}
     graph.close()
     for b in [head, xh, xf, yh, ykv, yff, ylog] + list(masters.values()) + [b for L in layers for b in L.values()]:
         b.close()
@@ -525,7 +525,7 @@ def _tp_decode(be, infr_b200, dist, rank, world, local, steps, warmup):
                         f"(peer-memory kernel of this library) + 1 NCCL all-gather",
             "us_per_step": us, "tok_per_s_matmul_only": 1e6 / us, "mode": mode, "scaling": "strong",
             "us_per_step_with_nccl_all_reduce": us_nccl, "us_per_step_without_all_reduce": us_none, "all_reduce_16KB_us": ar_us if N > 1 else None,
-            "not_included": "attention, norms, RoPE, sampling (not built)"}
+            "not_included": "attention, norms, RoPE, sampling: see decode_step"}
 
 
 def _ep_moe(be, infr_b200, dist, rank, world, local, steps, warmup):

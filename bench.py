@@ -528,6 +528,125 @@ def _tp_decode(be, infr_b200, dist, rank, world, local, steps, warmup):
             "not_included": "attention, norms, RoPE, sampling: see decode_step"}
 
 
+def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmup, pos=4096):
+    """Tensor-parallel form of the WHOLE 8B-shape decode step (section of the reference: tp.rs:7-21): q/k/v by heads,
+    attention by KV head on the rank's own slice of the KV cache, gate/up by FFN slice, o and down by input columns
+    with an all-reduce of the [batch, 4096] result after each (the library's peer-memory kernel while it fits its
+    64 K-float limit, NCCL otherwise), norms and the residual stream replicated, the head by vocabulary slice with one
+    NCCL all-gather of the logits.  One CUDA graph on the backend's stream.  Strong scaling: one model on N GPUs."""
+    import numpy as np
+    import torch
+    from infr_b200 import synth
+    from infr_b200.decode import DecodeStep, LlamaShape
+
+    Q4K = infr_b200.Q4K
+    dev = torch.device("cuda", local)
+    N = world
+    full = LlamaShape()
+    s = LlamaShape(n_head=full.n_head // N, n_kv=full.n_kv // N, ffn=full.ffn // N, vocab=full.vocab // N)
+    max_ctx = pos + 8
+    masters = {name: be.from_numpy(synth.random_blocks(dt, o * i, 300 + k + 16 * rank), infr_b200.USAGE_WEIGHTS)
+               for k, (name, dt, o, i) in enumerate(s.linears())}
+    norm = be.from_numpy((1.0 + 0.02 * synth.normal(40, (s.hidden,))).astype(np.float32))
+    layers, owned, w_bytes = [], [], 0
+    for _ in range(s.n_layer):
+        L = {"attn_norm": norm, "ffn_norm": norm}
+        for name, dt, o, i in s.linears():
+            nbytes = o * i // synth.BLOCK_ELEMS[dt] * synth.BLOCK_BYTES[dt]
+            b_ = be.alloc_uninit(nbytes, infr_b200.USAGE_WEIGHTS)
+            be.copy_buffer(masters[name], b_, nbytes)
+            L[name] = b_
+            owned.append(b_)
+            w_bytes += nbytes
+        layers.append(L)
+    head = be.from_numpy(synth.random_blocks(Q4K, s.vocab * s.hidden, 399 + rank), infr_b200.USAGE_WEIGHTS)
+    w_bytes += s.vocab * s.hidden // 256 * 144
+    seq_bytes = max_ctx * s.kv_dim * 2
+    kv_master = be.from_numpy(synth.normal(9 + rank, (max_ctx, s.kv_dim)).astype(np.float16).view(np.uint16))
+    kc, vc = [], []
+    for _ in range(s.n_layer):
+        for lst in (kc, vc):
+            c = be.alloc_uninit(batch * seq_bytes, infr_b200.USAGE_ACTIVATIONS)
+            for q in range(batch):
+                view = be.wrap(c.device_ptr() + q * seq_bytes, seq_bytes, infr_b200.USAGE_ACTIVATIONS)
+                be.copy_buffer(kv_master, view, seq_bytes)
+                view.close()
+            lst.append(c)
+    f32 = dict(device=dev, dtype=torch.float32)
+    sub_t = torch.zeros(batch * s.hidden, **f32)
+    gathered = torch.empty(batch * s.vocab * N, **f32)
+    torch.cuda.synchronize(dev)
+    sub = be.wrap(sub_t.data_ptr(), sub_t.numel() * 4, infr_b200.USAGE_ACTIVATIONS)
+    n_red = batch * s.hidden
+    comm = None
+    if N > 1 and n_red <= 65536:
+        comm = be.comm_create(rank, N, n_red)
+        handles = [None] * N
+        dist.all_gather_object(handles, comm.export())
+        comm.connect(handles)
+    if N == 1:
+        reduce = None
+    elif comm is not None:
+        reduce = lambda buf, n: be.all_reduce(comm, buf, n)
+    else:
+        reduce = lambda buf, n: dist.all_reduce(sub_t)
+    step = DecodeStep(be, s, batch, max_ctx, layers, norm, head, Q4K, kc, vc, sub=sub, reduce=reduce, argmax=N == 1)
+    hidden0 = be.from_numpy(synth.normal(31, (batch, s.hidden)))
+    step.set_inputs(synth.normal(31, (batch, s.hidden)), pos)
+    logits_t = None
+    if N > 1:  # the rank's logits slice as a torch tensor for the all-gather: copy through a wrapped view
+        logits_t = torch.empty(batch * s.vocab, **f32)
+        torch.cuda.synchronize(dev)
+        logits_w = be.wrap(logits_t.data_ptr(), logits_t.numel() * 4, infr_b200.USAGE_ACTIVATIONS)
+
+    def one():
+        be.copy_buffer(hidden0, step.hidden, batch * s.hidden * 4)
+        n = step.run(pos, fused=True)
+        if N > 1:
+            be.copy_buffer(step.logits, logits_w, batch * s.vocab * 4)
+            dist.all_gather_into_tensor(gathered, logits_t)
+        return n
+
+    ext = torch.cuda.ExternalStream(be.stream(), device=dev)
+    mode = "cuda graph"
+    with torch.cuda.stream(ext):
+        for _ in range(2):
+            n_ops = one()  # sizes the context's scratch before capture
+        ext.synchronize()
+        graph = None
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=ext):
+                one()
+        except Exception as e:
+            graph, mode = None, f"eager ({type(e).__name__}: {str(e)[:80]})"
+        run = graph.replay if graph is not None else one
+        for _ in range(warmup):
+            run()
+        ext.synchronize()
+        _barrier(dist)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ext)
+        for _ in range(steps):
+            run()
+        e1.record(ext)
+        e1.synchronize()
+        ms = e0.elapsed_time(e1)
+        del graph
+    us = _max_over_ranks(dist, ms) * 1e3 / steps
+    be.sync()
+    finite = bool(torch.isfinite(gathered).all().item()) if N > 1 else True
+    if comm is not None:
+        comm.close()
+    for b_ in owned + kc + vc + [head, kv_master, hidden0, norm, sub] + list(masters.values()):
+        b_.close()
+    return {"workload": f"tensor-parallel 8B-shape decode step, batch {batch}, KV context {pos}, {N} GPU(s): heads, FFN and vocabulary "
+                        f"split over the ranks ({w_bytes / 1e9:.2f} GB of weights per rank), {2 * s.n_layer if N > 1 else 0} all-reduces of "
+                        f"{n_red * 4 // 1024} KB ({'peer-memory kernel' if comm is not None else 'NCCL' if N > 1 else 'none'}) + 1 NCCL all-gather",
+            "us_per_step": us, "tok_per_s": batch / (us * 1e-6), "ops_per_step": n_ops, "mode": mode, "scaling": "strong",
+            "logits_finite": finite}
+
+
 def _ep_moe(be, infr_b200, dist, rank, world, local, steps, warmup):
     """Expert-parallel form of the C4 MoE layer: every rank holds 128 / N experts and all 256 tokens, routes all
     tokens (the router is replicated), runs its experts' grouped GEMMs and adds its share of the output; the
@@ -711,16 +830,27 @@ def run_b200(args):
     if not args.no_sweep:
         tp = _tp_decode(be, infr_b200, dist, rank, world, local, 10, 3)
         ep = _ep_moe(be, infr_b200, dist, rank, world, local, 20, 3)
+        tps = [_tp_decode_step(be, infr_b200, dist, rank, world, local, b_, 10, 3) for b_ in (1, 32)] if world > 1 else None
+        dps = None
+        if world > 1:
+            # data-parallel replicas: every rank holds the whole model and decodes its own 32 sequences (no exchange)
+            mine = _decode_step_case(be, infr_b200, 32, 5, 3, hbm_peak)
+            us_dp = _max_over_ranks(dist, mine["us_per_step"])
+            dps = {"workload": f"{world} replicas of the 8B-shape decode step, batch 32 each, KV context 4096, no exchange",
+                   "us_per_step": us_dp, "tok_per_s": world * 32 / (us_dp * 1e-6), "scaling": "weak"}
         if rank == 0:
             out["tp_decode"] = tp
             out["ep_moe"] = ep
+            if tps:
+                out["tp_decode_step"] = tps
+                out["dp_decode_step"] = dps
 
     if rank == 0 and world == 1 and not args.no_cpu:
         out["cpu_baseline"] = _cpu_baseline(w, x, budget_s=10.0)
 
     be.close()
     if rank == 0:
-        print(json.dumps(out))
+        _emit(out)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -734,22 +864,22 @@ def run_profile_case(args):
     name, out_f, in_f, m = args.profile_case.split(":")
     if name == "moe":
         be = infr_b200.CudaBackend(device=0)
-        print(json.dumps(_moe_case(be, infr_b200, args.steps, 2)))
+        _emit(_moe_case(be, infr_b200, args.steps, 2))
         be.close()
         return
     if name == "decode":  # decode:0:0:BATCH — the Linear ops of an 8B-shape decode step
         be = infr_b200.CudaBackend(device=0)
-        print(json.dumps(_decode_linears_case(be, infr_b200, int(m), args.steps, 2)))
+        _emit(_decode_linears_case(be, infr_b200, int(m), args.steps, 2))
         be.close()
         return
     if name == "step":  # step:0:CONTEXT:BATCH — the whole 8B-shape decode step
         be = infr_b200.CudaBackend(device=0)
-        print(json.dumps(_decode_step_case(be, infr_b200, int(m), args.steps, 2, 6542.7, pos=int(in_f) or 4096)))
+        _emit(_decode_step_case(be, infr_b200, int(m), args.steps, 2, 6542.7, pos=int(in_f) or 4096))
         be.close()
         return
     if name == "mmq":  # mmq:OUT_F:IN_F:M — the prefill GEMM (Linear with m > 8)
         be = infr_b200.CudaBackend(device=0)
-        print(json.dumps(_mmq_case(be, infr_b200, int(m), int(in_f), int(out_f), 5, args.steps, 2)))
+        _emit(_mmq_case(be, infr_b200, int(m), int(in_f), int(out_f), 5, args.steps, 2))
         be.close()
         return
     dtype = {v: k for k, v in synth.DTYPE_NAMES.items()}[name]
@@ -770,8 +900,8 @@ def run_profile_case(args):
     for i in range(args.steps):
         be.gemv_q8(dtype, bufs[i % len(bufs)], qs, d, s32, s16 if dtype == infr_b200.Q6K else None, yb, m, in_f, out_f)
     ms = be.timer_stop()
-    print(json.dumps({"profile_case": args.profile_case, "launches": args.steps, "copies": len(bufs),
-                      "alg_bytes_per_launch": w.nbytes + 4 * m * (in_f + out_f), "us_per_launch_incl_host": ms * 1e3 / args.steps}))
+    _emit({"profile_case": args.profile_case, "launches": args.steps, "copies": len(bufs),
+           "alg_bytes_per_launch": w.nbytes + 4 * m * (in_f + out_f), "us_per_launch_incl_host": ms * 1e3 / args.steps})
     be.close()
 
 
@@ -826,7 +956,7 @@ def run_reference(args):
            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
-    print(json.dumps(out))
+    _emit(out)
 
 
 def main():
@@ -848,5 +978,20 @@ def main():
         run_b200(args)
 
 
+_RESULT_STREAM = None
+
+
+def _emit(obj):
+    """The one JSON line of the contract, on the process's original stdout."""
+    stream = _RESULT_STREAM or sys.stdout
+    print(json.dumps(obj), file=stream)
+    stream.flush()
+
+
 if __name__ == "__main__":
+    # Libraries write banners to stdout (NCCL prints its version there when NCCL_DEBUG asks for it): everything but
+    # the result line goes to stderr.
+    sys.stdout.flush()
+    _RESULT_STREAM = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     main()

@@ -48,13 +48,19 @@ class DecodeStep:
     "ffn_norm", f32), `head` the lm_head weight (`head_dtype`), `out_norm` the output norm.  `k_cache` / `v_cache`
     are per-layer Buffers holding `n_seq` caches of `max_ctx` rows each."""
 
-    def __init__(self, be, shape: LlamaShape, n_seq: int, max_ctx: int, layers, out_norm, head, head_dtype, k_cache, v_cache):
+    def __init__(self, be, shape: LlamaShape, n_seq: int, max_ctx: int, layers, out_norm, head, head_dtype, k_cache, v_cache,
+                 sub=None, reduce=None, argmax: bool = True):
+        """Tensor-parallel use: `shape` holds this rank's share (n_head, n_kv, ffn and vocab divided by the ranks, hidden
+        whole), `reduce(buffer, n_floats)` sums the row-parallel Linears' partial results (attention output, FFN down)
+        over the ranks in place, `sub` optionally supplies the buffer those results live in (e.g. memory a collective
+        library can address), and `argmax=False` leaves the rank's slice of the logits for the caller to gather."""
         self.be, self.s, self.n_seq, self.max_ctx = be, shape, n_seq, max_ctx
+        self.reduce, self.do_argmax = reduce, argmax
         self.layers, self.out_norm, self.head, self.head_dtype = layers, out_norm, head, head_dtype
         self.k_cache, self.v_cache = k_cache, v_cache
         s, b = shape, n_seq
         f32 = lambda n: be.alloc(b * n * 4, USAGE_ACTIVATIONS)
-        self.hidden, self.hn, self.sub = f32(s.hidden), f32(s.hidden), f32(s.hidden)
+        self.hidden, self.hn, self.sub = f32(s.hidden), f32(s.hidden), (sub if sub is not None else f32(s.hidden))
         self.q, self.k, self.v, self.k_rot, self.attn = f32(s.q_dim), f32(s.kv_dim), f32(s.kv_dim), f32(s.kv_dim), f32(s.q_dim)
         self.g, self.u, self.act = f32(s.ffn), f32(s.ffn), f32(s.ffn)
         self.logits = f32(s.vocab)
@@ -99,16 +105,21 @@ class DecodeStep:
             be.attention_q8(self.q, self.k_cache[li], self.v_cache[li], *a8, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
                             head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride)
             gemv(Q4K, L["wo"], self.sub, s.q_dim, h)
+            if self.reduce:
+                self.reduce(self.sub, b * h)
             be.add_rms_norm_q8(self.hidden, self.sub, self.hidden, L["ffn_norm"], b, h, s.eps, *a8)
             gemv(Q4K, L["gate"], self.g, h, ff)
             gemv(Q4K, L["up"], self.u, h, ff)
             be.gated_act_q8(self.g, self.u, b, ff, *a8)
             gemv(Q6K, L["down"], self.sub, ff, h)
+            if self.reduce:
+                self.reduce(self.sub, b * h)
             nxt = self.layers[li + 1]["attn_norm"] if li + 1 < len(self.layers) else self.out_norm
             be.add_rms_norm_q8(self.hidden, self.sub, self.hidden, nxt, b, h, s.eps, *a8)
             n += 13
         gemv(self.head_dtype, self.head, self.logits, h, s.vocab)
-        be.argmax(self.logits, self.tok, s.vocab, b)
+        if self.do_argmax:
+            be.argmax(self.logits, self.tok, s.vocab, b)
         return n + 2
 
     def _run_f32(self, pos: int, fused: bool) -> int:
@@ -155,6 +166,8 @@ class DecodeStep:
                          head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride)
             lin(Q4K, L["wo"], self.attn, self.sub, s.q_dim, h)
             n += 2
+            if self.reduce:
+                self.reduce(self.sub, b * h)
             if fused:
                 be.add_rms_norm(self.hidden, self.sub, self.hidden, L["ffn_norm"], self.hn, b, h, s.eps)
                 n += 1
@@ -166,6 +179,8 @@ class DecodeStep:
             be.gated_act(self.g, self.u, self.act, b, ff)
             lin(Q6K, L["down"], self.act, self.sub, ff, h)
             n += 2
+            if self.reduce:
+                self.reduce(self.sub, b * h)
             nxt = self.layers[li + 1]["attn_norm"] if li + 1 < len(self.layers) else self.out_norm
             if fused:
                 be.add_rms_norm(self.hidden, self.sub, self.hidden, nxt, self.hn, b, h, s.eps)
@@ -175,5 +190,6 @@ class DecodeStep:
                 be.rms_norm(self.hidden, nxt, self.hn, b, h, s.eps)
                 n += 2
         lin(self.head_dtype, self.head, self.hn, self.logits, h, s.vocab)
-        be.argmax(self.logits, self.tok, s.vocab, b)
+        if self.do_argmax:
+            be.argmax(self.logits, self.tok, s.vocab, b)
         return n + 2

@@ -717,7 +717,7 @@ def run_b200(args):
 
     rank, world, local, dist = _dist_setup(args.gpus)
     hbm_peak, peak_src = _peaks()
-    be = infr_b200.CudaBackend(device=local, _dev_opts=[int(os.environ.get('INFR_DEV_GEMV_IMPL', '0'))])
+    be = infr_b200.CudaBackend(device=local)
     caps = be.capabilities()
     steps, warmup = args.steps, max(args.warmup, 3)
 
@@ -884,7 +884,7 @@ def run_profile_case(args):
         return
     dtype = {v: k for k, v in synth.DTYPE_NAMES.items()}[name]
     out_f, in_f, m = int(out_f), int(in_f), int(m)
-    be = infr_b200.CudaBackend(device=0, _dev_opts=[int(os.environ.get('INFR_DEV_GEMV_IMPL', '0'))])
+    be = infr_b200.CudaBackend(device=0)
     caps = be.capabilities()
     bufs, w = _rotation(be, infr_b200, dtype, out_f, in_f, 5, caps.l2_bytes + (32 << 20))
     if args.copies:

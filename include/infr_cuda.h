@@ -69,10 +69,17 @@ typedef struct infr_cuda_graph infr_cuda_graph;
 /* Options of infr_cuda_create.  `reference` mirrors CpuCfg::reference
  * (crates/infr-core/src/config/mod.rs:425-438): when non-zero every quantized Linear / MoeFfn run by
  * infr_cuda_execute uses INFR_ACT_F32 arithmetic. */
+/* gemv_kernel / mmq_kernel choose between kernels that compute the same op (0 = the default dispatch); they exist
+ * so that the parity tests can reach every kernel of the library on every shape:
+ *   gemv_kernel 1: the direct-load byte-dot GEMV for all formats and batches;
+ *   mmq_kernel  1: the Q4_K prefill GEMM whose f32 output is bit-identical to the CPU's (slower),
+ *               2: the default tensor-memory GEMM also for batches the dispatch would walk through the GEMV. */
 typedef struct {
     int32_t device;
     int32_t reference;
-    int32_t reserved[6];
+    int32_t gemv_kernel;
+    int32_t mmq_kernel;
+    int32_t reserved[4];
 } infr_cuda_opts;
 
 /* The subset of `struct Capabilities` (crates/infr-core/src/backend.rs:43-213) this backend sets;
@@ -117,10 +124,22 @@ INFR_API void infr_cuda_free(infr_cuda_ctx *ctx, infr_cuda_buf *buf);
  * Set-up: every rank creates a comm, exports its 64-byte handle (a CUDA IPC memory handle), the host program
  * gathers the handles of all ranks in rank order by whatever channel it has, and every rank connects.
  * All ranks must issue the same sequence of all-reduces.  A peer that never arrives makes the bounded wait
- * expire: the data is left unsummed and the next infr_cuda_sync returns INFR_E_TIMEOUT. */
+ * expire: the data is left unsummed and the next infr_cuda_sync returns INFR_E_TIMEOUT.
+ * Ordering the host program owes (one process per GPU, so only the host can give it):
+ *  - a host barrier over all ranks after every rank has connected and BEFORE the first exchange: the wait is a
+ *    few seconds of polling, and a rank still loading weights or capturing a graph would let its peers' waits expire;
+ *  - a host barrier after every rank has synchronised its last exchange and BEFORE any rank calls
+ *    infr_cuda_comm_destroy: destroy frees memory the peers have mapped and may still be storing into.
+ * Where the reference's multi-GPU sketch has one `group` object owning N devices in one process, this library has
+ * one context and one comm per process; infr_cuda_comm_* stands in for a group constructor. */
 INFR_API int32_t infr_cuda_comm_create(infr_cuda_ctx *ctx, int32_t rank, int32_t world, uint32_t max_floats, infr_cuda_comm **out);
 INFR_API int32_t infr_cuda_comm_export(infr_cuda_ctx *ctx, infr_cuda_comm *comm, uint8_t *handle64);
 INFR_API int32_t infr_cuda_comm_connect(infr_cuda_ctx *ctx, infr_cuda_comm *comm, const uint8_t *handles /* [world][64] */);
+/* Failure-detection aid: instead of connecting real peers, map every peer slot onto a private buffer of this
+ * rank that nobody writes, and let a wait give up after spin_limit polls (1 .. 4194304).  The next all-reduce
+ * then returns without summing and infr_cuda_sync reports INFR_E_TIMEOUT; the context stays usable.  This is how
+ * a host program (and this library's tests) exercise the path a vanished rank would take, without one. */
+INFR_API int32_t infr_cuda_comm_connect_silent(infr_cuda_ctx *ctx, infr_cuda_comm *comm, uint32_t spin_limit);
 INFR_API int32_t infr_cuda_all_reduce_f32(infr_cuda_ctx *ctx, infr_cuda_comm *comm, infr_cuda_buf *data, uint32_t n);
 INFR_API void infr_cuda_comm_destroy(infr_cuda_ctx *ctx, infr_cuda_comm *comm);
 INFR_API size_t infr_cuda_buf_len(const infr_cuda_buf *buf);
@@ -219,7 +238,8 @@ INFR_API int32_t infr_cuda_gemv_q8(infr_cuda_ctx *ctx, int32_t dtype, const infr
  * y: f32 [m,out_f]) and a cudaStream_t passed as void* (NULL = the default stream), needs no context,
  * and keeps its quantised activations in a 192 KiB array built into the library (held by every GPU
  * that loads it) instead of allocating: the call runs no cudaMalloc / cudaFree / allocating routine.
- * Limits: m <= 8, in_f <= 16384; larger sizes are rejected with INFR_E_INVALID.  The first call on a
+ * Limits: m <= 8, in_f <= 16384; larger sizes are rejected with INFR_E_INVALID.  Alignment: x on 16 bytes,
+ * y on 4, w on 16 for Q4_K and on 2 for Q6_K / Q2_0; a misaligned pointer is INFR_E_INVALID.  The first call on a
  * device looks up the array's device address (cudaGetSymbolAddress) — make that call before any
  * stream capture.  All calls share the one array: calls that overlap on the GPU (different streams,
  * or threads) race on it; calls on one stream are ordered and need no clearing in between.  Work is
@@ -330,6 +350,13 @@ INFR_API int32_t infr_cuda_timer_start(infr_cuda_ctx *ctx);
 INFR_API int32_t infr_cuda_timer_stop(infr_cuda_ctx *ctx, float *ms);
 /* Overwrites a context-owned buffer larger than L2 (evicts cached weights between timed runs). */
 INFR_API int32_t infr_cuda_flush_l2(infr_cuda_ctx *ctx);
+/* No counterpart in the reference: the device's dense int8 tensor-core rate, measured, as the denominator of the
+ * prefill GEMM's roofline.  Runs `launches` launches of a kernel in which every SM issues 2 x n_batches x 64
+ * tcgen05 kind::i8 instructions of shape 128 x 256 x 32 on operands resident in shared memory (no unpacking, no
+ * epilogue), timed with CUDA events on the context's stream; *ms is the time, *int8_ops the operations (2 per
+ * multiply-add) it covered.  One accumulator element per issuing thread is checked against the value the operand
+ * pattern implies; a mismatch is INFR_E_CUDA.  n_batches 1..4096, launches 1..100000. */
+INFR_API int32_t infr_cuda_tensor_peak_i8(infr_cuda_ctx *ctx, uint32_t n_batches, uint32_t launches, float *ms, double *int8_ops);
 /* Number of kernels this context has launched since creation (graph replays count their nodes). */
 INFR_API uint64_t infr_cuda_launch_count(infr_cuda_ctx *ctx);
 

@@ -32,13 +32,13 @@ E_INVALID, E_UNSUPPORTED, E_OOM, E_CUDA, E_NCCL, E_TIMEOUT = -1, -2, -3, -4, -5,
 EXPORTED_SYMBOLS = [
     "infr_cuda_create", "infr_cuda_destroy", "infr_cuda_get_caps", "infr_cuda_last_error",
     "infr_cuda_alloc", "infr_cuda_alloc_uninit", "infr_cuda_free", "infr_cuda_buf_len",
-    "infr_cuda_buf_device_ptr", "infr_cuda_wrap", "infr_cuda_stream", "infr_cuda_comm_create", "infr_cuda_comm_export", "infr_cuda_comm_connect",
+    "infr_cuda_buf_device_ptr", "infr_cuda_wrap", "infr_cuda_stream", "infr_cuda_comm_create", "infr_cuda_comm_export", "infr_cuda_comm_connect", "infr_cuda_comm_connect_silent",
     "infr_cuda_all_reduce_f32", "infr_cuda_comm_destroy", "infr_cuda_upload", "infr_cuda_upload_at", "infr_cuda_download",
     "infr_cuda_copy", "infr_cuda_host_alloc", "infr_cuda_host_free", "infr_cuda_sync", "infr_cuda_compile", "infr_cuda_plan_free", "infr_cuda_execute",
     "infr_cuda_quantize_q8", "infr_cuda_quantize_q8_1", "infr_cuda_gemv", "infr_cuda_gemv_q8", "infr_cuda_gemv_noalloc", "infr_cuda_gemv_block_acc",
     "infr_cuda_linear", "infr_cuda_moe_ffn", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
     "infr_cuda_graph_free", "infr_cuda_timer_start", "infr_cuda_timer_stop", "infr_cuda_flush_l2",
-    "infr_cuda_launch_count",
+    "infr_cuda_launch_count", "infr_cuda_tensor_peak_i8",
     "infr_cuda_rms_norm", "infr_cuda_add_rms_norm", "infr_cuda_rope", "infr_cuda_write_kv", "infr_cuda_attention", "infr_cuda_rope_write_kv",
     "infr_cuda_gated_act", "infr_cuda_add", "infr_cuda_argmax", "infr_cuda_add_rms_norm_q8", "infr_cuda_gated_act_q8", "infr_cuda_attention_q8",
 ]
@@ -53,7 +53,7 @@ class BackendError(RuntimeError):
 
 
 class _Opts(C.Structure):
-    _fields_ = [("device", C.c_int32), ("reference", C.c_int32), ("reserved", C.c_int32 * 6)]
+    _fields_ = [("device", C.c_int32), ("reference", C.c_int32), ("gemv_kernel", C.c_int32), ("mmq_kernel", C.c_int32), ("reserved", C.c_int32 * 4)]
 
 
 class _Caps(C.Structure):
@@ -133,6 +133,7 @@ def load_library() -> C.CDLL:
         "infr_cuda_comm_create": (i32, [vp, i32, i32, u32, C.POINTER(vp)]),
         "infr_cuda_comm_export": (i32, [vp, vp, vp]),
         "infr_cuda_comm_connect": (i32, [vp, vp, vp]),
+        "infr_cuda_comm_connect_silent": (i32, [vp, vp, u32]),
         "infr_cuda_all_reduce_f32": (i32, [vp, vp, vp, u32]),
         "infr_cuda_comm_destroy": (None, [vp, vp]),
         "infr_cuda_gemv": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
@@ -149,6 +150,7 @@ def load_library() -> C.CDLL:
         "infr_cuda_timer_stop": (i32, [vp, C.POINTER(C.c_float)]),
         "infr_cuda_flush_l2": (i32, [vp]),
         "infr_cuda_launch_count": (u64, [vp]),
+        "infr_cuda_tensor_peak_i8": (i32, [vp, u32, u32, C.POINTER(C.c_float), C.POINTER(C.c_double)]),
         "infr_cuda_rms_norm": (i32, [vp, vp, vp, vp, u32, u32, C.c_float]),
         "infr_cuda_add_rms_norm": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, C.c_float]),
         "infr_cuda_rope": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, C.c_float, i32]),
@@ -227,7 +229,12 @@ class Comm:
         blob = (C.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(handles))
         self._be._check(self._be.L.infr_cuda_comm_connect(self._be.ctx, self.handle, blob))
 
+    def connect_silent(self, spin_limit: int = 4096):
+        """Failure-detection aid: peers that never answer (see infr_cuda_comm_connect_silent)."""
+        self._be._check(self._be.L.infr_cuda_comm_connect_silent(self._be.ctx, self.handle, spin_limit))
+
     def close(self):
+        """All ranks must have synchronised their last exchange and passed a host barrier before any rank closes."""
         if self.handle and self._be.ctx:
             self._be.L.infr_cuda_comm_destroy(self._be.ctx, self.handle)
         self.handle = None
@@ -308,12 +315,11 @@ class CudaGraph:
 class CudaBackend:
     """`impl Backend for CudaBackend` over the C ABI."""
 
-    def __init__(self, device: int = 0, reference: bool = False, _dev_opts: Sequence[int] = ()):
+    def __init__(self, device: int = 0, reference: bool = False, gemv_kernel: int = 0, mmq_kernel: int = 0):
+        """gemv_kernel / mmq_kernel: infr_cuda_opts' kernel selectors (0 = the default dispatch), used by the parity tests."""
         self.L = load_library()
         self.ctx = None
-        opts = _Opts(device=device, reference=int(reference))
-        for i, v in enumerate(_dev_opts):
-            opts.reserved[i] = int(v)
+        opts = _Opts(device=device, reference=int(reference), gemv_kernel=int(gemv_kernel), mmq_kernel=int(mmq_kernel))
         ctx = C.c_void_p()
         rc = self.L.infr_cuda_create(C.byref(opts), C.byref(ctx))
         if rc != 0:
@@ -561,6 +567,12 @@ class CudaBackend:
 
     def launch_count(self) -> int:
         return int(self.L.infr_cuda_launch_count(self.ctx))
+
+    def tensor_peak_i8(self, n_batches: int = 64, launches: int = 20):
+        """(milliseconds, int8 operations) of `launches` launches of the dense kind::i8 peak microbenchmark."""
+        ms, ops = C.c_float(), C.c_double()
+        self._check(self.L.infr_cuda_tensor_peak_i8(self.ctx, n_batches, launches, C.byref(ms), C.byref(ops)))
+        return float(ms.value), float(ops.value)
 
     # ---- convenience used by tests: host arrays in, host array out, through the graph seam ----
     def run_linear(self, dtype: int, w_bytes: np.ndarray, x: np.ndarray, m: int, in_f: int, out_f: int,

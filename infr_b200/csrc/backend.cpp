@@ -58,8 +58,8 @@ Status CudaBackend::create(const infr_cuda_opts &opts, CudaBackend **out) {
         delete be;
         return s;
     }
-    be->gemv_impl_ = opts.reserved[0];
-    be->mmq_impl_ = opts.reserved[1];
+    be->gemv_impl_ = opts.gemv_kernel;
+    be->mmq_impl_ = opts.mmq_kernel;
     if (!(s = be->cuda_status(cudaHostAlloc((void **)&be->status_host_, 64, cudaHostAllocMapped), "cudaHostAlloc")).ok() ||
         !(s = be->cuda_status(cudaHostGetDevicePointer((void **)&be->status_dev_, be->status_host_, 0), "cudaHostGetDevicePointer")).ok()) {
         delete be;
@@ -819,6 +819,35 @@ Status CudaBackend::flush_l2() {
     Status s = cuda_status(launch_fill_u32(static_cast<uint32_t *>(flush_), flush_bytes_ / 4, (uint32_t)launches_, stream_), "flush_l2");
     if (s.ok()) launches_++;
     return s;
+}
+
+Status CudaBackend::tensor_peak_i8(uint32_t n_batches, uint32_t launches, float *ms, double *ops) {
+    if (!ms || !ops || launches == 0 || launches > 100000 || n_batches == 0 || n_batches > 4096)
+        return Status::Err(INFR_E_INVALID, "tensor_peak_i8: 1..4096 batches, 1..100000 launches, non-null outputs");
+    if (capturing_) return Status::Err(INFR_E_INVALID, "tensor_peak_i8 during stream capture");
+    cudaSetDevice(device_);
+    Status s = ensure_scratch(256);
+    if (!s.ok()) return s;
+    int32_t *check = reinterpret_cast<int32_t *>(scratch());
+    if (!(s = cuda_status(cudaMemsetAsync(check, 0xff, 8, stream_), "tensor_peak memset")).ok()) return s;
+    // one untimed launch: module load, first tensor-memory allocation
+    if (!(s = cuda_status(launch_tensor_peak_i8(n_batches, check, dev_, status_dev_, stream_), "tensor_peak_i8")).ok()) return s;
+    if (!(s = cuda_status(cudaEventRecord(ev0_, stream_), "cudaEventRecord")).ok()) return s;
+    for (uint32_t i = 0; i < launches; i++)
+        if (!(s = cuda_status(launch_tensor_peak_i8(n_batches, check, dev_, status_dev_, stream_), "tensor_peak_i8")).ok()) return s;
+    launches_ += launches + 1;
+    if (!(s = cuda_status(cudaEventRecord(ev1_, stream_), "cudaEventRecord")).ok()) return s;
+    if (!(s = cuda_status(cudaEventSynchronize(ev1_), "cudaEventSynchronize")).ok()) return s;
+    if (!(s = cuda_status(cudaEventElapsedTime(ms, ev0_, ev1_), "cudaEventElapsedTime")).ok()) return s;
+    if (!(s = check_device_status()).ok()) return s;
+    int32_t got[2] = {0, 0};
+    if (!(s = cuda_status(cudaMemcpyAsync(got, check, 8, cudaMemcpyDeviceToHost, stream_), "tensor_peak readback")).ok()) return s;
+    if (!(s = cuda_status(cudaStreamSynchronize(stream_), "tensor_peak sync")).ok()) return s;
+    const int32_t want = tensor_peak_i8_expected(n_batches);
+    if (got[0] != want || got[1] != want)
+        return Status::Err(INFR_E_CUDA, fmt("tensor_peak_i8: accumulator check failed (got %d and %d, the operand pattern implies %d)", got[0], got[1], want));
+    *ops = tensor_peak_i8_ops(n_batches, dev_) * launches;
+    return Status::Ok();
 }
 
 }  // namespace infr

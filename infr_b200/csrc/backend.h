@@ -71,6 +71,7 @@ public:
     Status comm_create(int rank, int world, uint32_t max_floats, infr_cuda_comm **out);
     Status comm_export(infr_cuda_comm *c, uint8_t *handle64);
     Status comm_connect(infr_cuda_comm *c, const uint8_t *handles);
+    Status comm_connect_silent(infr_cuda_comm *c, uint32_t spin_limit);
     Status all_reduce_f32(infr_cuda_comm *c, float *data, uint32_t n);
     void comm_destroy(infr_cuda_comm *c);
     Status upload(infr_cuda_buf *dst, size_t dst_off, const void *src, size_t bytes);
@@ -129,6 +130,8 @@ public:
     Status timer_start();
     Status timer_stop(float *ms);
     Status flush_l2();
+    // Measures the dense int8 tensor-core rate: `launches` launches of the microbenchmark kernel, CUDA-event timed.
+    Status tensor_peak_i8(uint32_t n_batches, uint32_t launches, float *ms, double *ops);
     uint64_t launch_count() const { return launches_; }
 
     std::mutex &mutex() { return mu_; }

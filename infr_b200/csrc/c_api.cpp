@@ -104,6 +104,11 @@ int32_t infr_cuda_comm_connect(infr_cuda_ctx *ctx, infr_cuda_comm *comm, const u
     return finish(ctx, ctx->be->comm_connect(comm, handles));
 }
 
+int32_t infr_cuda_comm_connect_silent(infr_cuda_ctx *ctx, infr_cuda_comm *comm, uint32_t spin_limit) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->comm_connect_silent(comm, spin_limit));
+}
+
 int32_t infr_cuda_all_reduce_f32(infr_cuda_ctx *ctx, infr_cuda_comm *comm, infr_cuda_buf *data, uint32_t n) {
     INFR_CTX_OR_RETURN(ctx);
     if (!data || (size_t)n * 4 > data->len) return finish(ctx, Status::Err(INFR_E_INVALID, "all_reduce: buffer smaller than n floats"));
@@ -544,6 +549,10 @@ int32_t infr_cuda_timer_stop(infr_cuda_ctx *ctx, float *ms) {
 int32_t infr_cuda_flush_l2(infr_cuda_ctx *ctx) {
     INFR_CTX_OR_RETURN(ctx);
     return finish(ctx, ctx->be->flush_l2());
+}
+int32_t infr_cuda_tensor_peak_i8(infr_cuda_ctx *ctx, uint32_t n_batches, uint32_t launches, float *ms, double *int8_ops) {
+    INFR_CTX_OR_RETURN(ctx);
+    return finish(ctx, ctx->be->tensor_peak_i8(n_batches, launches, ms, int8_ops));
 }
 uint64_t infr_cuda_launch_count(infr_cuda_ctx *ctx) {
     if (!ctx || !ctx->be) return 0;

@@ -43,7 +43,7 @@ struct ArPeers {
 // ctrl[0] = epoch, ctrl[1] = CTAs done in the current launch (both in this rank's memory)
 __global__ void __launch_bounds__(kArThreads, 1)
     allreduce_oneshot_kernel(float *__restrict__ data, uint32_t n4, int rank, int world, uint32_t cap, ArPeers peers,
-                             uint32_t *__restrict__ ctrl, uint32_t *__restrict__ status) {
+                             uint32_t *__restrict__ ctrl, uint32_t *__restrict__ status, uint32_t spin) {
     __shared__ int s_bad;
     const uint32_t i = blockIdx.x * kArThreads + threadIdx.x;  // float4 index
     if (threadIdx.x == 0) s_bad = 0;
@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(kArThreads, 1)
         // wait for rank `threadIdx.x`'s part in MY staging buffer
         volatile uint32_t *fl = peers.flags[rank] + ((size_t)p * kArMaxCtas + blockIdx.x) * world + threadIdx.x;
         uint32_t it = 0;
-        while (*fl != want && ++it < kArSpin) {
+        while (*fl != want && ++it < spin) {
         }
         if (*fl != want) {
             s_bad = 1;
@@ -107,6 +107,8 @@ struct infr_cuda_comm {
     size_t stage_bytes = 0, flag_bytes = 0;
     void *peer_base[infr::kMaxWorld] = {};  // mapped allocations of the peers (own entry = local)
     bool connected = false;
+    uint32_t spin = infr::kArSpin;  // polls a wait may take before it gives up
+    uint8_t *silent = nullptr;      // comm_connect_silent: a stand-in for the peers that nobody ever writes to
 };
 
 namespace infr {
@@ -163,6 +165,27 @@ Status CudaBackend::comm_connect(infr_cuda_comm *c, const uint8_t *handles) {
     return Status::Ok();
 }
 
+// Failure-detection hook: every peer slot is mapped onto one private, zeroed buffer of THIS rank, so this rank's
+// stores land somewhere harmless and the peers' flags never arrive; with a short poll limit the next exchange's
+// wait runs out, the kernel returns, and the host sees INFR_E_TIMEOUT at its next sync.
+Status CudaBackend::comm_connect_silent(infr_cuda_comm *c, uint32_t spin_limit) {
+    if (!c) return Status::Err(INFR_E_INVALID, "comm_connect_silent: null comm");
+    if (c->connected && c->world > 1) return Status::Err(INFR_E_INVALID, "comm_connect_silent: already connected");
+    if (capturing_) return Status::Err(INFR_E_INVALID, "comm_connect_silent during stream capture");
+    if (spin_limit == 0 || spin_limit > kArSpin) return Status::Err(INFR_E_INVALID, "comm_connect_silent: poll limit out of range");
+    cudaSetDevice(device_);
+    const size_t total = c->stage_bytes + c->flag_bytes + 256;
+    Status s = cuda_status(cudaMalloc((void **)&c->silent, total), "cudaMalloc(comm stand-in)");
+    if (s.ok()) s = cuda_status(cudaMemsetAsync(c->silent, 0, total, stream_), "cudaMemsetAsync(comm stand-in)");
+    if (s.ok()) s = cuda_status(cudaStreamSynchronize(stream_), "comm sync");
+    if (!s.ok()) return s;
+    for (int r = 0; r < c->world; r++)
+        if (r != c->rank) c->peer_base[r] = c->silent;
+    c->spin = spin_limit;
+    c->connected = true;
+    return Status::Ok();
+}
+
 Status CudaBackend::all_reduce_f32(infr_cuda_comm *c, float *data, uint32_t n) {
     if (!c || !data) return Status::Err(INFR_E_INVALID, "all_reduce: null argument");
     if (!c->connected) return Status::Err(INFR_E_INVALID, "all_reduce: the peers' buffers are not connected");
@@ -187,7 +210,7 @@ Status CudaBackend::all_reduce_f32(infr_cuda_comm *c, float *data, uint32_t n) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    Status s = cuda_status(cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel, data, n4, c->rank, c->world, c->cap, peers, ctrl, status_dev_), "all_reduce");
+    Status s = cuda_status(cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel, data, n4, c->rank, c->world, c->cap, peers, ctrl, status_dev_, c->spin), "all_reduce");
     if (s.ok()) launches_ += 1;
     return s;
 }
@@ -197,7 +220,8 @@ void CudaBackend::comm_destroy(infr_cuda_comm *c) {
     cudaSetDevice(device_);
     if (!capturing_) cudaStreamSynchronize(stream_);
     for (int r = 0; r < c->world; r++)
-        if (r != c->rank && c->peer_base[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
+        if (r != c->rank && c->peer_base[r] && c->peer_base[r] != c->silent) cudaIpcCloseMemHandle(c->peer_base[r]);
+    if (c->silent) cudaFree(c->silent);
     if (c->local) cudaFree(c->local);
     delete c;
 }

@@ -719,12 +719,10 @@ size_t attention_workspace_bytes(int q_rows, int n_head, int head_dim, int max_k
 template <int HD, int G>
 static cudaError_t launch_attn_one(dim3 grid, cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *po, float *pml, int rows,
                                    int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride) {
-    static bool configured = false;  // per instantiation: the tile needs more than the default 48 KB of dynamic shared memory
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<HD>::kBytes);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    // the tile needs more than the default 48 KB of dynamic shared memory; the attribute is per device, so it is set
+    // on every launch (cheap, allocates nothing) rather than remembered per process
+    cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<HD>::kBytes);
+    if (e != cudaSuccess) return e;
     return launch_pdl(attn_split_kernel<HD, G>, grid, dim3(kAttnThreads), (size_t)AttnSmem<HD>::kBytes, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos,
                       scale, n_splits, seq_stride);
 }

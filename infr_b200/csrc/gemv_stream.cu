@@ -422,17 +422,12 @@ cudaError_t launch_stream_m(int dt, const uint8_t *w, const Q8Dev &a, float *y, 
     return launch_stream_dt<DT_Q2_0, M>(w, a, y, m, in_f, out_f, dev, status, st);
 }
 
-bool getenv_flag(const char *name) {
-    const char *v = getenv(name);
-    return v && v[0] && v[0] != '0';
-}
-
 }  // namespace
 
 cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
                                const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
     if (m < 1 || m > 8 || (dt != DT_Q4K && dt != DT_Q6K && dt != DT_Q2_0)) return cudaErrorInvalidValue;
-    if (dt == DT_Q2_0 && m > 1 && in_f % 512 == 0 && a.gran == 32 && !getenv_flag("INFR_DEV_Q2_STREAM")) {
+    if (dt == DT_Q2_0 && m > 1 && in_f % 512 == 0 && a.gran == 32) {
         // batches on rows of whole 512-element chunks take the matrix-unit kernel (1.6x faster at m = 4 and 8,
         // no gain at m = 1); it declines shapes whose staged activations do not fit, and those fall through
         // to the byte-dot kernel below
@@ -440,7 +435,7 @@ cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *
         if (e != cudaErrorInvalidValue) return e;
         cudaGetLastError();
     }
-    if (dt == DT_Q6K && in_f % 2048 == 0 && a.gran == 256 && a.sums16 && !getenv_flag("INFR_DEV_Q6_STREAM")) {
+    if (dt == DT_Q6K && in_f % 2048 == 0 && a.gran == 256 && a.sums16) {
         // rows whose byte length is a multiple of 16 take the matrix-unit kernel (same fall-through rule)
         const cudaError_t e = launch_gemv_q6_mma(w, a, y, m, in_f, out_f, dev, status, st);
         if (e != cudaErrorInvalidValue) return e;

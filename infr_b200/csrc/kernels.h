@@ -100,6 +100,12 @@ cudaError_t launch_moe_combine(const float *y_pairs, const int32_t *pair_of_slot
 cudaError_t launch_gemv_q4k_f32_sel(const uint8_t *bank, const int32_t *sel, size_t w_stride, const float *x, int x_div,
                                     float *y, int n_pairs, int in_f, int out_f, const DeviceInfo &dev, cudaStream_t st);
 
+// Dense int8 tensor-core peak microbenchmark (tensor_peak.cu): one launch = every SM issues 2 x n_batches x 64
+// tcgen05 kind::i8 instructions of shape 128 x 256 x 32 from resident shared-memory operands.
+cudaError_t launch_tensor_peak_i8(uint32_t n_batches, int32_t *check, const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
+double tensor_peak_i8_ops(uint32_t n_batches, const DeviceInfo &dev);
+int32_t tensor_peak_i8_expected(uint32_t n_batches);
+
 cudaError_t launch_fill_u32(uint32_t *p, size_t n, uint32_t v, cudaStream_t st);
 
 // ---- dense decode-step ops (decode_ops.cu) ----

@@ -181,12 +181,6 @@ __global__ void mmq_ws_prep_kernel(const int8_t *__restrict__ qs, const int32_t 
 }
 
 
-#ifdef MMQ_TRACE
-__device__ long long g_trace[8][64][4];
-#define TR(role, j, k) do { if (blockIdx.x == 0 && (j) >= 32 && (j) < 96 && (threadIdx.x & 31) == 0) g_trace[role][(j) - 32][k] = clock64(); } while (0)
-#else
-#define TR(role, j, k)
-#endif
 namespace {
 
 __device__ __forceinline__ bool wait_plain(uint32_t bar, uint32_t parity, uint32_t limit) {
@@ -256,7 +250,6 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                         ok = false;
                         break;
                     }
-                    TR(0, j, 0);
                     uint8_t *st = stage0 + (size_t)s * kStageBytes;
                     const uint32_t fb = bar(B_FULL + s);
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb), "r"(kStageBytes) : "memory");
@@ -291,7 +284,6 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 const int s = j & 1, ls = j % kStages;
                 const int slot0 = (2 * j) % (int)kSlots, n0 = (2 * j) / (int)kSlots;
                 const int slot1 = (2 * j + 1) % (int)kSlots, n1 = (2 * j + 1) / (int)kSlots;
-                TR(1, j, 0);
                 uint32_t wb = 0, wp = 0;
                 bool need = false;
                 if (lane == 0) wb = bar(B_FULL + ls), wp = (uint32_t)((j / kStages) & 1), need = true;
@@ -309,7 +301,6 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                     ok = false;
                     break;
                 }
-                TR(1, j, 1);
                 tc_fence_after();
                 if (lane == 0) {
                     const uint64_t db0 = mk_desc(su32(stage0 + (size_t)ls * kStageBytes + kRawBytes), kTN * 16, 128);
@@ -337,7 +328,6 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                     mma_commit(bar(B_DONE + ls));
                 }
                 __syncwarp();
-                TR(1, j, 2);
             }
         }
         if (!ok && lane == 0) {
@@ -359,7 +349,6 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
             for (int b = 0; b < nb; b++, j++) {
                 const int ls = j % kStages;
                 const int r = 2 * j + h, slot = r % (int)kSlots, n = r / (int)kSlots;
-                if (quarter == 0) TR(2 + h, j, 0);
                 // two waits on two lanes: the rows have landed, the operand slot's previous MMAs are complete
                 uint32_t wb = 0, wp = 0;
                 bool need = false;
@@ -371,7 +360,6 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                     ok = false;
                     break;
                 }
-                if (quarter == 0) TR(2 + h, j, 1);
                 const uint8_t *blk = stage0 + (size_t)ls * kStageBytes + (size_t)row * 144;
                 const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
                 const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 64 * h), q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 64 * h);
@@ -424,12 +412,10 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                     __syncwarp();
                     if (lane == 0) bar_arrive(bar(B_MINREADY + (j & 1)));
                 }
-                if (quarter == 0) TR(2 + h, j, 2);
                 tst_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) bar_arrive(bar(B_AREADY + slot));
-                if (quarter == 0) TR(2 + h, j, 3);
             }
         }
         if (!ok) {
@@ -454,12 +440,10 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 float4 dd[4];
 #pragma unroll
                 for (int i4 = 0; i4 < 4; i4++) dd[i4] = __ldg(d8p + (size_t)b * (m_pad / 4) + i4);
-                if (warp == 8) TR(4, j, 0);
                 if (!wait_bar_warp(bar(B_DONE + j % kStages), (uint32_t)((j / kStages) & 1), dead)) {
                     ok = false;
                     break;
                 }
-                if (warp == 8) TR(4, j, 1);
                 tc_fence_after();
                 const float dw = dwring[(j % kRing) * kTM + row];
 #pragma unroll
@@ -476,7 +460,6 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) bar_arrive(bar(B_ACCFREE + s));
-                        if (warp == 8) TR(4, j, 2);
                     }
 #pragma unroll
                     for (int i4 = 0; i4 < 4; i4++) {
@@ -490,7 +473,6 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                     }
                 }
             }
-            if (warp == 8) TR(4, j - 1, 3);
             if (!ok) break;
             // tile end: subtract the min sums and store
             const int grow = rt * kTM + row;
@@ -574,15 +556,6 @@ cudaError_t launch_mmq_ws_q4k(const uint8_t *w, const Q8Dev &a, void *records, f
     const int n_tiles = ((out_f + kTM - 1) / kTM) * ((m + kTN - 1) / kTN);
     const int grid = n_tiles < dev.sm_count ? n_tiles : dev.sm_count;
     mmq_ws_kernel<<<grid, kThreadsWs, kSmem, st>>>(map_w, map_q, d8t, c, m, m_pad, in_f, out_f, status);
-#ifdef MMQ_TRACE
-    if (getenv("INFR_MMQ_TRACE")) {
-        cudaDeviceSynchronize();
-        static long long h[8][64][4];
-        cudaMemcpyFromSymbol(h, g_trace, sizeof(h));
-        for (int r = 0; r < 5; r++)
-            for (int j = 0; j < 64; j++) fprintf(stderr, "TR %d %d %lld %lld %lld %lld\n", r, j + 32, h[r][j][0], h[r][j][1], h[r][j][2], h[r][j][3]);
-    }
-#endif
     return cudaGetLastError();
 }
 

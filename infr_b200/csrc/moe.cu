@@ -82,12 +82,25 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
                 bi = oi;
             }
         }
+        if (bi == 0x7fffffff) {
+            // No probability compared greater than -inf: the row is all NaN (a NaN or infinite logit poisons the
+            // softmax sum).  The CPU's stable sort leaves such a row in index order, so take the lowest expert
+            // not selected yet; its NaN weight travels on as it does there.
+            for (int e = lane; e < n_expert; e += 32)
+                if (p[e] != -1.0f) {
+                    bi = e;
+                    break;
+                }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) bi = min(bi, __shfl_xor_sync(0xffffffffu, bi, o));
+            if (bi < n_expert) best = p[bi];
+        }
         wsum = __fadd_rn(wsum, best);
         if (lane == k) {
             myw = best;
-            myid = bi;
+            myid = bi < n_expert ? bi : 0;
         }
-        if (lane == 0) p[bi] = -1.0f;  // probabilities are >= 0: never selected again
+        if (lane == 0 && bi < n_expert) p[bi] = -1.0f;  // probabilities are >= 0: never selected again
         __syncwarp();
     }
     wsum = fmaxf(wsum, 1e-20f);
@@ -112,11 +125,11 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
     __shared__ int s_cnt[1024], s_off[1024], s_ioff[1024];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_pairs = rows * n_used;
-    if (n_local < n_expert)
-        for (int i = threadIdx.x; i < n_pairs; i += 1024) {
-            const int e = sel_ids[i];
-            if (e < e_lo || e >= e_lo + n_local) pair_of_slot[i] = -1;
-        }
+    // pairs whose expert is not listed below (another rank's, or an id outside the bank) contribute nothing
+    for (int i = threadIdx.x; i < n_pairs; i += 1024) {
+        const int e = sel_ids[i];
+        if (e < e_lo || e >= e_lo + n_local || e < 0 || e >= n_expert) pair_of_slot[i] = -1;
+    }
     for (int e = warp; e < n_expert; e += 32) {
         int cnt = 0;
         if (e < e_lo || e >= e_lo + n_local) {  // not this rank's expert: no pairs, no items

@@ -69,6 +69,15 @@ extern "C" int32_t infr_cuda_gemv_noalloc(int32_t dtype, const void *w, const fl
         put_error(err, err_cap, "gemv_noalloc: in_f is not a whole number of weight blocks");
         return INFR_E_INVALID;
     }
+    // Raw pointers come from the caller's own pool, possibly at odd offsets: the quantiser reads x with 16-byte
+    // loads, the Q4_K kernel reads whole 16-byte words of a block, Q6_K / Q2_0 blocks are read in 2-byte units and
+    // y is written as f32.  A misaligned pointer must be an error here, not a fault on the device.
+    const uintptr_t wa = reinterpret_cast<uintptr_t>(w), xa = reinterpret_cast<uintptr_t>(x), ya = reinterpret_cast<uintptr_t>(y);
+    if (xa % 16 || ya % 4 || wa % (dtype == DT_Q4K ? 16u : 2u)) {
+        put_error(err, err_cap,
+                  "gemv_noalloc: misaligned pointer (x: 16 bytes, y: 4 bytes, w: 16 bytes for Q4_K, 2 bytes for Q6_K / Q2_0)");
+        return INFR_E_INVALID;
+    }
     if (out_f == 0) return INFR_OK;
     int device = -1;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {

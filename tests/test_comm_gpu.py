@@ -22,6 +22,29 @@ def test_single_rank_all_reduce_is_the_identity_and_repeats(backend):
     buf.close()
 
 
+def test_a_peer_that_never_answers_times_out_and_the_context_survives(backend):
+    """The bounded wait of the exchange runs out (the second rank's slot is a private buffer nobody writes and the
+    poll limit is short): the kernel returns by itself, sync reports E_TIMEOUT once, and the context goes on working."""
+    comm = backend.comm_create(0, 2, 4096)
+    comm.connect_silent(spin_limit=2048)
+    x = np.linspace(-1.0, 1.0, 4096, dtype=np.float32)
+    buf = backend.from_numpy(x)
+    backend.all_reduce(comm, buf, 4096)
+    with pytest.raises(infr_b200.BackendError) as e:
+        backend.sync()
+    assert e.value.code == infr_b200.E_TIMEOUT
+    backend.sync()  # the status word was consumed: the stream itself is healthy
+    np.testing.assert_array_equal(backend.download(buf, np.float32), x)  # left unsummed, not garbage
+    # an exchange that has all its ranks still works on the same context
+    solo = backend.comm_create(0, 1, 4096)
+    backend.all_reduce(solo, buf, 4096)
+    backend.sync()
+    np.testing.assert_array_equal(backend.download(buf, np.float32), x)
+    for c in (comm, solo):
+        c.close()
+    buf.close()
+
+
 def test_comm_argument_checks(backend):
     for rank, world, n in ((0, 0, 64), (2, 2, 64), (0, 9, 64), (0, 1, 6), (0, 1, 0), (0, 1, 1 << 20)):
         with pytest.raises(infr_b200.BackendError) as e:

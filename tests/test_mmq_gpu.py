@@ -22,7 +22,7 @@ WS_TOL = 1e-5  # f32 rounding noise; the bar for f32 outputs is 1e-3 relative L2
 
 @pytest.fixture(scope="module")
 def exact_backend():
-    be = infr_b200.CudaBackend(device=0, _dev_opts=(0, 1))
+    be = infr_b200.CudaBackend(device=0, mmq_kernel=1)
     yield be
     be.close()
 
@@ -31,7 +31,7 @@ def exact_backend():
 def ws_backend():
     """Every m > 8 Q4_K Linear on the warp-specialised GEMM, also the small batches that the default context would
     walk through the GEMV 8 rows at a time."""
-    be = infr_b200.CudaBackend(device=0, _dev_opts=(0, 2))
+    be = infr_b200.CudaBackend(device=0, mmq_kernel=2)
     yield be
     be.close()
 
@@ -41,7 +41,8 @@ SHAPES = [
     (64, 768, 128),       # exactly one tile, 3 blocks
     (70, 1024, 200),      # ragged in both tile dimensions
     (130, 2048, 300),
-    (512, 4096, 1024),    # the prefill shape at reduced N (the CPU checker stays in seconds)
+    (512, 4096, 1024),    # the prefill shape at reduced N
+    (512, 4096, 14336),   # the prefill configuration itself: 112 row tiles x 8 token tiles, several tiles per persistent CTA
 ]
 
 

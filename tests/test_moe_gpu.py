@@ -15,7 +15,17 @@ from infr_b200 import synth
 pytestmark = pytest.mark.gpu
 
 
+_BANKS = {}
+
+
 def _banks(n_expert, nff, ne, seed):
+    key = (n_expert, nff, ne, seed)
+    if key not in _BANKS:
+        _BANKS[key] = _make_banks(n_expert, nff, ne, seed)
+    return _BANKS[key]
+
+
+def _make_banks(n_expert, nff, ne, seed):
     gate = np.concatenate([synth.weight(Q4K, nff, ne, seed + 3 * e) for e in range(n_expert)])
     up = np.concatenate([synth.weight(Q4K, nff, ne, seed + 3 * e + 1) for e in range(n_expert)])
     down = np.concatenate([synth.weight(Q4K, ne, nff, seed + 3 * e + 2) for e in range(n_expert)])
@@ -46,6 +56,7 @@ def _run(backend, x, router, gate, up, down, rows, ne, n_expert, n_used, nff, no
     (19, 512, 16, 4, 768, True, 1.0),       # 3-block down projection, ragged 8-row items
     (33, 1024, 32, 8, 256, False, 2.5),     # no renormalisation, scale != 1
     (64, 2048, 128, 8, 768, True, 1.0),     # the Qwen3-30B-A3B layer shape with 64 tokens
+    (256, 2048, 128, 8, 768, True, 1.0),    # the MoE configuration itself: 256 tokens, 2048 routed pairs
 ])
 def test_moe_ffn_matches_production_cpu(backend, oracle, rows, ne, n_expert, n_used, nff, norm_w, scale):
     gate, up, down = _banks(n_expert, nff, ne, seed=100)
@@ -60,6 +71,26 @@ def test_moe_ffn_matches_production_cpu(backend, oracle, rows, ne, n_expert, n_u
     rel = fx.rel_l2(got, want)
     assert rel < 1e-3, rel
     assert np.abs(want).max() > 1e-4
+
+
+def test_moe_row_with_a_nan_activation_routes_like_the_cpu(backend, oracle):
+    """An overflowed activation makes a row's logits NaN: the CPU's stable sort then keeps index order (experts
+    0..k-1) and carries NaN weights; the router must answer the same, in range, and the other rows are untouched."""
+    rows, ne, n_expert, n_used, nff = 6, 256, 8, 3, 256
+    gate, up, down = _banks(n_expert, nff, ne, seed=31)
+    router = synth.normal(7, (n_expert, ne), 1.0 / np.sqrt(ne))
+    x = synth.normal(8, (rows, ne))
+    x[2, 17] = np.nan
+    x[4, 3] = np.inf
+    got, ids, w, _ = _run(backend, x, router, gate, up, down, rows, ne, n_expert, n_used, nff)
+    want, o_ids, o_w, _ = oracle.moe_ffn(x, router, gate, up, down, rows=rows, ne=ne, n_expert=n_expert, n_used=n_used, n_ff_exp=nff)
+    np.testing.assert_array_equal(ids, o_ids)
+    np.testing.assert_array_equal(ids[2], np.arange(n_used))
+    assert np.isnan(w[2]).all() and np.isnan(o_w[2]).all()
+    ok = [0, 1, 3, 5]
+    np.testing.assert_allclose(w[ok], o_w[ok], rtol=2e-6, atol=1e-7)
+    assert fx.rel_l2(got[ok], want[ok]) < 1e-3
+    assert np.isnan(got[2]).all() and np.isnan(want[2]).all()
 
 
 def test_moe_ties_keep_the_lower_expert_id(backend):

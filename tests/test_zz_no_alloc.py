@@ -28,13 +28,15 @@ def _sync_device():
     torch.cuda.synchronize()
 
 
-def _noalloc(lib, dt, wb, xb, yb, m, in_f, out_f):
+def _noalloc(lib, dt, wb, xb, yb, m, in_f, out_f, w_skew=0, x_skew=0, y_skew=0):
     err = C.create_string_buffer(256)
-    rc = lib.infr_cuda_gemv_noalloc(dt, wb.device_ptr(), xb.device_ptr(), yb.device_ptr(), m, in_f, out_f, None, err, 256)
+    rc = lib.infr_cuda_gemv_noalloc(dt, wb.device_ptr() + w_skew, xb.device_ptr() + x_skew, yb.device_ptr() + y_skew, m, in_f, out_f,
+                                    None, err, 256)
     return rc, err.value.decode()
 
 
-@pytest.mark.parametrize("dt,in_f,out_f", [(Q6K, 4096, 1536), (Q2_0, 14336, 512), (Q4K, 2048, 768)])
+# the last case is the documented maximum (8 rows of 16384 activations): the largest staging the entry point accepts
+@pytest.mark.parametrize("dt,in_f,out_f", [(Q6K, 4096, 1536), (Q2_0, 14336, 512), (Q4K, 2048, 768), (Q4K, 16384, 64)])
 def test_noalloc_matches_regular_entry_point_twice(backend, dt, in_f, out_f):
     lib = infr_b200.load_library()
     w = synth.weight(dt, out_f, in_f, seed=41 + dt)
@@ -64,5 +66,12 @@ def test_noalloc_rejects_sizes_beyond_its_scratch(backend):
     assert rc == infr_b200.E_INVALID and "at most" in msg
     rc, msg = _noalloc(lib, 5, b, b, b, 1, 4096, 16)            # a dtype this library does not run
     assert rc == infr_b200.E_UNSUPPORTED
+    # pointers at odd offsets of a pool are refused on the host (nothing is launched): x needs 16 bytes, y 4,
+    # w 16 for Q4_K and 2 for the other formats
+    for kw in (dict(x_skew=4), dict(y_skew=2), dict(w_skew=8)):
+        rc, msg = _noalloc(lib, Q4K, b, b, b, 1, 4096, 16, **kw)
+        assert rc == infr_b200.E_INVALID and "misaligned" in msg, kw
+    rc, msg = _noalloc(lib, Q6K, b, b, b, 1, 4096, 16, w_skew=1)
+    assert rc == infr_b200.E_INVALID and "misaligned" in msg
     err = C.create_string_buffer(64)
     assert lib.infr_cuda_gemv_noalloc(Q4K, None, None, None, 1, 4096, 16, None, err, 64) == infr_b200.E_INVALID

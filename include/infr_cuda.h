@@ -168,17 +168,39 @@ typedef struct {
     uint64_t numel;
 } infr_tensor_decl;
 
-#define INFR_OP_LINEAR 1  /* Op::Linear, graph.rs:179-191 */
-#define INFR_OP_MOE_FFN 2 /* Op::MoeFfn, graph.rs:918-1011 */
+#define INFR_OP_LINEAR 1    /* Op::Linear, graph.rs:179-191 */
+#define INFR_OP_MOE_FFN 2   /* Op::MoeFfn, graph.rs:918-1011 */
+#define INFR_OP_RMS_NORM 3  /* Op::RmsNorm, graph.rs:141-148 */
+#define INFR_OP_ROPE 4      /* Op::Rope, graph.rs:268-319 */
+#define INFR_OP_WRITE_KV 5  /* Op::WriteKv, graph.rs:343-349 */
+#define INFR_OP_ATTENTION 6 /* Op::Attention, graph.rs:353-397 */
+#define INFR_OP_GATED_ACT 7 /* Op::GatedAct, graph.rs:707-736 */
+#define INFR_OP_ADD 8       /* Op::Add, graph.rs:753-758 */
+#define INFR_OP_ARGMAX 9    /* Op::Argmax, graph.rs:803-808 */
+#define INFR_OP_COPY 10     /* Op::Copy, graph.rs:890-896 */
 
-/* One op.  Field use per tag:
- *  INFR_OP_LINEAR : t = {x, weight, dst}; u = {m, in_f, out_f, w_off}
- *  INFR_OP_MOE_FFN: t = {x, router_x, router, gate_exps, up_exps, down_exps, dst};
- *                   u = {ne, n_expert, n_used, n_ff_exp, norm_w, fused_gate_up, weight_before,
- *                        act (0 = SiLU), gating (0 = Softmax)}; f = {scale}
- *    Fields of Op::MoeFfn without a slot here (down_scale, swiglu_clamp, ep_band, exp_probs_b,
- *    expert groups, expert_ids) must be None/0 on the Rust side; the binding returns
- *    Error::Unsupported otherwise. */
+/* One op.  Field use per tag, in the field order of the Rust variant (an `Option` field travels as a has_* flag;
+ * where this backend does not run the option the flag must be 0, else compile returns INFR_E_UNSUPPORTED):
+ *  INFR_OP_LINEAR   : t = {x, weight, dst}; u = {m, in_f, out_f, w_off}
+ *  INFR_OP_MOE_FFN  : t = {x, router_x, router, gate_exps, up_exps, down_exps, dst};
+ *                     u = {ne, n_expert, n_used, n_ff_exp, norm_w, fused_gate_up, weight_before,
+ *                          act (0 = SiLU), gating (0 = Softmax)}; f = {scale}
+ *      Fields of Op::MoeFfn without a slot here (down_scale, swiglu_clamp, ep_band, exp_probs_b,
+ *      expert groups, expert_ids) must be None/0 on the Rust side; the binding returns
+ *      Error::Unsupported otherwise.  Banks: Q4_K, router F32.
+ *  INFR_OP_RMS_NORM : t = {x, weight, dst}; u = {rows, dim}; f = {eps}
+ *  INFR_OP_ROPE     : t = {x, positions, dst}; u = {rows, n_head, head_dim, rope_dim, x_stride, neox, backward,
+ *                     has_freq_factors}; f = {theta}          (x_stride 0 or packed; backward, freq_factors: not run)
+ *  INFR_OP_WRITE_KV : t = {src, cache}; u = {rows, row_stride, pos}                       (cache dtype F16)
+ *  INFR_OP_ATTENTION: t = {q, k_cache, v_cache, dst}; u = {rows, kv_len, n_head, n_kv, head_dim, mask (0 = Causal),
+ *                     pos, has_sinks}; f = {scale}            (F16 caches, kv_len = pos + rows, no sinks)
+ *  INFR_OP_GATED_ACT: t = {gate, up, dst}; u = {rows, nff, act (0 = SiLU), up_off, up_stride, gate_stride,
+ *                     gate_block_width, has_swiglu_clamp}     (packed rows, SiLU, no clamp)
+ *  INFR_OP_ADD      : t = {a, b, dst}; u = {n}
+ *  INFR_OP_ARGMAX   : t = {x, dst}; u = {n, rows}             (dst holds u32 ids)
+ *  INFR_OP_COPY     : t = {src, dst}; u = {src_off, dst_off, n}  (element offsets of 4-byte elements)
+ * This is the op list `generate_dense_backend` emits for a Llama-family decode step when the backend advertises
+ * the conservative capability set (crates/infr-llama/src/seam/runner.rs:2641-4493). */
 typedef struct {
     uint32_t tag;
     uint32_t t[8];

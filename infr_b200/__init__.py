@@ -25,7 +25,8 @@ LIB_PATH = os.path.join(_HERE, "libinfr_cuda.so")
 ACT_INT8, ACT_F32 = 0, 1
 TK_INPUT, TK_WEIGHT, TK_INTERNAL, TK_OUTPUT = 0, 1, 2, 3
 USAGE_WEIGHTS, USAGE_ACTIVATIONS, USAGE_KV, USAGE_READBACK = 0, 1, 2, 3
-OP_LINEAR, OP_MOE_FFN = 1, 2
+OP_LINEAR, OP_MOE_FFN, OP_RMS_NORM, OP_ROPE, OP_WRITE_KV, OP_ATTENTION, OP_GATED_ACT, OP_ADD, OP_ARGMAX, OP_COPY = range(1, 11)
+F16, I32 = 1, 3
 E_INVALID, E_UNSUPPORTED, E_OOM, E_CUDA, E_NCCL, E_TIMEOUT = -1, -2, -3, -4, -5, -6
 
 # Every symbol include/infr_cuda.h declares (checked by the CPU test-suite against the built library).
@@ -281,6 +282,43 @@ class Graph:
             op.u[i] = v
         op.f[0] = scale
         self.ops.append(op)
+
+
+    def _op(self, tag, tensors, u=(), f=()):
+        op = _OpDesc()
+        op.tag = tag
+        for i, t in enumerate(tensors):
+            op.t[i] = t
+        for i, v in enumerate(u):
+            op.u[i] = int(v)
+        for i, v in enumerate(f):
+            op.f[i] = float(v)
+        self.ops.append(op)
+
+    # The remaining ops of a dense decode step, field for field with the Rust variants (graph.rs:141-896).
+    def rms_norm(self, x, weight, dst, rows, dim, eps):
+        self._op(OP_RMS_NORM, (x, weight, dst), (rows, dim), (eps,))
+
+    def rope(self, x, positions, dst, rows, n_head, head_dim, rope_dim, theta, neox=False, x_stride=0, backward=False, freq_factors=None):
+        self._op(OP_ROPE, (x, positions, dst), (rows, n_head, head_dim, rope_dim, x_stride, int(neox), int(backward), int(freq_factors is not None)), (theta,))
+
+    def write_kv(self, src, cache, rows, row_stride, pos):
+        self._op(OP_WRITE_KV, (src, cache), (rows, row_stride, pos))
+
+    def attention(self, q, k_cache, v_cache, dst, rows, kv_len, n_head, n_kv, head_dim, scale, pos, mask=0, sinks=None):
+        self._op(OP_ATTENTION, (q, k_cache, v_cache, dst), (rows, kv_len, n_head, n_kv, head_dim, mask, pos, int(sinks is not None)), (scale,))
+
+    def gated_act(self, gate, up, dst, rows, nff, act=0, up_off=0, up_stride=0, gate_stride=0, gate_block_width=0, swiglu_clamp=None):
+        self._op(OP_GATED_ACT, (gate, up, dst), (rows, nff, act, up_off, up_stride, gate_stride, gate_block_width, int(swiglu_clamp is not None)))
+
+    def add(self, a, b, dst, n):
+        self._op(OP_ADD, (a, b, dst), (n,))
+
+    def argmax(self, x, dst, n, rows=1):
+        self._op(OP_ARGMAX, (x, dst), (n, rows))
+
+    def copy(self, src, src_off, dst, dst_off, n):
+        self._op(OP_COPY, (src, dst), (src_off, dst_off, n))
 
 
 class Plan:

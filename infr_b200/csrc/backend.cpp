@@ -94,6 +94,7 @@ CudaBackend::~CudaBackend() {
     if (stream_) cudaStreamSynchronize(stream_);
     if (scratch_) cudaFree(scratch_);
     if (flush_) cudaFree(flush_);
+    for (auto &b : pool_) cudaFree(b.ptr);
     if (status_host_) cudaFreeHost(status_host_);
     if (up_ring_) cudaFreeHost(up_ring_);
     for (cudaEvent_t e : up_ev_)
@@ -415,11 +416,11 @@ Status CudaBackend::write_kv(const float *src, void *cache_at_pos, size_t n) {
 }
 
 Status CudaBackend::rope_write_kv(const infr_attn_desc &d, float theta, int neox, float *q, const float *k, const float *v,
-                                  const int32_t *positions, void *k_cache, void *v_cache) {
+                                  const int32_t *positions, void *k_cache, void *v_cache, int write_pos) {
     cudaSetDevice(device_);
     const uint32_t n_seq = d.n_seq ? d.n_seq : 1;
     Status s = cuda_status(launch_rope_write_kv(q, k, v, positions, k_cache, v_cache, (int)(n_seq * d.rows), (int)d.n_head, (int)d.n_kv,
-                                                (int)d.head_dim, theta, neox, (int)d.rows, (size_t)d.seq_stride, dev_, stream_),
+                                                (int)d.head_dim, theta, neox, (int)d.rows, (size_t)d.seq_stride, dev_, stream_, write_pos),
                            "rope_write_kv");
     if (s.ok()) launches_++;
     return s;
@@ -609,138 +610,6 @@ Status CudaBackend::gemv_block_acc(int dtype, const uint8_t *w, const float *x, 
     s = cuda_status(launch_gemv_q8(dtype, w, a, nullptr, 1, (int)in_f, (int)out_f, acc, dev_, stream_), "gemv_block_acc");
     if (s.ok()) launches_++;
     return s;
-}
-
-// ----------------------------------------------------------------------------------------- graphs
-static size_t dtype_bytes(uint32_t dt, uint64_t numel) {
-    const int be = block_elems((int)dt), bb = block_bytes((int)dt);
-    if (dt == DT_I32) return (size_t)numel * 4;
-    if (!bb) return 0;
-    return (size_t)(numel / (uint64_t)be) * (size_t)bb;
-}
-
-Status CudaBackend::compile(const infr_graph_desc &g, infr_cuda_plan **out) {
-    if ((g.n_tensors && !g.tensors) || (g.n_ops && !g.ops)) return Status::Err(INFR_E_INVALID, "compile: null graph arrays");
-    auto plan = new infr_cuda_plan();
-    plan->tensors.assign(g.tensors, g.tensors + g.n_tensors);
-    plan->ops.assign(g.ops, g.ops + g.n_ops);
-    plan->internal.assign(g.n_tensors, nullptr);
-    plan->internal_bytes.assign(g.n_tensors, 0);
-    auto fail = [&](Status s) {
-        free_plan(plan);
-        return s;
-    };
-    for (uint32_t i = 0; i < g.n_ops; i++) {
-        const infr_op_desc &op = g.ops[i];
-        const int nt = op.tag == INFR_OP_LINEAR ? 3 : (op.tag == INFR_OP_MOE_FFN ? 7 : -1);
-        if (nt < 0) return fail(Status::Err(INFR_E_UNSUPPORTED, fmt("compile: op %u has tag %u; this backend runs Linear and MoeFfn", i, op.tag)));
-        for (int k = 0; k < nt; k++)
-            if (op.t[k] >= g.n_tensors) return fail(Status::Err(INFR_E_INVALID, fmt("compile: op %u names tensor %u of %u", i, op.t[k], g.n_tensors)));
-        if (op.tag == INFR_OP_LINEAR) {
-            const uint32_t in_f = op.u[1], w_off = op.u[3];
-            const infr_tensor_decl &w = g.tensors[op.t[1]];
-            if (w.dtype != DT_Q4K && w.dtype != DT_Q6K && w.dtype != DT_Q2_0)
-                return fail(Status::Err(INFR_E_UNSUPPORTED, fmt("compile: Linear weight dtype code %u", w.dtype)));
-            if (in_f == 0 || w_off % in_f) return fail(Status::Err(INFR_E_INVALID, fmt("compile: Linear w_off=%u is not row-aligned (in_f=%u)", w_off, in_f)));
-            if ((uint64_t)w_off + (uint64_t)op.u[2] * in_f > w.numel)
-                return fail(Status::Err(INFR_E_INVALID, fmt("compile: Linear rows [%u,+%u) leave the %llu-element weight", w_off / in_f, op.u[2], (unsigned long long)w.numel)));
-        } else {
-            // u = {ne, n_expert, n_used, n_ff_exp, norm_w, fused_gate_up, weight_before, act, gating}
-            if (op.u[5] || op.u[6] || op.u[7] || op.u[8])
-                return fail(Status::Err(INFR_E_UNSUPPORTED, "compile: MoeFfn with fused gate/up, weight_before, a non-SiLU activation or non-softmax gating"));
-            if (g.tensors[op.t[2]].dtype != DT_F32)
-                return fail(Status::Err(INFR_E_UNSUPPORTED, "compile: MoeFfn router weights must be F32"));
-            for (int k = 3; k <= 5; k++)
-                if (g.tensors[op.t[k]].dtype != DT_Q4K)
-                    return fail(Status::Err(INFR_E_UNSUPPORTED, "compile: MoeFfn expert banks must be Q4_K"));
-        }
-    }
-    cudaSetDevice(device_);
-    for (uint32_t i = 0; i < g.n_tensors; i++) {
-        if (g.tensors[i].kind != INFR_TK_INTERNAL) continue;
-        const size_t bytes = align_up(dtype_bytes(g.tensors[i].dtype, g.tensors[i].numel), 256);
-        if (!bytes) continue;
-        Status s = cuda_status(cudaMalloc(&plan->internal[i], bytes), "plan scratch cudaMalloc");
-        if (!s.ok()) return fail(s);
-        plan->internal_bytes[i] = bytes;
-    }
-    *out = plan;
-    return Status::Ok();
-}
-
-void CudaBackend::free_plan(infr_cuda_plan *p) {
-    if (!p) return;
-    cudaSetDevice(device_);
-    cudaStreamSynchronize(stream_);
-    for (void *q : p->internal)
-        if (q) cudaFree(q);
-    delete p;
-}
-
-Status CudaBackend::execute(infr_cuda_plan *plan, infr_cuda_buf *const *bindings, uint32_t n) {
-    if (!plan) return Status::Err(INFR_E_INVALID, "execute: null plan");
-    cudaSetDevice(device_);
-    const uint32_t nt = (uint32_t)plan->tensors.size();
-    // Provision: Internal handles are zeroed backend scratch (crates/infr-core/src/exec.rs:53-92).
-    for (uint32_t i = 0; i < nt; i++)
-        if (plan->internal[i]) {
-            Status s = cuda_status(cudaMemsetAsync(plan->internal[i], 0, plan->internal_bytes[i], stream_), "zero internal");
-            if (!s.ok()) return s;
-        }
-    auto resolve = [&](uint32_t id, size_t need, const char *role, DevSpan *out) -> Status {
-        const infr_tensor_decl &d = plan->tensors[id];
-        if (d.kind == INFR_TK_INTERNAL) {
-            *out = DevSpan{static_cast<uint8_t *>(plan->internal[id]), plan->internal_bytes[id]};
-        } else {
-            if (id >= n || !bindings || !bindings[id])
-                return Status::Err(INFR_E_INVALID, fmt("execute: %s handle %u is unbound", role, id));
-            *out = DevSpan{static_cast<uint8_t *>(bindings[id]->ptr), bindings[id]->len};
-        }
-        if (out->bytes < need)
-            return Status::Err(INFR_E_INVALID, fmt("execute: %s handle %u holds %zu bytes, op needs %zu", role, id, out->bytes, need));
-        return Status::Ok();
-    };
-    for (size_t i = 0; i < plan->ops.size(); i++) {
-        const infr_op_desc &op = plan->ops[i];
-        if (op.tag == INFR_OP_LINEAR) {
-            const uint32_t m = op.u[0], in_f = op.u[1], out_f = op.u[2], w_off = op.u[3];
-            const int dt = (int)plan->tensors[op.t[1]].dtype;
-            const size_t bpr = (size_t)(in_f / block_elems(dt)) * block_bytes(dt);
-            const size_t row0 = w_off / in_f;
-            DevSpan x, w, y;
-            Status s;
-            if (!(s = resolve(op.t[0], (size_t)m * in_f * 4, "Linear x", &x)).ok()) return s;
-            if (!(s = resolve(op.t[1], (row0 + out_f) * bpr, "Linear weight", &w)).ok()) return s;
-            if (!(s = resolve(op.t[2], (size_t)m * out_f * 4, "Linear dst", &y)).ok()) return s;
-            s = linear(dt, w.ptr + row0 * bpr, reinterpret_cast<const float *>(x.ptr), reinterpret_cast<float *>(y.ptr), m, in_f,
-                       out_f, reference_ ? INFR_ACT_F32 : INFR_ACT_INT8);
-            if (!s.ok()) return s;
-        } else if (op.tag == INFR_OP_MOE_FFN) {
-            const uint32_t ne = op.u[0], nx = op.u[1], nu = op.u[2], nff = op.u[3];
-            const infr_tensor_decl &xd = plan->tensors[op.t[0]];
-            const uint32_t rows = ne ? (uint32_t)(xd.numel / ne) : 0;
-            const size_t bank_gu = (size_t)nx * nff * (ne / 256) * 144, bank_d = (size_t)nx * ne * (nff / 256) * 144;
-            DevSpan x, rx, r, gt, up, dn, dst;
-            Status s;
-            if (!(s = resolve(op.t[0], (size_t)rows * ne * 4, "MoeFfn x", &x)).ok()) return s;
-            if (!(s = resolve(op.t[1], (size_t)rows * ne * 4, "MoeFfn router_x", &rx)).ok()) return s;
-            if (!(s = resolve(op.t[2], (size_t)nx * ne * 4, "MoeFfn router", &r)).ok()) return s;
-            if (!(s = resolve(op.t[3], bank_gu, "MoeFfn gate_exps", &gt)).ok()) return s;
-            if (!(s = resolve(op.t[4], bank_gu, "MoeFfn up_exps", &up)).ok()) return s;
-            if (!(s = resolve(op.t[5], bank_d, "MoeFfn down_exps", &dn)).ok()) return s;
-            if (!(s = resolve(op.t[6], (size_t)rows * ne * 4, "MoeFfn dst", &dst)).ok()) return s;
-            MoeArgs a{reinterpret_cast<const float *>(x.ptr), reinterpret_cast<const float *>(rx.ptr), reinterpret_cast<const float *>(r.ptr),
-                      gt.ptr, up.ptr, dn.ptr, DT_Q4K, DT_Q4K, DT_Q4K, reinterpret_cast<float *>(dst.ptr), rows, ne, nx, nu, nff, op.f[0],
-                      (int)op.u[4], nullptr, nullptr, nullptr, 0u, nx};
-            s = moe_ffn(a);
-            if (!s.ok()) return s;
-        } else {
-            return Status::Err(INFR_E_UNSUPPORTED, fmt("execute: op %zu tag %u", i, op.tag));
-        }
-    }
-    // Outputs live in their bound device buffers already; the caller's download (or sync) orders
-    // after this stream's work, as Backend::execute + Backend::download do on the other backends.
-    return Status::Ok();
 }
 
 // ------------------------------------------------------------------------------ capture and timing

@@ -24,11 +24,20 @@ struct infr_cuda_buf {
 
 struct infr_cuda_comm;  // comm.cu
 
+// One launch group of a compiled plan: a single op, or neighbouring ops one kernel computes.
+struct PlanStep {
+    enum Kind { kSingle = 0, kAddRmsNorm = 1, kRopeWriteKv = 2 };
+    int kind;
+    uint32_t op0, n_ops;
+};
+
 struct infr_cuda_plan {
     std::vector<infr_tensor_decl> tensors;
     std::vector<infr_op_desc> ops;
-    std::vector<void *> internal;  // device scratch of every Internal handle (null for the others)
+    std::vector<PlanStep> steps;
+    std::vector<void *> internal;  // device scratch of every Internal handle (null for the others), from the context's pool
     std::vector<size_t> internal_bytes;
+    std::vector<char> needs_zero;  // the handle's zero fill is observable (read, or partly written, before a full overwrite)
 };
 
 struct infr_cuda_graph {
@@ -111,8 +120,9 @@ public:
     Status rope(const float *x, const int32_t *positions, float *dst, uint32_t rows, uint32_t n_head, uint32_t head_dim, uint32_t rope_dim,
                 float theta, int neox);
     Status write_kv(const float *src, void *cache_at_pos, size_t n);
+    // write_pos >= 0: cache row = write_pos + row (Op::WriteKv's `pos`); < 0: the row's own position
     Status rope_write_kv(const infr_attn_desc &d, float theta, int neox, float *q, const float *k, const float *v, const int32_t *positions,
-                         void *k_cache, void *v_cache);
+                         void *k_cache, void *v_cache, int write_pos = -1);
     Status attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst, const Q8Dev *q8 = nullptr);
     Status rms_norm_q8(const float *a, const float *b, float *sum_dst, const float *w, uint32_t rows, uint32_t dim, float eps, const Q8Dev &q8);
     Status gated_act_q8(const float *gate, const float *up, uint32_t rows, uint32_t nff, const Q8Dev &q8);
@@ -178,6 +188,16 @@ private:
     int gemv_impl_ = 0;                // 0 = bulk-copy ring kernel, 1 = direct-load kernel
     int mmq_impl_ = 0;                 // 0 = warp-specialised MMQ (f32 within rounding of the CPU), 1 = bit-identical MMQ
     Status check_device_status();
+    // Device blocks behind the Internal handles of compiled plans; a freed plan's blocks are reused by the next
+    // compile (the reference rebuilds its graph every step, so compile must not cost an allocation each time).
+    struct PoolBlock {
+        void *ptr;
+        size_t bytes;
+        bool in_use;
+    };
+    std::vector<PoolBlock> pool_;
+    Status pool_acquire(size_t bytes, void **out);
+    void pool_release(void *p);
 };
 
 }  // namespace infr

@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(256) rope_kernel(const float *__restrict__ x, 
 __global__ void __launch_bounds__(256) rope_write_kv_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                                             const int32_t *__restrict__ positions, __half *__restrict__ k_cache,
                                                             __half *__restrict__ v_cache, int rows, int n_head, int n_kv, int head_dim,
-                                                            float theta, int neox, int rows_per_seq, size_t seq_stride) {
+                                                            float theta, int neox, int rows_per_seq, size_t seq_stride, int write_pos) {
     pdl_go();
     pdl_wait();
     const int hf = head_dim / 2;
@@ -164,7 +164,9 @@ __global__ void __launch_bounds__(256) rope_write_kv_kernel(float *__restrict__ 
             const size_t rh = t / hf;  // row * n_kv + head
             const int r = (int)(rh / n_kv), h = (int)(rh % n_kv);
             const size_t b = rh * head_dim;
-            const size_t cb = (size_t)(r / rows_per_seq) * seq_stride + ((size_t)positions[r] * n_kv + h) * head_dim;
+            // cache row: the op's own `pos` + row when the caller gives one (Op::WriteKv), else the row's position
+            const size_t crow = write_pos >= 0 ? (size_t)(write_pos + r % rows_per_seq) : (size_t)positions[r];
+            const size_t cb = (size_t)(r / rows_per_seq) * seq_stride + (crow * n_kv + h) * head_dim;
             if (is_v) {
                 v_cache[cb + 2 * p] = __float2half_rn(v[b + 2 * p]);
                 v_cache[cb + 2 * p + 1] = __float2half_rn(v[b + 2 * p + 1]);
@@ -699,11 +701,11 @@ cudaError_t launch_rope(const float *x, const int32_t *positions, float *dst, in
 
 cudaError_t launch_rope_write_kv(float *q, const float *k, const float *v, const int32_t *positions, void *k_cache, void *v_cache, int rows,
                                  int n_head, int n_kv, int head_dim, float theta, int neox, int rows_per_seq, size_t seq_stride,
-                                 const DeviceInfo &dev, cudaStream_t st) {
+                                 const DeviceInfo &dev, cudaStream_t st, int write_pos) {
     if (rows <= 0 || n_head <= 0 || n_kv <= 0 || head_dim <= 0 || (head_dim & 1) || rows_per_seq <= 0) return cudaErrorInvalidValue;
     const size_t total = (size_t)rows * (n_head + 2 * n_kv) * (head_dim / 2);
     return launch_pdl(rope_write_kv_kernel, dim3(grid_for(total, 256, dev)), dim3(256), 0, st, q, k, v, positions, (__half *)k_cache,
-                      (__half *)v_cache, rows, n_head, n_kv, head_dim, theta, neox, rows_per_seq, seq_stride);
+                      (__half *)v_cache, rows, n_head, n_kv, head_dim, theta, neox, rows_per_seq, seq_stride, write_pos);
 }
 
 cudaError_t launch_write_kv_f16(const float *src, void *cache_at_pos, size_t n, const DeviceInfo &dev, cudaStream_t st) {

@@ -116,7 +116,7 @@ cudaError_t launch_rope(const float *x, const int32_t *positions, float *dst, in
                         int neox, const DeviceInfo &dev, cudaStream_t st);
 cudaError_t launch_rope_write_kv(float *q, const float *k, const float *v, const int32_t *positions, void *k_cache, void *v_cache, int rows,
                                  int n_head, int n_kv, int head_dim, float theta, int neox, int rows_per_seq, size_t seq_stride,
-                                 const DeviceInfo &dev, cudaStream_t st);
+                                 const DeviceInfo &dev, cudaStream_t st, int write_pos = -1);
 cudaError_t launch_write_kv_f16(const float *src, void *cache_at_pos, size_t n, const DeviceInfo &dev, cudaStream_t st);
 size_t attention_workspace_bytes(int q_rows, int n_head, int head_dim, int max_keys);
 // With qs != nullptr the merged rows are quantised (256-element blocks) instead of stored to dst.

@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
             // softmax sum).  The CPU's stable sort leaves such a row in index order, so take the lowest expert
             // not selected yet; its NaN weight travels on as it does there.
             for (int e = lane; e < n_expert; e += 32)
-                if (p[e] != -1.0f) {
+                if (p[e] != -INFINITY) {
                     bi = e;
                     break;
                 }
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
             myw = best;
             myid = bi < n_expert ? bi : 0;
         }
-        if (lane == 0 && bi < n_expert) p[bi] = -1.0f;  // probabilities are >= 0: never selected again
+        if (lane == 0 && bi < n_expert) p[bi] = -INFINITY;  // never compares greater than the running best again
         __syncwarp();
     }
     wsum = fmaxf(wsum, 1e-20f);

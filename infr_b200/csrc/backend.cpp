@@ -384,9 +384,6 @@ Status CudaBackend::gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *
     if (dtype == DT_Q6K && !a.sums16) return Status::Err(INFR_E_INVALID, "gemv_q8: Q6_K needs the per-16 sums");
     cudaSetDevice(device_);
     Status s = cuda_status(gemv_impl_ == 1   ? launch_gemv_q8(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, nullptr, dev_, stream_)
-                           : gemv_impl_ == 2 ? launch_gemv_stream(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_, 1)
-                           : (gemv_impl_ >= 3 && dtype == DT_Q4K && m == 1)
-                               ? launch_gemv_q4k_rows(w, a, y, (int)in_f, (int)out_f, gemv_impl_ - 3, dev_, status_dev_, stream_)
                            : (dtype == DT_Q4K && gemv_impl_ == 0)
                                ? launch_gemv_q4k_mma(w, &a, nullptr, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_)
                                : launch_gemv_stream(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_),

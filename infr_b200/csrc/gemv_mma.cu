@@ -63,10 +63,11 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
     }
     return false;
 }
-// Tiled TMA load of one box: x = word offset inside the row (a multiple of 4 -> 16-byte aligned), y = row.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-                 "l"(map), "r"(x), "r"(y), "r"(bar)
+// Tiled TMA load of one box: x = word offset inside the row (a multiple of 4 -> 16-byte aligned), y = row; `policy` is
+// an L2 eviction-priority hint.
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar), "l"(policy)
                  : "memory");
 }
 // D = A(16x32, u8) * B(32x8, s8), int32, zero accumulator input.
@@ -85,6 +86,7 @@ __device__ __forceinline__ void k4_all(uint32_t y, uint32_t z, uint32_t w, uint3
     sc[1] = (w & 0x0F0F0F0Fu) | ((y >> 2) & 0x30303030u);
     mn[1] = ((w >> 4) & 0x0F0F0F0Fu) | ((z >> 2) & 0x30303030u);
 }
+
 
 struct MmaGeom {
     int nb;         // super-blocks per row
@@ -159,6 +161,10 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
     uint8_t *ring = rings + (size_t)warp * S * kSlotBytes;
     uint64_t *wbar = bars + warp * kMaxSlotsMma;
 
+    // Weights are read once per launch: evict-first keeps them from pushing the activations (a few kilobytes that
+    // every CTA of every launch reads) out of L2.
+    uint64_t l2_policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(l2_policy));
     // ---- issue side: one elected lane fetches the 16-row x K-step box of the slot ----
     int j_issue = 0, i_tile = 0, i_step = 0;
     auto issue = [&](int slot) {
@@ -169,7 +175,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
             // order this warp's earlier reads of the slot before the engine overwrites it
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             bar_expect_tx(bar, (uint32_t)kSlotBytes);
-            tma_load_2d(s_u32(ring + (size_t)slot * kSlotBytes), &tmap, blk0 * 36, row_base + r_begin + i_tile * kTileRows, bar);
+            tma_load_2d_hint(s_u32(ring + (size_t)slot * kSlotBytes), &tmap, blk0 * 36, row_base + r_begin + i_tile * kTileRows, bar, l2_policy);
         }
         __syncwarp();
         j_issue++;
@@ -226,19 +232,44 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
         }
     } else {
         if (M == 1) {
-            // one row: a plain strided copy (the batched form below costs a barrier more than it saves here)
+            // One row.  Every global load of a thread is issued before its first shared-memory store (the compiler
+            // may not move a load of a generic pointer across such a store), so the staging costs one round trip to
+            // L2 instead of one per loop.
             const size_t ar = (size_t)(grp.pair_row ? grp.pair_row[p0] : p0);
-            for (int u = threadIdx.x; u < in_f / 8; u += kThreadsMma) {
-                const uint2 v = *reinterpret_cast<const uint2 *>(a.qs + ar * in_f + (size_t)u * 8);
-                const int b = u >> 5, uu = u & 31, s = uu >> 2, tt = uu & 3;
-                *reinterpret_cast<uint2 *>(s_codes + (size_t)b * kStagedBytes + tt * kLaneBytes + s * 8) = v;
+            const int units = in_f / 8;
+            const int8_t *qrow = a.qs + ar * in_f;
+            const int32_t *srow = a.sums + ar * nb * 8;
+            const float *drow = a.d + ar * nb;
+            const int tid = threadIdx.x;
+            const int sum0 = tid < nb * 8 ? srow[tid] : 0;
+            const float d0 = tid < nb ? drow[tid] : 0.f;
+            for (int u0 = tid; u0 < units; u0 += 4 * kThreadsMma) {
+                uint2 v[4];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const int u = u0 + k * kThreadsMma;
+                    v[k] = make_uint2(0, 0);
+                    if (u < units) v[k] = *reinterpret_cast<const uint2 *>(qrow + (size_t)u * 8);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const int u = u0 + k * kThreadsMma;
+                    const int b = u >> 5, uu = u & 31, s = uu >> 2, tt = uu & 3;
+                    if (u < units) *reinterpret_cast<uint2 *>(s_codes + (size_t)b * kStagedBytes + tt * kLaneBytes + s * 8) = v[k];
+                }
             }
-            for (int r = threadIdx.x; r < nb * 8; r += kThreadsMma) {
-                const int b = r >> 3, s = r & 7, sum = a.sums[ar * nb * 8 + r];
+            if (tid < nb * 8) {
+                const int b = tid >> 3, s = tid & 7;
+                s_bsplit[(size_t)b * 16 + s] = (uint8_t)(sum0 & 63);
+                s_bsplit[(size_t)b * 16 + 8 + s] = (uint8_t)(int8_t)(sum0 >> 6);
+            }
+            if (tid < nb) s_d8[tid * 8] = d0;
+            for (int r = tid + kThreadsMma; r < nb * 8; r += kThreadsMma) {
+                const int b = r >> 3, s = r & 7, sum = srow[r];
                 s_bsplit[(size_t)b * 16 + s] = (uint8_t)(sum & 63);
                 s_bsplit[(size_t)b * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
             }
-            for (int b = threadIdx.x; b < nb; b += kThreadsMma) s_d8[b * 8] = a.d[ar * nb + b];
+            for (int b = tid + kThreadsMma; b < nb; b += kThreadsMma) s_d8[b * 8] = drow[b];
         } else {
         // activation row of column n: the item's n-th pair (gathered through pair_row when given)
         __shared__ uint32_t s_row[8];
@@ -429,10 +460,17 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
     const size_t budget = (size_t)dev.max_smem_optin / per_sm - (per_sm > 1 ? 2048 : 1024);
     int slots = (int)((budget - fixed) / per_slot);
     if (slots > kMaxSlotsMma) slots = kMaxSlotsMma;
-    geo.slots = slots;
-    const size_t smem = fixed + (size_t)slots * per_slot;
     int grid = (out_f + kTileRows - 1) / kTileRows;
     if (grid > dev.sm_count * per_sm) grid = dev.sm_count * per_sm;
+    if (!grp.item_expert) {
+        // no more ring slots than a warp has jobs: what a small matrix leaves of the SM's shared memory lets the
+        // next kernel of the stream become resident, and prefetch its weights, while this one computes
+        const int tiles = (out_f + kTileRows - 1) / kTileRows, tiles_cta = (tiles + grid - 1) / grid;
+        const int jobs = tiles_cta * ((geo.bpw + SB - 1) / SB);
+        if (slots > jobs) slots = jobs < 1 ? 1 : jobs;
+    }
+    geo.slots = slots;
+    const size_t smem = fixed + (size_t)slots * per_slot;
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return cudaErrorNotSupported;
     CUtensorMap tmap;

@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(kStreamThreads, (M <= 2 ? 2 : 1))
 
 template <int DT, int M>
 cudaError_t launch_stream_dt(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
-                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st, bool half_sm) {
+                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
     using F = Fmt<DT>;
     StreamGeom geo;
     geo.nb = in_f / F::kBlockElems;
@@ -391,19 +391,13 @@ cudaError_t launch_stream_dt(const uint8_t *w, const Q8Dev &a, float *y, int m, 
     // Two resident CTAs per SM when they fit with at least 2 ring slots per warp.
     const size_t half = (size_t)dev.max_smem_optin / 2 - 2048;
     int per_sm = (M <= 2 && fixed + 2 * per_slot <= half) ? 2 : 1;
-    // half_sm: one CTA per SM that takes at most half of the SM (shared memory, threads, registers), so that the
-    // NEXT kernel of the stream, started early by programmatic dependent launch, is resident beside this one and
-    // has its own first weights in flight while this one is still computing.
-    const bool leave_half = half_sm && per_sm == 2;
-    if (leave_half) per_sm = 1;
-    const size_t budget = (per_sm == 2 || leave_half) ? half : (size_t)dev.max_smem_optin - 1024;
+    const size_t budget = per_sm == 2 ? half : (size_t)dev.max_smem_optin - 1024;
     int slots = (int)((budget - fixed) / per_slot);
     if (slots > kMaxSlots) slots = kMaxSlots;
     geo.slots = slots;
     const size_t smem = (size_t)slots * per_slot + fixed;
     int grid = (out_f + kStreamWarps - 1) / kStreamWarps;
     if (grid > dev.sm_count * per_sm) grid = dev.sm_count * per_sm;
-    if (leave_half) grid = out_f < dev.sm_count ? out_f : dev.sm_count;
     auto kernel = gemv_stream_kernel<DT, M>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -422,22 +416,17 @@ cudaError_t launch_stream_dt(const uint8_t *w, const Q8Dev &a, float *y, int m, 
 
 template <int M>
 cudaError_t launch_stream_m(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
-                            const DeviceInfo &dev, uint32_t *status, cudaStream_t st, bool half_sm) {
-    if (dt == DT_Q4K) return launch_stream_dt<DT_Q4K, M>(w, a, y, m, in_f, out_f, dev, status, st, half_sm);
-    if (dt == DT_Q6K) return launch_stream_dt<DT_Q6K, M>(w, a, y, m, in_f, out_f, dev, status, st, half_sm);
-    return launch_stream_dt<DT_Q2_0, M>(w, a, y, m, in_f, out_f, dev, status, st, half_sm);
+                            const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+    if (dt == DT_Q4K) return launch_stream_dt<DT_Q4K, M>(w, a, y, m, in_f, out_f, dev, status, st);
+    if (dt == DT_Q6K) return launch_stream_dt<DT_Q6K, M>(w, a, y, m, in_f, out_f, dev, status, st);
+    return launch_stream_dt<DT_Q2_0, M>(w, a, y, m, in_f, out_f, dev, status, st);
 }
 
 }  // namespace
 
 cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
-                               const DeviceInfo &dev, uint32_t *status, cudaStream_t st, int variant) {
+                               const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
     if (m < 1 || m > 8 || (dt != DT_Q4K && dt != DT_Q6K && dt != DT_Q2_0)) return cudaErrorInvalidValue;
-    const bool half_sm = variant == 1;
-    if (variant == 1 && m <= 2) {
-        if (m == 1) return launch_stream_m<1>(dt, w, a, y, m, in_f, out_f, dev, status, st, true);
-        return launch_stream_m<2>(dt, w, a, y, m, in_f, out_f, dev, status, st, true);
-    }
     if (dt == DT_Q2_0 && m > 1 && in_f % 512 == 0 && a.gran == 32) {
         // batches on rows of whole 512-element chunks take the matrix-unit kernel (1.6x faster at m = 4 and 8,
         // no gain at m = 1); it declines shapes whose staged activations do not fit, and those fall through
@@ -452,10 +441,10 @@ cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *
         if (e != cudaErrorInvalidValue) return e;
         cudaGetLastError();
     }
-    if (m == 1) return launch_stream_m<1>(dt, w, a, y, m, in_f, out_f, dev, status, st, half_sm);
-    if (m == 2) return launch_stream_m<2>(dt, w, a, y, m, in_f, out_f, dev, status, st, half_sm);
-    if (m <= 4) return launch_stream_m<4>(dt, w, a, y, m, in_f, out_f, dev, status, st, half_sm);
-    return launch_stream_m<8>(dt, w, a, y, m, in_f, out_f, dev, status, st, half_sm);
+    if (m == 1) return launch_stream_m<1>(dt, w, a, y, m, in_f, out_f, dev, status, st);
+    if (m == 2) return launch_stream_m<2>(dt, w, a, y, m, in_f, out_f, dev, status, st);
+    if (m <= 4) return launch_stream_m<4>(dt, w, a, y, m, in_f, out_f, dev, status, st);
+    return launch_stream_m<8>(dt, w, a, y, m, in_f, out_f, dev, status, st);
 }
 
 }  // namespace infr

@@ -47,7 +47,7 @@ cudaError_t launch_gemv_q8(int dt, const uint8_t *w, const Q8Dev &a, float *y, i
 // Same contract as launch_gemv_q8 without the accumulator dump: the bulk-copy ring kernel.  `status`
 // is a device-visible word the kernel sets non-zero if a bounded wait expires.
 cudaError_t launch_gemv_stream(int dt, const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f,
-                               const DeviceInfo &dev, uint32_t *status, cudaStream_t st, int variant = 0);
+                               const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
 // Q2_0, m <= 8, rows of whole 512-element chunks, on the warp-level int8 matrix unit (activations quantised
 // per 32).  cudaErrorInvalidValue = shape not taken (the caller uses the byte-dot kernel).
 cudaError_t launch_gemv_q2_mma(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f, const DeviceInfo &dev,
@@ -60,10 +60,6 @@ cudaError_t launch_gemv_q6_mma(const uint8_t *w, const Q8Dev &a, float *y, int m
 // (f32 rows, quantised inside the kernel) is non-null.
 cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,
                                 const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
-// Q4_K, one pre-quantised activation row: contiguous row ranges streamed by 1-D bulk copies into less than half an SM,
-// K split over the warps, activations in registers (gemv_rows.cu).  mode 0 / 1 / 2: see the definition.
-cudaError_t launch_gemv_q4k_rows(const uint8_t *w, const Q8Dev &a, float *y, int in_f, int out_f, int mode, const DeviceInfo &dev,
-                                 uint32_t *status, cudaStream_t st);
 // y[m,out_f] (m <= 8) from f32 activations and dequantised weights.
 cudaError_t launch_gemv_f32(int dt, const uint8_t *w, const float *x, float *y, int m, int in_f, int out_f,
                             const DeviceInfo &dev, cudaStream_t st);

@@ -203,7 +203,19 @@ def _gemv_case(be, infr_b200, dtype, out_f, in_f, m, seed, steps, warmup, l2_byt
     return res
 
 
-def _mmq_case(be, infr_b200, m, in_f, out_f, seed, steps, warmup):
+def _int8_peak(be):
+    """Dense int8 tensor-core peak of this GPU, measured: tcgen05 kind::i8 128x256x32 instructions on operands resident
+    in shared memory, two issuing threads per SM, no unpack and no epilogue (infr_cuda_tensor_peak_i8, which also
+    checks one accumulator element per issuer).  `burst` is a few milliseconds (what a kernel timed alone sees),
+    `sustained` is > 100 ms under the power cap."""
+    ms_b, ops_b = be.tensor_peak_i8(n_batches=64, launches=10)
+    ms_s, ops_s = be.tensor_peak_i8(n_batches=256, launches=100)
+    return {"burst_tops": ops_b / (ms_b * 1e-3) / 1e12, "burst_ms": ms_b,
+            "sustained_tops": ops_s / (ms_s * 1e-3) / 1e12, "sustained_ms": ms_s, "spec_tops": 4500.0,
+            "how": "tcgen05.mma kind::i8 M=128 N=256 K=32 from resident shared-memory operands, 2 issuers per SM, CUDA events"}
+
+
+def _mmq_case(be, infr_b200, m, in_f, out_f, seed, steps, warmup, peak=None):
     """Prefill MMQ (Linear with m > 8): int8 TOPS = 2*m*in_f*out_f / time; the activation quantiser is inside."""
     from infr_b200 import synth
 
@@ -219,15 +231,21 @@ def _mmq_case(be, infr_b200, m, in_f, out_f, seed, steps, warmup):
         be.linear(infr_b200.Q4K, wb, xb, yb, m, in_f, out_f)
     ms = be.timer_stop()
     ops = 2.0 * m * in_f * out_f
+    tops = ops * steps / (ms * 1e-3) / 1e12
     res = {"workload": f"prefill MMQ q4_k M={m} K={in_f} N={out_f} (quantise + tcgen05 kind::i8 GEMM)",
-           "int8_ops": ops, "us": ms * 1e3 / steps, "tops": ops * steps / (ms * 1e-3) / 1e12,
-           "frac_of_4500_tops_spec": ops * steps / (ms * 1e-3) / 1e12 / 4500.0}
+           "int8_ops": ops, "us": ms * 1e3 / steps, "tops": tops, "frac_of_4500_tops_spec": tops / 4500.0}
+    if peak:
+        # algorithmic ops 2*M*K*N; the kernel issues twice that on the tensor cores (the 6-bit sub-block scale is
+        # split into two int8 operands so that the int32 block sums stay exact) plus the tf32 min term
+        res["roofline"] = {"bound": "int8", "achieved": tops, "peak": peak["burst_tops"], "unit": "TOPS", "frac": tops / peak["burst_tops"],
+                           "peak_source": "measured (infr_cuda_tensor_peak_i8, burst)", "peak_spec": 4500.0,
+                           "alg_ops_per_launch": ops, "kernel": "quantize_q8 + mmq_ws_prep + mmq_ws_kernel"}
     for b in (wb, xb, yb):
         b.close()
     return res
 
 
-def _moe_case(be, infr_b200, steps, warmup):
+def _moe_case(be, infr_b200, steps, warmup, hbm_peak=None):
     """Qwen3-30B-A3B-shaped MoE layer: 256 tokens, hidden 2048, 128 experts (gate/up 2048->768, down 768->2048,
     Q4_K), softmax top-8.  Bank bytes are random valid Q4_K blocks (timing does not depend on the values)."""
     from infr_b200 import synth
@@ -252,6 +270,11 @@ def _moe_case(be, infr_b200, steps, warmup):
     res = {"workload": "MoE layer 256 tok x hidden 2048, 128 experts x (2048->768->2048) Q4_K, softmax top-8 (9 kernels)",
            "us": ms * 1e3 / steps, "weight_bytes": w_bytes, "weights_gbs": w_bytes * steps / (ms * 1e-3) / 1e9,
            "int8_tops": ops * steps / (ms * 1e-3) / 1e12, "l2": "weights 340 MB > L2"}
+    if hbm_peak:
+        alg = w_bytes + 2 * rows * ne * 4  # every expert is hit with 2048 routed pairs: all banks once, x in, y out
+        gbs = alg * steps / (ms * 1e-3) / 1e9
+        res["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+                           "alg_bytes_per_layer": alg, "peak_source": "measured HBM copy bandwidth"}
     for b in (gate, up, down, router, x, dst):
         b.close()
     return res
@@ -384,6 +407,9 @@ def _decode_step_case(be, infr_b200, batch, steps, warmup, hbm_peak, pos=4096):
                        f"{n_ops} ops in one CUDA graph",
            "us_per_step": us, "tok_per_s": batch / (us * 1e-6), "weight_bytes": w_bytes, "kv_bytes_read": kv_bytes,
            "hbm_gbs": alg / (us * 1e-6) / 1e9, "frac_of_measured_hbm": alg / (us * 1e-6) / 1e9 / hbm_peak,
+           "roofline": {"bound": "hbm", "achieved": alg / (us * 1e-6) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                        "frac": alg / (us * 1e-6) / 1e9 / hbm_peak, "alg_bytes_per_step": alg,
+                        "peak_source": "measured HBM copy bandwidth (sustained over the step)"},
            "kernels_per_step": kernels, "tokens_same_eager_and_graph": bool((tok == tok_eager).all()),
            "first_token_ids": [int(t) for t in tok[:4]]}
     graph.close()
@@ -435,6 +461,7 @@ def _tp_decode(be, infr_b200, dist, rank, world, local, steps, warmup):
         handles = [None] * N
         dist.all_gather_object(handles, comm.export())
         comm.connect(handles)
+        _barrier(dist)  # every rank is connected before the first exchange
         # same sums as NCCL on random data before it is trusted with the timing
         probe = torch.randn(h, **f32)
         ref = probe.clone()
@@ -516,6 +543,7 @@ def _tp_decode(be, infr_b200, dist, rank, world, local, steps, warmup):
     us_nccl = timed(False)[0] if N > 1 else None
     us_none = timed(None)[0] if N > 1 else None  # the ranks' Linears alone (no exchange: not a valid step, a floor)
     be.sync()  # a bounded wait that expired in the exchange surfaces here
+    _barrier(dist)  # every rank has synchronised its last exchange before any rank frees its staging
     if comm is not None:
         comm.close()
     for v in list(b.values()) + list(masters.values()) + [head] + [x for L in layers for x in L.values()]:
@@ -533,10 +561,14 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
     attention by KV head on the rank's own slice of the KV cache, gate/up by FFN slice, o and down by input columns
     with an all-reduce of the [batch, 4096] result after each (the library's peer-memory kernel while it fits its
     64 K-float limit, NCCL otherwise), norms and the residual stream replicated, the head by vocabulary slice with one
-    NCCL all-gather of the logits.  One CUDA graph on the backend's stream.  Strong scaling: one model on N GPUs."""
+    NCCL all-gather of the logits.  One CUDA graph on the backend's stream.  Strong scaling: one model on N GPUs.
+
+    Every rank builds the SAME seeded model on the host and uploads its shard of it (rows of q/k/v/gate/up/head,
+    input columns of o/down, its KV heads' columns of the caches).  Before anything is timed, rank 0 also runs the
+    unsharded step on its own GPU and the gathered logits of the sharded step are compared with it."""
     import numpy as np
     import torch
-    from infr_b200 import synth
+    from infr_b200 import shard, synth
     from infr_b200.decode import DecodeStep, LlamaShape
 
     Q4K = infr_b200.Q4K
@@ -545,33 +577,66 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
     full = LlamaShape()
     s = LlamaShape(n_head=full.n_head // N, n_kv=full.n_kv // N, ffn=full.ffn // N, vocab=full.vocab // N)
     max_ctx = pos + 8
-    masters = {name: be.from_numpy(synth.random_blocks(dt, o * i, 300 + k + 16 * rank), infr_b200.USAGE_WEIGHTS)
-               for k, (name, dt, o, i) in enumerate(s.linears())}
-    norm = be.from_numpy((1.0 + 0.02 * synth.normal(40, (s.hidden,))).astype(np.float32))
-    layers, owned, w_bytes = [], [], 0
-    for _ in range(s.n_layer):
-        L = {"attn_norm": norm, "ffn_norm": norm}
-        for name, dt, o, i in s.linears():
-            nbytes = o * i // synth.BLOCK_ELEMS[dt] * synth.BLOCK_BYTES[dt]
-            b_ = be.alloc_uninit(nbytes, infr_b200.USAGE_WEIGHTS)
-            be.copy_buffer(masters[name], b_, nbytes)
-            L[name] = b_
-            owned.append(b_)
-            w_bytes += nbytes
-        layers.append(L)
-    head = be.from_numpy(synth.random_blocks(Q4K, s.vocab * s.hidden, 399 + rank), infr_b200.USAGE_WEIGHTS)
-    w_bytes += s.vocab * s.hidden // 256 * 144
-    seq_bytes = max_ctx * s.kv_dim * 2
-    kv_master = be.from_numpy(synth.normal(9 + rank, (max_ctx, s.kv_dim)).astype(np.float16).view(np.uint16))
-    kc, vc = [], []
-    for _ in range(s.n_layer):
-        for lst in (kc, vc):
-            c = be.alloc_uninit(batch * seq_bytes, infr_b200.USAGE_ACTIVATIONS)
-            for q in range(batch):
-                view = be.wrap(c.device_ptr() + q * seq_bytes, seq_bytes, infr_b200.USAGE_ACTIVATIONS)
-                be.copy_buffer(kv_master, view, seq_bytes)
-                view.close()
-            lst.append(c)
+    row_parallel = {"wo", "down"}  # input columns split, partial sums all-reduced
+    host_full = {name: synth.random_blocks(dt, o * i, 300 + k) for k, (name, dt, o, i) in enumerate(full.linears())}
+    host_head = synth.random_blocks(Q4K, full.vocab * full.hidden, 399)
+    norm_h = (1.0 + 0.02 * synth.normal(40, (full.hidden,))).astype(np.float32)
+    kv_full = synth.normal(9, (max_ctx, full.kv_dim)).astype(np.float16).view(np.uint16)
+    hidden_h = synth.normal(31, (batch, full.hidden))
+
+    def build(shape, n_ranks, r):
+        """Device buffers of rank r's share of the model split n_ranks ways (n_ranks = 1: the whole model)."""
+        masters = {}
+        for name, dt, o, i in full.linears():
+            if name in row_parallel:
+                w, _, _ = shard.col_shard(dt, host_full[name], o, i, r, n_ranks, unit=256)
+            else:
+                w, _, _ = shard.row_shard(dt, host_full[name], o, i, r, n_ranks)
+            masters[name] = be.from_numpy(w, infr_b200.USAGE_WEIGHTS)
+        norm = be.from_numpy(norm_h)
+        layers, owned, w_bytes = [], [], 0
+        for _ in range(shape.n_layer):
+            L = {"attn_norm": norm, "ffn_norm": norm}
+            for name, dt, o, i in shape.linears():
+                nbytes = o * i // synth.BLOCK_ELEMS[dt] * synth.BLOCK_BYTES[dt]
+                b_ = be.alloc_uninit(nbytes, infr_b200.USAGE_WEIGHTS)
+                be.copy_buffer(masters[name], b_, nbytes)
+                L[name] = b_
+                owned.append(b_)
+                w_bytes += nbytes
+            layers.append(L)
+        hw, _, _ = shard.row_shard(Q4K, host_head, full.vocab, full.hidden, r, n_ranks)
+        head = be.from_numpy(hw, infr_b200.USAGE_WEIGHTS)
+        w_bytes += hw.nbytes
+        kvd = shape.kv_dim
+        kv_master = be.from_numpy(np.ascontiguousarray(kv_full[:, r * kvd:(r + 1) * kvd]))
+        seq_bytes = max_ctx * kvd * 2
+        kc, vc = [], []
+        for _ in range(shape.n_layer):
+            for lst in (kc, vc):
+                c = be.alloc_uninit(batch * seq_bytes, infr_b200.USAGE_ACTIVATIONS)
+                for q in range(batch):
+                    view = be.wrap(c.device_ptr() + q * seq_bytes, seq_bytes, infr_b200.USAGE_ACTIVATIONS)
+                    be.copy_buffer(kv_master, view, seq_bytes)
+                    view.close()
+                lst.append(c)
+        be.sync()
+        return dict(layers=layers, owned=owned + kc + vc + [head, kv_master, norm] + list(masters.values()), head=head, norm=norm, kc=kc, vc=vc,
+                    w_bytes=w_bytes)
+
+    # ---- the unsharded step on rank 0 (eager, once): the result the sharded step has to reproduce ----
+    ref_logits = None
+    if N > 1 and rank == 0:
+        m1 = build(full, 1, 0)
+        st1 = DecodeStep(be, full, batch, max_ctx, m1["layers"], m1["norm"], m1["head"], Q4K, m1["kc"], m1["vc"])
+        st1.set_inputs(hidden_h, pos)
+        st1.run(pos, fused=True)
+        ref_logits = be.download(st1.logits, np.float32).reshape(batch, full.vocab)
+        for b_ in m1["owned"]:
+            b_.close()
+        del st1, m1
+
+    mine = build(s, N, rank)
     f32 = dict(device=dev, dtype=torch.float32)
     sub_t = torch.zeros(batch * s.hidden, **f32)
     gathered = torch.empty(batch * s.vocab * N, **f32)
@@ -584,15 +649,17 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
         handles = [None] * N
         dist.all_gather_object(handles, comm.export())
         comm.connect(handles)
+        _barrier(dist)  # every rank is connected before the first exchange
     if N == 1:
         reduce = None
     elif comm is not None:
         reduce = lambda buf, n: be.all_reduce(comm, buf, n)
     else:
         reduce = lambda buf, n: dist.all_reduce(sub_t)
-    step = DecodeStep(be, s, batch, max_ctx, layers, norm, head, Q4K, kc, vc, sub=sub, reduce=reduce, argmax=N == 1)
-    hidden0 = be.from_numpy(synth.normal(31, (batch, s.hidden)))
-    step.set_inputs(synth.normal(31, (batch, s.hidden)), pos)
+    step = DecodeStep(be, s, batch, max_ctx, mine["layers"], mine["norm"], mine["head"], Q4K, mine["kc"], mine["vc"], sub=sub, reduce=reduce,
+                      argmax=N == 1)
+    hidden0 = be.from_numpy(hidden_h)
+    step.set_inputs(hidden_h, pos)
     logits_t = None
     if N > 1:  # the rank's logits slice as a torch tensor for the all-gather: copy through a wrapped view
         logits_t = torch.empty(batch * s.vocab, **f32)
@@ -609,10 +676,19 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
 
     ext = torch.cuda.ExternalStream(be.stream(), device=dev)
     mode = "cuda graph"
+    parity = None
     with torch.cuda.stream(ext):
         for _ in range(2):
             n_ops = one()  # sizes the context's scratch before capture
         ext.synchronize()
+        if N > 1 and rank == 0:
+            # gathered is [rank][row][vocab / N]: rank r holds vocabulary rows [r * vocab / N, (r + 1) * vocab / N)
+            got = gathered.cpu().numpy().reshape(N, batch, s.vocab).transpose(1, 0, 2).reshape(batch, full.vocab)
+            rel = float(np.linalg.norm(got - ref_logits) / np.linalg.norm(ref_logits))
+            parity = {"vs": "the unsharded step on one GPU, same seeded model", "logits_rel_l2": rel,
+                      "max_abs_diff": float(np.abs(got - ref_logits).max()),
+                      "same_argmax": bool((got.argmax(axis=1) == ref_logits.argmax(axis=1)).all()), "bar_rel_l2": 1e-3}
+            assert rel < 1e-3 and parity["same_argmax"], f"tensor-parallel step differs from the single-GPU step: {parity}"
         graph = None
         try:
             graph = torch.cuda.CUDAGraph()
@@ -635,16 +711,16 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
         del graph
     us = _max_over_ranks(dist, ms) * 1e3 / steps
     be.sync()
-    finite = bool(torch.isfinite(gathered).all().item()) if N > 1 else True
+    _barrier(dist)  # every rank has synchronised its last exchange before any rank frees its staging
     if comm is not None:
         comm.close()
-    for b_ in owned + kc + vc + [head, kv_master, hidden0, norm, sub] + list(masters.values()):
+    for b_ in mine["owned"] + [hidden0, sub]:
         b_.close()
     return {"workload": f"tensor-parallel 8B-shape decode step, batch {batch}, KV context {pos}, {N} GPU(s): heads, FFN and vocabulary "
-                        f"split over the ranks ({w_bytes / 1e9:.2f} GB of weights per rank), {2 * s.n_layer if N > 1 else 0} all-reduces of "
+                        f"split over the ranks ({mine['w_bytes'] / 1e9:.2f} GB of weights per rank), {2 * s.n_layer if N > 1 else 0} all-reduces of "
                         f"{n_red * 4 // 1024} KB ({'peer-memory kernel' if comm is not None else 'NCCL' if N > 1 else 'none'}) + 1 NCCL all-gather",
             "us_per_step": us, "tok_per_s": batch / (us * 1e-6), "ops_per_step": n_ops, "mode": mode, "scaling": "strong",
-            "logits_finite": finite}
+            "parity": parity}
 
 
 def _ep_moe(be, infr_b200, dist, rank, world, local, steps, warmup):
@@ -660,11 +736,25 @@ def _ep_moe(be, infr_b200, dist, rank, world, local, steps, warmup):
     rows, ne, nx, nu, nff = 256, 2048, 128, 8, 768
     n_local = nx // world
     lo = rank * n_local
-    gate = be.from_numpy(synth.random_blocks(infr_b200.Q4K, n_local * nff * ne, 100 + rank), infr_b200.USAGE_WEIGHTS)
-    up = be.from_numpy(synth.random_blocks(infr_b200.Q4K, n_local * nff * ne, 200 + rank), infr_b200.USAGE_WEIGHTS)
-    down = be.from_numpy(synth.random_blocks(infr_b200.Q4K, n_local * ne * nff, 300 + rank), infr_b200.USAGE_WEIGHTS)
-    router = be.from_numpy(synth.normal(7, (nx, ne), 1.0 / np.sqrt(ne)))
-    x = be.from_numpy(synth.normal(8, (rows, ne)))
+    # every rank builds the same seeded banks on the host and uploads the band of its experts
+    banks = [synth.random_blocks(infr_b200.Q4K, nx * nff * ne, 100 + k) for k in range(3)]
+    per_expert = nff * ne // 256 * 144
+    band = lambda a: a[lo * per_expert:(lo + n_local) * per_expert]
+    router_h = synth.normal(7, (nx, ne), 1.0 / np.sqrt(ne))
+    x_h = synth.normal(8, (rows, ne))
+    router = be.from_numpy(router_h)
+    x = be.from_numpy(x_h)
+    ref = None
+    if world > 1 and rank == 0:
+        # the unsharded layer on this GPU: what the sum of the ranks' shares has to reproduce
+        fg, fu, fd = (be.from_numpy(a, infr_b200.USAGE_WEIGHTS) for a in banks)
+        ref_b = be.alloc(rows * ne * 4)
+        be.moe_ffn(x, x, router, fg, fu, fd, ref_b, rows=rows, ne=ne, n_expert=nx, n_used=nu, n_ff_exp=nff)
+        ref = be.download(ref_b, np.float32)
+        for b in (fg, fu, fd, ref_b):
+            b.close()
+    gate, up, down = (be.from_numpy(band(a), infr_b200.USAGE_WEIGHTS) for a in banks)
+    del banks
     out_t = torch.zeros(rows * ne, dtype=torch.float32, device=dev)
     torch.cuda.synchronize(dev)
     dst = be.wrap(out_t.data_ptr(), rows * ne * 4, infr_b200.USAGE_ACTIVATIONS)
@@ -677,10 +767,17 @@ def _ep_moe(be, infr_b200, dist, rank, world, local, steps, warmup):
 
     ext = torch.cuda.ExternalStream(be.stream(), device=dev)
     mode = "cuda graph"
+    parity = None
     with torch.cuda.stream(ext):
         for _ in range(3):
             step()
         ext.synchronize()
+        if ref is not None:
+            got = out_t.cpu().numpy()
+            rel = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
+            parity = {"vs": "the unsharded layer on one GPU, same seeded banks", "rel_l2": rel, "max_abs_diff": float(np.abs(got - ref).max()),
+                      "bar_rel_l2": 1e-3}
+            assert rel < 1e-3, f"expert-parallel layer differs from the single-GPU layer: {parity}"
         graph = None
         try:
             graph = torch.cuda.CUDAGraph()
@@ -707,7 +804,55 @@ def _ep_moe(be, infr_b200, dist, rank, world, local, steps, warmup):
         b.close()
     return {"workload": f"expert-parallel MoE layer, {world} GPU(s): 256 tok x hidden 2048, {n_local} of 128 experts per rank "
                         f"(2048->768->2048, Q4_K), softmax top-8, tokens replicated, 1 NCCL all-reduce of 2 MB",
-            "us_per_layer": us, "mode": mode, "scaling": "strong"}
+            "us_per_layer": us, "mode": mode, "scaling": "strong", "parity": parity}
+
+
+def _mmq_sharded(be, infr_b200, dist, rank, world, steps, warmup, peak_tops=None):
+    """The prefill configuration (M = 512 tokens, K = 4096, N = 14336 Q4_K rows) split by output rows over the ranks
+    (the column-parallel half of the reference's tensor-parallel lowering, crates/infr-llama/src/seam/mod.rs:2711-2798):
+    rank r multiplies the same 512 activation rows, quantised redundantly on every rank, with rows
+    [r * 14336 / N, (r + 1) * 14336 / N) of one seeded weight.  No collective: a consumer of the full result would
+    all-gather.  Reports per-GPU and aggregate int8 TOPS; rank 0 checks its shard against the unsharded product."""
+    from infr_b200 import shard, synth
+
+    m, in_f, out_f = 512, 4096, 14336
+    w = synth.random_blocks(infr_b200.Q4K, out_f * in_f, 5)
+    x = synth.normal(6, (m, in_f))
+    xb = be.from_numpy(x)
+    ws, lo, cnt = shard.row_shard(infr_b200.Q4K, w, out_f, in_f, rank, world)
+    wb = be.from_numpy(ws, infr_b200.USAGE_WEIGHTS)
+    yb = be.alloc(m * cnt * 4)
+    parity = None
+    if world > 1 and rank == 0:
+        fb, fy = be.from_numpy(w, infr_b200.USAGE_WEIGHTS), be.alloc(m * out_f * 4)
+        be.linear(infr_b200.Q4K, fb, xb, fy, m, in_f, out_f)
+        be.linear(infr_b200.Q4K, wb, xb, yb, m, in_f, cnt)
+        full = be.download(fy, np.float32).reshape(m, out_f)[:, lo:lo + cnt]
+        mine = be.download(yb, np.float32).reshape(m, cnt)
+        rel = float(np.linalg.norm(mine - full) / np.linalg.norm(full))
+        parity = {"vs": "the same rows of the unsharded product on one GPU", "rel_l2": rel, "bit_identical": bool((mine == full).all())}
+        assert rel < 1e-5, parity
+        fb.close()
+        fy.close()
+    del w
+    for _ in range(warmup):
+        be.linear(infr_b200.Q4K, wb, xb, yb, m, in_f, cnt)
+    be.sync()
+    _barrier(dist)
+    be.timer_start()
+    for _ in range(steps):
+        be.linear(infr_b200.Q4K, wb, xb, yb, m, in_f, cnt)
+    ms = _max_over_ranks(dist, be.timer_stop())
+    us = ms * 1e3 / steps
+    agg = 2.0 * m * in_f * out_f / (us * 1e-6) / 1e12
+    res = {"workload": f"prefill MMQ q4_k M={m} K={in_f} N={out_f} split by output rows over {world} GPU(s) ({cnt} rows on rank 0), "
+                       f"activations quantised on every rank, no collective",
+           "us": us, "aggregate_tops": agg, "per_gpu_tops": agg / world, "scaling": "strong", "parity": parity}
+    if peak_tops:
+        res["per_gpu_frac_of_measured_int8_peak"] = agg / world / peak_tops
+    for b in (wb, xb, yb):
+        b.close()
+    return res
 
 
 # ------------------------------------------------------------------------------------------------
@@ -796,7 +941,9 @@ def run_b200(args):
         "config": {"workload": f"Q4_K GEMV W 4096x4096 (fp32 N(0,0.02) seed 0 -> Q4_K), x fp32 [1,4096] N(0,1); "
                                f"step = one pass over {ROT} device copies at distinct addresses",
                    "l2": f"inputs larger than L2: {ROT * w.nbytes / 1e6:.0f} MB of weights per step vs {caps.l2_bytes / 1e6:.0f} MB L2",
-                   "parallelism": f"{world} x independent row shards (no collective)" if world > 1 else "1 GPU",
+                   "parallelism": (f"weak scaling: rank r holds rows [r*4096, (r+1)*4096) of each of {ROT} Q4_K matrices of {world * 4096} x 4096 "
+                                   f"(output-row shards, activations replicated, no collective; sharded results are checked against one GPU "
+                                   f"in mmq_sharded / tp_decode_step / ep_moe)") if world > 1 else "1 GPU",
                    "fraction_of_8TBs": value / world / 8000.0},
         "roofline": {"bound": "hbm", "achieved": kern_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": kern_gbs / hbm_peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of this kernel at this shape from the committed
@@ -822,12 +969,17 @@ def run_b200(args):
             for m in ms_:
                 sweep.append(_gemv_case(be, infr_b200, dtype, o, i_, m, seed, sw_steps, 5, caps.l2_bytes, hbm_peak))
         out["sweep"] = sweep
-        out["mmq"] = _mmq_case(be, infr_b200, 512, 4096, 14336, 5, 20, 3)
-        out["moe"] = _moe_case(be, infr_b200, 20, 3)
+        out["int8_peak"] = _int8_peak(be)
+        out["mmq"] = _mmq_case(be, infr_b200, 512, 4096, 14336, 5, 20, 3, out["int8_peak"])
+        out["moe"] = _moe_case(be, infr_b200, 20, 3, hbm_peak)
         out["decode_linears"] = [_decode_linears_case(be, infr_b200, b, 10, 3) for b in (1, 32)]
         out["decode_step"] = [_decode_step_case(be, infr_b200, b, 10, 3, hbm_peak) for b in (1, 32)]
 
     if not args.no_sweep:
+        peak_tops = out["int8_peak"]["burst_tops"] if "int8_peak" in out else _int8_peak(be)["burst_tops"]
+        mq = _mmq_sharded(be, infr_b200, dist, rank, world, 20, 3, peak_tops)
+        if rank == 0:
+            out["mmq_sharded"] = mq
         tp = _tp_decode(be, infr_b200, dist, rank, world, local, 10, 3)
         ep = _ep_moe(be, infr_b200, dist, rank, world, local, 20, 3)
         tps = [_tp_decode_step(be, infr_b200, dist, rank, world, local, b_, 10, 3) for b_ in (1, 32)] if world > 1 else None
@@ -864,7 +1016,7 @@ def run_profile_case(args):
     name, out_f, in_f, m = args.profile_case.split(":")
     if name == "moe":
         be = infr_b200.CudaBackend(device=0)
-        _emit(_moe_case(be, infr_b200, args.steps, 2))
+        _emit(_moe_case(be, infr_b200, args.steps, 2, _peaks()[0]))
         be.close()
         return
     if name == "decode":  # decode:0:0:BATCH — the Linear ops of an 8B-shape decode step
@@ -874,7 +1026,7 @@ def run_profile_case(args):
         return
     if name == "step":  # step:0:CONTEXT:BATCH — the whole 8B-shape decode step
         be = infr_b200.CudaBackend(device=0)
-        _emit(_decode_step_case(be, infr_b200, int(m), args.steps, 2, 6542.7, pos=int(in_f) or 4096))
+        _emit(_decode_step_case(be, infr_b200, int(m), args.steps, 2, _peaks()[0], pos=int(in_f) or 4096))
         be.close()
         return
     if name == "mmq":  # mmq:OUT_F:IN_F:M — the prefill GEMM (Linear with m > 8)

@@ -192,43 +192,56 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
         for (int i = threadIdx.x; i < nb * 8; i += kThreadsMma)
             if ((i & 7) >= M) s_d8[i] = 0.f;
     if (FUSED) {
-        // quantize_q8 (crates/infr-cpu/src/quant.rs:27-58) per 256-block, one warp per block
-        for (int n = 0; n < M; n++)
-        for (int b = warp; b < nb; b += kW) {
-            float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
-            if (n < m) {
-                const float *xp = x + (size_t)n * in_f + (size_t)b * 256;
-                v0 = *reinterpret_cast<const float4 *>(xp + lane * 8);
-                v1 = *reinterpret_cast<const float4 *>(xp + lane * 8 + 4);
-            }
-            float am = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
-                             fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+        // quantize_q8 (crates/infr-cpu/src/quant.rs:27-58) per 256-block, one warp per (row, block) item.  A warp
+        // fetches up to four of its items before it works on the first, so the fetches share one round trip to L2.
+        const int items = M * nb;
+        for (int i0 = warp; i0 < items; i0 += 4 * kW) {
+            float4 pa[4], pb[4];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-            const float dd = am / 127.0f;
-            const float id = dd > 0.0f ? 1.0f / dd : 0.0f;
-            const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-            int q[8], sum = 0;
+            for (int k = 0; k < 4; k++) {
+                const int i = i0 + k * kW, n = i / nb, b = i - n * nb;
+                pa[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                pb[k] = pa[k];
+                if (i < items && n < m) {
+                    const float *xp = x + (size_t)n * in_f + (size_t)b * 256;
+                    pa[k] = *reinterpret_cast<const float4 *>(xp + lane * 8);
+                    pb[k] = *reinterpret_cast<const float4 *>(xp + lane * 8 + 4);
+                }
+            }
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                float r = roundf(vv[i] * id);
-                r = fminf(fmaxf(r, -127.0f), 127.0f);
-                q[i] = (int)r;
-                sum += q[i];
+            for (int k = 0; k < 4; k++) {
+                const int i = i0 + k * kW, n = i / nb, b = i - n * nb;
+                if (i >= items) break;
+                const float4 v0 = pa[k], v1 = pb[k];
+                float am = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                                 fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+                const float dd = am / 127.0f;
+                const float id = dd > 0.0f ? 1.0f / dd : 0.0f;
+                const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                int q[8], sum = 0;
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    float r = roundf(vv[e] * id);
+                    r = fminf(fmaxf(r, -127.0f), 127.0f);
+                    q[e] = (int)r;
+                    sum += q[e];
+                }
+                // lane holds elements 8*lane..8*lane+7 = sub-block s = lane/4, l = 8*(lane&3)+e
+                const int s = lane >> 2, tt = lane & 3;
+                uint2 pk;
+                pk.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+                pk.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+                *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * kStagedBytes + tt * kLaneBytes + s * 8) = pk;
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                if (tt == 0) {
+                    s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum & 63);
+                    s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
+                }
+                if (lane == 0) s_d8[b * 8 + n] = dd;
             }
-            // lane holds elements 8*lane..8*lane+7 = sub-block s = lane/4, l = 8*(lane&3)+i
-            const int s = lane >> 2, tt = lane & 3;
-            uint2 pk;
-            pk.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
-            pk.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
-            *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * kStagedBytes + tt * kLaneBytes + s * 8) = pk;
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            if (tt == 0) {
-                s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum & 63);
-                s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
-            }
-            if (lane == 0) s_d8[b * 8 + n] = dd;
         }
     } else {
         if (M == 1) {

@@ -542,6 +542,11 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
     const size_t rows = a.rows, ne = a.ne, nff = a.n_ff, nu = a.n_used, nx = a.n_expert;
     const size_t n_pairs = rows * nu;
     const size_t max_items = n_pairs / 8 + nx + 1;
+    // Experts that see a few dozen rows each run on the tensor-memory GEMM in grouped form (one 64-row slab of an
+    // expert's rows per tile column: the expert's weights are unpacked once per slab); with only a handful of rows
+    // per expert the 8-row grouped GEMV does less padded work.
+    const bool grouped_gemm = mmq_impl_ == 2 || (mmq_impl_ == 0 && n_pairs >= (size_t)8 * a.n_local);
+    const size_t max_slabs = n_pairs / 64 + a.n_local + 1;
     // scratch carve-up (all 256-byte aligned)
     size_t off = 0;
     auto take = [&](size_t bytes) {
@@ -556,6 +561,8 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
     const size_t o_g = take(n_pairs * nff * 4), o_u = take(n_pairs * nff * 4);
     const size_t o_aq = take(n_pairs * nff), o_ad = take(n_pairs * (nff / 256) * 4), o_as = take(n_pairs * (nff / 32) * 4);
     const size_t o_y = take(n_pairs * ne * 4);
+    const size_t o_px = grouped_gemm ? take(mmq_ws_record_bytes((int)max_slabs * 64, (int)ne)) : 0;
+    const size_t o_pa = grouped_gemm ? take(mmq_ws_record_bytes((int)max_slabs * 64, (int)nff)) : 0;
     Status s = ensure_scratch(off);
     if (!s.ok()) return s;
     uint8_t *b = scratch();
@@ -581,10 +588,31 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
     } while (0)
     INFR_STEP(launch_moe_router(a.router, a.router_x, logits, (int)rows, (int)ne, (int)nx, stream_), "moe router");
     INFR_STEP(launch_moe_route(logits, (int)rows, (int)nx, (int)nu, a.scale, a.norm_w, ids, w, stream_), "moe route");
-    INFR_STEP(launch_moe_bucket(ids, (int)rows, (int)nu, (int)nx, (int)a.expert_lo, (int)a.n_local, prow, pslot, ie, ip, ic, ni, nullptr, stream_), "moe bucket");
+    INFR_STEP(launch_moe_bucket(ids, (int)rows, (int)nu, (int)nx, (int)a.expert_lo, (int)a.n_local, grouped_gemm ? 64 : 8, prow, pslot, ie, ip, ic, ni,
+                                nullptr, stream_),
+              "moe bucket");
     // stage A: every distinct row quantised once (lib.rs:2688-2718)
     INFR_STEP(launch_quantize_q8(a.x, (int)rows, (int)ne, 256, xq, xd, xs, nullptr, nullptr, nullptr, stream_), "moe quantize x");
     Q8Dev xa{xq, xd, xs, nullptr, 256};
+    if (grouped_gemm) {
+        // stage B: both banks read the same gathered activation planes (laid out once); stage C; stage D on the
+        // re-quantised pairs; stage E
+        INFR_STEP(launch_mmq_ws_q4k_grouped(a.gate, (int)a.n_local, xa, b + o_px, g, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_slabs, true, dev_,
+                                            status_dev_, stream_),
+                  "moe gate (grouped gemm)");
+        launches_++;  // the plane layout kernel
+        INFR_STEP(launch_mmq_ws_q4k_grouped(a.up, (int)a.n_local, xa, b + o_px, u, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_slabs, false, dev_,
+                                            status_dev_, stream_),
+                  "moe up (grouped gemm)");
+        INFR_STEP(launch_moe_swiglu_quant(g, u, (int)n_pairs, (int)nff, aq, ad, as, nullptr, stream_), "moe swiglu");
+        Q8Dev aa{aq, ad, as, nullptr, 256};
+        INFR_STEP(launch_mmq_ws_q4k_grouped(a.down, (int)a.n_local, aa, b + o_pa, y, (int)nff, (int)ne, ie, ip, ic, ni, nullptr, (int)max_slabs, true, dev_,
+                                            status_dev_, stream_),
+                  "moe down (grouped gemm)");
+        launches_++;
+        INFR_STEP(launch_moe_combine(y, pslot, w, (int)rows, (int)nu, (int)ne, a.dst, stream_), "moe combine");
+        return Status::Ok();
+    }
     // stage B: gate and up expert GEMMs, rows gathered per pair
     INFR_STEP(launch_grouped_q4k_mma(a.gate, (int)a.n_local, xa, g, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_items, dev_, status_dev_, stream_), "moe gate");
     INFR_STEP(launch_grouped_q4k_mma(a.up, (int)a.n_local, xa, u, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_items, dev_, status_dev_, stream_), "moe up");

@@ -76,6 +76,12 @@ cudaError_t launch_mmq_q4k(const uint8_t *w, const Q8Dev &a, void *records, floa
 size_t mmq_ws_record_bytes(int m, int in_f);
 cudaError_t launch_mmq_ws_q4k(const uint8_t *w, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
                               const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
+// The same tensor-memory GEMM over a bank of expert matrices, one 64-token slab of routed rows per tile column
+// (mmq_ws.cu).  `records`: mmq_ws_record_bytes(max_slabs * 64, in_f) bytes; prep = false reuses planes already laid.
+cudaError_t launch_mmq_ws_q4k_grouped(const uint8_t *bank, int n_experts, const Q8Dev &a, void *records, float *y, int in_f, int out_f,
+                                      const int *slab_expert, const int *slab_p0, const int *slab_cnt, const int *n_slabs,
+                                      const int *pair_row, int max_slabs, bool prep, const DeviceInfo &dev, uint32_t *status,
+                                      cudaStream_t st);
 // Grouped Q4_K GEMM over a bank of n_experts matrices [out_f, in_f] stored back to back: work item i
 // multiplies up to 8 quantised activation rows (pairs item_p0[i]..+item_cnt[i], gathered through
 // pair_row when non-null) with expert item_expert[i]; y is [n_pairs, out_f].
@@ -87,8 +93,8 @@ cudaError_t launch_moe_router(const float *router, const float *x, float *logits
                               cudaStream_t st);
 cudaError_t launch_moe_route(const float *logits, int rows, int n_expert, int n_used, float scale, int norm_w,
                              int32_t *sel_ids, float *sel_w, cudaStream_t st);
-cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int n_expert, int e_lo, int n_local, int32_t *pair_row,
-                              int32_t *pair_of_slot, int32_t *item_expert, int32_t *item_p0, int32_t *item_cnt,
+cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int n_expert, int e_lo, int n_local, int item_rows,
+                              int32_t *pair_row, int32_t *pair_of_slot, int32_t *item_expert, int32_t *item_p0, int32_t *item_cnt,
                               int32_t *n_items, int32_t *counts_out, cudaStream_t st);
 cudaError_t launch_moe_swiglu_quant(const float *gate, const float *up, int n_pairs, int nff, int8_t *qs, float *d,
                                     int32_t *sums, float *act_out, cudaStream_t st);

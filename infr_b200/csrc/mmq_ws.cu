@@ -150,18 +150,44 @@ __device__ __forceinline__ void tma2(uint32_t dst, const CUtensorMap *map, int x
 }  // namespace
 
 
+// Grouped (mixture-of-experts) form: the token dimension is a list of 64-token slabs, each slab holding up to 64
+// activation rows routed to ONE expert (moe_bucket_kernel with 64-row items); the weight rows of a slab's tiles are
+// those of its expert inside the bank (experts back to back, out_f rows each) and its results go to the rows of
+// its routed pairs.  slab_expert == nullptr: the plain GEMM.
+struct MmqGroup {
+    const int *slab_expert;  // [n_slabs] expert (index inside the bank) of the slab
+    const int *slab_p0;      // [n_slabs] first routed pair of the slab; output row = pair
+    const int *slab_cnt;     // [n_slabs] pairs in the slab (1..64)
+    const int *n_slabs;      // device scalar
+    const int *pair_row;     // [n_pairs] activation row of each pair, or nullptr: pair p reads row p
+};
+
 // Re-lays the quantised activations for the kernel.  Output: for every super-block b, 20 planes of
 // [m tokens][16 bytes]: planes 0..15 = the int8 codes of K chunk k/16, planes 16..19 = B1[0..3], B1[4..7],
 // B2[0..3], B2[4..7] (tf32 pieces of d8 * bsum_s); a 64-token tile of one block is then 20 runs of 1 KB,
 // which the copy engine moves at full rate (16-byte runs do not).  Behind the planes: d8 transposed to
 // [nb][m_pad] f32 for the epilogue's broadcast loads.
 __global__ void mmq_ws_prep_kernel(const int8_t *__restrict__ qs, const int32_t *__restrict__ sums, const float *__restrict__ d,
-                                   int m, int m_pad, int nb, uint4 *__restrict__ out) {
+                                   int m, int m_pad, int nb, uint4 *__restrict__ out, MmqGroup grp) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;  // token fastest: a warp writes 512 contiguous bytes per plane
     if (i >= m * nb) return;
     const int tok = i % m, b = i / m;
-    const size_t rec = (size_t)tok * nb + b;
+    size_t rec = (size_t)tok * nb + b;
     uint4 *o = out + (size_t)b * kPlanes * m + tok;
+    if (grp.slab_expert) {
+        // `tok` is a slot of a slab: its activation row is the slab's pair, empty slots read as zero
+        const int slab = tok / kTN, slot = tok - slab * kTN;
+        if (slab >= *grp.n_slabs) return;
+        if (slot >= grp.slab_cnt[slab]) {
+            const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int k = 0; k < kPlanes; k++) o[(size_t)k * m] = z;
+            reinterpret_cast<float *>(out + (size_t)nb * kPlanes * m)[(size_t)b * m_pad + tok] = 0.f;
+            return;
+        }
+        const int pair = grp.slab_p0[slab] + slot;
+        rec = (size_t)(grp.pair_row ? grp.pair_row[pair] : pair) * nb + b;
+    }
     const uint4 *src = reinterpret_cast<const uint4 *>(qs + rec * 256);
 #pragma unroll
     for (int k = 0; k < 16; k++) o[(size_t)k * m] = src[k];
@@ -201,7 +227,7 @@ __device__ __forceinline__ bool wait_plain(uint32_t bar, uint32_t parity, uint32
 __global__ void __launch_bounds__(kThreadsWs, 1)
     mmq_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q,
                   const float *__restrict__ d8t, float *__restrict__ C, int m, int m_pad, int in_f, int out_f,
-                  uint32_t *__restrict__ status) {
+                  uint32_t *__restrict__ status, MmqGroup grp) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *stage0 = smem;                                              // [kStages]{raw rows, activation planes}
     uint8_t *minbuf0 = smem + kStages * kStageBytes;                     // [2][kMinBytes]
@@ -213,7 +239,8 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb = in_f >> 8;
-    const int row_tiles = (out_f + kTM - 1) / kTM, tok_tiles = (m + kTN - 1) / kTN;
+    // grouped: one token tile per slab (their number is known only on the device)
+    const int row_tiles = (out_f + kTM - 1) / kTM, tok_tiles = grp.slab_expert ? *grp.n_slabs : (m + kTN - 1) / kTN;
     const int n_tiles = row_tiles * tok_tiles;
 
     if (tid == 0) {
@@ -246,6 +273,7 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 const int rt = t % row_tiles, tt = t / row_tiles;  // consecutive CTAs share a token tile
+                const int wrow0 = (grp.slab_expert ? grp.slab_expert[tt] * out_f : 0) + rt * kTM;
                 for (int b = 0; b < nb; b++, j++) {
                     const int s = j % kStages;
                     // the stage's previous job is complete (its operands were read by the MMAs, its rows unpacked)
@@ -256,7 +284,7 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                     uint8_t *st = stage0 + (size_t)s * kStageBytes;
                     const uint32_t fb = bar(B_FULL + s);
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb), "r"(kStageBytes) : "memory");
-                    tma2(su32(st), &map_w, b * 36, rt * kTM, fb);
+                    tma2(su32(st), &map_w, b * 36, wrow0, fb);
                     tma2(su32(st + kRawBytes), &map_q, tt * kTN * 4, b * kPlanes, fb);
                 }
             }
@@ -479,6 +507,8 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
             if (!ok) break;
             // tile end: subtract the min sums and store
             const int grow = rt * kTM + row;
+            const int tok_lim = grp.slab_expert ? grp.slab_cnt[tt] : m - tt * kTN;      // valid token slots of the tile
+            const size_t out_row0 = grp.slab_expert ? (size_t)grp.slab_p0[tt] : (size_t)tt * kTN;  // output row of slot 0
 #pragma unroll
             for (int c = 0; c < 2; c++) {
                 uint32_t mv[16];
@@ -491,8 +521,8 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 }
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    const int tok = tt * kTN + half * 32 + c * 16 + i;
-                    if (grow < out_f && tok < m) C[(size_t)tok * out_f + grow] = acc[c * 16 + i] - __uint_as_float(mv[i]);
+                    const int slot = half * 32 + c * 16 + i;
+                    if (grow < out_f && slot < tok_lim) C[(out_row0 + slot) * out_f + grow] = acc[c * 16 + i] - __uint_as_float(mv[i]);
                 }
             }
         }
@@ -526,18 +556,20 @@ size_t mmq_ws_record_bytes(int m, int in_f) {
     return nb * kPlanes * (size_t)m * 16 + nb * m_pad * 4;
 }
 
-cudaError_t launch_mmq_ws_q4k(const uint8_t *w, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
-                              const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
-    if (m < 1 || in_f % 256 || out_f < 1) return cudaErrorInvalidValue;
+namespace {
+// Common launch: `m` token slots (a multiple of 64 in grouped mode: all slabs that can exist), weight tensor map over
+// `w_rows` rows.  prep = false reuses the planes a previous call with the same activations and slabs has written.
+cudaError_t launch_ws(const uint8_t *w, size_t w_rows, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
+                      const MmqGroup &grp, int max_tok_tiles, bool prep, const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
     EncodeFn enc = encode_fn();
     if (!enc) return cudaErrorNotSupported;
     const int nb = in_f / 256, m_pad = (m + kTN - 1) / kTN * kTN;
     const int n_rec = m * nb;
-    mmq_ws_prep_kernel<<<(n_rec + 255) / 256, 256, 0, st>>>(a.qs, a.sums, a.d, m, m_pad, nb, static_cast<uint4 *>(records));
+    if (prep) mmq_ws_prep_kernel<<<(n_rec + 255) / 256, 256, 0, st>>>(a.qs, a.sums, a.d, m, m_pad, nb, static_cast<uint4 *>(records), grp);
     CUtensorMap map_w, map_q;
     const cuuint32_t one2[2] = {1, 1};
     {
-        const cuuint64_t gdim[2] = {(cuuint64_t)nb * 36, (cuuint64_t)out_f};
+        const cuuint64_t gdim[2] = {(cuuint64_t)nb * 36, (cuuint64_t)w_rows};
         const cuuint64_t gstr[1] = {(cuuint64_t)nb * 144};
         const cuuint32_t box[2] = {36, (cuuint32_t)kTM};
         if (enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(w), gdim, gstr, box, one2, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -556,10 +588,30 @@ cudaError_t launch_mmq_ws_q4k(const uint8_t *w, const Q8Dev &a, void *records, f
     const float *d8t = reinterpret_cast<const float *>(static_cast<const uint8_t *>(records) + (size_t)nb * kPlanes * m * 16);
     cudaError_t e = cudaFuncSetAttribute(mmq_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) return e;
-    const int n_tiles = ((out_f + kTM - 1) / kTM) * ((m + kTN - 1) / kTN);
+    const int n_tiles = ((out_f + kTM - 1) / kTM) * max_tok_tiles;
     const int grid = n_tiles < dev.sm_count ? n_tiles : dev.sm_count;
-    mmq_ws_kernel<<<grid, kThreadsWs, kSmem, st>>>(map_w, map_q, d8t, c, m, m_pad, in_f, out_f, status);
+    mmq_ws_kernel<<<grid, kThreadsWs, kSmem, st>>>(map_w, map_q, d8t, c, m, m_pad, in_f, out_f, status, grp);
     return cudaGetLastError();
+}
+}  // namespace
+
+cudaError_t launch_mmq_ws_q4k(const uint8_t *w, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
+                              const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+    if (m < 1 || in_f % 256 || out_f < 1) return cudaErrorInvalidValue;
+    return launch_ws(w, (size_t)out_f, a, records, c, m, in_f, out_f, MmqGroup{}, (m + kTN - 1) / kTN, true, dev, status, st);
+}
+
+// Expert-grouped GEMM over a bank of n_experts Q4_K matrices [out_f, in_f] stored back to back: slab i (a work item
+// of moe_bucket_kernel with 64-row items) multiplies up to 64 quantised activation rows (pairs slab_p0[i]..+slab_cnt[i],
+// gathered through pair_row when non-null) with expert slab_expert[i]; y is [n_pairs, out_f].  max_slabs bounds the
+// number of slabs (n_pairs / 64 + n_experts); `records` holds mmq_ws_record_bytes(max_slabs * 64, in_f) bytes.
+cudaError_t launch_mmq_ws_q4k_grouped(const uint8_t *bank, int n_experts, const Q8Dev &a, void *records, float *y, int in_f, int out_f,
+                                      const int *slab_expert, const int *slab_p0, const int *slab_cnt, const int *n_slabs,
+                                      const int *pair_row, int max_slabs, bool prep, const DeviceInfo &dev, uint32_t *status,
+                                      cudaStream_t st) {
+    if (in_f % 256 || out_f < 1 || max_slabs < 1 || n_experts < 1) return cudaErrorInvalidValue;
+    MmqGroup grp{slab_expert, slab_p0, slab_cnt, n_slabs, pair_row};
+    return launch_ws(bank, (size_t)n_experts * out_f, a, records, y, max_slabs * kTN, in_f, out_f, grp, max_slabs, prep, dev, status, st);
 }
 
 }  // namespace infr

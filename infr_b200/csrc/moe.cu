@@ -112,12 +112,13 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
 
 // One CTA of 32 warps.  Warp w owns experts w, w+32, ...: it counts an expert's pairs with ballots over
 // 32 pairs at a time, the block scans the counts, then the warp lists the pairs in (row, rank) order
-// (ballot + prefix popcount keeps the order) and cuts them into work items of up to 8 rows.
+// (ballot + prefix popcount keeps the order) and cuts them into work items of up to `item_rows` rows (8 for the
+// grouped GEMV, 64 = one token tile for the grouped tensor-memory GEMM).
 //   pair_row[p], pair_of_slot[r * n_used + rank] = p, item_{expert,p0,cnt}[], n_items
 // Expert parallelism: only experts [e_lo, e_lo + n_local) are listed (item_expert is the index inside this
 // rank's banks); pairs routed elsewhere get pair_of_slot = -1 and contribute nothing to this rank's output.
 __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restrict__ sel_ids, int rows, int n_used, int n_expert,
-                                                          int e_lo, int n_local,
+                                                          int e_lo, int n_local, int item_rows,
                                                           int32_t *__restrict__ pair_row, int32_t *__restrict__ pair_of_slot,
                                                           int32_t *__restrict__ item_expert, int32_t *__restrict__ item_p0,
                                                           int32_t *__restrict__ item_cnt, int32_t *__restrict__ n_items,
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
             s_off[k] = off;
             s_ioff[k] = ioff;
             off += s_cnt[k];
-            ioff += (s_cnt[k] + 7) / 8;
+            ioff += (s_cnt[k] + item_rows - 1) / item_rows;
         }
         *n_items = ioff;
     }
@@ -170,11 +171,11 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
             }
             p += __popc(mask);
         }
-        for (int c = lane * 8; c < cnt; c += 256) {
-            const int it = s_ioff[e] + c / 8;
+        for (int c = lane * item_rows; c < cnt; c += 32 * item_rows) {
+            const int it = s_ioff[e] + c / item_rows;
             item_expert[it] = e - e_lo;
             item_p0[it] = s_off[e] + c;
-            item_cnt[it] = cnt - c < 8 ? cnt - c : 8;
+            item_cnt[it] = cnt - c < item_rows ? cnt - c : item_rows;
         }
     }
 }
@@ -263,11 +264,11 @@ cudaError_t launch_moe_route(const float *logits, int rows, int n_expert, int n_
     return cudaGetLastError();
 }
 
-cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int n_expert, int e_lo, int n_local, int32_t *pair_row,
-                              int32_t *pair_of_slot, int32_t *item_expert, int32_t *item_p0, int32_t *item_cnt,
+cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int n_expert, int e_lo, int n_local, int item_rows,
+                              int32_t *pair_row, int32_t *pair_of_slot, int32_t *item_expert, int32_t *item_p0, int32_t *item_cnt,
                               int32_t *n_items, int32_t *counts_out, cudaStream_t st) {
-    if (n_expert > 1024) return cudaErrorInvalidValue;
-    moe_bucket_kernel<<<1, 1024, 0, st>>>(sel_ids, rows, n_used, n_expert, e_lo, n_local, pair_row, pair_of_slot, item_expert, item_p0, item_cnt,
+    if (n_expert > 1024 || item_rows < 1) return cudaErrorInvalidValue;
+    moe_bucket_kernel<<<1, 1024, 0, st>>>(sel_ids, rows, n_used, n_expert, e_lo, n_local, item_rows, pair_row, pair_of_slot, item_expert, item_p0, item_cnt,
                                           n_items, counts_out);
     return cudaGetLastError();
 }

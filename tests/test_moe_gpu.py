@@ -15,6 +15,15 @@ from infr_b200 import synth
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(scope="module")
+def gemm_backend():
+    """Every expert bank on the grouped tensor-memory GEMM, also where the default dispatch (few rows per expert) would
+    take the 8-row grouped GEMV."""
+    be = infr_b200.CudaBackend(device=0, mmq_kernel=2)
+    yield be
+    be.close()
+
+
 _BANKS = {}
 
 
@@ -58,7 +67,9 @@ def _run(backend, x, router, gate, up, down, rows, ne, n_expert, n_used, nff, no
     (64, 2048, 128, 8, 768, True, 1.0),     # the Qwen3-30B-A3B layer shape with 64 tokens
     (256, 2048, 128, 8, 768, True, 1.0),    # the MoE configuration itself: 256 tokens, 2048 routed pairs
 ])
-def test_moe_ffn_matches_production_cpu(backend, oracle, rows, ne, n_expert, n_used, nff, norm_w, scale):
+@pytest.mark.parametrize("path", ["default", "grouped-gemm"])
+def test_moe_ffn_matches_production_cpu(backend, gemm_backend, oracle, rows, ne, n_expert, n_used, nff, norm_w, scale, path):
+    backend = backend if path == "default" else gemm_backend
     gate, up, down = _banks(n_expert, nff, ne, seed=100)
     router = synth.normal(7, (n_expert, ne), 1.0 / np.sqrt(ne))
     x = synth.normal(8, (rows, ne))
@@ -198,8 +209,10 @@ def test_expert_parallel_slices_add_up_to_the_whole_layer(backend):
     whole = run(0, nx)
     halves = run(0, nx // 2) + run(nx // 2, nx // 2)
     assert np.abs(whole).max() > 1e-3
-    assert fx.rel_l2(halves, whole) < 1e-6
+    # (a slice with more rows per expert may take the grouped GEMM where the whole layer takes the grouped GEMV: the
+    # integer block sums are the same, the f32 sums are rounded in a different order)
+    assert fx.rel_l2(halves, whole) < 1e-5
     thirds = run(0, 3) + run(3, 3) + run(6, 2)
-    assert fx.rel_l2(thirds, whole) < 1e-6
+    assert fx.rel_l2(thirds, whole) < 1e-5
     with pytest.raises(infr_b200.BackendError):
         run(6, 3)  # leaves [0, n_expert)

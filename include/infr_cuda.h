@@ -187,7 +187,7 @@ typedef struct {
  *                          act (0 = SiLU), gating (0 = Softmax)}; f = {scale}
  *      Fields of Op::MoeFfn without a slot here (down_scale, swiglu_clamp, ep_band, exp_probs_b,
  *      expert groups, expert_ids) must be None/0 on the Rust side; the binding returns
- *      Error::Unsupported otherwise.  Banks: Q4_K, router F32.
+ *      Error::Unsupported otherwise.  Banks: Q4_K or Q6_K (each bank on its own), router F32.
  *  INFR_OP_RMS_NORM : t = {x, weight, dst}; u = {rows, dim}; f = {eps}
  *  INFR_OP_ROPE     : t = {x, positions, dst}; u = {rows, n_head, head_dim, rope_dim, x_stride, neox, backward,
  *                     has_freq_factors}; f = {theta}          (x_stride 0 or packed; backward, freq_factors: not run)
@@ -284,7 +284,8 @@ INFR_API int32_t infr_cuda_linear(infr_cuda_ctx *ctx, int32_t dtype, const infr_
 
 /* Op::MoeFfn as a direct call (crates/infr-core/src/graph.rs:918-1011; CPU semantics
  * crates/infr-cpu/src/lib.rs:2264-2984): F32 router [n_expert, ne], expert banks gate/up
- * [n_expert][n_ff_exp, ne] and down [n_expert][ne, n_ff_exp] as raw GGUF blocks, softmax gating,
+ * [n_expert][n_ff_exp, ne] and down [n_expert][ne, n_ff_exp] as raw GGUF blocks (Q4_K or Q6_K, `expert_acts_kind`
+ * Super of crates/infr-cpu/src/moe.rs:42-53; Q6_K banks on the int8 path, rows >= 2), softmax gating,
  * top-n_used with ties to the lower expert id, SiLU gate, output-side weighting.  dst is f32 [rows, ne].
  * Optional outputs for parity checks (NULL = not wanted): sel_ids i32 [rows, n_used] in rank order,
  * sel_w f32 [rows, n_used], logits f32 [rows, n_expert]. */

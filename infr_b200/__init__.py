@@ -511,11 +511,13 @@ class CudaBackend:
 
     def moe_ffn(self, x: Buffer, router_x: Buffer, router: Buffer, gate: Buffer, up: Buffer, down: Buffer, dst: Buffer, *,
                 rows: int, ne: int, n_expert: int, n_used: int, n_ff_exp: int, scale: float = 1.0, norm_w: bool = True,
-                wdt: int = Q4K, sel_ids: Optional[Buffer] = None, sel_w: Optional[Buffer] = None,
+                wdt: int = Q4K, down_dt: Optional[int] = None, sel_ids: Optional[Buffer] = None, sel_w: Optional[Buffer] = None,
                 logits: Optional[Buffer] = None, expert_lo: int = 0, n_local: int = 0):
-        """Op::MoeFfn as a direct call.  n_local != 0: expert-parallel slice — the banks hold experts
-        [expert_lo, expert_lo + n_local) and dst gets their contribution only (the ranks' dst add up)."""
-        d = _MoeDesc(rows, ne, n_expert, n_used, n_ff_exp, scale, int(norm_w), F32, wdt, wdt, wdt, expert_lo, n_local)
+        """Op::MoeFfn as a direct call.  wdt: format of the gate / up banks, down_dt: of the down bank (default wdt).
+        n_local != 0: expert-parallel slice — the banks hold experts [expert_lo, expert_lo + n_local) and dst gets
+        their contribution only (the ranks' dst add up)."""
+        d = _MoeDesc(rows, ne, n_expert, n_used, n_ff_exp, scale, int(norm_w), F32, wdt, wdt, wdt if down_dt is None else down_dt,
+                     expert_lo, n_local)
         h = lambda b: b.handle if b is not None else None
         self._check(self.L.infr_cuda_moe_ffn(self.ctx, C.byref(d), x.handle, router_x.handle, router.handle, gate.handle,
                                              up.handle, down.handle, dst.handle, h(sel_ids), h(sel_w), h(logits)))

@@ -519,7 +519,7 @@ Status CudaBackend::moe_ffn_f32(const MoeArgs &a) {
     INFR_STEP(launch_gemv_q4k_f32_sel(a.gate, ids, gu_stride, a.x, (int)nu, g, (int)n_pairs, (int)ne, (int)nff, dev_, stream_), "moe gate f32");
     INFR_STEP(launch_gemv_q4k_f32_sel(a.up, ids, gu_stride, a.x, (int)nu, u, (int)n_pairs, (int)ne, (int)nff, dev_, stream_), "moe up f32");
     INFR_STEP(launch_moe_swiglu_quant(g, u, (int)n_pairs, (int)nff, reinterpret_cast<int8_t *>(b + o_q), reinterpret_cast<float *>(b + o_d),
-                                      reinterpret_cast<int32_t *>(b + o_s), act, stream_), "moe swiglu");
+                                      reinterpret_cast<int32_t *>(b + o_s), nullptr, act, stream_), "moe swiglu");
     INFR_STEP(launch_gemv_q4k_f32_sel(a.down, ids, d_stride, act, 0, y, (int)n_pairs, (int)nff, (int)ne, dev_, stream_), "moe down f32");
     INFR_STEP(launch_moe_combine(y, nullptr, w, (int)rows, (int)nu, (int)ne, a.dst, stream_), "moe combine");
 #undef INFR_STEP
@@ -527,8 +527,10 @@ Status CudaBackend::moe_ffn_f32(const MoeArgs &a) {
 }
 
 Status CudaBackend::moe_ffn(const MoeArgs &a) {
-    if (a.gate_dt != DT_Q4K || a.up_dt != DT_Q4K || a.down_dt != DT_Q4K)
-        return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: expert banks must be Q4_K");
+    auto bank_ok = [](int dt) { return dt == DT_Q4K || dt == DT_Q6K; };
+    if (!bank_ok(a.gate_dt) || !bank_ok(a.up_dt) || !bank_ok(a.down_dt))
+        return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: expert banks must be Q4_K or Q6_K");
+    const bool any_q6 = a.gate_dt == DT_Q6K || a.up_dt == DT_Q6K || a.down_dt == DT_Q6K;
     if (a.ne == 0 || a.ne % 256 || a.n_ff == 0 || a.n_ff % 256)
         return Status::Err(INFR_E_UNSUPPORTED, fmt("moe_ffn: ne=%u and n_ff_exp=%u must be multiples of 256", a.ne, a.n_ff));
     if (a.n_expert == 0 || a.n_expert > 1024 || a.n_used == 0 || a.n_used > 32 || a.n_used > a.n_expert)
@@ -536,6 +538,7 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
     if (a.rows == 0) return Status::Ok();
     if (a.rows < 2 || reference_) {
         if (a.n_local != a.n_expert) return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: a local expert range needs the int8 path (rows >= 2, no reference mode)");
+        if (any_q6) return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: Q6_K expert banks run on the int8 path only (rows >= 2, no reference mode)");
         return moe_ffn_f32(a);
     }
     cudaSetDevice(device_);
@@ -545,7 +548,8 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
     // Experts that see a few dozen rows each run on the tensor-memory GEMM in grouped form (one 64-row slab of an
     // expert's rows per tile column: the expert's weights are unpacked once per slab); with only a handful of rows
     // per expert the 8-row grouped GEMV does less padded work.
-    const bool grouped_gemm = mmq_impl_ == 2 || (mmq_impl_ == 0 && n_pairs >= (size_t)8 * a.n_local);
+    // (a Q6_K bank has no tensor-memory GEMM: such a layer takes 8-row items throughout)
+    const bool grouped_gemm = !any_q6 && (mmq_impl_ == 2 || (mmq_impl_ == 0 && n_pairs >= (size_t)8 * a.n_local));
     const size_t max_slabs = n_pairs / 64 + a.n_local + 1;
     // scratch carve-up (all 256-byte aligned)
     size_t off = 0;
@@ -558,6 +562,7 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
     const size_t o_prow = take(n_pairs * 4), o_pslot = take(n_pairs * 4);
     const size_t o_ie = take(max_items * 4), o_ip = take(max_items * 4), o_ic = take(max_items * 4), o_ni = take(4);
     const size_t o_xq = take(rows * ne), o_xd = take(rows * (ne / 256) * 4), o_xs = take(rows * (ne / 32) * 4);
+    const size_t o_xs16 = any_q6 ? take(rows * (ne / 16) * 4) : 0, o_as16 = any_q6 ? take(n_pairs * (nff / 16) * 4) : 0;
     const size_t o_g = take(n_pairs * nff * 4), o_u = take(n_pairs * nff * 4);
     const size_t o_aq = take(n_pairs * nff), o_ad = take(n_pairs * (nff / 256) * 4), o_as = take(n_pairs * (nff / 32) * 4);
     const size_t o_y = take(n_pairs * ne * 4);
@@ -592,8 +597,15 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
                                 nullptr, stream_),
               "moe bucket");
     // stage A: every distinct row quantised once (lib.rs:2688-2718)
-    INFR_STEP(launch_quantize_q8(a.x, (int)rows, (int)ne, 256, xq, xd, xs, nullptr, nullptr, nullptr, stream_), "moe quantize x");
-    Q8Dev xa{xq, xd, xs, nullptr, 256};
+    int32_t *xs16 = any_q6 ? reinterpret_cast<int32_t *>(b + o_xs16) : nullptr, *as16 = any_q6 ? reinterpret_cast<int32_t *>(b + o_as16) : nullptr;
+    INFR_STEP(launch_quantize_q8(a.x, (int)rows, (int)ne, 256, xq, xd, xs, xs16, nullptr, nullptr, stream_), "moe quantize x");
+    Q8Dev xa{xq, xd, xs, xs16, 256};
+    // one expert bank against the routed rows, 8-row items: Q4_K on the warp matrix unit, Q6_K on the byte-dot kernel
+    auto bank_gemm = [&](int dt, const uint8_t *bank, const Q8Dev &acts, float *out, uint32_t k, uint32_t o, const int32_t *rows_of) {
+        return dt == DT_Q4K ? launch_grouped_q4k_mma(bank, (int)a.n_local, acts, out, (int)k, (int)o, ie, ip, ic, ni, rows_of, (int)max_items, dev_,
+                                                     status_dev_, stream_)
+                            : launch_grouped_q6k(bank, acts, out, (int)k, (int)o, ie, ip, ic, ni, rows_of, (int)max_items, dev_, stream_);
+    };
     if (grouped_gemm) {
         // stage B: both banks read the same gathered activation planes (laid out once); stage C; stage D on the
         // re-quantised pairs; stage E
@@ -604,7 +616,7 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
         INFR_STEP(launch_mmq_ws_q4k_grouped(a.up, (int)a.n_local, xa, b + o_px, u, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_slabs, false, dev_,
                                             status_dev_, stream_),
                   "moe up (grouped gemm)");
-        INFR_STEP(launch_moe_swiglu_quant(g, u, (int)n_pairs, (int)nff, aq, ad, as, nullptr, stream_), "moe swiglu");
+        INFR_STEP(launch_moe_swiglu_quant(g, u, (int)n_pairs, (int)nff, aq, ad, as, nullptr, nullptr, stream_), "moe swiglu");
         Q8Dev aa{aq, ad, as, nullptr, 256};
         INFR_STEP(launch_mmq_ws_q4k_grouped(a.down, (int)a.n_local, aa, b + o_pa, y, (int)nff, (int)ne, ie, ip, ic, ni, nullptr, (int)max_slabs, true, dev_,
                                             status_dev_, stream_),
@@ -614,13 +626,13 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
         return Status::Ok();
     }
     // stage B: gate and up expert GEMMs, rows gathered per pair
-    INFR_STEP(launch_grouped_q4k_mma(a.gate, (int)a.n_local, xa, g, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_items, dev_, status_dev_, stream_), "moe gate");
-    INFR_STEP(launch_grouped_q4k_mma(a.up, (int)a.n_local, xa, u, (int)ne, (int)nff, ie, ip, ic, ni, prow, (int)max_items, dev_, status_dev_, stream_), "moe up");
+    INFR_STEP(bank_gemm(a.gate_dt, a.gate, xa, g, (uint32_t)ne, (uint32_t)nff, prow), "moe gate");
+    INFR_STEP(bank_gemm(a.up_dt, a.up, xa, u, (uint32_t)ne, (uint32_t)nff, prow), "moe up");
     // stage C: SwiGLU and re-quantisation per pair
-    INFR_STEP(launch_moe_swiglu_quant(g, u, (int)n_pairs, (int)nff, aq, ad, as, nullptr, stream_), "moe swiglu");
-    Q8Dev aa{aq, ad, as, nullptr, 256};
+    INFR_STEP(launch_moe_swiglu_quant(g, u, (int)n_pairs, (int)nff, aq, ad, as, as16, nullptr, stream_), "moe swiglu");
+    Q8Dev aa{aq, ad, as, as16, 256};
     // stage D: down GEMMs; stage E: rank-order combine
-    INFR_STEP(launch_grouped_q4k_mma(a.down, (int)a.n_local, aa, y, (int)nff, (int)ne, ie, ip, ic, ni, nullptr, (int)max_items, dev_, status_dev_, stream_), "moe down");
+    INFR_STEP(bank_gemm(a.down_dt, a.down, aa, y, (uint32_t)nff, (uint32_t)ne, nullptr), "moe down");
     INFR_STEP(launch_moe_combine(y, pslot, w, (int)rows, (int)nu, (int)ne, a.dst, stream_), "moe combine");
 #undef INFR_STEP
     return Status::Ok();

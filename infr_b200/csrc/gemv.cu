@@ -115,17 +115,18 @@ __global__ void __launch_bounds__(kThreads) gemv_q4k_q8_kernel(const uint8_t *__
 // 4 bytes of ql[l], 4 of ql[l+32], 4 of qh[l] -> the 16 elements l, l+32, l+64, l+96 (x4).  Two blocks
 // per warp step.
 // ------------------------------------------------------------------------------------------------
+// Body shared by the plain kernel and the expert-grouped one: token t reads activation row row_of[row0 + t]
+// (row0 + t without a list) and writes row t of `y`, which the caller has offset to its first output row.
 template <int M, bool DUMP>
-__global__ void __launch_bounds__(kThreads) gemv_q6k_q8_kernel(const uint8_t *__restrict__ W, Q8Dev a,
-                                                               float *__restrict__ y, int m, int in_f,
-                                                               int out_f, int32_t *__restrict__ acc_out) {
+__device__ __forceinline__ void q6k_q8_body(const uint8_t *__restrict__ W, const Q8Dev &a, float *__restrict__ y, int m, int in_f,
+                                            int out_f, int32_t *__restrict__ acc_out, const int32_t *row_of, int row0) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int nb = in_f >> 8;
     const int tok_stride = (nb + 1) / 2 * 512;  // bytes of staged codes per token (block pairs)
     int8_t *s_qa = reinterpret_cast<int8_t *>(smem);
     float *s_d = reinterpret_cast<float *>(smem + (size_t)M * tok_stride);
     int32_t *s_bs = reinterpret_cast<int32_t *>(s_d + M * nb);  // per-16 sums
-    stage_q8<DT_Q6K>(a, m, M, in_f, s_qa, s_d, s_bs);
+    stage_q8<DT_Q6K>(a, m, M, in_f, s_qa, s_d, s_bs, row_of, row0);
     __syncthreads();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -191,6 +192,27 @@ __global__ void __launch_bounds__(kThreads) gemv_q6k_q8_kernel(const uint8_t *__
             }
         }
     }
+}
+
+template <int M, bool DUMP>
+__global__ void __launch_bounds__(kThreads) gemv_q6k_q8_kernel(const uint8_t *__restrict__ W, Q8Dev a,
+                                                               float *__restrict__ y, int m, int in_f,
+                                                               int out_f, int32_t *__restrict__ acc_out) {
+    q6k_q8_body<M, DUMP>(W, a, y, m, in_f, out_f, acc_out, nullptr, 0);
+}
+
+// Expert-grouped form (mixture of experts): blockIdx.y walks the device-built list of work items, each up to 8
+// routed pairs of one expert; the bank holds the experts' [out_f, in_f] matrices back to back; pair p reads
+// activation row pair_row[p] (or p) and writes y row p.
+__global__ void __launch_bounds__(kThreads) gemv_q6k_q8_grouped_kernel(const uint8_t *__restrict__ bank, Q8Dev a, float *__restrict__ y,
+                                                                       int in_f, int out_f, const int *__restrict__ item_expert,
+                                                                       const int *__restrict__ item_p0, const int *__restrict__ item_cnt,
+                                                                       const int *__restrict__ n_items, const int *__restrict__ pair_row) {
+    const int item = blockIdx.y;
+    if (item >= *n_items) return;
+    const int p0 = item_p0[item];
+    const size_t w_off = (size_t)item_expert[item] * out_f * (size_t)(in_f >> 8) * 210;
+    q6k_q8_body<8, false>(bank + w_off, a, y + (size_t)p0 * out_f, item_cnt[item], in_f, out_f, nullptr, pair_row, p0);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -534,6 +556,22 @@ cudaError_t launch_gemv_q4k_f32_sel(const uint8_t *bank, const int32_t *sel, siz
     const int cap = (dev.sm_count * 4 + n_pairs - 1) / n_pairs;
     if (gx > cap) gx = cap < 1 ? 1 : cap;
     gemv_q4k_f32_kernel<1><<<dim3((unsigned)gx, (unsigned)n_pairs), kThreads, smem, st>>>(bank, x, y, 1, in_f, out_f, SelArgs{sel, w_stride, x_div});
+    return cudaGetLastError();
+}
+
+cudaError_t launch_grouped_q6k(const uint8_t *bank, const Q8Dev &a, float *y, int in_f, int out_f, const int *item_expert, const int *item_p0,
+                               const int *item_cnt, const int *n_items, const int *pair_row, int max_items, const DeviceInfo &dev,
+                               cudaStream_t st) {
+    if (in_f % 256 || max_items < 1 || !a.sums16 || a.gran != 256) return cudaErrorInvalidValue;
+    const size_t smem = q8_smem(DT_Q6K, 8, in_f);
+    if (smem > (size_t)dev.max_smem_optin) return cudaErrorInvalidValue;
+    cudaError_t e = set_smem(gemv_q6k_q8_grouped_kernel, smem);
+    if (e != cudaSuccess) return e;
+    // a few CTAs per item (the staged activations are copied by each of them); the SMs fill up across items
+    int gx = (out_f + kWarps - 1) / kWarps;
+    if (gx > 8) gx = 8;
+    gemv_q6k_q8_grouped_kernel<<<dim3((unsigned)gx, (unsigned)max_items), kThreads, smem, st>>>(bank, a, y, in_f, out_f, item_expert, item_p0,
+                                                                                              item_cnt, n_items, pair_row);
     return cudaGetLastError();
 }
 

@@ -63,14 +63,16 @@ __device__ __forceinline__ void k4_pair(uint32_t y, uint32_t z, uint32_t w, int 
 //   Q2_0 : every 16-byte group is transposed 4x4 so word i holds elements (i, 4+i, 8+i, 12+i), the
 //          order in which a 2-bit code word yields its fields.
 // ------------------------------------------------------------------------------------------------
+// Token t reads activation row row_of[row0 + t] (row_of == nullptr: row row0 + t) of the quantised rows in `a`.
 template <int DT>
 __device__ __forceinline__ void stage_q8(const Q8Dev &a, int m, int M, int in_f, int8_t *s_qa, float *s_d,
-                                         int32_t *s_sum) {
+                                         int32_t *s_sum, const int32_t *row_of = nullptr, int row0 = 0) {
     const int units = in_f / 16;
+    auto src_row = [&](int t) -> size_t { return (size_t)(row_of ? row_of[row0 + t] : row0 + t); };
     for (int idx = threadIdx.x; idx < M * units; idx += blockDim.x) {
         const int t = idx / units, u = idx - t * units;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (t < m) v = *reinterpret_cast<const uint4 *>(a.qs + (size_t)t * in_f + (size_t)u * 16);
+        if (t < m) v = *reinterpret_cast<const uint4 *>(a.qs + src_row(t) * in_f + (size_t)u * 16);
         if (DT == DT_Q4K) {
             const int b = u >> 4, uu = u & 15, s = uu >> 1, h = uu & 1;
             const int nu = (s & 1) * 8 + (s >> 1) * 2 + h;
@@ -98,13 +100,13 @@ __device__ __forceinline__ void stage_q8(const Q8Dev &a, int m, int M, int in_f,
     const int nd = in_f / a.gran;
     for (int idx = threadIdx.x; idx < M * nd; idx += blockDim.x) {
         const int t = idx / nd, i = idx - t * nd;
-        s_d[idx] = t < m ? a.d[(size_t)t * nd + i] : 0.f;
+        s_d[idx] = t < m ? a.d[src_row(t) * nd + i] : 0.f;
     }
     const int ns = DT == DT_Q6K ? in_f / 16 : in_f / 32;
     const int32_t *src = DT == DT_Q6K ? a.sums16 : a.sums;
     for (int idx = threadIdx.x; idx < M * ns; idx += blockDim.x) {
         const int t = idx / ns, i = idx - t * ns;
-        s_sum[idx] = t < m ? src[(size_t)t * ns + i] : 0;
+        s_sum[idx] = t < m ? src[src_row(t) * ns + i] : 0;
     }
 }
 

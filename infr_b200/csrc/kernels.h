@@ -89,6 +89,10 @@ cudaError_t launch_grouped_q4k_mma(const uint8_t *bank, int n_experts, const Q8D
                                    const int *item_expert, const int *item_p0, const int *item_cnt, const int *n_items,
                                    const int *pair_row, int max_items, const DeviceInfo &dev, uint32_t *status,
                                    cudaStream_t st);
+// The same grouped product for a Q6_K bank (direct-load byte-dot kernel, any row length); `a` needs the sums per 16.
+cudaError_t launch_grouped_q6k(const uint8_t *bank, const Q8Dev &a, float *y, int in_f, int out_f, const int *item_expert, const int *item_p0,
+                               const int *item_cnt, const int *n_items, const int *pair_row, int max_items, const DeviceInfo &dev,
+                               cudaStream_t st);
 cudaError_t launch_moe_router(const float *router, const float *x, float *logits, int rows, int ne, int n_expert,
                               cudaStream_t st);
 cudaError_t launch_moe_route(const float *logits, int rows, int n_expert, int n_used, float scale, int norm_w,
@@ -97,7 +101,7 @@ cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int 
                               int32_t *pair_row, int32_t *pair_of_slot, int32_t *item_expert, int32_t *item_p0, int32_t *item_cnt,
                               int32_t *n_items, int32_t *counts_out, cudaStream_t st);
 cudaError_t launch_moe_swiglu_quant(const float *gate, const float *up, int n_pairs, int nff, int8_t *qs, float *d,
-                                    int32_t *sums, float *act_out, cudaStream_t st);
+                                    int32_t *sums, int32_t *sums16, float *act_out, cudaStream_t st);
 cudaError_t launch_moe_combine(const float *y_pairs, const int32_t *pair_of_slot, const float *sel_w, int rows, int n_used,
                                int ne, float *out, cudaStream_t st);
 

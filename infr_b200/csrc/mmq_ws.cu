@@ -50,9 +50,6 @@ constexpr int kRing = 4;                      // depth of the row-scale ring rea
 constexpr int kSmem = kStages * kStageBytes + 2 * kMinBytes + kRing * kTM * 4;
 constexpr int kThreadsWs = 20 * 32;
 constexpr uint32_t kSpin = 1u << 22;
-// Suspend-time hint of every mbarrier.try_wait: a waiting role is parked by the hardware until its phase completes
-// (or this many nanoseconds pass) instead of spinning in the issue slots the unpack and epilogue warps need.
-constexpr uint32_t kSuspendNs = 500;
 // tensor-memory columns
 constexpr uint32_t kColMin = 256, kColA = 320, kSlotCols = 64, kSlots = 3;
 
@@ -106,9 +103,9 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int *dead) {
     for (uint32_t i = 0; i < kSpin; i++) {
         uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok)
-                     : "r"(bar), "r"(parity), "r"(kSuspendNs)
+                     : "r"(bar), "r"(parity)
                      : "memory");
         if (ok) return true;
         if ((i & 1023u) == 1023u && *dead) return false;
@@ -123,9 +120,9 @@ __device__ __forceinline__ bool wait_multi(uint32_t bar, uint32_t parity, bool n
     for (uint32_t i = 0; i < kSpin; i++) {
         if (pending) {
             uint32_t ok;
-            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                          : "=r"(ok)
-                         : "r"(bar), "r"(parity), "r"(kSuspendNs)
+                         : "r"(bar), "r"(parity)
                          : "memory");
             pending = !ok;
         }
@@ -215,9 +212,9 @@ namespace {
 __device__ __forceinline__ bool wait_plain(uint32_t bar, uint32_t parity, uint32_t limit) {
     for (uint32_t i = 0; i < limit; i++) {
         uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok)
-                     : "r"(bar), "r"(parity), "r"(kSuspendNs)
+                     : "r"(bar), "r"(parity)
                      : "memory");
         if (ok) return true;
     }

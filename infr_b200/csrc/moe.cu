@@ -28,7 +28,20 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const float *__restrict
     const float *w = router + (size_t)e * ne, *xr = x + (size_t)r * ne;
     const int chunks = ne / 8;
     float acc = 0.f;
-    for (int c = 0; c < chunks; c++) acc = fmaf(w[c * 8 + j], xr[c * 8 + j], acc);
+    // eight chunks are fetched before the first of them is multiplied: the loop is bound by the latency of its loads
+    // (a lane touches 4 bytes of a line per chunk), the order of the multiply-adds is the CPU's
+    int c = 0;
+    for (; c + 8 <= chunks; c += 8) {
+        float wv[8], xv[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            wv[k] = __ldg(w + (c + k) * 8 + j);
+            xv[k] = __ldg(xr + (c + k) * 8 + j);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc = fmaf(wv[k], xv[k], acc);
+    }
+    for (; c < chunks; c++) acc = fmaf(w[c * 8 + j], xr[c * 8 + j], acc);
     // s = ((((acc0 + acc1) + acc2) + ...) + acc7), then the FMA tail
     float s = 0.f;
 #pragma unroll
@@ -122,13 +135,20 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
                                                           int32_t *__restrict__ pair_row, int32_t *__restrict__ pair_of_slot,
                                                           int32_t *__restrict__ item_expert, int32_t *__restrict__ item_p0,
                                                           int32_t *__restrict__ item_cnt, int32_t *__restrict__ n_items,
-                                                          int32_t *__restrict__ counts_out) {
+                                                          int32_t *__restrict__ counts_out, int staged) {
     __shared__ int s_cnt[1024], s_off[1024], s_ioff[1024];
+    extern __shared__ int32_t s_ids[];  // the selected experts, read many times below: once from global memory
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_pairs = rows * n_used;
+    const int32_t *ids = sel_ids;  // (lists too long for shared memory are scanned where they are)
+    if (staged) {
+        for (int i = threadIdx.x; i < n_pairs; i += 1024) s_ids[i] = sel_ids[i];
+        ids = s_ids;
+    }
+    __syncthreads();
     // pairs whose expert is not listed below (another rank's, or an id outside the bank) contribute nothing
     for (int i = threadIdx.x; i < n_pairs; i += 1024) {
-        const int e = sel_ids[i];
+        const int e = ids[i];
         if (e < e_lo || e >= e_lo + n_local || e < 0 || e >= n_expert) pair_of_slot[i] = -1;
     }
     for (int e = warp; e < n_expert; e += 32) {
@@ -139,7 +159,7 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
         }
         for (int i0 = 0; i0 < n_pairs; i0 += 32) {
             const int i = i0 + lane;
-            cnt += __popc(__ballot_sync(0xffffffffu, i < n_pairs && sel_ids[i] == e));
+            cnt += __popc(__ballot_sync(0xffffffffu, i < n_pairs && ids[i] == e));
         }
         if (lane == 0) s_cnt[e] = cnt;
     }
@@ -162,7 +182,7 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
         int p = s_off[e];
         for (int i0 = 0; i0 < n_pairs; i0 += 32) {
             const int i = i0 + lane;
-            const bool hit = i < n_pairs && sel_ids[i] == e;
+            const bool hit = i < n_pairs && ids[i] == e;
             const uint32_t mask = __ballot_sync(0xffffffffu, hit);
             if (hit) {
                 const int q = p + __popc(mask & ((1u << lane) - 1u));
@@ -183,7 +203,8 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
 // One warp per (pair, 256-block): act = silu(gate) * up, then quantize_q8 of that block.
 __global__ void __launch_bounds__(256) moe_swiglu_quant_kernel(const float *__restrict__ gate, const float *__restrict__ up,
                                                                int n_pairs, int nff, int8_t *__restrict__ qs, float *__restrict__ d,
-                                                               int32_t *__restrict__ sums, float *__restrict__ act_out) {
+                                                               int32_t *__restrict__ sums, int32_t *__restrict__ sums16,
+                                                               float *__restrict__ act_out) {
     const int lane = threadIdx.x & 31;
     const int nbk = nff / 256;
     const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -225,6 +246,7 @@ __global__ void __launch_bounds__(256) moe_swiglu_quant_kernel(const float *__re
     pk.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
     *reinterpret_cast<uint2 *>(qs + base) = pk;
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    if (sums16 && (lane & 1) == 0) sums16[((size_t)p * nbk + b) * 16 + (lane >> 1)] = sum;  // Q6_K banks: sums per 16 codes
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     if ((lane & 3) == 0) sums[((size_t)p * nbk + b) * 8 + (lane >> 2)] = sum;
     if (lane == 0) d[(size_t)p * nbk + b] = dd;
@@ -268,16 +290,21 @@ cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int 
                               int32_t *pair_row, int32_t *pair_of_slot, int32_t *item_expert, int32_t *item_p0, int32_t *item_cnt,
                               int32_t *n_items, int32_t *counts_out, cudaStream_t st) {
     if (n_expert > 1024 || item_rows < 1) return cudaErrorInvalidValue;
-    moe_bucket_kernel<<<1, 1024, 0, st>>>(sel_ids, rows, n_used, n_expert, e_lo, n_local, item_rows, pair_row, pair_of_slot, item_expert, item_p0, item_cnt,
-                                          n_items, counts_out);
+    size_t ids_bytes = (size_t)rows * n_used * 4;
+    const int staged = ids_bytes <= 160 * 1024;
+    if (!staged) ids_bytes = 0;
+    cudaError_t e = cudaFuncSetAttribute(moe_bucket_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ids_bytes);
+    if (e != cudaSuccess) return e;
+    moe_bucket_kernel<<<1, 1024, ids_bytes, st>>>(sel_ids, rows, n_used, n_expert, e_lo, n_local, item_rows, pair_row, pair_of_slot, item_expert, item_p0, item_cnt,
+                                          n_items, counts_out, staged);
     return cudaGetLastError();
 }
 
 cudaError_t launch_moe_swiglu_quant(const float *gate, const float *up, int n_pairs, int nff, int8_t *qs, float *d,
-                                    int32_t *sums, float *act_out, cudaStream_t st) {
+                                    int32_t *sums, int32_t *sums16, float *act_out, cudaStream_t st) {
     if (nff % 256) return cudaErrorInvalidValue;
     const long long warps = (long long)n_pairs * (nff / 256);
-    moe_swiglu_quant_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(gate, up, n_pairs, nff, qs, d, sums, act_out);
+    moe_swiglu_quant_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(gate, up, n_pairs, nff, qs, d, sums, sums16, act_out);
     return cudaGetLastError();
 }
 

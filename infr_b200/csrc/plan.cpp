@@ -151,7 +151,7 @@ Status CudaBackend::compile(const infr_graph_desc &g, infr_cuda_plan **out) {
             if (op.u[5] || op.u[6] || op.u[7] || op.u[8]) return unsupported(i, "MoeFfn with fused gate/up, weight_before, a non-SiLU activation or non-softmax gating");
             if (dt(op.t[2]) != DT_F32) return unsupported(i, "MoeFfn router weights must be F32");
             for (int k = 3; k <= 5; k++)
-                if (dt(op.t[k]) != DT_Q4K) return unsupported(i, "MoeFfn expert banks must be Q4_K");
+                if (dt(op.t[k]) != DT_Q4K && dt(op.t[k]) != DT_Q6K) return unsupported(i, "MoeFfn expert banks must be Q4_K or Q6_K");
             break;
         case INFR_OP_RMS_NORM:
             if (op.u[0] == 0 || op.u[1] == 0) return fail(Status::Err(INFR_E_INVALID, pfmt("compile: op %u: RmsNorm of %u rows x %u", i, op.u[0], op.u[1])));

@@ -194,7 +194,7 @@ class Oracle:
         return (out, qsum) if want_qsum else out
 
     # ---- Op::MoeFfn ------------------------------------------------------------------------
-    def moe_ffn(self, x, router, gate, up, down, *, rows, ne, n_expert, n_used, n_ff_exp, wdt=Q4K,
+    def moe_ffn(self, x, router, gate, up, down, *, rows, ne, n_expert, n_used, n_ff_exp, wdt=Q4K, down_dt=None,
                 scale=1.0, norm_w=True, reference=False, router_x=None, threads=0):
         x = np.ascontiguousarray(x, np.float32).ravel()
         rx = x if router_x is None else np.ascontiguousarray(router_x, np.float32).ravel()
@@ -207,7 +207,7 @@ class Oracle:
         wts = np.empty((rows, n_used), np.float32)
         logits = np.empty((rows, n_expert), np.float32)
         rc = self.L.orc_moe_ffn(_p(x, _f32p), _p(rx, _f32p), rows, ne, n_expert, n_used, n_ff_exp, F32,
-                                _p(router, _u8p), wdt, _p(gate, _u8p), wdt, _p(up, _u8p), wdt,
+                                _p(router, _u8p), wdt, _p(gate, _u8p), wdt, _p(up, _u8p), wdt if down_dt is None else down_dt,
                                 _p(down, _u8p), scale, int(norm_w), int(reference), _p(dst, _f32p),
                                 _p(ids, _i32p), _p(wts, _f32p), _p(logits, _f32p), threads)
         assert rc == 0

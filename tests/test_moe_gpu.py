@@ -41,7 +41,7 @@ def _make_banks(n_expert, nff, ne, seed):
     return gate, up, down
 
 
-def _run(backend, x, router, gate, up, down, rows, ne, n_expert, n_used, nff, norm_w=True, scale=1.0):
+def _run(backend, x, router, gate, up, down, rows, ne, n_expert, n_used, nff, norm_w=True, scale=1.0, wdt=Q4K, down_dt=None):
     xb = backend.from_numpy(x)
     rb = backend.from_numpy(router)
     gb = backend.from_numpy(gate, infr_b200.USAGE_WEIGHTS)
@@ -52,7 +52,7 @@ def _run(backend, x, router, gate, up, down, rows, ne, n_expert, n_used, nff, no
     w = backend.alloc(rows * n_used * 4)
     lg = backend.alloc(rows * n_expert * 4)
     backend.moe_ffn(xb, xb, rb, gb, ub, db, dst, rows=rows, ne=ne, n_expert=n_expert, n_used=n_used, n_ff_exp=nff,
-                    scale=scale, norm_w=norm_w, sel_ids=ids, sel_w=w, logits=lg)
+                    scale=scale, norm_w=norm_w, sel_ids=ids, sel_w=w, logits=lg, wdt=wdt, down_dt=down_dt)
     out = (backend.download(dst, np.float32).reshape(rows, ne), backend.download(ids, np.int32).reshape(rows, n_used),
            backend.download(w, np.float32).reshape(rows, n_used), backend.download(lg, np.float32).reshape(rows, n_expert))
     for b in (xb, rb, gb, ub, db, dst, ids, w, lg):
@@ -81,6 +81,26 @@ def test_moe_ffn_matches_production_cpu(backend, gemm_backend, oracle, rows, ne,
     np.testing.assert_allclose(w, o_w, rtol=2e-6, atol=1e-7)
     rel = fx.rel_l2(got, want)
     assert rel < 1e-3, rel
+    assert np.abs(want).max() > 1e-4
+
+
+@pytest.mark.parametrize("gu_dt,down_dt", [(Q4K, infr_b200.Q6K), (infr_b200.Q6K, infr_b200.Q6K)], ids=["q4k-gate-up-q6k-down", "all-q6k"])
+def test_moe_q6k_expert_banks(backend, oracle, gu_dt, down_dt):
+    """Expert banks in Q6_K (`expert_acts_kind` Super, crates/infr-cpu/src/moe.rs:42-53): the Q4_K_M mix keeps the down
+    experts in Q6_K.  n_ff_exp = 768 makes the down rows 3 blocks = 630 bytes long (not a multiple of 16)."""
+    rows, ne, n_expert, n_used, nff = 21, 512, 8, 2, 768
+    gate = np.concatenate([synth.weight(gu_dt, nff, ne, 400 + 3 * e) for e in range(n_expert)])
+    up = np.concatenate([synth.weight(gu_dt, nff, ne, 401 + 3 * e) for e in range(n_expert)])
+    down = np.concatenate([synth.weight(down_dt, ne, nff, 402 + 3 * e) for e in range(n_expert)])
+    router = synth.normal(7, (n_expert, ne), 1.0 / np.sqrt(ne))
+    x = synth.normal(8, (rows, ne))
+    got, ids, w, lg = _run(backend, x, router, gate, up, down, rows, ne, n_expert, n_used, nff, wdt=gu_dt, down_dt=down_dt)
+    want, o_ids, o_w, o_lg = oracle.moe_ffn(x, router, gate, up, down, rows=rows, ne=ne, n_expert=n_expert, n_used=n_used, n_ff_exp=nff,
+                                            wdt=gu_dt, down_dt=down_dt)
+    np.testing.assert_array_equal(lg.view(np.uint32), o_lg.view(np.uint32))
+    np.testing.assert_array_equal(ids, o_ids)
+    np.testing.assert_allclose(w, o_w, rtol=2e-6, atol=1e-7)
+    assert fx.rel_l2(got, want) < 1e-3
     assert np.abs(want).max() > 1e-4
 
 

@@ -536,6 +536,8 @@ Status CudaBackend::moe_ffn(const MoeArgs &a) {
     if (a.n_expert == 0 || a.n_expert > 1024 || a.n_used == 0 || a.n_used > 32 || a.n_used > a.n_expert)
         return Status::Err(INFR_E_INVALID, fmt("moe_ffn: n_expert=%u (<=1024), n_used=%u (<=32)", a.n_expert, a.n_used));
     if (a.rows == 0) return Status::Ok();
+    if (((size_t)a.rows * a.n_used + 31) / 32 * a.n_expert * 4 > (size_t)200 * 1024)
+        return Status::Err(INFR_E_UNSUPPORTED, fmt("moe_ffn: %u rows x %u experts per row exceed what one call sorts (split the rows)", a.rows, a.n_used));
     if (a.rows < 2 || reference_) {
         if (a.n_local != a.n_expert) return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: a local expert range needs the int8 path (rows >= 2, no reference mode)");
         if (any_q6) return Status::Err(INFR_E_UNSUPPORTED, "moe_ffn: Q6_K expert banks run on the int8 path only (rows >= 2, no reference mode)");

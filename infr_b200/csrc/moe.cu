@@ -17,37 +17,57 @@
 
 namespace infr {
 
-// logits[r, e] = dot(router[e, :], x[r, :]).  Eight lanes per dot product replay the eight
-// accumulators of the CPU `dot`; four dot products per warp.
+// logits[r, e] = dot(router[e, :], x[r, :]).  Eight lanes per dot product replay the eight accumulators of the CPU
+// `dot` (lane j takes elements j, 8 + j, ... in order, the lanes are then summed in order, the tail is added by fused
+// multiply-adds).  A block computes 8 rows x 16 experts; a group of eight lanes holds a 2 x 2 corner of it, so every
+// shared-memory read feeds two multiply-adds.  Rows and router rows are staged 256 columns at a time, coalesced;
+// the row pitch (260 words) puts the four groups of a warp on disjoint banks.
+constexpr int kRtRows = 8, kRtExperts = 16, kRtK = 256, kRtPitch = kRtK + 4;
 __global__ void __launch_bounds__(256) moe_router_kernel(const float *__restrict__ router, const float *__restrict__ x,
                                                          float *__restrict__ logits, int rows, int ne, int n_expert) {
-    const int lane = threadIdx.x & 31, sub = lane >> 3, j = lane & 7;
-    const long long dot_id = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 4 + sub;
-    const bool live = dot_id < (long long)rows * n_expert;
-    const int r = live ? (int)(dot_id / n_expert) : 0, e = live ? (int)(dot_id % n_expert) : 0;
-    const float *w = router + (size_t)e * ne, *xr = x + (size_t)r * ne;
-    const int chunks = ne / 8;
-    float acc = 0.f;
-    // eight chunks are fetched before the first of them is multiplied: the loop is bound by the latency of its loads
-    // (a lane touches 4 bytes of a line per chunk), the order of the multiply-adds is the CPU's
-    int c = 0;
-    for (; c + 8 <= chunks; c += 8) {
-        float wv[8], xv[8];
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            wv[k] = __ldg(w + (c + k) * 8 + j);
-            xv[k] = __ldg(xr + (c + k) * 8 + j);
+    __shared__ float s_x[kRtRows * kRtPitch], s_w[kRtExperts * kRtPitch];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, j = lane & 7;
+    const int rp = warp >> 1, ep = (warp & 1) * 4 + grp;  // row pair 0..3, expert pair 0..7
+    const int r0 = blockIdx.x * kRtRows, e0 = blockIdx.y * kRtExperts;
+    const int chunks = ne / 8;  // whole groups of eight columns; the rest is the tail
+    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    for (int k0 = 0; k0 < chunks * 8; k0 += kRtK) {
+        const int kc = min(kRtK, chunks * 8 - k0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < kRtRows * kRtK; i += 256) {
+            const int r = i / kRtK, k = i - r * kRtK;
+            s_x[r * kRtPitch + k] = (r0 + r < rows && k < kc) ? x[(size_t)(r0 + r) * ne + k0 + k] : 0.f;
         }
-#pragma unroll
-        for (int k = 0; k < 8; k++) acc = fmaf(wv[k], xv[k], acc);
+        for (int i = threadIdx.x; i < kRtExperts * kRtK; i += 256) {
+            const int e = i / kRtK, k = i - e * kRtK;
+            s_w[e * kRtPitch + k] = (e0 + e < n_expert && k < kc) ? router[(size_t)(e0 + e) * ne + k0 + k] : 0.f;
+        }
+        __syncthreads();
+        const float *xa = s_x + (2 * rp) * kRtPitch + j, *xb = xa + kRtPitch;
+        const float *wa = s_w + (2 * ep) * kRtPitch + j, *wb = wa + kRtPitch;
+        for (int c = 0; c < kc / 8; c++) {
+            const float x0 = xa[c * 8], x1 = xb[c * 8], w0 = wa[c * 8], w1 = wb[c * 8];
+            acc[0][0] = fmaf(w0, x0, acc[0][0]);
+            acc[0][1] = fmaf(w1, x0, acc[0][1]);
+            acc[1][0] = fmaf(w0, x1, acc[1][0]);
+            acc[1][1] = fmaf(w1, x1, acc[1][1]);
+        }
     }
-    for (; c < chunks; c++) acc = fmaf(w[c * 8 + j], xr[c * 8 + j], acc);
-    // s = ((((acc0 + acc1) + acc2) + ...) + acc7), then the FMA tail
-    float s = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; k++) s = __fadd_rn(s, __shfl_sync(0xffffffffu, acc, sub * 8 + k));
-    for (int i = chunks * 8; i < ne; i++) s = fmaf(w[i], xr[i], s);
-    if (live && j == 0) logits[(size_t)r * n_expert + e] = s;
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            // s = ((((acc0 + acc1) + acc2) + ...) + acc7), then the FMA tail
+            float sum = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; k++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, acc[a][b], grp * 8 + k));
+            const int r = r0 + 2 * rp + a, e = e0 + 2 * ep + b;
+            if (r < rows && e < n_expert) {
+                const float *w = router + (size_t)e * ne, *xr = x + (size_t)r * ne;
+                for (int i = chunks * 8; i < ne; i++) sum = fmaf(w[i], xr[i], sum);
+                if (j == 0) logits[(size_t)r * n_expert + e] = sum;
+            }
+        }
 }
 
 // One warp per row.  n_expert <= 1024.
@@ -123,10 +143,9 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
     }
 }
 
-// One CTA of 32 warps.  Warp w owns experts w, w+32, ...: it counts an expert's pairs with ballots over
-// 32 pairs at a time, the block scans the counts, then the warp lists the pairs in (row, rank) order
-// (ballot + prefix popcount keeps the order) and cuts them into work items of up to `item_rows` rows (8 for the
-// grouped GEMV, 64 = one token tile for the grouped tensor-memory GEMM).
+// One CTA of 32 warps lists the routed pairs by expert, in (row, rank) order inside an expert, and cuts every
+// expert's pairs into work items of up to `item_rows` rows (8 for the grouped GEMV, 64 = one token tile for the
+// grouped tensor-memory GEMM).
 //   pair_row[p], pair_of_slot[r * n_used + rank] = p, item_{expert,p0,cnt}[], n_items
 // Expert parallelism: only experts [e_lo, e_lo + n_local) are listed (item_expert is the index inside this
 // rank's banks); pairs routed elsewhere get pair_of_slot = -1 and contribute nothing to this rank's output.
@@ -135,33 +154,38 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
                                                           int32_t *__restrict__ pair_row, int32_t *__restrict__ pair_of_slot,
                                                           int32_t *__restrict__ item_expert, int32_t *__restrict__ item_p0,
                                                           int32_t *__restrict__ item_cnt, int32_t *__restrict__ n_items,
-                                                          int32_t *__restrict__ counts_out, int staged) {
+                                                          int32_t *__restrict__ counts_out, int n_chunks) {
+    // A stable counting sort over chunks of 32 pairs: hist[chunk][expert] = pairs of the expert inside the chunk
+    // (lanes with the same expert find each other with a match), an exclusive scan down the chunks gives the place of
+    // a chunk's first such pair inside its expert, and a pair's place is that plus its rank among the lanes before it:
+    // (row, rank) order is kept and the work is linear in the number of pairs.
     __shared__ int s_cnt[1024], s_off[1024], s_ioff[1024];
-    extern __shared__ int32_t s_ids[];  // the selected experts, read many times below: once from global memory
+    extern __shared__ int32_t s_hist[];  // [n_chunks][n_expert]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_pairs = rows * n_used;
-    const int32_t *ids = sel_ids;  // (lists too long for shared memory are scanned where they are)
-    if (staged) {
-        for (int i = threadIdx.x; i < n_pairs; i += 1024) s_ids[i] = sel_ids[i];
-        ids = s_ids;
+    for (int i = threadIdx.x; i < n_chunks * n_expert; i += 1024) s_hist[i] = 0;
+    __syncthreads();
+    // the expert of pair i as this rank sees it: -1 for another rank's expert or an id outside the bank
+    auto local_expert = [&](int i) {
+        if (i >= n_pairs) return -1;
+        const int e = sel_ids[i];
+        return (e < e_lo || e >= e_lo + n_local || e < 0 || e >= n_expert) ? -1 : e;
+    };
+    for (int c = warp; c < n_chunks; c += 32) {
+        const int e = local_expert(c * 32 + lane);
+        const uint32_t same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && (same & ((1u << lane) - 1u)) == 0) s_hist[c * n_expert + e] = __popc(same);
     }
     __syncthreads();
-    // pairs whose expert is not listed below (another rank's, or an id outside the bank) contribute nothing
-    for (int i = threadIdx.x; i < n_pairs; i += 1024) {
-        const int e = ids[i];
-        if (e < e_lo || e >= e_lo + n_local || e < 0 || e >= n_expert) pair_of_slot[i] = -1;
-    }
-    for (int e = warp; e < n_expert; e += 32) {
-        int cnt = 0;
-        if (e < e_lo || e >= e_lo + n_local) {  // not this rank's expert: no pairs, no items
-            if (lane == 0) s_cnt[e] = 0;
-            continue;
+    for (int e = threadIdx.x; e < n_expert; e += 1024) {
+        int run = 0;
+        for (int c = 0; c < n_chunks; c++) {
+            const int t = s_hist[c * n_expert + e];
+            s_hist[c * n_expert + e] = run;
+            run += t;
         }
-        for (int i0 = 0; i0 < n_pairs; i0 += 32) {
-            const int i = i0 + lane;
-            cnt += __popc(__ballot_sync(0xffffffffu, i < n_pairs && ids[i] == e));
-        }
-        if (lane == 0) s_cnt[e] = cnt;
+        s_cnt[e] = run;
+        if (counts_out) counts_out[e] = run;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -175,22 +199,21 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
         *n_items = ioff;
     }
     __syncthreads();
+    for (int c = warp; c < n_chunks; c += 32) {
+        const int i = c * 32 + lane;
+        const int e = local_expert(i);
+        const uint32_t same = __match_any_sync(0xffffffffu, e);
+        if (i < n_pairs) {
+            int q = -1;  // pairs routed to an expert that is not listed contribute nothing to this rank's output
+            if (e >= 0) {
+                q = s_off[e] + s_hist[c * n_expert + e] + __popc(same & ((1u << lane) - 1u));
+                pair_row[q] = i / n_used;
+            }
+            pair_of_slot[i] = q;
+        }
+    }
     for (int e = warp; e < n_expert; e += 32) {
         const int cnt = s_cnt[e];
-        if (counts_out && lane == 0) counts_out[e] = cnt;
-        if (e < e_lo || e >= e_lo + n_local) continue;
-        int p = s_off[e];
-        for (int i0 = 0; i0 < n_pairs; i0 += 32) {
-            const int i = i0 + lane;
-            const bool hit = i < n_pairs && ids[i] == e;
-            const uint32_t mask = __ballot_sync(0xffffffffu, hit);
-            if (hit) {
-                const int q = p + __popc(mask & ((1u << lane) - 1u));
-                pair_row[q] = i / n_used;
-                pair_of_slot[i] = q;
-            }
-            p += __popc(mask);
-        }
         for (int c = lane * item_rows; c < cnt; c += 32 * item_rows) {
             const int it = s_ioff[e] + c / item_rows;
             item_expert[it] = e - e_lo;
@@ -270,10 +293,10 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restric
 
 cudaError_t launch_moe_router(const float *router, const float *x, float *logits, int rows, int ne, int n_expert,
                               cudaStream_t st) {
-    const long long dots = (long long)rows * n_expert;
-    const long long warps = (dots + 3) / 4;
-    const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
-    moe_router_kernel<<<blocks, 256, 0, st>>>(router, x, logits, rows, ne, n_expert);
+    if (rows < 1 || n_expert < 1) return cudaErrorInvalidValue;
+    const dim3 grid((unsigned)((rows + kRtRows - 1) / kRtRows), (unsigned)((n_expert + kRtExperts - 1) / kRtExperts));
+    if (grid.y > 65535) return cudaErrorInvalidValue;
+    moe_router_kernel<<<grid, 256, 0, st>>>(router, x, logits, rows, ne, n_expert);
     return cudaGetLastError();
 }
 
@@ -290,13 +313,13 @@ cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int 
                               int32_t *pair_row, int32_t *pair_of_slot, int32_t *item_expert, int32_t *item_p0, int32_t *item_cnt,
                               int32_t *n_items, int32_t *counts_out, cudaStream_t st) {
     if (n_expert > 1024 || item_rows < 1) return cudaErrorInvalidValue;
-    size_t ids_bytes = (size_t)rows * n_used * 4;
-    const int staged = ids_bytes <= 160 * 1024;
-    if (!staged) ids_bytes = 0;
-    cudaError_t e = cudaFuncSetAttribute(moe_bucket_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ids_bytes);
+    const int n_chunks = (rows * n_used + 31) / 32;
+    const size_t hist_bytes = (size_t)n_chunks * n_expert * 4;
+    if (hist_bytes > 200 * 1024) return cudaErrorInvalidValue;  // ~51 000 pairs of 128 experts; more would need a multi-CTA sort
+    cudaError_t e = cudaFuncSetAttribute(moe_bucket_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes);
     if (e != cudaSuccess) return e;
-    moe_bucket_kernel<<<1, 1024, ids_bytes, st>>>(sel_ids, rows, n_used, n_expert, e_lo, n_local, item_rows, pair_row, pair_of_slot, item_expert, item_p0, item_cnt,
-                                          n_items, counts_out, staged);
+    moe_bucket_kernel<<<1, 1024, hist_bytes, st>>>(sel_ids, rows, n_used, n_expert, e_lo, n_local, item_rows, pair_row, pair_of_slot, item_expert,
+                                                   item_p0, item_cnt, n_items, counts_out, n_chunks);
     return cudaGetLastError();
 }
 

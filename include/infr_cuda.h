@@ -253,6 +253,14 @@ INFR_API int32_t infr_cuda_gemv_q8(infr_cuda_ctx *ctx, int32_t dtype, const infr
                                    const infr_cuda_buf *qs, const infr_cuda_buf *d, const infr_cuda_buf *sums,
                                    const infr_cuda_buf *sums16, infr_cuda_buf *y, uint32_t m, uint32_t in_f,
                                    uint32_t out_f);
+/* Two weights of one format against the same quantised rows (infr_cuda_gemv_q8 twice, same results): q and k, or gate
+ * and up, of a decode step.  The reference gets the same effect from `w_off` slices of one fused weight
+ * (crates/infr-llama/src/seam/runner.rs:3445-3461, :3842-3879); here the two weights may live anywhere, and Q4_K
+ * pairs run as ONE launch (a decode step pays a fixed few microseconds per dependent launch). */
+INFR_API int32_t infr_cuda_gemv_q8_pair(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w1, uint64_t w_off1, infr_cuda_buf *y1,
+                                        uint32_t out_f1, const infr_cuda_buf *w2, uint64_t w_off2, infr_cuda_buf *y2, uint32_t out_f2,
+                                        const infr_cuda_buf *qs, const infr_cuda_buf *d, const infr_cuda_buf *sums,
+                                        const infr_cuda_buf *sums16, uint32_t m, uint32_t in_f);
 /* No counterpart in the reference: a decode GEMV (INFR_ACT_INT8 arithmetic, same results as
  * infr_cuda_gemv) for callers that cannot allocate device memory when they need it — plugins living
  * inside another engine's memory pool, loops that must stay clear of the driver's allocator after

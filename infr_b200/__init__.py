@@ -36,7 +36,7 @@ EXPORTED_SYMBOLS = [
     "infr_cuda_buf_device_ptr", "infr_cuda_wrap", "infr_cuda_stream", "infr_cuda_comm_create", "infr_cuda_comm_export", "infr_cuda_comm_connect", "infr_cuda_comm_connect_silent",
     "infr_cuda_all_reduce_f32", "infr_cuda_comm_destroy", "infr_cuda_upload", "infr_cuda_upload_at", "infr_cuda_download",
     "infr_cuda_copy", "infr_cuda_host_alloc", "infr_cuda_host_free", "infr_cuda_sync", "infr_cuda_compile", "infr_cuda_plan_free", "infr_cuda_execute",
-    "infr_cuda_quantize_q8", "infr_cuda_quantize_q8_1", "infr_cuda_gemv", "infr_cuda_gemv_q8", "infr_cuda_gemv_noalloc", "infr_cuda_gemv_block_acc",
+    "infr_cuda_quantize_q8", "infr_cuda_quantize_q8_1", "infr_cuda_gemv", "infr_cuda_gemv_q8", "infr_cuda_gemv_q8_pair", "infr_cuda_gemv_noalloc", "infr_cuda_gemv_block_acc",
     "infr_cuda_linear", "infr_cuda_moe_ffn", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
     "infr_cuda_graph_free", "infr_cuda_timer_start", "infr_cuda_timer_stop", "infr_cuda_flush_l2",
     "infr_cuda_launch_count", "infr_cuda_tensor_peak_i8",
@@ -139,6 +139,7 @@ def load_library() -> C.CDLL:
         "infr_cuda_comm_destroy": (None, [vp, vp]),
         "infr_cuda_gemv": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
         "infr_cuda_gemv_q8": (i32, [vp, i32, vp, u64, vp, vp, vp, vp, vp, u32, u32, u32]),
+        "infr_cuda_gemv_q8_pair": (i32, [vp, i32, vp, u64, vp, u32, vp, u64, vp, u32, vp, vp, vp, vp, u32, u32]),
         "infr_cuda_gemv_noalloc": (i32, [i32, vp, vp, vp, u32, u32, u32, vp, C.c_char_p, sz]),
         "infr_cuda_gemv_block_acc": (i32, [vp, i32, vp, u64, vp, vp, u32, u32]),
         "infr_cuda_linear": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
@@ -504,6 +505,12 @@ class CudaBackend:
                 y: Buffer, m: int, in_f: int, out_f: int, w_off: int = 0):
         self._check(self.L.infr_cuda_gemv_q8(self.ctx, dtype, w.handle, w_off, qs.handle, d.handle, sums.handle,
                                              sums16.handle if sums16 else None, y.handle, m, in_f, out_f))
+
+    def gemv_q8_pair(self, dtype: int, w1: Buffer, y1: Buffer, out_f1: int, w2: Buffer, y2: Buffer, out_f2: int, qs: Buffer, d: Buffer,
+                     sums: Buffer, sums16: Optional[Buffer], m: int, in_f: int, w_off1: int = 0, w_off2: int = 0):
+        """Two weights of one format against the same quantised rows (one launch for Q4_K)."""
+        self._check(self.L.infr_cuda_gemv_q8_pair(self.ctx, dtype, w1.handle, w_off1, y1.handle, out_f1, w2.handle, w_off2, y2.handle, out_f2,
+                                                  qs.handle, d.handle, sums.handle, sums16.handle if sums16 is not None else None, m, in_f))
 
     def linear(self, dtype: int, w: Buffer, x: Buffer, y: Buffer, m: int, in_f: int, out_f: int,
                act: int = ACT_INT8, w_off: int = 0):

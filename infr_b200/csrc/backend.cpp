@@ -392,6 +392,19 @@ Status CudaBackend::gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *
     return s;
 }
 
+Status CudaBackend::gemv_q8_pair(int dtype, const uint8_t *w1, float *y1, uint32_t out_f1, const uint8_t *w2, float *y2, uint32_t out_f2,
+                                 const Q8Dev &a, uint32_t m, uint32_t in_f) {
+    if (dtype == DT_Q4K && gemv_impl_ == 0 && m >= 1 && m <= 8 && in_f && in_f % 256 == 0 && out_f1 && out_f2 && a.gran == 256) {
+        cudaSetDevice(device_);
+        Status s = cuda_status(launch_gemv_q4k_mma_pair(w1, y1, (int)out_f1, w2, y2, (int)out_f2, a, (int)m, (int)in_f, dev_, status_dev_, stream_),
+                               "gemv_q8_pair");
+        if (s.ok()) launches_++;
+        return s;
+    }
+    Status s = gemv_q8(dtype, w1, a, y1, m, in_f, out_f1);
+    return s.ok() ? gemv_q8(dtype, w2, a, y2, m, in_f, out_f2) : s;
+}
+
 // ---- the other ops of a dense decode step ----
 Status CudaBackend::rms_norm(const float *a, const float *b, float *sum_dst, const float *w, float *dst, uint32_t rows, uint32_t dim, float eps) {
     cudaSetDevice(device_);

@@ -115,6 +115,9 @@ public:
     Status moe_ffn(const MoeArgs &a);
     Status moe_ffn_f32(const MoeArgs &a);
     Status gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f);
+    // Two weights of one format against the same quantised rows: one launch where the format's kernel can (Q4_K).
+    Status gemv_q8_pair(int dtype, const uint8_t *w1, float *y1, uint32_t out_f1, const uint8_t *w2, float *y2, uint32_t out_f2, const Q8Dev &a,
+                        uint32_t m, uint32_t in_f);
     // ---- the other ops of a dense decode step (decode_ops.cu); arguments checked by the C ABI ----
     Status rms_norm(const float *a, const float *b, float *sum_dst, const float *w, float *dst, uint32_t rows, uint32_t dim, float eps);
     Status rope(const float *x, const int32_t *positions, float *dst, uint32_t rows, uint32_t n_head, uint32_t head_dim, uint32_t rope_dim,

@@ -281,6 +281,30 @@ int32_t infr_cuda_gemv_q8(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf
     return finish(ctx, ctx->be->gemv_q8(dtype, pw + row0 * bpr, a, (float *)py, m, in_f, out_f));
 }
 
+int32_t infr_cuda_gemv_q8_pair(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w1, uint64_t w_off1, infr_cuda_buf *y1, uint32_t out_f1,
+                               const infr_cuda_buf *w2, uint64_t w_off2, infr_cuda_buf *y2, uint32_t out_f2, const infr_cuda_buf *qs,
+                               const infr_cuda_buf *d, const infr_cuda_buf *sums, const infr_cuda_buf *sums16, uint32_t m, uint32_t in_f) {
+    INFR_CTX_OR_RETURN(ctx);
+    uint8_t *pw1, *pw2, *pq, *pd, *ps, *p16 = nullptr, *py1, *py2;
+    const int be = infr::block_elems(dtype), bb = infr::block_bytes(dtype);
+    if (dtype != INFR_DT_Q4K && dtype != INFR_DT_Q6K && dtype != INFR_DT_Q2_0)
+        return finish(ctx, Status::Err(INFR_E_UNSUPPORTED, "gemv_q8_pair: weight dtype is not supported"));
+    if (in_f == 0 || in_f % (uint32_t)be || w_off1 % in_f || w_off2 % in_f) return finish(ctx, Status::Err(INFR_E_INVALID, "gemv_q8_pair: in_f / w_off"));
+    if (m == 0 || m > 8 || out_f1 == 0 || out_f2 == 0) return finish(ctx, Status::Err(INFR_E_INVALID, "gemv_q8_pair: m in 1..8, both out_f positive"));
+    const int gran = infr::act_gran(dtype);
+    const size_t bpr = (size_t)(in_f / (uint32_t)be) * (size_t)bb, r1 = (size_t)(w_off1 / in_f), r2 = (size_t)(w_off2 / in_f), n = (size_t)m * in_f;
+    Status s;
+    if (!(s = span(w1, (r1 + out_f1) * bpr, "gemv_q8_pair weight 1", &pw1)).ok() || !(s = span(w2, (r2 + out_f2) * bpr, "gemv_q8_pair weight 2", &pw2)).ok() ||
+        !(s = span(qs, n, "gemv_q8_pair qs", &pq)).ok() || !(s = span(d, n / (size_t)gran * 4, "gemv_q8_pair d", &pd)).ok() ||
+        !(s = span(sums, n / 32 * 4, "gemv_q8_pair sums", &ps)).ok() || !(s = span(y1, (size_t)m * out_f1 * 4, "gemv_q8_pair y1", &py1)).ok() ||
+        !(s = span(y2, (size_t)m * out_f2 * 4, "gemv_q8_pair y2", &py2)).ok())
+        return finish(ctx, s);
+    if (sums16 && !(s = span(sums16, n / 16 * 4, "gemv_q8_pair sums16", &p16)).ok()) return finish(ctx, s);
+    if (dtype == INFR_DT_Q6K && !p16) return finish(ctx, Status::Err(INFR_E_INVALID, "gemv_q8_pair: Q6_K needs the per-16 sums"));
+    infr::Q8Dev a{(const int8_t *)pq, (const float *)pd, (const int32_t *)ps, (const int32_t *)p16, gran};
+    return finish(ctx, ctx->be->gemv_q8_pair(dtype, pw1 + r1 * bpr, (float *)py1, out_f1, pw2 + r2 * bpr, (float *)py2, out_f2, a, m, in_f));
+}
+
 int32_t infr_cuda_gemv_block_acc(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off,
                                  const infr_cuda_buf *x, infr_cuda_buf *acc, uint32_t in_f, uint32_t out_f) {
     INFR_CTX_OR_RETURN(ctx);

@@ -31,6 +31,8 @@
 // stops consuming (the block still reaches its barriers, results of the launch are invalid).
 #include <cuda.h>
 
+#include <cstring>
+
 #include "gemv_common.cuh"
 
 namespace infr {
@@ -106,6 +108,14 @@ struct MmaGroup {
     const int *pair_row;     // [n_pairs] activation row of each pair, or nullptr: pair p reads row p
 };
 
+// A second matrix with the same in_f and the same activations, multiplied in the same launch (the q and k
+// projections, gate and up): its 16-row tiles follow the first matrix's in the CTAs' tile ranges.  out_f == 0: none.
+struct MmaSecond {
+    CUtensorMap map;
+    float *y;
+    int out_f;
+};
+
 // Shared-memory layout of the staged activations, per token n (0..7) and super-block b:
 //   codes  : 320 B at (n*nb + b)*320, element (sub-block s, l = 8t+i) at t*80 + s*8 + i
 //   bsplit : 16 B at (n*nb + b)*16: bytes 0..7 = low 6 bits of bsum_s, bytes 8..15 = bsum_s >> 6
@@ -113,8 +123,9 @@ struct MmaGroup {
 // KW = warps per CTA (they split K), SB = super-blocks per ring slot per row.
 template <int M, bool FUSED, int KW, int SB>
 __global__ void __launch_bounds__(KW * 32, 16 / KW)
-    gemv_q4k_mma_kernel(const __grid_constant__ CUtensorMap tmap, Q8Dev a, const float *__restrict__ x, float *__restrict__ y, int m,
-                        int in_f, int out_f, MmaGeom geo, MmaGroup grp, uint32_t *__restrict__ status) {
+    gemv_q4k_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ MmaSecond sec, Q8Dev a,
+                        const float *__restrict__ x, float *__restrict__ y, int m, int in_f, int out_f, MmaGeom geo, MmaGroup grp,
+                        uint32_t *__restrict__ status) {
     constexpr int kW = KW, kThreadsMma = KW * 32, kStepBlocks = SB, kSlotBytes = kTileRows * SB * 144;
     extern __shared__ __align__(128) uint8_t smem[];
     const int nb = geo.nb, S = geo.slots;
@@ -146,12 +157,11 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
     }
 
     // balanced contiguous range of 16-row tiles of this CTA (only the matrix's last tile can be partial)
-    const int total_tiles = (out_f + kTileRows - 1) / kTileRows;
+    const int tiles1 = (out_f + kTileRows - 1) / kTileRows;  // tiles of the first matrix; the second's follow
+    const int total_tiles = tiles1 + (sec.out_f + kTileRows - 1) / kTileRows;
     const int G = gridDim.x, base = total_tiles / G, rem = total_tiles % G;
     const int t_begin = blockIdx.x * base + (blockIdx.x < rem ? blockIdx.x : rem);
     const int n_tiles = base + (blockIdx.x < rem ? 1 : 0);
-    const int r_begin = t_begin * kTileRows;
-    const int r_count = min(out_f - r_begin, n_tiles * kTileRows);
     // this warp's K range
     const int kb0 = warp * geo.bpw;
     const int kb1 = min(nb, kb0 + geo.bpw);
@@ -175,7 +185,11 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
             // order this warp's earlier reads of the slot before the engine overwrites it
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             bar_expect_tx(bar, (uint32_t)kSlotBytes);
-            tma_load_2d_hint(s_u32(ring + (size_t)slot * kSlotBytes), &tmap, blk0 * 36, row_base + r_begin + i_tile * kTileRows, bar, l2_policy);
+            const int T = t_begin + i_tile;
+            if (T < tiles1)
+                tma_load_2d_hint(s_u32(ring + (size_t)slot * kSlotBytes), &tmap, blk0 * 36, row_base + T * kTileRows, bar, l2_policy);
+            else
+                tma_load_2d_hint(s_u32(ring + (size_t)slot * kSlotBytes), &sec.map, blk0 * 36, (T - tiles1) * kTileRows, bar, l2_policy);
         }
         __syncwarp();
         j_issue++;
@@ -427,13 +441,15 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
         __syncthreads();
         if (threadIdx.x < kTileRows * 8) {  // 16 rows x 8 token columns; CTAs have at least 128 threads
             const int r = threadIdx.x >> 3, n = threadIdx.x & 7;
-            const int row = r_begin + tile * kTileRows + r;
-            if (n < m && row < r_begin + r_count) {
+            const int T = t_begin + tile;
+            const bool second = T >= tiles1;
+            const int row = (second ? T - tiles1 : T) * kTileRows + r, of = second ? sec.out_f : out_f;
+            if (n < m && row < of) {
                 const float *pp = s_part + (size_t)(tile & 1) * kW * 128 + r * 8 + n;
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < kW; w++) v += pp[w * 128];
-                y[(size_t)(p0 + n) * out_f + row] = v;
+                (second ? sec.y : y)[(size_t)(p0 + n) * of + row] = v;
             }
         }
     }
@@ -457,7 +473,7 @@ EncodeTiledFn encode_tiled() {
 template <int M, bool FUSED, int KW, int SB>
 cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
                            const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const MmaGroup &grp = MmaGroup{},
-                           int n_experts = 1, int max_items = 1) {
+                           int n_experts = 1, int max_items = 1, const uint8_t *w2 = nullptr, float *y2 = nullptr, int out_f2 = 0) {
     constexpr int kSlotBytes = kTileRows * SB * 144;
     MmaGeom geo;
     geo.nb = in_f / 256;
@@ -473,12 +489,13 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
     const size_t budget = (size_t)dev.max_smem_optin / per_sm - (per_sm > 1 ? 2048 : 1024);
     int slots = (int)((budget - fixed) / per_slot);
     if (slots > kMaxSlotsMma) slots = kMaxSlotsMma;
-    int grid = (out_f + kTileRows - 1) / kTileRows;
+    const int all_tiles = (out_f + kTileRows - 1) / kTileRows + (out_f2 + kTileRows - 1) / kTileRows;
+    int grid = all_tiles;
     if (grid > dev.sm_count * per_sm) grid = dev.sm_count * per_sm;
     if (!grp.item_expert) {
         // no more ring slots than a warp has jobs: what a small matrix leaves of the SM's shared memory lets the
         // next kernel of the stream become resident, and prefetch its weights, while this one computes
-        const int tiles = (out_f + kTileRows - 1) / kTileRows, tiles_cta = (tiles + grid - 1) / grid;
+        const int tiles = all_tiles, tiles_cta = (tiles + grid - 1) / grid;
         const int jobs = tiles_cta * ((geo.bpw + SB - 1) / SB);
         if (slots > jobs) slots = jobs < 1 ? 1 : jobs;
     }
@@ -487,15 +504,21 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return cudaErrorNotSupported;
     CUtensorMap tmap;
-    {
-        const cuuint64_t gdim[2] = {(cuuint64_t)geo.nb * 36, (cuuint64_t)out_f * (cuuint64_t)n_experts};
+    MmaSecond sec;
+    memset(&sec, 0, sizeof sec);
+    auto encode = [&](CUtensorMap *map, const uint8_t *base, cuuint64_t rows) {
+        const cuuint64_t gdim[2] = {(cuuint64_t)geo.nb * 36, rows};
         const cuuint64_t gstride[1] = {(cuuint64_t)geo.nb * 144};
         const cuuint32_t box[2] = {(cuuint32_t)SB * 36, (cuuint32_t)kTileRows};
         const cuuint32_t estr[2] = {1, 1};
-        if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return cudaErrorInvalidValue;
+        return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    if (!encode(&tmap, w, (cuuint64_t)out_f * (cuuint64_t)n_experts)) return cudaErrorInvalidValue;
+    if (out_f2 > 0) {
+        if (!encode(&sec.map, w2, (cuuint64_t)out_f2)) return cudaErrorInvalidValue;
+        sec.y = y2;
+        sec.out_f = out_f2;
     }
     auto kernel = gemv_q4k_mma_kernel<M, FUSED, KW, SB>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -515,15 +538,16 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, tmap, a, x, y, m, in_f, out_f, geo, grp, status);
+    return cudaLaunchKernelEx(&cfg, kernel, tmap, sec, a, x, y, m, in_f, out_f, geo, grp, status);
 }
 
 // Few 16-row tiles (small matrices) -> more warps share a tile's K range so that a tile's latency is short;
 // many tiles -> four warps per tile and the SM overlaps independent tiles instead.
 template <int M, bool FUSED>
 cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
-                         const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
-    const int nb = in_f / 256, tiles = (out_f + kTileRows - 1) / kTileRows;
+                         const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const uint8_t *w2 = nullptr, float *y2 = nullptr,
+                         int out_f2 = 0) {
+    const int nb = in_f / 256, tiles = (out_f + kTileRows - 1) / kTileRows + (out_f2 + kTileRows - 1) / kTileRows;
     // shared memory a configuration needs with two ring slots per warp of `sb` super-blocks each
     auto need_sb = [&](int kw, int sb) {
         return (size_t)M * nb * (kStagedBytes + 16) + (size_t)nb * 32 + (size_t)2 * kw * 512 + (size_t)kw * kMaxSlotsMma * 8 + 64 +
@@ -547,7 +571,8 @@ cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float
         kw = 8;
         bpw = 1;  // selects SB = 1 below; the kernel walks a warp's blocks one slot at a time
     }
-#define INFR_MMA(KW_, SB_) return launch_mma_cfg<M, FUSED, KW_, SB_>(w, a, x, y, m, in_f, out_f, dev, status, st)
+#define INFR_MMA(KW_, SB_) \
+    return launch_mma_cfg<M, FUSED, KW_, SB_>(w, a, x, y, m, in_f, out_f, dev, status, st, MmaGroup{}, 1, 1, w2, y2, out_f2)
     if (kw == 16) {
         if (bpw == 1) INFR_MMA(16, 1);
         INFR_MMA(16, 2);
@@ -563,11 +588,12 @@ cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float
 
 template <bool FUSED>
 cudaError_t launch_mma(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
-                       const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
-    if (m == 1) return launch_mma_m<1, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st);
-    if (m == 2) return launch_mma_m<2, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st);
-    if (m <= 4) return launch_mma_m<4, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st);
-    return launch_mma_m<8, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st);
+                       const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const uint8_t *w2 = nullptr, float *y2 = nullptr,
+                       int out_f2 = 0) {
+    if (m == 1) return launch_mma_m<1, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2);
+    if (m == 2) return launch_mma_m<2, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2);
+    if (m <= 4) return launch_mma_m<4, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2);
+    return launch_mma_m<8, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2);
 }
 
 }  // namespace
@@ -583,6 +609,13 @@ cudaError_t launch_grouped_q4k_mma(const uint8_t *bank, int n_experts, const Q8D
     // reduction are shared by two blocks per warp where the rows are long enough
     if ((nb + 3) / 4 == 1) return launch_mma_cfg<8, false, 4, 1>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
     return launch_mma_cfg<8, false, 4, 2>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
+}
+
+// Two Q4_K matrices with the same in_f against the same pre-quantised rows, one launch.
+cudaError_t launch_gemv_q4k_mma_pair(const uint8_t *w1, float *y1, int out_f1, const uint8_t *w2, float *y2, int out_f2, const Q8Dev &a, int m,
+                                     int in_f, const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+    if (m < 1 || m > 8 || in_f % 256 || out_f1 < 1 || out_f2 < 1) return cudaErrorInvalidValue;
+    return launch_mma<false>(w1, a, nullptr, y1, m, in_f, out_f1, dev, status, st, w2, y2, out_f2);
 }
 
 cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,

@@ -60,6 +60,10 @@ cudaError_t launch_gemv_q6_mma(const uint8_t *w, const Q8Dev &a, float *y, int m
 // (f32 rows, quantised inside the kernel) is non-null.
 cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,
                                 const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
+// Two Q4_K matrices [out_f1, in_f] and [out_f2, in_f] against the same pre-quantised rows in ONE launch (q and k,
+// gate and up: a decode step pays a fixed few microseconds per dependent launch).
+cudaError_t launch_gemv_q4k_mma_pair(const uint8_t *w1, float *y1, int out_f1, const uint8_t *w2, float *y2, int out_f2, const Q8Dev &a, int m,
+                                     int in_f, const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
 // y[m,out_f] (m <= 8) from f32 activations and dequantised weights.
 cudaError_t launch_gemv_f32(int dt, const uint8_t *w, const float *x, float *y, int m, int in_f, int out_f,
                             const DeviceInfo &dev, cudaStream_t st);

@@ -97,8 +97,7 @@ class DecodeStep:
         be.add_rms_norm_q8(self.hidden, None, None, self.layers[0]["attn_norm"], b, h, s.eps, *a8)
         n = 1
         for li, L in enumerate(self.layers):
-            gemv(Q4K, L["wq"], self.q, h, s.q_dim)
-            gemv(Q4K, L["wk"], self.k, h, s.kv_dim)
+            be.gemv_q8_pair(Q4K, L["wq"], self.q, s.q_dim, L["wk"], self.k, s.kv_dim, *a8, b, h)  # q and k: one launch
             gemv(Q6K, L["wv"], self.v, h, s.kv_dim)
             be.rope_write_kv(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], rows=1, pos=pos,
                              n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
@@ -108,15 +107,14 @@ class DecodeStep:
             if self.reduce:
                 self.reduce(self.sub, b * h)
             be.add_rms_norm_q8(self.hidden, self.sub, self.hidden, L["ffn_norm"], b, h, s.eps, *a8)
-            gemv(Q4K, L["gate"], self.g, h, ff)
-            gemv(Q4K, L["up"], self.u, h, ff)
+            be.gemv_q8_pair(Q4K, L["gate"], self.g, ff, L["up"], self.u, ff, *a8, b, h)  # gate and up: one launch
             be.gated_act_q8(self.g, self.u, b, ff, *a8)
             gemv(Q6K, L["down"], self.sub, ff, h)
             if self.reduce:
                 self.reduce(self.sub, b * h)
             nxt = self.layers[li + 1]["attn_norm"] if li + 1 < len(self.layers) else self.out_norm
             be.add_rms_norm_q8(self.hidden, self.sub, self.hidden, nxt, b, h, s.eps, *a8)
-            n += 13
+            n += 13  # ops (q/k and gate/up share a launch: 11 launches per layer)
         gemv(self.head_dtype, self.head, self.logits, h, s.vocab)
         if self.do_argmax:
             be.argmax(self.logits, self.tok, s.vocab, b)

@@ -207,3 +207,27 @@ def test_errors_are_returned_not_raised_as_faults(backend):
         backend.upload(small, np.zeros(200, np.uint8))
     caps = backend.capabilities()
     assert caps.name == "cuda-sm100a" and caps.i8_dot and not caps.unified_memory and caps.sm_count > 0
+
+
+@pytest.mark.parametrize("dt,in_f,out1,out2,m", [(Q4K, 1024, 320, 96, 1), (Q4K, 1024, 333, 40, 5), (Q4K, 4096, 4096, 1024, 1),
+                                                 (Q4K, 2048, 24, 7000, 8), (Q6K, 2048, 64, 48, 2)])
+def test_two_weights_against_the_same_rows_in_one_call(backend, oracle, dt, in_f, out1, out2, m):
+    """infr_cuda_gemv_q8_pair (q and k, gate and up of a decode step): both results as from two separate calls (the
+    integer block sums are the same; one launch may split K over a different number of warps, which reorders the f32
+    additions) and within the parity bar of the CPU."""
+    w1, w2 = synth.weight(dt, out1, in_f, seed=11), synth.weight(dt, out2, in_f, seed=12)
+    x = synth.normal(13, (m, in_f))
+    b1, b2 = backend.from_numpy(w1, infr_b200.USAGE_WEIGHTS), backend.from_numpy(w2, infr_b200.USAGE_WEIGHTS)
+    xb = backend.from_numpy(x)
+    qs, d, s32, s16 = backend.alloc(m * in_f), backend.alloc(m * (in_f // 256) * 4), backend.alloc(m * (in_f // 32) * 4), backend.alloc(m * (in_f // 16) * 4)
+    backend.quantize_q8(256, xb, m, in_f, qs, d, s32, s16)
+    y1, y2, z1, z2 = (backend.alloc(m * o * 4) for o in (out1, out2, out1, out2))
+    backend.gemv_q8_pair(dt, b1, y1, out1, b2, y2, out2, qs, d, s32, s16, m, in_f)
+    backend.gemv_q8(dt, b1, qs, d, s32, s16, z1, m, in_f, out1)
+    backend.gemv_q8(dt, b2, qs, d, s32, s16, z2, m, in_f, out2)
+    for got_b, ref_b, w, o in ((y1, z1, w1, out1), (y2, z2, w2, out2)):
+        got, ref = backend.download(got_b, np.float32).reshape(m, o), backend.download(ref_b, np.float32).reshape(m, o)
+        assert fx.rel_l2(got, ref) < TIGHT_REL_L2
+        assert fx.rel_l2(got, oracle.linear(dt, w, x, m, in_f, o)) < TIGHT_REL_L2
+    for b in (b1, b2, xb, qs, d, s32, s16, y1, y2, z1, z2):
+        b.close()

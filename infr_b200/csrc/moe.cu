@@ -31,20 +31,52 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const float *__restrict
     const int r0 = blockIdx.x * kRtRows, e0 = blockIdx.y * kRtExperts;
     const int chunks = ne / 8;  // whole groups of eight columns; the rest is the tail
     float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-    for (int k0 = 0; k0 < chunks * 8; k0 += kRtK) {
-        const int kc = min(kRtK, chunks * 8 - k0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < kRtRows * kRtK; i += 256) {
-            const int r = i / kRtK, k = i - r * kRtK;
-            s_x[r * kRtPitch + k] = (r0 + r < rows && k < kc) ? x[(size_t)(r0 + r) * ne + k0 + k] : 0.f;
+    // Staging: 16-byte loads, the next 256 columns are fetched into registers while the current ones are multiplied
+    // (rows start on 16-byte boundaries when ne is a multiple of 4; otherwise element loads).
+    const bool vec = (ne & 3) == 0 && (((uintptr_t)x | (uintptr_t)router) & 15) == 0;
+    const int kend = chunks * 8;
+    float4 px[2], pw[4];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int u = 0; u < 6; u++) {
+            const int i = threadIdx.x + u * 256;            // float4 slot: 0..511 rows of x, 512..1535 router rows
+            const bool is_w = i >= 512;
+            const int ii = is_w ? i - 512 : i, r = ii >> 6, k = (ii & 63) * 4;
+            const int gr = (is_w ? e0 : r0) + r, lim = is_w ? n_expert : rows;
+            const float *src = (is_w ? router : x) + (size_t)gr * ne + k0 + k;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gr < lim) {
+                if (vec && k0 + k + 4 <= kend) {
+                    v = __ldg(reinterpret_cast<const float4 *>(src));
+                } else {
+                    if (k0 + k < kend) v.x = src[0];
+                    if (k0 + k + 1 < kend) v.y = src[1];
+                    if (k0 + k + 2 < kend) v.z = src[2];
+                    if (k0 + k + 3 < kend) v.w = src[3];
+                }
+            }
+            if (is_w) pw[u - 2] = v; else px[u] = v;
         }
-        for (int i = threadIdx.x; i < kRtExperts * kRtK; i += 256) {
-            const int e = i / kRtK, k = i - e * kRtK;
-            s_w[e * kRtPitch + k] = (e0 + e < n_expert && k < kc) ? router[(size_t)(e0 + e) * ne + k0 + k] : 0.f;
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int u = 0; u < 6; u++) {
+            const int i = threadIdx.x + u * 256;
+            const bool is_w = i >= 512;
+            const int ii = is_w ? i - 512 : i, r = ii >> 6, k = (ii & 63) * 4;
+            *reinterpret_cast<float4 *>((is_w ? s_w : s_x) + r * kRtPitch + k) = is_w ? pw[u - 2] : px[u];
         }
+    };
+    if (kend > 0) fetch(0);
+    for (int k0 = 0; k0 < kend; k0 += kRtK) {
+        const int kc = min(kRtK, kend - k0);
+        __syncthreads();  // everybody has finished with the previous columns
+        stash();
         __syncthreads();
+        if (k0 + kRtK < kend) fetch(k0 + kRtK);
         const float *xa = s_x + (2 * rp) * kRtPitch + j, *xb = xa + kRtPitch;
         const float *wa = s_w + (2 * ep) * kRtPitch + j, *wb = wa + kRtPitch;
+#pragma unroll 4
         for (int c = 0; c < kc / 8; c++) {
             const float x0 = xa[c * 8], x1 = xb[c * 8], w0 = wa[c * 8], w1 = wb[c * 8];
             acc[0][0] = fmaf(w0, x0, acc[0][0]);

@@ -73,7 +73,8 @@ typedef struct infr_cuda_graph infr_cuda_graph;
  * so that the parity tests can reach every kernel of the library on every shape:
  *   gemv_kernel 1: the direct-load byte-dot GEMV for all formats and batches;
  *   mmq_kernel  1: the Q4_K prefill GEMM whose f32 output is bit-identical to the CPU's (slower),
- *               2: the default tensor-memory GEMM also for batches the dispatch would walk through the GEMV. */
+ *               2: the grouped tensor-memory GEMM also for MoE layers with a handful of rows per expert,
+ *               3: no GEMM: batches of more than 8 rows are walked through the GEMV 8 rows at a time. */
 typedef struct {
     int32_t device;
     int32_t reference;
@@ -289,6 +290,13 @@ INFR_API int32_t infr_cuda_gemv_block_acc(infr_cuda_ctx *ctx, int32_t dtype, con
 INFR_API int32_t infr_cuda_linear(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off,
                                   const infr_cuda_buf *x, infr_cuda_buf *y, uint32_t m, uint32_t in_f,
                                   uint32_t out_f, int32_t act);
+
+/* Two Op::Linear of one weight format on the same rows (q and k, gate and up), results as from two infr_cuda_linear
+ * calls: the rows are quantised once (and laid out once for the prefill GEMM); for at most 8 rows of Q4_K the two
+ * products are one launch.  infr_cuda_execute pairs neighbouring Linear ops of a graph the same way. */
+INFR_API int32_t infr_cuda_linear_pair(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w1, uint64_t w_off1, infr_cuda_buf *y1,
+                                       uint32_t out_f1, const infr_cuda_buf *w2, uint64_t w_off2, infr_cuda_buf *y2, uint32_t out_f2,
+                                       const infr_cuda_buf *x, uint32_t m, uint32_t in_f, int32_t act);
 
 /* Op::MoeFfn as a direct call (crates/infr-core/src/graph.rs:918-1011; CPU semantics
  * crates/infr-cpu/src/lib.rs:2264-2984): F32 router [n_expert, ne], expert banks gate/up

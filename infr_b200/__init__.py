@@ -37,7 +37,7 @@ EXPORTED_SYMBOLS = [
     "infr_cuda_all_reduce_f32", "infr_cuda_comm_destroy", "infr_cuda_upload", "infr_cuda_upload_at", "infr_cuda_download",
     "infr_cuda_copy", "infr_cuda_host_alloc", "infr_cuda_host_free", "infr_cuda_sync", "infr_cuda_compile", "infr_cuda_plan_free", "infr_cuda_execute",
     "infr_cuda_quantize_q8", "infr_cuda_quantize_q8_1", "infr_cuda_gemv", "infr_cuda_gemv_q8", "infr_cuda_gemv_q8_pair", "infr_cuda_gemv_noalloc", "infr_cuda_gemv_block_acc",
-    "infr_cuda_linear", "infr_cuda_moe_ffn", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
+    "infr_cuda_linear", "infr_cuda_linear_pair", "infr_cuda_moe_ffn", "infr_cuda_capture_begin", "infr_cuda_capture_end", "infr_cuda_graph_launch",
     "infr_cuda_graph_free", "infr_cuda_timer_start", "infr_cuda_timer_stop", "infr_cuda_flush_l2",
     "infr_cuda_launch_count", "infr_cuda_tensor_peak_i8",
     "infr_cuda_rms_norm", "infr_cuda_add_rms_norm", "infr_cuda_rope", "infr_cuda_write_kv", "infr_cuda_attention", "infr_cuda_rope_write_kv",
@@ -143,6 +143,7 @@ def load_library() -> C.CDLL:
         "infr_cuda_gemv_noalloc": (i32, [i32, vp, vp, vp, u32, u32, u32, vp, C.c_char_p, sz]),
         "infr_cuda_gemv_block_acc": (i32, [vp, i32, vp, u64, vp, vp, u32, u32]),
         "infr_cuda_linear": (i32, [vp, i32, vp, u64, vp, vp, u32, u32, u32, i32]),
+        "infr_cuda_linear_pair": (i32, [vp, i32, vp, u64, vp, u32, vp, u64, vp, u32, vp, u32, u32, i32]),
         "infr_cuda_moe_ffn": (i32, [vp, C.POINTER(_MoeDesc), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
         "infr_cuda_capture_begin": (i32, [vp]),
         "infr_cuda_capture_end": (i32, [vp, C.POINTER(vp)]),
@@ -515,6 +516,12 @@ class CudaBackend:
     def linear(self, dtype: int, w: Buffer, x: Buffer, y: Buffer, m: int, in_f: int, out_f: int,
                act: int = ACT_INT8, w_off: int = 0):
         self._check(self.L.infr_cuda_linear(self.ctx, dtype, w.handle, w_off, x.handle, y.handle, m, in_f, out_f, act))
+
+    def linear_pair(self, dtype: int, w1: Buffer, y1: Buffer, out_f1: int, w2: Buffer, y2: Buffer, out_f2: int, x: Buffer, m: int, in_f: int,
+                    act: int = ACT_INT8, w_off1: int = 0, w_off2: int = 0):
+        """Two Linears of one weight format on the same rows (rows quantised once; one launch for <= 8 rows of Q4_K)."""
+        self._check(self.L.infr_cuda_linear_pair(self.ctx, dtype, w1.handle, w_off1, y1.handle, out_f1, w2.handle, w_off2, y2.handle, out_f2,
+                                                 x.handle, m, in_f, act))
 
     def moe_ffn(self, x: Buffer, router_x: Buffer, router: Buffer, gate: Buffer, up: Buffer, down: Buffer, dst: Buffer, *,
                 rows: int, ne: int, n_expert: int, n_used: int, n_ff_exp: int, scale: float = 1.0, norm_w: bool = True,

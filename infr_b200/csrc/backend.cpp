@@ -282,28 +282,22 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
     if (in_f % 16) return Status::Err(INFR_E_INVALID, fmt("linear: in_f=%u must be a multiple of 16", in_f));
     if (m == 0 || out_f == 0) return Status::Ok();
     cudaSetDevice(device_);
-    // Prefill shapes: Q4_K with int8 activations goes to the tcgen05 MMQ GEMM (all rows quantised once).
-    bool use_mmq = m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0;
-    if (use_mmq && mmq_impl_ == 0 && m <= 32) {
-        // A batch of a few dozen rows is still bandwidth work, and the GEMM's serial walk over K (about 1 us per
-        // 256-column block and tile, whatever the number of rows) plus its activation re-layout cost ~31 us on
-        // 4096 columns: below that, 8 rows at a time through the GEMV (measured ~2.5 us + 0.34 us per MB of weights
-        // per launch) is faster.  The large matrices of a decode step (gate / up) stay on the GEMM.
-        const double mb = (double)out_f * in_f * 0.5625e-6, gemm_us = 7.0 + 1.5 * (in_f / 256);
-        if (((m + 7) / 8) * (2.5 + 0.34 * mb) < gemm_us) use_mmq = false;
-    }
-    if (use_mmq) {
+    // Q4_K with int8 activations and more than 8 rows goes to the tensor-memory GEMM (all rows quantised once, the
+    // weights unpacked once).  A batch of a few dozen rows against a matrix with few 128-row tiles would leave most
+    // SMs idle there while a handful walk all of K, so the GEMM splits K across CTAs for such shapes
+    // (mmq_ws_k_splits).  mmq_kernel 3 walks the batch through the GEMV 8 rows at a time instead (the parity tests
+    // and the bench compare the two).
+    const bool use_mmq = m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0 && mmq_impl_ != 3;
+    if (use_mmq && mmq_impl_ == 1) {
         Q8Dev a;
         uint8_t *rec = nullptr;
-        const size_t rec_bytes = mmq_impl_ == 1 ? mmq_q4k_record_bytes((int)m, (int)in_f) : mmq_ws_record_bytes((int)m, (int)in_f);
-        Status s = quantize_for(dtype, x, m, in_f, &a, rec_bytes, &rec);
+        Status s = quantize_for(dtype, x, m, in_f, &a, mmq_q4k_record_bytes((int)m, (int)in_f), &rec);
         if (!s.ok()) return s;
-        s = cuda_status(mmq_impl_ == 1 ? launch_mmq_q4k(w, a, rec, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_)
-                                       : launch_mmq_ws_q4k(w, a, rec, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_),
-                        "mmq_q4k");
+        s = cuda_status(launch_mmq_q4k(w, a, rec, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_), "mmq_q4k");
         if (s.ok()) launches_ += 2;
         return s;
     }
+    if (use_mmq) return mmq_linear(w, x, y, m, in_f, out_f, false);
     // Decode shapes (m <= 8) run the streaming GEMV; wider batches are walked 8 rows at a time, all rows quantised once.
     Q8Dev a_all{};
     // (a single Q4_K chunk quantises its rows inside the GEMV; with several chunks that would repeat the work in every CTA)
@@ -373,6 +367,47 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
         }
     }
     return Status::Ok();
+}
+
+// The tensor-memory GEMM from f32 rows.  The context scratch holds the activation planes (and the K-split partial
+// results behind them); reuse = the planes are those of the previous call's rows (same x, m, in_f) and are not rebuilt.
+Status CudaBackend::mmq_linear(const uint8_t *w, const float *x, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, bool reuse) {
+    const size_t rec_bytes = align_up(mmq_ws_record_bytes((int)m, (int)in_f), 256);
+    // the partial results sit behind the planes at an offset that does not depend on out_f, so that two weights of
+    // different height can share the planes
+    const size_t part_bytes = mmq_ws_partial_bytes((int)m, (int)in_f, (int)out_f, dev_);
+    Status s = ensure_scratch(rec_bytes + part_bytes);
+    if (!s.ok()) return s;
+    float *partials = part_bytes ? reinterpret_cast<float *>(scratch() + rec_bytes) : nullptr;
+    s = cuda_status(launch_mmq_ws_q4k_f32(w, reuse ? nullptr : x, scratch(), y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_, partials),
+                    "mmq_q4k");
+    if (s.ok()) launches_ += (reuse ? 1 : 2) + (part_bytes ? 1 : 0);
+    return s;
+}
+
+// Two weights of one format against the same f32 rows (q and k, gate and up): the rows are quantised once.
+Status CudaBackend::linear_pair(int dtype, const uint8_t *w1, float *y1, uint32_t out_f1, const uint8_t *w2, float *y2, uint32_t out_f2,
+                                const float *x, uint32_t m, uint32_t in_f, int act) {
+    const bool q4_gemm = m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0 && (mmq_impl_ == 0 || mmq_impl_ == 2);
+    if (q4_gemm && in_f && in_f % 256 == 0 && out_f1 && out_f2) {
+        cudaSetDevice(device_);
+        // scratch for the larger of the two before the first launch: growing it would drop the planes
+        const size_t rec_bytes = align_up(mmq_ws_record_bytes((int)m, (int)in_f), 256);
+        const size_t p1 = mmq_ws_partial_bytes((int)m, (int)in_f, (int)out_f1, dev_), p2 = mmq_ws_partial_bytes((int)m, (int)in_f, (int)out_f2, dev_);
+        Status s = ensure_scratch(rec_bytes + (p1 > p2 ? p1 : p2));
+        if (!s.ok()) return s;
+        s = mmq_linear(w1, x, y1, m, in_f, out_f1, false);
+        return s.ok() ? mmq_linear(w2, x, y2, m, in_f, out_f2, true) : s;
+    }
+    if (act == INFR_ACT_INT8 && m >= 1 && m <= 8 && (dtype == DT_Q4K || dtype == DT_Q6K || dtype == DT_Q2_0) && in_f &&
+        in_f % (uint32_t)block_elems(dtype) == 0 && in_f % 16 == 0 && out_f1 && out_f2) {
+        cudaSetDevice(device_);
+        Q8Dev a;
+        Status s = quantize_for(dtype, x, m, in_f, &a);
+        return s.ok() ? gemv_q8_pair(dtype, w1, y1, out_f1, w2, y2, out_f2, a, m, in_f) : s;
+    }
+    Status s = linear(dtype, w1, x, y1, m, in_f, out_f1, act);
+    return s.ok() ? linear(dtype, w2, x, y2, m, in_f, out_f2, act) : s;
 }
 
 Status CudaBackend::gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f) {

@@ -26,7 +26,7 @@ struct infr_cuda_comm;  // comm.cu
 
 // One launch group of a compiled plan: a single op, or neighbouring ops one kernel computes.
 struct PlanStep {
-    enum Kind { kSingle = 0, kAddRmsNorm = 1, kRopeWriteKv = 2 };
+    enum Kind { kSingle = 0, kAddRmsNorm = 1, kRopeWriteKv = 2, kLinearPair = 3 };
     int kind;
     uint32_t op0, n_ops;
 };
@@ -98,6 +98,10 @@ public:
                        int32_t *sums, int32_t *sums16, uint16_t *dact, uint16_t *sact);
     Status linear(int dtype, const uint8_t *w, const float *x, float *y, uint32_t m, uint32_t in_f,
                   uint32_t out_f, int act);
+    // Two Linears of one weight format on the same rows (q and k, gate and up): the rows are quantised once, and laid
+    // out once for the tensor-memory GEMM; results are those of two `linear` calls.
+    Status linear_pair(int dtype, const uint8_t *w1, float *y1, uint32_t out_f1, const uint8_t *w2, float *y2, uint32_t out_f2, const float *x,
+                       uint32_t m, uint32_t in_f, int act);
     // Op::MoeFfn (crates/infr-cpu/src/lib.rs:2264-2984), qwen3moe configuration.  Optional debug outputs:
     // sel_ids [rows,n_used] i32, sel_w [rows,n_used] f32, logits [rows,n_expert] f32 (null = not wanted).
     struct MoeArgs {
@@ -191,6 +195,7 @@ private:
     int gemv_impl_ = 0;                // 0 = bulk-copy ring kernel, 1 = direct-load kernel
     int mmq_impl_ = 0;                 // 0 = warp-specialised MMQ (f32 within rounding of the CPU), 1 = bit-identical MMQ
     Status check_device_status();
+    Status mmq_linear(const uint8_t *w, const float *x, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, bool reuse);
     // Device blocks behind the Internal handles of compiled plans; a freed plan's blocks are reused by the next
     // compile (the reference rebuilds its graph every step, so compile must not cost an allocation each time).
     struct PoolBlock {

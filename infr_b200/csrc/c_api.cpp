@@ -260,6 +260,18 @@ int32_t infr_cuda_linear(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf 
     return finish(ctx, ctx->be->linear(dtype, pw, (const float *)px, (float *)py, m, in_f, out_f, act));
 }
 
+int32_t infr_cuda_linear_pair(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w1, uint64_t w_off1, infr_cuda_buf *y1, uint32_t out_f1,
+                              const infr_cuda_buf *w2, uint64_t w_off2, infr_cuda_buf *y2, uint32_t out_f2, const infr_cuda_buf *x, uint32_t m,
+                              uint32_t in_f, int32_t act) {
+    INFR_CTX_OR_RETURN(ctx);
+    uint8_t *pw1, *pw2, *px, *py1, *py2;
+    Status s = linear_args(w1, w_off1, x, y1, dtype, m, in_f, out_f1, &pw1, &px, &py1);
+    if (s.ok()) s = linear_args(w2, w_off2, x, y2, dtype, m, in_f, out_f2, &pw2, &px, &py2);
+    if (!s.ok()) return finish(ctx, s);
+    if (py1 == py2) return finish(ctx, Status::Err(INFR_E_INVALID, "linear_pair: the two results need different buffers"));
+    return finish(ctx, ctx->be->linear_pair(dtype, pw1, (float *)py1, out_f1, pw2, (float *)py2, out_f2, (const float *)px, m, in_f, act));
+}
+
 int32_t infr_cuda_gemv_q8(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off, const infr_cuda_buf *qs,
                           const infr_cuda_buf *d, const infr_cuda_buf *sums, const infr_cuda_buf *sums16, infr_cuda_buf *y,
                           uint32_t m, uint32_t in_f, uint32_t out_f) {

@@ -78,8 +78,16 @@ cudaError_t launch_mmq_q4k(const uint8_t *w, const Q8Dev &a, void *records, floa
 // The same GEMM with specialised warps (unpack / MMA issue / epilogue overlap) and the min term summed in
 // tensor memory by kind::tf32 MMAs: int32 block sums identical, f32 result within rounding of the CPU's.
 size_t mmq_ws_record_bytes(int m, int in_f);
+// Few row x token tiles (a batch of a few dozen rows, a few thousand outputs): K is split across CTAs and a second
+// kernel adds the partial results in split order; `partials` is mmq_ws_partial_bytes(...) bytes of scratch.
+int mmq_ws_k_splits(int m, int in_f, int out_f, const DeviceInfo &dev);
+size_t mmq_ws_partial_bytes(int m, int in_f, int out_f, const DeviceInfo &dev);
 cudaError_t launch_mmq_ws_q4k(const uint8_t *w, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
-                              const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
+                              const DeviceInfo &dev, uint32_t *status, cudaStream_t st, float *partials = nullptr);
+// The GEMM from f32 activations: x != nullptr quantises them straight into the kernel's layout in `records`; x == nullptr
+// reuses what a previous call wrote there for the same activations (q and k, gate and up of a batch).
+cudaError_t launch_mmq_ws_q4k_f32(const uint8_t *w, const float *x, void *records, float *c, int m, int in_f, int out_f,
+                                  const DeviceInfo &dev, uint32_t *status, cudaStream_t st, float *partials = nullptr);
 // The same tensor-memory GEMM over a bank of expert matrices, one 64-token slab of routed rows per tile column
 // (mmq_ws.cu).  `records`: mmq_ws_record_bytes(max_slabs * 64, in_f) bytes; prep = false reuses planes already laid.
 cudaError_t launch_mmq_ws_q4k_grouped(const uint8_t *bank, int n_experts, const Q8Dev &a, void *records, float *y, int in_f, int out_f,

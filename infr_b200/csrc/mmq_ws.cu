@@ -207,6 +207,53 @@ __global__ void mmq_ws_prep_kernel(const int8_t *__restrict__ qs, const int32_t 
 }
 
 
+// f32 activations straight to the kernel's planes: quantize_q8 (crates/infr-cpu/src/quant.rs:27-58, the operations of
+// quantize.cu in the same order, so the same codes, scales and sums) and the re-layout above in one pass.  One warp per
+// (token, super-block); lane l owns elements [4l, 4l+4) and [128+4l, 128+4l+4).
+__global__ void __launch_bounds__(256) mmq_ws_quant_planes_kernel(const float *__restrict__ x, int m, int m_pad, int nb,
+                                                                  uint32_t *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wg >= (long long)m * nb) return;
+    const int tok = (int)(wg / nb), b = (int)(wg % nb);
+    const float *xp = x + ((size_t)tok * nb + b) * 256;
+    const float4 v0 = *reinterpret_cast<const float4 *>(xp + lane * 4), v1 = *reinterpret_cast<const float4 *>(xp + 128 + lane * 4);
+    float am = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                     fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    const float dd = am / 127.0f;
+    const float id = dd > 0.0f ? 1.0f / dd : 0.0f;
+    auto q1 = [&](float v) {
+        float r = roundf(v * id);
+        r = fminf(fmaxf(r, -127.0f), 127.0f);
+        return (int)r;
+    };
+    uint32_t *pl = out + ((size_t)b * kPlanes * m + tok) * 4;  // word 0 of this token's entry in plane 0 of block b
+    const size_t plane_words = (size_t)m * 4;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const float4 v = h ? v1 : v0;
+        const int q0 = q1(v.x), qq1 = q1(v.y), q2 = q1(v.z), q3 = q1(v.w);
+        int sum = q0 + qq1 + q2 + q3;
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        // elements [128h + 4l, +4) = 16-byte chunk 8h + l/4 of the block, word l%4 of the chunk
+        pl[(size_t)(8 * h + (lane >> 2)) * plane_words + (lane & 3)] =
+            (uint32_t)(q0 & 0xff) | ((uint32_t)(qq1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+        if ((lane & 7) == 0) {
+            // sub-block 4h + l/8: d8 * bsum as two tf32-representable pieces
+            const float t = __fmul_rn(dd, (float)sum);
+            const uint32_t hi = __float_as_uint(t) & 0xFFFFE000u;
+            const float r = __fsub_rn(t, __uint_as_float(hi));
+            pl[(size_t)(16 + h) * plane_words + (lane >> 3)] = hi;
+            pl[(size_t)(18 + h) * plane_words + (lane >> 3)] = __float_as_uint(r) & 0xFFFFE000u;
+        }
+    }
+    if (lane == 0) reinterpret_cast<float *>(out + (size_t)nb * kPlanes * m * 4)[(size_t)b * m_pad + tok] = dd;
+}
+
 namespace {
 
 __device__ __forceinline__ bool wait_plain(uint32_t bar, uint32_t parity, uint32_t limit) {
@@ -224,7 +271,7 @@ __device__ __forceinline__ bool wait_plain(uint32_t bar, uint32_t parity, uint32
 __global__ void __launch_bounds__(kThreadsWs, 1)
     mmq_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q,
                   const float *__restrict__ d8t, float *__restrict__ C, int m, int m_pad, int in_f, int out_f,
-                  uint32_t *__restrict__ status, MmqGroup grp) {
+                  uint32_t *__restrict__ status, MmqGroup grp, int kz) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *stage0 = smem;                                              // [kStages]{raw rows, activation planes}
     uint8_t *minbuf0 = smem + kStages * kStageBytes;                     // [2][kMinBytes]
@@ -238,7 +285,18 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
     const int nb = in_f >> 8;
     // grouped: one token tile per slab (their number is known only on the device)
     const int row_tiles = (out_f + kTM - 1) / kTM, tok_tiles = grp.slab_expert ? *grp.n_slabs : (m + kTN - 1) / kTN;
-    const int n_tiles = row_tiles * tok_tiles;
+    // kz > 1: K is split kz ways across tiles (a batch of a few dozen rows against a matrix with few row tiles would
+    // otherwise keep most SMs idle while a handful walk all of K); split s writes its partial result to C + s * m * out_f
+    // and a second kernel adds the partial results in order.
+    const int n_tiles = row_tiles * tok_tiles * kz;
+    auto tile_of = [&](int t, int *rt, int *tt, int *b0, int *b1) {
+        const int ks = t % kz, tr = t / kz;
+        *rt = tr % row_tiles;  // consecutive CTAs share a token tile
+        *tt = tr / row_tiles;
+        *b0 = ks * nb / kz;
+        *b1 = (ks + 1) * nb / kz;
+        return ks;
+    };
 
     if (tid == 0) {
         s_dead = 0;
@@ -269,9 +327,10 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
             int j = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                const int rt = t % row_tiles, tt = t / row_tiles;  // consecutive CTAs share a token tile
+                int rt, tt, b0, b1;
+                tile_of(t, &rt, &tt, &b0, &b1);
                 const int wrow0 = (grp.slab_expert ? grp.slab_expert[tt] * out_f : 0) + rt * kTM;
-                for (int b = 0; b < nb; b++, j++) {
+                for (int b = b0; b < b1; b++, j++) {
                     const int s = j % kStages;
                     // the stage's previous job is complete (its operands were read by the MMAs, its rows unpacked)
                     if (j >= kStages && !wait_bar(bar(B_DONE + s), (uint32_t)((j / kStages - 1) & 1), dead)) {
@@ -308,7 +367,9 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
         int j = 0, tile_i = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, tile_i++) {
-            for (int b = 0; b < nb && ok; b++, j++) {
+            int rt_, tt_, b0, b1;
+            tile_of(t, &rt_, &tt_, &b0, &b1);
+            for (int b = b0; b < b1 && ok; b++, j++) {
                 const int s = j & 1, ls = j % kStages;
                 const int slot0 = (2 * j) % (int)kSlots, n0 = (2 * j) / (int)kSlots;
                 const int slot1 = (2 * j + 1) % (int)kSlots, n1 = (2 * j + 1) / (int)kSlots;
@@ -324,7 +385,7 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                 // ahead: its next arrival needs the commit of this job.
                 if (lane == 5) wb = bar(B_MINREADY + s), wp = (uint32_t)((j >> 1) & 1), need = role == 2;
                 // the tile's first min MMA overwrites the sums of the previous tile: the epilogue has read them
-                if (lane == 4) wb = bar(B_MINFREE), wp = (uint32_t)((tile_i - 1) & 1), need = role == 2 && b == 0 && tile_i >= 1;
+                if (lane == 4) wb = bar(B_MINFREE), wp = (uint32_t)((tile_i - 1) & 1), need = role == 2 && b == b0 && tile_i >= 1;
                 if (!wait_multi(wb, wp, need, dead)) {
                     ok = false;
                     break;
@@ -335,10 +396,10 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
                     if (role == 2) {
                         const uint8_t *mb = minbuf0 + (size_t)s * kMinBytes;
                         const uint64_t a1 = mk_desc(su32(mb), kTM * 16, 128), a2 = mk_desc(su32(mb + 2 * kTM * 16), kTM * 16, 128);
-                        const uint64_t b1 = db0 + (uint64_t)(16 * kTN), b2 = db0 + (uint64_t)(18 * kTN);
-                        mma_tf32(tmin, a1, b1, idesc_tf, b > 0 ? 1u : 0u);
-                        mma_tf32(tmin, a2, b1, idesc_tf, 1u);
-                        mma_tf32(tmin, a1, b2, idesc_tf, 1u);
+                        const uint64_t bd1 = db0 + (uint64_t)(16 * kTN), bd2 = db0 + (uint64_t)(18 * kTN);
+                        mma_tf32(tmin, a1, bd1, idesc_tf, b > b0 ? 1u : 0u);
+                        mma_tf32(tmin, a2, bd1, idesc_tf, 1u);
+                        mma_tf32(tmin, a1, bd2, idesc_tf, 1u);
                     } else {
                         const uint32_t td = tmem + (uint32_t)s * 2 * kTN + (uint32_t)role * kTN;
 #pragma unroll
@@ -374,7 +435,9 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
         int j = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-            for (int b = 0; b < nb; b++, j++) {
+            int rt_, tt_, b0, b1;
+            tile_of(t, &rt_, &tt_, &b0, &b1);
+            for (int b = b0; b < b1; b++, j++) {
                 const int ls = j % kStages;
                 const int r = 2 * j + h, slot = r % (int)kSlots, n = r / (int)kSlots;
                 // two waits on two lanes: the rows have landed, the operand slot's previous MMAs are complete
@@ -459,11 +522,13 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
         int j = 0, tile_i = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, tile_i++) {
-            const int rt = t % row_tiles, tt = t / row_tiles;
+            int rt, tt, b0, b1;
+            const int ks = tile_of(t, &rt, &tt, &b0, &b1);
+            float *Ct = C + (size_t)ks * m * out_f;  // this K split's partial result
             const float4 *d8p = reinterpret_cast<const float4 *>(d8t + (size_t)tt * kTN + half * 32);
 #pragma unroll
             for (int i = 0; i < 32; i++) acc[i] = 0.f;
-            for (int b = 0; b < nb; b++, j++) {
+            for (int b = b0; b < b1; b++, j++) {
                 const int s = j & 1;
                 float4 dd[4];
 #pragma unroll
@@ -519,7 +584,7 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
                     const int slot = half * 32 + c * 16 + i;
-                    if (grow < out_f && slot < tok_lim) C[(out_row0 + slot) * out_f + grow] = acc[c * 16 + i] - __uint_as_float(mv[i]);
+                    if (grow < out_f && slot < tok_lim) Ct[(out_row0 + slot) * out_f + grow] = acc[c * 16 + i] - __uint_as_float(mv[i]);
                 }
             }
         }
@@ -553,16 +618,47 @@ size_t mmq_ws_record_bytes(int m, int in_f) {
     return nb * kPlanes * (size_t)m * 16 + nb * m_pad * 4;
 }
 
+// How many ways K is split for C[m, out_f]: 1 when the row x token tiles alone fill the SMs, else enough splits to
+// occupy them (at most one split per super-block, at most 16).
+int mmq_ws_k_splits(int m, int in_f, int out_f, const DeviceInfo &dev) {
+    const int tiles = ((out_f + kTM - 1) / kTM) * ((m + kTN - 1) / kTN), nb = in_f / 256;
+    if (tiles * 2 > dev.sm_count) return 1;
+    int kz = dev.sm_count / tiles;
+    if (kz > nb) kz = nb;
+    if (kz > 16) kz = 16;
+    return kz < 1 ? 1 : kz;
+}
+size_t mmq_ws_partial_bytes(int m, int in_f, int out_f, const DeviceInfo &dev) {
+    const int kz = mmq_ws_k_splits(m, in_f, out_f, dev);
+    return kz > 1 ? (size_t)kz * m * out_f * 4 : 0;
+}
+
+// y[i] = part[0][i] + part[1][i] + ... in split order (the same bits on every run).
+__global__ void mmq_ws_sum_splits_kernel(const float4 *__restrict__ part, float4 *__restrict__ y, size_t n4, int kz) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    float4 acc = part[i];
+    for (int s = 1; s < kz; s++) {
+        const float4 v = part[(size_t)s * n4 + i];
+        acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+    }
+    y[i] = acc;
+}
+
 namespace {
 // Common launch: `m` token slots (a multiple of 64 in grouped mode: all slabs that can exist), weight tensor map over
 // `w_rows` rows.  prep = false reuses the planes a previous call with the same activations and slabs has written.
 cudaError_t launch_ws(const uint8_t *w, size_t w_rows, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
-                      const MmqGroup &grp, int max_tok_tiles, bool prep, const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+                      const MmqGroup &grp, int max_tok_tiles, bool prep, const DeviceInfo &dev, uint32_t *status, cudaStream_t st,
+                      int kz = 1, float *partials = nullptr, const float *x_f32 = nullptr) {
     EncodeFn enc = encode_fn();
     if (!enc) return cudaErrorNotSupported;
     const int nb = in_f / 256, m_pad = (m + kTN - 1) / kTN * kTN;
     const int n_rec = m * nb;
-    if (prep) mmq_ws_prep_kernel<<<(n_rec + 255) / 256, 256, 0, st>>>(a.qs, a.sums, a.d, m, m_pad, nb, static_cast<uint4 *>(records), grp);
+    if (prep && x_f32)
+        mmq_ws_quant_planes_kernel<<<(unsigned)(((size_t)n_rec * 32 + 255) / 256), 256, 0, st>>>(x_f32, m, m_pad, nb, static_cast<uint32_t *>(records));
+    else if (prep)
+        mmq_ws_prep_kernel<<<(n_rec + 255) / 256, 256, 0, st>>>(a.qs, a.sums, a.d, m, m_pad, nb, static_cast<uint4 *>(records), grp);
     CUtensorMap map_w, map_q;
     const cuuint32_t one2[2] = {1, 1};
     {
@@ -585,17 +681,36 @@ cudaError_t launch_ws(const uint8_t *w, size_t w_rows, const Q8Dev &a, void *rec
     const float *d8t = reinterpret_cast<const float *>(static_cast<const uint8_t *>(records) + (size_t)nb * kPlanes * m * 16);
     cudaError_t e = cudaFuncSetAttribute(mmq_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) return e;
-    const int n_tiles = ((out_f + kTM - 1) / kTM) * max_tok_tiles;
+    const int n_tiles = ((out_f + kTM - 1) / kTM) * max_tok_tiles * kz;
     const int grid = n_tiles < dev.sm_count ? n_tiles : dev.sm_count;
-    mmq_ws_kernel<<<grid, kThreadsWs, kSmem, st>>>(map_w, map_q, d8t, c, m, m_pad, in_f, out_f, status, grp);
+    mmq_ws_kernel<<<grid, kThreadsWs, kSmem, st>>>(map_w, map_q, d8t, kz > 1 ? partials : c, m, m_pad, in_f, out_f, status, grp, kz);
+    if (kz > 1) {
+        const size_t n = (size_t)m * out_f;
+        if (n % 4) return cudaErrorInvalidValue;  // (callers split K only when out_f is a multiple of 4)
+        mmq_ws_sum_splits_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(reinterpret_cast<const float4 *>(partials),
+                                                                                 reinterpret_cast<float4 *>(c), n / 4, kz);
+    }
     return cudaGetLastError();
 }
 }  // namespace
 
+// `partials`: mmq_ws_partial_bytes(m, in_f, out_f) bytes of scratch (may be null when that is 0).
 cudaError_t launch_mmq_ws_q4k(const uint8_t *w, const Q8Dev &a, void *records, float *c, int m, int in_f, int out_f,
-                              const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+                              const DeviceInfo &dev, uint32_t *status, cudaStream_t st, float *partials) {
     if (m < 1 || in_f % 256 || out_f < 1) return cudaErrorInvalidValue;
-    return launch_ws(w, (size_t)out_f, a, records, c, m, in_f, out_f, MmqGroup{}, (m + kTN - 1) / kTN, true, dev, status, st);
+    int kz = (out_f % 4 == 0 && partials && ((uintptr_t)c % 16) == 0) ? mmq_ws_k_splits(m, in_f, out_f, dev) : 1;
+    return launch_ws(w, (size_t)out_f, a, records, c, m, in_f, out_f, MmqGroup{}, (m + kTN - 1) / kTN, true, dev, status, st, kz, partials);
+}
+
+// From f32 activations: x != nullptr quantises them straight into the planes in `records` (one kernel instead of the
+// quantiser plus the re-layout); x == nullptr reuses the planes a previous call wrote for the same activations.
+cudaError_t launch_mmq_ws_q4k_f32(const uint8_t *w, const float *x, void *records, float *c, int m, int in_f, int out_f,
+                                  const DeviceInfo &dev, uint32_t *status, cudaStream_t st, float *partials) {
+    if (m < 1 || in_f % 256 || out_f < 1) return cudaErrorInvalidValue;
+    if (x && ((uintptr_t)x % 16)) return cudaErrorInvalidValue;
+    int kz = (out_f % 4 == 0 && partials && ((uintptr_t)c % 16) == 0) ? mmq_ws_k_splits(m, in_f, out_f, dev) : 1;
+    return launch_ws(w, (size_t)out_f, Q8Dev{}, records, c, m, in_f, out_f, MmqGroup{}, (m + kTN - 1) / kTN, x != nullptr, dev, status, st, kz,
+                     partials, x);
 }
 
 // Expert-grouped GEMM over a bank of n_experts Q4_K matrices [out_f, in_f] stored back to back: slab i (a work item

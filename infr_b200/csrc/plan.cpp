@@ -6,10 +6,13 @@
 // and groups neighbouring ops that one launch can do:
 //   Add, RmsNorm                      -> the residual add fused in front of the norm
 //                                        (runner.rs:3824-3838 emits exactly this pair between the two halves of a layer)
+//   Linear, Linear (same rows, same format) -> rows quantised once, one launch for a decode batch of Q4_K
+//                                        (runner.rs:3476-3523 q/k/v, :3882-3933 gate/up)
 //   Rope(k), Rope(q), WriteKv, WriteKv -> q rotated in place, k rotated and v cast straight into the f16 caches
 //                                        (runner.rs:3611-3656), when the rotated k has no other reader
-// The grouped launches compute the same values with the same roundings as the separate ops (the kernels are the same
-// templates), so a graph gives the same bits either way.
+// The grouped norm and rope launches compute the same values with the same roundings as the separate ops (the kernels
+// are the same templates); a pair of Linears has the separate ops' integer block sums and may add its f32 partial sums
+// in a different order (K is split over a different number of warps).
 // execute follows the provisioning contract of crates/infr-core/src/exec.rs:53-139: Internal handles are backend
 // scratch that reads as zero until an op writes it, Inputs / Weights / Outputs are the caller's bound buffers,
 // KV-cache Inputs are written in place, and every Output is in its bound buffer when the stream reaches the caller's
@@ -204,6 +207,13 @@ Status CudaBackend::compile(const infr_graph_desc &g, infr_cuda_plan **out) {
                 n.t[2] != a.t[1])
                 st = PlanStep{PlanStep::kAddRmsNorm, i, 2};
         }
+        if (a.tag == INFR_OP_LINEAR && i + 1 < g.n_ops) {
+            // two Linears of one weight format reading the same rows (q and k, gate and up): quantised once
+            const infr_op_desc &n = g.ops[i + 1];
+            if (n.tag == INFR_OP_LINEAR && n.t[0] == a.t[0] && n.u[0] == a.u[0] && n.u[1] == a.u[1] &&
+                plan->tensors[n.t[1]].dtype == plan->tensors[a.t[1]].dtype && n.t[2] != a.t[2] && a.t[2] != a.t[0] && n.t[2] != a.t[0])
+                st = PlanStep{PlanStep::kLinearPair, i, 2};
+        }
         if (a.tag == INFR_OP_ROPE && i + 3 < g.n_ops) {
             const infr_op_desc &rq = g.ops[i + 1], &wk = g.ops[i + 2], &wv = g.ops[i + 3];
             bool ok = rq.tag == INFR_OP_ROPE && wk.tag == INFR_OP_WRITE_KV && wv.tag == INFR_OP_WRITE_KV;
@@ -307,6 +317,23 @@ Status CudaBackend::execute(infr_cuda_plan *plan, infr_cuda_buf *const *bindings
             INFR_RESOLVE(nm.t[1], (size_t)dim * 4, "RmsNorm weight", &w);
             INFR_RESOLVE(nm.t[2], nb, "RmsNorm dst", &dst);
             s = rms_norm(f32p(a), f32p(b), f32p(sum), f32p(w), f32p(dst), rows, dim, nm.f[0]);
+            if (!s.ok()) return s;
+            continue;
+        }
+        if (st.kind == PlanStep::kLinearPair) {
+            const infr_op_desc &o2 = plan->ops[st.op0 + 1];
+            const uint32_t m = op.u[0], in_f = op.u[1];
+            const int wdt = (int)plan->tensors[op.t[1]].dtype;
+            const size_t bpr = (size_t)(in_f / block_elems(wdt)) * block_bytes(wdt);
+            const size_t r1 = op.u[3] / in_f, r2 = o2.u[3] / in_f;
+            DevSpan x, w1, w2, y1, y2;
+            INFR_RESOLVE(op.t[0], (size_t)m * in_f * 4, "Linear x", &x);
+            INFR_RESOLVE(op.t[1], (r1 + op.u[2]) * bpr, "Linear weight", &w1);
+            INFR_RESOLVE(o2.t[1], (r2 + o2.u[2]) * bpr, "Linear weight", &w2);
+            INFR_RESOLVE(op.t[2], (size_t)m * op.u[2] * 4, "Linear dst", &y1);
+            INFR_RESOLVE(o2.t[2], (size_t)m * o2.u[2] * 4, "Linear dst", &y2);
+            s = linear_pair(wdt, w1.ptr + r1 * bpr, f32p(y1), op.u[2], w2.ptr + r2 * bpr, f32p(y2), o2.u[2], f32p(x), m, in_f,
+                            reference_ ? INFR_ACT_F32 : INFR_ACT_INT8);
             if (!s.ok()) return s;
             continue;
         }

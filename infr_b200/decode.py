@@ -132,6 +132,20 @@ class DecodeStep:
 
         def lin_many(x, k, outs):
             nonlocal n
+            if fused and not share:
+                # wider batches: neighbours of one weight format share the quantised (and re-laid) rows
+                i = 0
+                while i < len(outs):
+                    if i + 1 < len(outs) and outs[i][0] == outs[i + 1][0]:
+                        (dt, w1, y1, o1), (_, w2, y2, o2) = outs[i], outs[i + 1]
+                        be.linear_pair(dt, w1, y1, o1, w2, y2, o2, x, b, k, ACT_INT8)
+                        i += 2
+                    else:
+                        dt, w, y, o = outs[i]
+                        lin(dt, w, x, y, k, o)
+                        i += 1
+                n += len(outs)
+                return
             if share:
                 be.quantize_q8(256, x, b, k, self.a_qs, self.a_d, self.a_sums, self.a_sums16)
                 for dt, w, y, o in outs:

@@ -135,7 +135,7 @@ def test_decode_graph_through_compile_execute_equals_direct_calls_and_cpu(backen
         np.testing.assert_array_equal(backend.download(kcb2[li], np.uint16), want_k[li])
         np.testing.assert_array_equal(backend.download(vcb2[li], np.uint16), want_v[li])
     # the plan groups launches: fewer kernels than the 17 ops per layer it was given
-    assert launches < 17 * s.n_layer + 4, launches
+    assert launches <= 15 * s.n_layer + 4, launches
     # the mutated f32 Input is visible in its bound buffer (graph_input_inplace): hidden now holds the residual stream
     assert not np.array_equal(backend.download(hidden_b, np.float32), hidden.ravel())
 
@@ -192,8 +192,7 @@ def test_prefill_rows_of_one_sequence_through_the_graph(backend):
     for li, L in enumerate(dev_layers):
         dts = {name: dt for name, dt, _, _ in s.linears()}
         be.rms_norm(hid, L["attn_norm"], hn, rows, h, s.eps)
-        be.linear(dts["wq"], L["wq"], hn, q, rows, h, qd)
-        be.linear(dts["wk"], L["wk"], hn, k, rows, h, kvd)
+        be.linear_pair(dts["wq"], L["wq"], q, qd, L["wk"], k, kvd, hn, rows, h)  # the plan pairs q / k and gate / up too
         be.linear(dts["wv"], L["wv"], hn, v, rows, h, kvd)
         be.rope(k, pos_b, k16, rows, s.n_kv, s.head_dim, s.head_dim, s.theta)
         be.rope(q, pos_b, q, rows, s.n_head, s.head_dim, s.head_dim, s.theta)
@@ -203,8 +202,7 @@ def test_prefill_rows_of_one_sequence_through_the_graph(backend):
         be.linear(dts["wo"], L["wo"], attn, sub, rows, qd, h)
         be.add(hid, sub, hid, rows * h)
         be.rms_norm(hid, L["ffn_norm"], hn, rows, h, s.eps)
-        be.linear(dts["gate"], L["gate"], hn, gb, rows, h, ff)
-        be.linear(dts["up"], L["up"], hn, ub, rows, h, ff)
+        be.linear_pair(dts["gate"], L["gate"], gb, ff, L["up"], ub, ff, hn, rows, h)
         be.gated_act(gb, ub, act, rows, ff)
         be.linear(dts["down"], L["down"], act, sub, rows, ff, h)
         be.add(hid, sub, hid, rows * h)

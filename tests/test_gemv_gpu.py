@@ -70,8 +70,6 @@ SHAPES = [
 
 
 def _weight(dt, out_f, in_f, seed):
-    if out_f * in_f <= 1 << 20:
-        return synth.weight(dt, out_f, in_f, seed)
     return synth.weight(dt, out_f, in_f, seed)
 
 

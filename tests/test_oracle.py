@@ -133,6 +133,53 @@ def test_quantize_q8_32_and_q8_1_share_codes(oracle):
     np.testing.assert_array_equal(sact, (d * bs.astype(np.float32)).astype(np.float16).view(np.uint16))
 
 
+# ---- the 32-granular "Q8_1" GEMM tier of the reference's GPU backend
+# (crates/infr-vulkan/shaders/native_gemm_mmq_q4k.comp:170-223, native_gemm_mmq_q6k.comp:151-219,
+#  native_gemm_mmq_q2_0.comp:160-199): its integer block sums are the dequantised codes' dot products, and its f32
+# result sits within quantisation distance of the production CPU tier and of the dequant reference.
+@pytest.mark.parametrize("dt", [Q4K, Q6K, Q2_0])
+def test_q8_1_gemm_tier_block_sums_and_distance_to_production(oracle, dt):
+    import infr_b200.synth as synth
+    m, in_f, out_f = 3, 512, 24
+    w = synth.weight(dt, out_f, in_f, seed=40 + dt)
+    x = np.stack([fx.det_x(in_f, 60 + r) * np.float32(1.0 + r) for r in range(m)])
+    qa = np.empty((m, in_f), np.int8)
+    dact = np.empty((m, in_f // 32), np.uint16)
+    sact = np.empty((m, in_f // 32), np.uint16)
+    for r in range(m):
+        qa[r], dact[r], sact[r] = oracle.quantize_q8_1(x[r])
+    got, qsum = oracle.mmq_q8_1(dt, w, qa, dact, sact, m, in_f, out_f, want_qsum=True)
+
+    # Integer block sums: weight codes (no scale) against activation codes, exact.
+    wq = np.asarray(w, np.uint8).reshape(out_f, -1)
+    step = 16 if dt == Q6K else 32
+    codes = np.empty((out_f, in_f), np.int64)
+    for o in range(out_f):
+        wz = wq[o].copy()
+        be, bb = fx.BLOCK[dt]
+        one = np.float16(1.0).view(np.uint16)
+        for b in range(in_f // be):
+            # d = 1, every sub-scale 1, min 0: dequant returns the bare codes (Q6_K: code-32, Q2_0: code-1).
+            blk = wz[b * bb:(b + 1) * bb]
+            if dt == Q4K:
+                blk[0:2] = np.frombuffer(one.tobytes(), np.uint8); blk[2:4] = 0
+                blk[4:8] = 1; blk[8:12] = 0; blk[12:16] = 1
+            elif dt == Q6K:
+                blk[192:208] = 1; blk[208:210] = np.frombuffer(one.tobytes(), np.uint8)
+            else:
+                blk[0:2] = np.frombuffer(one.tobytes(), np.uint8)
+        codes[o] = np.rint(oracle.dequant(dt, wz)).astype(np.int64)
+    want_qsum = np.einsum("okl,rkl->rok", codes.reshape(out_f, -1, step), qa.astype(np.int64).reshape(m, -1, step))
+    np.testing.assert_array_equal(qsum, want_qsum)
+
+    prod = oracle.linear(dt, w, x, m, in_f, out_f)
+    ref = oracle.linear(dt, w, x, m, in_f, out_f, reference=True)
+    rel = lambda a, b: float(np.linalg.norm(a - b) / np.linalg.norm(b))
+    assert rel(got, ref) < 2e-2      # the reference's own production-vs-reference bar
+    assert rel(got, prod) < 2e-2     # two quantisation granularities of the same activations
+    assert rel(got, prod) > 0        # ... which are different computations
+
+
 def _dequant_q8(q8, gran):
     qs, d = q8[0], q8[1]
     return (qs.reshape(-1, gran).astype(np.float32) * d[:, None]).ravel()

@@ -282,11 +282,18 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
     if (in_f % 16) return Status::Err(INFR_E_INVALID, fmt("linear: in_f=%u must be a multiple of 16", in_f));
     if (m == 0 || out_f == 0) return Status::Ok();
     cudaSetDevice(device_);
-    // Q4_K with int8 activations and more than 8 rows goes to the tensor-memory GEMM (all rows quantised once, the
-    // weights unpacked once).  A batch of a few dozen rows against a matrix with few 128-row tiles would leave most
-    // SMs idle there while a handful walk all of K, so the GEMM splits K across CTAs for such shapes
-    // (mmq_ws_k_splits).  mmq_kernel 3 walks the batch through the GEMV 8 rows at a time instead (the parity tests
-    // and the bench compare the two).
+    // More than 8 rows with int8 activations: a few dozen rows (a decode step over that many sequences) take the wide
+    // GEMV, which unpacks every weight byte once per 32 rows and is bound by the weight stream; beyond that Q4_K goes
+    // to the tensor-memory GEMM (all rows quantised once, the weights unpacked once per 64 rows, K split across CTAs
+    // when the row x token tiles alone would leave SMs idle: mmq_ws_k_splits).  mmq_kernel 2 sends every Q4_K batch
+    // above 8 rows to the GEMM, 3 walks every batch through the GEMV 8 rows at a time (the parity tests and the bench
+    // compare the three).
+    if (wide_applies(dtype, m, in_f, act)) {
+        Q8Dev a;
+        uint8_t *partials = nullptr;
+        Status s = quantize_for(dtype, x, m, in_f, &a, gemv_wide_partial_bytes(m < 32 ? (int)m : 32, (int)in_f, (int)out_f), &partials);
+        return s.ok() ? wide_gemm(dtype, w, a, y, m, in_f, out_f, reinterpret_cast<float *>(partials)) : s;
+    }
     const bool use_mmq = m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0 && mmq_impl_ != 3;
     if (use_mmq && mmq_impl_ == 1) {
         Q8Dev a;
@@ -369,6 +376,31 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
     return Status::Ok();
 }
 
+bool CudaBackend::wide_applies(int dtype, uint32_t m, uint32_t in_f, int act) const {
+    if (act != INFR_ACT_INT8 || m <= 8 || gemv_impl_ != 0 || mmq_impl_ != 0 || in_f == 0 || in_f % 256) return false;
+    if (dtype == DT_Q4K) return m <= 64;           // above: the tensor-memory GEMM
+    if (dtype == DT_Q6K) return in_f % 2048 == 0;  // (rows of a whole number of 16-byte units: the TMA stride rule)
+    return false;
+}
+
+// y[m, out_f] from quantised rows, 32 rows per pass of the weights.
+Status CudaBackend::wide_gemm(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, float *partials) {
+    const uint32_t nb = in_f / 256;
+    for (uint32_t r0 = 0; r0 < m; r0 += 32) {
+        const uint32_t mm = m - r0 < 32 ? m - r0 : 32;
+        Q8Dev sub = a;
+        sub.qs = a.qs + (size_t)r0 * in_f;
+        sub.d = a.d + (size_t)r0 * nb;
+        sub.sums = a.sums + (size_t)r0 * nb * 8;
+        if (a.sums16) sub.sums16 = a.sums16 + (size_t)r0 * nb * 16;
+        Status s = cuda_status(launch_gemv_wide(dtype, w, sub, y + (size_t)r0 * out_f, partials, (int)mm, (int)in_f, (int)out_f, dev_, status_dev_, stream_),
+                               "gemv_wide");
+        if (!s.ok()) return s;
+        launches_ += (uint64_t)gemv_wide_launches((int)in_f);
+    }
+    return Status::Ok();
+}
+
 // The tensor-memory GEMM from f32 rows.  The context scratch holds the activation planes (and the K-split partial
 // results behind them); reuse = the planes are those of the previous call's rows (same x, m, in_f) and are not rebuilt.
 Status CudaBackend::mmq_linear(const uint8_t *w, const float *x, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, bool reuse) {
@@ -388,6 +420,16 @@ Status CudaBackend::mmq_linear(const uint8_t *w, const float *x, float *y, uint3
 // Two weights of one format against the same f32 rows (q and k, gate and up): the rows are quantised once.
 Status CudaBackend::linear_pair(int dtype, const uint8_t *w1, float *y1, uint32_t out_f1, const uint8_t *w2, float *y2, uint32_t out_f2,
                                 const float *x, uint32_t m, uint32_t in_f, int act) {
+    if (wide_applies(dtype, m, in_f, act) && out_f1 && out_f2) {
+        cudaSetDevice(device_);
+        const int mm = m < 32 ? (int)m : 32;
+        const size_t p1 = gemv_wide_partial_bytes(mm, (int)in_f, (int)out_f1), p2 = gemv_wide_partial_bytes(mm, (int)in_f, (int)out_f2);
+        Q8Dev a;
+        uint8_t *partials = nullptr;
+        Status s = quantize_for(dtype, x, m, in_f, &a, p1 > p2 ? p1 : p2, &partials);
+        if (s.ok()) s = wide_gemm(dtype, w1, a, y1, m, in_f, out_f1, reinterpret_cast<float *>(partials));
+        return s.ok() ? wide_gemm(dtype, w2, a, y2, m, in_f, out_f2, reinterpret_cast<float *>(partials)) : s;
+    }
     const bool q4_gemm = m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0 && (mmq_impl_ == 0 || mmq_impl_ == 2);
     if (q4_gemm && in_f && in_f % 256 == 0 && out_f1 && out_f2) {
         cudaSetDevice(device_);
@@ -402,6 +444,17 @@ Status CudaBackend::linear_pair(int dtype, const uint8_t *w1, float *y1, uint32_
     if (act == INFR_ACT_INT8 && m >= 1 && m <= 8 && (dtype == DT_Q4K || dtype == DT_Q6K || dtype == DT_Q2_0) && in_f &&
         in_f % (uint32_t)block_elems(dtype) == 0 && in_f % 16 == 0 && out_f1 && out_f2) {
         cudaSetDevice(device_);
+        if (dtype == DT_Q4K && gemv_impl_ == 0 && in_f % 256 == 0) {
+            // one kernel: the rows are quantised inside the GEMV while the first weights stream in
+            const cudaError_t e = launch_gemv_q4k_mma_pair(w1, y1, (int)out_f1, w2, y2, (int)out_f2, nullptr, x, (int)m, (int)in_f, dev_,
+                                                           status_dev_, stream_);
+            if (e == cudaSuccess) {
+                launches_++;
+                return Status::Ok();
+            }
+            if (e != cudaErrorInvalidValue) return cuda_status(e, "linear_pair");
+            cudaGetLastError();  // rows too long to stage m of them in one CTA: quantise first, then the pair
+        }
         Q8Dev a;
         Status s = quantize_for(dtype, x, m, in_f, &a);
         return s.ok() ? gemv_q8_pair(dtype, w1, y1, out_f1, w2, y2, out_f2, a, m, in_f) : s;
@@ -431,7 +484,7 @@ Status CudaBackend::gemv_q8_pair(int dtype, const uint8_t *w1, float *y1, uint32
                                  const Q8Dev &a, uint32_t m, uint32_t in_f) {
     if (dtype == DT_Q4K && gemv_impl_ == 0 && m >= 1 && m <= 8 && in_f && in_f % 256 == 0 && out_f1 && out_f2 && a.gran == 256) {
         cudaSetDevice(device_);
-        Status s = cuda_status(launch_gemv_q4k_mma_pair(w1, y1, (int)out_f1, w2, y2, (int)out_f2, a, (int)m, (int)in_f, dev_, status_dev_, stream_),
+        Status s = cuda_status(launch_gemv_q4k_mma_pair(w1, y1, (int)out_f1, w2, y2, (int)out_f2, &a, nullptr, (int)m, (int)in_f, dev_, status_dev_, stream_),
                                "gemv_q8_pair");
         if (s.ok()) launches_++;
         return s;

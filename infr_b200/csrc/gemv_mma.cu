@@ -611,11 +611,14 @@ cudaError_t launch_grouped_q4k_mma(const uint8_t *bank, int n_experts, const Q8D
     return launch_mma_cfg<8, false, 4, 2>(bank, a, nullptr, y, 8, in_f, out_f, dev, status, st, grp, n_experts, max_items);
 }
 
-// Two Q4_K matrices with the same in_f against the same pre-quantised rows, one launch.
-cudaError_t launch_gemv_q4k_mma_pair(const uint8_t *w1, float *y1, int out_f1, const uint8_t *w2, float *y2, int out_f2, const Q8Dev &a, int m,
-                                     int in_f, const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+// Two Q4_K matrices with the same in_f against the same rows, one launch: pre-quantised rows (a), or f32 rows (x, a null)
+// quantised inside the kernel.
+cudaError_t launch_gemv_q4k_mma_pair(const uint8_t *w1, float *y1, int out_f1, const uint8_t *w2, float *y2, int out_f2, const Q8Dev *a,
+                                     const float *x, int m, int in_f, const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
     if (m < 1 || m > 8 || in_f % 256 || out_f1 < 1 || out_f2 < 1) return cudaErrorInvalidValue;
-    return launch_mma<false>(w1, a, nullptr, y1, m, in_f, out_f1, dev, status, st, w2, y2, out_f2);
+    if (a) return launch_mma<false>(w1, *a, nullptr, y1, m, in_f, out_f1, dev, status, st, w2, y2, out_f2);
+    Q8Dev none{nullptr, nullptr, nullptr, nullptr, 256};
+    return launch_mma<true>(w1, none, x, y1, m, in_f, out_f1, dev, status, st, w2, y2, out_f2);
 }
 
 cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,

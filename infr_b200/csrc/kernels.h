@@ -62,11 +62,18 @@ cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x
                                 const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
 // Two Q4_K matrices [out_f1, in_f] and [out_f2, in_f] against the same pre-quantised rows in ONE launch (q and k,
 // gate and up: a decode step pays a fixed few microseconds per dependent launch).
-cudaError_t launch_gemv_q4k_mma_pair(const uint8_t *w1, float *y1, int out_f1, const uint8_t *w2, float *y2, int out_f2, const Q8Dev &a, int m,
-                                     int in_f, const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
+cudaError_t launch_gemv_q4k_mma_pair(const uint8_t *w1, float *y1, int out_f1, const uint8_t *w2, float *y2, int out_f2, const Q8Dev *a,
+                                     const float *x, int m, int in_f, const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
 // y[m,out_f] (m <= 8) from f32 activations and dequantised weights.
 cudaError_t launch_gemv_f32(int dt, const uint8_t *w, const float *x, float *y, int m, int in_f, int out_f,
                             const DeviceInfo &dev, cudaStream_t st);
+
+// Batched GEMV for 9..32 pre-quantised rows (Q4_K, Q6_K): every weight byte unpacked once for all rows, activations in
+// registers, K cut into chunks of 2048 elements across CTAs (`partials`: gemv_wide_partial_bytes(...) bytes of scratch).
+size_t gemv_wide_partial_bytes(int m, int in_f, int out_f);
+int gemv_wide_launches(int in_f);
+cudaError_t launch_gemv_wide(int dtype, const uint8_t *w, const Q8Dev &a, float *y, float *partials, int m, int in_f, int out_f,
+                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
 
 // Prefill GEMM C[m,out_f] = Q8(256) activations x Q4_K weights on tcgen05 (kind::i8, TMEM accumulators);
 // bit-identical to the CPU production path.

@@ -29,8 +29,8 @@ def exact_backend():
 
 @pytest.fixture(scope="module")
 def ws_backend():
-    """Every m > 8 Q4_K Linear on the warp-specialised GEMM, also the small batches that the default context would
-    walk through the GEMV 8 rows at a time."""
+    """Every m > 8 Q4_K Linear on the warp-specialised GEMM, also the batches of a few dozen rows that the default
+    context gives to the wide GEMV."""
     be = infr_b200.CudaBackend(device=0, mmq_kernel=2)
     yield be
     be.close()
@@ -121,8 +121,8 @@ def test_mmq_matches_the_gemv_path_row_for_row(ws_backend):
 @pytest.mark.parametrize("dt,m,in_f,out_f", [(Q4K, 32, 1024, 256), (Q4K, 19, 2048, 96), (infr_b200.Q6K, 32, 2048, 64), (infr_b200.Q6K, 27, 1024, 40),
                                              (infr_b200.Q2_0, 20, 1024, 48)])
 def test_batches_of_a_few_dozen_rows(backend, oracle, dt, m, in_f, out_f):
-    """Default context, 8 < m <= 32: small Q4_K matrices are walked 8 rows at a time through the GEMV instead of the
-    GEMM; Q6_K / Q2_0 batches are quantised once for all rows and walked 8 rows at a time."""
+    """Default context, 8 < m <= 32: Q4_K and Q6_K rows of whole 2048-element chunks take the wide GEMV, the other
+    Q6_K shapes and Q2_0 are quantised once for all rows and walked 8 rows at a time."""
     w = synth.weight(dt, out_f, in_f, seed=91)
     x = synth.normal(92, (m, in_f))
     got = backend.run_linear(dt, w, x, m, in_f, out_f)

@@ -1055,7 +1055,10 @@ def run_profile_case(args):
     be.quantize_q8(gran, xb, m, in_f, qs, d, s32, s16 if gran == 256 else None)
     be.timer_start()
     for i in range(args.steps):
-        be.gemv_q8(dtype, bufs[i % len(bufs)], qs, d, s32, s16 if dtype == infr_b200.Q6K else None, yb, m, in_f, out_f)
+        if m > 8:  # batches of a few dozen rows: the whole Linear (quantise + wide GEMV [+ sum of the K chunks])
+            be.linear(dtype, bufs[i % len(bufs)], xb, yb, m, in_f, out_f)
+        else:
+            be.gemv_q8(dtype, bufs[i % len(bufs)], qs, d, s32, s16 if dtype == infr_b200.Q6K else None, yb, m, in_f, out_f)
     ms = be.timer_stop()
     _emit({"profile_case": args.profile_case, "launches": args.steps, "copies": len(bufs),
            "alg_bytes_per_launch": w.nbytes + 4 * m * (in_f + out_f), "us_per_launch_incl_host": ms * 1e3 / args.steps})

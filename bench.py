@@ -644,7 +644,7 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
     sub = be.wrap(sub_t.data_ptr(), sub_t.numel() * 4, infr_b200.USAGE_ACTIVATIONS)
     n_red = batch * s.hidden
     comm = None
-    if N > 1 and n_red <= 65536:
+    if N > 1 and n_red <= 262144:
         comm = be.comm_create(rank, N, n_red)
         handles = [None] * N
         dist.all_gather_object(handles, comm.export())

@@ -120,7 +120,7 @@ INFR_API void infr_cuda_free(infr_cuda_ctx *ctx, infr_cuda_buf *buf);
 
 /* No counterpart in the reference (it has no multi-GPU path): the exchange a row-parallel Linear needs when a
  * model is split over the GPUs of one box, one process per GPU.  In-place sum of n f32 (a multiple of 4, at
- * most max_floats <= 65536) over `world` <= 8 ranks, as one kernel over NVLink peer memory on the context's
+ * most max_floats <= 262144) over `world` <= 8 ranks, as one kernel over NVLink peer memory on the context's
  * stream (capturable in a CUDA graph); every rank gets the same bits (slots are summed in rank order).
  * Set-up: every rank creates a comm, exports its 64-byte handle (a CUDA IPC memory handle), the host program
  * gathers the handles of all ranks in rank order by whatever channel it has, and every rank connects.

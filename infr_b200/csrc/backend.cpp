@@ -282,7 +282,7 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
     if (in_f % 16) return Status::Err(INFR_E_INVALID, fmt("linear: in_f=%u must be a multiple of 16", in_f));
     if (m == 0 || out_f == 0) return Status::Ok();
     cudaSetDevice(device_);
-    // More than 8 rows with int8 activations: a few dozen rows (a decode step over that many sequences) take the wide
+    // More than 8 rows with int8 activations: up to 32 rows (a decode step over that many sequences) take the wide
     // GEMV, which unpacks every weight byte once per 32 rows and is bound by the weight stream; beyond that Q4_K goes
     // to the tensor-memory GEMM (all rows quantised once, the weights unpacked once per 64 rows, K split across CTAs
     // when the row x token tiles alone would leave SMs idle: mmq_ws_k_splits).  mmq_kernel 2 sends every Q4_K batch
@@ -378,7 +378,7 @@ Status CudaBackend::linear(int dtype, const uint8_t *w, const float *x, float *y
 
 bool CudaBackend::wide_applies(int dtype, uint32_t m, uint32_t in_f, int act) const {
     if (act != INFR_ACT_INT8 || m <= 8 || gemv_impl_ != 0 || mmq_impl_ != 0 || in_f == 0 || in_f % 256) return false;
-    if (dtype == DT_Q4K) return m <= 64;           // above: the tensor-memory GEMM
+    if (dtype == DT_Q4K) return m <= 32;           // one pass of the weights; above, the tensor-memory GEMM is faster
     if (dtype == DT_Q6K) return in_f % 2048 == 0;  // (rows of a whole number of 16-byte units: the TMA stride rule)
     return false;
 }

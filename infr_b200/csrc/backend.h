@@ -195,7 +195,7 @@ private:
     int gemv_impl_ = 0;                // 0 = bulk-copy ring kernel, 1 = direct-load kernel
     int mmq_impl_ = 0;                 // 0 = warp-specialised MMQ (f32 within rounding of the CPU), 1 = bit-identical MMQ
     Status check_device_status();
-    // Batches of 9..64 rows (Q4_K) / any batch above 8 rows (Q6_K) through the wide GEMV, 32 rows per pass.
+    // Batches of 9..32 rows (Q4_K) / any batch above 8 rows (Q6_K) through the wide GEMV, 32 rows per pass.
     bool wide_applies(int dtype, uint32_t m, uint32_t in_f, int act) const;
     Status wide_gemm(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, float *partials);
     Status mmq_linear(const uint8_t *w, const float *x, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, bool reuse);

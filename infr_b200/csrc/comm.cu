@@ -32,7 +32,7 @@ std::string fmt(const char *f, ...) {
 
 constexpr int kMaxWorld = 8;
 constexpr int kArThreads = 1024;
-constexpr int kArMaxCtas = 16;  // 16 x 1024 float4 = 64 K floats per exchange
+constexpr int kArMaxCtas = 64;  // 64 x 1024 float4 = 256 K floats (1 MB) per exchange; one CTA per SM, all resident
 constexpr uint32_t kArSpin = 1u << 22;
 
 struct ArPeers {

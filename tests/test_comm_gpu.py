@@ -22,6 +22,20 @@ def test_single_rank_all_reduce_is_the_identity_and_repeats(backend):
     buf.close()
 
 
+def test_single_rank_largest_exchange(backend):
+    """1 MB, the most one exchange takes (64 CTAs): a batch-32 step of a 4096-wide model sums 512 KB per layer."""
+    n = 262144
+    comm = backend.comm_create(0, 1, n)
+    x = np.cos(np.arange(n, dtype=np.float32))
+    buf = backend.from_numpy(x)
+    for k in (n, 131072, n):
+        backend.all_reduce(comm, buf, k)
+    backend.sync()
+    np.testing.assert_array_equal(backend.download(buf, np.float32), x)
+    comm.close()
+    buf.close()
+
+
 def test_a_peer_that_never_answers_times_out_and_the_context_survives(backend):
     """The bounded wait of the exchange runs out (the second rank's slot is a private buffer nobody writes and the
     poll limit is short): the kernel returns by itself, sync reports E_TIMEOUT once, and the context goes on working."""
@@ -46,7 +60,7 @@ def test_a_peer_that_never_answers_times_out_and_the_context_survives(backend):
 
 
 def test_comm_argument_checks(backend):
-    for rank, world, n in ((0, 0, 64), (2, 2, 64), (0, 9, 64), (0, 1, 6), (0, 1, 0), (0, 1, 1 << 20)):
+    for rank, world, n in ((0, 0, 64), (2, 2, 64), (0, 9, 64), (0, 1, 6), (0, 1, 0), (0, 1, (1 << 18) + 4)):
         with pytest.raises(infr_b200.BackendError) as e:
             backend.comm_create(rank, world, n)
         assert e.value.code == infr_b200.E_INVALID

@@ -33,8 +33,8 @@ CASES = [
     (Q4K, 32, 4096, 4096),   # the attention projections of the 8B shape at batch 32
     (Q4K, 32, 14336, 4096),  # its FFN down: 7 K chunks
     (Q4K, 32, 4096, 14336),  # its FFN gate / up: many tiles per CTA
-    (Q4K, 33, 1024, 96),     # two passes: 32 rows + 1
-    (Q4K, 64, 2048, 520),    # two full passes
+    (Q4K, 33, 1024, 96),     # one row more than a pass holds: the tensor-memory GEMM takes over
+    (Q4K, 64, 2048, 520),
     (Q6K, 9, 2048, 8),
     (Q6K, 20, 2048, 100),
     (Q6K, 32, 4096, 1024),

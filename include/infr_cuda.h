@@ -399,6 +399,45 @@ INFR_API int32_t infr_cuda_tensor_peak_i8(infr_cuda_ctx *ctx, uint32_t n_batches
 /* Number of kernels this context has launched since creation (graph replays count their nodes). */
 INFR_API uint64_t infr_cuda_launch_count(infr_cuda_ctx *ctx);
 
+/* ---- GGUF container: the weight file on the input side of the hot path ------------------------------------------
+ * Replaces, for one file, Gguf::open / tensor_bytes / tensor_file_range and the Metadata getters of
+ * crates/infr-gguf/src/lib.rs:82-145, :476, :893-930 (a gguf-split shard set is not read).  The file is mapped
+ * read-only; tensor data is a pointer into the mapping, valid until infr_gguf_close, and goes to the device with
+ * infr_cuda_upload_at (q / k / v back to back in one buffer give the `w_off` slices of a fused-QKV Linear,
+ * crates/infr-llama/src/seam/runner.rs:3445-3461).  These entry points need no GPU.
+ * Errors as in the reference's open (lib.rs:735-870): not GGUF, version other than 2 / 3, reads past the end, nesting
+ * deeper than 64, general.alignment not a power of two or above 1 MiB, more than 8 dimensions, shape or byte-size
+ * overflow, a quantised tensor that is not a whole number of blocks, data outside the file: INFR_E_INVALID
+ * (Error::Loader) with a message in `err`; an unknown ggml type: INFR_E_UNSUPPORTED (Error::Unsupported). */
+typedef struct infr_gguf infr_gguf;
+typedef struct {
+    const char *name;   /* NUL-terminated, owned by the infr_gguf */
+    uint32_t ggml_type; /* the file's type code (12 = Q4_K, 14 = Q6_K, 42 = Q2_0, 0 = F32, 1 = F16, ...) */
+    int32_t dtype;      /* the INFR_DT_* code this library runs the type under, or -1 */
+    uint32_t n_dims;
+    uint64_t dims[8];   /* dims[0] is the fastest-varying axis (the columns of a weight); unused entries are 1 */
+    uint64_t numel, nbytes, file_offset;
+} infr_gguf_tensor;
+INFR_API int32_t infr_gguf_open(const char *path, infr_gguf **out, char *err, size_t err_len);
+INFR_API void infr_gguf_close(infr_gguf *g);
+INFR_API uint32_t infr_gguf_version(const infr_gguf *g);
+INFR_API uint64_t infr_gguf_alignment(const infr_gguf *g);
+INFR_API uint64_t infr_gguf_tensor_count(const infr_gguf *g);
+INFR_API int32_t infr_gguf_tensor_at(const infr_gguf *g, uint64_t index, infr_gguf_tensor *out);
+INFR_API int32_t infr_gguf_find(const infr_gguf *g, const char *name, infr_gguf_tensor *out);
+INFR_API const void *infr_gguf_tensor_data(const infr_gguf *g, const infr_gguf_tensor *t);
+/* Metadata.  Value type codes are the file's: 0 u8, 1 i8, 2 u16, 3 i16, 4 u32, 5 i32, 6 f32, 7 bool, 8 string,
+ * 9 array, 10 u64, 11 i64, 12 f64; infr_gguf_meta_type returns -1 for an absent key.  _u64 takes any non-negative
+ * integer or bool, _f64 any number; a string is a pointer into the mapping and a length (not NUL-terminated); an
+ * array gives its element type and count and, for fixed-size element types, its packed elements. */
+INFR_API uint64_t infr_gguf_meta_count(const infr_gguf *g);
+INFR_API const char *infr_gguf_meta_key(const infr_gguf *g, uint64_t index);
+INFR_API int32_t infr_gguf_meta_type(const infr_gguf *g, const char *key);
+INFR_API int32_t infr_gguf_meta_u64(const infr_gguf *g, const char *key, uint64_t *out);
+INFR_API int32_t infr_gguf_meta_f64(const infr_gguf *g, const char *key, double *out);
+INFR_API int32_t infr_gguf_meta_str(const infr_gguf *g, const char *key, const char **s, uint64_t *len);
+INFR_API int32_t infr_gguf_meta_array(const infr_gguf *g, const char *key, uint32_t *elem_type, uint64_t *count, const void **data);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,6 +42,9 @@ EXPORTED_SYMBOLS = [
     "infr_cuda_launch_count", "infr_cuda_tensor_peak_i8",
     "infr_cuda_rms_norm", "infr_cuda_add_rms_norm", "infr_cuda_rope", "infr_cuda_write_kv", "infr_cuda_attention", "infr_cuda_rope_write_kv",
     "infr_cuda_gated_act", "infr_cuda_add", "infr_cuda_argmax", "infr_cuda_add_rms_norm_q8", "infr_cuda_gated_act_q8", "infr_cuda_attention_q8",
+    "infr_gguf_open", "infr_gguf_close", "infr_gguf_version", "infr_gguf_alignment", "infr_gguf_tensor_count", "infr_gguf_tensor_at", "infr_gguf_find",
+    "infr_gguf_tensor_data", "infr_gguf_meta_count", "infr_gguf_meta_key", "infr_gguf_meta_type", "infr_gguf_meta_u64", "infr_gguf_meta_f64",
+    "infr_gguf_meta_str", "infr_gguf_meta_array",
 ]
 
 
@@ -51,6 +54,11 @@ class BackendError(RuntimeError):
     def __init__(self, code: int, msg: str):
         super().__init__(f"[{code}] {msg}")
         self.code = code
+
+
+class _GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("ggml_type", C.c_uint32), ("dtype", C.c_int32), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 8),
+                ("numel", C.c_uint64), ("nbytes", C.c_uint64), ("file_offset", C.c_uint64)]
 
 
 class _Opts(C.Structure):
@@ -166,6 +174,21 @@ def load_library() -> C.CDLL:
         "infr_cuda_add_rms_norm_q8": (i32, [vp, vp, vp, vp, vp, u32, u32, C.c_float, C.POINTER(_Q8Out)]),
         "infr_cuda_gated_act_q8": (i32, [vp, vp, vp, u32, u32, C.POINTER(_Q8Out)]),
         "infr_cuda_attention_q8": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, C.POINTER(_Q8Out)]),
+        "infr_gguf_open": (i32, [C.c_char_p, C.POINTER(vp), C.c_char_p, sz]),
+        "infr_gguf_close": (None, [vp]),
+        "infr_gguf_version": (u32, [vp]),
+        "infr_gguf_alignment": (u64, [vp]),
+        "infr_gguf_tensor_count": (u64, [vp]),
+        "infr_gguf_tensor_at": (i32, [vp, u64, C.POINTER(_GgufTensor)]),
+        "infr_gguf_find": (i32, [vp, C.c_char_p, C.POINTER(_GgufTensor)]),
+        "infr_gguf_tensor_data": (vp, [vp, C.POINTER(_GgufTensor)]),
+        "infr_gguf_meta_count": (u64, [vp]),
+        "infr_gguf_meta_key": (C.c_char_p, [vp, u64]),
+        "infr_gguf_meta_type": (i32, [vp, C.c_char_p]),
+        "infr_gguf_meta_u64": (i32, [vp, C.c_char_p, C.POINTER(u64)]),
+        "infr_gguf_meta_f64": (i32, [vp, C.c_char_p, C.POINTER(C.c_double)]),
+        "infr_gguf_meta_str": (i32, [vp, C.c_char_p, C.POINTER(vp), C.POINTER(u64)]),
+        "infr_gguf_meta_array": (i32, [vp, C.c_char_p, C.POINTER(u32), C.POINTER(u64), C.POINTER(vp)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

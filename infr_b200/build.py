@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libinfr_cuda.so")
-SOURCES = ["quantize.cu", "gemv.cu", "gemv_stream.cu", "gemv_mma.cu", "gemv_mma_q2.cu", "gemv_mma_q6.cu", "gemv_wide.cu", "noalloc.cu", "moe.cu", "mmq.cu", "mmq_ws.cu", "comm.cu", "tensor_peak.cu", "decode_ops.cu", "backend.cpp", "plan.cpp", "c_api.cpp"]
+SOURCES = ["quantize.cu", "gemv.cu", "gemv_stream.cu", "gemv_mma.cu", "gemv_mma_q2.cu", "gemv_mma_q6.cu", "gemv_wide.cu", "noalloc.cu", "moe.cu", "mmq.cu", "mmq_ws.cu", "comm.cu", "tensor_peak.cu", "decode_ops.cu", "backend.cpp", "plan.cpp", "c_api.cpp", "gguf.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "--expt-relaxed-constexpr",

@@ -45,8 +45,9 @@ class DecodeStep:
     """Holds the device buffers of one model replica and issues one decode step.
 
     `layers` is a list of dicts name -> weight Buffer (the names of LlamaShape.linears plus "attn_norm" and
-    "ffn_norm", f32), `head` the lm_head weight (`head_dtype`), `out_norm` the output norm.  `k_cache` / `v_cache`
-    are per-layer Buffers holding `n_seq` caches of `max_ctx` rows each."""
+    "ffn_norm", f32; an optional entry "dtypes": name -> weight format overrides the Q4_K_M mix of LlamaShape.linears
+    for that layer, as a model file's per-layer mix does), `head` the lm_head weight (`head_dtype`), `out_norm` the
+    output norm.  `k_cache` / `v_cache` are per-layer Buffers holding `n_seq` caches of `max_ctx` rows each."""
 
     def __init__(self, be, shape: LlamaShape, n_seq: int, max_ctx: int, layers, out_norm, head, head_dtype, k_cache, v_cache,
                  sub=None, reduce=None, argmax: bool = True):
@@ -75,6 +76,11 @@ class DecodeStep:
         self.a_sums = be.alloc(b * (kmax // 32) * 4, USAGE_ACTIVATIONS)
         self.a_sums16 = be.alloc(b * (kmax // 16) * 4, USAGE_ACTIVATIONS)
 
+    _MIX = {"wq": Q4K, "wk": Q4K, "wv": Q6K, "wo": Q4K, "gate": Q4K, "up": Q4K, "down": Q6K}
+
+    def _dt(self, layer: dict, name: str) -> int:
+        return layer.get("dtypes", self._MIX).get(name, self._MIX[name])
+
     def set_inputs(self, hidden: np.ndarray, pos: int):
         self.be.upload(self.hidden, np.ascontiguousarray(hidden, np.float32))
         self.be.upload(self.positions, np.full(self.n_seq, pos, np.int32))
@@ -94,22 +100,30 @@ class DecodeStep:
         scale = 1.0 / float(np.sqrt(s.head_dim))
         a8 = (self.a_qs, self.a_d, self.a_sums, self.a_sums16)
         gemv = lambda dt, w, y, k, o: be.gemv_q8(dt, w, self.a_qs, self.a_d, self.a_sums, self.a_sums16, y, b, k, o)
+
+        def pair(d1, w1, y1, o1, d2, w2, y2, o2, k):  # two Linears on the same codes: one launch where the formats agree
+            if d1 == d2:
+                be.gemv_q8_pair(d1, w1, y1, o1, w2, y2, o2, *a8, b, k)
+            else:
+                gemv(d1, w1, y1, k, o1)
+                gemv(d2, w2, y2, k, o2)
+        dt = self._dt
         be.add_rms_norm_q8(self.hidden, None, None, self.layers[0]["attn_norm"], b, h, s.eps, *a8)
         n = 1
         for li, L in enumerate(self.layers):
-            be.gemv_q8_pair(Q4K, L["wq"], self.q, s.q_dim, L["wk"], self.k, s.kv_dim, *a8, b, h)  # q and k: one launch
-            gemv(Q6K, L["wv"], self.v, h, s.kv_dim)
+            pair(dt(L, "wq"), L["wq"], self.q, s.q_dim, dt(L, "wk"), L["wk"], self.k, s.kv_dim, h)  # q and k: one launch
+            gemv(dt(L, "wv"), L["wv"], self.v, h, s.kv_dim)
             be.rope_write_kv(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], rows=1, pos=pos,
                              n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
             be.attention_q8(self.q, self.k_cache[li], self.v_cache[li], *a8, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
                             head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride)
-            gemv(Q4K, L["wo"], self.sub, s.q_dim, h)
+            gemv(dt(L, "wo"), L["wo"], self.sub, s.q_dim, h)
             if self.reduce:
                 self.reduce(self.sub, b * h)
             be.add_rms_norm_q8(self.hidden, self.sub, self.hidden, L["ffn_norm"], b, h, s.eps, *a8)
-            be.gemv_q8_pair(Q4K, L["gate"], self.g, ff, L["up"], self.u, ff, *a8, b, h)  # gate and up: one launch
+            pair(dt(L, "gate"), L["gate"], self.g, ff, dt(L, "up"), L["up"], self.u, ff, h)  # gate and up: one launch
             be.gated_act_q8(self.g, self.u, b, ff, *a8)
-            gemv(Q6K, L["down"], self.sub, ff, h)
+            gemv(dt(L, "down"), L["down"], self.sub, ff, h)
             if self.reduce:
                 self.reduce(self.sub, b * h)
             nxt = self.layers[li + 1]["attn_norm"] if li + 1 < len(self.layers) else self.out_norm
@@ -157,7 +171,9 @@ class DecodeStep:
         be.rms_norm(self.hidden, self.layers[0]["attn_norm"], self.hn, b, h, s.eps)
         n += 1
         for li, L in enumerate(self.layers):
-            lin_many(self.hn, h, [(Q4K, L["wq"], self.q, s.q_dim), (Q4K, L["wk"], self.k, s.kv_dim), (Q6K, L["wv"], self.v, s.kv_dim)])
+            dt = self._dt
+            lin_many(self.hn, h, [(dt(L, "wq"), L["wq"], self.q, s.q_dim), (dt(L, "wk"), L["wk"], self.k, s.kv_dim),
+                                  (dt(L, "wv"), L["wv"], self.v, s.kv_dim)])
             if fused:
                 be.rope_write_kv(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], rows=1, pos=pos,
                                  n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
@@ -176,7 +192,7 @@ class DecodeStep:
                         n += 1
             be.attention(self.q, self.k_cache[li], self.v_cache[li], self.attn, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
                          head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride)
-            lin(Q4K, L["wo"], self.attn, self.sub, s.q_dim, h)
+            lin(dt(L, "wo"), L["wo"], self.attn, self.sub, s.q_dim, h)
             n += 2
             if self.reduce:
                 self.reduce(self.sub, b * h)
@@ -187,9 +203,9 @@ class DecodeStep:
                 be.add(self.hidden, self.sub, self.hidden, b * h)
                 be.rms_norm(self.hidden, L["ffn_norm"], self.hn, b, h, s.eps)
                 n += 2
-            lin_many(self.hn, h, [(Q4K, L["gate"], self.g, ff), (Q4K, L["up"], self.u, ff)])
+            lin_many(self.hn, h, [(dt(L, "gate"), L["gate"], self.g, ff), (dt(L, "up"), L["up"], self.u, ff)])
             be.gated_act(self.g, self.u, self.act, b, ff)
-            lin(Q6K, L["down"], self.act, self.sub, ff, h)
+            lin(dt(L, "down"), L["down"], self.act, self.sub, ff, h)
             n += 2
             if self.reduce:
                 self.reduce(self.sub, b * h)

@@ -12,7 +12,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _header_symbols():
     text = open(os.path.join(ROOT, "include", "infr_cuda.h")).read()
-    return sorted(set(re.findall(r"INFR_API\s+[\w\s\*]+?\b(infr_cuda_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"INFR_API\s+[\w\s\*]+?\b(infr_(?:cuda|gguf)_\w+)\s*\(", text)))
 
 
 def test_header_and_binding_agree():

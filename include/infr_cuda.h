@@ -249,7 +249,9 @@ INFR_API int32_t infr_cuda_gemv(infr_cuda_ctx *ctx, int32_t dtype, const infr_cu
 /* infr_cuda_gemv(INFR_ACT_INT8) on activations that are ALREADY quantised by infr_cuda_quantize_q8
  * (gran 256 for Q4_K / Q6_K — Q6_K also needs sums16 —, gran 32 for Q2_0): the CPU reference
  * quantises an activation row once and reuses it for every weight row and every projection that
- * reads it (crates/infr-cpu/src/lib.rs:1043-1062); this entry point is that reuse. */
+ * reads it (crates/infr-cpu/src/lib.rs:1043-1062); this entry point is that reuse.  m <= 8, and more rows where the
+ * wide GEMV applies (Q4_K: m <= 32; Q6_K with in_f a multiple of 2048: any m), so that a decode step over a few dozen
+ * sequences keeps its activations in int8 between ops like a step over one. */
 INFR_API int32_t infr_cuda_gemv_q8(infr_cuda_ctx *ctx, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off,
                                    const infr_cuda_buf *qs, const infr_cuda_buf *d, const infr_cuda_buf *sums,
                                    const infr_cuda_buf *sums16, infr_cuda_buf *y, uint32_t m, uint32_t in_f,

@@ -466,11 +466,19 @@ Status CudaBackend::linear_pair(int dtype, const uint8_t *w1, float *y1, uint32_
 Status CudaBackend::gemv_q8(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f) {
     if (dtype != DT_Q4K && dtype != DT_Q6K && dtype != DT_Q2_0)
         return Status::Err(INFR_E_UNSUPPORTED, fmt("gemv_q8: weight dtype code %d", dtype));
-    if (m == 0 || m > 8) return Status::Err(INFR_E_INVALID, fmt("gemv_q8: m=%u (1..8)", m));
+    const bool wide = m > 8 && wide_applies(dtype, m, in_f, INFR_ACT_INT8);
+    if (m == 0 || (m > 8 && !wide))
+        return Status::Err(INFR_E_INVALID, fmt("gemv_q8: m=%u (1..8; more rows where the wide GEMV applies: Q4_K up to 32, Q6_K with in_f a multiple of 2048)", m));
     if (in_f == 0 || in_f % (uint32_t)block_elems(dtype) || in_f % 16) return Status::Err(INFR_E_INVALID, fmt("gemv_q8: in_f=%u", in_f));
     if (a.gran != act_gran(dtype)) return Status::Err(INFR_E_INVALID, fmt("gemv_q8: activations have granularity %d, dtype needs %d", a.gran, act_gran(dtype)));
     if (dtype == DT_Q6K && !a.sums16) return Status::Err(INFR_E_INVALID, "gemv_q8: Q6_K needs the per-16 sums");
     cudaSetDevice(device_);
+    if (wide) {
+        // a decode batch of a few dozen rows: the context scratch holds the partial results of the K chunks
+        const size_t pb = gemv_wide_partial_bytes(m < 32 ? (int)m : 32, (int)in_f, (int)out_f);
+        Status s = ensure_scratch(pb);
+        return s.ok() ? wide_gemm(dtype, w, a, y, m, in_f, out_f, reinterpret_cast<float *>(scratch())) : s;
+    }
     Status s = cuda_status(gemv_impl_ == 1   ? launch_gemv_q8(dtype, w, a, y, (int)m, (int)in_f, (int)out_f, nullptr, dev_, stream_)
                            : (dtype == DT_Q4K && gemv_impl_ == 0)
                                ? launch_gemv_q4k_mma(w, &a, nullptr, y, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_)

@@ -302,7 +302,8 @@ int32_t infr_cuda_gemv_q8_pair(infr_cuda_ctx *ctx, int32_t dtype, const infr_cud
     if (dtype != INFR_DT_Q4K && dtype != INFR_DT_Q6K && dtype != INFR_DT_Q2_0)
         return finish(ctx, Status::Err(INFR_E_UNSUPPORTED, "gemv_q8_pair: weight dtype is not supported"));
     if (in_f == 0 || in_f % (uint32_t)be || w_off1 % in_f || w_off2 % in_f) return finish(ctx, Status::Err(INFR_E_INVALID, "gemv_q8_pair: in_f / w_off"));
-    if (m == 0 || m > 8 || out_f1 == 0 || out_f2 == 0) return finish(ctx, Status::Err(INFR_E_INVALID, "gemv_q8_pair: m in 1..8, both out_f positive"));
+    // (the row limit is infr_cuda_gemv_q8's: the backend checks it)
+    if (m == 0 || out_f1 == 0 || out_f2 == 0) return finish(ctx, Status::Err(INFR_E_INVALID, "gemv_q8_pair: m and both out_f must be positive"));
     const int gran = infr::act_gran(dtype);
     const size_t bpr = (size_t)(in_f / (uint32_t)be) * (size_t)bb, r1 = (size_t)(w_off1 / in_f), r2 = (size_t)(w_off2 / in_f), n = (size_t)m * in_f;
     Status s;

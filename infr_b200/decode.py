@@ -81,6 +81,16 @@ class DecodeStep:
     def _dt(self, layer: dict, name: str) -> int:
         return layer.get("dtypes", self._MIX).get(name, self._MIX[name])
 
+    def _wide_ok(self) -> bool:
+        """9..32 sequences: every Linear can take pre-quantised rows (the wide GEMV: Q4_K, or Q6_K rows of whole
+        2048-element chunks), so the step keeps its activations in int8 between ops as a step over one sequence does."""
+        s = self.s
+        if self.n_seq > 32:
+            return False
+        ins = {"wq": s.hidden, "wk": s.hidden, "wv": s.hidden, "wo": s.q_dim, "gate": s.hidden, "up": s.hidden, "down": s.ffn}
+        ok = lambda dt, k: dt == Q4K or (dt == Q6K and k % 2048 == 0)
+        return all(ok(self._dt(L, n), k) for L in self.layers for n, k in ins.items()) and ok(self.head_dtype, s.hidden)
+
     def set_inputs(self, hidden: np.ndarray, pos: int):
         self.be.upload(self.hidden, np.ascontiguousarray(hidden, np.float32))
         self.be.upload(self.positions, np.full(self.n_seq, pos, np.int32))
@@ -90,11 +100,12 @@ class DecodeStep:
         Returns the number of ops issued."""
         s, b = self.s, self.n_seq
         if q8_fused is None:
-            q8_fused = fused and b <= 8 and s.hidden % 256 == 0 and s.ffn % 256 == 0 and s.q_dim % 256 == 0
+            q8_fused = fused and (b <= 8 or self._wide_ok()) and s.hidden % 256 == 0 and s.ffn % 256 == 0 and s.q_dim % 256 == 0
         return self._run_q8(pos) if q8_fused else self._run_f32(pos, fused)
 
     def _run_q8(self, pos: int) -> int:
-        """At most 8 rows: activations travel between ops as int8 codes wherever the consumer is a Linear."""
+        """Activations travel between ops as int8 codes wherever the consumer is a Linear (at most 8 rows, or up to 32
+        where every Linear can run on the wide GEMV)."""
         be, s, b = self.be, self.s, self.n_seq
         h, ff = s.hidden, s.ffn
         scale = 1.0 / float(np.sqrt(s.head_dim))

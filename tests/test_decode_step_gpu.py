@@ -91,3 +91,35 @@ def test_decode_step_matches_the_cpu_op_sequence(backend, oracle, fused, q8_fuse
         keep = np.ones(g.shape[0], bool)
         keep[rows] = False
         np.testing.assert_array_equal(g[keep], vc[li][keep])
+
+
+def test_a_dozen_sequences_keep_int8_activations_between_ops(backend):
+    """9..32 sequences with every Linear on the wide GEMV: the step runs its int8-producer form (RMSNorm, attention
+    merge and SiLU gate end in the quantiser, Linears take the codes) and gives what the op-by-op form gives."""
+    s = LlamaShape(n_layer=2, hidden=2048, n_head=16, n_kv=4, head_dim=128, ffn=2048, vocab=512)
+    b, ctx, pos = 12, 24, 9
+    dev_layers = []
+    for li in range(s.n_layer):
+        d = {name: backend.from_numpy(synth.weight(dt, o, i, seed=2000 + 16 * li + t), infr_b200.USAGE_WEIGHTS)
+             for t, (name, dt, o, i) in enumerate(s.linears())}
+        d["attn_norm"] = backend.from_numpy((1.0 + 0.02 * synth.normal(2100 + li, (s.hidden,))).astype(np.float32))
+        d["ffn_norm"] = backend.from_numpy((1.0 + 0.02 * synth.normal(2200 + li, (s.hidden,))).astype(np.float32))
+        dev_layers.append(d)
+    out_norm = backend.from_numpy((1.0 + 0.02 * synth.normal(2300, (s.hidden,))).astype(np.float32))
+    head = backend.from_numpy(synth.weight(Q6K, s.vocab, s.hidden, seed=2301), infr_b200.USAGE_WEIGHTS)
+    kc = [synth.normal(50 + li, (b * ctx, s.kv_dim)).astype(np.float16).view(np.uint16) for li in range(s.n_layer)]
+    vc = [synth.normal(60 + li, (b * ctx, s.kv_dim)).astype(np.float16).view(np.uint16) for li in range(s.n_layer)]
+    hidden = synth.normal(70, (b, s.hidden))
+    outs = []
+    for fused, q8 in ((False, False), (True, None)):
+        step = DecodeStep(backend, s, b, ctx, dev_layers, out_norm, head, Q6K, [backend.from_numpy(c) for c in kc], [backend.from_numpy(c) for c in vc])
+        assert step._wide_ok()
+        step.set_inputs(hidden, pos)
+        l0 = backend.launch_count()
+        step.run(pos, fused=fused, q8_fused=q8)
+        outs.append((backend.download(step.logits, np.float32).reshape(b, s.vocab), backend.download(step.tok, np.uint32), backend.launch_count() - l0))
+    (ref_logits, ref_tok, ref_launches), (got_logits, got_tok, got_launches) = outs
+    assert np.isfinite(got_logits).all()
+    assert fx.rel_l2(got_logits, ref_logits) < 1e-5
+    np.testing.assert_array_equal(got_tok, ref_tok)
+    assert got_launches < ref_launches

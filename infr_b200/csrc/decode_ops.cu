@@ -190,21 +190,32 @@ __global__ void __launch_bounds__(256) write_kv_kernel(const float *__restrict__
 
 // ---------------------------------------------------------------------------------------------- attention
 constexpr int kAttnTile = 128;     // keys per CTA
-constexpr int kAttnThreads = 256;  // two threads per key in the score phase, eight warps over the values
+constexpr int kAttnThreads = 256;  // eight warps: 16 keys each in the score phase, 16 output dims each in the value phase
 
 // CTA = (key tile, KV head, query row).  The tile's 128 key rows and 128 value rows (head_dim halves each) are
 // copied into shared memory with 16-byte cp.async, consecutive threads taking consecutive 16-byte pieces of a row, so
 // every global request is a whole 128-byte line; all copies of the CTA are in flight together and none occupies a
-// register.  Phase 1: two threads per key, each over half of the dims, score the key against the G query heads that
-// share the KV head (q in shared memory; the key rows sit 16 bytes apart from a multiple of 128, which spreads the
-// threads' 16-byte reads over all banks).
-// Phase 2: one warp per head turns the tile's scores into exp(s - m) and their sum.  Phase 3: warp w multiplies keys
-// 16w..16w+15 into the outputs (lane = HD/32 dims), the eight warps' partial sums are added through shared memory
-// (over the key tile, which is dead by then), and the tile's (m, l, o) goes to the workspace for the merge kernel.
+// register.
+//
+// Both products run on the warp-level matrix unit in tf32 WITHOUT giving up f32 operands: an f16 cache value is exact
+// in tf32 (10 mantissa bits), and the f32 operand (q, then the softmax weights p) is split into two tf32 pieces,
+// hi = the top 11 significant bits, mid = the next 11 of the remainder, which sit in two neighbouring columns of the
+// instruction's N dimension and are added afterwards; what is dropped is below 2^-22 of the operand, the size of the
+// rounding of an f32 accumulation itself.  Products are exact, sums are f32.  This takes the instruction count of a tile
+// from ~7100 (scalar FMAs on converted halves, which cost more issue slots than the tile's bytes cost HBM time) to
+// ~2800.
+// Phase 1: warp w scores keys 16w..16w+15 against the G query heads that share the KV head: A = the keys (ldmatrix,
+// halves -> f32), B = the q pieces, K = head_dim in steps of 8.  Phase 2: one warp per head turns the tile's scores into
+// exp(s - m), their sum, and the two tf32 pieces of each weight.  Phase 3: warp w owns output dims 16 (w mod HD/16):
+// A = the values transposed (ldmatrix.trans), B = the weight pieces, K = the keys in steps of 8; with head_dim 64 the
+// two halves of the keys go to two warps and meet in shared memory (over the key tile, dead by then).  The tile's
+// (m, l, o) goes to the workspace for the merge kernel.
+// The K index of the instruction is only a summation index: slot t takes element 2t of a group of 8 and slot t + 4
+// element 2t + 1, which is how ldmatrix hands out halves in pairs.
 template <int HD>
 struct AttnSmem {
-    static constexpr int kKeyStride = HD * 2 + 16;  // bytes
-    static constexpr int kValStride = HD * 2;
+    static constexpr int kKeyStride = HD * 2 + 16;  // bytes; 16 past a multiple of 128: the 8 rows of an ldmatrix hit distinct banks
+    static constexpr int kValStride = HD * 2 + 16;
     static constexpr int kBytes = kAttnTile * (kKeyStride + kValStride);
 };
 
@@ -215,27 +226,59 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Four 8x8 matrices of halves; lane l supplies the address of row l % 8 of matrix l / 8.  Plain: thread (g, t) gets
+// elements [g][2t], [g][2t+1] of each matrix; .trans: elements [2t][g], [2t+1][g].
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const void *row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(row)));
+}
+__device__ __forceinline__ void ldsm4_trans(uint32_t (&r)[4], const void *row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(row)));
+}
+// D += A(16x8, tf32) * B(8x8, tf32), f32 accumulate
+__device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// the two halves of a word as f32 bit patterns (exact, and representable in tf32)
+__device__ __forceinline__ void half2_bits(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    lo = __float_as_uint(f.x);
+    hi = __float_as_uint(f.y);
+}
+// tf32 pieces of an f32 value: piece 0 = its top 11 significant bits, piece 1 = the top 11 of what is left
+__device__ __forceinline__ uint32_t tf32_piece(float v, int piece) {
+    const uint32_t hi = __float_as_uint(v) & 0xFFFFE000u;
+    return piece == 0 ? hi : (__float_as_uint(v - __uint_as_float(hi)) & 0xFFFFE000u);
+}
+
 template <int HD, int G>
 __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *__restrict__ q, const __half *__restrict__ k_cache,
                                                                const __half *__restrict__ v_cache, float *__restrict__ part_o,
                                                                float *__restrict__ part_ml, int rows, int n_head, int n_kv, int pos,
                                                                float scale, int n_splits, size_t seq_stride) {
-    constexpr int DPL = HD / 32;       // dims per lane in phase 3
-    constexpr int CPR = HD * 2 / 16;   // 16-byte pieces per row
+    constexpr int CPR = HD * 2 / 16;           // 16-byte pieces per row
+    constexpr int NT = (2 * G + 7) / 8;        // 8-column groups of the instruction: column c = head c / 2, piece c % 2
+    constexpr int DG = HD / 16;                // 16-dim output groups
+    constexpr int KP = (kAttnThreads / 32) / DG;  // warps per output group: they split the keys (1 for head_dim 128, 2 for 64)
     using L = AttnSmem<HD>;
     extern __shared__ __align__(16) uint8_t dyn_smem[];
     uint8_t *s_k = dyn_smem, *s_v = dyn_smem + kAttnTile * L::kKeyStride;
-    float(*s_o)[G][HD] = reinterpret_cast<float(*)[G][HD]>(dyn_smem);  // 8 x G x HD floats <= the key tile (G <= 8)
+    float(*s_o)[G][HD] = reinterpret_cast<float(*)[G][HD]>(dyn_smem);  // KP x G x HD floats over the key tile (KP > 1 only)
     __shared__ __align__(16) float s_q[G * HD];
-    __shared__ float s_p[G][kAttnTile];
-    __shared__ float s_p2[G][kAttnTile];  // the second half of the dims of each dot product
+    __shared__ __align__(16) float s_pp[2][G][kAttnTile];  // [0]: scores, then the hi pieces of exp(s - m); [1]: the mid pieces
     __shared__ float s_ml[G][2];
-    static_assert(8 * G * HD * 4 <= kAttnTile * L::kKeyStride, "the partial outputs reuse the key tile");
+    static_assert(KP * G * HD * 4 <= kAttnTile * L::kKeyStride, "the partial outputs reuse the key tile");
+    static_assert(KP >= 1 && KP * DG == kAttnThreads / 32, "head_dim 64 or 128");
     const int split = blockIdx.x, kvh = blockIdx.y, qr = blockIdx.z;
     const int seq = qr / rows, ti = qr % rows;
     const int n_keys = pos + ti + 1;
     const int key0 = split * kAttnTile;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
     pdl_go();
     pdl_wait();
     const size_t out_idx = ((size_t)qr * n_head + (size_t)kvh * G) * n_splits + split;  // + g * n_splits
@@ -260,46 +303,53 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *_
         cp_async16(s_v + key * L::kValStride + c * 16, vbase + (size_t)key * kv_row + c * 8);
     }
     cp_async_commit();
+    // rows past the end of a partial tile: zero, so that the matrix unit multiplies 0 (not stale bits) by the weight 0
+    for (int i = tid; i < (kAttnTile - tile_keys) * CPR; i += kAttnThreads) {
+        const int key = tile_keys + i / CPR, c = i % CPR;
+        *reinterpret_cast<uint4 *>(s_k + key * L::kKeyStride + c * 16) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4 *>(s_v + key * L::kValStride + c * 16) = make_uint4(0, 0, 0, 0);
+    }
     const float *qrow = q + ((size_t)qr * n_head + (size_t)kvh * G) * HD;
     for (int i = tid; i < G * HD; i += kAttnThreads) s_q[i] = qrow[i];
     cp_async_wait<1>();  // this thread's key pieces have landed
     __syncthreads();     // everybody's have, and q is staged
-    // ---- phase 1: two threads per key, each over half of the dims, two accumulators per head
+    // ---- phase 1: scores of keys 16 warp .. 16 warp + 15
     {
-        const int key = tid & (kAttnTile - 1), half = tid >> 7;
-        float acc[G][2];
+        float acc[NT][4];
 #pragma unroll
-        for (int g = 0; g < G; g++) acc[g][0] = acc[g][1] = 0.f;
-        if (key < tile_keys) {
-            const uint4 *kr = reinterpret_cast<const uint4 *>(s_k + key * L::kKeyStride) + half * (CPR / 2);
-            const float *qh = s_q + half * (HD / 2);
+        for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        // ldmatrix rows: matrices 0 / 1 = keys 0..7 / 8..15 at dims d0.., matrices 2 / 3 = the same keys at dims d0 + 8..
+        const uint8_t *arow = s_k + (size_t)(16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8) * L::kKeyStride + (lane >> 4) * 16;
 #pragma unroll 4
-            for (int c = 0; c < CPR / 2; c++) {
-                const uint4 raw = kr[c];
-                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
-                float kf[8];
+        for (int j = 0; j < HD / 16; j++) {
+            uint32_t r[4];
+            ldsm4(r, arow + j * 32);
+            uint32_t a[2][4];  // [dim group of 8][a0..a3]
+            half2_bits(r[0], a[0][0], a[0][2]);  // keys g8:     (slot t4, slot t4 + 4) = dims 2 t4, 2 t4 + 1
+            half2_bits(r[1], a[0][1], a[0][3]);  // keys g8 + 8
+            half2_bits(r[2], a[1][0], a[1][2]);
+            half2_bits(r[3], a[1][1], a[1][3]);
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float2 f = __half22float2(h2[e]);
-                    kf[2 * e] = f.x, kf[2 * e + 1] = f.y;
+            for (int nt = 0; nt < NT; nt++) {
+                const int c = nt * 8 + g8, head = c >> 1, piece = c & 1;  // this lane's B column
+                float2 q0 = make_float2(0.f, 0.f), q1 = q0;
+                if (head < G) {
+                    q0 = *reinterpret_cast<const float2 *>(s_q + head * HD + j * 16 + 2 * t4);
+                    q1 = *reinterpret_cast<const float2 *>(s_q + head * HD + j * 16 + 8 + 2 * t4);
                 }
-#pragma unroll
-                for (int g = 0; g < G; g++) {
-                    const float4 q0 = *reinterpret_cast<const float4 *>(qh + g * HD + c * 8);
-                    const float4 q1 = *reinterpret_cast<const float4 *>(qh + g * HD + c * 8 + 4);
-                    acc[g][0] = fmaf(q0.x, kf[0], acc[g][0]);
-                    acc[g][0] = fmaf(q0.y, kf[1], acc[g][0]);
-                    acc[g][0] = fmaf(q0.z, kf[2], acc[g][0]);
-                    acc[g][0] = fmaf(q0.w, kf[3], acc[g][0]);
-                    acc[g][1] = fmaf(q1.x, kf[4], acc[g][1]);
-                    acc[g][1] = fmaf(q1.y, kf[5], acc[g][1]);
-                    acc[g][1] = fmaf(q1.z, kf[6], acc[g][1]);
-                    acc[g][1] = fmaf(q1.w, kf[7], acc[g][1]);
-                }
+                mma_tf32(acc[nt], a[0][0], a[0][1], a[0][2], a[0][3], tf32_piece(q0.x, piece), tf32_piece(q0.y, piece));
+                mma_tf32(acc[nt], a[1][0], a[1][1], a[1][2], a[1][3], tf32_piece(q1.x, piece), tf32_piece(q1.y, piece));
             }
         }
+        // columns 2 t4, 2 t4 + 1 of group nt = the two pieces of head 4 nt + t4; rows g8 and g8 + 8 of the warp's keys
 #pragma unroll
-        for (int g = 0; g < G; g++) (half ? s_p2 : s_p)[g][key] = acc[g][0] + acc[g][1];
+        for (int nt = 0; nt < NT; nt++) {
+            const int head = nt * 4 + t4;
+            if (head < G) {
+                s_pp[0][head][16 * warp + g8] = acc[nt][0] + acc[nt][1];
+                s_pp[0][head][16 * warp + g8 + 8] = acc[nt][2] + acc[nt][3];
+            }
+        }
     }
     cp_async_wait<0>();  // this thread's value pieces
     __syncthreads();     // scores complete, value tile complete, key tile no longer read
@@ -309,7 +359,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *_
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int key = lane + 32 * e;
-            v[e] = key < tile_keys ? (s_p[g][key] + s_p2[g][key]) * scale : -INFINITY;
+            v[e] = key < tile_keys ? s_pp[0][g][key] * scale : -INFINITY;
             m = fmaxf(m, v[e]);
         }
         m = warp_max(m);  // finite: the tile holds at least one valid key
@@ -317,55 +367,70 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *_
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const float p = expf(v[e] - m);
-            s_p[g][lane + 32 * e] = p;
+            s_pp[0][g][lane + 32 * e] = __uint_as_float(tf32_piece(p, 0));
+            s_pp[1][g][lane + 32 * e] = __uint_as_float(tf32_piece(p, 1));
             l += p;
         }
         l = warp_sum(l);
         if (lane == 0) s_ml[g][0] = m, s_ml[g][1] = l;
     }
     __syncthreads();
-    // ---- phase 3
+    // ---- phase 3: output dims 16 dg .. + 15 over this warp's share of the keys
     {
-        float o[G][DPL];
+        const int dg = warp % DG, kp = warp / DG;
+        constexpr int KEYS = kAttnTile / KP;
+        float acc[NT][4];
 #pragma unroll
-        for (int g = 0; g < G; g++)
-#pragma unroll
-            for (int e = 0; e < DPL; e++) o[g][e] = 0.f;
-        constexpr int KPW = kAttnTile / (kAttnThreads / 32);  // keys per warp
-        const int cnt = min(KPW, tile_keys - warp * KPW);  // may be <= 0
-        const uint8_t *vr = s_v + (size_t)(warp * KPW) * L::kValStride + lane * DPL * 2;
+        for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        // ldmatrix.trans rows: matrices 0 / 1 = keys 0..7 at dims 0..7 / 8..15 of the group, matrices 2 / 3 = keys 8..15
+        const uint8_t *vrow = s_v + (size_t)(kp * KEYS + (lane & 7) + (lane >> 4) * 8) * L::kValStride + (size_t)(16 * dg + ((lane >> 3) & 1) * 8) * 2;
 #pragma unroll 4
-        for (int jj = 0; jj < cnt; jj++) {
-            float vf[DPL];
-            if (DPL == 4) {
-                const uint2 raw = *reinterpret_cast<const uint2 *>(vr + jj * L::kValStride);
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-                const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-                vf[0] = f0.x, vf[1] = f0.y, vf[DPL - 2] = f1.x, vf[DPL - 1] = f1.y;
-            } else {
-                const uint32_t raw = *reinterpret_cast<const uint32_t *>(vr + jj * L::kValStride);
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&raw));
-                vf[0] = f0.x, vf[1] = f0.y;
-            }
+        for (int s16 = 0; s16 < KEYS / 16; s16++) {
+            uint32_t r[4];
+            ldsm4_trans(r, vrow + (size_t)s16 * 16 * L::kValStride);
+            uint32_t a[2][4];  // [key group of 8][a0..a3]
+            half2_bits(r[0], a[0][0], a[0][2]);  // dims g8:     (slot t4, slot t4 + 4) = keys 2 t4, 2 t4 + 1
+            half2_bits(r[1], a[0][1], a[0][3]);  // dims g8 + 8
+            half2_bits(r[2], a[1][0], a[1][2]);
+            half2_bits(r[3], a[1][1], a[1][3]);
+            const int k0 = kp * KEYS + s16 * 16 + 2 * t4;
 #pragma unroll
-            for (int g = 0; g < G; g++) {
-                const float p = s_p[g][warp * KPW + jj];
-#pragma unroll
-                for (int e = 0; e < DPL; e++) o[g][e] = fmaf(vf[e], p, o[g][e]);
+            for (int nt = 0; nt < NT; nt++) {
+                const int c = nt * 8 + g8, head = c >> 1, piece = c & 1;
+                float2 p0 = make_float2(0.f, 0.f), p1 = p0;
+                if (head < G) {
+                    p0 = *reinterpret_cast<const float2 *>(&s_pp[piece][head][k0]);
+                    p1 = *reinterpret_cast<const float2 *>(&s_pp[piece][head][k0 + 8]);
+                }
+                mma_tf32(acc[nt], a[0][0], a[0][1], a[0][2], a[0][3], __float_as_uint(p0.x), __float_as_uint(p0.y));
+                mma_tf32(acc[nt], a[1][0], a[1][1], a[1][2], a[1][3], __float_as_uint(p1.x), __float_as_uint(p1.y));
             }
         }
 #pragma unroll
-        for (int g = 0; g < G; g++)
-#pragma unroll
-            for (int e = 0; e < DPL; e++) s_o[warp][g][lane * DPL + e] = o[g][e];
+        for (int nt = 0; nt < NT; nt++) {
+            const int head = nt * 4 + t4;
+            if (head < G) {
+                const float o0 = acc[nt][0] + acc[nt][1], o1 = acc[nt][2] + acc[nt][3];  // dims 16 dg + g8, + 8
+                if (KP == 1) {
+                    float *po = part_o + (out_idx + (size_t)head * n_splits) * HD + 16 * dg + g8;
+                    po[0] = o0;
+                    po[8] = o1;
+                } else {
+                    s_o[kp][head][16 * dg + g8] = o0;
+                    s_o[kp][head][16 * dg + g8 + 8] = o1;
+                }
+            }
+        }
     }
-    __syncthreads();
-    for (int i = tid; i < G * HD; i += kAttnThreads) {
-        const int g = i / HD, d = i % HD;
-        float t = s_o[0][g][d];
+    if (KP > 1) {
+        __syncthreads();
+        for (int i = tid; i < G * HD; i += kAttnThreads) {
+            const int g = i / HD, d = i % HD;
+            float t = s_o[0][g][d];
 #pragma unroll
-        for (int w = 1; w < kAttnThreads / 32; w++) t += s_o[w][g][d];
-        part_o[(out_idx + (size_t)g * n_splits) * HD + d] = t;
+            for (int w = 1; w < KP; w++) t += s_o[w][g][d];
+            part_o[(out_idx + (size_t)g * n_splits) * HD + d] = t;
+        }
     }
     if (tid < G) {
         part_ml[(out_idx + (size_t)tid * n_splits) * 2] = s_ml[tid][0];

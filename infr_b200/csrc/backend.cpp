@@ -560,7 +560,7 @@ Status CudaBackend::attention(const infr_attn_desc &d, const float *q, const voi
     Status s = ensure_scratch(ws);
     if (!s.ok()) return s;
     s = cuda_status(launch_attention(q, k_cache, v_cache, dst, scratch_, (int)n_seq, (int)d.rows, (int)d.n_head, (int)d.n_kv, (int)d.head_dim,
-                                     d.scale, (int)d.pos, (size_t)d.seq_stride, dev_.sm_count, stream_, q8 ? const_cast<int8_t *>(q8->qs) : nullptr,
+                                     d.scale, (int)d.pos, (size_t)d.seq_stride, dev_.sm_count, stream_, status_dev_, q8 ? const_cast<int8_t *>(q8->qs) : nullptr,
                                      q8 ? const_cast<float *>(q8->d) : nullptr, q8 ? const_cast<int32_t *>(q8->sums) : nullptr,
                                      q8 ? const_cast<int32_t *>(q8->sums16) : nullptr),
                     "attention");

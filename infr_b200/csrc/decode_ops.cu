@@ -226,6 +226,20 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Bounded wait for phase 0 of a copy barrier.
+__device__ __forceinline__ bool attn_wait(uint64_t *bar) {
+    const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
+    for (uint32_t i = 0; i < (1u << 22); i++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok)
+                     : "r"(b), "r"(0u)
+                     : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 // Four 8x8 matrices of halves; lane l supplies the address of row l % 8 of matrix l / 8.  Plain: thread (g, t) gets
 // elements [g][2t], [g][2t+1] of each matrix; .trans: elements [2t][g], [2t+1][g].
 __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const void *row) {
@@ -256,11 +270,11 @@ __device__ __forceinline__ uint32_t tf32_piece(float v, int piece) {
     return piece == 0 ? hi : (__float_as_uint(v - __uint_as_float(hi)) & 0xFFFFE000u);
 }
 
-template <int HD, int G>
+template <int HD, int G, bool BULK>
 __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *__restrict__ q, const __half *__restrict__ k_cache,
                                                                const __half *__restrict__ v_cache, float *__restrict__ part_o,
                                                                float *__restrict__ part_ml, int rows, int n_head, int n_kv, int pos,
-                                                               float scale, int n_splits, size_t seq_stride) {
+                                                               float scale, int n_splits, size_t seq_stride, uint32_t *__restrict__ status) {
     constexpr int CPR = HD * 2 / 16;           // 16-byte pieces per row
     constexpr int NT = (2 * G + 7) / 8;        // 8-column groups of the instruction: column c = head c / 2, piece c % 2
     constexpr int DG = HD / 16;                // 16-dim output groups
@@ -272,6 +286,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *_
     __shared__ __align__(16) float s_q[G * HD];
     __shared__ __align__(16) float s_pp[2][G][kAttnTile];  // [0]: scores, then the hi pieces of exp(s - m); [1]: the mid pieces
     __shared__ float s_ml[G][2];
+    __shared__ __align__(8) uint64_t s_bar[2];
     static_assert(KP * G * HD * 4 <= kAttnTile * L::kKeyStride, "the partial outputs reuse the key tile");
     static_assert(KP >= 1 && KP * DG == kAttnThreads / 32, "head_dim 64 or 128");
     const int split = blockIdx.x, kvh = blockIdx.y, qr = blockIdx.z;
@@ -293,26 +308,69 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *_
     const __half *kbase = k_cache + (size_t)seq * seq_stride + (size_t)kvh * HD + (size_t)key0 * kv_row;
     const __half *vbase = v_cache + (size_t)seq * seq_stride + (size_t)kvh * HD + (size_t)key0 * kv_row;
     const int tile_keys = min(kAttnTile, n_keys - key0);
-    for (int i = tid; i < tile_keys * CPR; i += kAttnThreads) {
-        const int key = i / CPR, c = i % CPR;
-        cp_async16(s_k + key * L::kKeyStride + c * 16, kbase + (size_t)key * kv_row + c * 8);
-    }
-    cp_async_commit();
-    for (int i = tid; i < tile_keys * CPR; i += kAttnThreads) {
-        const int key = i / CPR, c = i % CPR;
-        cp_async16(s_v + key * L::kValStride + c * 16, vbase + (size_t)key * kv_row + c * 8);
-    }
-    cp_async_commit();
-    // rows past the end of a partial tile: zero, so that the matrix unit multiplies 0 (not stale bits) by the weight 0
-    for (int i = tid; i < (kAttnTile - tile_keys) * CPR; i += kAttnThreads) {
-        const int key = tile_keys + i / CPR, c = i % CPR;
-        *reinterpret_cast<uint4 *>(s_k + key * L::kKeyStride + c * 16) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4 *>(s_v + key * L::kValStride + c * 16) = make_uint4(0, 0, 0, 0);
+    // Two ways to fetch the tile.  BULK (many CTAs per SM over the launch: a batch of sequences): one bulk copy per row
+    // (head_dim halves, contiguous in the cache) into the padded tile, thread r < 128 the key row r, thread 128 + r the
+    // value row r, so a tile costs each warp two instructions instead of 32 cp.async with their address arithmetic (a
+    // third of the kernel's instructions); keys and values complete on separate barriers.  Otherwise (a single wave of
+    // CTAs, where the latency of the first byte is what counts): 16-byte cp.async, consecutive threads taking consecutive
+    // pieces of a row.  Rows past the end of a partial tile are zeroed, so that the matrix unit multiplies 0 (not stale
+    // bits) by the weight 0.
+    if (BULK) {
+        if (tid == 0) {
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const uint32_t b = (uint32_t)__cvta_generic_to_shared(&s_bar[i]);
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b) : "memory");
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"((uint32_t)(tile_keys * HD * 2)) : "memory");
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();  // the barriers are armed before any copy can complete
+        const int which = tid >> 7, r = tid & (kAttnTile - 1);  // 0: key row r, 1: value row r
+        uint8_t *dst = (which ? s_v + r * L::kValStride : s_k + r * L::kKeyStride);
+        if (r < tile_keys) {
+            const __half *src = (which ? vbase : kbase) + (size_t)r * kv_row;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(dst)),
+                         "l"(src), "r"((uint32_t)(HD * 2)), "r"((uint32_t)__cvta_generic_to_shared(&s_bar[which]))
+                         : "memory");
+        } else {
+#pragma unroll
+            for (int c = 0; c < CPR; c++) *reinterpret_cast<uint4 *>(dst + c * 16) = make_uint4(0, 0, 0, 0);
+        }
+    } else {
+        for (int i = tid; i < tile_keys * CPR; i += kAttnThreads) {
+            const int key = i / CPR, c = i % CPR;
+            cp_async16(s_k + key * L::kKeyStride + c * 16, kbase + (size_t)key * kv_row + c * 8);
+        }
+        cp_async_commit();
+        for (int i = tid; i < tile_keys * CPR; i += kAttnThreads) {
+            const int key = i / CPR, c = i % CPR;
+            cp_async16(s_v + key * L::kValStride + c * 16, vbase + (size_t)key * kv_row + c * 8);
+        }
+        cp_async_commit();
+        for (int i = tid; i < (kAttnTile - tile_keys) * CPR; i += kAttnThreads) {
+            const int key = tile_keys + i / CPR, c = i % CPR;
+            *reinterpret_cast<uint4 *>(s_k + key * L::kKeyStride + c * 16) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4 *>(s_v + key * L::kValStride + c * 16) = make_uint4(0, 0, 0, 0);
+        }
     }
     const float *qrow = q + ((size_t)qr * n_head + (size_t)kvh * G) * HD;
     for (int i = tid; i < G * HD; i += kAttnThreads) s_q[i] = qrow[i];
-    cp_async_wait<1>();  // this thread's key pieces have landed
-    __syncthreads();     // everybody's have, and q is staged
+    // the keys have landed; q is staged, the zeroed rows are in place.  (BULK: a bounded wait; if it runs out, the CTA
+    // records it and leaves after the wait for the values has had its own limit, so that no copy can land in shared
+    // memory that is no longer this CTA's.)
+    if (BULK) {
+        const bool k_ok = attn_wait(&s_bar[0]);
+        if (!__syncthreads_and(k_ok)) {
+            attn_wait(&s_bar[1]);
+            if (tid == 0) atomicExch(status, 12u);
+            return;
+        }
+    } else {
+        cp_async_wait<1>();
+        __syncthreads();
+    }
     // ---- phase 1: scores of keys 16 warp .. 16 warp + 15
     {
         float acc[NT][4];
@@ -351,8 +409,17 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *_
             }
         }
     }
-    cp_async_wait<0>();  // this thread's value pieces
-    __syncthreads();     // scores complete, value tile complete, key tile no longer read
+    // the values have landed; scores complete, key tile no longer read
+    if (BULK) {
+        const bool v_ok = attn_wait(&s_bar[1]);
+        if (!__syncthreads_and(v_ok)) {
+            if (tid == 0) atomicExch(status, 12u);
+            return;
+        }
+    } else {
+        cp_async_wait<0>();
+        __syncthreads();
+    }
     // ---- phase 2
     for (int g = warp; g < G; g += kAttnThreads / 32) {
         float v[4], m = -INFINITY;
@@ -785,44 +852,48 @@ size_t attention_workspace_bytes(int q_rows, int n_head, int head_dim, int max_k
 
 template <int HD, int G>
 static cudaError_t launch_attn_one(dim3 grid, cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *po, float *pml, int rows,
-                                   int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride) {
+                                   int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride, uint32_t *status, bool bulk) {
     // the tile needs more than the default 48 KB of dynamic shared memory; the attribute is per device, so it is set
     // on every launch (cheap, allocates nothing) rather than remembered per process
-    cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<HD>::kBytes);
+    auto kernel = bulk ? attn_split_kernel<HD, G, true> : attn_split_kernel<HD, G, false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<HD>::kBytes);
     if (e != cudaSuccess) return e;
-    return launch_pdl(attn_split_kernel<HD, G>, grid, dim3(kAttnThreads), (size_t)AttnSmem<HD>::kBytes, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos,
-                      scale, n_splits, seq_stride);
+    return launch_pdl(kernel, grid, dim3(kAttnThreads), (size_t)AttnSmem<HD>::kBytes, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits,
+                      seq_stride, status);
 }
 
 template <int HD>
 static cudaError_t launch_attn_hd(int group, dim3 grid, cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *po, float *pml,
-                                  int rows, int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride) {
+                                  int rows, int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride, uint32_t *status, bool bulk) {
     switch (group) {
-        case 1: return launch_attn_one<HD, 1>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
-        case 2: return launch_attn_one<HD, 2>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
-        case 4: return launch_attn_one<HD, 4>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
-        case 8: return launch_attn_one<HD, 8>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        case 1: return launch_attn_one<HD, 1>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
+        case 2: return launch_attn_one<HD, 2>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
+        case 4: return launch_attn_one<HD, 4>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
+        case 8: return launch_attn_one<HD, 8>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
         default: return cudaErrorInvalidValue;
     }
 }
 
 cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_cache, float *dst, void *workspace, int n_seq, int rows, int n_head,
-                             int n_kv, int head_dim, float scale, int pos, size_t seq_stride, int sm_count, cudaStream_t st, int8_t *qs, float *d,
+                             int n_kv, int head_dim, float scale, int pos, size_t seq_stride, int sm_count, cudaStream_t st, uint32_t *status, int8_t *qs, float *d,
                              int32_t *sums, int32_t *sums16) {
     if (n_seq <= 0 || rows <= 0 || n_head <= 0 || n_kv <= 0 || n_head % n_kv || pos < 0) return cudaErrorInvalidValue;
     const int max_keys = pos + rows, n_splits = (max_keys + kAttnTile - 1) / kAttnTile, q_rows = n_seq * rows;
     if (n_kv > 65535 || q_rows > 65535) return cudaErrorInvalidValue;
+    // the tiles are fetched with 16-byte-granular bulk copies of whole rows
+    if (((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 || seq_stride % 8 || ((size_t)n_kv * head_dim) % 8) return cudaErrorInvalidValue;
     float *po = static_cast<float *>(workspace);
     float *pml = po + (size_t)q_rows * n_head * n_splits * head_dim;
     const dim3 grid(n_splits, n_kv, q_rows);
     const __half *kc = static_cast<const __half *>(k_cache), *vc = static_cast<const __half *>(v_cache);
     cudaError_t e;
-    (void)sm_count;
+    // more than two waves of CTAs (three fit an SM): the per-tile instruction count decides, else the first byte's latency
+    const bool bulk = (size_t)n_splits * n_kv * q_rows > (size_t)6 * (sm_count > 0 ? sm_count : 148);
     const int g = n_head / n_kv;
     if (head_dim == 128)
-        e = launch_attn_hd<128>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        e = launch_attn_hd<128>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
     else if (head_dim == 64)
-        e = launch_attn_hd<64>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride);
+        e = launch_attn_hd<64>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
     else
         return cudaErrorInvalidValue;
     if (e != cudaSuccess) return e;

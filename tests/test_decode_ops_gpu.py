@@ -87,8 +87,10 @@ def test_attention(backend, oracle, n_head, n_kv, hd, pos, rows):
     assert fx.rel_l2(got, want) < TIGHT < TOL
 
 
-def test_attention_independent_sequences(backend, oracle):
-    n_seq, n_head, n_kv, hd, pos = 3, 8, 2, 128, 200
+@pytest.mark.parametrize("n_seq,n_head,n_kv,hd,pos", [(3, 8, 2, 128, 200),      # a single wave of CTAs: tiles fetched with cp.async
+                                                      (16, 32, 8, 128, 1000),   # several waves: one bulk copy per row, partial last tile
+                                                      (20, 8, 8, 64, 700)])     # the same with head_dim 64 (two warps per output group)
+def test_attention_independent_sequences(backend, oracle, n_seq, n_head, n_kv, hd, pos):
     ctx = pos + 8
     stride = ctx * n_kv * hd
     kc, vc = _f16_cache(13, n_seq * ctx, n_kv * hd), _f16_cache(14, n_seq * ctx, n_kv * hd)
@@ -96,6 +98,7 @@ def test_attention_independent_sequences(backend, oracle):
     scale = 1.0 / np.sqrt(hd)
     qb, kb, vb, db = backend.from_numpy(q), backend.from_numpy(kc), backend.from_numpy(vc), backend.alloc(q.nbytes)
     backend.attention(qb, kb, vb, db, rows=1, pos=pos, n_head=n_head, n_kv=n_kv, head_dim=hd, scale=scale, n_seq=n_seq, seq_stride=stride)
+    backend.sync()
     got = backend.download(db, np.float32).reshape(q.shape)
     for s in range(n_seq):
         want = oracle.attention(q[s], kc[s * ctx:(s + 1) * ctx], vc[s * ctx:(s + 1) * ctx], 1, n_head, n_kv, hd, scale, pos)

@@ -352,6 +352,15 @@ typedef struct infr_attn_desc {
 /* Op::Attention with AttnMask::Causal over f16 K / V caches [max_ctx, n_kv * head_dim] (cpu lib.rs:1744-1888). */
 INFR_API int32_t infr_cuda_attention(infr_cuda_ctx *ctx, const infr_attn_desc *desc, const infr_cuda_buf *q,
                                      const infr_cuda_buf *k_cache, const infr_cuda_buf *v_cache, infr_cuda_buf *dst);
+/* Sequences at positions of their own (a batch that is served continuously: sequences join and finish at different
+ * times).  No counterpart in the reference, whose Op::Attention takes one pos for all rows
+ * (crates/infr-llama/src/parallel.rs:9-17 names the per-row KV table as the missing throughput lever).  seq_pos is an
+ * int32 device array [n_seq]: the position of sequence s's first query row; desc->pos must be the largest of them (it
+ * sizes the launch and the bounds checks; a larger seq_pos[s] is read as desc->pos).  Sequence s attends keys
+ * [0, seq_pos[s] + row] of its own cache.  With infr_cuda_rope_write_kv, whose `positions` are per row already, a decode
+ * step over sequences of different lengths needs nothing else. */
+INFR_API int32_t infr_cuda_attention_seqpos(infr_cuda_ctx *ctx, const infr_attn_desc *desc, const infr_cuda_buf *seq_pos, const infr_cuda_buf *q,
+                                            const infr_cuda_buf *k_cache, const infr_cuda_buf *v_cache, infr_cuda_buf *dst);
 /* Rope(q) in place, Rope(k) and v straight into the f16 caches: the four ops of runner.rs:3611-3656 in one launch.
  * rope_dim == head_dim.  Row r belongs to sequence r / desc->rows and is written at cache row positions[r]. */
 INFR_API int32_t infr_cuda_rope_write_kv(infr_cuda_ctx *ctx, const infr_attn_desc *desc, float theta, int32_t neox, infr_cuda_buf *q,
@@ -375,6 +384,8 @@ INFR_API int32_t infr_cuda_gated_act_q8(infr_cuda_ctx *ctx, const infr_cuda_buf 
                                         const infr_q8_out *out);
 INFR_API int32_t infr_cuda_attention_q8(infr_cuda_ctx *ctx, const infr_attn_desc *desc, const infr_cuda_buf *q, const infr_cuda_buf *k_cache,
                                         const infr_cuda_buf *v_cache, const infr_q8_out *out);
+INFR_API int32_t infr_cuda_attention_seqpos_q8(infr_cuda_ctx *ctx, const infr_attn_desc *desc, const infr_cuda_buf *seq_pos, const infr_cuda_buf *q,
+                                               const infr_cuda_buf *k_cache, const infr_cuda_buf *v_cache, const infr_q8_out *out);
 /* Op::Argmax (cpu lib.rs:2167-2187): dst uint32 [rows], lowest index on ties. */
 INFR_API int32_t infr_cuda_argmax(infr_cuda_ctx *ctx, const infr_cuda_buf *x, infr_cuda_buf *dst, uint32_t n, uint32_t rows);
 

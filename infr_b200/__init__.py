@@ -42,6 +42,7 @@ EXPORTED_SYMBOLS = [
     "infr_cuda_launch_count", "infr_cuda_tensor_peak_i8",
     "infr_cuda_rms_norm", "infr_cuda_add_rms_norm", "infr_cuda_rope", "infr_cuda_write_kv", "infr_cuda_attention", "infr_cuda_rope_write_kv",
     "infr_cuda_gated_act", "infr_cuda_add", "infr_cuda_argmax", "infr_cuda_add_rms_norm_q8", "infr_cuda_gated_act_q8", "infr_cuda_attention_q8",
+    "infr_cuda_attention_seqpos", "infr_cuda_attention_seqpos_q8",
     "infr_gguf_open", "infr_gguf_close", "infr_gguf_version", "infr_gguf_alignment", "infr_gguf_tensor_count", "infr_gguf_tensor_at", "infr_gguf_find",
     "infr_gguf_tensor_data", "infr_gguf_meta_count", "infr_gguf_meta_key", "infr_gguf_meta_type", "infr_gguf_meta_u64", "infr_gguf_meta_f64",
     "infr_gguf_meta_str", "infr_gguf_meta_array",
@@ -174,6 +175,8 @@ def load_library() -> C.CDLL:
         "infr_cuda_add_rms_norm_q8": (i32, [vp, vp, vp, vp, vp, u32, u32, C.c_float, C.POINTER(_Q8Out)]),
         "infr_cuda_gated_act_q8": (i32, [vp, vp, vp, u32, u32, C.POINTER(_Q8Out)]),
         "infr_cuda_attention_q8": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, C.POINTER(_Q8Out)]),
+        "infr_cuda_attention_seqpos": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, vp, vp]),
+        "infr_cuda_attention_seqpos_q8": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, vp, C.POINTER(_Q8Out)]),
         "infr_gguf_open": (i32, [C.c_char_p, C.POINTER(vp), C.c_char_p, sz]),
         "infr_gguf_close": (None, [vp]),
         "infr_gguf_version": (u32, [vp]),
@@ -578,8 +581,12 @@ class CudaBackend:
         return _AttnDesc(rows, pos, n_head, n_kv, head_dim, scale, n_seq, 0, seq_stride)
 
     def attention(self, q: Buffer, k_cache: Buffer, v_cache: Buffer, dst: Buffer, *, rows: int, pos: int, n_head: int, n_kv: int,
-                  head_dim: int, scale: float, n_seq: int = 1, seq_stride: int = 0):
+                  head_dim: int, scale: float, n_seq: int = 1, seq_stride: int = 0, seq_pos: Optional[Buffer] = None):
+        """seq_pos: int32 [n_seq] on the device, each sequence's own position (pos is then their maximum)."""
         d = self._attn_desc(rows, pos, n_head, n_kv, head_dim, scale, n_seq, seq_stride)
+        if seq_pos is not None:
+            self._check(self.L.infr_cuda_attention_seqpos(self.ctx, C.byref(d), seq_pos.handle, q.handle, k_cache.handle, v_cache.handle, dst.handle))
+            return
         self._check(self.L.infr_cuda_attention(self.ctx, C.byref(d), q.handle, k_cache.handle, v_cache.handle, dst.handle))
 
     def rope_write_kv(self, q: Buffer, k: Buffer, v: Buffer, positions: Buffer, k_cache: Buffer, v_cache: Buffer, *, rows: int, pos: int,
@@ -611,9 +618,13 @@ class CudaBackend:
         self._check(self.L.infr_cuda_gated_act_q8(self.ctx, gate.handle, up.handle, rows, nff, C.byref(o)))
 
     def attention_q8(self, q: Buffer, k_cache: Buffer, v_cache: Buffer, qs: Buffer, d: Buffer, sums: Buffer, sums16: Optional[Buffer] = None, *,
-                     rows: int, pos: int, n_head: int, n_kv: int, head_dim: int, scale: float, n_seq: int = 1, seq_stride: int = 0):
+                     rows: int, pos: int, n_head: int, n_kv: int, head_dim: int, scale: float, n_seq: int = 1, seq_stride: int = 0,
+                     seq_pos: Optional[Buffer] = None):
         dsc = self._attn_desc(rows, pos, n_head, n_kv, head_dim, scale, n_seq, seq_stride)
         o = self._q8_out(qs, d, sums, sums16)
+        if seq_pos is not None:
+            self._check(self.L.infr_cuda_attention_seqpos_q8(self.ctx, C.byref(dsc), seq_pos.handle, q.handle, k_cache.handle, v_cache.handle, C.byref(o)))
+            return
         self._check(self.L.infr_cuda_attention_q8(self.ctx, C.byref(dsc), q.handle, k_cache.handle, v_cache.handle, C.byref(o)))
 
     def argmax(self, x: Buffer, dst: Buffer, n: int, rows: int):

@@ -553,7 +553,8 @@ Status CudaBackend::gated_act_q8(const float *gate, const float *up, uint32_t ro
     return s;
 }
 
-Status CudaBackend::attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst, const Q8Dev *q8) {
+Status CudaBackend::attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst, const Q8Dev *q8,
+                              const int32_t *seq_pos) {
     cudaSetDevice(device_);
     const uint32_t n_seq = d.n_seq ? d.n_seq : 1;
     const size_t ws = attention_workspace_bytes((int)(n_seq * d.rows), (int)d.n_head, (int)d.head_dim, (int)(d.pos + d.rows));
@@ -562,7 +563,7 @@ Status CudaBackend::attention(const infr_attn_desc &d, const float *q, const voi
     s = cuda_status(launch_attention(q, k_cache, v_cache, dst, scratch_, (int)n_seq, (int)d.rows, (int)d.n_head, (int)d.n_kv, (int)d.head_dim,
                                      d.scale, (int)d.pos, (size_t)d.seq_stride, dev_.sm_count, stream_, status_dev_, q8 ? const_cast<int8_t *>(q8->qs) : nullptr,
                                      q8 ? const_cast<float *>(q8->d) : nullptr, q8 ? const_cast<int32_t *>(q8->sums) : nullptr,
-                                     q8 ? const_cast<int32_t *>(q8->sums16) : nullptr),
+                                     q8 ? const_cast<int32_t *>(q8->sums16) : nullptr, seq_pos),
                     "attention");
     if (s.ok()) launches_ += 2;
     return s;

@@ -399,19 +399,43 @@ Status check_attn(const infr_attn_desc *d, const char *what) {
 }
 }  // namespace
 
-int32_t infr_cuda_attention(infr_cuda_ctx *ctx, const infr_attn_desc *d, const infr_cuda_buf *q, const infr_cuda_buf *k_cache,
-                            const infr_cuda_buf *v_cache, infr_cuda_buf *dst) {
+Status q8_out_args(const infr_q8_out *o, size_t rows, size_t k, const char *what, infr::Q8Dev *out);
+static int32_t attention_entry(infr_cuda_ctx *ctx, const infr_attn_desc *d, const infr_cuda_buf *seq_pos, bool with_pos, const infr_cuda_buf *q,
+                               const infr_cuda_buf *k_cache, const infr_cuda_buf *v_cache, infr_cuda_buf *dst, const infr_q8_out *out, bool q8_form) {
     INFR_CTX_OR_RETURN(ctx);
-    Status s = check_attn(d, "attention");
+    const char *what = q8_form ? "attention_q8" : "attention";
+    Status s = check_attn(d, what);
     if (!s.ok()) return finish(ctx, s);
     const size_t n_seq = d->n_seq ? d->n_seq : 1;
     const size_t qn = n_seq * d->rows * d->n_head * d->head_dim * 4;
     const size_t cn = ((n_seq - 1) * (size_t)d->seq_stride + (size_t)(d->pos + d->rows) * d->n_kv * d->head_dim) * 2;
-    uint8_t *pq, *pk, *pv, *pd;
+    uint8_t *pq, *pk, *pv, *pd = nullptr, *pp = nullptr;
     if (!(s = span(q, qn, "attention q", &pq)).ok() || !(s = span(k_cache, cn, "attention k_cache", &pk)).ok() ||
-        !(s = span(v_cache, cn, "attention v_cache", &pv)).ok() || !(s = span(dst, qn, "attention dst", &pd)).ok())
+        !(s = span(v_cache, cn, "attention v_cache", &pv)).ok())
         return finish(ctx, s);
-    return finish(ctx, ctx->be->attention(*d, (const float *)pq, pk, pv, (float *)pd));
+    if (with_pos && !(s = span(seq_pos, n_seq * 4, "attention seq_pos", &pp)).ok()) return finish(ctx, s);
+    if (q8_form) {
+        infr::Q8Dev q8;
+        if (!(s = q8_out_args(out, n_seq * d->rows, (size_t)d->n_head * d->head_dim, "attention_q8 output", &q8)).ok()) return finish(ctx, s);
+        return finish(ctx, ctx->be->attention(*d, (const float *)pq, pk, pv, nullptr, &q8, (const int32_t *)pp));
+    }
+    if (!(s = span(dst, qn, "attention dst", &pd)).ok()) return finish(ctx, s);
+    return finish(ctx, ctx->be->attention(*d, (const float *)pq, pk, pv, (float *)pd, nullptr, (const int32_t *)pp));
+}
+
+int32_t infr_cuda_attention(infr_cuda_ctx *ctx, const infr_attn_desc *d, const infr_cuda_buf *q, const infr_cuda_buf *k_cache,
+                            const infr_cuda_buf *v_cache, infr_cuda_buf *dst) {
+    return attention_entry(ctx, d, nullptr, false, q, k_cache, v_cache, dst, nullptr, false);
+}
+
+int32_t infr_cuda_attention_seqpos(infr_cuda_ctx *ctx, const infr_attn_desc *d, const infr_cuda_buf *seq_pos, const infr_cuda_buf *q,
+                                   const infr_cuda_buf *k_cache, const infr_cuda_buf *v_cache, infr_cuda_buf *dst) {
+    return attention_entry(ctx, d, seq_pos, true, q, k_cache, v_cache, dst, nullptr, false);
+}
+
+int32_t infr_cuda_attention_seqpos_q8(infr_cuda_ctx *ctx, const infr_attn_desc *d, const infr_cuda_buf *seq_pos, const infr_cuda_buf *q,
+                                      const infr_cuda_buf *k_cache, const infr_cuda_buf *v_cache, const infr_q8_out *out) {
+    return attention_entry(ctx, d, seq_pos, true, q, k_cache, v_cache, nullptr, out, true);
 }
 
 int32_t infr_cuda_rope_write_kv(infr_cuda_ctx *ctx, const infr_attn_desc *d, float theta, int32_t neox, infr_cuda_buf *q, const infr_cuda_buf *k,
@@ -478,19 +502,7 @@ int32_t infr_cuda_gated_act_q8(infr_cuda_ctx *ctx, const infr_cuda_buf *gate, co
 
 int32_t infr_cuda_attention_q8(infr_cuda_ctx *ctx, const infr_attn_desc *d, const infr_cuda_buf *q, const infr_cuda_buf *k_cache,
                                const infr_cuda_buf *v_cache, const infr_q8_out *out) {
-    INFR_CTX_OR_RETURN(ctx);
-    Status s = check_attn(d, "attention_q8");
-    if (!s.ok()) return finish(ctx, s);
-    const size_t n_seq = d->n_seq ? d->n_seq : 1;
-    infr::Q8Dev q8;
-    if (!(s = q8_out_args(out, n_seq * d->rows, (size_t)d->n_head * d->head_dim, "attention_q8 output", &q8)).ok()) return finish(ctx, s);
-    const size_t qn = n_seq * d->rows * d->n_head * d->head_dim * 4;
-    const size_t cn = ((n_seq - 1) * (size_t)d->seq_stride + (size_t)(d->pos + d->rows) * d->n_kv * d->head_dim) * 2;
-    uint8_t *pq, *pk, *pv;
-    if (!(s = span(q, qn, "attention_q8 q", &pq)).ok() || !(s = span(k_cache, cn, "attention_q8 k_cache", &pk)).ok() ||
-        !(s = span(v_cache, cn, "attention_q8 v_cache", &pv)).ok())
-        return finish(ctx, s);
-    return finish(ctx, ctx->be->attention(*d, (const float *)pq, pk, pv, nullptr, &q8));
+    return attention_entry(ctx, d, nullptr, false, q, k_cache, v_cache, nullptr, out, true);
 }
 
 int32_t infr_cuda_gated_act(infr_cuda_ctx *ctx, const infr_cuda_buf *gate, const infr_cuda_buf *up, infr_cuda_buf *dst, uint32_t rows,

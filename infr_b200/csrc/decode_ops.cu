@@ -274,7 +274,8 @@ template <int HD, int G, bool BULK>
 __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *__restrict__ q, const __half *__restrict__ k_cache,
                                                                const __half *__restrict__ v_cache, float *__restrict__ part_o,
                                                                float *__restrict__ part_ml, int rows, int n_head, int n_kv, int pos,
-                                                               float scale, int n_splits, size_t seq_stride, uint32_t *__restrict__ status) {
+                                                               float scale, int n_splits, size_t seq_stride, uint32_t *__restrict__ status,
+                                                               const int32_t *__restrict__ seq_pos) {
     constexpr int CPR = HD * 2 / 16;           // 16-byte pieces per row
     constexpr int NT = (2 * G + 7) / 8;        // 8-column groups of the instruction: column c = head c / 2, piece c % 2
     constexpr int DG = HD / 16;                // 16-dim output groups
@@ -291,11 +292,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *_
     static_assert(KP >= 1 && KP * DG == kAttnThreads / 32, "head_dim 64 or 128");
     const int split = blockIdx.x, kvh = blockIdx.y, qr = blockIdx.z;
     const int seq = qr / rows, ti = qr % rows;
-    const int n_keys = pos + ti + 1;
     const int key0 = split * kAttnTile;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
     pdl_go();
     pdl_wait();
+    // sequences at positions of their own (seq_pos, written by an earlier kernel or the host): `pos` is their maximum
+    const int n_keys = (seq_pos ? max(0, min(seq_pos[seq], pos)) : pos) + ti + 1;
     const size_t out_idx = ((size_t)qr * n_head + (size_t)kvh * G) * n_splits + split;  // + g * n_splits
     if (key0 >= n_keys) {  // a tile beyond this row's causal end contributes nothing
         if (tid < G) {
@@ -852,31 +854,33 @@ size_t attention_workspace_bytes(int q_rows, int n_head, int head_dim, int max_k
 
 template <int HD, int G>
 static cudaError_t launch_attn_one(dim3 grid, cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *po, float *pml, int rows,
-                                   int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride, uint32_t *status, bool bulk) {
+                                   int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride, uint32_t *status, bool bulk,
+                                   const int32_t *seq_pos) {
     // the tile needs more than the default 48 KB of dynamic shared memory; the attribute is per device, so it is set
     // on every launch (cheap, allocates nothing) rather than remembered per process
     auto kernel = bulk ? attn_split_kernel<HD, G, true> : attn_split_kernel<HD, G, false>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<HD>::kBytes);
     if (e != cudaSuccess) return e;
     return launch_pdl(kernel, grid, dim3(kAttnThreads), (size_t)AttnSmem<HD>::kBytes, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits,
-                      seq_stride, status);
+                      seq_stride, status, seq_pos);
 }
 
 template <int HD>
 static cudaError_t launch_attn_hd(int group, dim3 grid, cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *po, float *pml,
-                                  int rows, int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride, uint32_t *status, bool bulk) {
+                                  int rows, int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride, uint32_t *status, bool bulk,
+                                  const int32_t *seq_pos) {
     switch (group) {
-        case 1: return launch_attn_one<HD, 1>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
-        case 2: return launch_attn_one<HD, 2>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
-        case 4: return launch_attn_one<HD, 4>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
-        case 8: return launch_attn_one<HD, 8>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
+        case 1: return launch_attn_one<HD, 1>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
+        case 2: return launch_attn_one<HD, 2>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
+        case 4: return launch_attn_one<HD, 4>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
+        case 8: return launch_attn_one<HD, 8>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
         default: return cudaErrorInvalidValue;
     }
 }
 
 cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_cache, float *dst, void *workspace, int n_seq, int rows, int n_head,
                              int n_kv, int head_dim, float scale, int pos, size_t seq_stride, int sm_count, cudaStream_t st, uint32_t *status, int8_t *qs, float *d,
-                             int32_t *sums, int32_t *sums16) {
+                             int32_t *sums, int32_t *sums16, const int32_t *seq_pos) {
     if (n_seq <= 0 || rows <= 0 || n_head <= 0 || n_kv <= 0 || n_head % n_kv || pos < 0) return cudaErrorInvalidValue;
     const int max_keys = pos + rows, n_splits = (max_keys + kAttnTile - 1) / kAttnTile, q_rows = n_seq * rows;
     if (n_kv > 65535 || q_rows > 65535) return cudaErrorInvalidValue;
@@ -891,9 +895,9 @@ cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_
     const bool bulk = (size_t)n_splits * n_kv * q_rows > (size_t)6 * (sm_count > 0 ? sm_count : 148);
     const int g = n_head / n_kv;
     if (head_dim == 128)
-        e = launch_attn_hd<128>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
+        e = launch_attn_hd<128>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
     else if (head_dim == 64)
-        e = launch_attn_hd<64>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk);
+        e = launch_attn_hd<64>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
     else
         return cudaErrorInvalidValue;
     if (e != cudaSuccess) return e;

@@ -151,7 +151,8 @@ size_t attention_workspace_bytes(int q_rows, int n_head, int head_dim, int max_k
 // With qs != nullptr the merged rows are quantised (256-element blocks) instead of stored to dst.
 cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_cache, float *dst, void *workspace, int n_seq, int rows, int n_head,
                              int n_kv, int head_dim, float scale, int pos, size_t seq_stride, int sm_count, cudaStream_t st, uint32_t *status,
-                             int8_t *qs = nullptr, float *d = nullptr, int32_t *sums = nullptr, int32_t *sums16 = nullptr);
+                             int8_t *qs = nullptr, float *d = nullptr, int32_t *sums = nullptr, int32_t *sums16 = nullptr,
+                             const int32_t *seq_pos = nullptr);
 // Producers that end in the activation quantiser (256-element blocks; sums16 may be null).
 cudaError_t launch_rms_norm_q8(const float *a, const float *b, float *sum_dst, const float *w, int rows, int dim, float eps, int8_t *qs, float *d,
                                int32_t *sums, int32_t *sums16, cudaStream_t st);

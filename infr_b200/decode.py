@@ -4,7 +4,8 @@ RmsNorm, Linear gate/up, GatedAct, Linear down, Add, ..., RmsNorm, Linear lm_hea
 C ABI.  `fused=True` uses the fused launches (Add+RmsNorm, Rope+Rope+WriteKv+WriteKv) and, for at most 8 rows, the
 producers that end in the activation quantiser, so that every Linear is one GEMV launch on int8 codes shared by all
 Linears that read the same input; `fused=False` issues the reference's ops one by one.  The batch is `n_seq` independent sequences, one new token each, all at position `pos`,
-every sequence with its own f16 KV cache."""
+every sequence with its own f16 KV cache; `set_inputs` also takes one position per sequence (a continuously served batch),
+which the rotation, the cache write and the attention then follow per sequence."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -91,14 +92,22 @@ class DecodeStep:
         ok = lambda dt, k: dt == Q4K or (dt == Q6K and k % 2048 == 0)
         return all(ok(self._dt(L, n), k) for L in self.layers for n, k in ins.items()) and ok(self.head_dtype, s.hidden)
 
-    def set_inputs(self, hidden: np.ndarray, pos: int):
+    def set_inputs(self, hidden: np.ndarray, pos):
+        """pos: one position for every sequence, or one per sequence (sequences that joined the batch at different
+        times: `run` then takes the largest)."""
         self.be.upload(self.hidden, np.ascontiguousarray(hidden, np.float32))
-        self.be.upload(self.positions, np.full(self.n_seq, pos, np.int32))
+        p = np.full(self.n_seq, pos, np.int32) if np.isscalar(pos) else np.ascontiguousarray(pos, np.int32)
+        assert p.shape == (self.n_seq,)
+        self.uniform_pos = bool((p == p[0]).all())
+        self.host_pos = p
+        self.be.upload(self.positions, p)
 
     def run(self, pos: int, fused: bool = True, q8_fused=None) -> int:
         """Enqueues one step (reads self.hidden / self.positions, leaves logits and token ids on the device).
         Returns the number of ops issued."""
         s, b = self.s, self.n_seq
+        # sequences at positions of their own: attention reads them from the device, `pos` bounds them
+        self._seq_pos = None if getattr(self, "uniform_pos", True) else self.positions
         if q8_fused is None:
             q8_fused = fused and (b <= 8 or self._wide_ok()) and s.hidden % 256 == 0 and s.ffn % 256 == 0 and s.q_dim % 256 == 0
         return self._run_q8(pos) if q8_fused else self._run_f32(pos, fused)
@@ -127,7 +136,7 @@ class DecodeStep:
             be.rope_write_kv(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], rows=1, pos=pos,
                              n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
             be.attention_q8(self.q, self.k_cache[li], self.v_cache[li], *a8, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
-                            head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride)
+                            head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride, seq_pos=self._seq_pos)
             gemv(dt(L, "wo"), L["wo"], self.sub, s.q_dim, h)
             if self.reduce:
                 self.reduce(self.sub, b * h)
@@ -197,12 +206,12 @@ class DecodeStep:
                     for src, cache in ((self.k_rot, self.k_cache[li]), (self.v, self.v_cache[li])):
                         row = be.wrap(src.device_ptr() + sq * s.kv_dim * 4, s.kv_dim * 4, USAGE_ACTIVATIONS)
                         one = be.wrap(cache.device_ptr() + sq * self.seq_stride * 2, self.seq_stride * 2, USAGE_ACTIVATIONS)
-                        be.write_kv(row, one, 1, s.kv_dim, pos)
+                        be.write_kv(row, one, 1, s.kv_dim, int(self.host_pos[sq]) if self._seq_pos is not None else pos)
                         row.close()
                         one.close()
                         n += 1
             be.attention(self.q, self.k_cache[li], self.v_cache[li], self.attn, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
-                         head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride)
+                         head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride, seq_pos=self._seq_pos)
             lin(dt(L, "wo"), L["wo"], self.attn, self.sub, s.q_dim, h)
             n += 2
             if self.reduce:

@@ -216,3 +216,23 @@ def test_producers_ending_in_the_quantiser_emit_the_quantisers_bits(backend, ora
     _q8_equal(backend, got, want)
     with pytest.raises(infr_b200.BackendError):
         backend.gated_act_q8(gb, ub, rows, 1000, *got)  # not whole 256-element blocks
+
+
+def test_attention_with_a_position_per_sequence(backend, oracle):
+    n_seq, n_head, n_kv, hd = 5, 8, 2, 128
+    pos = np.array([300, 0, 127, 128, 1], np.int32)  # tile boundaries of 128 keys, an empty history
+    ctx = int(pos.max()) + 4
+    stride = ctx * n_kv * hd
+    kc, vc = _f16_cache(21, n_seq * ctx, n_kv * hd), _f16_cache(22, n_seq * ctx, n_kv * hd)
+    q = synth.normal(23, (n_seq, n_head * hd))
+    scale = 1.0 / np.sqrt(hd)
+    qb, kb, vb, db, pb = backend.from_numpy(q), backend.from_numpy(kc), backend.from_numpy(vc), backend.alloc(q.nbytes), backend.from_numpy(pos)
+    backend.attention(qb, kb, vb, db, rows=1, pos=int(pos.max()), n_head=n_head, n_kv=n_kv, head_dim=hd, scale=scale, n_seq=n_seq, seq_stride=stride,
+                      seq_pos=pb)
+    got = backend.download(db, np.float32).reshape(q.shape)
+    for s in range(n_seq):
+        want = oracle.attention(q[s], kc[s * ctx:(s + 1) * ctx], vc[s * ctx:(s + 1) * ctx], 1, n_head, n_kv, hd, scale, int(pos[s]))
+        assert fx.rel_l2(got[s], want) < TIGHT, s
+    with pytest.raises(infr_b200.BackendError):  # the position array must cover every sequence
+        backend.attention(qb, kb, vb, db, rows=1, pos=int(pos.max()), n_head=n_head, n_kv=n_kv, head_dim=hd, scale=scale, n_seq=n_seq,
+                          seq_stride=stride, seq_pos=backend.from_numpy(pos[:2]))

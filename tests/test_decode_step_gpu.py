@@ -123,3 +123,54 @@ def test_a_dozen_sequences_keep_int8_activations_between_ops(backend):
     assert fx.rel_l2(got_logits, ref_logits) < 1e-5
     np.testing.assert_array_equal(got_tok, ref_tok)
     assert got_launches < ref_launches
+
+
+def test_sequences_at_positions_of_their_own(backend, oracle):
+    """A continuously served batch: every sequence has its own length.  Each sequence's logits are those of the same
+    sequence run alone at its position (the CPU op sequence per sequence), in the op-by-op, fused and int8-producer forms."""
+    s = SHAPE
+    layers, out_norm, head, kc, vc = _model(seed0=3000)
+    b, positions = N_SEQ, np.array([5, 31], np.int32)
+    hidden = synth.normal(78, (b, s.hidden))
+    dev_layers = []
+    for L in layers:
+        d = {name: backend.from_numpy(L[name][1], infr_b200.USAGE_WEIGHTS) for name, *_ in s.linears()}
+        d["attn_norm"], d["ffn_norm"] = backend.from_numpy(L["attn_norm"]), backend.from_numpy(L["ffn_norm"])
+        dev_layers.append(d)
+    on, hd = backend.from_numpy(out_norm), backend.from_numpy(head, infr_b200.USAGE_WEIGHTS)
+    # the CPU: one sequence at a time at its own position
+    want = np.empty((b, s.vocab), np.float32)
+    scale = 1.0 / np.sqrt(s.head_dim)
+    for sq in range(b):
+        pos = int(positions[sq])
+        lin = lambda w, x: oracle.linear(w[0], w[1], x, 1, w[3], w[2])
+        h = hidden[sq:sq + 1].copy()
+        for li, L in enumerate(layers):
+            hn = oracle.rms_norm(h, L["attn_norm"], s.eps)
+            q, k, v = lin(L["wq"], hn), lin(L["wk"], hn), lin(L["wv"], hn)
+            pf = np.full(1, pos, np.float32)
+            k16 = oracle.rope(k, pf, s.n_kv, s.head_dim, s.head_dim, s.theta)
+            q = oracle.rope(q, pf, s.n_head, s.head_dim, s.head_dim, s.theta)
+            ks, vs = kc[li][sq * MAX_CTX:(sq + 1) * MAX_CTX].copy(), vc[li][sq * MAX_CTX:(sq + 1) * MAX_CTX].copy()
+            oracle.write_kv_f16(k16[0], ks, 1, s.kv_dim, pos)
+            oracle.write_kv_f16(v[0], vs, 1, s.kv_dim, pos)
+            attn = oracle.attention(q[0], ks, vs, 1, s.n_head, s.n_kv, s.head_dim, scale, pos).reshape(1, -1)
+            h = oracle.add(h, lin(L["wo"], attn))
+            hn = oracle.rms_norm(h, L["ffn_norm"], s.eps)
+            h = oracle.add(h, lin(L["down"], oracle.gated_act(lin(L["gate"], hn), lin(L["up"], hn))))
+        want[sq] = oracle.linear(Q4K, head, oracle.rms_norm(h, out_norm, s.eps), 1, s.hidden, s.vocab)
+    for fused, q8 in ((False, False), (True, False), (True, True)):
+        step = DecodeStep(backend, s, b, MAX_CTX, dev_layers, on, hd, Q4K, [backend.from_numpy(c) for c in kc], [backend.from_numpy(c) for c in vc])
+        step.set_inputs(hidden, positions)
+        step.run(int(positions.max()), fused=fused, q8_fused=q8)
+        got = backend.download(step.logits, np.float32).reshape(b, s.vocab)
+        for sq in range(b):
+            assert fx.rel_l2(got[sq], want[sq]) < 1e-3, (fused, q8, sq)
+            assert int(np.argmax(got[sq])) == int(np.argmax(want[sq]))
+        # the rows written are each sequence's own position
+        for li in range(s.n_layer):
+            g = backend.download(step.v_cache[li], np.uint16).reshape(vc[li].shape)
+            keep = np.ones(g.shape[0], bool)
+            keep[[int(positions[0]), MAX_CTX + int(positions[1])]] = False
+            np.testing.assert_array_equal(g[keep], vc[li][keep])
+            assert (g[~keep] != vc[li][~keep]).any()

@@ -386,6 +386,20 @@ INFR_API int32_t infr_cuda_attention_q8(infr_cuda_ctx *ctx, const infr_attn_desc
                                         const infr_cuda_buf *v_cache, const infr_q8_out *out);
 INFR_API int32_t infr_cuda_attention_seqpos_q8(infr_cuda_ctx *ctx, const infr_attn_desc *desc, const infr_cuda_buf *seq_pos, const infr_cuda_buf *q,
                                                const infr_cuda_buf *k_cache, const infr_cuda_buf *v_cache, const infr_q8_out *out);
+/* Paged caches (the per-row KV block table that crates/infr-llama/src/parallel.rs:9-17 names; no counterpart in the
+ * reference): k_pool / v_pool hold n_pages pages of 128 rows [n_pages][128][n_kv * head_dim] f16 shared by all sequences,
+ * block_table is an int32 device array [n_seq][table_stride] whose entry (s, i) is the page with rows 128 i .. 128 i + 127
+ * of sequence s (an entry outside [0, n_pages) is read as the nearest valid page: a wrong table gives wrong numbers, not a
+ * fault).  table_stride >= (desc->pos + desc->rows + 127) / 128; desc->seq_stride is ignored; seq_pos may be NULL (every
+ * sequence at desc->pos).  attention_paged writes f32 rows to dst or, with dst NULL, the int8 form to out (exactly one).
+ * rope_write_kv_paged is infr_cuda_rope_write_kv with row r of sequence s stored at page table[s][positions[r] / 128]. */
+INFR_API int32_t infr_cuda_attention_paged(infr_cuda_ctx *ctx, const infr_attn_desc *desc, const infr_cuda_buf *seq_pos, const infr_cuda_buf *block_table,
+                                           uint32_t table_stride, uint32_t n_pages, const infr_cuda_buf *q, const infr_cuda_buf *k_pool,
+                                           const infr_cuda_buf *v_pool, infr_cuda_buf *dst, const infr_q8_out *out);
+INFR_API int32_t infr_cuda_rope_write_kv_paged(infr_cuda_ctx *ctx, const infr_attn_desc *desc, float theta, int32_t neox, infr_cuda_buf *q,
+                                               const infr_cuda_buf *k, const infr_cuda_buf *v, const infr_cuda_buf *positions,
+                                               const infr_cuda_buf *block_table, uint32_t table_stride, uint32_t n_pages, infr_cuda_buf *k_pool,
+                                               infr_cuda_buf *v_pool);
 /* Op::Argmax (cpu lib.rs:2167-2187): dst uint32 [rows], lowest index on ties. */
 INFR_API int32_t infr_cuda_argmax(infr_cuda_ctx *ctx, const infr_cuda_buf *x, infr_cuda_buf *dst, uint32_t n, uint32_t rows);
 

@@ -42,7 +42,7 @@ EXPORTED_SYMBOLS = [
     "infr_cuda_launch_count", "infr_cuda_tensor_peak_i8",
     "infr_cuda_rms_norm", "infr_cuda_add_rms_norm", "infr_cuda_rope", "infr_cuda_write_kv", "infr_cuda_attention", "infr_cuda_rope_write_kv",
     "infr_cuda_gated_act", "infr_cuda_add", "infr_cuda_argmax", "infr_cuda_add_rms_norm_q8", "infr_cuda_gated_act_q8", "infr_cuda_attention_q8",
-    "infr_cuda_attention_seqpos", "infr_cuda_attention_seqpos_q8",
+    "infr_cuda_attention_seqpos", "infr_cuda_attention_seqpos_q8", "infr_cuda_attention_paged", "infr_cuda_rope_write_kv_paged",
     "infr_gguf_open", "infr_gguf_close", "infr_gguf_version", "infr_gguf_alignment", "infr_gguf_tensor_count", "infr_gguf_tensor_at", "infr_gguf_find",
     "infr_gguf_tensor_data", "infr_gguf_meta_count", "infr_gguf_meta_key", "infr_gguf_meta_type", "infr_gguf_meta_u64", "infr_gguf_meta_f64",
     "infr_gguf_meta_str", "infr_gguf_meta_array",
@@ -177,6 +177,8 @@ def load_library() -> C.CDLL:
         "infr_cuda_attention_q8": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, C.POINTER(_Q8Out)]),
         "infr_cuda_attention_seqpos": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, vp, vp]),
         "infr_cuda_attention_seqpos_q8": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, vp, C.POINTER(_Q8Out)]),
+        "infr_cuda_attention_paged": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, u32, u32, vp, vp, vp, vp, C.POINTER(_Q8Out)]),
+        "infr_cuda_rope_write_kv_paged": (i32, [vp, C.POINTER(_AttnDesc), C.c_float, i32, vp, vp, vp, vp, vp, u32, u32, vp, vp]),
         "infr_gguf_open": (i32, [C.c_char_p, C.POINTER(vp), C.c_char_p, sz]),
         "infr_gguf_close": (None, [vp]),
         "infr_gguf_version": (u32, [vp]),
@@ -594,6 +596,24 @@ class CudaBackend:
         d = self._attn_desc(rows, pos, n_head, n_kv, head_dim, 0.0, n_seq, seq_stride)
         self._check(self.L.infr_cuda_rope_write_kv(self.ctx, C.byref(d), theta, int(neox), q.handle, k.handle, v.handle, positions.handle,
                                                    k_cache.handle, v_cache.handle))
+
+    def attention_paged(self, q: Buffer, k_pool: Buffer, v_pool: Buffer, block_table: Buffer, table_stride: int, n_pages: int, *, rows: int,
+                        pos: int, n_head: int, n_kv: int, head_dim: int, scale: float, n_seq: int = 1, seq_pos: Optional[Buffer] = None,
+                        dst: Optional[Buffer] = None, q8=None):
+        """Attention over paged caches (pools of 128-row pages, a page table per sequence); q8 = (qs, d, sums, sums16)
+        for the int8 form instead of dst."""
+        d = self._attn_desc(rows, pos, n_head, n_kv, head_dim, scale, n_seq, 0)
+        o = self._q8_out(*q8) if q8 is not None else None
+        self._check(self.L.infr_cuda_attention_paged(self.ctx, C.byref(d), seq_pos.handle if seq_pos else None, block_table.handle, table_stride,
+                                                     n_pages, q.handle, k_pool.handle, v_pool.handle, dst.handle if dst else None,
+                                                     C.byref(o) if o is not None else None))
+
+    def rope_write_kv_paged(self, q: Buffer, k: Buffer, v: Buffer, positions: Buffer, k_pool: Buffer, v_pool: Buffer, block_table: Buffer,
+                            table_stride: int, n_pages: int, *, rows: int, pos: int, n_head: int, n_kv: int, head_dim: int, theta: float,
+                            neox: bool = False, n_seq: int = 1):
+        d = self._attn_desc(rows, pos, n_head, n_kv, head_dim, 0.0, n_seq, 0)
+        self._check(self.L.infr_cuda_rope_write_kv_paged(self.ctx, C.byref(d), theta, int(neox), q.handle, k.handle, v.handle, positions.handle,
+                                                         block_table.handle, table_stride, n_pages, k_pool.handle, v_pool.handle))
 
     def gated_act(self, gate: Buffer, up: Buffer, dst: Buffer, rows: int, nff: int):
         self._check(self.L.infr_cuda_gated_act(self.ctx, gate.handle, up.handle, dst.handle, rows, nff))

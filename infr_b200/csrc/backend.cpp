@@ -525,11 +525,13 @@ Status CudaBackend::write_kv(const float *src, void *cache_at_pos, size_t n) {
 }
 
 Status CudaBackend::rope_write_kv(const infr_attn_desc &d, float theta, int neox, float *q, const float *k, const float *v,
-                                  const int32_t *positions, void *k_cache, void *v_cache, int write_pos) {
+                                  const int32_t *positions, void *k_cache, void *v_cache, int write_pos, const int32_t *block_table,
+                                  uint32_t table_stride, uint32_t n_pages) {
     cudaSetDevice(device_);
     const uint32_t n_seq = d.n_seq ? d.n_seq : 1;
     Status s = cuda_status(launch_rope_write_kv(q, k, v, positions, k_cache, v_cache, (int)(n_seq * d.rows), (int)d.n_head, (int)d.n_kv,
-                                                (int)d.head_dim, theta, neox, (int)d.rows, (size_t)d.seq_stride, dev_, stream_, write_pos),
+                                                (int)d.head_dim, theta, neox, (int)d.rows, block_table ? 0 : (size_t)d.seq_stride, dev_, stream_, write_pos, block_table,
+                                                (int)table_stride, (int)n_pages),
                            "rope_write_kv");
     if (s.ok()) launches_++;
     return s;
@@ -554,16 +556,16 @@ Status CudaBackend::gated_act_q8(const float *gate, const float *up, uint32_t ro
 }
 
 Status CudaBackend::attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst, const Q8Dev *q8,
-                              const int32_t *seq_pos) {
+                              const int32_t *seq_pos, const int32_t *block_table, uint32_t table_stride, uint32_t n_pages) {
     cudaSetDevice(device_);
     const uint32_t n_seq = d.n_seq ? d.n_seq : 1;
     const size_t ws = attention_workspace_bytes((int)(n_seq * d.rows), (int)d.n_head, (int)d.head_dim, (int)(d.pos + d.rows));
     Status s = ensure_scratch(ws);
     if (!s.ok()) return s;
     s = cuda_status(launch_attention(q, k_cache, v_cache, dst, scratch_, (int)n_seq, (int)d.rows, (int)d.n_head, (int)d.n_kv, (int)d.head_dim,
-                                     d.scale, (int)d.pos, (size_t)d.seq_stride, dev_.sm_count, stream_, status_dev_, q8 ? const_cast<int8_t *>(q8->qs) : nullptr,
+                                     d.scale, (int)d.pos, block_table ? 0 : (size_t)d.seq_stride, dev_.sm_count, stream_, status_dev_, q8 ? const_cast<int8_t *>(q8->qs) : nullptr,
                                      q8 ? const_cast<float *>(q8->d) : nullptr, q8 ? const_cast<int32_t *>(q8->sums) : nullptr,
-                                     q8 ? const_cast<int32_t *>(q8->sums16) : nullptr, seq_pos),
+                                     q8 ? const_cast<int32_t *>(q8->sums16) : nullptr, seq_pos, block_table, (int)table_stride, (int)n_pages),
                     "attention");
     if (s.ok()) launches_ += 2;
     return s;

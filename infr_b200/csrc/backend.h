@@ -129,10 +129,12 @@ public:
     Status write_kv(const float *src, void *cache_at_pos, size_t n);
     // write_pos >= 0: cache row = write_pos + row (Op::WriteKv's `pos`); < 0: the row's own position
     Status rope_write_kv(const infr_attn_desc &d, float theta, int neox, float *q, const float *k, const float *v, const int32_t *positions,
-                         void *k_cache, void *v_cache, int write_pos = -1);
+                         void *k_cache, void *v_cache, int write_pos = -1,
+                         const int32_t *block_table = nullptr, uint32_t table_stride = 0, uint32_t n_pages = 0);
     // seq_pos: optional device array of per-sequence positions (d.pos is then their maximum)
+    // block_table: optional paged caches (int32 [n_seq][table_stride] on the device; k_cache / v_cache are then pools of n_pages pages)
     Status attention(const infr_attn_desc &d, const float *q, const void *k_cache, const void *v_cache, float *dst, const Q8Dev *q8 = nullptr,
-                     const int32_t *seq_pos = nullptr);
+                     const int32_t *seq_pos = nullptr, const int32_t *block_table = nullptr, uint32_t table_stride = 0, uint32_t n_pages = 0);
     Status rms_norm_q8(const float *a, const float *b, float *sum_dst, const float *w, uint32_t rows, uint32_t dim, float eps, const Q8Dev &q8);
     Status gated_act_q8(const float *gate, const float *up, uint32_t rows, uint32_t nff, const Q8Dev &q8);
     Status gated_act(const float *gate, const float *up, float *dst, size_t n);

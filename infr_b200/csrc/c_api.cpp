@@ -386,14 +386,14 @@ int32_t infr_cuda_write_kv(infr_cuda_ctx *ctx, const infr_cuda_buf *src, infr_cu
 }
 
 namespace {
-Status check_attn(const infr_attn_desc *d, const char *what) {
+Status check_attn(const infr_attn_desc *d, const char *what, bool paged = false) {
     if (!d) return Status::Err(INFR_E_INVALID, std::string(what) + ": null descriptor");
     if (d->rows == 0 || d->n_head == 0 || d->n_kv == 0 || d->n_head % d->n_kv)
         return Status::Err(INFR_E_INVALID, std::string(what) + ": rows, n_head, n_kv positive and n_head a multiple of n_kv");
     const uint32_t g = d->n_head / d->n_kv;
     if ((d->head_dim != 64 && d->head_dim != 128) || (g != 1 && g != 2 && g != 4 && g != 8))
         return Status::Err(INFR_E_UNSUPPORTED, std::string(what) + ": head_dim 64 or 128 and n_head / n_kv in {1, 2, 4, 8}");
-    if (d->n_seq > 1 && (d->seq_stride < (uint64_t)(d->pos + d->rows) * d->n_kv * d->head_dim || d->seq_stride % 8))
+    if (!paged && d->n_seq > 1 && (d->seq_stride < (uint64_t)(d->pos + d->rows) * d->n_kv * d->head_dim || d->seq_stride % 8))
         return Status::Err(INFR_E_INVALID, std::string(what) + ": seq_stride must cover one sequence's rows and be a multiple of 8 elements");
     return Status::Ok();
 }
@@ -436,6 +436,60 @@ int32_t infr_cuda_attention_seqpos(infr_cuda_ctx *ctx, const infr_attn_desc *d, 
 int32_t infr_cuda_attention_seqpos_q8(infr_cuda_ctx *ctx, const infr_attn_desc *d, const infr_cuda_buf *seq_pos, const infr_cuda_buf *q,
                                       const infr_cuda_buf *k_cache, const infr_cuda_buf *v_cache, const infr_q8_out *out) {
     return attention_entry(ctx, d, seq_pos, true, q, k_cache, v_cache, nullptr, out, true);
+}
+
+// Paged caches: pools of n_pages pages of 128 rows, a table of pages per sequence.
+static Status paged_args(const infr_attn_desc *d, const infr_cuda_buf *block_table, uint32_t table_stride, uint32_t n_pages, const infr_cuda_buf *k_pool,
+                         const infr_cuda_buf *v_pool, uint8_t **pt, uint8_t **pk, uint8_t **pv) {
+    const size_t n_seq = d->n_seq ? d->n_seq : 1;
+    const size_t need_pages = ((size_t)d->pos + d->rows + 127) / 128;
+    if (n_pages == 0 || n_pages > (1u << 24) || table_stride < need_pages)
+        return Status::Err(INFR_E_INVALID, "paged cache: n_pages must be positive and table_stride must cover (pos + rows) / 128 pages");
+    const size_t pool = (size_t)n_pages * 128 * d->n_kv * d->head_dim * 2;
+    Status s;
+    if (!(s = span(block_table, n_seq * table_stride * 4, "paged cache block_table", pt)).ok() || !(s = span(k_pool, pool, "paged cache k_pool", pk)).ok() ||
+        !(s = span(v_pool, pool, "paged cache v_pool", pv)).ok())
+        return s;
+    return Status::Ok();
+}
+
+int32_t infr_cuda_attention_paged(infr_cuda_ctx *ctx, const infr_attn_desc *d, const infr_cuda_buf *seq_pos, const infr_cuda_buf *block_table,
+                                  uint32_t table_stride, uint32_t n_pages, const infr_cuda_buf *q, const infr_cuda_buf *k_pool,
+                                  const infr_cuda_buf *v_pool, infr_cuda_buf *dst, const infr_q8_out *out) {
+    INFR_CTX_OR_RETURN(ctx);
+    Status s = check_attn(d, "attention_paged", true);
+    if (!s.ok()) return finish(ctx, s);
+    if ((dst != nullptr) == (out != nullptr)) return finish(ctx, Status::Err(INFR_E_INVALID, "attention_paged: exactly one of dst and out"));
+    const size_t n_seq = d->n_seq ? d->n_seq : 1, qn = n_seq * d->rows * d->n_head * d->head_dim * 4;
+    uint8_t *pq, *pk, *pv, *pt, *pd = nullptr, *pp = nullptr;
+    if (!(s = paged_args(d, block_table, table_stride, n_pages, k_pool, v_pool, &pt, &pk, &pv)).ok() || !(s = span(q, qn, "attention_paged q", &pq)).ok())
+        return finish(ctx, s);
+    if (seq_pos && !(s = span(seq_pos, n_seq * 4, "attention_paged seq_pos", &pp)).ok()) return finish(ctx, s);
+    if (out) {
+        infr::Q8Dev q8;
+        if (!(s = q8_out_args(out, n_seq * d->rows, (size_t)d->n_head * d->head_dim, "attention_paged output", &q8)).ok()) return finish(ctx, s);
+        return finish(ctx, ctx->be->attention(*d, (const float *)pq, pk, pv, nullptr, &q8, (const int32_t *)pp, (const int32_t *)pt, table_stride, n_pages));
+    }
+    if (!(s = span(dst, qn, "attention_paged dst", &pd)).ok()) return finish(ctx, s);
+    return finish(ctx, ctx->be->attention(*d, (const float *)pq, pk, pv, (float *)pd, nullptr, (const int32_t *)pp, (const int32_t *)pt, table_stride, n_pages));
+}
+
+int32_t infr_cuda_rope_write_kv_paged(infr_cuda_ctx *ctx, const infr_attn_desc *d, float theta, int32_t neox, infr_cuda_buf *q, const infr_cuda_buf *k,
+                                      const infr_cuda_buf *v, const infr_cuda_buf *positions, const infr_cuda_buf *block_table, uint32_t table_stride,
+                                      uint32_t n_pages, infr_cuda_buf *k_pool, infr_cuda_buf *v_pool) {
+    INFR_CTX_OR_RETURN(ctx);
+    Status s = check_attn(d, "rope_write_kv_paged", true);
+    if (!s.ok()) return finish(ctx, s);
+    const size_t n_seq = d->n_seq ? d->n_seq : 1, rows = n_seq * d->rows;
+    uint8_t *pq, *pk, *pv, *pp, *pt, *pkc, *pvc;
+    if (!(s = paged_args(d, block_table, table_stride, n_pages, k_pool, v_pool, &pt, &pkc, &pvc)).ok() ||
+        !(s = span(q, rows * d->n_head * d->head_dim * 4, "rope_write_kv_paged q", &pq)).ok() ||
+        !(s = span(k, rows * d->n_kv * d->head_dim * 4, "rope_write_kv_paged k", &pk)).ok() ||
+        !(s = span(v, rows * d->n_kv * d->head_dim * 4, "rope_write_kv_paged v", &pv)).ok() ||
+        !(s = span(positions, rows * 4, "rope_write_kv_paged positions", &pp)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->rope_write_kv(*d, theta, neox != 0, (float *)pq, (const float *)pk, (const float *)pv, (const int32_t *)pp, pkc, pvc, -1,
+                                              (const int32_t *)pt, table_stride, n_pages));
 }
 
 int32_t infr_cuda_rope_write_kv(infr_cuda_ctx *ctx, const infr_attn_desc *d, float theta, int32_t neox, infr_cuda_buf *q, const infr_cuda_buf *k,

@@ -138,10 +138,12 @@ __global__ void __launch_bounds__(256) rope_kernel(const float *__restrict__ x, 
 // Rope, Rope, WriteKv, WriteKv (crates/infr-llama/src/seam/runner.rs:3611-3656).  Row r belongs to sequence
 // r / rows_per_seq, whose caches start seq_stride elements after the previous sequence's, and lands at cache
 // row positions[r].  Full-head rotation only (rope_dim == head_dim).
+constexpr int kPageRows = 128;  // rows of a page of a paged KV cache = keys of an attention tile
 __global__ void __launch_bounds__(256) rope_write_kv_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                                             const int32_t *__restrict__ positions, __half *__restrict__ k_cache,
                                                             __half *__restrict__ v_cache, int rows, int n_head, int n_kv, int head_dim,
-                                                            float theta, int neox, int rows_per_seq, size_t seq_stride, int write_pos) {
+                                                            float theta, int neox, int rows_per_seq, size_t seq_stride, int write_pos,
+                                                            const int32_t *__restrict__ block_table, int table_stride, int n_pages) {
     pdl_go();
     pdl_wait();
     const int hf = head_dim / 2;
@@ -166,7 +168,13 @@ __global__ void __launch_bounds__(256) rope_write_kv_kernel(float *__restrict__ 
             const size_t b = rh * head_dim;
             // cache row: the op's own `pos` + row when the caller gives one (Op::WriteKv), else the row's position
             const size_t crow = write_pos >= 0 ? (size_t)(write_pos + r % rows_per_seq) : (size_t)positions[r];
-            const size_t cb = (size_t)(r / rows_per_seq) * seq_stride + (crow * n_kv + h) * head_dim;
+            size_t cb;
+            if (block_table) {  // paged caches: row crow of the sequence lives in page table[seq][crow / 128] of the pool
+                const int pg = min(max(block_table[(size_t)(r / rows_per_seq) * table_stride + crow / kPageRows], 0), n_pages - 1);
+                cb = (((size_t)pg * kPageRows + crow % kPageRows) * n_kv + h) * head_dim;
+            } else {
+                cb = (size_t)(r / rows_per_seq) * seq_stride + (crow * n_kv + h) * head_dim;
+            }
             if (is_v) {
                 v_cache[cb + 2 * p] = __float2half_rn(v[b + 2 * p]);
                 v_cache[cb + 2 * p + 1] = __float2half_rn(v[b + 2 * p + 1]);
@@ -275,7 +283,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *_
                                                                const __half *__restrict__ v_cache, float *__restrict__ part_o,
                                                                float *__restrict__ part_ml, int rows, int n_head, int n_kv, int pos,
                                                                float scale, int n_splits, size_t seq_stride, uint32_t *__restrict__ status,
-                                                               const int32_t *__restrict__ seq_pos) {
+                                                               const int32_t *__restrict__ seq_pos, const int32_t *__restrict__ block_table,
+                                                               int table_stride, int n_pages) {
     constexpr int CPR = HD * 2 / 16;           // 16-byte pieces per row
     constexpr int NT = (2 * G + 7) / 8;        // 8-column groups of the instruction: column c = head c / 2, piece c % 2
     constexpr int DG = HD / 16;                // 16-dim output groups
@@ -307,8 +316,11 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(const float *_
         return;
     }
     const size_t kv_row = (size_t)n_kv * HD;
-    const __half *kbase = k_cache + (size_t)seq * seq_stride + (size_t)kvh * HD + (size_t)key0 * kv_row;
-    const __half *vbase = v_cache + (size_t)seq * seq_stride + (size_t)kvh * HD + (size_t)key0 * kv_row;
+    // contiguous caches: the sequence's own; paged: the tile is one page of the pool (a page holds a tile's 128 rows)
+    const size_t tile_off = block_table ? (size_t)min(max(block_table[(size_t)seq * table_stride + split], 0), n_pages - 1) * kAttnTile * kv_row
+                                        : (size_t)seq * seq_stride + (size_t)key0 * kv_row;
+    const __half *kbase = k_cache + (size_t)kvh * HD + tile_off;
+    const __half *vbase = v_cache + (size_t)kvh * HD + tile_off;
     const int tile_keys = min(kAttnTile, n_keys - key0);
     // Two ways to fetch the tile.  BULK (many CTAs per SM over the launch: a batch of sequences): one bulk copy per row
     // (head_dim halves, contiguous in the cache) into the padded tile, thread r < 128 the key row r, thread 128 + r the
@@ -835,11 +847,12 @@ cudaError_t launch_rope(const float *x, const int32_t *positions, float *dst, in
 
 cudaError_t launch_rope_write_kv(float *q, const float *k, const float *v, const int32_t *positions, void *k_cache, void *v_cache, int rows,
                                  int n_head, int n_kv, int head_dim, float theta, int neox, int rows_per_seq, size_t seq_stride,
-                                 const DeviceInfo &dev, cudaStream_t st, int write_pos) {
+                                 const DeviceInfo &dev, cudaStream_t st, int write_pos, const int32_t *block_table, int table_stride, int n_pages) {
     if (rows <= 0 || n_head <= 0 || n_kv <= 0 || head_dim <= 0 || (head_dim & 1) || rows_per_seq <= 0) return cudaErrorInvalidValue;
     const size_t total = (size_t)rows * (n_head + 2 * n_kv) * (head_dim / 2);
     return launch_pdl(rope_write_kv_kernel, dim3(grid_for(total, 256, dev)), dim3(256), 0, st, q, k, v, positions, (__half *)k_cache,
-                      (__half *)v_cache, rows, n_head, n_kv, head_dim, theta, neox, rows_per_seq, seq_stride, write_pos);
+                      (__half *)v_cache, rows, n_head, n_kv, head_dim, theta, neox, rows_per_seq, seq_stride, write_pos, block_table, table_stride,
+                      n_pages);
 }
 
 cudaError_t launch_write_kv_f16(const float *src, void *cache_at_pos, size_t n, const DeviceInfo &dev, cudaStream_t st) {
@@ -855,37 +868,42 @@ size_t attention_workspace_bytes(int q_rows, int n_head, int head_dim, int max_k
 template <int HD, int G>
 static cudaError_t launch_attn_one(dim3 grid, cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *po, float *pml, int rows,
                                    int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride, uint32_t *status, bool bulk,
-                                   const int32_t *seq_pos) {
+                                   const int32_t *seq_pos, const int32_t *block_table, int table_stride, int n_pages) {
     // the tile needs more than the default 48 KB of dynamic shared memory; the attribute is per device, so it is set
     // on every launch (cheap, allocates nothing) rather than remembered per process
     auto kernel = bulk ? attn_split_kernel<HD, G, true> : attn_split_kernel<HD, G, false>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<HD>::kBytes);
     if (e != cudaSuccess) return e;
     return launch_pdl(kernel, grid, dim3(kAttnThreads), (size_t)AttnSmem<HD>::kBytes, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits,
-                      seq_stride, status, seq_pos);
+                      seq_stride, status, seq_pos, block_table, table_stride, n_pages);
 }
 
 template <int HD>
 static cudaError_t launch_attn_hd(int group, dim3 grid, cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *po, float *pml,
                                   int rows, int n_head, int n_kv, int pos, float scale, int n_splits, size_t seq_stride, uint32_t *status, bool bulk,
-                                  const int32_t *seq_pos) {
+                                  const int32_t *seq_pos, const int32_t *block_table, int table_stride, int n_pages) {
     switch (group) {
-        case 1: return launch_attn_one<HD, 1>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
-        case 2: return launch_attn_one<HD, 2>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
-        case 4: return launch_attn_one<HD, 4>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
-        case 8: return launch_attn_one<HD, 8>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
+        case 1: return launch_attn_one<HD, 1>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos, block_table,
+                                                  table_stride, n_pages);
+        case 2: return launch_attn_one<HD, 2>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos, block_table,
+                                                  table_stride, n_pages);
+        case 4: return launch_attn_one<HD, 4>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos, block_table,
+                                                  table_stride, n_pages);
+        case 8: return launch_attn_one<HD, 8>(grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos, block_table,
+                                                  table_stride, n_pages);
         default: return cudaErrorInvalidValue;
     }
 }
 
 cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_cache, float *dst, void *workspace, int n_seq, int rows, int n_head,
                              int n_kv, int head_dim, float scale, int pos, size_t seq_stride, int sm_count, cudaStream_t st, uint32_t *status, int8_t *qs, float *d,
-                             int32_t *sums, int32_t *sums16, const int32_t *seq_pos) {
+                             int32_t *sums, int32_t *sums16, const int32_t *seq_pos, const int32_t *block_table, int table_stride, int n_pages) {
     if (n_seq <= 0 || rows <= 0 || n_head <= 0 || n_kv <= 0 || n_head % n_kv || pos < 0) return cudaErrorInvalidValue;
     const int max_keys = pos + rows, n_splits = (max_keys + kAttnTile - 1) / kAttnTile, q_rows = n_seq * rows;
     if (n_kv > 65535 || q_rows > 65535) return cudaErrorInvalidValue;
     // the tiles are fetched with 16-byte-granular bulk copies of whole rows
     if (((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 || seq_stride % 8 || ((size_t)n_kv * head_dim) % 8) return cudaErrorInvalidValue;
+    if (block_table && (n_pages < 1 || table_stride < n_splits)) return cudaErrorInvalidValue;
     float *po = static_cast<float *>(workspace);
     float *pml = po + (size_t)q_rows * n_head * n_splits * head_dim;
     const dim3 grid(n_splits, n_kv, q_rows);
@@ -895,9 +913,11 @@ cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_
     const bool bulk = (size_t)n_splits * n_kv * q_rows > (size_t)6 * (sm_count > 0 ? sm_count : 148);
     const int g = n_head / n_kv;
     if (head_dim == 128)
-        e = launch_attn_hd<128>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
+        e = launch_attn_hd<128>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos, block_table, table_stride,
+                                n_pages);
     else if (head_dim == 64)
-        e = launch_attn_hd<64>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos);
+        e = launch_attn_hd<64>(g, grid, st, q, kc, vc, po, pml, rows, n_head, n_kv, pos, scale, n_splits, seq_stride, status, bulk, seq_pos, block_table, table_stride,
+                               n_pages);
     else
         return cudaErrorInvalidValue;
     if (e != cudaSuccess) return e;

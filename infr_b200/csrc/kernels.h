@@ -145,14 +145,14 @@ cudaError_t launch_rope(const float *x, const int32_t *positions, float *dst, in
                         int neox, const DeviceInfo &dev, cudaStream_t st);
 cudaError_t launch_rope_write_kv(float *q, const float *k, const float *v, const int32_t *positions, void *k_cache, void *v_cache, int rows,
                                  int n_head, int n_kv, int head_dim, float theta, int neox, int rows_per_seq, size_t seq_stride,
-                                 const DeviceInfo &dev, cudaStream_t st, int write_pos = -1);
+                                 const DeviceInfo &dev, cudaStream_t st, int write_pos = -1, const int32_t *block_table = nullptr, int table_stride = 0, int n_pages = 0);
 cudaError_t launch_write_kv_f16(const float *src, void *cache_at_pos, size_t n, const DeviceInfo &dev, cudaStream_t st);
 size_t attention_workspace_bytes(int q_rows, int n_head, int head_dim, int max_keys);
 // With qs != nullptr the merged rows are quantised (256-element blocks) instead of stored to dst.
 cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_cache, float *dst, void *workspace, int n_seq, int rows, int n_head,
                              int n_kv, int head_dim, float scale, int pos, size_t seq_stride, int sm_count, cudaStream_t st, uint32_t *status,
                              int8_t *qs = nullptr, float *d = nullptr, int32_t *sums = nullptr, int32_t *sums16 = nullptr,
-                             const int32_t *seq_pos = nullptr);
+                             const int32_t *seq_pos = nullptr, const int32_t *block_table = nullptr, int table_stride = 0, int n_pages = 0);
 // Producers that end in the activation quantiser (256-element blocks; sums16 may be null).
 cudaError_t launch_rms_norm_q8(const float *a, const float *b, float *sum_dst, const float *w, int rows, int dim, float eps, int8_t *qs, float *d,
                                int32_t *sums, int32_t *sums16, cudaStream_t st);

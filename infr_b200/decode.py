@@ -51,13 +51,16 @@ class DecodeStep:
     output norm.  `k_cache` / `v_cache` are per-layer Buffers holding `n_seq` caches of `max_ctx` rows each."""
 
     def __init__(self, be, shape: LlamaShape, n_seq: int, max_ctx: int, layers, out_norm, head, head_dtype, k_cache, v_cache,
-                 sub=None, reduce=None, argmax: bool = True):
+                 sub=None, reduce=None, argmax: bool = True, pages=None):
         """Tensor-parallel use: `shape` holds this rank's share (n_head, n_kv, ffn and vocab divided by the ranks, hidden
         whole), `reduce(buffer, n_floats)` sums the row-parallel Linears' partial results (attention output, FFN down)
         over the ranks in place, `sub` optionally supplies the buffer those results live in (e.g. memory a collective
         library can address), and `argmax=False` leaves the rank's slice of the logits for the caller to gather."""
         self.be, self.s, self.n_seq, self.max_ctx = be, shape, n_seq, max_ctx
         self.reduce, self.do_argmax = reduce, argmax
+        # paged caches: pages = (block_table Buffer int32 [n_seq][stride], stride, n_pages); k_cache / v_cache are then
+        # per-layer pools of n_pages pages of 128 rows shared by the sequences (fused forms only)
+        self.pages = pages
         self.layers, self.out_norm, self.head, self.head_dtype = layers, out_norm, head, head_dtype
         self.k_cache, self.v_cache = k_cache, v_cache
         s, b = shape, n_seq
@@ -133,10 +136,17 @@ class DecodeStep:
         for li, L in enumerate(self.layers):
             pair(dt(L, "wq"), L["wq"], self.q, s.q_dim, dt(L, "wk"), L["wk"], self.k, s.kv_dim, h)  # q and k: one launch
             gemv(dt(L, "wv"), L["wv"], self.v, h, s.kv_dim)
-            be.rope_write_kv(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], rows=1, pos=pos,
-                             n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
-            be.attention_q8(self.q, self.k_cache[li], self.v_cache[li], *a8, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
-                            head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride, seq_pos=self._seq_pos)
+            if self.pages:
+                tbl, stride, n_pages = self.pages
+                be.rope_write_kv_paged(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], tbl, stride, n_pages, rows=1,
+                                       pos=pos, n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b)
+                be.attention_paged(self.q, self.k_cache[li], self.v_cache[li], tbl, stride, n_pages, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
+                                   head_dim=s.head_dim, scale=scale, n_seq=b, seq_pos=self._seq_pos, q8=a8)
+            else:
+                be.rope_write_kv(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], rows=1, pos=pos,
+                                 n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
+                be.attention_q8(self.q, self.k_cache[li], self.v_cache[li], *a8, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
+                                head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride, seq_pos=self._seq_pos)
             gemv(dt(L, "wo"), L["wo"], self.sub, s.q_dim, h)
             if self.reduce:
                 self.reduce(self.sub, b * h)
@@ -194,11 +204,18 @@ class DecodeStep:
             dt = self._dt
             lin_many(self.hn, h, [(dt(L, "wq"), L["wq"], self.q, s.q_dim), (dt(L, "wk"), L["wk"], self.k, s.kv_dim),
                                   (dt(L, "wv"), L["wv"], self.v, s.kv_dim)])
-            if fused:
+            if fused and self.pages:
+                tbl, stride, n_pages = self.pages
+                be.rope_write_kv_paged(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], tbl, stride, n_pages, rows=1,
+                                       pos=pos, n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b)
+                n += 1
+            elif fused:
                 be.rope_write_kv(self.q, self.k, self.v, self.positions, self.k_cache[li], self.v_cache[li], rows=1, pos=pos,
                                  n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
                 n += 1
             else:
+                if self.pages:
+                    raise ValueError("paged caches run in the fused forms (Op::WriteKv addresses one contiguous cache)")
                 be.rope(self.k, self.positions, self.k_rot, b, s.n_kv, s.head_dim, s.head_dim, s.theta)
                 be.rope(self.q, self.positions, self.q, b, s.n_head, s.head_dim, s.head_dim, s.theta)
                 n += 2
@@ -210,8 +227,13 @@ class DecodeStep:
                         row.close()
                         one.close()
                         n += 1
-            be.attention(self.q, self.k_cache[li], self.v_cache[li], self.attn, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
-                         head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride, seq_pos=self._seq_pos)
+            if self.pages:
+                tbl, stride, n_pages = self.pages
+                be.attention_paged(self.q, self.k_cache[li], self.v_cache[li], tbl, stride, n_pages, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
+                                   head_dim=s.head_dim, scale=scale, n_seq=b, seq_pos=self._seq_pos, dst=self.attn)
+            else:
+                be.attention(self.q, self.k_cache[li], self.v_cache[li], self.attn, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
+                             head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride, seq_pos=self._seq_pos)
             lin(dt(L, "wo"), L["wo"], self.attn, self.sub, s.q_dim, h)
             n += 2
             if self.reduce:

@@ -174,3 +174,56 @@ def test_sequences_at_positions_of_their_own(backend, oracle):
             keep[[int(positions[0]), MAX_CTX + int(positions[1])]] = False
             np.testing.assert_array_equal(g[keep], vc[li][keep])
             assert (g[~keep] != vc[li][~keep]).any()
+
+
+def test_paged_caches_give_what_contiguous_caches_give(backend):
+    """The same sequences, their cache rows scattered over a pool of 128-row pages through a page table: same logits, same
+    tokens, bit for bit, in the fused and the int8-producer form; the new rows land in the right pages."""
+    s = LlamaShape(n_layer=2, hidden=512, n_head=4, n_kv=2, head_dim=128, ffn=1024, vocab=400)
+    b, ctx = 3, 384  # three pages per sequence
+    positions = np.array([300, 129, 5], np.int32)
+    layers = []
+    for li in range(s.n_layer):
+        d = {name: backend.from_numpy(synth.weight(dt, o, i, seed=4000 + 16 * li + t), infr_b200.USAGE_WEIGHTS)
+             for t, (name, dt, o, i) in enumerate(s.linears())}
+        d["attn_norm"] = backend.from_numpy((1.0 + 0.02 * synth.normal(4100 + li, (s.hidden,))).astype(np.float32))
+        d["ffn_norm"] = backend.from_numpy((1.0 + 0.02 * synth.normal(4200 + li, (s.hidden,))).astype(np.float32))
+        layers.append(d)
+    out_norm = backend.from_numpy((1.0 + 0.02 * synth.normal(4300, (s.hidden,))).astype(np.float32))
+    head = backend.from_numpy(synth.weight(Q4K, s.vocab, s.hidden, seed=4301), infr_b200.USAGE_WEIGHTS)
+    kc = [synth.normal(80 + li, (b * ctx, s.kv_dim)).astype(np.float16).view(np.uint16) for li in range(s.n_layer)]
+    vc = [synth.normal(90 + li, (b * ctx, s.kv_dim)).astype(np.float16).view(np.uint16) for li in range(s.n_layer)]
+    hidden = synth.normal(95, (b, s.hidden))
+    # page table: sequence sq's page i -> a scrambled page of a pool with spare pages
+    n_pages, stride = 13, 4
+    perm = np.random.default_rng(7).permutation(n_pages)
+    table = np.full((b, stride), -1, np.int32)
+    for sq in range(b):
+        for i in range(3):
+            table[sq, i] = perm[sq * 3 + i]
+    table[:, 3] = 10 ** 6  # an entry nobody should need: out of range on purpose
+
+    def pool(c):
+        p = np.zeros((n_pages * 128, s.kv_dim), np.uint16)
+        for sq in range(b):
+            for i in range(3):
+                p[table[sq, i] * 128:(table[sq, i] + 1) * 128] = c[sq * ctx + i * 128: sq * ctx + (i + 1) * 128]
+        return p
+    for fused, q8 in ((True, False), (True, True)):
+        ref = DecodeStep(backend, s, b, ctx, layers, out_norm, head, Q4K, [backend.from_numpy(c) for c in kc], [backend.from_numpy(c) for c in vc])
+        ref.set_inputs(hidden, positions)
+        ref.run(int(positions.max()), fused=fused, q8_fused=q8)
+        kp, vp = [backend.from_numpy(pool(c)) for c in kc], [backend.from_numpy(pool(c)) for c in vc]
+        pg = DecodeStep(backend, s, b, ctx, layers, out_norm, head, Q4K, kp, vp, pages=(backend.from_numpy(table), stride, n_pages))
+        pg.set_inputs(hidden, positions)
+        pg.run(int(positions.max()), fused=fused, q8_fused=q8)
+        np.testing.assert_array_equal(backend.download(pg.logits, np.uint32), backend.download(ref.logits, np.uint32))
+        np.testing.assert_array_equal(backend.download(pg.tok, np.uint32), backend.download(ref.tok, np.uint32))
+        for li in range(s.n_layer):
+            want = pool(backend.download(ref.v_cache[li], np.uint16).reshape(b * ctx, s.kv_dim))
+            np.testing.assert_array_equal(backend.download(vp[li], np.uint16).reshape(n_pages * 128, s.kv_dim), want)
+            want_k = pool(backend.download(ref.k_cache[li], np.uint16).reshape(b * ctx, s.kv_dim))
+            np.testing.assert_array_equal(backend.download(kp[li], np.uint16).reshape(n_pages * 128, s.kv_dim), want_k)
+    with pytest.raises(infr_b200.BackendError):  # a table too narrow for the positions
+        backend.attention_paged(ref.q, kp[0], vp[0], backend.from_numpy(table), 2, n_pages, rows=1, pos=300, n_head=s.n_head, n_kv=s.n_kv,
+                                head_dim=s.head_dim, scale=1.0, n_seq=b, dst=ref.attn)

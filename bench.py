@@ -575,7 +575,12 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
     dev = torch.device("cuda", local)
     N = world
     full = LlamaShape()
-    s = LlamaShape(n_head=full.n_head // N, n_kv=full.n_kv // N, ffn=full.ffn // N, vocab=full.vocab // N)
+    # the FFN is cut in whole 2048-column chunks while there are enough of them (14336 = 7 chunks: 4 + 3 on two ranks,
+    # 2 + 2 + 2 + 1 on four): a Q6_K `down` whose rows are whole chunks keeps the wide GEMV (rows of 14336 / N columns
+    # are 5880 or 2940 bytes: no TMA stride), and an uneven cut costs less than the 8-row walk it avoids
+    ffn_unit = 2048 if full.ffn // 2048 >= N else 256
+    ffn_of = lambda r, n: shard.col_range(Q4K, full.ffn, r, n, unit=ffn_unit)
+    s = LlamaShape(n_head=full.n_head // N, n_kv=full.n_kv // N, ffn=ffn_of(rank, N)[1] - ffn_of(rank, N)[0], vocab=full.vocab // N)
     max_ctx = pos + 8
     row_parallel = {"wo", "down"}  # input columns split, partial sums all-reduced
     host_full = {name: synth.random_blocks(dt, o * i, 300 + k) for k, (name, dt, o, i) in enumerate(full.linears())}
@@ -587,9 +592,15 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
     def build(shape, n_ranks, r):
         """Device buffers of rank r's share of the model split n_ranks ways (n_ranks = 1: the whole model)."""
         masters = {}
+        f0, f1 = ffn_of(r, n_ranks)
         for name, dt, o, i in full.linears():
-            if name in row_parallel:
+            if name == "down":
+                w, _, _ = shard.col_shard(dt, host_full[name], o, i, r, n_ranks, unit=ffn_unit)
+            elif name in row_parallel:
                 w, _, _ = shard.col_shard(dt, host_full[name], o, i, r, n_ranks, unit=256)
+            elif name in ("gate", "up"):  # the rows that feed this rank's columns of `down`
+                bpr = synth.row_bytes(dt, i)
+                w = np.ascontiguousarray(host_full[name]).reshape(-1)[f0 * bpr:f1 * bpr]
             else:
                 w, _, _ = shard.row_shard(dt, host_full[name], o, i, r, n_ranks)
             masters[name] = be.from_numpy(w, infr_b200.USAGE_WEIGHTS)

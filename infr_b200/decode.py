@@ -85,6 +85,11 @@ class DecodeStep:
     def _dt(self, layer: dict, name: str) -> int:
         return layer.get("dtypes", self._MIX).get(name, self._MIX[name])
 
+    def _q8_formats(self) -> bool:
+        """Every Linear takes activations quantised per 256 elements (Q4_K, Q6_K); Q2_0 wants them per 32."""
+        names = ("wq", "wk", "wv", "wo", "gate", "up", "down")
+        return all(self._dt(L, n) in (Q4K, Q6K) for L in self.layers for n in names) and self.head_dtype in (Q4K, Q6K)
+
     def _wide_ok(self) -> bool:
         """9..32 sequences: every Linear can take pre-quantised rows (the wide GEMV: Q4_K, or Q6_K rows of whole
         2048-element chunks), so the step keeps its activations in int8 between ops as a step over one sequence does."""
@@ -112,7 +117,8 @@ class DecodeStep:
         # sequences at positions of their own: attention reads them from the device, `pos` bounds them
         self._seq_pos = None if getattr(self, "uniform_pos", True) else self.positions
         if q8_fused is None:
-            q8_fused = fused and (b <= 8 or self._wide_ok()) and s.hidden % 256 == 0 and s.ffn % 256 == 0 and s.q_dim % 256 == 0
+            q8_fused = (fused and (b <= 8 or self._wide_ok()) and self._q8_formats() and s.hidden % 256 == 0 and s.ffn % 256 == 0 and
+                        s.q_dim % 256 == 0)
         return self._run_q8(pos) if q8_fused else self._run_f32(pos, fused)
 
     def _run_q8(self, pos: int) -> int:

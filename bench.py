@@ -556,7 +556,7 @@ def _tp_decode(be, infr_b200, dist, rank, world, local, steps, warmup):
             "not_included": "attention, norms, RoPE, sampling: see decode_step"}
 
 
-def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmup, pos=4096):
+def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmup, pos=4096, exchange="fused"):
     """Tensor-parallel form of the WHOLE 8B-shape decode step (section of the reference: tp.rs:7-21): q/k/v by heads,
     attention by KV head on the rank's own slice of the KV cache, gate/up by FFN slice, o and down by input columns
     with an all-reduce of the [batch, 4096] result after each (the library's peer-memory kernel while it fits its
@@ -667,8 +667,11 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
         reduce = lambda buf, n: be.all_reduce(comm, buf, n)
     else:
         reduce = lambda buf, n: dist.all_reduce(sub_t)
+    # exchange == "fused": at most 8 sequences push from the GEMV epilogues and sum in the norms (no exchange kernel);
+    # "kernel": the stand-alone all-reduce after every row-parallel GEMV
     step = DecodeStep(be, s, batch, max_ctx, mine["layers"], mine["norm"], mine["head"], Q4K, mine["kc"], mine["vc"], sub=sub, reduce=reduce,
-                      argmax=N == 1)
+                      argmax=N == 1, comm=comm if exchange == "fused" else None)
+    pushed = N > 1 and step._push_ok()
     hidden0 = be.from_numpy(hidden_h)
     step.set_inputs(hidden_h, pos)
     logits_t = None
@@ -734,7 +737,7 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
         b_.close()
     return {"workload": f"tensor-parallel 8B-shape decode step, batch {batch}, KV context {pos}, {N} GPU(s): heads, FFN and vocabulary "
                         f"split over the ranks ({mine['w_bytes'] / 1e9:.2f} GB of weights per rank), {2 * s.n_layer if N > 1 else 0} all-reduces of "
-                        f"{n_red * 4 // 1024} KB ({'peer-memory kernel' if comm is not None else 'NCCL' if N > 1 else 'none'}) + 1 NCCL all-gather",
+                        f"{n_red * 4 // 1024} KB ({'pushed from the GEMV epilogues, summed in the norms: no exchange kernel' if pushed else 'peer-memory kernel' if comm is not None else 'NCCL' if N > 1 else 'none'}) + 1 NCCL all-gather",
             "us_per_step": us, "tok_per_s": batch / (us * 1e-6), "ops_per_step": n_ops, "mode": mode, "scaling": "strong",
             "parity": parity}
 
@@ -999,6 +1002,8 @@ def run_b200(args):
         tp = _tp_decode(be, infr_b200, dist, rank, world, local, 10, 3)
         ep = _ep_moe(be, infr_b200, dist, rank, world, local, 20, 3)
         tps = [_tp_decode_step(be, infr_b200, dist, rank, world, local, b_, 10, 3) for b_ in (1, 32)] if world > 1 else None
+        if tps:  # batch 1 again with the stand-alone exchange kernel, to show what the fused form saves
+            tps.append(_tp_decode_step(be, infr_b200, dist, rank, world, local, 1, 10, 3, exchange="kernel"))
         dps = None
         if world > 1:
             # data-parallel replicas: every rank holds the whole model and decodes its own 32 sequences (no exchange)

@@ -41,7 +41,7 @@ EXPORTED_SYMBOLS = [
     "infr_cuda_graph_free", "infr_cuda_timer_start", "infr_cuda_timer_stop", "infr_cuda_flush_l2",
     "infr_cuda_launch_count", "infr_cuda_tensor_peak_i8",
     "infr_cuda_rms_norm", "infr_cuda_add_rms_norm", "infr_cuda_rope", "infr_cuda_write_kv", "infr_cuda_attention", "infr_cuda_rope_write_kv",
-    "infr_cuda_gated_act", "infr_cuda_add", "infr_cuda_argmax", "infr_cuda_add_rms_norm_q8", "infr_cuda_gated_act_q8", "infr_cuda_attention_q8",
+    "infr_cuda_gated_act", "infr_cuda_add", "infr_cuda_argmax", "infr_cuda_add_rms_norm_q8", "infr_cuda_gemv_q8_push", "infr_cuda_add_rms_norm_q8_pull", "infr_cuda_gated_act_q8", "infr_cuda_attention_q8",
     "infr_cuda_attention_seqpos", "infr_cuda_attention_seqpos_q8", "infr_cuda_attention_paged", "infr_cuda_rope_write_kv_paged",
     "infr_gguf_open", "infr_gguf_close", "infr_gguf_version", "infr_gguf_alignment", "infr_gguf_tensor_count", "infr_gguf_tensor_at", "infr_gguf_find",
     "infr_gguf_tensor_data", "infr_gguf_meta_count", "infr_gguf_meta_key", "infr_gguf_meta_type", "infr_gguf_meta_u64", "infr_gguf_meta_f64",
@@ -173,6 +173,8 @@ def load_library() -> C.CDLL:
         "infr_cuda_add": (i32, [vp, vp, vp, vp, u64]),
         "infr_cuda_argmax": (i32, [vp, vp, vp, u32, u32]),
         "infr_cuda_add_rms_norm_q8": (i32, [vp, vp, vp, vp, vp, u32, u32, C.c_float, C.POINTER(_Q8Out)]),
+        "infr_cuda_gemv_q8_push": (i32, [vp, vp, i32, vp, u64, vp, vp, vp, vp, u32, u32, u32]),
+        "infr_cuda_add_rms_norm_q8_pull": (i32, [vp, vp, vp, vp, vp, u32, u32, C.c_float, C.POINTER(_Q8Out)]),
         "infr_cuda_gated_act_q8": (i32, [vp, vp, vp, u32, u32, C.POINTER(_Q8Out)]),
         "infr_cuda_attention_q8": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, C.POINTER(_Q8Out)]),
         "infr_cuda_attention_seqpos": (i32, [vp, C.POINTER(_AttnDesc), vp, vp, vp, vp, vp]),
@@ -631,6 +633,19 @@ class CudaBackend:
         o = self._q8_out(qs, d, sums, sums16)
         self._check(self.L.infr_cuda_add_rms_norm_q8(self.ctx, a.handle, b.handle if b else None, sum_dst.handle if sum_dst else None,
                                                      weight.handle, rows, dim, eps, C.byref(o)))
+
+    def gemv_q8_push(self, comm: "Comm", dtype: int, w: Buffer, qs: Buffer, d: Buffer, sums: Buffer, sums16: Optional[Buffer], m: int, in_f: int,
+                     out_f: int, w_off: int = 0):
+        """gemv_q8 of a row-parallel Linear whose epilogue stores the partial result into every rank's staging (no buffer,
+        no exchange kernel); add_rms_norm_q8_pull must follow."""
+        self._check(self.L.infr_cuda_gemv_q8_push(self.ctx, comm.handle, dtype, w.handle, w_off, qs.handle, d.handle, sums.handle,
+                                                  sums16.handle if sums16 is not None else None, m, in_f, out_f))
+
+    def add_rms_norm_q8_pull(self, comm: "Comm", a: Buffer, sum_dst: Buffer, weight: Buffer, rows: int, dim: int, eps: float, qs: Buffer, d: Buffer,
+                             sums: Buffer, sums16: Optional[Buffer] = None):
+        """add_rms_norm_q8 with b = the sum over the ranks of the results pushed by gemv_q8_push."""
+        o = self._q8_out(qs, d, sums, sums16)
+        self._check(self.L.infr_cuda_add_rms_norm_q8_pull(self.ctx, comm.handle, a.handle, sum_dst.handle, weight.handle, rows, dim, eps, C.byref(o)))
 
     def gated_act_q8(self, gate: Buffer, up: Buffer, rows: int, nff: int, qs: Buffer, d: Buffer, sums: Buffer,
                      sums16: Optional[Buffer] = None):

@@ -82,6 +82,9 @@ public:
     Status comm_connect(infr_cuda_comm *c, const uint8_t *handles);
     Status comm_connect_silent(infr_cuda_comm *c, uint32_t spin_limit);
     Status all_reduce_f32(infr_cuda_comm *c, float *data, uint32_t n);
+    // the exchange without a kernel of its own: pushed by the GEMV's epilogue, summed by the norm that follows
+    Status gemv_q8_push(infr_cuda_comm *c, int dtype, const uint8_t *w, const Q8Dev &a, uint32_t m, uint32_t in_f, uint32_t out_f);
+    Status rms_norm_q8_pull(infr_cuda_comm *c, const float *a, float *sum_dst, const float *w, uint32_t rows, uint32_t dim, float eps, const Q8Dev &out);
     void comm_destroy(infr_cuda_comm *c);
     Status upload(infr_cuda_buf *dst, size_t dst_off, const void *src, size_t bytes);
     Status download(const infr_cuda_buf *src, void *dst, size_t bytes);

@@ -541,6 +541,38 @@ int32_t infr_cuda_add_rms_norm_q8(infr_cuda_ctx *ctx, const infr_cuda_buf *a, co
     return finish(ctx, ctx->be->rms_norm_q8((const float *)pa, (const float *)pb, (float *)ps, (const float *)pw, rows, dim, eps, q8));
 }
 
+int32_t infr_cuda_gemv_q8_push(infr_cuda_ctx *ctx, infr_cuda_comm *comm, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off, const infr_cuda_buf *qs,
+                               const infr_cuda_buf *d, const infr_cuda_buf *sums, const infr_cuda_buf *sums16, uint32_t m, uint32_t in_f,
+                               uint32_t out_f) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (dtype != INFR_DT_Q4K && dtype != INFR_DT_Q6K) return finish(ctx, Status::Err(INFR_E_UNSUPPORTED, "gemv_q8_push: Q4_K and Q6_K weights"));
+    if (in_f == 0 || in_f % 256 || w_off % in_f || m == 0) return finish(ctx, Status::Err(INFR_E_INVALID, "gemv_q8_push: m / in_f / w_off"));
+    uint8_t *pw, *pq, *pd, *ps, *p16 = nullptr;
+    const size_t bpr = (size_t)(in_f / 256) * (size_t)infr::block_bytes(dtype), row0 = (size_t)(w_off / in_f), n = (size_t)m * in_f;
+    Status s;
+    if (!(s = span(w, (row0 + out_f) * bpr, "gemv_q8_push weight", &pw)).ok() || !(s = span(qs, n, "gemv_q8_push qs", &pq)).ok() ||
+        !(s = span(d, n / 256 * 4, "gemv_q8_push d", &pd)).ok() || !(s = span(sums, n / 32 * 4, "gemv_q8_push sums", &ps)).ok())
+        return finish(ctx, s);
+    if (sums16 && !(s = span(sums16, n / 16 * 4, "gemv_q8_push sums16", &p16)).ok()) return finish(ctx, s);
+    infr::Q8Dev a{(const int8_t *)pq, (const float *)pd, (const int32_t *)ps, (const int32_t *)p16, 256};
+    return finish(ctx, ctx->be->gemv_q8_push(comm, dtype, pw + row0 * bpr, a, m, in_f, out_f));
+}
+
+int32_t infr_cuda_add_rms_norm_q8_pull(infr_cuda_ctx *ctx, infr_cuda_comm *comm, const infr_cuda_buf *a, infr_cuda_buf *sum_dst,
+                                       const infr_cuda_buf *weight, uint32_t rows, uint32_t dim, float eps, const infr_q8_out *out) {
+    INFR_CTX_OR_RETURN(ctx);
+    if (rows == 0) return finish(ctx, Status::Err(INFR_E_INVALID, "add_rms_norm_q8_pull: rows must be positive"));
+    infr::Q8Dev q8;
+    Status s = q8_out_args(out, rows, dim, "add_rms_norm_q8_pull output", &q8);
+    if (!s.ok()) return finish(ctx, s);
+    uint8_t *pa, *ps, *pw;
+    const size_t n = (size_t)rows * dim * 4;
+    if (!(s = span(a, n, "add_rms_norm_q8_pull a", &pa)).ok() || !(s = span(weight, (size_t)dim * 4, "add_rms_norm_q8_pull weight", &pw)).ok() ||
+        !(s = span(sum_dst, n, "add_rms_norm_q8_pull sum_dst", &ps)).ok())
+        return finish(ctx, s);
+    return finish(ctx, ctx->be->rms_norm_q8_pull(comm, (const float *)pa, (float *)ps, (const float *)pw, rows, dim, eps, q8));
+}
+
 int32_t infr_cuda_gated_act_q8(infr_cuda_ctx *ctx, const infr_cuda_buf *gate, const infr_cuda_buf *up, uint32_t rows, uint32_t nff,
                                const infr_q8_out *out) {
     INFR_CTX_OR_RETURN(ctx);

@@ -34,6 +34,7 @@ constexpr int kMaxWorld = 8;
 constexpr int kArThreads = 1024;
 constexpr int kArMaxCtas = 64;  // 64 x 1024 float4 = 256 K floats (1 MB) per exchange; one CTA per SM, all resident
 constexpr uint32_t kArSpin = 1u << 22;
+constexpr uint32_t kPushMaxFloats = 8 * 16384;  // a pushed GEMV result: at most 8 rows (1 MB of staged words per rank and parity)
 
 struct ArPeers {
     float *stage[kMaxWorld];     // peer r's staging: [2][world][cap] f32
@@ -105,10 +106,13 @@ struct infr_cuda_comm {
     uint32_t cap = 0;            // floats per slot
     uint8_t *local = nullptr;    // this rank's allocation: staging | flags | ctrl
     size_t stage_bytes = 0, flag_bytes = 0;
+    size_t push_off = 0, total_bytes = 0;  // the pushed GEMVs' staging ([2][world][push_cap] 8-byte words) follows the control words
+    uint32_t push_cap = 0;
     void *peer_base[infr::kMaxWorld] = {};  // mapped allocations of the peers (own entry = local)
     bool connected = false;
     uint32_t spin = infr::kArSpin;  // polls a wait may take before it gives up
     uint8_t *silent = nullptr;      // comm_connect_silent: a stand-in for the peers that nobody ever writes to
+    bool pushed = false;            // a GEMV has pushed its result and the consumer has not been enqueued yet
 };
 
 namespace infr {
@@ -125,7 +129,10 @@ Status CudaBackend::comm_create(int rank, int world, uint32_t max_floats, infr_c
     c->cap = max_floats;
     c->stage_bytes = (size_t)2 * world * max_floats * 4;
     c->flag_bytes = (size_t)2 * kArMaxCtas * world * 4;
-    const size_t total = c->stage_bytes + c->flag_bytes + 256;
+    c->push_off = c->stage_bytes + c->flag_bytes + 256;
+    c->push_cap = max_floats < kPushMaxFloats ? max_floats : kPushMaxFloats;
+    c->total_bytes = c->push_off + (size_t)2 * world * c->push_cap * 8;
+    const size_t total = c->total_bytes;
     Status s = cuda_status(cudaMalloc((void **)&c->local, total), "cudaMalloc(comm)");
     if (s.ok()) s = cuda_status(cudaMemsetAsync(c->local, 0, total, stream_), "cudaMemsetAsync(comm)");
     if (s.ok()) s = cuda_status(cudaStreamSynchronize(stream_), "comm sync");
@@ -174,7 +181,7 @@ Status CudaBackend::comm_connect_silent(infr_cuda_comm *c, uint32_t spin_limit) 
     if (capturing_) return Status::Err(INFR_E_INVALID, "comm_connect_silent during stream capture");
     if (spin_limit == 0 || spin_limit > kArSpin) return Status::Err(INFR_E_INVALID, "comm_connect_silent: poll limit out of range");
     cudaSetDevice(device_);
-    const size_t total = c->stage_bytes + c->flag_bytes + 256;
+    const size_t total = c->total_bytes;
     Status s = cuda_status(cudaMalloc((void **)&c->silent, total), "cudaMalloc(comm stand-in)");
     if (s.ok()) s = cuda_status(cudaMemsetAsync(c->silent, 0, total, stream_), "cudaMemsetAsync(comm stand-in)");
     if (s.ok()) s = cuda_status(cudaStreamSynchronize(stream_), "comm sync");
@@ -189,6 +196,7 @@ Status CudaBackend::comm_connect_silent(infr_cuda_comm *c, uint32_t spin_limit) 
 Status CudaBackend::all_reduce_f32(infr_cuda_comm *c, float *data, uint32_t n) {
     if (!c || !data) return Status::Err(INFR_E_INVALID, "all_reduce: null argument");
     if (!c->connected) return Status::Err(INFR_E_INVALID, "all_reduce: the peers' buffers are not connected");
+    if (c->pushed) return Status::Err(INFR_E_INVALID, "all_reduce: a pushed GEMV result is waiting for its consumer (rms_norm_q8_pull)");
     if (n == 0) return Status::Ok();
     if (n % 4 || n > c->cap || (uintptr_t)data % 16) return Status::Err(INFR_E_INVALID, fmt("all_reduce: %u floats (a multiple of 4, at most %u, 16-byte aligned)", n, c->cap));
     cudaSetDevice(device_);
@@ -212,6 +220,69 @@ Status CudaBackend::all_reduce_f32(infr_cuda_comm *c, float *data, uint32_t n) {
     cfg.numAttrs = 1;
     Status s = cuda_status(cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel, data, n4, c->rank, c->world, c->cap, peers, ctrl, status_dev_, c->spin), "all_reduce");
     if (s.ok()) launches_ += 1;
+    return s;
+}
+
+// The exchange fused into its producer and its consumer: the row-parallel GEMV's epilogue stores the rank's partial
+// result into every rank's staging (slot [rank], the parity of the exchange count), each value in one 8-byte word with
+// the exchange's sequence number; the norm that follows polls the words it adds, sums the slots in rank order and
+// advances the count (the epoch word of the stand-alone all-reduce, so the two forms can alternate on one comm).  No
+// kernel of its own, no fence, no arrival flag; the stores of a tile leave while the other tiles are still computed.
+// A slot is written again two exchanges later: by then every rank has consumed it, because a rank pushes exchange
+// e + 2 only after its consumer of e + 1 has finished, which needed every rank's push of e + 1, which follows that
+// rank's consumer of e in its stream.
+Status CudaBackend::gemv_q8_push(infr_cuda_comm *c, int dtype, const uint8_t *w, const Q8Dev &a, uint32_t m, uint32_t in_f, uint32_t out_f) {
+    if (!c) return Status::Err(INFR_E_INVALID, "gemv_q8_push: null comm");
+    if (!c->connected) return Status::Err(INFR_E_INVALID, "gemv_q8_push: the peers' buffers are not connected");
+    if (c->pushed) return Status::Err(INFR_E_INVALID, "gemv_q8_push: the previous pushed result has not been consumed (rms_norm_q8_pull)");
+    if (m < 1 || m > 8) return Status::Err(INFR_E_INVALID, fmt("gemv_q8_push: m=%u (1..8)", m));
+    if ((uint64_t)m * out_f > c->push_cap)
+        return Status::Err(INFR_E_INVALID, fmt("gemv_q8_push: %u x %u results, the comm stages %u pushed floats", m, out_f, c->push_cap));
+    const bool q4 = dtype == DT_Q4K && in_f && in_f % 256 == 0, q6 = dtype == DT_Q6K && in_f && in_f % 2048 == 0 && a.sums16;
+    if (!q4 && !q6)
+        return Status::Err(INFR_E_UNSUPPORTED, "gemv_q8_push: Q4_K rows of whole blocks or Q6_K rows of whole 2048-element chunks (with the per-16 sums)");
+    if (a.gran != 256) return Status::Err(INFR_E_INVALID, "gemv_q8_push: activations quantised per 256 elements");
+    cudaSetDevice(device_);
+    GemvPush p;
+    memset(&p, 0, sizeof p);
+    for (int r = 0; r < kPushMaxWorld; r++)
+        p.stage[r] = reinterpret_cast<unsigned long long *>(static_cast<uint8_t *>(c->peer_base[r < c->world ? r : c->rank]) + c->push_off);
+    p.ctrl = reinterpret_cast<const uint32_t *>(c->local + c->stage_bytes + c->flag_bytes);
+    p.cap = c->push_cap;
+    p.world = c->world;
+    p.rank = c->rank;
+    const cudaError_t e = q4 ? launch_gemv_q4k_mma(w, &a, nullptr, nullptr, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_, &p)
+                             : launch_gemv_q6_mma(w, a, nullptr, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_, &p);
+    if (e == cudaErrorInvalidValue) return Status::Err(INFR_E_UNSUPPORTED, "gemv_q8_push: the matrix-unit GEMV does not take this shape");
+    Status s = cuda_status(e, "gemv_q8_push");
+    if (s.ok()) {
+        launches_++;
+        c->pushed = true;
+    }
+    return s;
+}
+
+Status CudaBackend::rms_norm_q8_pull(infr_cuda_comm *c, const float *a, float *sum_dst, const float *w, uint32_t rows, uint32_t dim, float eps,
+                                     const Q8Dev &out) {
+    if (!c) return Status::Err(INFR_E_INVALID, "rms_norm_q8_pull: null comm");
+    if (!c->pushed) return Status::Err(INFR_E_INVALID, "rms_norm_q8_pull: no pushed GEMV result is waiting (gemv_q8_push comes first)");
+    if (rows < 1 || dim == 0 || dim % 256 || (uint64_t)rows * dim > c->push_cap)
+        return Status::Err(INFR_E_INVALID, fmt("rms_norm_q8_pull: %u rows of %u (a multiple of 256; the comm stages %u pushed floats)", rows, dim, c->push_cap));
+    cudaSetDevice(device_);
+    PullArgs p;
+    p.stage = reinterpret_cast<const unsigned long long *>(c->local + c->push_off);
+    p.ctrl = reinterpret_cast<uint32_t *>(c->local + c->stage_bytes + c->flag_bytes);
+    p.cap = c->push_cap;
+    p.spin = c->spin;
+    p.world = c->world;
+    p.status = status_dev_;
+    Status s = cuda_status(launch_rms_norm_q8_pull(a, sum_dst, w, (int)rows, (int)dim, eps, const_cast<int8_t *>(out.qs), const_cast<float *>(out.d),
+                                                   const_cast<int32_t *>(out.sums), const_cast<int32_t *>(out.sums16), p, stream_),
+                           "rms_norm_q8_pull");
+    if (s.ok()) {
+        launches_++;
+        c->pushed = false;
+    }
     return s;
 }
 

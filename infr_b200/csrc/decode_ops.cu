@@ -651,6 +651,12 @@ __device__ __forceinline__ void quantize_block256(const float4 v[2], int lane, s
     if (lane == 0) d[row * (k / 256) + chunk] = dd;
 }
 
+// Sum of squares of four values with every product and sum rounded on its own (no fused multiply-add): two kernels
+// that share this get the same bits whatever the compiler does around it, and it is how the CPU forms the sum.
+__device__ __forceinline__ float sumsq4(const float4 v) {
+    return __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(v.x, v.x), __fmul_rn(v.y, v.y)), __fmul_rn(v.z, v.z)), __fmul_rn(v.w, v.w));
+}
+
 // RMSNorm (optionally of a + b, written to sum_dst) whose output goes straight to int8; dim % 256 == 0.
 // Warp c owns the 256-element blocks c, c + warps, ...; with one block per warp (dim <= 256 * warps, the launcher's
 // choice up to dim 8192) the row stays in registers between the sum of squares and the scaling.
@@ -684,7 +690,7 @@ __global__ void __launch_bounds__(1024) rms_norm_q8_kernel(const float *a, const
                 v.x += u.x, v.y += u.y, v.z += u.z, v.w += u.w;
                 *reinterpret_cast<float4 *>(sum_dst + base + e) = v;
             }
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            ss = __fadd_rn(ss, sumsq4(v));
             x[h] = v;
         }
     }
@@ -715,6 +721,100 @@ __global__ void __launch_bounds__(1024) rms_norm_q8_kernel(const float *a, const
         } else {
 #pragma unroll
             for (int h = 0; h < 2; h++) *reinterpret_cast<float4 *>(dst + base + chunk * 256 + h * 128 + lane * 4) = v[h];
+        }
+    }
+}
+
+// The consumer of a pushed row-parallel GEMV (GemvPush): row = a + sum over ranks of the partial results that the
+// ranks' GEMV epilogues stored into this rank's staging, summed in rank order from zero (the order of the stand-alone
+// all-reduce, so both forms give the same bits), written to sum_dst, then RMSNorm and the quantiser.  Every staged word
+// carries its value and the exchange's sequence number: a thread polls, bounded, the four words of each rank that it
+// is about to add, so nothing waits for data it does not read.  A thread whose poll runs out adds nothing and raises
+// the status word.  The grid's last CTA opens the next exchange.  One CTA per row, dim % 256 == 0.
+__device__ __forceinline__ void ld_words2(const unsigned long long *p, unsigned long long &a, unsigned long long &b) {
+    asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+__global__ void __launch_bounds__(1024) rms_norm_q8_pull_kernel(const float *a, float *sum_dst, const float *__restrict__ w, int dim, float eps,
+                                                                int8_t *__restrict__ qs, float *__restrict__ d, int32_t *__restrict__ sums,
+                                                                int32_t *__restrict__ sums16, PullArgs pull) {
+    __shared__ float s_part[32];
+    __shared__ float s_scale;
+    pdl_go();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, chunks = dim / 256;
+    const bool in_regs = chunks <= nw;
+    // the norm weights do not depend on the previous kernel: fetch them before waiting for it
+    float4 g[2];
+    if (in_regs && warp < chunks) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) g[h] = *reinterpret_cast<const float4 *>(w + warp * 256 + h * 128 + lane * 4);
+    }
+    pdl_wait();
+    const uint32_t done = *reinterpret_cast<volatile uint32_t *>(pull.ctrl);
+    const uint32_t par = done & 1u, want = done + 1u;
+    const size_t base = (size_t)blockIdx.x * dim;
+    float4 x[2];
+    float ss = 0.f;
+    for (int chunk = warp; chunk < chunks; chunk += nw) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int e = chunk * 256 + h * 128 + lane * 4;
+            float4 v = *reinterpret_cast<const float4 *>(a + base + e);  // the residual row does not depend on the peers
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            bool all = true;
+            for (int r = 0; r < pull.world; r++) {
+                const unsigned long long *src = pull.stage + ((size_t)par * pull.world + r) * pull.cap + base + e;
+                unsigned long long w0, w1, w2, w3;
+                uint32_t it = 0;
+                bool ok;
+                do {
+                    ld_words2(src, w0, w1);
+                    ld_words2(src + 2, w2, w3);
+                    ok = (uint32_t)(w0 >> 32) == want && (uint32_t)(w1 >> 32) == want && (uint32_t)(w2 >> 32) == want && (uint32_t)(w3 >> 32) == want;
+                } while (!ok && ++it < pull.spin);
+                all = all && ok;
+                acc.x += __uint_as_float((uint32_t)w0), acc.y += __uint_as_float((uint32_t)w1);
+                acc.z += __uint_as_float((uint32_t)w2), acc.w += __uint_as_float((uint32_t)w3);
+            }
+            if (all)
+                v.x += acc.x, v.y += acc.y, v.z += acc.z, v.w += acc.w;
+            else
+                atomicExch(pull.status, 11u);
+            *reinterpret_cast<float4 *>(sum_dst + base + e) = v;
+            ss = __fadd_rn(ss, sumsq4(v));
+            x[h] = v;
+        }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) s_part[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? s_part[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) s_scale = 1.0f / sqrtf(t / (float)dim + eps);
+    }
+    __syncthreads();
+    const float s = s_scale;
+    for (int chunk = warp; chunk < chunks; chunk += nw) {
+        float4 v[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int e = chunk * 256 + h * 128 + lane * 4;
+            if (!in_regs) {
+                x[h] = *reinterpret_cast<const float4 *>(sum_dst + base + e);  // re-read by the warp that wrote it
+                g[h] = *reinterpret_cast<const float4 *>(w + e);
+            }
+            v[h] = make_float4(x[h].x * s * g[h].x, x[h].y * s * g[h].y, x[h].z * s * g[h].z, x[h].w * s * g[h].w);
+        }
+        quantize_block256(v, lane, blockIdx.x, dim, chunk, qs, d, sums, sums16);
+    }
+    // every CTA has read the count and its words: the last one opens the next exchange
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(pull.ctrl + 1, 1u) == gridDim.x - 1) {
+            pull.ctrl[1] = 0;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(pull.ctrl) = done + 1u;
         }
     }
 }
@@ -931,6 +1031,14 @@ cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_
                           (const float *)pml, n_head, head_dim, n_splits, dst, (int8_t *)nullptr, (float *)nullptr, (int32_t *)nullptr,
                           (int32_t *)nullptr);
     return launch_pdl(attn_combine_kernel, dim3(q_rows * n_head), dim3(head_dim), 0, st, (const float *)po, (const float *)pml, dst, head_dim, n_splits);
+}
+
+cudaError_t launch_rms_norm_q8_pull(const float *a, float *sum_dst, const float *w, int rows, int dim, float eps, int8_t *qs, float *d,
+                                    int32_t *sums, int32_t *sums16, const PullArgs &pull, cudaStream_t st) {
+    if (rows <= 0 || dim <= 0 || dim % 256 || pull.world < 1 || pull.world > kPushMaxWorld) return cudaErrorInvalidValue;
+    int threads = dim / 256 * 32;
+    threads = threads > 1024 ? 1024 : threads;
+    return launch_pdl(rms_norm_q8_pull_kernel, dim3(rows), dim3(threads), 0, st, a, sum_dst, w, dim, eps, qs, d, sums, sums16, pull);
 }
 
 cudaError_t launch_rms_norm_q8(const float *a, const float *b, float *sum_dst, const float *w, int rows, int dim, float eps, int8_t *qs, float *d,

@@ -34,6 +34,18 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// ---- epilogue of a GEMV that pushes its result to the peers (GemvPush) ----
+// One value of the result: slot [rank] of the exchange's parity on every rank, value and sequence number in one
+// aligned 8-byte store.  The loop bound is a constant so that the pointer table is read from the kernel's parameters
+// with constant indices.
+__device__ __forceinline__ void push_store(const GemvPush &p, uint32_t done, size_t idx, float v) {
+    const size_t off = ((size_t)(done & 1u) * p.world + p.rank) * p.cap + idx;
+    const unsigned long long word = ((unsigned long long)(done + 1u) << 32) | (unsigned long long)__float_as_uint(v);
+#pragma unroll
+    for (int r = 0; r < kPushMaxWorld; r++)
+        if (r < p.world) *reinterpret_cast<volatile unsigned long long *>(p.stage[r] + off) = word;
+}
+
 // get_scale_min_k4 (crates/infr-gguf/src/dequant.rs:73-83) for the sub-block pair (2j, 2j+1) of a
 // Q4_K header held in registers: y = scales[0..3], z = scales[4..7], w = scales[8..11].
 __device__ __forceinline__ void k4_pair(uint32_t y, uint32_t z, uint32_t w, int j, int &sc0, int &m0,

@@ -125,7 +125,7 @@ template <int M, bool FUSED, int KW, int SB>
 __global__ void __launch_bounds__(KW * 32, 16 / KW)
     gemv_q4k_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ MmaSecond sec, Q8Dev a,
                         const float *__restrict__ x, float *__restrict__ y, int m, int in_f, int out_f, MmaGeom geo, MmaGroup grp,
-                        uint32_t *__restrict__ status) {
+                        uint32_t *__restrict__ status, const __grid_constant__ GemvPush push) {
     constexpr int kW = KW, kThreadsMma = KW * 32, kStepBlocks = SB, kSlotBytes = kTileRows * SB * 144;
     extern __shared__ __align__(128) uint8_t smem[];
     const int nb = geo.nb, S = geo.slots;
@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
     float *s_part = s_d8 + (size_t)nb * 8;                         // [2][kW][16][8]
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_part + 2 * kW * 128);  // [kW][kMaxSlotsMma]
     __shared__ int s_bad;
+    __shared__ uint32_t s_epoch;  // push mode: exchanges completed before this launch
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -202,6 +203,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
 
     // ---- activations (from the previous kernel in the stream) ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (push.world && threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile uint32_t *>(push.ctrl);  // read by all after the barrier below
     if (M < 8)  // scale columns of tokens the template does not stage
         for (int i = threadIdx.x; i < nb * 8; i += kThreadsMma)
             if ((i & 7) >= M) s_d8[i] = 0.f;
@@ -449,7 +451,10 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < kW; w++) v += pp[w * 128];
-                (second ? sec.y : y)[(size_t)(p0 + n) * of + row] = v;
+                if (push.world)
+                    push_store(push, s_epoch, (size_t)n * of + row, v);
+                else
+                    (second ? sec.y : y)[(size_t)(p0 + n) * of + row] = v;
             }
         }
     }
@@ -473,7 +478,8 @@ EncodeTiledFn encode_tiled() {
 template <int M, bool FUSED, int KW, int SB>
 cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
                            const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const MmaGroup &grp = MmaGroup{},
-                           int n_experts = 1, int max_items = 1, const uint8_t *w2 = nullptr, float *y2 = nullptr, int out_f2 = 0) {
+                           int n_experts = 1, int max_items = 1, const uint8_t *w2 = nullptr, float *y2 = nullptr, int out_f2 = 0,
+                           const GemvPush *push = nullptr) {
     constexpr int kSlotBytes = kTileRows * SB * 144;
     MmaGeom geo;
     geo.nb = in_f / 256;
@@ -538,7 +544,9 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, tmap, sec, a, x, y, m, in_f, out_f, geo, grp, status);
+    GemvPush pz;
+    memset(&pz, 0, sizeof pz);
+    return cudaLaunchKernelEx(&cfg, kernel, tmap, sec, a, x, y, m, in_f, out_f, geo, grp, status, push ? *push : pz);
 }
 
 // Few 16-row tiles (small matrices) -> more warps share a tile's K range so that a tile's latency is short;
@@ -546,7 +554,7 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
 template <int M, bool FUSED>
 cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
                          const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const uint8_t *w2 = nullptr, float *y2 = nullptr,
-                         int out_f2 = 0) {
+                         int out_f2 = 0, const GemvPush *push = nullptr) {
     const int nb = in_f / 256, tiles = (out_f + kTileRows - 1) / kTileRows + (out_f2 + kTileRows - 1) / kTileRows;
     // shared memory a configuration needs with two ring slots per warp of `sb` super-blocks each
     auto need_sb = [&](int kw, int sb) {
@@ -572,7 +580,7 @@ cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float
         bpw = 1;  // selects SB = 1 below; the kernel walks a warp's blocks one slot at a time
     }
 #define INFR_MMA(KW_, SB_) \
-    return launch_mma_cfg<M, FUSED, KW_, SB_>(w, a, x, y, m, in_f, out_f, dev, status, st, MmaGroup{}, 1, 1, w2, y2, out_f2)
+    return launch_mma_cfg<M, FUSED, KW_, SB_>(w, a, x, y, m, in_f, out_f, dev, status, st, MmaGroup{}, 1, 1, w2, y2, out_f2, push)
     if (kw == 16) {
         if (bpw == 1) INFR_MMA(16, 1);
         INFR_MMA(16, 2);
@@ -589,11 +597,11 @@ cudaError_t launch_mma_m(const uint8_t *w, const Q8Dev &a, const float *x, float
 template <bool FUSED>
 cudaError_t launch_mma(const uint8_t *w, const Q8Dev &a, const float *x, float *y, int m, int in_f, int out_f,
                        const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const uint8_t *w2 = nullptr, float *y2 = nullptr,
-                       int out_f2 = 0) {
-    if (m == 1) return launch_mma_m<1, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2);
-    if (m == 2) return launch_mma_m<2, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2);
-    if (m <= 4) return launch_mma_m<4, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2);
-    return launch_mma_m<8, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2);
+                       int out_f2 = 0, const GemvPush *push = nullptr) {
+    if (m == 1) return launch_mma_m<1, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2, push);
+    if (m == 2) return launch_mma_m<2, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2, push);
+    if (m <= 4) return launch_mma_m<4, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2, push);
+    return launch_mma_m<8, FUSED>(w, a, x, y, m, in_f, out_f, dev, status, st, w2, y2, out_f2, push);
 }
 
 }  // namespace
@@ -622,11 +630,11 @@ cudaError_t launch_gemv_q4k_mma_pair(const uint8_t *w1, float *y1, int out_f1, c
 }
 
 cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,
-                                const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+                                const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push) {
     if (m < 1 || m > 8 || in_f % 256) return cudaErrorInvalidValue;
-    if (a) return launch_mma<false>(w, *a, nullptr, y, m, in_f, out_f, dev, status, st);
+    if (a) return launch_mma<false>(w, *a, nullptr, y, m, in_f, out_f, dev, status, st, nullptr, nullptr, 0, push);
     Q8Dev none{nullptr, nullptr, nullptr, nullptr, 256};
-    return launch_mma<true>(w, none, x, y, m, in_f, out_f, dev, status, st);
+    return launch_mma<true>(w, none, x, y, m, in_f, out_f, dev, status, st, nullptr, nullptr, 0, push);
 }
 
 }  // namespace infr

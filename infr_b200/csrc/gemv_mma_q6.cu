@@ -19,6 +19,8 @@
 // reduction, programmatic dependent launch, bounded waits) is the scheme of the Q4_K kernel in gemv_mma.cu.
 #include <cuda.h>
 
+#include <cstring>
+
 #include "gemv_common.cuh"
 
 namespace infr {
@@ -146,7 +148,8 @@ __device__ __forceinline__ void block_q6(const uint8_t *p0, const uint8_t *p1, c
 template <int M, int KW>
 __global__ void __launch_bounds__(KW * 32, 16 / KW)
     gemv_q6_mma_kernel(const __grid_constant__ CUtensorMap tmap, Q8Dev a, float *__restrict__ y, int m, int in_f, int out_f,
-                       Q6Geom geo, uint32_t *__restrict__ status) {
+                       Q6Geom geo, uint32_t *__restrict__ status, const __grid_constant__ GemvPush push) {
+    __shared__ uint32_t s_epoch;  // push mode: exchanges completed before this launch
     extern __shared__ __align__(128) uint8_t smem[];
     const int nb = geo.nb, S = geo.slots;
     uint8_t *rings = smem;
@@ -199,6 +202,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
 
     // ---- activations (from the previous kernel in the stream) ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (push.world && threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile uint32_t *>(push.ctrl);  // read by all after the barrier below
     {
         // 16 bytes = the 16 codes of one sub-block = one word for each of the four K lanes; four loads in flight per
         // thread (the copy is latency-bound)
@@ -282,7 +286,10 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < KW; w++) v += pp[w * 128];
-                y[(size_t)n * out_f + row] = v;
+                if (push.world)
+                    push_store(push, s_epoch, (size_t)n * out_f + row, v);
+                else
+                    y[(size_t)n * out_f + row] = v;
             }
         }
     }
@@ -303,7 +310,7 @@ EncQ6 enc_q6() {
 
 template <int M, int KW>
 cudaError_t launch_cfg6(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f, const DeviceInfo &dev,
-                        uint32_t *status, cudaStream_t st) {
+                        uint32_t *status, cudaStream_t st, const GemvPush *push) {
     Q6Geom geo;
     geo.nb = in_f / 256;
     geo.bpw = (geo.nb + KW - 1) / KW;
@@ -343,12 +350,14 @@ cudaError_t launch_cfg6(const uint8_t *w, const Q8Dev &a, float *y, int m, int i
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, tmap, a, y, m, in_f, out_f, geo, status);
+    GemvPush pz;
+    memset(&pz, 0, sizeof pz);
+    return cudaLaunchKernelEx(&cfg, kernel, tmap, a, y, m, in_f, out_f, geo, status, push ? *push : pz);
 }
 
 template <int M>
 cudaError_t launch_m6(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f, const DeviceInfo &dev,
-                      uint32_t *status, cudaStream_t st) {
+                      uint32_t *status, cudaStream_t st, const GemvPush *push) {
     const int nb = in_f / 256, tiles = (out_f + kRows6 - 1) / kRows6;
     auto need_slots = [&](int kw, int slots) {
         return (size_t)M * nb * kStagedBlock + (size_t)nb * 32 + (size_t)2 * kw * 512 + (size_t)kw * kMaxSlots6 * 8 + 64 +
@@ -362,9 +371,9 @@ cudaError_t launch_m6(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_
     while (kw < 16 && need(kw) > (size_t)dev.max_smem_optin / (16 / kw) - 2048) kw *= 2;
     while (kw > 4 && kw > nb) kw /= 2;
     while (kw > 4 && need(kw) > (size_t)dev.max_smem_optin - 1024) kw /= 2;
-    if (kw == 16) return launch_cfg6<M, 16>(w, a, y, m, in_f, out_f, dev, status, st);
-    if (kw == 8) return launch_cfg6<M, 8>(w, a, y, m, in_f, out_f, dev, status, st);
-    return launch_cfg6<M, 4>(w, a, y, m, in_f, out_f, dev, status, st);
+    if (kw == 16) return launch_cfg6<M, 16>(w, a, y, m, in_f, out_f, dev, status, st, push);
+    if (kw == 8) return launch_cfg6<M, 8>(w, a, y, m, in_f, out_f, dev, status, st, push);
+    return launch_cfg6<M, 4>(w, a, y, m, in_f, out_f, dev, status, st, push);
 }
 
 }  // namespace
@@ -372,12 +381,12 @@ cudaError_t launch_m6(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_
 // cudaErrorInvalidValue when the shape does not qualify (row bytes not a multiple of 16, no 16-element sums,
 // or the staged activations do not fit): the caller falls back to the byte-dot kernel.
 cudaError_t launch_gemv_q6_mma(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f, const DeviceInfo &dev,
-                               uint32_t *status, cudaStream_t st) {
+                               uint32_t *status, cudaStream_t st, const GemvPush *push) {
     if (m < 1 || m > 8 || in_f % 2048 || a.gran != 256 || !a.sums16) return cudaErrorInvalidValue;
-    if (m == 1) return launch_m6<1>(w, a, y, m, in_f, out_f, dev, status, st);
-    if (m == 2) return launch_m6<2>(w, a, y, m, in_f, out_f, dev, status, st);
-    if (m <= 4) return launch_m6<4>(w, a, y, m, in_f, out_f, dev, status, st);
-    return launch_m6<8>(w, a, y, m, in_f, out_f, dev, status, st);
+    if (m == 1) return launch_m6<1>(w, a, y, m, in_f, out_f, dev, status, st, push);
+    if (m == 2) return launch_m6<2>(w, a, y, m, in_f, out_f, dev, status, st, push);
+    if (m <= 4) return launch_m6<4>(w, a, y, m, in_f, out_f, dev, status, st, push);
+    return launch_m6<8>(w, a, y, m, in_f, out_f, dev, status, st, push);
 }
 
 }  // namespace infr

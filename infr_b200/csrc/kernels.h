@@ -37,6 +37,28 @@ struct DeviceInfo {
     size_t l2_bytes;
 };
 
+// A row-parallel GEMV of a tensor-parallel step whose partial result goes straight to the peers: the epilogue stores
+// every value, paired with the exchange's sequence number in ONE 8-byte word, into slot [rank] of EVERY rank's staging
+// (plain remote stores over NVLink peer mappings) instead of y.  An aligned 8-byte store arrives whole, so a word
+// that carries the expected number carries its value: no fence, no arrival flag, no count of finished CTAs.  The
+// consumer (launch_rms_norm_q8_pull) polls the words of its own staging and sums the slots in rank order.
+// world == 0: an ordinary GEMV (the result goes to y).
+constexpr int kPushMaxWorld = 8;
+struct GemvPush {
+    unsigned long long *stage[kPushMaxWorld];  // rank r's staging: [2 parities][world][cap] words of (number << 32 | f32 bits)
+    const uint32_t *ctrl;                      // this rank's control words: [0] = exchanges completed so far
+    uint32_t cap;
+    int world, rank;
+};
+// The consumer's view: this rank's own staging.
+struct PullArgs {
+    const unsigned long long *stage;
+    uint32_t *ctrl;  // [0] exchanges completed (advanced by the consumer's last CTA), [1] consumer CTAs done
+    uint32_t cap, spin;
+    int world;
+    uint32_t *status;
+};
+
 cudaError_t launch_quantize_q8(const float *x, int rows, int k, int gran, int8_t *qs, float *d,
                                int32_t *sums, int32_t *sums16, uint16_t *dact, uint16_t *sact,
                                cudaStream_t st);
@@ -55,11 +77,11 @@ cudaError_t launch_gemv_q2_mma(const uint8_t *w, const Q8Dev &a, float *y, int m
 // Q6_K, m <= 8, rows of 8k blocks (row bytes a multiple of 16), on the warp-level int8 matrix unit; needs the
 // 16-element activation sums.  cudaErrorInvalidValue = shape not taken.
 cudaError_t launch_gemv_q6_mma(const uint8_t *w, const Q8Dev &a, float *y, int m, int in_f, int out_f, const DeviceInfo &dev,
-                               uint32_t *status, cudaStream_t st);
+                               uint32_t *status, cudaStream_t st, const GemvPush *push = nullptr);
 // Q4_K, m <= 8, on the warp-level int8 matrix unit.  Exactly one of `a` (pre-quantised rows) and `x`
 // (f32 rows, quantised inside the kernel) is non-null.
 cudaError_t launch_gemv_q4k_mma(const uint8_t *w, const Q8Dev *a, const float *x, float *y, int m, int in_f, int out_f,
-                                const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
+                                const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push = nullptr);
 // Two Q4_K matrices [out_f1, in_f] and [out_f2, in_f] against the same pre-quantised rows in ONE launch (q and k,
 // gate and up: a decode step pays a fixed few microseconds per dependent launch).
 cudaError_t launch_gemv_q4k_mma_pair(const uint8_t *w1, float *y1, int out_f1, const uint8_t *w2, float *y2, int out_f2, const Q8Dev *a,
@@ -156,6 +178,9 @@ cudaError_t launch_attention(const float *q, const void *k_cache, const void *v_
 // Producers that end in the activation quantiser (256-element blocks; sums16 may be null).
 cudaError_t launch_rms_norm_q8(const float *a, const float *b, float *sum_dst, const float *w, int rows, int dim, float eps, int8_t *qs, float *d,
                                int32_t *sums, int32_t *sums16, cudaStream_t st);
+// a + (the sum over ranks of the pushed partial results, in rank order) -> sum_dst, then RMSNorm and the quantiser.
+cudaError_t launch_rms_norm_q8_pull(const float *a, float *sum_dst, const float *w, int rows, int dim, float eps, int8_t *qs, float *d,
+                                    int32_t *sums, int32_t *sums16, const PullArgs &pull, cudaStream_t st);
 cudaError_t launch_gated_silu_q8(const float *gate, const float *up, int rows, int nff, int8_t *qs, float *d, int32_t *sums, int32_t *sums16,
                                  cudaStream_t st);
 cudaError_t launch_gated_silu(const float *gate, const float *up, float *dst, size_t n, const DeviceInfo &dev, cudaStream_t st);

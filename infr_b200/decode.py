@@ -51,13 +51,16 @@ class DecodeStep:
     output norm.  `k_cache` / `v_cache` are per-layer Buffers holding `n_seq` caches of `max_ctx` rows each."""
 
     def __init__(self, be, shape: LlamaShape, n_seq: int, max_ctx: int, layers, out_norm, head, head_dtype, k_cache, v_cache,
-                 sub=None, reduce=None, argmax: bool = True, pages=None):
+                 sub=None, reduce=None, argmax: bool = True, pages=None, comm=None):
         """Tensor-parallel use: `shape` holds this rank's share (n_head, n_kv, ffn and vocab divided by the ranks, hidden
         whole), `reduce(buffer, n_floats)` sums the row-parallel Linears' partial results (attention output, FFN down)
         over the ranks in place, `sub` optionally supplies the buffer those results live in (e.g. memory a collective
-        library can address), and `argmax=False` leaves the rank's slice of the logits for the caller to gather."""
+        library can address), and `argmax=False` leaves the rank's slice of the logits for the caller to gather.
+        With `comm` (a connected Comm) a step over at most 8 sequences has no exchange kernel at all: the row-parallel
+        GEMVs push their partial results to the peers from their epilogues and the norm that follows sums them
+        (gemv_q8_push / add_rms_norm_q8_pull); `reduce` stays the fallback for shapes that form does not take."""
         self.be, self.s, self.n_seq, self.max_ctx = be, shape, n_seq, max_ctx
-        self.reduce, self.do_argmax = reduce, argmax
+        self.reduce, self.do_argmax, self.comm = reduce, argmax, comm
         # paged caches: pages = (block_table Buffer int32 [n_seq][stride], stride, n_pages); k_cache / v_cache are then
         # per-layer pools of n_pages pages of 128 rows shared by the sequences (fused forms only)
         self.pages = pages
@@ -100,6 +103,14 @@ class DecodeStep:
         ok = lambda dt, k: dt == Q4K or (dt == Q6K and k % 2048 == 0)
         return all(ok(self._dt(L, n), k) for L in self.layers for n, k in ins.items()) and ok(self.head_dtype, s.hidden)
 
+    def _push_ok(self) -> bool:
+        """The row-parallel Linears (o, down) can push their results from the matrix-unit GEMV's epilogue."""
+        s = self.s
+        if self.comm is None or self.n_seq > 8:
+            return False
+        ok = lambda dt, k: (dt == Q4K and k % 256 == 0) or (dt == Q6K and k % 2048 == 0)
+        return all(ok(self._dt(L, "wo"), s.q_dim) and ok(self._dt(L, "down"), s.ffn) for L in self.layers)
+
     def set_inputs(self, hidden: np.ndarray, pos):
         """pos: one position for every sequence, or one per sequence (sequences that joined the batch at different
         times: `run` then takes the largest)."""
@@ -137,6 +148,17 @@ class DecodeStep:
                 gemv(d1, w1, y1, k, o1)
                 gemv(d2, w2, y2, k, o2)
         dt = self._dt
+        push = self._push_ok()
+
+        def row_parallel(d_, w, k, norm_w):  # o / down, the sum over the ranks, the residual add, the next norm
+            if push:
+                be.gemv_q8_push(self.comm, d_, w, *a8, b, k, h)
+                be.add_rms_norm_q8_pull(self.comm, self.hidden, self.hidden, norm_w, b, h, s.eps, *a8)
+                return
+            gemv(d_, w, self.sub, k, h)
+            if self.reduce:
+                self.reduce(self.sub, b * h)
+            be.add_rms_norm_q8(self.hidden, self.sub, self.hidden, norm_w, b, h, s.eps, *a8)
         be.add_rms_norm_q8(self.hidden, None, None, self.layers[0]["attn_norm"], b, h, s.eps, *a8)
         n = 1
         for li, L in enumerate(self.layers):
@@ -153,17 +175,11 @@ class DecodeStep:
                                  n_head=s.n_head, n_kv=s.n_kv, head_dim=s.head_dim, theta=s.theta, n_seq=b, seq_stride=self.seq_stride)
                 be.attention_q8(self.q, self.k_cache[li], self.v_cache[li], *a8, rows=1, pos=pos, n_head=s.n_head, n_kv=s.n_kv,
                                 head_dim=s.head_dim, scale=scale, n_seq=b, seq_stride=self.seq_stride, seq_pos=self._seq_pos)
-            gemv(dt(L, "wo"), L["wo"], self.sub, s.q_dim, h)
-            if self.reduce:
-                self.reduce(self.sub, b * h)
-            be.add_rms_norm_q8(self.hidden, self.sub, self.hidden, L["ffn_norm"], b, h, s.eps, *a8)
+            row_parallel(dt(L, "wo"), L["wo"], s.q_dim, L["ffn_norm"])
             pair(dt(L, "gate"), L["gate"], self.g, ff, dt(L, "up"), L["up"], self.u, ff, h)  # gate and up: one launch
             be.gated_act_q8(self.g, self.u, b, ff, *a8)
-            gemv(dt(L, "down"), L["down"], self.sub, ff, h)
-            if self.reduce:
-                self.reduce(self.sub, b * h)
             nxt = self.layers[li + 1]["attn_norm"] if li + 1 < len(self.layers) else self.out_norm
-            be.add_rms_norm_q8(self.hidden, self.sub, self.hidden, nxt, b, h, s.eps, *a8)
+            row_parallel(dt(L, "down"), L["down"], ff, nxt)
             n += 13  # ops (q/k and gate/up share a launch: 11 launches per layer)
         gemv(self.head_dtype, self.head, self.logits, h, s.vocab)
         if self.do_argmax:

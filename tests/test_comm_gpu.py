@@ -5,8 +5,11 @@ import numpy as np
 import pytest
 
 import infr_b200
+from infr_b200 import synth
 
 pytestmark = pytest.mark.gpu
+
+Q4K, Q6K = infr_b200.Q4K, infr_b200.Q6K
 
 
 def test_single_rank_all_reduce_is_the_identity_and_repeats(backend):
@@ -76,3 +79,75 @@ def test_comm_argument_checks(backend):
     for c in (comm, c2):
         c.close()
     buf.close()
+
+
+def _q8_set(backend, rows, k):
+    return backend.alloc(rows * k), backend.alloc(rows * (k // 256) * 4), backend.alloc(rows * (k // 32) * 4), backend.alloc(rows * (k // 16) * 4)
+
+
+@pytest.mark.parametrize("dt,in_f,m", [(Q4K, 2048, 1), (Q4K, 1024, 5), (Q6K, 4096, 1), (Q6K, 2048, 8), (Q4K, 4096, 8)])
+def test_pushed_gemv_and_pulling_norm_match_gemv_all_reduce_norm(backend, dt, in_f, m):
+    """The exchange without a kernel of its own (infr_cuda_gemv_q8_push + infr_cuda_add_rms_norm_q8_pull) on one rank:
+    the same bits as gemv_q8 -> all_reduce -> add_rms_norm_q8, several pairs in a row (both parities of the staging),
+    alternating with stand-alone all-reduces on the same comm."""
+    h = 1024
+    w = synth.weight(dt, h, in_f, seed=21)
+    x, res = synth.normal(22, (m, in_f)), synth.normal(23, (m, h))
+    nw = (1.0 + 0.05 * synth.normal(24, (h,))).astype(np.float32)
+    wb, xb, nb = backend.from_numpy(w, infr_b200.USAGE_WEIGHTS), backend.from_numpy(x), backend.from_numpy(nw)
+    a8 = _q8_set(backend, m, in_f)
+    backend.quantize_q8(256, xb, m, in_f, *a8)
+    comm = backend.comm_create(0, 1, m * h)
+    # reference: the three separate ops
+    y, hid_ref = backend.alloc(m * h * 4), backend.from_numpy(res)
+    o_ref = _q8_set(backend, m, h)
+    backend.gemv_q8(dt, wb, *a8, y, m, in_f, h)
+    backend.all_reduce(comm, y, m * h)
+    backend.add_rms_norm_q8(hid_ref, y, hid_ref, nb, m, h, 1e-5, *o_ref)
+    ref = [backend.download(b, np.uint8) for b in (hid_ref,) + o_ref]
+    for _ in range(3):
+        hid = backend.from_numpy(res)
+        o = _q8_set(backend, m, h)
+        backend.gemv_q8_push(comm, dt, wb, *a8, m, in_f, h)
+        backend.add_rms_norm_q8_pull(comm, hid, hid, nb, m, h, 1e-5, *o)
+        backend.all_reduce(comm, y, m * h)  # a stand-alone exchange between pairs shares the epochs
+        backend.sync()
+        for got_b, want in zip((hid,) + o, ref):
+            np.testing.assert_array_equal(backend.download(got_b, np.uint8), want)
+        for b in (hid,) + o:
+            b.close()
+    comm.close()
+    for b in (wb, xb, nb, y, hid_ref) + a8 + o_ref:
+        b.close()
+
+
+def test_push_without_its_peer_times_out_and_call_order_is_checked(backend):
+    """A rank whose peer never pushes: the norm's bounded wait runs out, the row keeps a + nothing, sync reports
+    E_TIMEOUT once and the context goes on.  The pair's order is checked on the host."""
+    m, in_f, h = 1, 1024, 512
+    wb = backend.from_numpy(synth.weight(Q4K, h, in_f, seed=31), infr_b200.USAGE_WEIGHTS)
+    xb, nb = backend.from_numpy(synth.normal(32, (m, in_f))), backend.from_numpy(np.ones(h, np.float32))
+    res = synth.normal(33, (m, h))
+    hid = backend.from_numpy(res)
+    a8, o = _q8_set(backend, m, in_f), _q8_set(backend, m, h)
+    backend.quantize_q8(256, xb, m, in_f, *a8)
+    comm = backend.comm_create(0, 2, m * h)
+    comm.connect_silent(spin_limit=2048)
+    with pytest.raises(infr_b200.BackendError):  # nothing was pushed
+        backend.add_rms_norm_q8_pull(comm, hid, hid, nb, m, h, 1e-5, *o)
+    backend.gemv_q8_push(comm, Q4K, wb, *a8, m, in_f, h)
+    with pytest.raises(infr_b200.BackendError):  # the first result has not been consumed
+        backend.gemv_q8_push(comm, Q4K, wb, *a8, m, in_f, h)
+    with pytest.raises(infr_b200.BackendError):  # nor may another exchange come between the two halves
+        backend.all_reduce(comm, hid, m * h)
+    backend.add_rms_norm_q8_pull(comm, hid, hid, nb, m, h, 1e-5, *o)
+    with pytest.raises(infr_b200.BackendError) as e:
+        backend.sync()
+    assert e.value.code == infr_b200.E_TIMEOUT
+    backend.sync()
+    np.testing.assert_array_equal(backend.download(hid, np.float32).reshape(m, h), res)  # nothing was added
+    with pytest.raises(infr_b200.BackendError):  # shapes the matrix-unit GEMV does not take are refused, not walked
+        backend.gemv_q8_push(comm, Q6K, wb, *a8, m, in_f, h)
+    comm.close()
+    for b in (wb, xb, nb, hid) + a8 + o:
+        b.close()

@@ -384,14 +384,16 @@ INFR_API int32_t infr_cuda_gated_act_q8(infr_cuda_ctx *ctx, const infr_cuda_buf 
                                         const infr_q8_out *out);
 /* The exchange of a row-parallel Linear with no kernel of its own (no counterpart in the reference, which has no
  * multi-GPU path; the reference's tensor-parallel sketch sums after the row-parallel Linears,
- * crates/infr-vulkan/src/tp_allreduce.rs:320).  infr_cuda_gemv_q8_push is infr_cuda_gemv_q8 (m <= 8; Q4_K rows of
- * whole blocks, or Q6_K rows of whole 2048-element chunks with sums16) whose epilogue stores the rank's partial
- * [m, out_f] result into every rank's staging over NVLink peer mappings instead of a buffer;
- * infr_cuda_add_rms_norm_q8_pull is infr_cuda_add_rms_norm_q8 with b = the sum of all ranks' pushed results (waits,
- * bounded, for every rank's arrival word; sums in rank order from zero, so the result has the bits of
- * infr_cuda_gemv_q8 + infr_cuda_all_reduce_f32 + infr_cuda_add_rms_norm_q8).  The two calls come in pairs on one comm,
- * in the same order on every rank, m * out_f == rows * dim <= the comm's max_floats; other exchanges of the comm may
- * come between pairs, not inside one.  A rank that never pushes makes the wait expire: INFR_E_TIMEOUT at the next sync. */
+ * crates/infr-vulkan/src/tp_allreduce.rs:320).  infr_cuda_gemv_q8_push is infr_cuda_gemv_q8 (Q4_K rows of whole
+ * blocks, or Q6_K rows of whole 2048-element chunks with sums16; m <= 8, or m <= 32 where infr_cuda_gemv_q8 takes that
+ * many rows) whose epilogue stores the rank's partial [m, out_f] result into every rank's staging over NVLink peer
+ * mappings instead of a buffer, each value in one 8-byte word with the exchange's sequence number (no fence, no flag);
+ * infr_cuda_add_rms_norm_q8_pull is infr_cuda_add_rms_norm_q8 with b = the sum of all ranks' pushed results (polls,
+ * bounded, the words it adds; sums in rank order from zero, so the result has the bits of infr_cuda_gemv_q8 +
+ * infr_cuda_all_reduce_f32 + infr_cuda_add_rms_norm_q8).  The two calls come in pairs on one comm, in the same order on
+ * every rank, m * out_f == rows * dim <= min(the comm's max_floats, 262144); other exchanges of the comm may come
+ * between pairs, not inside one.  A rank that never pushes makes the poll run out: the row keeps `a` alone and the next
+ * sync returns INFR_E_TIMEOUT. */
 INFR_API int32_t infr_cuda_gemv_q8_push(infr_cuda_ctx *ctx, infr_cuda_comm *comm, int32_t dtype, const infr_cuda_buf *w, uint64_t w_off,
                                         const infr_cuda_buf *qs, const infr_cuda_buf *d, const infr_cuda_buf *sums, const infr_cuda_buf *sums16,
                                         uint32_t m, uint32_t in_f, uint32_t out_f);

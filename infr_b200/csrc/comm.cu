@@ -34,7 +34,7 @@ constexpr int kMaxWorld = 8;
 constexpr int kArThreads = 1024;
 constexpr int kArMaxCtas = 64;  // 64 x 1024 float4 = 256 K floats (1 MB) per exchange; one CTA per SM, all resident
 constexpr uint32_t kArSpin = 1u << 22;
-constexpr uint32_t kPushMaxFloats = 8 * 16384;  // a pushed GEMV result: at most 8 rows (1 MB of staged words per rank and parity)
+constexpr uint32_t kPushMaxFloats = 32 * 8192;  // a pushed GEMV result: at most 32 rows (2 MB of staged words per rank and parity)
 
 struct ArPeers {
     float *stage[kMaxWorld];     // peer r's staging: [2][world][cap] f32
@@ -235,7 +235,9 @@ Status CudaBackend::gemv_q8_push(infr_cuda_comm *c, int dtype, const uint8_t *w,
     if (!c) return Status::Err(INFR_E_INVALID, "gemv_q8_push: null comm");
     if (!c->connected) return Status::Err(INFR_E_INVALID, "gemv_q8_push: the peers' buffers are not connected");
     if (c->pushed) return Status::Err(INFR_E_INVALID, "gemv_q8_push: the previous pushed result has not been consumed (rms_norm_q8_pull)");
-    if (m < 1 || m > 8) return Status::Err(INFR_E_INVALID, fmt("gemv_q8_push: m=%u (1..8)", m));
+    const bool wide = m > 8 && m <= 32 && wide_applies(dtype, m, in_f, INFR_ACT_INT8);
+    if (m < 1 || (m > 8 && !wide))
+        return Status::Err(INFR_E_INVALID, fmt("gemv_q8_push: m=%u (1..8; up to 32 where the wide GEMV applies)", m));
     if ((uint64_t)m * out_f > c->push_cap)
         return Status::Err(INFR_E_INVALID, fmt("gemv_q8_push: %u x %u results, the comm stages %u pushed floats", m, out_f, c->push_cap));
     const bool q4 = dtype == DT_Q4K && in_f && in_f % 256 == 0, q6 = dtype == DT_Q6K && in_f && in_f % 2048 == 0 && a.sums16;
@@ -251,12 +253,23 @@ Status CudaBackend::gemv_q8_push(infr_cuda_comm *c, int dtype, const uint8_t *w,
     p.cap = c->push_cap;
     p.world = c->world;
     p.rank = c->rank;
-    const cudaError_t e = q4 ? launch_gemv_q4k_mma(w, &a, nullptr, nullptr, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_, &p)
-                             : launch_gemv_q6_mma(w, a, nullptr, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_, &p);
+    cudaError_t e;
+    int n_launch = 1;
+    if (wide) {
+        // a few dozen rows: the wide GEMV; with several K chunks the kernel that adds them is the one that pushes
+        const size_t pb = gemv_wide_partial_bytes((int)m, (int)in_f, (int)out_f);
+        Status s = ensure_scratch(pb);
+        if (!s.ok()) return s;
+        e = launch_gemv_wide(dtype, w, a, nullptr, reinterpret_cast<float *>(scratch()), (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_, &p);
+        n_launch = gemv_wide_launches((int)in_f);
+    } else {
+        e = q4 ? launch_gemv_q4k_mma(w, &a, nullptr, nullptr, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_, &p)
+               : launch_gemv_q6_mma(w, a, nullptr, (int)m, (int)in_f, (int)out_f, dev_, status_dev_, stream_, &p);
+    }
     if (e == cudaErrorInvalidValue) return Status::Err(INFR_E_UNSUPPORTED, "gemv_q8_push: the matrix-unit GEMV does not take this shape");
     Status s = cuda_status(e, "gemv_q8_push");
     if (s.ok()) {
-        launches_++;
+        launches_ += (uint64_t)n_launch;
         c->pushed = true;
     }
     return s;

@@ -20,6 +20,8 @@
 // All mbarrier waits are bounded; an expired wait records a status word for the host and the warp stops consuming.
 #include <cuda.h>
 
+#include <cstring>
+
 #include "gemv_common.cuh"
 
 namespace infr {
@@ -256,8 +258,9 @@ struct WideQ6 {
 template <class F, int NT>
 __global__ void __launch_bounds__(kWWarps * 32, 1)
     gemv_wide_kernel(const __grid_constant__ CUtensorMap tmap, Q8Dev a, float *__restrict__ out, int m, int in_f, int out_f, int slots,
-                     uint32_t *__restrict__ status) {
+                     uint32_t *__restrict__ status, const __grid_constant__ GemvPush push) {
     constexpr int kPart = 8 * NT * kWPitch;  // floats of one warp's partial tile
+    __shared__ uint32_t s_epoch;  // push mode (one K chunk only): exchanges completed before this launch
     extern __shared__ __align__(128) uint8_t smem[];
     const int S = slots;
     uint8_t *rings = smem;
@@ -303,6 +306,7 @@ __global__ void __launch_bounds__(kWWarps * 32, 1)
 
     // ---- activations (from the previous kernel in the stream): this warp's super-block of every row, in registers ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (push.world && threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile uint32_t *>(push.ctrl);  // read after the tile barrier below
     uint32_t bw[NT][F::kBWords];
     float2 e[NT];
 #pragma unroll
@@ -355,20 +359,27 @@ __global__ void __launch_bounds__(kWWarps * 32, 1)
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < kWWarps; w++) v += pp[w * kPart];
-                dst[(size_t)n * out_f + row0 + r] = v;
+                if (push.world)
+                    push_store(push, s_epoch, (size_t)n * out_f + row0 + r, v);
+                else
+                    dst[(size_t)n * out_f + row0 + r] = v;
             }
         }
     }
 }
 
 // y[i] = part[0][i] + part[1][i] + ... in chunk order (the same bits on every run).
-__global__ void wide_sum_chunks_kernel(const float *__restrict__ part, float *__restrict__ y, size_t n, int kz) {
+// With push.world != 0 the sums go to the peers' staging instead (GemvPush).
+__global__ void wide_sum_chunks_kernel(const float *__restrict__ part, float *__restrict__ y, size_t n, int kz, const __grid_constant__ GemvPush push) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float acc = part[i];
     for (int s = 1; s < kz; s++) acc += part[(size_t)s * n + i];
-    y[i] = acc;
+    if (push.world)
+        push_store(push, *reinterpret_cast<const volatile uint32_t *>(push.ctrl), i, acc);
+    else
+        y[i] = acc;
 }
 
 typedef CUresult (*EncWide)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -386,7 +397,10 @@ EncWide enc_wide() {
 
 template <class F, int NT>
 cudaError_t launch_wide_cfg(const CUtensorMap &tmap, const Q8Dev &a, float *y, float *partials, int m, int in_f, int out_f,
-                            const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+                            const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push) {
+    GemvPush none, mine;
+    memset(&none, 0, sizeof none);
+    mine = push ? *push : none;
     const int nb = in_f / 256, kz = (nb + kWWarps - 1) / kWWarps, tiles = (out_f + kWRows - 1) / kWRows;
     int gx = dev.sm_count / kz;
     if (gx < 1) gx = 1;
@@ -408,7 +422,7 @@ cudaError_t launch_wide_cfg(const CUtensorMap &tmap, const Q8Dev &a, float *y, f
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    err = cudaLaunchKernelEx(&cfg, kernel, tmap, a, kz > 1 ? partials : y, m, in_f, out_f, slots, status);
+    err = cudaLaunchKernelEx(&cfg, kernel, tmap, a, kz > 1 ? partials : y, m, in_f, out_f, slots, status, kz > 1 ? none : mine);
     if (err != cudaSuccess || kz == 1) return err;
     const size_t n = (size_t)m * out_f;
     cudaLaunchConfig_t c2 = {};
@@ -417,15 +431,15 @@ cudaError_t launch_wide_cfg(const CUtensorMap &tmap, const Q8Dev &a, float *y, f
     c2.stream = st;
     c2.attrs = attr;
     c2.numAttrs = 1;
-    return cudaLaunchKernelEx(&c2, wide_sum_chunks_kernel, (const float *)partials, y, n, kz);
+    return cudaLaunchKernelEx(&c2, wide_sum_chunks_kernel, (const float *)partials, y, n, kz, mine);
 }
 
 template <class F>
 cudaError_t launch_wide_nt(const CUtensorMap &tmap, const Q8Dev &a, float *y, float *partials, int m, int in_f, int out_f,
-                           const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
-    if (m <= 16) return launch_wide_cfg<F, 2>(tmap, a, y, partials, m, in_f, out_f, dev, status, st);
-    if (m <= 24) return launch_wide_cfg<F, 3>(tmap, a, y, partials, m, in_f, out_f, dev, status, st);
-    return launch_wide_cfg<F, 4>(tmap, a, y, partials, m, in_f, out_f, dev, status, st);
+                           const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push) {
+    if (m <= 16) return launch_wide_cfg<F, 2>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push);
+    if (m <= 24) return launch_wide_cfg<F, 3>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push);
+    return launch_wide_cfg<F, 4>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push);
 }
 
 }  // namespace
@@ -443,7 +457,7 @@ int gemv_wide_launches(int in_f) { return in_f / 256 > kWWarps ? 2 : 1; }
 // Q4_K or Q6_K matrix.  cudaErrorInvalidValue when the shape does not qualify (Q6_K rows whose byte length is not a
 // multiple of 16 have no tensor map): the caller takes another kernel.
 cudaError_t launch_gemv_wide(int dtype, const uint8_t *w, const Q8Dev &a, float *y, float *partials, int m, int in_f, int out_f,
-                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st) {
+                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push) {
     if (m < 1 || m > 32 || in_f < 256 || in_f % 256 || out_f < 1 || a.gran != 256) return cudaErrorInvalidValue;
     if (gemv_wide_partial_bytes(m, in_f, out_f) && !partials) return cudaErrorInvalidValue;
     if ((in_f / 256 + kWWarps - 1) / kWWarps > 65535) return cudaErrorInvalidValue;
@@ -460,7 +474,7 @@ cudaError_t launch_gemv_wide(int dtype, const uint8_t *w, const Q8Dev &a, float 
         if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
-        return launch_wide_nt<WideQ4>(tmap, a, y, partials, m, in_f, out_f, dev, status, st);
+        return launch_wide_nt<WideQ4>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push);
     }
     if (dtype == DT_Q6K) {
         if (in_f % 2048 || !a.sums16 || ((uintptr_t)a.sums16 % 16)) return cudaErrorInvalidValue;
@@ -471,7 +485,7 @@ cudaError_t launch_gemv_wide(int dtype, const uint8_t *w, const Q8Dev &a, float 
         if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
-        return launch_wide_nt<WideQ6>(tmap, a, y, partials, m, in_f, out_f, dev, status, st);
+        return launch_wide_nt<WideQ6>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push);
     }
     return cudaErrorInvalidValue;
 }

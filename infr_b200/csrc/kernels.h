@@ -95,7 +95,7 @@ cudaError_t launch_gemv_f32(int dt, const uint8_t *w, const float *x, float *y, 
 size_t gemv_wide_partial_bytes(int m, int in_f, int out_f);
 int gemv_wide_launches(int in_f);
 cudaError_t launch_gemv_wide(int dtype, const uint8_t *w, const Q8Dev &a, float *y, float *partials, int m, int in_f, int out_f,
-                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st);
+                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push = nullptr);
 
 // Prefill GEMM C[m,out_f] = Q8(256) activations x Q4_K weights on tcgen05 (kind::i8, TMEM accumulators);
 // bit-identical to the CPU production path.

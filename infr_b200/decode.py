@@ -56,7 +56,7 @@ class DecodeStep:
         whole), `reduce(buffer, n_floats)` sums the row-parallel Linears' partial results (attention output, FFN down)
         over the ranks in place, `sub` optionally supplies the buffer those results live in (e.g. memory a collective
         library can address), and `argmax=False` leaves the rank's slice of the logits for the caller to gather.
-        With `comm` (a connected Comm) a step over at most 8 sequences has no exchange kernel at all: the row-parallel
+        With `comm` (a connected Comm) a step over at most 8 sequences (32 where the wide GEMV applies) has no exchange kernel at all: the row-parallel
         GEMVs push their partial results to the peers from their epilogues and the norm that follows sums them
         (gemv_q8_push / add_rms_norm_q8_pull); `reduce` stays the fallback for shapes that form does not take."""
         self.be, self.s, self.n_seq, self.max_ctx = be, shape, n_seq, max_ctx
@@ -106,7 +106,7 @@ class DecodeStep:
     def _push_ok(self) -> bool:
         """The row-parallel Linears (o, down) can push their results from the matrix-unit GEMV's epilogue."""
         s = self.s
-        if self.comm is None or self.n_seq > 8:
+        if self.comm is None or self.n_seq > 32 or (self.n_seq > 8 and not self._wide_ok()):
             return False
         ok = lambda dt, k: (dt == Q4K and k % 256 == 0) or (dt == Q6K and k % 2048 == 0)
         return all(ok(self._dt(L, "wo"), s.q_dim) and ok(self._dt(L, "down"), s.ffn) for L in self.layers)

@@ -85,7 +85,8 @@ def _q8_set(backend, rows, k):
     return backend.alloc(rows * k), backend.alloc(rows * (k // 256) * 4), backend.alloc(rows * (k // 32) * 4), backend.alloc(rows * (k // 16) * 4)
 
 
-@pytest.mark.parametrize("dt,in_f,m", [(Q4K, 2048, 1), (Q4K, 1024, 5), (Q6K, 4096, 1), (Q6K, 2048, 8), (Q4K, 4096, 8)])
+@pytest.mark.parametrize("dt,in_f,m", [(Q4K, 2048, 1), (Q4K, 1024, 5), (Q6K, 4096, 1), (Q6K, 2048, 8), (Q4K, 4096, 8),
+                                       (Q4K, 2048, 12), (Q4K, 4096, 32), (Q6K, 6144, 20)])  # 9..32 rows: the wide GEMV, one or several K chunks
 def test_pushed_gemv_and_pulling_norm_match_gemv_all_reduce_norm(backend, dt, in_f, m):
     """The exchange without a kernel of its own (infr_cuda_gemv_q8_push + infr_cuda_add_rms_norm_q8_pull) on one rank:
     the same bits as gemv_q8 -> all_reduce -> add_rms_norm_q8, several pairs in a row (both parities of the staging),

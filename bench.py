@@ -578,9 +578,12 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
     # the FFN is cut in whole 2048-column chunks while there are enough of them (14336 = 7 chunks: 4 + 3 on two ranks,
     # 2 + 2 + 2 + 1 on four): a Q6_K `down` whose rows are whole chunks keeps the wide GEMV (rows of 14336 / N columns
     # are 5880 or 2940 bytes: no TMA stride), and an uneven cut costs less than the 8-row walk it avoids
+    # With more ranks than chunks (8 ranks: 1792 columns each) the slice is padded to whole chunks with zero blocks
+    # (2048: 14 % more bytes of gate / up / down, and every Linear keeps its fast kernel and the pushed exchange).
     ffn_unit = 2048 if full.ffn // 2048 >= N else 256
     ffn_of = lambda r, n: shard.col_range(Q4K, full.ffn, r, n, unit=ffn_unit)
-    s = LlamaShape(n_head=full.n_head // N, n_kv=full.n_kv // N, ffn=ffn_of(rank, N)[1] - ffn_of(rank, N)[0], vocab=full.vocab // N)
+    ffn_pad = lambda r, n: -(-(ffn_of(r, n)[1] - ffn_of(r, n)[0]) // 2048) * 2048 if n > 1 else full.ffn
+    s = LlamaShape(n_head=full.n_head // N, n_kv=full.n_kv // N, ffn=ffn_pad(rank, N), vocab=full.vocab // N)
     max_ctx = pos + 8
     row_parallel = {"wo", "down"}  # input columns split, partial sums all-reduced
     host_full = {name: synth.random_blocks(dt, o * i, 300 + k) for k, (name, dt, o, i) in enumerate(full.linears())}
@@ -593,14 +596,19 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
         """Device buffers of rank r's share of the model split n_ranks ways (n_ranks = 1: the whole model)."""
         masters = {}
         f0, f1 = ffn_of(r, n_ranks)
+        fp = ffn_pad(r, n_ranks)
         for name, dt, o, i in full.linears():
             if name == "down":
                 w, _, _ = shard.col_shard(dt, host_full[name], o, i, r, n_ranks, unit=ffn_unit)
+                if fp != f1 - f0:
+                    w = shard.pad_cols(dt, w, o, f1 - f0, fp)
             elif name in row_parallel:
                 w, _, _ = shard.col_shard(dt, host_full[name], o, i, r, n_ranks, unit=256)
             elif name in ("gate", "up"):  # the rows that feed this rank's columns of `down`
                 bpr = synth.row_bytes(dt, i)
                 w = np.ascontiguousarray(host_full[name]).reshape(-1)[f0 * bpr:f1 * bpr]
+                if fp != f1 - f0:
+                    w = shard.pad_rows(dt, w, f1 - f0, i, fp)
             else:
                 w, _, _ = shard.row_shard(dt, host_full[name], o, i, r, n_ranks)
             masters[name] = be.from_numpy(w, infr_b200.USAGE_WEIGHTS)

@@ -103,12 +103,15 @@ class DecodeStep:
         ok = lambda dt, k: dt == Q4K or (dt == Q6K and k % 2048 == 0)
         return all(ok(self._dt(L, n), k) for L in self.layers for n, k in ins.items()) and ok(self.head_dtype, s.hidden)
 
-    def _push_ok(self) -> bool:
-        """The row-parallel Linears (o, down) can push their results from the matrix-unit GEMV's epilogue."""
+    def _push_ok(self, dt: int = None, k: int = None) -> bool:
+        """The row-parallel Linear of format `dt` over `k` input columns can push its result from its GEMV's epilogue
+        (no arguments: every o and down of the model can)."""
         s = self.s
         if self.comm is None or self.n_seq > 32 or (self.n_seq > 8 and not self._wide_ok()):
             return False
-        ok = lambda dt, k: (dt == Q4K and k % 256 == 0) or (dt == Q6K and k % 2048 == 0)
+        ok = lambda d_, k_: (d_ == Q4K and k_ % 256 == 0) or (d_ == Q6K and k_ % 2048 == 0)
+        if dt is not None:
+            return ok(dt, k)
         return all(ok(self._dt(L, "wo"), s.q_dim) and ok(self._dt(L, "down"), s.ffn) for L in self.layers)
 
     def set_inputs(self, hidden: np.ndarray, pos):
@@ -148,10 +151,8 @@ class DecodeStep:
                 gemv(d1, w1, y1, k, o1)
                 gemv(d2, w2, y2, k, o2)
         dt = self._dt
-        push = self._push_ok()
-
         def row_parallel(d_, w, k, norm_w):  # o / down, the sum over the ranks, the residual add, the next norm
-            if push:
+            if self._push_ok(d_, k):
                 be.gemv_q8_push(self.comm, d_, w, *a8, b, k, h)
                 be.add_rms_norm_q8_pull(self.comm, self.hidden, self.hidden, norm_w, b, h, s.eps, *a8)
                 return

@@ -62,6 +62,32 @@ def col_shard(dtype: int, w_bytes: np.ndarray, out_f: int, in_f: int, rank: int,
     return np.ascontiguousarray(w[:, lo // be * bb:hi // be * bb]).reshape(-1), lo, hi - lo
 
 
+def pad_cols(dtype: int, w_bytes: np.ndarray, out_f: int, in_f: int, to: int) -> np.ndarray:
+    """A dense [out_f, in_f] weight widened to `to` input columns with zero blocks (all-zero bytes are zero weights in
+    Q4_K and Q6_K: d = 0).  A rank's column slice whose width is not one the fast kernels take (a Q6_K row must be whole
+    2048-element chunks for the tiled copies) is padded instead of taking a slower kernel; the rows of the producer that
+    feed the padding are zero rows (pad_rows), so the padded columns meet zero activations and add nothing."""
+    from .synth import BLOCK_BYTES, BLOCK_ELEMS
+
+    be, bb = BLOCK_ELEMS[dtype], BLOCK_BYTES[dtype]
+    if to < in_f or to % be:
+        raise ValueError(f"cannot pad {in_f} columns to {to}")
+    w = np.ascontiguousarray(w_bytes, dtype=np.uint8).reshape(out_f, in_f // be * bb)
+    out = np.zeros((out_f, to // be * bb), np.uint8)
+    out[:, :w.shape[1]] = w
+    return out.reshape(-1)
+
+
+def pad_rows(dtype: int, w_bytes: np.ndarray, out_f: int, in_f: int, to: int) -> np.ndarray:
+    """A dense [out_f, in_f] weight with zero rows appended up to `to` rows (their outputs are exactly 0)."""
+    bpr = row_bytes(dtype, in_f)
+    if to < out_f:
+        raise ValueError(f"cannot pad {out_f} rows to {to}")
+    out = np.zeros(to * bpr, np.uint8)
+    out[:out_f * bpr] = np.ascontiguousarray(w_bytes, dtype=np.uint8).reshape(-1)[:out_f * bpr]
+    return out
+
+
 def gather_rows(dist, y_local: np.ndarray, out_f: int, rank: int, world: int) -> np.ndarray:
     """All-gather of the ranks' y slices [m, rows_r] into the full [m, out_f] (torch.distributed)."""
     import torch

@@ -122,3 +122,31 @@ def test_row_range_is_a_balanced_partition():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         shard.row_range(10, 2, 2)
+
+
+@pytest.mark.parametrize("dt", [12, 14])
+def test_zero_padding_of_a_column_slice_changes_nothing(dt):
+    """A slice of 1792 columns widened to 2048 with zero blocks (and its producer with zero rows): the padded product
+    against zero-padded activations has the bits of the unpadded one, and the producer's extra rows are exactly 0."""
+    sys.path.insert(0, ROOT)
+    from infr_b200 import shard, synth
+    from oracle.cpu_oracle import Oracle
+
+    orc = Oracle()
+    out_f, in_f, to, m = 24, 1792, 2048, 2
+    w = synth.weight(dt, out_f, in_f, seed=5)
+    x = synth.normal(6, (m, in_f))
+    wp = shard.pad_cols(dt, w, out_f, in_f, to)
+    xp = np.zeros((m, to), np.float32)
+    xp[:, :in_f] = x
+    want = orc.linear(dt, w, x, m, in_f, out_f, threads=2)
+    got = orc.linear(dt, wp, xp, m, to, out_f, threads=2)
+    np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+    # the producer side: rows appended to a [in_f_rows, k] weight give zeros
+    k = 512
+    g = synth.weight(dt, in_f, k, seed=7)
+    gp = shard.pad_rows(dt, g, in_f, k, to)
+    y = orc.linear(dt, gp, synth.normal(8, (1, k)), 1, k, to, threads=2)
+    assert not y[0, in_f:].any() and y[0, :in_f].any()
+    with pytest.raises(ValueError):
+        shard.pad_cols(dt, w, out_f, in_f, 1024)

@@ -12,8 +12,10 @@ the 126 MB L2, so a STEP is one pass over ROT = 64 device copies of the matrix a
   value     device-resident: one CUDA graph per step holding ROT x (quantise x -> int8, GEMV)
   roofline  the GEMV kernel alone on pre-quantised activations, timed live with CUDA events on the
             library's stream, against the measured HBM copy bandwidth in MEASURED_PEAKS.json
-  e2e       the same pass through the Backend interface with HOST buffers: per matrix, upload x from
-            pinned memory, execute a one-Linear plan, download y to pinned memory
+  e2e       the same pass through the Backend interface with HOST buffers: per step, one upload of the step's
+            ROT input rows from pinned memory, one execute of a plan holding the step's ROT Linear ops, one download
+            of the ROT result rows to pinned memory; beside it the latency of one synchronous upload / execute /
+            download round trip per matrix (round_trip_us_per_call)
   sweep     (N=1) the other GEMV configurations: Q6_K 14336x4096 and ternary Q2_0 4096x14336 at
             batch 1/4/8, Q4_K 14336x4096; each rotated over > 4x L2 of distinct copies
   decode_step   (N=1) a whole 8B-shape decode step (32 layers: norms, Linears, RoPE + KV write, causal
@@ -932,22 +934,33 @@ def run_b200(args):
     ms_kern = _max_over_ranks(dist, ms_kern)
 
     # ---- end to end through the Backend interface with host buffers ----
+    # The step as a caller of the trait issues it: ONE plan holding the step's ROT Linear ops (one input, one weight
+    # and one output handle each), one upload of the step's inputs from pinned memory (ROT rows of x, 1 MB), one
+    # execute, one download of the step's results to pinned memory (1 MB; download waits for the stream).  The handles
+    # are views into one input and one output allocation, so that a copy serves all of them.
     g = infr_b200.Graph()
-    xid = g.input(IN_F)
-    wid = g.weight(OUT_F * IN_F, infr_b200.Q4K)
-    did = g.output(OUT_F)
-    g.linear(xid, wid, did, 1, IN_F, OUT_F)
+    xids = [g.input(IN_F) for _ in range(ROT)]
+    wids = [g.weight(OUT_F * IN_F, infr_b200.Q4K) for _ in range(ROT)]
+    dids = [g.output(OUT_F) for _ in range(ROT)]
+    for i in range(ROT):
+        g.linear(xids[i], wids[i], dids[i], 1, IN_F, OUT_F)
     plan = be.compile(g)
-    hx = be.host_array((IN_F,), np.float32)
+    x_all, y_all = be.alloc(ROT * IN_F * 4), be.alloc(ROT * OUT_F * 4)
+    views = [be.wrap(x_all.device_ptr() + i * IN_F * 4, IN_F * 4, infr_b200.USAGE_ACTIVATIONS) for i in range(ROT)]
+    views += [be.wrap(y_all.device_ptr() + i * OUT_F * 4, OUT_F * 4, infr_b200.USAGE_ACTIVATIONS) for i in range(ROT)]
+    bound = {}
+    for i in range(ROT):
+        bound[xids[i]], bound[wids[i]], bound[dids[i]] = views[i], ws[i], views[ROT + i]
+    bound = be.bind(bound)
+    hx = be.host_array((ROT, IN_F), np.float32)
     hy = be.host_array((ROT, OUT_F), np.float32)
     hx[:] = x[0]
     e2e_steps = max(3, min(steps, 50))
 
     def e2e_pass():
-        for i in range(ROT):
-            be.upload_raw(xb, hx.ctypes.data, IN_F * 4)
-            be.execute(plan, {xid: xb, wid: ws[i], did: ys[i]})
-            be.download_raw(ys[i], hy[i].ctypes.data, OUT_F * 4)
+        be.upload_raw(x_all, hx.ctypes.data, ROT * IN_F * 4)
+        be.execute(plan, bound)
+        be.download_raw(y_all, hy.ctypes.data, ROT * OUT_F * 4)
 
     for _ in range(3):
         e2e_pass()
@@ -956,6 +969,28 @@ def run_b200(args):
     for _ in range(e2e_steps):
         e2e_pass()
     e2e_s = _max_over_ranks(dist, time.perf_counter() - t0)
+    # the same kernel on the same inputs as the device-resident pass: the rows that came back are those results
+    for i in (0, ROT - 1):
+        assert np.array_equal(hy[i], be.download(ys[i], np.float32).reshape(-1)), "end-to-end pass differs from the device-resident pass"
+
+    # one synchronous round trip per matrix (upload x, execute a one-Linear plan, download y): the latency of a
+    # single call through the interface, reported beside the throughput above
+    g1 = infr_b200.Graph()
+    xid, wid, did = g1.input(IN_F), g1.weight(OUT_F * IN_F, infr_b200.Q4K), g1.output(OUT_F)
+    g1.linear(xid, wid, did, 1, IN_F, OUT_F)
+    plan1 = be.compile(g1)
+
+    def call_pass():
+        for i in range(ROT):
+            be.upload_raw(xb, hx.ctypes.data, IN_F * 4)
+            be.execute(plan1, {xid: xb, wid: ws[i], did: ys[i]})
+            be.download_raw(ys[i], hy[i].ctypes.data, OUT_F * 4)
+
+    call_pass()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        call_pass()
+    call_us = _max_over_ranks(dist, time.perf_counter() - t0) * 1e6 / (3 * ROT)
 
     total_bytes = C1_BYTES * ROT * world
     value = total_bytes * steps / (ms * 1e-3) / 1e9
@@ -980,7 +1015,10 @@ def run_b200(args):
                      "alg_bytes_per_launch": C1_BYTES},
         "e2e": {"value": total_bytes * e2e_steps / e2e_s / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": ROT * IN_F * 4, "d2h_bytes_per_step": ROT * OUT_F * 4,
-                "ms_per_step": e2e_s * 1e3 / e2e_steps, "steps": e2e_steps},
+                "ms_per_step": e2e_s * 1e3 / e2e_steps, "steps": e2e_steps,
+                "how": f"per step: one upload of the step's {ROT} input rows from pinned memory, one execute of a plan of {ROT} Linear ops, "
+                       f"one download of the {ROT} result rows to pinned memory (waits for the stream)",
+                "round_trip_us_per_call": call_us},
         "gpu_launches": int(launches),
         "clocks": sampler.summary(),
     }

@@ -221,7 +221,10 @@ INFR_API void infr_cuda_plan_free(infr_cuda_ctx *ctx, infr_cuda_plan *plan);
 /* bindings[i] is the buffer bound to TensorId(i), NULL = unbound (`Bindings`, backend.rs:457-483).
  * Internal handles are backend scratch, zeroed before the walk (crates/infr-core/src/exec.rs:53-92).
  * An unbound Input/Weight/Output handle used by an op is INFR_E_INVALID (the CPU reference panics
- * there, crates/infr-cpu/src/lib.rs:754). */
+ * there, crates/infr-cpu/src/lib.rs:754).
+ * A plan of two or more launches that is run again on the same buffers is replayed as a CUDA graph from its second
+ * run (one graph launch instead of one launch per op); other buffers, a reallocated context scratch or other kernel
+ * options run it op by op again.  Inside a caller's own stream capture the ops are always issued directly. */
 INFR_API int32_t infr_cuda_execute(infr_cuda_ctx *ctx, infr_cuda_plan *plan,
                                    infr_cuda_buf *const *bindings, uint32_t n_bindings);
 

@@ -512,11 +512,17 @@ class CudaBackend:
         self._check(self.L.infr_cuda_compile(self.ctx, C.byref(desc), C.byref(h)))
         return Plan(self, h)
 
-    def execute(self, plan: Plan, bindings: dict[int, Buffer]):
+    def bind(self, bindings: dict[int, Buffer]):
+        """The handle table of `execute` built once, for a plan that runs many times on the same buffers."""
         n = (max(bindings) + 1) if bindings else 0
         arr = (C.c_void_p * max(n, 1))()
         for i, b in bindings.items():
             arr[i] = b.handle
+        return (arr, n, list(bindings.values()))  # the Buffers stay referenced as long as the table does
+
+    def execute(self, plan: Plan, bindings):
+        """bindings: {tensor id: Buffer}, or what bind() returned for such a dict."""
+        arr, n, _ = bindings if isinstance(bindings, tuple) else self.bind(bindings)
         self._check(self.L.infr_cuda_execute(self.ctx, plan.handle, arr, n))
 
     # ---- direct kernels ----

@@ -237,6 +237,7 @@ Status CudaBackend::ensure_scratch(size_t bytes) {
     s = cuda_status(cudaMalloc(&scratch_, want), "scratch cudaMalloc");
     if (!s.ok()) return s;
     scratch_bytes_ = want;
+    scratch_gen_++;
     return Status::Ok();
 }
 

@@ -38,6 +38,12 @@ struct infr_cuda_plan {
     std::vector<void *> internal;  // device scratch of every Internal handle (null for the others), from the context's pool
     std::vector<size_t> internal_bytes;
     std::vector<char> needs_zero;  // the handle's zero fill is observable (read, or partly written, before a full overwrite)
+    // The launch sequence of an execute kept as a CUDA graph: replayed while the bound buffers, the context scratch and
+    // the kernel options are the ones it was captured with (a plan run again on the same buffers, as a decode loop or
+    // a serving step does, then costs one graph launch on the host instead of one launch per op).
+    struct infr_cuda_graph *cached = nullptr;
+    std::vector<uint64_t> cached_key, last_key;
+    bool no_graph = false;  // a capture of this plan failed once: it runs op by op from then on
 };
 
 struct infr_cuda_graph {
@@ -169,6 +175,7 @@ public:
     Status ensure_scratch(size_t bytes);
     uint8_t *scratch() const { return static_cast<uint8_t *>(scratch_); }
     void count_launches(uint64_t n) { launches_ += n; }
+    Status execute_steps(infr_cuda_plan *plan, infr_cuda_buf *const *bindings, uint32_t n);
 
 private:
     CudaBackend() = default;
@@ -184,6 +191,7 @@ private:
     std::mutex mu_;
     std::string last_error_;
     void *scratch_ = nullptr;
+    uint64_t scratch_gen_ = 0;  // counts reallocations of the scratch: graphs captured before one hold stale pointers
     size_t scratch_bytes_ = 0;
     void *flush_ = nullptr;
     size_t flush_bytes_ = 0;

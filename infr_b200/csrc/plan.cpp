@@ -272,11 +272,64 @@ void CudaBackend::free_plan(infr_cuda_plan *p) {
     // anything a later plan enqueues (one stream), so no synchronisation is needed here.
     for (void *q : p->internal)
         if (q) pool_release(q);
+    if (p->cached) graph_free(p->cached);
     delete p;
 }
 
+// The second execute of a plan on the same buffers captures its launches into a CUDA graph (the first one ran op by
+// op and sized the context scratch); later ones replay it.  Anything that changes what the kernels would be given
+// (other buffers, a reallocated scratch, other kernel options) runs op by op again and starts over.  Inside a
+// caller's own stream capture the ops are issued directly.
 Status CudaBackend::execute(infr_cuda_plan *plan, infr_cuda_buf *const *bindings, uint32_t n) {
     if (!plan) return Status::Err(INFR_E_INVALID, "execute: null plan");
+    if (capturing_ || plan->no_graph || plan->steps.size() < 2) return execute_steps(plan, bindings, n);
+    cudaSetDevice(device_);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream_, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)
+        return execute_steps(plan, bindings, n);  // somebody else is capturing this stream
+    std::vector<uint64_t> key;
+    key.reserve(2 * (size_t)n + 5);
+    key.push_back(n);
+    key.push_back(scratch_gen_);
+    key.push_back((uint64_t)reference_);
+    key.push_back((uint64_t)gemv_impl_);
+    key.push_back((uint64_t)mmq_impl_);
+    for (uint32_t i = 0; i < n; i++) {
+        key.push_back(bindings && bindings[i] ? (uint64_t)(uintptr_t)bindings[i]->ptr : 0);
+        key.push_back(bindings && bindings[i] ? (uint64_t)bindings[i]->len : 0);
+    }
+    if (plan->cached && key == plan->cached_key) return graph_launch(plan->cached);
+    if (key != plan->last_key) {
+        plan->last_key = key;
+        return execute_steps(plan, bindings, n);
+    }
+    // same buffers as the previous, op-by-op run: capture
+    if (plan->cached) {
+        graph_free(plan->cached);
+        plan->cached = nullptr;
+        plan->cached_key.clear();
+    }
+    const uint64_t launches_before = launches_;
+    Status s = capture_begin();
+    if (!s.ok()) return execute_steps(plan, bindings, n);
+    Status run = execute_steps(plan, bindings, n);
+    infr_cuda_graph *g = nullptr;
+    s = capture_end(&g);
+    launches_ = launches_before;  // nothing ran while capturing
+    if (!run.ok() || !s.ok()) {
+        // an op that cannot be captured: the plan runs op by op from now on
+        if (g) graph_free(g);
+        cudaGetLastError();
+        plan->no_graph = true;
+        return execute_steps(plan, bindings, n);
+    }
+    plan->cached = g;
+    plan->cached_key = key;
+    return graph_launch(g);
+}
+
+
+Status CudaBackend::execute_steps(infr_cuda_plan *plan, infr_cuda_buf *const *bindings, uint32_t n) {
     cudaSetDevice(device_);
     const uint32_t nt = (uint32_t)plan->tensors.size();
     // Provision: Internal handles read as zero until written (crates/infr-core/src/exec.rs:53-92).

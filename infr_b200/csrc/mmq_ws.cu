@@ -36,6 +36,7 @@
 #include <cstdlib>
 
 #include "gemv_common.cuh"
+#include "pdl.cuh"
 
 namespace infr {
 namespace {
@@ -166,6 +167,8 @@ struct MmqGroup {
 // [nb][m_pad] f32 for the epilogue's broadcast loads.
 __global__ void mmq_ws_prep_kernel(const int8_t *__restrict__ qs, const int32_t *__restrict__ sums, const float *__restrict__ d,
                                    int m, int m_pad, int nb, uint4 *__restrict__ out, MmqGroup grp) {
+    pdl_go();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;  // token fastest: a warp writes 512 contiguous bytes per plane
     if (i >= m * nb) return;
     const int tok = i % m, b = i / m;
@@ -212,6 +215,8 @@ __global__ void mmq_ws_prep_kernel(const int8_t *__restrict__ qs, const int32_t 
 // (token, super-block); lane l owns elements [4l, 4l+4) and [128+4l, 128+4l+4).
 __global__ void __launch_bounds__(256) mmq_ws_quant_planes_kernel(const float *__restrict__ x, int m, int m_pad, int nb,
                                                                   uint32_t *__restrict__ out) {
+    pdl_go();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (wg >= (long long)m * nb) return;
@@ -283,21 +288,8 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb = in_f >> 8;
-    // grouped: one token tile per slab (their number is known only on the device)
-    const int row_tiles = (out_f + kTM - 1) / kTM, tok_tiles = grp.slab_expert ? *grp.n_slabs : (m + kTN - 1) / kTN;
-    // kz > 1: K is split kz ways across tiles (a batch of a few dozen rows against a matrix with few row tiles would
-    // otherwise keep most SMs idle while a handful walk all of K); split s writes its partial result to C + s * m * out_f
-    // and a second kernel adds the partial results in order.
-    const int n_tiles = row_tiles * tok_tiles * kz;
-    auto tile_of = [&](int t, int *rt, int *tt, int *b0, int *b1) {
-        const int ks = t % kz, tr = t / kz;
-        *rt = tr % row_tiles;  // consecutive CTAs share a token tile
-        *tt = tr / row_tiles;
-        *b0 = ks * nb / kz;
-        *b1 = (ks + 1) * nb / kz;
-        return ks;
-    };
-
+    pdl_go();
+    // barriers and tensor memory do not depend on the previous kernel: they are set up while it finishes
     if (tid == 0) {
         s_dead = 0;
         for (int i = 0; i < B_COUNT; i++) {
@@ -318,6 +310,22 @@ __global__ void __launch_bounds__(kThreadsWs, 1)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();  // every thread, before the first read of what the previous kernels wrote (planes, scales, slab lists)
+    // grouped: one token tile per slab (their number is known only on the device)
+    const int row_tiles = (out_f + kTM - 1) / kTM, tok_tiles = grp.slab_expert ? *grp.n_slabs : (m + kTN - 1) / kTN;
+    // kz > 1: K is split kz ways across tiles (a batch of a few dozen rows against a matrix with few row tiles would
+    // otherwise keep most SMs idle while a handful walk all of K); split s writes its partial result to C + s * m * out_f
+    // and a second kernel adds the partial results in order.
+    const int n_tiles = row_tiles * tok_tiles * kz;
+    auto tile_of = [&](int t, int *rt, int *tt, int *b0, int *b1) {
+        const int ks = t % kz, tr = t / kz;
+        *rt = tr % row_tiles;  // consecutive CTAs share a token tile
+        *tt = tr / row_tiles;
+        *b0 = ks * nb / kz;
+        *b1 = (ks + 1) * nb / kz;
+        return ks;
+    };
+
     const uint32_t tmem = tmem_base_s;
     auto bar = [&](int i) { return su32(&bars[i]); };
 
@@ -635,6 +643,8 @@ size_t mmq_ws_partial_bytes(int m, int in_f, int out_f, const DeviceInfo &dev) {
 
 // y[i] = part[0][i] + part[1][i] + ... in split order (the same bits on every run).
 __global__ void mmq_ws_sum_splits_kernel(const float4 *__restrict__ part, float4 *__restrict__ y, size_t n4, int kz) {
+    pdl_go();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n4) return;
     float4 acc = part[i];
@@ -655,10 +665,14 @@ cudaError_t launch_ws(const uint8_t *w, size_t w_rows, const Q8Dev &a, void *rec
     if (!enc) return cudaErrorNotSupported;
     const int nb = in_f / 256, m_pad = (m + kTN - 1) / kTN * kTN;
     const int n_rec = m * nb;
+    cudaError_t pe = cudaSuccess;
     if (prep && x_f32)
-        mmq_ws_quant_planes_kernel<<<(unsigned)(((size_t)n_rec * 32 + 255) / 256), 256, 0, st>>>(x_f32, m, m_pad, nb, static_cast<uint32_t *>(records));
+        pe = launch_pdl(mmq_ws_quant_planes_kernel, dim3((unsigned)(((size_t)n_rec * 32 + 255) / 256)), dim3(256), 0, st, x_f32, m, m_pad, nb,
+                        static_cast<uint32_t *>(records));
     else if (prep)
-        mmq_ws_prep_kernel<<<(n_rec + 255) / 256, 256, 0, st>>>(a.qs, a.sums, a.d, m, m_pad, nb, static_cast<uint4 *>(records), grp);
+        pe = launch_pdl(mmq_ws_prep_kernel, dim3((unsigned)((n_rec + 255) / 256)), dim3(256), 0, st, a.qs, a.sums, a.d, m, m_pad, nb,
+                        static_cast<uint4 *>(records), grp);
+    if (pe != cudaSuccess) return pe;
     CUtensorMap map_w, map_q;
     const cuuint32_t one2[2] = {1, 1};
     {
@@ -683,14 +697,16 @@ cudaError_t launch_ws(const uint8_t *w, size_t w_rows, const Q8Dev &a, void *rec
     if (e != cudaSuccess) return e;
     const int n_tiles = ((out_f + kTM - 1) / kTM) * max_tok_tiles * kz;
     const int grid = n_tiles < dev.sm_count ? n_tiles : dev.sm_count;
-    mmq_ws_kernel<<<grid, kThreadsWs, kSmem, st>>>(map_w, map_q, d8t, kz > 1 ? partials : c, m, m_pad, in_f, out_f, status, grp, kz);
+    e = launch_pdl(mmq_ws_kernel, dim3((unsigned)grid), dim3(kThreadsWs), (size_t)kSmem, st, map_w, map_q, d8t, kz > 1 ? partials : c, m, m_pad, in_f,
+                   out_f, status, grp, kz);
+    if (e != cudaSuccess) return e;
     if (kz > 1) {
         const size_t n = (size_t)m * out_f;
         if (n % 4) return cudaErrorInvalidValue;  // (callers split K only when out_f is a multiple of 4)
-        mmq_ws_sum_splits_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(reinterpret_cast<const float4 *>(partials),
-                                                                                 reinterpret_cast<float4 *>(c), n / 4, kz);
+        return launch_pdl(mmq_ws_sum_splits_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, reinterpret_cast<const float4 *>(partials),
+                          reinterpret_cast<float4 *>(c), n / 4, kz);
     }
-    return cudaGetLastError();
+    return cudaSuccess;
 }
 }  // namespace
 

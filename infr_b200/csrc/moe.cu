@@ -14,6 +14,7 @@
 //                    (lib.rs:2862-2873) with the arithmetic of quantize.cu
 //   combine        : out[r] += w * y in rank order, multiply and add rounded separately (:2970-2982)
 #include "kernels.h"
+#include "pdl.cuh"
 
 namespace infr {
 
@@ -25,6 +26,8 @@ namespace infr {
 constexpr int kRtRows = 8, kRtExperts = 16, kRtK = 256, kRtPitch = kRtK + 4;
 __global__ void __launch_bounds__(256) moe_router_kernel(const float *__restrict__ router, const float *__restrict__ x,
                                                          float *__restrict__ logits, int rows, int ne, int n_expert) {
+    pdl_go();
+    pdl_wait();
     __shared__ float s_x[kRtRows * kRtPitch], s_w[kRtExperts * kRtPitch];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, j = lane & 7;
     const int rp = warp >> 1, ep = (warp & 1) * 4 + grp;  // row pair 0..3, expert pair 0..7
@@ -106,6 +109,8 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const float *__restrict
 __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict__ logits, int rows, int n_expert, int n_used,
                                                         float scale, int norm_w, int32_t *__restrict__ sel_ids,
                                                         float *__restrict__ sel_w) {
+    pdl_go();
+    pdl_wait();
     extern __shared__ float s_p[];  // [warps][n_expert]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -187,6 +192,8 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int32_t *__restr
                                                           int32_t *__restrict__ item_expert, int32_t *__restrict__ item_p0,
                                                           int32_t *__restrict__ item_cnt, int32_t *__restrict__ n_items,
                                                           int32_t *__restrict__ counts_out, int n_chunks) {
+    pdl_go();
+    pdl_wait();
     // A stable counting sort over chunks of 32 pairs: hist[chunk][expert] = pairs of the expert inside the chunk
     // (lanes with the same expert find each other with a match), an exclusive scan down the chunks gives the place of
     // a chunk's first such pair inside its expert, and a pair's place is that plus its rank among the lanes before it:
@@ -260,6 +267,8 @@ __global__ void __launch_bounds__(256) moe_swiglu_quant_kernel(const float *__re
                                                                int n_pairs, int nff, int8_t *__restrict__ qs, float *__restrict__ d,
                                                                int32_t *__restrict__ sums, int32_t *__restrict__ sums16,
                                                                float *__restrict__ act_out) {
+    pdl_go();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int nbk = nff / 256;
     const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -311,6 +320,8 @@ __global__ void __launch_bounds__(256) moe_swiglu_quant_kernel(const float *__re
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restrict__ y_pairs, const int32_t *__restrict__ pair_of_slot,
                                                           const float *__restrict__ sel_w, int rows, int n_used, int ne,
                                                           float *__restrict__ out) {
+    pdl_go();
+    pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)rows * ne) return;
     const int r = (int)(idx / ne), i = (int)(idx % ne);
@@ -328,17 +339,15 @@ cudaError_t launch_moe_router(const float *router, const float *x, float *logits
     if (rows < 1 || n_expert < 1) return cudaErrorInvalidValue;
     const dim3 grid((unsigned)((rows + kRtRows - 1) / kRtRows), (unsigned)((n_expert + kRtExperts - 1) / kRtExperts));
     if (grid.y > 65535) return cudaErrorInvalidValue;
-    moe_router_kernel<<<grid, 256, 0, st>>>(router, x, logits, rows, ne, n_expert);
-    return cudaGetLastError();
+    return launch_pdl(moe_router_kernel, grid, dim3(256), 0, st, router, x, logits, rows, ne, n_expert);
 }
 
 cudaError_t launch_moe_route(const float *logits, int rows, int n_expert, int n_used, float scale, int norm_w,
                              int32_t *sel_ids, float *sel_w, cudaStream_t st) {
     if (n_expert > 1024 || n_used > 32 || n_used > n_expert) return cudaErrorInvalidValue;
     const int warps = 4;
-    moe_route_kernel<<<(rows + warps - 1) / warps, warps * 32, (size_t)warps * n_expert * 4, st>>>(logits, rows, n_expert, n_used,
-                                                                                              scale, norm_w, sel_ids, sel_w);
-    return cudaGetLastError();
+    return launch_pdl(moe_route_kernel, dim3((unsigned)((rows + warps - 1) / warps)), dim3(warps * 32), (size_t)warps * n_expert * 4, st, logits, rows,
+                      n_expert, n_used, scale, norm_w, sel_ids, sel_w);
 }
 
 cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int n_expert, int e_lo, int n_local, int item_rows,
@@ -350,24 +359,22 @@ cudaError_t launch_moe_bucket(const int32_t *sel_ids, int rows, int n_used, int 
     if (hist_bytes > 200 * 1024) return cudaErrorInvalidValue;  // ~51 000 pairs of 128 experts; more would need a multi-CTA sort
     cudaError_t e = cudaFuncSetAttribute(moe_bucket_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes);
     if (e != cudaSuccess) return e;
-    moe_bucket_kernel<<<1, 1024, hist_bytes, st>>>(sel_ids, rows, n_used, n_expert, e_lo, n_local, item_rows, pair_row, pair_of_slot, item_expert,
-                                                   item_p0, item_cnt, n_items, counts_out, n_chunks);
-    return cudaGetLastError();
+    return launch_pdl(moe_bucket_kernel, dim3(1), dim3(1024), hist_bytes, st, sel_ids, rows, n_used, n_expert, e_lo, n_local, item_rows, pair_row,
+                      pair_of_slot, item_expert, item_p0, item_cnt, n_items, counts_out, n_chunks);
 }
 
 cudaError_t launch_moe_swiglu_quant(const float *gate, const float *up, int n_pairs, int nff, int8_t *qs, float *d,
                                     int32_t *sums, int32_t *sums16, float *act_out, cudaStream_t st) {
     if (nff % 256) return cudaErrorInvalidValue;
     const long long warps = (long long)n_pairs * (nff / 256);
-    moe_swiglu_quant_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(gate, up, n_pairs, nff, qs, d, sums, sums16, act_out);
-    return cudaGetLastError();
+    return launch_pdl(moe_swiglu_quant_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, st, gate, up, n_pairs, nff, qs, d, sums, sums16,
+                      act_out);
 }
 
 cudaError_t launch_moe_combine(const float *y_pairs, const int32_t *pair_of_slot, const float *sel_w, int rows, int n_used,
                                int ne, float *out, cudaStream_t st) {
     const long long n = (long long)rows * ne;
-    moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(y_pairs, pair_of_slot, sel_w, rows, n_used, ne, out);
-    return cudaGetLastError();
+    return launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, y_pairs, pair_of_slot, sel_w, rows, n_used, ne, out);
 }
 
 }  // namespace infr

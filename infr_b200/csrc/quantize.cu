@@ -14,6 +14,7 @@
 #include <cuda_fp16.h>
 
 #include "kernels.h"
+#include "pdl.cuh"
 
 namespace infr {
 
@@ -34,6 +35,8 @@ __global__ void __launch_bounds__(256) quantize_q8_kernel(const float *__restric
                                                           int32_t *__restrict__ sums16,
                                                           __half *__restrict__ dact,
                                                           __half *__restrict__ sact) {
+    pdl_go();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int cpr = (k + 255) / 256;
     const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -101,12 +104,10 @@ cudaError_t launch_quantize_q8(const float *x, int rows, int k, int gran, int8_t
     const int threads = 256;
     const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
     if (gran == 256)
-        quantize_q8_kernel<256><<<blocks, threads, 0, st>>>(x, rows, k, qs, d, sums, sums16, nullptr, nullptr);
-    else
-        quantize_q8_kernel<32><<<blocks, threads, 0, st>>>(x, rows, k, qs, d, sums, sums16,
-                                                            reinterpret_cast<__half *>(dact),
-                                                            reinterpret_cast<__half *>(sact));
-    return cudaGetLastError();
+        return launch_pdl(quantize_q8_kernel<256>, dim3(blocks), dim3(threads), 0, st, x, rows, k, qs, d, sums, sums16, (__half *)nullptr,
+                          (__half *)nullptr);
+    return launch_pdl(quantize_q8_kernel<32>, dim3(blocks), dim3(threads), 0, st, x, rows, k, qs, d, sums, sums16, reinterpret_cast<__half *>(dact),
+                      reinterpret_cast<__half *>(sact));
 }
 
 __global__ void fill_u32_kernel(uint32_t *p, size_t n, uint32_t v) {

@@ -385,7 +385,9 @@ bool CudaBackend::wide_applies(int dtype, uint32_t m, uint32_t in_f, int act) co
 }
 
 // y[m, out_f] from quantised rows, 32 rows per pass of the weights.
-Status CudaBackend::wide_gemm(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, float *partials) {
+// w2 / y2 / out_f2: a second weight against the same rows in the same launches (partials sized for out_f + out_f2).
+Status CudaBackend::wide_gemm(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, float *partials,
+                              const uint8_t *w2, float *y2, uint32_t out_f2) {
     const uint32_t nb = in_f / 256;
     for (uint32_t r0 = 0; r0 < m; r0 += 32) {
         const uint32_t mm = m - r0 < 32 ? m - r0 : 32;
@@ -394,7 +396,8 @@ Status CudaBackend::wide_gemm(int dtype, const uint8_t *w, const Q8Dev &a, float
         sub.d = a.d + (size_t)r0 * nb;
         sub.sums = a.sums + (size_t)r0 * nb * 8;
         if (a.sums16) sub.sums16 = a.sums16 + (size_t)r0 * nb * 16;
-        Status s = cuda_status(launch_gemv_wide(dtype, w, sub, y + (size_t)r0 * out_f, partials, (int)mm, (int)in_f, (int)out_f, dev_, status_dev_, stream_),
+        Status s = cuda_status(launch_gemv_wide(dtype, w, sub, y + (size_t)r0 * out_f, partials, (int)mm, (int)in_f, (int)out_f, dev_, status_dev_, stream_,
+                                                nullptr, w2, y2 ? y2 + (size_t)r0 * out_f2 : nullptr, (int)out_f2),
                                "gemv_wide");
         if (!s.ok()) return s;
         launches_ += (uint64_t)gemv_wide_launches((int)in_f);
@@ -424,12 +427,10 @@ Status CudaBackend::linear_pair(int dtype, const uint8_t *w1, float *y1, uint32_
     if (wide_applies(dtype, m, in_f, act) && out_f1 && out_f2) {
         cudaSetDevice(device_);
         const int mm = m < 32 ? (int)m : 32;
-        const size_t p1 = gemv_wide_partial_bytes(mm, (int)in_f, (int)out_f1), p2 = gemv_wide_partial_bytes(mm, (int)in_f, (int)out_f2);
         Q8Dev a;
         uint8_t *partials = nullptr;
-        Status s = quantize_for(dtype, x, m, in_f, &a, p1 > p2 ? p1 : p2, &partials);
-        if (s.ok()) s = wide_gemm(dtype, w1, a, y1, m, in_f, out_f1, reinterpret_cast<float *>(partials));
-        return s.ok() ? wide_gemm(dtype, w2, a, y2, m, in_f, out_f2, reinterpret_cast<float *>(partials)) : s;
+        Status s = quantize_for(dtype, x, m, in_f, &a, gemv_wide_partial_bytes(mm, (int)in_f, (int)(out_f1 + out_f2)), &partials);
+        return s.ok() ? wide_gemm(dtype, w1, a, y1, m, in_f, out_f1, reinterpret_cast<float *>(partials), w2, y2, out_f2) : s;
     }
     const bool q4_gemm = m > 8 && dtype == DT_Q4K && act == INFR_ACT_INT8 && gemv_impl_ == 0 && (mmq_impl_ == 0 || mmq_impl_ == 2);
     if (q4_gemm && in_f && in_f % 256 == 0 && out_f1 && out_f2) {
@@ -497,6 +498,12 @@ Status CudaBackend::gemv_q8_pair(int dtype, const uint8_t *w1, float *y1, uint32
                                "gemv_q8_pair");
         if (s.ok()) launches_++;
         return s;
+    }
+    if (m > 8 && m <= 32 && out_f1 && out_f2 && wide_applies(dtype, m, in_f, INFR_ACT_INT8) && a.gran == 256 && (dtype != DT_Q6K || a.sums16)) {
+        // a few dozen rows: both weights in one launch of the wide GEMV (and one launch that adds the K chunks of both)
+        cudaSetDevice(device_);
+        Status s = ensure_scratch(gemv_wide_partial_bytes((int)m, (int)in_f, (int)(out_f1 + out_f2)));
+        return s.ok() ? wide_gemm(dtype, w1, a, y1, m, in_f, out_f1, reinterpret_cast<float *>(scratch()), w2, y2, out_f2) : s;
     }
     Status s = gemv_q8(dtype, w1, a, y1, m, in_f, out_f1);
     return s.ok() ? gemv_q8(dtype, w2, a, y2, m, in_f, out_f2) : s;

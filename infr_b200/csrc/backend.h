@@ -212,7 +212,8 @@ private:
     Status check_device_status();
     // Batches of 9..32 rows (Q4_K) / any batch above 8 rows (Q6_K) through the wide GEMV, 32 rows per pass.
     bool wide_applies(int dtype, uint32_t m, uint32_t in_f, int act) const;
-    Status wide_gemm(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, float *partials);
+    Status wide_gemm(int dtype, const uint8_t *w, const Q8Dev &a, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, float *partials,
+                     const uint8_t *w2 = nullptr, float *y2 = nullptr, uint32_t out_f2 = 0);
     Status mmq_linear(const uint8_t *w, const float *x, float *y, uint32_t m, uint32_t in_f, uint32_t out_f, bool reuse);
     // Device blocks behind the Internal handles of compiled plans; a freed plan's blocks are reused by the next
     // compile (the reference rebuilds its graph every step, so compile must not cost an allocation each time).

@@ -254,11 +254,19 @@ struct WideQ6 {
     }
 };
 
+// A second matrix of the same format and in_f against the same rows in the same launch (q and k, gate and up): its
+// 16-row tiles follow the first matrix's in the CTAs' tile ranges.  out_f == 0: none.
+struct WideSecond {
+    CUtensorMap map;
+    float *out;  // its result, or its partial results [K chunk][m][out_f]
+    int out_f;
+};
+
 // Shared memory: rings [8 warps][slots][F::kSlotBytes], partial tiles [2][8 warps][8 NT tokens][17] f32, barriers.
 template <class F, int NT>
 __global__ void __launch_bounds__(kWWarps * 32, 1)
     gemv_wide_kernel(const __grid_constant__ CUtensorMap tmap, Q8Dev a, float *__restrict__ out, int m, int in_f, int out_f, int slots,
-                     uint32_t *__restrict__ status, const __grid_constant__ GemvPush push) {
+                     uint32_t *__restrict__ status, const __grid_constant__ GemvPush push, const __grid_constant__ WideSecond sec) {
     constexpr int kPart = 8 * NT * kWPitch;  // floats of one warp's partial tile
     __shared__ uint32_t s_epoch;  // push mode (one K chunk only): exchanges completed before this launch
     extern __shared__ __align__(128) uint8_t smem[];
@@ -277,7 +285,7 @@ __global__ void __launch_bounds__(kWWarps * 32, 1)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // this CTA's tiles (balanced contiguous ranges) and this warp's super-block
-    const int tiles = (out_f + kWRows - 1) / kWRows;
+    const int tiles1 = (out_f + kWRows - 1) / kWRows, tiles = tiles1 + (sec.out_f + kWRows - 1) / kWRows;
     const int G = gridDim.x, base = tiles / G, rem = tiles % G;
     const int t_begin = blockIdx.x * base + (blockIdx.x < rem ? blockIdx.x : rem);
     const int n_tiles = base + (blockIdx.x < rem ? 1 : 0);
@@ -297,7 +305,11 @@ __global__ void __launch_bounds__(kWWarps * 32, 1)
             // order this warp's earlier reads of the slot before the engine overwrites it
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)F::kSlotBytes) : "memory");
-            wide_tma(sw32(ring + (size_t)slot * F::kSlotBytes), &tmap, F::tma_x(b), (t_begin + j_issue) * kWRows, bar, l2_policy);
+            const int T = t_begin + j_issue;
+            if (T < tiles1)
+                wide_tma(sw32(ring + (size_t)slot * F::kSlotBytes), &tmap, F::tma_x(b), T * kWRows, bar, l2_policy);
+            else
+                wide_tma(sw32(ring + (size_t)slot * F::kSlotBytes), &sec.map, F::tma_x(b), (T - tiles1) * kWRows, bar, l2_policy);
         }
         __syncwarp();
         j_issue++;
@@ -320,6 +332,7 @@ __global__ void __launch_bounds__(kWWarps * 32, 1)
 
     // ---- consume ----
     float *dst = out + (size_t)blockIdx.y * (size_t)m * out_f;  // this K chunk's partial result
+    float *dst2 = sec.out + (size_t)blockIdx.y * (size_t)m * sec.out_f;
     int slot = 0;
     uint32_t phase = 0;
     bool dead = false;
@@ -351,18 +364,20 @@ __global__ void __launch_bounds__(kWWarps * 32, 1)
             part[(n0 + 1) * kWPitch + g + 8] = accf[nt][3];
         }
         __syncthreads();
-        const int row0 = (t_begin + tile) * kWRows;
+        const int T = t_begin + tile;
+        const bool second = T >= tiles1;
+        const int row0 = (second ? T - tiles1 : T) * kWRows, of = second ? sec.out_f : out_f;
         for (int idx = threadIdx.x; idx < 8 * NT * kWRows; idx += kWWarps * 32) {
             const int n = idx >> 4, r = idx & 15;
-            if (n < m && row0 + r < out_f) {
+            if (n < m && row0 + r < of) {
                 const float *pp = s_part + (size_t)(tile & 1) * kWWarps * kPart + n * kWPitch + r;
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < kWWarps; w++) v += pp[w * kPart];
                 if (push.world)
-                    push_store(push, s_epoch, (size_t)n * out_f + row0 + r, v);
+                    push_store(push, s_epoch, (size_t)n * of + row0 + r, v);  // (no second matrix in push mode)
                 else
-                    dst[(size_t)n * out_f + row0 + r] = v;
+                    (second ? dst2 : dst)[(size_t)n * of + row0 + r] = v;
             }
         }
     }
@@ -370,10 +385,16 @@ __global__ void __launch_bounds__(kWWarps * 32, 1)
 
 // y[i] = part[0][i] + part[1][i] + ... in chunk order (the same bits on every run).
 // With push.world != 0 the sums go to the peers' staging instead (GemvPush).
-__global__ void wide_sum_chunks_kernel(const float *__restrict__ part, float *__restrict__ y, size_t n, int kz, const __grid_constant__ GemvPush push) {
+// A second set of partial results (part2, n2 elements each) is added into y2 by the threads behind the first n.
+__global__ void wide_sum_chunks_kernel(const float *__restrict__ part, float *__restrict__ y, size_t n, int kz, const __grid_constant__ GemvPush push,
+                                       const float *__restrict__ part2, float *__restrict__ y2, size_t n2) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n + n2) return;
+    if (i >= n) {
+        i -= n;
+        part = part2, y = y2, n = n2;
+    }
     float acc = part[i];
     for (int s = 1; s < kz; s++) acc += part[(size_t)s * n + i];
     if (push.world)
@@ -397,11 +418,20 @@ EncWide enc_wide() {
 
 template <class F, int NT>
 cudaError_t launch_wide_cfg(const CUtensorMap &tmap, const Q8Dev &a, float *y, float *partials, int m, int in_f, int out_f,
-                            const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push) {
+                            const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push, const CUtensorMap *tmap2, float *y2,
+                            int out_f2) {
     GemvPush none, mine;
     memset(&none, 0, sizeof none);
     mine = push ? *push : none;
-    const int nb = in_f / 256, kz = (nb + kWWarps - 1) / kWWarps, tiles = (out_f + kWRows - 1) / kWRows;
+    const int nb = in_f / 256, kz = (nb + kWWarps - 1) / kWWarps, tiles = (out_f + kWRows - 1) / kWRows + (out_f2 + kWRows - 1) / kWRows;
+    WideSecond sec;
+    memset(&sec, 0, sizeof sec);
+    float *partials2 = partials ? partials + (size_t)kz * m * out_f : nullptr;
+    if (out_f2 > 0) {
+        sec.map = *tmap2;
+        sec.out = kz > 1 ? partials2 : y2;
+        sec.out_f = out_f2;
+    }
     int gx = dev.sm_count / kz;
     if (gx < 1) gx = 1;
     if (gx > tiles) gx = tiles;
@@ -422,24 +452,25 @@ cudaError_t launch_wide_cfg(const CUtensorMap &tmap, const Q8Dev &a, float *y, f
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    err = cudaLaunchKernelEx(&cfg, kernel, tmap, a, kz > 1 ? partials : y, m, in_f, out_f, slots, status, kz > 1 ? none : mine);
+    err = cudaLaunchKernelEx(&cfg, kernel, tmap, a, kz > 1 ? partials : y, m, in_f, out_f, slots, status, kz > 1 ? none : mine, sec);
     if (err != cudaSuccess || kz == 1) return err;
-    const size_t n = (size_t)m * out_f;
+    const size_t n = (size_t)m * out_f, n2 = (size_t)m * out_f2;
     cudaLaunchConfig_t c2 = {};
-    c2.gridDim = dim3((unsigned)((n + 255) / 256));
+    c2.gridDim = dim3((unsigned)((n + n2 + 255) / 256));
     c2.blockDim = dim3(256);
     c2.stream = st;
     c2.attrs = attr;
     c2.numAttrs = 1;
-    return cudaLaunchKernelEx(&c2, wide_sum_chunks_kernel, (const float *)partials, y, n, kz, mine);
+    return cudaLaunchKernelEx(&c2, wide_sum_chunks_kernel, (const float *)partials, y, n, kz, mine, (const float *)partials2, y2, n2);
 }
 
 template <class F>
 cudaError_t launch_wide_nt(const CUtensorMap &tmap, const Q8Dev &a, float *y, float *partials, int m, int in_f, int out_f,
-                           const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push) {
-    if (m <= 16) return launch_wide_cfg<F, 2>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push);
-    if (m <= 24) return launch_wide_cfg<F, 3>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push);
-    return launch_wide_cfg<F, 4>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push);
+                           const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push, const CUtensorMap *tmap2 = nullptr,
+                           float *y2 = nullptr, int out_f2 = 0) {
+    if (m <= 16) return launch_wide_cfg<F, 2>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push, tmap2, y2, out_f2);
+    if (m <= 24) return launch_wide_cfg<F, 3>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push, tmap2, y2, out_f2);
+    return launch_wide_cfg<F, 4>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push, tmap2, y2, out_f2);
 }
 
 }  // namespace
@@ -457,35 +488,41 @@ int gemv_wide_launches(int in_f) { return in_f / 256 > kWWarps ? 2 : 1; }
 // Q4_K or Q6_K matrix.  cudaErrorInvalidValue when the shape does not qualify (Q6_K rows whose byte length is not a
 // multiple of 16 have no tensor map): the caller takes another kernel.
 cudaError_t launch_gemv_wide(int dtype, const uint8_t *w, const Q8Dev &a, float *y, float *partials, int m, int in_f, int out_f,
-                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push) {
+                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push, const uint8_t *w2, float *y2,
+                             int out_f2) {
     if (m < 1 || m > 32 || in_f < 256 || in_f % 256 || out_f < 1 || a.gran != 256) return cudaErrorInvalidValue;
-    if (gemv_wide_partial_bytes(m, in_f, out_f) && !partials) return cudaErrorInvalidValue;
+    if (out_f2 < 0 || (out_f2 > 0 && (!w2 || !y2 || push))) return cudaErrorInvalidValue;
+    if (gemv_wide_partial_bytes(m, in_f, out_f + out_f2) && !partials) return cudaErrorInvalidValue;
     if ((in_f / 256 + kWWarps - 1) / kWWarps > 65535) return cudaErrorInvalidValue;
     if (((uintptr_t)a.qs % 8) || ((uintptr_t)a.sums % 16)) return cudaErrorInvalidValue;
     EncWide enc = enc_wide();
     if (!enc) return cudaErrorNotSupported;
     const int nb = in_f / 256;
-    CUtensorMap tmap;
+    CUtensorMap tmap, tmap2;
     const cuuint32_t estr[2] = {1, 1};
     if (dtype == DT_Q4K) {
-        const cuuint64_t gdim[2] = {(cuuint64_t)nb * 36, (cuuint64_t)out_f};
-        const cuuint64_t gstride[1] = {(cuuint64_t)nb * 144};
-        const cuuint32_t box[2] = {36, (cuuint32_t)kWRows};
-        if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return cudaErrorInvalidValue;
-        return launch_wide_nt<WideQ4>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push);
+        auto encode = [&](CUtensorMap *map, const uint8_t *base, int rows) {
+            const cuuint64_t gdim[2] = {(cuuint64_t)nb * 36, (cuuint64_t)rows};
+            const cuuint64_t gstride[1] = {(cuuint64_t)nb * 144};
+            const cuuint32_t box[2] = {36, (cuuint32_t)kWRows};
+            return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        };
+        if (!encode(&tmap, w, out_f) || (out_f2 > 0 && !encode(&tmap2, w2, out_f2))) return cudaErrorInvalidValue;
+        return launch_wide_nt<WideQ4>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push, &tmap2, y2, out_f2);
     }
     if (dtype == DT_Q6K) {
         if (in_f % 2048 || !a.sums16 || ((uintptr_t)a.sums16 % 16)) return cudaErrorInvalidValue;
         // rows of nb * 105 16-bit elements; a box is 112 elements (224 B) x 16 rows and may run past the row's end (zero-filled)
-        const cuuint64_t gdim[2] = {(cuuint64_t)nb * 105, (cuuint64_t)out_f};
-        const cuuint64_t gstride[1] = {(cuuint64_t)nb * 210};
-        const cuuint32_t box[2] = {(cuuint32_t)WideQ6::kPitch / 2, (cuuint32_t)kWRows};
-        if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return cudaErrorInvalidValue;
-        return launch_wide_nt<WideQ6>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push);
+        auto encode = [&](CUtensorMap *map, const uint8_t *base, int rows) {
+            const cuuint64_t gdim[2] = {(cuuint64_t)nb * 105, (cuuint64_t)rows};
+            const cuuint64_t gstride[1] = {(cuuint64_t)nb * 210};
+            const cuuint32_t box[2] = {(cuuint32_t)WideQ6::kPitch / 2, (cuuint32_t)kWRows};
+            return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<uint8_t *>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        };
+        if (!encode(&tmap, w, out_f) || (out_f2 > 0 && !encode(&tmap2, w2, out_f2))) return cudaErrorInvalidValue;
+        return launch_wide_nt<WideQ6>(tmap, a, y, partials, m, in_f, out_f, dev, status, st, push, &tmap2, y2, out_f2);
     }
     return cudaErrorInvalidValue;
 }

@@ -94,8 +94,11 @@ cudaError_t launch_gemv_f32(int dt, const uint8_t *w, const float *x, float *y, 
 // registers, K cut into chunks of 2048 elements across CTAs (`partials`: gemv_wide_partial_bytes(...) bytes of scratch).
 size_t gemv_wide_partial_bytes(int m, int in_f, int out_f);
 int gemv_wide_launches(int in_f);
+// w2 / y2 / out_f2: a second matrix of the same format and in_f against the same rows in the same launches (partials
+// then holds gemv_wide_partial_bytes(m, in_f, out_f + out_f2)).
 cudaError_t launch_gemv_wide(int dtype, const uint8_t *w, const Q8Dev &a, float *y, float *partials, int m, int in_f, int out_f,
-                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push = nullptr);
+                             const DeviceInfo &dev, uint32_t *status, cudaStream_t st, const GemvPush *push = nullptr, const uint8_t *w2 = nullptr,
+                             float *y2 = nullptr, int out_f2 = 0);
 
 // Prefill GEMM C[m,out_f] = Q8(256) activations x Q4_K weights on tcgen05 (kind::i8, TMEM accumulators);
 // bit-identical to the CPU production path.

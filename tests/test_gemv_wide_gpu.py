@@ -103,3 +103,32 @@ def test_two_weights_share_the_quantised_rows(backend, oracle, dt):
         assert fx.rel_l2(got, oracle.linear(dt, w, x, m, in_f, o)) < TOL
     for b in (b1, b2, xb, y1, y2):
         b.close()
+
+
+@pytest.mark.parametrize("dt,m,in_f,o1,o2", [(Q4K, 12, 2048, 200, 56), (Q4K, 32, 4096, 4096, 1024), (Q6K, 20, 4096, 136, 512),
+                                             (Q4K, 9, 6144, 24, 1000)])
+def test_pair_in_one_launch_has_the_bits_of_two_calls(backend, dt, m, in_f, o1, o2):
+    """Two weights in one launch of the wide GEMV (and one launch that adds the K chunks of both): every tile and every
+    chunk sum is computed as in a call of its own, so the results are the same bits - from f32 rows (linear_pair) and
+    from pre-quantised rows (gemv_q8_pair)."""
+    w1, w2 = synth.weight(dt, o1, in_f, seed=31), synth.weight(dt, o2, in_f, seed=32)
+    x = synth.normal(33, (m, in_f))
+    b1, b2 = backend.from_numpy(w1, infr_b200.USAGE_WEIGHTS), backend.from_numpy(w2, infr_b200.USAGE_WEIGHTS)
+    xb = backend.from_numpy(x)
+    ys = [backend.alloc(m * o * 4) for o in (o1, o2, o1, o2, o1, o2)]
+    l0 = backend.launch_count()
+    backend.linear_pair(dt, b1, ys[0], o1, b2, ys[1], o2, xb, m, in_f)
+    n_pair = backend.launch_count() - l0
+    backend.linear(dt, b1, xb, ys[2], m, in_f, o1)
+    backend.linear(dt, b2, xb, ys[3], m, in_f, o2)
+    n_two = backend.launch_count() - l0 - n_pair
+    assert n_pair < n_two
+    qs, d, s32, s16 = backend.alloc(m * in_f), backend.alloc(m * (in_f // 256) * 4), backend.alloc(m * (in_f // 32) * 4), backend.alloc(m * (in_f // 16) * 4)
+    backend.quantize_q8(256, xb, m, in_f, qs, d, s32, s16)
+    backend.gemv_q8_pair(dt, b1, ys[4], o1, b2, ys[5], o2, qs, d, s32, s16, m, in_f)
+    got = [backend.download(y, np.float32) for y in ys]
+    for k in (0, 1):
+        np.testing.assert_array_equal(got[k].view(np.uint32), got[2 + k].view(np.uint32))
+        np.testing.assert_array_equal(got[4 + k].view(np.uint32), got[2 + k].view(np.uint32))
+    for b in [b1, b2, xb, qs, d, s32, s16] + ys:
+        b.close()

@@ -116,6 +116,65 @@ struct MmaSecond {
     int out_f;
 };
 
+// quantize_q8 (crates/infr-cpu/src/quant.rs:27-58) of NK 256-element blocks held by one warp (item K0 + k of the
+// fetched set: lane l owns elements 8l..8l+7 of it), all NK worked on together phase by phase; the codes, the split
+// sums and the scale go to the staged layout described below.  Item i = i0 + (K0 + k) * kw is token i / nb, block i % nb.
+template <int NK, int K0>
+__device__ __forceinline__ void quant_items(const float4 (&pa)[4], const float4 (&pb)[4], int i0, int kw, int nb, int lane, uint8_t *s_codes,
+                                            uint8_t *s_bsplit, float *s_d8) {
+    float am[NK], dd[NK], id[NK];
+#pragma unroll
+    for (int k = 0; k < NK; k++) {
+        const float4 v0 = pa[K0 + k], v1 = pb[K0 + k];
+        am[k] = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                      fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int k = 0; k < NK; k++) am[k] = fmaxf(am[k], __shfl_xor_sync(0xffffffffu, am[k], o));
+    }
+#pragma unroll
+    for (int k = 0; k < NK; k++) {
+        dd[k] = am[k] / 127.0f;
+        id[k] = dd[k] > 0.0f ? 1.0f / dd[k] : 0.0f;
+    }
+    uint2 pk[NK];
+    int sum[NK];
+#pragma unroll
+    for (int k = 0; k < NK; k++) {
+        const float vv[8] = {pa[K0 + k].x, pa[K0 + k].y, pa[K0 + k].z, pa[K0 + k].w, pb[K0 + k].x, pb[K0 + k].y, pb[K0 + k].z, pb[K0 + k].w};
+        int q[8];
+        sum[k] = 0;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            float r = roundf(vv[e] * id[k]);
+            r = fminf(fmaxf(r, -127.0f), 127.0f);
+            q[e] = (int)r;
+            sum[k] += q[e];
+        }
+        pk[k].x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+        pk[k].y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+    }
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+#pragma unroll
+        for (int k = 0; k < NK; k++) sum[k] += __shfl_xor_sync(0xffffffffu, sum[k], o);
+    }
+    // lane holds elements 8*lane..8*lane+7 = sub-block s = lane/4, l = 8*(lane&3)+e
+    const int s = lane >> 2, tt = lane & 3;
+#pragma unroll
+    for (int k = 0; k < NK; k++) {
+        const int i = i0 + (K0 + k) * kw, n = i / nb, b = i - n * nb;
+        *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * kStagedBytes + tt * kLaneBytes + s * 8) = pk[k];
+        if (tt == 0) {
+            s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum[k] & 63);
+            s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum[k] >> 6);
+        }
+        if (lane == 0) s_d8[b * 8 + n] = dd[k];
+    }
+}
+
 // Shared-memory layout of the staged activations, per token n (0..7) and super-block b:
 //   codes  : 320 B at (n*nb + b)*320, element (sub-block s, l = 8t+i) at t*80 + s*8 + i
 //   bsplit : 16 B at (n*nb + b)*16: bytes 0..7 = low 6 bits of bsum_s, bytes 8..15 = bsum_s >> 6
@@ -224,39 +283,15 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                     pb[k] = *reinterpret_cast<const float4 *>(xp + lane * 8 + 4);
                 }
             }
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const int i = i0 + k * kW, n = i / nb, b = i - n * nb;
-                if (i >= items) break;
-                const float4 v0 = pa[k], v1 = pb[k];
-                float am = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
-                                 fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-                const float dd = am / 127.0f;
-                const float id = dd > 0.0f ? 1.0f / dd : 0.0f;
-                const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                int q[8], sum = 0;
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    float r = roundf(vv[e] * id);
-                    r = fminf(fmaxf(r, -127.0f), 127.0f);
-                    q[e] = (int)r;
-                    sum += q[e];
-                }
-                // lane holds elements 8*lane..8*lane+7 = sub-block s = lane/4, l = 8*(lane&3)+e
-                const int s = lane >> 2, tt = lane & 3;
-                uint2 pk;
-                pk.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
-                pk.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
-                *reinterpret_cast<uint2 *>(s_codes + (size_t)(n * nb + b) * kStagedBytes + tt * kLaneBytes + s * 8) = pk;
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                if (tt == 0) {
-                    s_bsplit[(size_t)(n * nb + b) * 16 + s] = (uint8_t)(sum & 63);
-                    s_bsplit[(size_t)(n * nb + b) * 16 + 8 + s] = (uint8_t)(int8_t)(sum >> 6);
-                }
-                if (lane == 0) s_d8[b * 8 + n] = dd;
+            // Items are worked on together, phase by phase (all maxima, then all reductions, ...), so that their
+            // dependent chains overlap: shuffles, two divisions and eight roundings per item are latency, not work.
+            const int left = (items - i0 + kW - 1) / kW;  // items of this warp from i0 on (warp-uniform)
+            if (left >= 4) {
+                quant_items<4, 0>(pa, pb, i0, kW, nb, lane, s_codes, s_bsplit, s_d8);
+            } else {
+                if (left >= 2) quant_items<2, 0>(pa, pb, i0, kW, nb, lane, s_codes, s_bsplit, s_d8);
+                if (left == 3) quant_items<1, 2>(pa, pb, i0, kW, nb, lane, s_codes, s_bsplit, s_d8);
+                if (left == 1) quant_items<1, 0>(pa, pb, i0, kW, nb, lane, s_codes, s_bsplit, s_d8);
             }
         }
     } else {

@@ -35,6 +35,17 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // ---- epilogue of a GEMV that pushes its result to the peers (GemvPush) ----
+// The last parameter of such a kernel: the peers' staging (PUSH), or nothing at all - the ordinary kernel carries
+// neither the parameter bytes nor the branch (the 148 bytes cost the 4096 x 4096 GEMV 2-3 % when they were always there).
+struct NoPush {};
+template <bool PUSH>
+struct PushParam {
+    typedef NoPush type;
+};
+template <>
+struct PushParam<true> {
+    typedef GemvPush type;
+};
 // One value of the result: slot [rank] of the exchange's parity on every rank, value and sequence number in one
 // aligned 8-byte store.  The loop bound is a constant so that the pointer table is read from the kernel's parameters
 // with constant indices.

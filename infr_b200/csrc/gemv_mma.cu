@@ -180,11 +180,11 @@ __device__ __forceinline__ void quant_items(const float4 (&pa)[4], const float4 
 //   bsplit : 16 B at (n*nb + b)*16: bytes 0..7 = low 6 bits of bsum_s, bytes 8..15 = bsum_s >> 6
 //   d8     : float [b][8 tokens], zero for absent tokens (a lane's two result columns are neighbours)
 // KW = warps per CTA (they split K), SB = super-blocks per ring slot per row.
-template <int M, bool FUSED, int KW, int SB>
+template <int M, bool FUSED, int KW, int SB, bool PUSH>
 __global__ void __launch_bounds__(KW * 32, 16 / KW)
     gemv_q4k_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ MmaSecond sec, Q8Dev a,
                         const float *__restrict__ x, float *__restrict__ y, int m, int in_f, int out_f, MmaGeom geo, MmaGroup grp,
-                        uint32_t *__restrict__ status, const __grid_constant__ GemvPush push) {
+                        uint32_t *__restrict__ status, const __grid_constant__ typename PushParam<PUSH>::type push) {
     constexpr int kW = KW, kThreadsMma = KW * 32, kStepBlocks = SB, kSlotBytes = kTileRows * SB * 144;
     extern __shared__ __align__(128) uint8_t smem[];
     const int nb = geo.nb, S = geo.slots;
@@ -262,7 +262,9 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
 
     // ---- activations (from the previous kernel in the stream) ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (push.world && threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile uint32_t *>(push.ctrl);  // read by all after the barrier below
+    if constexpr (PUSH) {
+        if (threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile uint32_t *>(push.ctrl);  // read by all after the barrier below
+    }
     if (M < 8)  // scale columns of tokens the template does not stage
         for (int i = threadIdx.x; i < nb * 8; i += kThreadsMma)
             if ((i & 7) >= M) s_d8[i] = 0.f;
@@ -486,7 +488,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < kW; w++) v += pp[w * 128];
-                if (push.world)
+                if constexpr (PUSH)
                     push_store(push, s_epoch, (size_t)n * of + row, v);
                 else
                     (second ? sec.y : y)[(size_t)(p0 + n) * of + row] = v;
@@ -561,8 +563,12 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
         sec.y = y2;
         sec.out_f = out_f2;
     }
-    auto kernel = gemv_q4k_mma_kernel<M, FUSED, KW, SB>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // the pushing form exists for pre-quantised rows only
+    auto kernel = gemv_q4k_mma_kernel<M, FUSED, KW, SB, false>;
+    auto kernel_push = gemv_q4k_mma_kernel<M, false, KW, SB, true>;
+    if (push && FUSED) return cudaErrorInvalidValue;
+    cudaError_t e = push ? cudaFuncSetAttribute(kernel_push, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                         : cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     if (grp.item_expert) {
@@ -579,9 +585,8 @@ cudaError_t launch_mma_cfg(const uint8_t *w, const Q8Dev &a, const float *x, flo
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    GemvPush pz;
-    memset(&pz, 0, sizeof pz);
-    return cudaLaunchKernelEx(&cfg, kernel, tmap, sec, a, x, y, m, in_f, out_f, geo, grp, status, push ? *push : pz);
+    if (push) return cudaLaunchKernelEx(&cfg, kernel_push, tmap, sec, a, x, y, m, in_f, out_f, geo, grp, status, *push);
+    return cudaLaunchKernelEx(&cfg, kernel, tmap, sec, a, x, y, m, in_f, out_f, geo, grp, status, NoPush{});
 }
 
 // Few 16-row tiles (small matrices) -> more warps share a tile's K range so that a tile's latency is short;

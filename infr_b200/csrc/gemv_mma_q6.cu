@@ -145,10 +145,10 @@ __device__ __forceinline__ void block_q6(const uint8_t *p0, const uint8_t *p1, c
 // Shared memory: rings [KW][slots][16 x 224 B]; staged activations per token n and block b: 352 B at
 // (n*nb + b)*352 = four K lanes of 80 B (lane t: its 4 bytes of sub-block s at t*80 + s*4) + the split sums;
 // d8 [block][8 tokens].
-template <int M, int KW>
+template <int M, int KW, bool PUSH>
 __global__ void __launch_bounds__(KW * 32, 16 / KW)
     gemv_q6_mma_kernel(const __grid_constant__ CUtensorMap tmap, Q8Dev a, float *__restrict__ y, int m, int in_f, int out_f,
-                       Q6Geom geo, uint32_t *__restrict__ status, const __grid_constant__ GemvPush push) {
+                       Q6Geom geo, uint32_t *__restrict__ status, const __grid_constant__ typename PushParam<PUSH>::type push) {
     __shared__ uint32_t s_epoch;  // push mode: exchanges completed before this launch
     extern __shared__ __align__(128) uint8_t smem[];
     const int nb = geo.nb, S = geo.slots;
@@ -202,7 +202,9 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
 
     // ---- activations (from the previous kernel in the stream) ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (push.world && threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile uint32_t *>(push.ctrl);  // read by all after the barrier below
+    if constexpr (PUSH) {
+        if (threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile uint32_t *>(push.ctrl);  // read by all after the barrier below
+    }
     {
         // 16 bytes = the 16 codes of one sub-block = one word for each of the four K lanes; four loads in flight per
         // thread (the copy is latency-bound)
@@ -286,7 +288,7 @@ __global__ void __launch_bounds__(KW * 32, 16 / KW)
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < KW; w++) v += pp[w * 128];
-                if (push.world)
+                if constexpr (PUSH)
                     push_store(push, s_epoch, (size_t)n * out_f + row, v);
                 else
                     y[(size_t)n * out_f + row] = v;
@@ -337,8 +339,10 @@ cudaError_t launch_cfg6(const uint8_t *w, const Q8Dev &a, float *y, int m, int i
     if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    auto kernel = gemv_q6_mma_kernel<M, KW>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    auto kernel = gemv_q6_mma_kernel<M, KW, false>;
+    auto kernel_push = gemv_q6_mma_kernel<M, KW, true>;
+    cudaError_t e = push ? cudaFuncSetAttribute(kernel_push, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                         : cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
@@ -350,9 +354,8 @@ cudaError_t launch_cfg6(const uint8_t *w, const Q8Dev &a, float *y, int m, int i
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    GemvPush pz;
-    memset(&pz, 0, sizeof pz);
-    return cudaLaunchKernelEx(&cfg, kernel, tmap, a, y, m, in_f, out_f, geo, status, push ? *push : pz);
+    if (push) return cudaLaunchKernelEx(&cfg, kernel_push, tmap, a, y, m, in_f, out_f, geo, status, *push);
+    return cudaLaunchKernelEx(&cfg, kernel, tmap, a, y, m, in_f, out_f, geo, status, NoPush{});
 }
 
 template <int M>

@@ -263,10 +263,11 @@ struct WideSecond {
 };
 
 // Shared memory: rings [8 warps][slots][F::kSlotBytes], partial tiles [2][8 warps][8 NT tokens][17] f32, barriers.
-template <class F, int NT>
+template <class F, int NT, bool PUSH>
 __global__ void __launch_bounds__(kWWarps * 32, 1)
     gemv_wide_kernel(const __grid_constant__ CUtensorMap tmap, Q8Dev a, float *__restrict__ out, int m, int in_f, int out_f, int slots,
-                     uint32_t *__restrict__ status, const __grid_constant__ GemvPush push, const __grid_constant__ WideSecond sec) {
+                     uint32_t *__restrict__ status, const __grid_constant__ typename PushParam<PUSH>::type push,
+                     const __grid_constant__ WideSecond sec) {
     constexpr int kPart = 8 * NT * kWPitch;  // floats of one warp's partial tile
     __shared__ uint32_t s_epoch;  // push mode (one K chunk only): exchanges completed before this launch
     extern __shared__ __align__(128) uint8_t smem[];
@@ -318,7 +319,9 @@ __global__ void __launch_bounds__(kWWarps * 32, 1)
 
     // ---- activations (from the previous kernel in the stream): this warp's super-block of every row, in registers ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (push.world && threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile uint32_t *>(push.ctrl);  // read after the tile barrier below
+    if constexpr (PUSH) {
+        if (threadIdx.x == 0) s_epoch = *reinterpret_cast<const volatile uint32_t *>(push.ctrl);  // read after the tile barrier below
+    }
     uint32_t bw[NT][F::kBWords];
     float2 e[NT];
 #pragma unroll
@@ -374,7 +377,7 @@ __global__ void __launch_bounds__(kWWarps * 32, 1)
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < kWWarps; w++) v += pp[w * kPart];
-                if (push.world)
+                if constexpr (PUSH)
                     push_store(push, s_epoch, (size_t)n * of + row0 + r, v);  // (no second matrix in push mode)
                 else
                     (second ? dst2 : dst)[(size_t)n * of + row0 + r] = v;
@@ -439,8 +442,12 @@ cudaError_t launch_wide_cfg(const CUtensorMap &tmap, const Q8Dev &a, float *y, f
     if (slots > kWSlots) slots = kWSlots;
     const size_t smem = (size_t)kWWarps * slots * F::kSlotBytes + (size_t)2 * kWWarps * 8 * NT * kWPitch * 4 + (size_t)kWWarps * kWSlots * 8 + 128;
     if (smem > (size_t)dev.max_smem_optin) return cudaErrorInvalidValue;
-    auto kernel = gemv_wide_kernel<F, NT>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // the GEMV itself pushes only when K is one chunk; otherwise the kernel that adds the chunks does
+    const bool push_here = push && kz == 1;
+    auto kernel = gemv_wide_kernel<F, NT, false>;
+    auto kernel_push = gemv_wide_kernel<F, NT, true>;
+    cudaError_t err = push_here ? cudaFuncSetAttribute(kernel_push, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                : cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return err;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -452,7 +459,8 @@ cudaError_t launch_wide_cfg(const CUtensorMap &tmap, const Q8Dev &a, float *y, f
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    err = cudaLaunchKernelEx(&cfg, kernel, tmap, a, kz > 1 ? partials : y, m, in_f, out_f, slots, status, kz > 1 ? none : mine, sec);
+    err = push_here ? cudaLaunchKernelEx(&cfg, kernel_push, tmap, a, y, m, in_f, out_f, slots, status, mine, sec)
+                    : cudaLaunchKernelEx(&cfg, kernel, tmap, a, kz > 1 ? partials : y, m, in_f, out_f, slots, status, NoPush{}, sec);
     if (err != cudaSuccess || kz == 1) return err;
     const size_t n = (size_t)m * out_f, n2 = (size_t)m * out_f2;
     cudaLaunchConfig_t c2 = {};

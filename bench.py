@@ -583,8 +583,8 @@ def _tp_decode_step(be, infr_b200, dist, rank, world, local, batch, steps, warmu
     # With more ranks than chunks (8 ranks: 1792 columns each) the slice is padded to whole chunks with zero blocks
     # (2048: 14 % more bytes of gate / up / down, and every Linear keeps its fast kernel and the pushed exchange).
     ffn_unit = 2048 if full.ffn // 2048 >= N else 256
-    ffn_of = lambda r, n: shard.col_range(Q4K, full.ffn, r, n, unit=ffn_unit)
-    ffn_pad = lambda r, n: -(-(ffn_of(r, n)[1] - ffn_of(r, n)[0]) // 2048) * 2048 if n > 1 else full.ffn
+    ffn_of = lambda r, n: shard.ffn_split(full.ffn, n)[r][:2]
+    ffn_pad = lambda r, n: shard.ffn_split(full.ffn, n)[r][2]
     s = LlamaShape(n_head=full.n_head // N, n_kv=full.n_kv // N, ffn=ffn_pad(rank, N), vocab=full.vocab // N)
     max_ctx = pos + 8
     row_parallel = {"wo", "down"}  # input columns split, partial sums all-reduced

@@ -62,6 +62,27 @@ def col_shard(dtype: int, w_bytes: np.ndarray, out_f: int, in_f: int, rank: int,
     return np.ascontiguousarray(w[:, lo // be * bb:hi // be * bb]).reshape(-1), lo, hi - lo
 
 
+def ffn_split(ffn: int, world: int, chunk: int = 2048, granule: int = 256) -> list[tuple[int, int, int]]:
+    """How a tensor-parallel step cuts the FFN width over the ranks: per rank (first column, end column, padded width).
+    While there are at least as many `chunk`-column pieces as ranks the cut is in whole chunks (uneven where they do
+    not divide: 14336 = 7 chunks is 4 + 3 on two ranks, 2 + 2 + 2 + 1 on four), so that a rank's slice of a Q6_K `down`
+    keeps rows the tiled copies can fetch; with more ranks than chunks the cut is in `granule`-column pieces (the
+    activation quantiser's block) and every slice is padded up to whole chunks with zero blocks (pad_cols / pad_rows).
+    One rank keeps the whole width unpadded."""
+    if world < 1 or ffn % granule:
+        raise ValueError(f"cannot split {ffn} columns over {world} ranks in pieces of {granule}")
+    if world == 1:
+        return [(0, ffn, ffn)]
+    unit = chunk if ffn % chunk == 0 and ffn // chunk >= world else granule
+    base, rem = divmod(ffn // unit, world)
+    out, lo = [], 0
+    for r in range(world):
+        n = (base + (1 if r < rem else 0)) * unit
+        out.append((lo, lo + n, -(-n // chunk) * chunk))
+        lo += n
+    return out
+
+
 def pad_cols(dtype: int, w_bytes: np.ndarray, out_f: int, in_f: int, to: int) -> np.ndarray:
     """A dense [out_f, in_f] weight widened to `to` input columns with zero blocks (all-zero bytes are zero weights in
     Q4_K and Q6_K: d = 0).  A rank's column slice whose width is not one the fast kernels take (a Q6_K row must be whole

@@ -150,3 +150,26 @@ def test_zero_padding_of_a_column_slice_changes_nothing(dt):
     assert not y[0, in_f:].any() and y[0, :in_f].any()
     with pytest.raises(ValueError):
         shard.pad_cols(dt, w, out_f, in_f, 1024)
+
+
+def test_ffn_split_of_a_tensor_parallel_step():
+    sys.path.insert(0, ROOT)
+    from infr_b200 import shard
+
+    assert shard.ffn_split(14336, 1) == [(0, 14336, 14336)]
+    assert [hi - lo for lo, hi, _ in shard.ffn_split(14336, 2)] == [8192, 6144]          # 4 + 3 chunks
+    assert [hi - lo for lo, hi, _ in shard.ffn_split(14336, 4)] == [4096, 4096, 4096, 2048]
+    eight = shard.ffn_split(14336, 8)                                                     # more ranks than chunks
+    assert all(hi - lo == 1792 and pad == 2048 for lo, hi, pad in eight)
+    for world in (1, 2, 3, 4, 7, 8):
+        parts = shard.ffn_split(14336, world)
+        assert parts[0][0] == 0 and parts[-1][1] == 14336
+        assert all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+        assert all(lo % 256 == 0 and hi % 256 == 0 and pad % 2048 == 0 and pad >= hi - lo and pad - (hi - lo) < 2048 for lo, hi, pad in parts)
+        if world > 1:
+            # what a rank's Q6_K `down` needs for the tiled copies: rows of whole 2048-column chunks
+            assert all(pad % 2048 == 0 for _, _, pad in parts)
+    assert [hi - lo for lo, hi, _ in shard.ffn_split(11008, 4)] == [2816, 2816, 2816, 2560]  # 5.375 chunks: cut in 256-column granules, padded
+    assert all(pad == 4096 for _, _, pad in shard.ffn_split(11008, 4))
+    with pytest.raises(ValueError):
+        shard.ffn_split(1000, 2)

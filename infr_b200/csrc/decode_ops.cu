@@ -14,6 +14,7 @@
 #include "kernels.h"
 
 #include "pdl.cuh"
+#include "q8_code.cuh"
 
 namespace infr {
 namespace {
@@ -606,11 +607,7 @@ __global__ void __launch_bounds__(256) argmax_stage2_kernel(const float *__restr
 // per-32 and per-16 code sums (crates/infr-cpu/src/quant.rs:27-58).  Same operations in the same order as
 // quantize_q8_kernel<256>, so a producer that ends with this emits the bits the separate quantiser would.
 __device__ __forceinline__ float q8_amax4(float4 v) { return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))); }
-__device__ __forceinline__ int q8_code(float v, float id) {
-    float r = roundf(v * id);
-    r = fminf(fmaxf(r, -127.0f), 127.0f);
-    return (int)r;
-}
+__device__ __forceinline__ int q8_code(float v, float id) { return q8_round_code(v, id); }
 __device__ __forceinline__ void quantize_block256(const float4 v[2], int lane, size_t row, int k, int chunk, int8_t *__restrict__ qs,
                                                   float *__restrict__ d, int32_t *__restrict__ sums, int32_t *__restrict__ sums16) {
     float m = fmaxf(q8_amax4(v[0]), q8_amax4(v[1]));

@@ -34,6 +34,7 @@
 #include <cstring>
 
 #include "gemv_common.cuh"
+#include "q8_code.cuh"
 
 namespace infr {
 namespace {
@@ -145,16 +146,16 @@ __device__ __forceinline__ void quant_items(const float4 (&pa)[4], const float4 
     for (int k = 0; k < NK; k++) {
         const float vv[8] = {pa[K0 + k].x, pa[K0 + k].y, pa[K0 + k].z, pa[K0 + k].w, pb[K0 + k].x, pb[K0 + k].y, pb[K0 + k].z, pb[K0 + k].w};
         int q[8];
-        sum[k] = 0;
+        if (id[k] <= 3.0e38f) {  // (warp-uniform) the usual case: a finite scale, no clamp needed
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-            float r = roundf(vv[e] * id[k]);
-            r = fminf(fmaxf(r, -127.0f), 127.0f);
-            q[e] = (int)r;
-            sum[k] += q[e];
+            for (int e = 0; e < 8; e++) q[e] = q8_round_code_inrange(vv[e], id[k]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) q[e] = q8_round_code(vv[e], id[k]);
         }
-        pk[k].x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
-        pk[k].y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+        pk[k].x = q8_pack4(q[0], q[1], q[2], q[3]);
+        pk[k].y = q8_pack4(q[4], q[5], q[6], q[7]);
+        sum[k] = q8_sum4(pk[k].x) + q8_sum4(pk[k].y);
     }
 #pragma unroll
     for (int o = 1; o <= 2; o <<= 1) {

@@ -37,6 +37,7 @@
 
 #include "gemv_common.cuh"
 #include "pdl.cuh"
+#include "q8_code.cuh"
 
 namespace infr {
 namespace {
@@ -229,11 +230,7 @@ __global__ void __launch_bounds__(256) mmq_ws_quant_planes_kernel(const float *_
     for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
     const float dd = am / 127.0f;
     const float id = dd > 0.0f ? 1.0f / dd : 0.0f;
-    auto q1 = [&](float v) {
-        float r = roundf(v * id);
-        r = fminf(fmaxf(r, -127.0f), 127.0f);
-        return (int)r;
-    };
+    auto q1 = [&](float v) { return q8_round_code(v, id); };
     uint32_t *pl = out + ((size_t)b * kPlanes * m + tok) * 4;  // word 0 of this token's entry in plane 0 of block b
     const size_t plane_words = (size_t)m * 4;
 #pragma unroll

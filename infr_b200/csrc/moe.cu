@@ -15,6 +15,7 @@
 //   combine        : out[r] += w * y in rank order, multiply and add rounded separately (:2970-2982)
 #include "kernels.h"
 #include "pdl.cuh"
+#include "q8_code.cuh"
 
 namespace infr {
 
@@ -300,9 +301,7 @@ __global__ void __launch_bounds__(256) moe_swiglu_quant_kernel(const float *__re
     int q[8], sum = 0;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        float r = roundf(v[i] * id);
-        r = fminf(fmaxf(r, -127.0f), 127.0f);
-        q[i] = (int)r;
+        q[i] = q8_round_code(v[i], id);
         sum += q[i];
     }
     uint2 pk;

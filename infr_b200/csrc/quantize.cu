@@ -15,6 +15,7 @@
 
 #include "kernels.h"
 #include "pdl.cuh"
+#include "q8_code.cuh"
 
 namespace infr {
 
@@ -22,11 +23,7 @@ __device__ __forceinline__ float amax4(float4 v) {
     return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
 }
 
-__device__ __forceinline__ int q1(float v, float id) {
-    float r = roundf(v * id);
-    r = fminf(fmaxf(r, -127.0f), 127.0f);
-    return (int)r;
-}
+__device__ __forceinline__ int q1(float v, float id) { return q8_round_code(v, id); }
 
 template <int GRAN>
 __global__ void __launch_bounds__(256) quantize_q8_kernel(const float *__restrict__ x, int rows, int k,

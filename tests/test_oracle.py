@@ -123,6 +123,24 @@ def test_quantize_q8_matches_numpy_restatement(oracle):
     assert np.abs(qs).max() == 127
 
 
+def test_quantize_q8_non_finite_elements_follow_rust_casts(oracle):
+    """`(v * id).round().clamp(-127.0, 127.0) as i8` (quant.rs:38): f32::max skips a NaN when the block's amax is
+    formed and the NaN's own code is 0 (`as i8` of a NaN); an infinite element makes d infinite and id 0, so every
+    code of its block is 0; a block so small that 1 / (amax / 127) overflows gets +-127 for its non-zero elements."""
+    x = np.linspace(-3.0, 3.0, 768, dtype=np.float32)
+    x[5] = np.nan
+    x[300] = np.inf
+    x[512:768] *= np.float32(1e-38)
+    x[512:600] *= np.float32(-1.0)
+    x[600] = 0.0
+    for qs, d in (oracle.quantize_q8(x)[:2], oracle.quantize_q8_32(x)[:2]):
+        gran = x.size // d.size
+        assert qs[5] == 0 and np.isfinite(d[0]) and d[0] == np.float32(np.nanmax(np.abs(x[:gran]))) / np.float32(127.0)
+        assert np.isinf(d[300 // gran]) and not qs[300 // gran * gran:(300 // gran + 1) * gran].any()
+        tiny = slice(512, 768)
+        assert set(np.unique(qs[tiny])) <= {-127, 0, 127} and qs[600] == 0 and (qs[512:600] == -127).all() and (qs[640:768] == 127).all()
+
+
 def test_quantize_q8_32_and_q8_1_share_codes(oracle):
     x = fx.det_x(704, 9) * np.float32(3.0)
     qs, d, bs = oracle.quantize_q8_32(x)

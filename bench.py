@@ -342,20 +342,25 @@ def _decode_linears_case(be, infr_b200, batch, steps, warmup):
     return res
 
 
-def _decode_step_case(be, infr_b200, batch, steps, warmup, hbm_peak, pos=4096):
+def _decode_step_case(be, infr_b200, batch, steps, warmup, hbm_peak, pos=4096, shard=1):
     """A whole Llama-3-8B-shape decode step: 32 layers of RmsNorm, q/k/v Linears, RoPE + f16 KV write, causal
     attention over a KV cache pre-filled to `pos` positions, o Linear, residual add + RmsNorm, gate/up Linears, SiLU
     gate, down Linear, residual add; then the output norm, the 128256-row head and argmax.  Q4_K_M mix (attn_v and
     ffn_down Q6_K, the rest Q4_K), every layer on its own device copy of the weights, `batch` independent sequences
     with their own caches, the step captured in one CUDA graph.  The input rows stand for the host-embedded token
     rows (the graph restores them at the start of every replay).  Weight bytes are random valid blocks; cache
-    values are N(0,1) halves."""
+    values are N(0,1) halves.
+    shard = N > 1: ONE rank's share of the step split N ways (heads, padded FFN slice, vocabulary slice), alone on this
+    GPU, its row-parallel results pushed to and pulled from a 1-rank comm: what a rank of the tensor-parallel step
+    computes, with the kernels it launches, without the waiting for peers."""
     import numpy as np
-    from infr_b200 import synth
+    from infr_b200 import shard as shard_mod, synth
     from infr_b200.decode import DecodeStep, LlamaShape
 
     Q4K = infr_b200.Q4K
     s = LlamaShape()
+    if shard > 1:
+        s = LlamaShape(n_head=s.n_head // shard, n_kv=s.n_kv // shard, ffn=shard_mod.ffn_split(s.ffn, shard)[0][2], vocab=s.vocab // shard)
     max_ctx = pos + 8
     masters = {name: be.from_numpy(synth.random_blocks(dt, o * i, 200 + k), infr_b200.USAGE_WEIGHTS)
                for k, (name, dt, o, i) in enumerate(s.linears())}
@@ -384,7 +389,8 @@ def _decode_step_case(be, infr_b200, batch, steps, warmup, hbm_peak, pos=4096):
                 be.copy_buffer(kv_master, view, seq_bytes)
                 view.close()
             lst.append(c)
-    step = DecodeStep(be, s, batch, max_ctx, layers, norm, head, Q4K, kc, vc)
+    comm = be.comm_create(0, 1, batch * s.hidden) if shard > 1 else None
+    step = DecodeStep(be, s, batch, max_ctx, layers, norm, head, Q4K, kc, vc, comm=comm)
     hidden0 = be.from_numpy(synth.normal(31, (batch, s.hidden)))
     step.set_inputs(synth.normal(31, (batch, s.hidden)), pos)
 
@@ -405,7 +411,8 @@ def _decode_step_case(be, infr_b200, batch, steps, warmup, hbm_peak, pos=4096):
     tok = be.download(step.tok, np.uint32)
     kv_bytes = s.n_layer * 2 * (pos + 1) * s.kv_dim * 2 * batch
     alg = w_bytes + kv_bytes
-    res = {"workload": f"8B-shape decode step, batch {batch} (independent sequences), KV context {pos} (kv_len {pos + 1}), Q4_K_M mix, "
+    what = "8B-shape decode step" if shard == 1 else f"one rank's share of the 8B-shape decode step split {shard} ways (exchange with itself)"
+    res = {"workload": f"{what}, batch {batch} (independent sequences), KV context {pos} (kv_len {pos + 1}), Q4_K_M mix, "
                        f"{n_ops} ops in one CUDA graph",
            "us_per_step": us, "tok_per_s": batch / (us * 1e-6), "weight_bytes": w_bytes, "kv_bytes_read": kv_bytes,
            "hbm_gbs": alg / (us * 1e-6) / 1e9, "frac_of_measured_hbm": alg / (us * 1e-6) / 1e9 / hbm_peak,
@@ -415,6 +422,8 @@ def _decode_step_case(be, infr_b200, batch, steps, warmup, hbm_peak, pos=4096):
            "kernels_per_step": kernels, "tokens_same_eager_and_graph": bool((tok == tok_eager).all()),
            "first_token_ids": [int(t) for t in tok[:4]]}
     graph.close()
+    if comm is not None:
+        comm.close()
     for b in owned + kc + vc + [head, kv_master, hidden0, norm] + list(masters.values()):
         b.close()
     return res
@@ -1091,9 +1100,9 @@ def run_profile_case(args):
         _emit(_decode_linears_case(be, infr_b200, int(m), args.steps, 2))
         be.close()
         return
-    if name == "step":  # step:0:CONTEXT:BATCH — the whole 8B-shape decode step
+    if name == "step":  # step:SHARD:CONTEXT:BATCH — the whole 8B-shape decode step (SHARD > 1: one rank's share of it)
         be = infr_b200.CudaBackend(device=0)
-        _emit(_decode_step_case(be, infr_b200, int(m), args.steps, 2, _peaks()[0], pos=int(in_f) or 4096))
+        _emit(_decode_step_case(be, infr_b200, int(m), args.steps, 2, _peaks()[0], pos=int(in_f) or 4096, shard=max(int(out_f), 1)))
         be.close()
         return
     if name == "mmq":  # mmq:OUT_F:IN_F:M — the prefill GEMM (Linear with m > 8)

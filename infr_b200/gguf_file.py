@@ -129,8 +129,62 @@ class GgufFile:
         return dst
 
 
+_BLOCK = {GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210), GGML_Q2_0: (64, 18)}
+
+
+def dequant_blocks(ggml_type: int, raw: np.ndarray) -> np.ndarray:
+    """f32 values of whole Q4_K / Q6_K / Q2_0 blocks (crates/infr-gguf/src/dequant.rs:11-51, the factored decode of
+    :311-331 and :361-385 and the codebook arm :1003-1019): out = (d * sc) * code + (dmin * -m), every product and the
+    sum rounded to f32 on its own.  Host side only: one embedding row per token of a file whose token_embd is
+    quantised (what a Q4_K_M file ships); the Linears never leave the device."""
+    be, bb = _BLOCK[ggml_type]
+    blk = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1, bb)
+    nb = blk.shape[0]
+    f32 = np.float32
+    out = np.empty((nb, be), f32)
+    if ggml_type == GGML_Q4_K:
+        d = blk[:, 0:2].copy().view(np.float16).astype(f32)      # [nb, 1]
+        dmin = blk[:, 2:4].copy().view(np.float16).astype(f32)
+        sc_b, qs = blk[:, 4:16].astype(np.int32), blk[:, 16:144]
+
+        def k4(j):  # get_scale_min_k4 (dequant.rs:73-83)
+            if j < 4:
+                return sc_b[:, j] & 63, sc_b[:, j + 4] & 63
+            return (sc_b[:, j + 4] & 0xF) | ((sc_b[:, j - 4] >> 6) << 4), (sc_b[:, j + 4] >> 4) | ((sc_b[:, j] >> 6) << 4)
+        for j in range(4):
+            for half, codes in ((0, qs[:, 32 * j:32 * j + 32] & 0xF), (1, qs[:, 32 * j:32 * j + 32] >> 4)):
+                sc, m = k4(2 * j + half)
+                s = d * sc.astype(f32)[:, None]
+                n = dmin * (-m).astype(f32)[:, None]
+                out[:, 64 * j + 32 * half:64 * j + 32 * half + 32] = s * codes.astype(f32) + n
+        return out.reshape(-1)
+    if ggml_type == GGML_Q6_K:
+        ql, qh = blk[:, 0:128], blk[:, 128:192]
+        scales = blk[:, 192:208].copy().view(np.int8).astype(np.int32)
+        d = blk[:, 208:210].copy().view(np.float16).astype(f32)
+        for half in range(2):
+            lo0, lo1 = ql[:, 64 * half:64 * half + 32], ql[:, 64 * half + 32:64 * half + 64]
+            h = qh[:, 32 * half:32 * half + 32]
+            codes = [(lo0 & 0xF) | ((h & 3) << 4), (lo1 & 0xF) | (((h >> 2) & 3) << 4), (lo0 >> 4) | (((h >> 4) & 3) << 4),
+                     (lo1 >> 4) | (((h >> 6) & 3) << 4)]
+            for k in range(4):
+                s16 = np.repeat(scales[:, 8 * half + 2 * k:8 * half + 2 * k + 2], 16, axis=1)  # the scale of l is scales[is + 2k], is = l / 16
+                sc = d * s16.astype(f32)
+                mn = d * (-32 * s16).astype(f32)
+                out[:, 128 * half + 32 * k:128 * half + 32 * k + 32] = sc * codes[k].astype(f32) + mn
+        return out.reshape(-1)
+    if ggml_type == GGML_Q2_0:
+        d = blk[:, 0:2].copy().view(np.float16).astype(f32)
+        qs = blk[:, 2:18]
+        codes = np.stack([(qs >> (2 * k)) & 3 for k in range(4)], axis=2).reshape(nb, 64).astype(np.int32)  # element j: byte j / 4, bits 2 (j % 4)
+        out[:] = (codes - 1).astype(f32) * d
+        return out.reshape(-1)
+    raise BackendError(-2, f"GGUF: no host decode for ggml type {ggml_type}")
+
+
 def _f32_row(g: GgufFile, name: str, row: int) -> np.ndarray:
-    """One row of an F32 / F16 tensor as f32 (the host-side embedding lookup: the backend reports no embed_gather)."""
+    """One row of a tensor as f32 (the host-side embedding lookup: the backend reports no embed_gather): F32, F16, or
+    the three block formats this backend runs, decoded on the host."""
     t = g.tensors[name]
     cols = t.dims[0]
     raw = g.data(name)
@@ -138,7 +192,13 @@ def _f32_row(g: GgufFile, name: str, row: int) -> np.ndarray:
         return raw.view(np.float32)[row * cols:(row + 1) * cols].copy()
     if t.ggml_type == GGML_F16:
         return raw.view(np.float16)[row * cols:(row + 1) * cols].astype(np.float32)
-    raise BackendError(-2, f"GGUF: embedding lookup from ggml type {t.ggml_type} is not built (F32 and F16 are)")
+    if t.ggml_type in _BLOCK:
+        be, bb = _BLOCK[t.ggml_type]
+        if cols % be:
+            raise BackendError(-1, f"GGUF: '{name}' has rows of {cols} elements, not whole {be}-element blocks")
+        bpr = cols // be * bb
+        return dequant_blocks(t.ggml_type, raw[row * bpr:(row + 1) * bpr])
+    raise BackendError(-2, f"GGUF: embedding lookup from ggml type {t.ggml_type} is not built (F32, F16, Q4_K, Q6_K and Q2_0 are)")
 
 
 @dataclass

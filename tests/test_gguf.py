@@ -134,3 +134,22 @@ def test_malformed_files_are_errors_not_faults(tmp_path):
     _expect(p, infr_b200.E_INVALID, "nested deeper")
     with pytest.raises(infr_b200.BackendError):
         GgufFile(tmp_path / "does-not-exist.gguf")
+
+
+@pytest.mark.parametrize("ggml_type,dt,cols", [(GGML_Q4_K, Q4K, 512), (GGML_Q6_K, Q6K, 768), (42, 27, 320)])
+def test_quantised_embedding_rows_decode_like_the_cpu(tmp_path, ggml_type, dt, cols):
+    """A Q4_K_M file ships token_embd in a block format: the host-side lookup decodes one row per token
+    (gguf_file.dequant_blocks), bit for bit what the CPU restatement of dequant.rs gives - seeded weights and raw
+    random blocks (every scale / min bit pattern)."""
+    from infr_b200 import gguf_file
+    from oracle.cpu_oracle import Oracle
+
+    orc = Oracle()
+    for raw in (synth.weight(dt, 6, cols, seed=9), synth.random_blocks(dt, 6 * cols, 10)):
+        want = orc.dequant(dt, raw).reshape(6, cols)
+        np.testing.assert_array_equal(gguf_file.dequant_blocks(ggml_type, raw).view(np.uint32), want.reshape(-1).view(np.uint32))
+        p = tmp_path / f"e{ggml_type}.gguf"
+        gw.write_gguf(p, [("general.architecture", gw.STR, "llama")], [("token_embd.weight", (cols, 6), ggml_type, raw)])
+        with GgufFile(p) as g:
+            for row in (0, 3, 5):
+                np.testing.assert_array_equal(gguf_file._f32_row(g, "token_embd.weight", row).view(np.uint32), want[row].view(np.uint32))

@@ -180,29 +180,51 @@ __device__ __forceinline__ void slice_q6k(const uint8_t *sl, int nblk, int gb0, 
     }
 }
 
+// Q2_0: one LANE per 64-element block (a warp step is 32 blocks), so that the block's scale, its 18 bytes and the
+// unpacking are fetched and done once per 64 elements: five aligned 32-bit reads cover the block wherever its even
+// address falls, a funnel shift lines the four code words up.  A code word holds 16 two-bit codes; masking it at
+// shifts 0 / 2 / 4 / 6 gives the codes of elements {0,4,8,12}, {1,5,9,13}, ... as bytes, which the staged activations
+// are permuted to match.  Staged activations are laid out [quarter][block] in 16-byte units, so the lanes of a warp
+// (consecutive blocks) read consecutive units.  Per 32-element group: (sum of code * x) - (sum of x), one float
+// multiply-add with the group's two scales (crates/infr-cpu/src/kernels.rs:5641-5668).
 template <int M>
 __device__ __forceinline__ void slice_q2_0(const uint8_t *sl, int nblk, int gb0, int nb, int in_f, const int8_t *s_qa,
                                            const float *s_d, const int32_t *s_bs, int lane, float (&acc)[M]) {
-    const int g = lane >> 2, q = lane & 3;
     const int ns = nb * 2;
-#pragma unroll 2
-    for (int b0 = 0; b0 < nblk; b0 += 8) {
-        const int bl = b0 + g;
+    for (int b0 = 0; b0 < nblk; b0 += 32) {
+        const int bl = b0 + lane;
         if (bl < nblk) {
             const int b = gb0 + bl;
-            const int s = 2 * b + (q >> 1);
             const uint8_t *blk = sl + bl * 18;
-            const float dw = h2f(lds_u16(blk));
-            const uint32_t w = lds_u32_a2(blk + 2 + q * 4);
+            const uint32_t mis = (uint32_t)(smem_u32(blk) & 2u);  // the block starts on a 4-byte boundary, or 2 past one
+            const uint32_t *wp = reinterpret_cast<const uint32_t *>(blk - mis);
+            const uint32_t w0 = wp[0], w1 = wp[1], w2 = wp[2], w3 = wp[3], w4 = wp[4];
+            const uint32_t sh = 16u + 8u * mis;  // 16, or 32 (= take the upper word)
+            const float dw = h2f(w0 >> (8u * mis));
+            const uint32_t c[4] = {__funnelshift_rc(w0, w1, sh), __funnelshift_rc(w1, w2, sh), __funnelshift_rc(w2, w3, sh),
+                                   __funnelshift_rc(w3, w4, sh)};
+            int ip[M][2];
+#pragma unroll
+            for (int t = 0; t < M; t++) ip[t][0] = ip[t][1] = 0;
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const uint32_t m0 = c[q] & 0x03030303u, m1 = (c[q] >> 2) & 0x03030303u, m2 = (c[q] >> 4) & 0x03030303u, m3 = (c[q] >> 6) & 0x03030303u;
+#pragma unroll
+                for (int t = 0; t < M; t++) {
+                    const uint4 av = reinterpret_cast<const uint4 *>(s_qa + (size_t)t * in_f)[q * nb + b];
+                    int v = dp4a_us(m0, (int)av.x, ip[t][q >> 1]);
+                    v = dp4a_us(m1, (int)av.y, v);
+                    v = dp4a_us(m2, (int)av.z, v);
+                    ip[t][q >> 1] = dp4a_us(m3, (int)av.w, v);
+                }
+            }
 #pragma unroll
             for (int t = 0; t < M; t++) {
-                const uint4 av = reinterpret_cast<const uint4 *>(s_qa + (size_t)t * in_f)[b * 4 + q];
-                int ip = dp4a_us(w & 0x03030303u, (int)av.x, 0);
-                ip = dp4a_us((w >> 2) & 0x03030303u, (int)av.y, ip);
-                ip = dp4a_us((w >> 4) & 0x03030303u, (int)av.z, ip);
-                ip = dp4a_us((w >> 6) & 0x03030303u, (int)av.w, ip);
-                const int v = ip - ((q & 1) ? 0 : s_bs[t * ns + s]);
-                acc[t] += dw * s_d[t * ns + s] * (float)v;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int s = 2 * b + h;
+                    acc[t] += dw * s_d[t * ns + s] * (float)(ip[t][h] - s_bs[t * ns + s]);
+                }
             }
         }
     }
@@ -310,7 +332,7 @@ __global__ void __launch_bounds__(kStreamThreads, (M <= 2 ? 2 : 1))
                 o.y = __byte_perm(t01, t23, 0x7632);
                 o.z = __byte_perm(u01, u23, 0x5410);
                 o.w = __byte_perm(u01, u23, 0x7632);
-                reinterpret_cast<uint4 *>(s_qa + (size_t)t * in_f)[u] = o;
+                reinterpret_cast<uint4 *>(s_qa + (size_t)t * in_f)[(u & 3) * nb + (u >> 2)] = o;  // [quarter][block]
             }
         }
         for (int idx = tid; idx < M * nd; idx += nthr) {
